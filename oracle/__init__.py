@@ -1,0 +1,264 @@
+"""ctypes bindings of the CPU oracle (``oracle/qt_oracle.c``, ``oracle/cpu_gemv.c``).
+
+TEST INFRASTRUCTURE ONLY. The package ``quintrit_b200`` never imports this module; only ``tests/``, the smoke check and
+the CPU-baseline leg of ``bench.py`` do, and only to check or to time the CPU restatement of the reference algorithm.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB_PATH = os.path.join(_HERE, "_build", "libqt_oracle.so")
+_lib = None
+
+
+def build(force: bool = False) -> str:
+    """Compiles the oracle with ``make`` (gcc, a few seconds) and returns the path of the shared object."""
+    if force or not os.path.exists(_LIB_PATH) or any(
+        os.path.getmtime(os.path.join(_HERE, f)) > os.path.getmtime(_LIB_PATH)
+        for f in os.listdir(_HERE)
+        if f.endswith((".c", ".h"))
+    ):
+        subprocess.run(["make", "-C", _HERE] + (["-B"] if force else []), check=True, capture_output=True)
+    return _LIB_PATH
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        _lib = C.CDLL(build())
+        _declare(_lib)
+    return _lib
+
+
+_u8p, _i8p, _i32p, _i64p, _f32p = (C.POINTER(t) for t in (C.c_uint8, C.c_int8, C.c_int32, C.c_int64, C.c_float))
+_sz = C.c_size_t
+
+
+def _declare(l: C.CDLL) -> None:
+    l.qto_pack_5trits.restype = C.c_uint8
+    l.qto_pack_5trits.argtypes = [_i8p]
+    l.qto_byte_to_trits.argtypes = [C.c_uint8, _i8p]
+    for name in ("qto_planar_row_bytes", "qto_tile_row_bytes"):
+        getattr(l, name).restype = _sz
+        getattr(l, name).argtypes = [_sz]
+    l.qto_column_activation_index.restype = _sz
+    l.qto_column_activation_index.argtypes = [_sz, _sz, _sz]
+    l.qto_pack_planar.argtypes = [_i8p, _sz, _sz, _u8p]
+    l.qto_unpack_planar.argtypes = [_u8p, _sz, _sz, _i8p]
+    l.qto_tile32.argtypes = [_u8p, _sz, _sz, _u8p]
+    l.qto_gemv_bruteforce.argtypes = [_i8p, _sz, _sz, _i8p, _i64p]
+    l.qto_gemv_planar.argtypes = [_u8p, _sz, _sz, _i8p, _i32p]
+    l.qto_gemv_lut_wide.argtypes = [_u8p, _sz, _sz, _i8p, _i32p]
+    l.qto_rescale.argtypes = [_i32p, _sz, C.c_float, C.c_float, _f32p]
+    l.qto_quantize_int8.restype = C.c_float
+    l.qto_quantize_int8.argtypes = [_f32p, _sz, _i8p]
+    for name in ("qto_decode_i2_s", "qto_decode_tq2_0", "qto_decode_tq1_0"):
+        getattr(l, name).restype = C.c_int
+        getattr(l, name).argtypes = [_u8p, _sz, _sz, _sz, _i8p]
+    l.qto_encode_i2_s.restype = C.c_int
+    l.qto_encode_i2_s.argtypes = [_i8p, _sz, _sz, _u8p]
+    l.qto_decode_q2_0.restype = C.c_long
+    l.qto_decode_q2_0.argtypes = [_u8p, _sz, _sz, _sz, _i8p, _f32p]
+    l.qto_uniform_block_scale.restype = C.c_int
+    l.qto_uniform_block_scale.argtypes = [C.c_int, _u8p, _sz, _f32p]
+    l.qto_half_to_f32.restype = C.c_float
+    l.qto_half_to_f32.argtypes = [C.c_uint16]
+    l.qto_cpu_has_avx512_vbmi.restype = C.c_int
+    l.qto_tile64_bytes.restype = _sz
+    l.qto_tile64_bytes.argtypes = [_sz, _sz]
+    l.qto_tile64.argtypes = [_u8p, _sz, _sz, _u8p]
+    l.qto_cpu_gemv_avx512.restype = C.c_int
+    l.qto_cpu_gemv_avx512.argtypes = [_u8p, _sz, _sz, _i8p, _i32p, C.c_int]
+    l.qto_cpu_gemv_portable.argtypes = [_u8p, _sz, _sz, _i8p, _i32p, C.c_int]
+
+
+def _p(a: np.ndarray, t):
+    return a.ctypes.data_as(t)
+
+
+def _c(a, dtype) -> np.ndarray:
+    return np.ascontiguousarray(a, dtype=dtype)
+
+
+# ---- packing -------------------------------------------------------------------------------------------------------
+
+def pack_5trits(t) -> int:
+    a = _c(t, np.int8)
+    assert a.size == 5
+    return int(lib().qto_pack_5trits(_p(a, _i8p)))
+
+
+def byte_to_trits(b: int) -> np.ndarray:
+    out = np.zeros(5, np.int8)
+    lib().qto_byte_to_trits(b, _p(out, _i8p))
+    return out
+
+
+def planar_row_bytes(cols: int) -> int:
+    return int(lib().qto_planar_row_bytes(cols))
+
+
+def tile_row_bytes(cols: int) -> int:
+    return int(lib().qto_tile_row_bytes(cols))
+
+
+def column_activation_index(cols: int, c: int, p: int) -> int:
+    return int(lib().qto_column_activation_index(cols, c, p))
+
+
+def pack_planar(trits, rows: int, cols: int) -> np.ndarray:
+    t = _c(trits, np.int8).reshape(-1)
+    assert t.size == rows * cols
+    out = np.zeros(rows * planar_row_bytes(cols), np.uint8)
+    lib().qto_pack_planar(_p(t, _i8p), rows, cols, _p(out, _u8p))
+    return out
+
+
+def unpack_planar(packed, rows: int, cols: int) -> np.ndarray:
+    p = _c(packed, np.uint8).reshape(-1)
+    assert p.size >= rows * planar_row_bytes(cols)
+    out = np.zeros(rows * cols, np.int8)
+    lib().qto_unpack_planar(_p(p, _u8p), rows, cols, _p(out, _i8p))
+    return out.reshape(rows, cols)
+
+
+def tile32(planar, rows: int, cols: int) -> np.ndarray:
+    assert rows % 32 == 0
+    p = _c(planar, np.uint8).reshape(-1)
+    out = np.zeros(rows * tile_row_bytes(cols), np.uint8)
+    lib().qto_tile32(_p(p, _u8p), rows, cols, _p(out, _u8p))
+    return out
+
+
+# ---- GEMV ----------------------------------------------------------------------------------------------------------
+
+def gemv_bruteforce(trits, rows: int, cols: int, act) -> np.ndarray:
+    t = _c(trits, np.int8).reshape(-1)
+    a = _c(act, np.int8)
+    assert t.size == rows * cols and a.size == cols
+    out = np.zeros(rows, np.int64)
+    lib().qto_gemv_bruteforce(_p(t, _i8p), rows, cols, _p(a, _i8p), _p(out, _i64p))
+    return out
+
+
+def gemv_planar(planar, rows: int, cols: int, act) -> np.ndarray:
+    p = _c(planar, np.uint8).reshape(-1)
+    a = _c(act, np.int8)
+    assert p.size >= rows * planar_row_bytes(cols) and a.size == cols
+    out = np.zeros(rows, np.int32)
+    lib().qto_gemv_planar(_p(p, _u8p), rows, cols, _p(a, _i8p), _p(out, _i32p))
+    return out
+
+
+def gemv_lut_wide(tiled, rows: int, cols: int, act) -> np.ndarray:
+    t = _c(tiled, np.uint8).reshape(-1)
+    a = _c(act, np.int8)
+    assert rows % 32 == 0 and t.size >= rows * tile_row_bytes(cols) and a.size == cols
+    out = np.zeros(rows, np.int32)
+    lib().qto_gemv_lut_wide(_p(t, _u8p), rows, cols, _p(a, _i8p), _p(out, _i32p))
+    return out
+
+
+def rescale(acc, weight_scale: float, act_scale: float) -> np.ndarray:
+    a = _c(acc, np.int32)
+    out = np.zeros(a.size, np.float32)
+    lib().qto_rescale(_p(a, _i32p), a.size, weight_scale, act_scale, _p(out, _f32p))
+    return out
+
+
+def quantize_int8(x):
+    xx = _c(x, np.float32)
+    out = np.zeros(xx.size, np.int8)
+    s = lib().qto_quantize_int8(_p(xx, _f32p), xx.size, _p(out, _i8p))
+    return out, np.float32(s)
+
+
+# ---- decoders ------------------------------------------------------------------------------------------------------
+
+def _decode(fn, data, rows, cols):
+    d = _c(data, np.uint8).reshape(-1)
+    out = np.zeros(rows * cols, np.int8)
+    rc = fn(_p(d, _u8p), d.size, rows, cols, _p(out, _i8p))
+    if rc != 0:
+        raise ValueError("payload does not fit the shape")
+    return out.reshape(rows, cols)
+
+
+def decode_i2_s(data, rows, cols):
+    return _decode(lib().qto_decode_i2_s, data, rows, cols)
+
+
+def decode_tq2_0(data, rows, cols):
+    return _decode(lib().qto_decode_tq2_0, data, rows, cols)
+
+
+def decode_tq1_0(data, rows, cols):
+    return _decode(lib().qto_decode_tq1_0, data, rows, cols)
+
+
+def encode_i2_s(trits, rows, cols):
+    t = _c(trits, np.int8).reshape(-1)
+    out = np.zeros(rows * cols // 4, np.uint8)
+    if lib().qto_encode_i2_s(_p(t, _i8p), rows, cols, _p(out, _u8p)) != 0:
+        raise ValueError("cols must be a multiple of 128")
+    return out
+
+
+def decode_q2_0(data, rows, cols):
+    d = _c(data, np.uint8).reshape(-1)
+    trits = np.zeros(rows * cols, np.int8)
+    scales = np.zeros(max(rows * cols // 64, 1), np.float32)
+    rc = lib().qto_decode_q2_0(_p(d, _u8p), d.size, rows, cols, _p(trits, _i8p), _p(scales, _f32p))
+    if rc == -1 and (cols == 0 or cols % 64 != 0 or d.size != rows * cols // 64 * 18):
+        raise ValueError("payload does not fit the shape")
+    if rc < 0:
+        raise ValueError(f"Q2_0 weight {-rc - 1} uses code 3")
+    return trits.reshape(rows, cols), scales[: rows * cols // 64]
+
+
+def uniform_block_scale(ggml_type: int, data):
+    d = _c(data, np.uint8).reshape(-1)
+    s = C.c_float(0)
+    ok = lib().qto_uniform_block_scale(ggml_type, _p(d, _u8p), d.size, C.byref(s))
+    return np.float32(s.value) if ok else None
+
+
+def half_to_f32(h: int) -> np.float32:
+    return np.float32(lib().qto_half_to_f32(h))
+
+
+# ---- timed CPU baseline ---------------------------------------------------------------------------------------------
+
+def cpu_has_avx512_vbmi() -> bool:
+    return bool(lib().qto_cpu_has_avx512_vbmi())
+
+
+def tile64(planar, rows: int, cols: int) -> np.ndarray:
+    p = _c(planar, np.uint8).reshape(-1)
+    out = np.zeros(lib().qto_tile64_bytes(rows, cols), np.uint8)
+    lib().qto_tile64(_p(p, _u8p), rows, cols, _p(out, _u8p))
+    return out
+
+
+def cpu_gemv_avx512(tiled64, rows: int, cols: int, act, threads: int, out=None) -> np.ndarray:
+    t = tiled64 if isinstance(tiled64, np.ndarray) and tiled64.dtype == np.uint8 and tiled64.flags.c_contiguous else _c(tiled64, np.uint8)
+    a = _c(act, np.int8)
+    if out is None:
+        out = np.zeros(rows, np.int32)
+    if lib().qto_cpu_gemv_avx512(_p(t, _u8p), rows, cols, _p(a, _i8p), _p(out, _i32p), threads) != 0:
+        raise RuntimeError("this CPU has no AVX-512 VBMI")
+    return out
+
+
+def cpu_gemv_portable(planar, rows: int, cols: int, act, threads: int, out=None) -> np.ndarray:
+    p = planar if isinstance(planar, np.ndarray) and planar.dtype == np.uint8 and planar.flags.c_contiguous else _c(planar, np.uint8)
+    a = _c(act, np.int8)
+    if out is None:
+        out = np.zeros(rows, np.int32)
+    lib().qto_cpu_gemv_portable(_p(p, _u8p), rows, cols, _p(a, _i8p), _p(out, _i32p), threads)
+    return out
