@@ -1,0 +1,310 @@
+#!/usr/bin/env python
+"""Benchmark of the B200 ternary decode path.
+
+Workload "falcon3_10b_gemv_sweep": the 280 ternary projections of one Falcon3-10B decode step at batch 1 (40 layers x
+q, k, v, o, gate, up, down), each with its own seeded int8 activation vector, weights resident in HBM (1.9 GB, far
+beyond L2). One step = one pass over all 280 projections = the velurex bytes of one decoded token.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--layers L]
+
+Prints ONE JSON line (rank 0). With --impl reference the CPU restatement of the reference's AVX-512 kernel is timed on
+the host cores instead (the reference itself is Rust and cannot be built here).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+from quintrit_b200 import synth  # noqa: E402
+
+CONFIG_ID = 0
+BYTES_PER_WEIGHT = 0.2  # 1.60 bits per weight: the algorithmic bytes of a velurex GEMV
+
+
+def sweep_shapes(layers: int):
+    return [(l, p, n, k) for l in range(layers) for p, (n, k) in enumerate(synth.falcon3_10b_shapes())]
+
+
+def shard_rows(n: int, rank: int, world: int):
+    """Rows [r0, r1) of a projection that rank `rank` of `world` streams: whole 32-row tiles, remainder to the low ranks."""
+    tiles = -(-n // 32)
+    t0 = tiles * rank // world
+    t1 = tiles * (rank + 1) // world
+    return min(t0 * 32, n), min(t1 * 32, n)
+
+
+def activations_for(layer: int, proj: int, cols: int) -> np.ndarray:
+    x = synth.normal_f32(synth.seed_for(CONFIG_ID, layer, proj, 2), cols)
+    return synth.quantize_int8_np(x)[0]
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons in the background while the timed region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                                          "-i", str(self.gpu_index)], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        try:
+            for line in open(self.path):
+                f = [x.strip() for x in line.split(",")]
+                if len(f) < 9:
+                    continue
+                try:
+                    sm.append(float(f[1]))
+                    mx.append(float(f[2]))
+                except ValueError:
+                    continue
+                for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        if sm:
+            out.update(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
+        return out
+
+
+def cpu_sweep(layers_sample: int, threads: int, reps: int = 9):
+    """Times the CPU restatement of the reference's AVX-512 kernel (oracle/cpu_gemv.c) on the first `layers_sample`
+    layers of the sweep: best of `reps` passes, averaged over two rounds with the second in reverse order
+    (the reference's method, docs/benchmarks.md:45-59). Returns (Gweights/s, results per projection, kind)."""
+    import oracle
+
+    probs = []
+    use512 = oracle.cpu_has_avx512_vbmi()
+    for (l, p, n, k) in sweep_shapes(layers_sample):
+        planar = synth.torch_planar(synth.seed_for(CONFIG_ID, l, p, 0), n, k, "cpu").numpy()
+        w = oracle.tile64(planar, n, k) if use512 else planar
+        probs.append((n, k, w, activations_for(l, p, k), np.zeros(n, np.int32)))
+    weights = sum(n * k for n, k, *_ in probs)
+    fn = oracle.cpu_gemv_avx512 if use512 else oracle.cpu_gemv_portable
+
+    def one_pass(order):
+        t0 = time.perf_counter()
+        for i in order:
+            n, k, w, a, o = probs[i]
+            fn(w, n, k, a, threads, out=o)
+        return time.perf_counter() - t0
+
+    fwd = list(range(len(probs)))
+    one_pass(fwd)
+    best1 = min(one_pass(fwd) for _ in range(reps))
+    best2 = min(one_pass(fwd[::-1]) for _ in range(reps))
+    secs = 0.5 * (best1 + best2)
+    return weights / secs / 1e9, [p[4] for p in probs], ("avx512_vbmi" if use512 else "portable")
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        return float(json.load(open(path))["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+def run_reference(args, rank: int, world: int):
+    """--impl reference: the CPU path, timed on the host cores (rank 0 only)."""
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    sample_layers = min(args.layers, 2)
+    steps = max(1, args.steps)
+    vals = []
+    kind = "port"
+    for _ in range(min(steps, 3)):
+        g, _, isa = cpu_sweep(sample_layers, threads, reps=3)
+        vals.append(g)
+    value = max(vals)
+    weights_sample = sum(n * k for _, _, n, k in sweep_shapes(sample_layers))
+    line = {
+        "impl": "reference", "metric": "gemv_gweights_per_s", "value": round(value, 2), "unit": "Gweights/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(weights_sample / value / 1e6, 3), "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "int8xternary->int32", "data": "synthetic",
+        "config": {"workload": "falcon3_10b_gemv_sweep", "layers": args.layers, "projections": 7 * args.layers, "batch": 1},
+        "cpu_baseline": {"value": round(value, 2), "unit": "Gweights/s", "cores": threads, "kind": kind,
+                         "sample": f"first {sample_layers} of {args.layers} layers ({weights_sample / 1e6:.0f} M weights), {isa} kernel, "
+                                   "best of 3 passes averaged over forward and reverse order"},
+        "e2e": {"value": round(value, 2), "unit": "Gweights/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args, rank: int, world: int, local_rank: int):
+    import torch
+
+    import quintrit_b200 as q
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback); use --impl reference for the CPU path")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist  # noqa: F811
+
+        dist.init_process_group("nccl", device_id=dev)
+
+    # ---- build the sweep: weights generated on the device, transcoded by the library ----
+    t_setup = time.time()
+    mats, acts, shapes = [], [], []
+    for (l, p, n, k) in sweep_shapes(args.layers):
+        r0, r1 = shard_rows(n, rank, world)
+        if r1 <= r0:
+            continue
+        planar = synth.torch_planar(synth.seed_for(CONFIG_ID, l, p, 0), r1 - r0, k, dev, row0=r0).cpu().numpy()
+        mats.append(q.Matrix(planar, r1 - r0, k, device=local_rank))
+        acts.append(activations_for(l, p, k))
+        shapes.append((l, p, r1 - r0, k))
+    torch.cuda.empty_cache()
+    plan = q.Plan(mats)
+    weights_local = sum(n * k for _, _, n, k in shapes)
+    weights_total = sum(n * k for _, _, n, k in sweep_shapes(args.layers))
+    act_host = torch.from_numpy(plan.pack_activations(acts)).pin_memory()
+    out_host = torch.zeros(plan.out_total, dtype=torch.int32).pin_memory()
+    act_np, out_np = act_host.numpy(), out_host.numpy()
+    t_setup = time.time() - t_setup
+
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident timing: activations already in HBM ----
+    plan.run(act_np, out_np)  # also places the activations on the device
+    first = out_np.copy()
+    for _ in range(max(3, args.warmup)):
+        plan.launch(stream)
+    sampler = ClockSampler(local_rank)
+    barrier()
+    sampler.start()
+    q.launch_count(reset=True)
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+    ev[0].record()
+    for i in range(args.steps):
+        plan.launch(stream)
+        ev[i + 1].record()
+    barrier()
+    launches = q.launch_count()
+    total_ms = ev[0].elapsed_time(ev[-1])
+    per_launch_ms = [ev[i].elapsed_time(ev[i + 1]) for i in range(args.steps)]
+    clocks = sampler.stop()
+
+    # ---- end to end through the C ABI with host buffers: H2D activations, kernel, D2H results, every step ----
+    for _ in range(2):
+        plan.run(act_np, out_np)
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        plan.run(act_np, out_np)
+    torch.cuda.synchronize()
+    e2e_ms = (time.perf_counter() - t0) * 1e3
+    same = bool(np.array_equal(first, out_np))
+
+    if dist is not None:
+        t = torch.tensor([total_ms, e2e_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms, e2e_ms = t.tolist()
+        ok = torch.tensor([1 if same else 0], device=dev)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        same = bool(ok.item())
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+
+    ms_per_step = total_ms / args.steps
+    value = weights_total / (ms_per_step * 1e-3) / 1e9
+    e2e_value = weights_total / (e2e_ms / args.steps * 1e-3) / 1e9
+    peak, peak_kind = measured_peaks()
+    kernel_ms = statistics.mean(per_launch_ms)
+    achieved = weights_local * BYTES_PER_WEIGHT / (kernel_ms * 1e-3) / 1e9
+    line = {
+        "metric": "gemv_gweights_per_s", "value": round(value, 1), "unit": "Gweights/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(3, args.warmup), "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "int8xternary->int32", "data": "synthetic",
+        "config": {"workload": "falcon3_10b_gemv_sweep", "layers": args.layers, "projections": 7 * args.layers, "batch": 1,
+                   "weights": weights_total, "l2": "inputs (1.9 GB of weights per pass) exceed L2", "sharding": f"rows/{world}, no collective"},
+        "tokens_per_s_gemv_only": round(1e3 / ms_per_step, 1),
+        "roofline_nominal_8tbs_frac": round(weights_total * BYTES_PER_WEIGHT / (ms_per_step * 1e-3) / (world * 8e12), 4),
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 4),
+                     "traffic": None, "peak_kind": peak_kind, "kernel": "gemv_lut_kernel", "launch_ms": round(kernel_ms, 4)},
+        "e2e": {"value": round(e2e_value, 1), "unit": "Gweights/s", "h2d_bytes_per_step": int(plan.act_total), "d2h_bytes_per_step": int(plan.out_total * 4),
+                "ms_per_step": round(e2e_ms / args.steps, 4)},
+        "gpu_launches": int(launches),
+        "clocks": clocks,
+        "deterministic": same,
+        "setup_s": round(t_setup, 1),
+    }
+    if world == 1 and not args.no_cpu:
+        threads = os.cpu_count() or 1
+        sample_layers = min(args.layers, 2)
+        g, cpu_out, isa = cpu_sweep(sample_layers, threads, reps=5)
+        res = plan.split_results(first)
+        n_check = len(sweep_shapes(sample_layers))
+        parity = all(np.array_equal(res[i], cpu_out[i]) for i in range(n_check))
+        line["cpu_baseline"] = {"value": round(g, 2), "unit": "Gweights/s", "cores": threads, "kind": "port",
+                                "sample": f"first {sample_layers} of {args.layers} layers, {isa} kernel, best of 5 passes averaged over forward and reverse order"}
+        line["parity_vs_cpu"] = {"projections_checked": n_check, "bit_exact": bool(parity)}
+    print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=40)
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+    else:
+        run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,147 @@
+/*
+ * quintrit_b200.h - C ABI of libquintrit_b200.so, the B200 (sm_100a) device for quintrit's ternary decode path.
+ *
+ * Conventions are those of the reference's C API (rust/crates/quintrit-c/include/quintrit.h:10-33): every fallible
+ * function returns an int status (0 = QUINTRIT_OK, the same numeric codes as quintrit.h:73-88), results go through
+ * out-parameters, the last error message is kept per thread, versioned structs start with a uint32_t struct_size,
+ * handles are opaque, tagged with a magic word and released by the matching *_free (NULL allowed). No function
+ * throws, aborts or prints. There is no CPU fallback: without a usable CUDA device every compute entry returns
+ * QUINTRIT_ERR_DEVICE or QUINTRIT_ERR_UNSUPPORTED.
+ *
+ * Plain C99: pointers and sizes only.
+ */
+#ifndef QUINTRIT_B200_H
+#define QUINTRIT_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#ifndef QUINTRIT_OK /* the codes of quintrit.h:73-88, repeated so that this header stands alone */
+#define QUINTRIT_OK 0
+#define QUINTRIT_ERR_NULL_POINTER 1
+#define QUINTRIT_ERR_INVALID_ARGUMENT 2
+#define QUINTRIT_ERR_INVALID_SHAPE 3
+#define QUINTRIT_ERR_BUFFER_TOO_SMALL 4
+#define QUINTRIT_ERR_INVALID_VALUE 5
+#define QUINTRIT_ERR_UNSUPPORTED 6
+#define QUINTRIT_ERR_IO 7
+#define QUINTRIT_ERR_FORMAT 8
+#define QUINTRIT_ERR_NOT_FOUND 9
+#define QUINTRIT_ERR_MODEL 10
+#define QUINTRIT_ERR_CONTEXT_OVERFLOW 11
+#define QUINTRIT_ERR_BUSY 12
+#define QUINTRIT_ERR_INTERNAL 13
+#define QUINTRIT_ERR_INVALID_HANDLE 14
+#define QUINTRIT_ERR_DEVICE 15
+#endif
+
+#define QUINTRIT_B200_ABI_VERSION 1
+
+/* ---- errors and version: replaces quintrit.h:91-110 (quintrit-c/src/error.rs:64-81, 149-157) ---- */
+const char* quintrit_status_string(int status);
+int quintrit_last_error_code(void);
+const char* quintrit_last_error_message(void);
+const char* quintrit_b200_version(void);
+uint32_t quintrit_b200_abi_version(void);
+
+/* ---- devices: same names, struct and meaning as quintrit.h:490-513 (quintrit-c/src/cuda.rs:20-104), except that
+ * `supported` is 1 only for compute capability 10.0 (the kernels are built for sm_100a alone). ---- */
+typedef struct quintrit_cuda_device_info {
+    uint32_t struct_size;
+    uint32_t index;
+    int32_t compute_major;
+    int32_t compute_minor;
+    uint32_t sm_count;
+    uint32_t supported;
+    uint64_t total_memory;
+    uint64_t l2_cache_bytes;
+    char name[64];
+} quintrit_cuda_device_info_t;
+
+int quintrit_cuda_device_count(uint32_t* out_count);
+int quintrit_cuda_device_info(uint32_t index, quintrit_cuda_device_info_t* out_info);
+
+/* ---- host-side layout helpers: replace quintrit-cuda/src/pack.rs:24-48 (blocks_per_row, row_bytes, pack_planar),
+ * i.e. quintrit-core/src/pack.rs:103-131. A trit outside {-1,0,1} gives QUINTRIT_ERR_INVALID_VALUE (as
+ * quintrit_pack_matrix, quintrit.h:196-202). ---- */
+size_t quintrit_b200_planar_row_bytes(size_t cols);
+int quintrit_b200_pack_planar(const int8_t* trits, size_t trits_len, size_t rows, size_t cols, uint8_t* out, size_t out_capacity);
+
+/* ---- a ternary matrix resident in HBM ---- */
+typedef struct quintrit_b200_matrix quintrit_b200_matrix_t;
+
+/* Source encodings accepted by quintrit_b200_matrix_upload; the numbers are the GGML type ids of
+ * quintrit-format/src/gguf.rs (I2_S 36, TQ1_0 34, TQ2_0 35), 0 stands for planar velurex bytes. */
+#define QUINTRIT_B200_SRC_PLANAR 0
+#define QUINTRIT_B200_SRC_TQ1_0 34
+#define QUINTRIT_B200_SRC_TQ2_0 35
+#define QUINTRIT_B200_SRC_I2_S 36
+
+/*
+ * Copies an encoded rows x cols ternary matrix from host memory to the device and transcodes it THERE into the
+ * streaming velurex layout the GEMV kernel reads (still five trits per byte, 1.60 bits per weight). Replaces the host
+ * transcode + upload of quintrit-runtime/src/gpu.rs:120-138, 212-219 (quintrit-format/src/transcoder.rs:165-200 then
+ * Device::upload). `data` holds the tensor payload exactly as the GGUF file stores it (for I2_S without the trailing
+ * scale, for TQ1_0 / TQ2_0 with the per-block f16 scales, which are ignored here) or planar bytes of
+ * quintrit_b200_planar_row_bytes(cols) per row. On failure *out_matrix is NULL.
+ */
+int quintrit_b200_matrix_upload(uint32_t device_index, int32_t source, const uint8_t* data, size_t data_len, size_t rows,
+                                size_t cols, quintrit_b200_matrix_t** out_matrix);
+int quintrit_b200_matrix_free(quintrit_b200_matrix_t* matrix);
+/* rows, cols and the bytes the matrix occupies in HBM (padding included). Any out pointer may be NULL. */
+int quintrit_b200_matrix_info(const quintrit_b200_matrix_t* matrix, size_t* out_rows, size_t* out_cols, size_t* out_device_bytes);
+/* Reads the matrix back as planar bytes (inverse of the device transcode; for tests and round trips). */
+int quintrit_b200_matrix_download_planar(const quintrit_b200_matrix_t* matrix, uint8_t* out, size_t out_capacity);
+
+/*
+ * Exact integer GEMV with host buffers: out[i] = sum_j W[i][j] * activations[j]. Replaces quintrit_gemv_i32
+ * (quintrit.h:214-216) for a device matrix and Gemv::plain + upload/download of the reference's GPU launcher
+ * (quintrit-cuda/src/gemv.rs:191-226). Copies the activations to the device, runs the kernel, copies the int32 sums
+ * back and waits. The full int8 range is exact; cols must not exceed 131072 (quintrit.h:211).
+ */
+int quintrit_b200_gemv_i32(const quintrit_b200_matrix_t* matrix, const int8_t* activations, size_t activations_len,
+                           int32_t* out, size_t out_capacity);
+/* As above with out[i] = scale * sum (quintrit_gemv_f32, quintrit.h:222-224; quintrit-runtime/src/layer.rs:143-150:
+ * pass weight_scale / act_scale). */
+int quintrit_b200_gemv_f32(const quintrit_b200_matrix_t* matrix, const int8_t* activations, size_t activations_len,
+                           float scale, float* out, size_t out_capacity);
+/*
+ * The same GEMV on device pointers, enqueued on `stream` (a cudaStream_t, NULL = default stream) without waiting:
+ * the device seam of quintrit-cuda/src/gemv.rs:191-226 (Gemv::plain). d_activations: cols int8; d_out: rows int32.
+ */
+int quintrit_b200_gemv_i32_device(const quintrit_b200_matrix_t* matrix, const int8_t* d_activations, int32_t* d_out, void* stream);
+
+/* ---- a list of GEMVs executed as one persistent launch (one decode step's projections) ---- */
+typedef struct quintrit_b200_plan quintrit_b200_plan_t;
+
+/*
+ * Builds a launch plan over `count` matrices of one device. Problem i multiplies matrices[i] with its own activation
+ * vector. The plan owns one device buffer for all activation vectors (concatenated, each padded to a multiple of 16
+ * bytes) and one for all int32 results (concatenated, each padded to a multiple of 4 values); the matrices must
+ * outlive the plan. There is no counterpart in the reference, which launches one kernel per projection
+ * (quintrit-runtime/src/gpu.rs:410-452); the plan exists because a B200 finishes a small projection faster than a
+ * launch can be issued.
+ */
+int quintrit_b200_plan_create(const quintrit_b200_matrix_t* const* matrices, size_t count, quintrit_b200_plan_t** out_plan);
+int quintrit_b200_plan_free(quintrit_b200_plan_t* plan);
+/* Offsets (in elements) of problem `index` inside the concatenated activation and result buffers, and their totals. */
+int quintrit_b200_plan_layout(const quintrit_b200_plan_t* plan, size_t index, size_t* out_act_offset, size_t* out_out_offset,
+                              size_t* out_act_total, size_t* out_out_total);
+/* Device pointers of the plan's activation (int8) and result (int32) buffers, for callers that fill them on the device. */
+int quintrit_b200_plan_buffers(const quintrit_b200_plan_t* plan, int8_t** out_d_activations, int32_t** out_d_results);
+/* Enqueues result clearing and the persistent GEMV kernel on `stream` (NULL = default); does not wait. */
+int quintrit_b200_plan_launch(quintrit_b200_plan_t* plan, void* stream);
+/* Host-buffer form: copies `activations` (act_total bytes) in, launches, copies out_total int32 back and waits. */
+int quintrit_b200_plan_run(quintrit_b200_plan_t* plan, const int8_t* activations, size_t activations_len, int32_t* out,
+                           size_t out_capacity);
+/* Kernel launches issued by this library on the calling thread since the last call with reset != 0 (counting aid). */
+uint64_t quintrit_b200_launch_count(int reset);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,249 @@
+"""ctypes host side of ``libquintrit_b200.so``.
+
+Names follow the reference's GPU crate: ``pack_planar`` / ``row_bytes`` (``rust/crates/quintrit-cuda/src/pack.rs:24-48``),
+``Matrix`` = an uploaded ``DeviceBuffer<u8>`` of planar weights plus its shape, ``Matrix.gemv_i32`` = ``Gemv::plain``
+(``rust/crates/quintrit-cuda/src/gemv.rs:191-226``) with upload and download, ``Matrix.forward`` =
+``TernaryGemvLayer::forward`` (``rust/crates/quintrit-runtime/src/layer.rs:123-177``).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from dataclasses import dataclass
+
+import numpy as np
+
+from . import build as _build
+
+SRC_PLANAR, SRC_TQ1_0, SRC_TQ2_0, SRC_I2_S = 0, 34, 35, 36
+
+_u8p, _i8p, _i32p, _f32p = (C.POINTER(t) for t in (C.c_uint8, C.c_int8, C.c_int32, C.c_float))
+_sz = C.c_size_t
+_lib = None
+
+
+class QuintritError(RuntimeError):
+    """A call into the C ABI returned a status other than QUINTRIT_OK."""
+
+    def __init__(self, code: int, message: str):
+        super().__init__(f"[{code}] {message}")
+        self.code = code
+        self.message = message
+
+
+class _DeviceInfoC(C.Structure):
+    _fields_ = [("struct_size", C.c_uint32), ("index", C.c_uint32), ("compute_major", C.c_int32), ("compute_minor", C.c_int32),
+                ("sm_count", C.c_uint32), ("supported", C.c_uint32), ("total_memory", C.c_uint64), ("l2_cache_bytes", C.c_uint64),
+                ("name", C.c_char * 64)]
+
+
+@dataclass
+class DeviceInfo:
+    index: int
+    compute_major: int
+    compute_minor: int
+    sm_count: int
+    supported: bool
+    total_memory: int
+    l2_cache_bytes: int
+    name: str
+
+
+def library_path() -> str:
+    return _build.LIB
+
+
+def load_library(build_if_missing: bool = True) -> C.CDLL:
+    """Loads the CUDA library; raises if it is absent and cannot be built (there is no fallback path)."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if build_if_missing and _build.needs_build():
+        _build.build()
+    if not os.path.exists(_build.LIB):
+        raise QuintritError(6, f"{_build.LIB} is missing: build it with `python -m quintrit_b200.build`")
+    l = C.CDLL(_build.LIB)
+    l.quintrit_status_string.restype = C.c_char_p
+    l.quintrit_last_error_message.restype = C.c_char_p
+    l.quintrit_b200_version.restype = C.c_char_p
+    l.quintrit_b200_abi_version.restype = C.c_uint32
+    l.quintrit_cuda_device_count.argtypes = [C.POINTER(C.c_uint32)]
+    l.quintrit_cuda_device_info.argtypes = [C.c_uint32, C.POINTER(_DeviceInfoC)]
+    l.quintrit_b200_planar_row_bytes.restype = _sz
+    l.quintrit_b200_planar_row_bytes.argtypes = [_sz]
+    l.quintrit_b200_pack_planar.argtypes = [_i8p, _sz, _sz, _sz, _u8p, _sz]
+    l.quintrit_b200_matrix_upload.argtypes = [C.c_uint32, C.c_int32, _u8p, _sz, _sz, _sz, C.POINTER(C.c_void_p)]
+    l.quintrit_b200_matrix_free.argtypes = [C.c_void_p]
+    l.quintrit_b200_matrix_info.argtypes = [C.c_void_p, C.POINTER(_sz), C.POINTER(_sz), C.POINTER(_sz)]
+    l.quintrit_b200_matrix_download_planar.argtypes = [C.c_void_p, _u8p, _sz]
+    l.quintrit_b200_gemv_i32.argtypes = [C.c_void_p, _i8p, _sz, _i32p, _sz]
+    l.quintrit_b200_gemv_f32.argtypes = [C.c_void_p, _i8p, _sz, C.c_float, _f32p, _sz]
+    l.quintrit_b200_gemv_i32_device.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
+    l.quintrit_b200_plan_create.argtypes = [C.POINTER(C.c_void_p), _sz, C.POINTER(C.c_void_p)]
+    l.quintrit_b200_plan_free.argtypes = [C.c_void_p]
+    l.quintrit_b200_plan_layout.argtypes = [C.c_void_p, _sz, C.POINTER(_sz), C.POINTER(_sz), C.POINTER(_sz), C.POINTER(_sz)]
+    l.quintrit_b200_plan_buffers.argtypes = [C.c_void_p, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p)]
+    l.quintrit_b200_plan_launch.argtypes = [C.c_void_p, C.c_void_p]
+    l.quintrit_b200_plan_run.argtypes = [C.c_void_p, _i8p, _sz, _i32p, _sz]
+    l.quintrit_b200_launch_count.restype = C.c_uint64
+    l.quintrit_b200_launch_count.argtypes = [C.c_int]
+    _lib = l
+    return l
+
+
+def _check(rc: int) -> None:
+    if rc != 0:
+        raise QuintritError(rc, load_library().quintrit_last_error_message().decode("utf-8", "replace"))
+
+
+def _p(a: np.ndarray, t):
+    return a.ctypes.data_as(t)
+
+
+def version() -> str:
+    return load_library().quintrit_b200_version().decode()
+
+
+def device_count() -> int:
+    n = C.c_uint32(0)
+    _check(load_library().quintrit_cuda_device_count(C.byref(n)))
+    return n.value
+
+
+def device_info(index: int = 0) -> DeviceInfo:
+    info = _DeviceInfoC()
+    info.struct_size = C.sizeof(_DeviceInfoC)
+    _check(load_library().quintrit_cuda_device_info(index, C.byref(info)))
+    return DeviceInfo(info.index, info.compute_major, info.compute_minor, info.sm_count, bool(info.supported), info.total_memory,
+                      info.l2_cache_bytes, info.name.decode("utf-8", "replace"))
+
+
+def launch_count(reset: bool = False) -> int:
+    return int(load_library().quintrit_b200_launch_count(1 if reset else 0))
+
+
+def row_bytes(cols: int) -> int:
+    """Bytes of one planar row (quintrit-cuda/src/pack.rs:29-32)."""
+    return int(load_library().quintrit_b200_planar_row_bytes(cols))
+
+
+def pack_planar(trits, rows: int, cols: int) -> np.ndarray:
+    """rows x cols trits -> planar velurex bytes (quintrit-cuda/src/pack.rs:42-48)."""
+    t = np.ascontiguousarray(trits, dtype=np.int8).reshape(-1)
+    out = np.zeros(rows * row_bytes(cols), np.uint8)
+    _check(load_library().quintrit_b200_pack_planar(_p(t, _i8p), t.size, rows, cols, _p(out, _u8p), out.size))
+    return out
+
+
+class Matrix:
+    """A ternary matrix resident in HBM in the stream layout."""
+
+    def __init__(self, data, rows: int, cols: int, source: int = SRC_PLANAR, device: int = 0):
+        d = np.ascontiguousarray(data, dtype=np.uint8).reshape(-1)
+        h = C.c_void_p()
+        _check(load_library().quintrit_b200_matrix_upload(device, source, _p(d, _u8p), d.size, rows, cols, C.byref(h)))
+        self._h, self.rows, self.cols, self.device = h, rows, cols, device
+
+    @classmethod
+    def from_trits(cls, trits, rows: int, cols: int, device: int = 0) -> "Matrix":
+        return cls(pack_planar(trits, rows, cols), rows, cols, SRC_PLANAR, device)
+
+    @property
+    def handle(self) -> C.c_void_p:
+        return self._h
+
+    @property
+    def device_bytes(self) -> int:
+        n = _sz(0)
+        _check(load_library().quintrit_b200_matrix_info(self._h, None, None, C.byref(n)))
+        return n.value
+
+    def download_planar(self) -> np.ndarray:
+        out = np.zeros(self.rows * row_bytes(self.cols), np.uint8)
+        _check(load_library().quintrit_b200_matrix_download_planar(self._h, _p(out, _u8p), out.size))
+        return out
+
+    def gemv_i32(self, activations) -> np.ndarray:
+        a = np.ascontiguousarray(activations, dtype=np.int8)
+        out = np.zeros(self.rows, np.int32)
+        _check(load_library().quintrit_b200_gemv_i32(self._h, _p(a, _i8p), a.size, _p(out, _i32p), out.size))
+        return out
+
+    def gemv_f32(self, activations, scale: float) -> np.ndarray:
+        a = np.ascontiguousarray(activations, dtype=np.int8)
+        out = np.zeros(self.rows, np.float32)
+        _check(load_library().quintrit_b200_gemv_f32(self._h, _p(a, _i8p), a.size, scale, _p(out, _f32p), out.size))
+        return out
+
+    def forward(self, activations, act_scale: float, weight_scale: float) -> np.ndarray:
+        """``TernaryGemvLayer::forward``: acc * (weight_scale / act_scale), zeros when act_scale <= 0."""
+        if not act_scale > 0:
+            return np.zeros(self.rows, np.float32)
+        return self.gemv_f32(activations, float(np.float32(weight_scale) / np.float32(act_scale)))
+
+    def gemv_i32_device(self, d_activations: int, d_out: int, stream: int = 0) -> None:
+        _check(load_library().quintrit_b200_gemv_i32_device(self._h, C.c_void_p(d_activations), C.c_void_p(d_out), C.c_void_p(stream)))
+
+    def free(self) -> None:
+        if self._h:
+            load_library().quintrit_b200_matrix_free(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+class Plan:
+    """Several GEMVs run as one persistent launch (one decode step's projections)."""
+
+    def __init__(self, matrices):
+        self.matrices = list(matrices)
+        arr = (C.c_void_p * len(self.matrices))(*[m.handle for m in self.matrices])
+        h = C.c_void_p()
+        _check(load_library().quintrit_b200_plan_create(arr, len(self.matrices), C.byref(h)))
+        self._h = h
+        ao, oo, at, ot = _sz(), _sz(), _sz(), _sz()
+        self.act_offsets, self.out_offsets = [], []
+        for i in range(len(self.matrices)):
+            _check(load_library().quintrit_b200_plan_layout(h, i, C.byref(ao), C.byref(oo), C.byref(at), C.byref(ot)))
+            self.act_offsets.append(ao.value)
+            self.out_offsets.append(oo.value)
+        self.act_total, self.out_total = at.value, ot.value
+
+    def pack_activations(self, acts) -> np.ndarray:
+        buf = np.zeros(self.act_total, np.int8)
+        for off, m, a in zip(self.act_offsets, self.matrices, acts):
+            buf[off:off + m.cols] = a
+        return buf
+
+    def split_results(self, out: np.ndarray):
+        return [out[off:off + m.rows] for off, m in zip(self.out_offsets, self.matrices)]
+
+    def buffers(self):
+        a, o = C.c_void_p(), C.c_void_p()
+        _check(load_library().quintrit_b200_plan_buffers(self._h, C.byref(a), C.byref(o)))
+        return a.value, o.value
+
+    def launch(self, stream: int = 0) -> None:
+        _check(load_library().quintrit_b200_plan_launch(self._h, C.c_void_p(stream)))
+
+    def run(self, activations: np.ndarray, out: np.ndarray | None = None) -> np.ndarray:
+        a = np.ascontiguousarray(activations, dtype=np.int8)
+        if out is None:
+            out = np.zeros(self.out_total, np.int32)
+        _check(load_library().quintrit_b200_plan_run(self._h, _p(a, _i8p), a.size, _p(out, _i32p), out.size))
+        return out
+
+    def free(self) -> None:
+        if self._h:
+            load_library().quintrit_b200_plan_free(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass

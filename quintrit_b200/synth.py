@@ -1,0 +1,114 @@
+"""Seeded synthetic inputs for the benchmark configurations (no dataset is involved anywhere).
+
+Generator: counter-based SplitMix64. Value ``i`` of a stream is ``mix(seed + (i + 1) * GAMMA)``; the 32 high bits are
+the uniform ``u``. Trits: ``u < 0.3 * 2^32 -> -1``, ``u < 0.6 * 2^32 -> +1``, else ``0`` (P = 0.3 / 0.3 / 0.4).
+Weight scale: ``0.5 + 1.5 * u / 2^32`` in fp32. Activations: N(0, 1) by Box-Muller on two uniforms in fp32, then the
+int8 absmax quantiser of the caller. Seeds: ``BASE ^ (config << 48) ^ (layer << 16) ^ (projection << 8) ^ stream`` with
+projection order q, k, v, o, gate, up, down = 0..6 and streams 0 = weights, 1 = scale, 2 = activation.
+
+The numpy functions are the definition; the torch functions compute the same integers on a CUDA device so that the
+9.5 G weights of a Falcon3-10B-shape sweep are generated in seconds (tests/test_synth.py checks they agree).
+"""
+from __future__ import annotations
+
+import numpy as np
+
+BASE_SEED = 0x5155494E54524954
+GAMMA = 0x9E3779B97F4A7C15
+M1 = 0xBF58476D1CE4E5B9
+M2 = 0x94D049BB133111EB
+T_NEG = int(0.3 * 2 ** 32)
+T_POS = int(0.6 * 2 ** 32)
+PROJECTIONS = ("q", "k", "v", "o", "gate", "up", "down")
+
+
+def falcon3_10b_shapes():
+    """(rows N, cols K) of the seven projections of one Falcon3-10B layer, in model order."""
+    return [(3072, 3072), (1024, 3072), (1024, 3072), (3072, 3072), (23040, 3072), (23040, 3072), (3072, 23040)]
+
+
+def bitnet_2b_shapes():
+    return [(2560, 2560), (640, 2560), (640, 2560), (2560, 2560), (6912, 2560), (6912, 2560), (2560, 6912)]
+
+
+def seed_for(config: int, layer: int, projection: int, stream: int) -> int:
+    return (BASE_SEED ^ (config << 48) ^ (layer << 16) ^ (projection << 8) ^ stream) & 0xFFFFFFFFFFFFFFFF
+
+
+def splitmix_u32(seed: int, start: int, n: int) -> np.ndarray:
+    """Uniform 32-bit values ``start .. start + n`` of the stream ``seed`` (numpy, the definition)."""
+    with np.errstate(over="ignore"):
+        i = np.arange(start + 1, start + n + 1, dtype=np.uint64)
+        z = np.uint64(seed) + i * np.uint64(GAMMA)
+        z = (z ^ (z >> np.uint64(30))) * np.uint64(M1)
+        z = (z ^ (z >> np.uint64(27))) * np.uint64(M2)
+        z = z ^ (z >> np.uint64(31))
+    return (z >> np.uint64(32)).astype(np.uint32)
+
+
+def trits(seed: int, n: int, start: int = 0) -> np.ndarray:
+    u = splitmix_u32(seed, start, n)
+    return np.where(u < T_NEG, -1, np.where(u < T_POS, 1, 0)).astype(np.int8)
+
+
+def weight_scale(seed: int) -> np.float32:
+    u = splitmix_u32(seed, 0, 1)[0]
+    return np.float32(0.5) + np.float32(1.5) * (np.float32(u) / np.float32(4294967296.0))
+
+
+def normal_f32(seed: int, n: int) -> np.ndarray:
+    """N(0,1) in fp32 by Box-Muller: pairs (u1, u2) -> sqrt(-2 ln u1) cos(2 pi u2), u1 in (0, 1]."""
+    u = splitmix_u32(seed, 0, 2 * n).astype(np.float64)
+    u1 = ((u[0::2] + 1.0) / 4294967296.0).astype(np.float32)
+    u2 = (u[1::2] / 4294967296.0).astype(np.float32)
+    r = np.sqrt(np.float32(-2.0) * np.log(u1)).astype(np.float32)
+    return (r * np.cos(np.float32(2.0 * np.pi) * u2).astype(np.float32)).astype(np.float32)
+
+
+# ---- the same integers on a torch device ---------------------------------------------------------------------------
+
+def _s64(v: int) -> int:
+    v &= 0xFFFFFFFFFFFFFFFF
+    return v - (1 << 64) if v >= (1 << 63) else v
+
+
+def torch_splitmix_u32(seed: int, start: int, n: int, device):
+    import torch
+
+    i = torch.arange(start + 1, start + n + 1, dtype=torch.int64, device=device)
+    z = i * _s64(GAMMA) + _s64(seed)
+    z = (z ^ ((z >> 30) & ((1 << 34) - 1))) * _s64(M1)
+    z = (z ^ ((z >> 27) & ((1 << 37) - 1))) * _s64(M2)
+    z = z ^ ((z >> 31) & ((1 << 33) - 1))
+    return (z >> 32) & 0xFFFFFFFF  # int64 holding the unsigned 32-bit value
+
+
+def torch_planar(seed: int, rows: int, cols: int, device, chunk_rows: int = 4096, row0: int = 0):
+    """Planar velurex bytes (uint8 tensor, rows * ceil(cols/160) * 32) of rows ``row0 .. row0 + rows`` of the seeded
+    ternary matrix, built on `device`."""
+    import torch
+
+    blocks = -(-cols // 160)
+    out = torch.empty((rows, blocks * 32), dtype=torch.uint8, device=device)
+    radix = torch.tensor([1, 3, 9, 28, 84], dtype=torch.int64, device=device).view(1, 1, 5, 1)
+    for r0 in range(0, rows, chunk_rows):
+        nr = min(chunk_rows, rows - r0)
+        u = torch_splitmix_u32(seed, (row0 + r0) * cols, nr * cols, device).view(nr, cols)
+        d = torch.where(u < T_NEG, 0, torch.where(u < T_POS, 2, 1))
+        if blocks * 160 != cols:
+            d = torch.nn.functional.pad(d, (0, blocks * 160 - cols), value=1)
+        out[r0:r0 + nr] = (d.view(nr, blocks, 5, 32) * radix).sum(dim=2).to(torch.uint8).view(nr, blocks * 32)
+    return out.view(-1)
+
+
+def quantize_int8_np(x: np.ndarray):
+    """Per-token absmax int8 quantisation of the synthetic activations (s = 127 / max|x|, round half away from zero,
+    clamp to [-128, 127]); returns (codes, s). Input preparation for the benchmark, not a product kernel."""
+    x = np.asarray(x, np.float32)
+    amax = np.float32(np.abs(x).max()) if x.size else np.float32(0)
+    if not amax > 0:
+        return np.zeros(x.size, np.int8), np.float32(0)
+    s = np.float32(127.0) / amax
+    y = x * s
+    q = np.sign(y) * np.floor(np.abs(y) + np.float32(0.5))
+    return np.clip(q, -128, 127).astype(np.int8), s
