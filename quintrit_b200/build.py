@@ -28,7 +28,8 @@ def needs_build() -> bool:
 
 def build(force: bool = False, verbose: bool = False) -> str:
     if force or needs_build():
-        cmd = [_nvcc(), *NVCC_FLAGS, "-o", LIB, *[os.path.join(HERE, s) for s in SOURCES]]
+        extra = os.environ.get("QUINTRIT_B200_NVCC_EXTRA", "").split()  # experiment knob, e.g. -DQTB_GEMV_DEPTH=2
+        cmd = [_nvcc(), *NVCC_FLAGS, *extra, "-o", LIB, *[os.path.join(HERE, s) for s in SOURCES]]
         if verbose:
             cmd.insert(1, "-Xptxas")
             cmd.insert(2, "-v")

@@ -23,7 +23,6 @@ struct quintrit_b200_matrix {
     // single-matrix launch state
     GemvItem* d_items;
     int n_items;
-    GemvProblem* d_problem;
     unsigned int* d_counters;
     int8_t* d_act;
     int32_t* d_out;
@@ -39,7 +38,6 @@ struct quintrit_b200_plan {
     size_t act_total, out_total;
     GemvItem* d_items;
     int n_items;
-    GemvProblem* d_problems;
     unsigned int* d_counters;
     int8_t* d_act;
     int32_t* d_out;
@@ -85,7 +83,8 @@ int item_tiles_override() {
     return v > 0 ? v : 0;
 }
 
-void build_items(std::vector<GemvItem>& items, unsigned problem, size_t blocks, size_t tiles, size_t tiles_per_item) {
+void build_items(std::vector<GemvItem>& items, const uint4* w, size_t act_off, size_t out_off, size_t rows, size_t cols, size_t blocks,
+                 size_t tiles, size_t tiles_per_item) {
     const size_t pairs = (blocks + 1) / 2;
     const size_t chunks = std::max<size_t>(1, (tiles + tiles_per_item - 1) / tiles_per_item);
     for (size_t p = 0; p < pairs; ++p) {
@@ -94,10 +93,13 @@ void build_items(std::vector<GemvItem>& items, unsigned problem, size_t blocks, 
             if (t1 == t0) continue;
             GemvItem it{};
             const size_t g = 2 * p;
-            it.w_off = (g * tiles + t0) * 64;
+            it.wa = w + (g * tiles + t0) * 64;
             it.nblk = g + 1 < blocks ? 2 : 1;
-            it.w2_off = it.nblk == 2 ? ((g + 1) * tiles + t0) * 64 : it.w_off;
-            it.problem = problem;
+            it.wb = it.nblk == 2 ? w + ((g + 1) * tiles + t0) * 64 : it.wa;
+            it.act_off = act_off;
+            it.out_off = out_off;
+            it.rows = static_cast<int>(rows);
+            it.cols = static_cast<int>(cols);
             it.col0 = static_cast<int>(g * kBlockTrits);
             it.tile0 = static_cast<int>(t0);
             it.ntiles = static_cast<int>(t1 - t0);
@@ -106,19 +108,57 @@ void build_items(std::vector<GemvItem>& items, unsigned problem, size_t blocks, 
     }
 }
 
-int launch_gemv(const GemvItem* d_items, int n_items, const GemvProblem* d_problems, const int8_t* d_act, int32_t* d_out,
-                unsigned int* d_counters, int sm_count, cudaStream_t stream) {
-    static bool attr_set[64] = {};
+using GemvKernel = void (*)(const GemvItem*, int, const int8_t*, int32_t*, unsigned int*);
+
+// Picks the kernel instantiation whose table-base constant equals the shared-window address this device gives to
+// dynamic shared memory (measured once per device with smem_base_kernel).
+int gemv_kernel_for_device(int dev, GemvKernel* out) {
+    static GemvKernel chosen[64] = {};
+    if (dev < 0 || dev >= 64) return fail(QUINTRIT_ERR_DEVICE, "device index %d out of range", dev);
+    if (chosen[dev] == nullptr) {
+        unsigned int* d_base = nullptr;
+        unsigned int base = 0xFFFFFFFFu;
+        QTB_CUDA(cudaMalloc(&d_base, sizeof(unsigned int)));
+        smem_base_kernel<<<1, 32, 1024>>>(d_base);
+        cudaError_t e = cudaGetLastError();
+        if (e == cudaSuccess) e = cudaMemcpy(&base, d_base, sizeof base, cudaMemcpyDeviceToHost);
+        cudaFree(d_base);
+        if (e != cudaSuccess) return cuda_fail(e, "smem_base_kernel");
+        GemvKernel k = nullptr;
+        switch (base) {
+            case 0: k = gemv_lut_kernel<0>; break;
+            case 1024: k = gemv_lut_kernel<1024>; break;
+            case 2048: k = gemv_lut_kernel<2048>; break;
+            case 3072: k = gemv_lut_kernel<3072>; break;
+            case 4096: k = gemv_lut_kernel<4096>; break;
+            default: return fail(QUINTRIT_ERR_DEVICE, "unexpected shared-memory base %u on CUDA device %d: no kernel was built for it", base, dev);
+        }
+        QTB_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemvSmemBytes));
+        chosen[dev] = k;
+    }
+    *out = chosen[dev];
+    return QUINTRIT_OK;
+}
+
+int launch_gemv(const GemvItem* d_items, int n_items, const int8_t* d_act, int32_t* d_out, unsigned int* d_counters, int sm_count,
+                cudaStream_t stream) {
     int dev = 0;
     QTB_CUDA(cudaGetDevice(&dev));
-    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        QTB_CUDA(cudaFuncSetAttribute(gemv_lut_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kTableBytes));
-        attr_set[dev] = true;
-    }
+    GemvKernel k = nullptr;
+    int rc = gemv_kernel_for_device(dev, &k);
+    if (rc != QUINTRIT_OK) return rc;
     const int grid = std::max(1, std::min(n_items, sm_count * kCtasPerSm));
-    gemv_lut_kernel<<<grid, kGemvThreads, kTableBytes, stream>>>(d_items, n_items, d_problems, d_act, d_out, d_counters);
+    k<<<grid, kGemvThreads, kGemvSmemBytes, stream>>>(d_items, n_items, d_act, d_out, d_counters);
     ++g_launches;
     QTB_CUDA(cudaGetLastError());
+    return QUINTRIT_OK;
+}
+
+// After a synchronisation: did the kernel refuse to run because its table-base constant was wrong?
+int check_kernel_status(unsigned int* d_counters) {
+    unsigned int flag = 0;
+    QTB_CUDA(cudaMemcpy(&flag, d_counters + 2, sizeof flag, cudaMemcpyDeviceToHost));
+    if (flag != 0) return fail(QUINTRIT_ERR_DEVICE, "GEMV kernel on the CUDA device found its shared-memory table at an unexpected address");
     return QUINTRIT_OK;
 }
 
@@ -232,7 +272,6 @@ void destroy_matrix(quintrit_b200_matrix* m) {
     DeviceGuard g(m->device);
     cudaFree(m->d_w);
     cudaFree(m->d_items);
-    cudaFree(m->d_problem);
     cudaFree(m->d_counters);
     cudaFree(m->d_act);
     cudaFree(m->d_out);
@@ -316,18 +355,15 @@ extern "C" int quintrit_b200_matrix_upload(uint32_t device_index, int32_t source
             const size_t chunks = std::max<size_t>(1, (slots + pairs - 1) / pairs);
             tiles_per_item = std::max<size_t>(16, (m->tiles + chunks - 1) / chunks);
         }
-        build_items(items, 0, m->blocks, m->tiles, tiles_per_item);
+        build_items(items, m->d_w, 0, 0, rows, cols, m->blocks, m->tiles, tiles_per_item);
         m->n_items = static_cast<int>(items.size());
-        GemvProblem pr{m->d_w, 0, 0, static_cast<int>(rows), static_cast<int>(cols)};
         if ((e = cudaMalloc(&m->d_items, items.size() * sizeof(GemvItem))) != cudaSuccess) return bail(e, "cudaMalloc(items)");
-        if ((e = cudaMalloc(&m->d_problem, sizeof(GemvProblem))) != cudaSuccess) return bail(e, "cudaMalloc(problem)");
-        if ((e = cudaMalloc(&m->d_counters, 2 * sizeof(unsigned int))) != cudaSuccess) return bail(e, "cudaMalloc(counters)");
+        if ((e = cudaMalloc(&m->d_counters, 4 * sizeof(unsigned int))) != cudaSuccess) return bail(e, "cudaMalloc(counters)");
         if ((e = cudaMalloc(&m->d_act, (cols + 15) / 16 * 16)) != cudaSuccess) return bail(e, "cudaMalloc(activations)");
         if ((e = cudaMalloc(&m->d_out, rows * sizeof(int32_t))) != cudaSuccess) return bail(e, "cudaMalloc(results)");
         if ((e = cudaMalloc(&m->d_outf, rows * sizeof(float))) != cudaSuccess) return bail(e, "cudaMalloc(results f32)");
         if ((e = cudaMemcpy(m->d_items, items.data(), items.size() * sizeof(GemvItem), cudaMemcpyHostToDevice)) != cudaSuccess) return bail(e, "cudaMemcpy(items)");
-        if ((e = cudaMemcpy(m->d_problem, &pr, sizeof pr, cudaMemcpyHostToDevice)) != cudaSuccess) return bail(e, "cudaMemcpy(problem)");
-        if ((e = cudaMemset(m->d_counters, 0, 2 * sizeof(unsigned int))) != cudaSuccess) return bail(e, "cudaMemset(counters)");
+        if ((e = cudaMemset(m->d_counters, 0, 4 * sizeof(unsigned int))) != cudaSuccess) return bail(e, "cudaMemset(counters)");
         *out_matrix = m;
         return ok();
     });
@@ -387,7 +423,7 @@ extern "C" int quintrit_b200_gemv_i32_device(const quintrit_b200_matrix_t* matri
         DeviceGuard g(matrix->device);
         cudaStream_t s = static_cast<cudaStream_t>(stream);
         QTB_CUDA(cudaMemsetAsync(d_out, 0, matrix->rows * sizeof(int32_t), s));
-        rc = launch_gemv(matrix->d_items, matrix->n_items, matrix->d_problem, d_activations, d_out, matrix->d_counters, matrix->sm_count, s);
+        rc = launch_gemv(matrix->d_items, matrix->n_items, d_activations, d_out, matrix->d_counters, matrix->sm_count, s);
         return rc == QUINTRIT_OK ? ok() : rc;
     });
 }
@@ -402,7 +438,7 @@ int gemv_host(const quintrit_b200_matrix* m, const int8_t* act, size_t act_len, 
     DeviceGuard g(m->device);
     QTB_CUDA(cudaMemcpyAsync(m->d_act, act, m->cols, cudaMemcpyHostToDevice, 0));
     QTB_CUDA(cudaMemsetAsync(m->d_out, 0, m->rows * sizeof(int32_t), 0));
-    rc = launch_gemv(m->d_items, m->n_items, m->d_problem, m->d_act, m->d_out, m->d_counters, m->sm_count, 0);
+    rc = launch_gemv(m->d_items, m->n_items, m->d_act, m->d_out, m->d_counters, m->sm_count, 0);
     if (rc != QUINTRIT_OK) return rc;
     if (as_float) {
         scale_kernel<<<static_cast<unsigned>((m->rows + 255) / 256), 256>>>(m->d_out, m->d_outf, m->rows, scale);
@@ -413,7 +449,8 @@ int gemv_host(const quintrit_b200_matrix* m, const int8_t* act, size_t act_len, 
         QTB_CUDA(cudaMemcpyAsync(out, m->d_out, m->rows * sizeof(int32_t), cudaMemcpyDeviceToHost, 0));
     }
     QTB_CUDA(cudaStreamSynchronize(0));
-    return ok();
+    rc = check_kernel_status(m->d_counters);
+    return rc == QUINTRIT_OK ? ok() : rc;
 }
 }  // namespace
 
@@ -436,7 +473,6 @@ void destroy_plan(quintrit_b200_plan* p) {
     if (p == nullptr) return;
     DeviceGuard g(p->device);
     cudaFree(p->d_items);
-    cudaFree(p->d_problems);
     cudaFree(p->d_counters);
     cudaFree(p->d_act);
     cudaFree(p->d_out);
@@ -463,7 +499,6 @@ extern "C" int quintrit_b200_plan_create(const quintrit_b200_matrix_t* const* ma
         p->count = count;
         DeviceGuard g(p->device);
         std::vector<GemvItem> items;
-        std::vector<GemvProblem> problems(count);
         size_t act = 0, out = 0;
         size_t tiles_per_item = item_tiles_override();
         if (tiles_per_item == 0) tiles_per_item = 64;
@@ -473,8 +508,7 @@ extern "C" int quintrit_b200_plan_create(const quintrit_b200_matrix_t* const* ma
             p->out_off.push_back(out);
             p->rows.push_back(m->rows);
             p->cols.push_back(m->cols);
-            problems[i] = GemvProblem{m->d_w, act, out, static_cast<int>(m->rows), static_cast<int>(m->cols)};
-            build_items(items, static_cast<unsigned>(i), m->blocks, m->tiles, tiles_per_item);
+            build_items(items, m->d_w, act, out, m->rows, m->cols, m->blocks, m->tiles, tiles_per_item);
             act += (m->cols + 15) / 16 * 16;
             out += (m->rows + 3) / 4 * 4;
         }
@@ -487,14 +521,11 @@ extern "C" int quintrit_b200_plan_create(const quintrit_b200_matrix_t* const* ma
         };
         cudaError_t e;
         if ((e = cudaMalloc(&p->d_items, items.size() * sizeof(GemvItem))) != cudaSuccess) return bail(e, "cudaMalloc(items)");
-        if ((e = cudaMalloc(&p->d_problems, count * sizeof(GemvProblem))) != cudaSuccess) return bail(e, "cudaMalloc(problems)");
-        if ((e = cudaMalloc(&p->d_counters, 2 * sizeof(unsigned int))) != cudaSuccess) return bail(e, "cudaMalloc(counters)");
+        if ((e = cudaMalloc(&p->d_counters, 4 * sizeof(unsigned int))) != cudaSuccess) return bail(e, "cudaMalloc(counters)");
         if ((e = cudaMalloc(&p->d_act, act)) != cudaSuccess) return bail(e, "cudaMalloc(activations)");
         if ((e = cudaMalloc(&p->d_out, out * sizeof(int32_t))) != cudaSuccess) return bail(e, "cudaMalloc(results)");
         if ((e = cudaMemcpy(p->d_items, items.data(), items.size() * sizeof(GemvItem), cudaMemcpyHostToDevice)) != cudaSuccess) return bail(e, "cudaMemcpy(items)");
-        if ((e = cudaMemcpy(p->d_problems, problems.data(), count * sizeof(GemvProblem), cudaMemcpyHostToDevice)) != cudaSuccess)
-            return bail(e, "cudaMemcpy(problems)");
-        if ((e = cudaMemset(p->d_counters, 0, 2 * sizeof(unsigned int))) != cudaSuccess) return bail(e, "cudaMemset(counters)");
+        if ((e = cudaMemset(p->d_counters, 0, 4 * sizeof(unsigned int))) != cudaSuccess) return bail(e, "cudaMemset(counters)");
         if ((e = cudaMemset(p->d_act, 0, act)) != cudaSuccess) return bail(e, "cudaMemset(activations)");
         *out_plan = p;
         return ok();
@@ -542,7 +573,7 @@ extern "C" int quintrit_b200_plan_launch(quintrit_b200_plan_t* plan, void* strea
         DeviceGuard g(plan->device);
         cudaStream_t s = static_cast<cudaStream_t>(stream);
         QTB_CUDA(cudaMemsetAsync(plan->d_out, 0, plan->out_total * sizeof(int32_t), s));
-        rc = launch_gemv(plan->d_items, plan->n_items, plan->d_problems, plan->d_act, plan->d_out, plan->d_counters, plan->sm_count, s);
+        rc = launch_gemv(plan->d_items, plan->n_items, plan->d_act, plan->d_out, plan->d_counters, plan->sm_count, s);
         return rc == QUINTRIT_OK ? ok() : rc;
     });
 }
@@ -558,10 +589,13 @@ extern "C" int quintrit_b200_plan_run(quintrit_b200_plan_t* plan, const int8_t* 
         DeviceGuard g(plan->device);
         QTB_CUDA(cudaMemcpyAsync(plan->d_act, activations, plan->act_total, cudaMemcpyHostToDevice, 0));
         QTB_CUDA(cudaMemsetAsync(plan->d_out, 0, plan->out_total * sizeof(int32_t), 0));
-        rc = launch_gemv(plan->d_items, plan->n_items, plan->d_problems, plan->d_act, plan->d_out, plan->d_counters, plan->sm_count, 0);
+        rc = launch_gemv(plan->d_items, plan->n_items, plan->d_act, plan->d_out, plan->d_counters, plan->sm_count, 0);
         if (rc != QUINTRIT_OK) return rc;
         QTB_CUDA(cudaMemcpyAsync(out, plan->d_out, plan->out_total * sizeof(int32_t), cudaMemcpyDeviceToHost, 0));
+        unsigned int flag = 0;
+        QTB_CUDA(cudaMemcpyAsync(&flag, plan->d_counters + 2, sizeof flag, cudaMemcpyDeviceToHost, 0));
         QTB_CUDA(cudaStreamSynchronize(0));
+        if (flag != 0) return fail(QUINTRIT_ERR_DEVICE, "GEMV kernel on the CUDA device found its shared-memory table at an unexpected address");
         return ok();
     });
 }
