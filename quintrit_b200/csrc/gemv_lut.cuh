@@ -194,13 +194,22 @@ __device__ __forceinline__ void load_tile(TileRegs& r, const uint4* wa, const ui
     }
 }
 
+// What a warp needs of the current item while it streams, boiled down to a few registers.
+struct ItemRegs {
+    const uint4* wa;  // block A, tile 0 of the item, this lane
+    const uint4* wb;  // block B, likewise
+    int32_t* out;     // result of the lane's row in tile 0 of the item
+    int rows_left;    // rows of the matrix from that row on (<= 0: the lane's rows do not exist)
+    int ntiles, nblk;
+};
+
 // Loads the tile this warp will need after tile `t` of the current item (iteration index i): tile t_next of the same
 // item, or else the warp's first tile of the next item, whose descriptor is already in shared memory. `tag` receives
 // the iteration index of the item the tile belongs to, or -1 if there is no such tile yet.
-__device__ __forceinline__ void preload(TileRegs& r, int& tag, int i, int t_next, const GemvItem& item, const GemvItem* s_items,
+__device__ __forceinline__ void preload(TileRegs& r, int& tag, int i, int t_next, const ItemRegs& item, const GemvItem* s_items,
                                         const int* s_idx, int n_items, int warp, int lane) {
     if (t_next < item.ntiles) {
-        load_tile(r, item.wa, item.wb, item.nblk, t_next, lane);
+        load_tile(r, item.wa, item.wb, item.nblk, t_next, 0);
         tag = i;
     } else {
         const int nx = (i + 1) & 3;
@@ -293,7 +302,16 @@ gemv_lut_kernel(const GemvItem* __restrict__ items, int n_items, const int8_t* _
     for (int i = 0;; ++i) {
         const int cur = i & 3;
         if (s_idx[cur] >= n_items) break;
-        const GemvItem item = s_items[cur];  // a register copy: the loops must not re-read it from shared memory
+        ItemRegs item;  // a register copy: the loops must not re-read the descriptor from shared memory
+        {
+            const GemvItem& d = s_items[cur];
+            item.wa = d.wa + lane;
+            item.wb = d.wb + lane;
+            item.out = out_base + d.out_off + d.tile0 * kTileRows + lane;
+            item.rows_left = d.rows - d.tile0 * kTileRows - lane;
+            item.ntiles = d.ntiles;
+            item.nblk = d.nblk;
+        }
         // The warp's first tile of this item is normally on its way already (loaded at the end of the previous item);
         // it is fetched here only at the very start or after items too small to give this warp a tile.
         if (tag_a < 0) preload(ra, tag_a, i, warp, item, s_items, s_idx, n_items, warp, lane);
@@ -323,14 +341,12 @@ gemv_lut_kernel(const GemvItem* __restrict__ items, int n_items, const int8_t* _
         }
         __syncthreads();
 
-        int32_t* out = out_base + item.out_off;
         int t = warp;
         while (tag_a == i) {
             preload(rb, tag_b, i, t + kGemvWarps, item, s_items, s_idx, n_items, warp, lane);
             {
                 const int acc = tile_sum<BASE>(ra, item.nblk, creg);
-                const int row = (item.tile0 + t) * kTileRows + lane;
-                if (row < item.rows) atomicAdd(out + row, acc);
+                if (t * kTileRows < item.rows_left) atomicAdd(item.out + t * kTileRows, acc);
             }
             t += kGemvWarps;
             if (tag_b != i) {  // rb holds a tile of the next item (or nothing): hand it over and leave
@@ -341,8 +357,7 @@ gemv_lut_kernel(const GemvItem* __restrict__ items, int n_items, const int8_t* _
             preload(ra, tag_a, i, t + kGemvWarps, item, s_items, s_idx, n_items, warp, lane);
             {
                 const int acc = tile_sum<BASE>(rb, item.nblk, creg);
-                const int row = (item.tile0 + t) * kTileRows + lane;
-                if (row < item.rows) atomicAdd(out + row, acc);
+                if (t * kTileRows < item.rows_left) atomicAdd(item.out + t * kTileRows, acc);
             }
             t += kGemvWarps;
         }
