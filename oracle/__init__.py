@@ -262,3 +262,168 @@ def cpu_gemv_portable(planar, rows: int, cols: int, act, threads: int, out=None)
         out = np.zeros(rows, np.int32)
     lib().qto_cpu_gemv_portable(_p(p, _u8p), rows, cols, _p(a, _i8p), _p(out, _i32p), threads)
     return out
+
+
+# ---- float decode primitives and the whole-token forward (oracle/qt_oracle_model.c) ---------------------------------
+
+_u16p, _u64p = C.POINTER(C.c_uint16), C.POINTER(C.c_uint64)
+
+
+def _declare_model(l: C.CDLL) -> None:
+    l.qto_f16_to_f32.restype = C.c_float
+    l.qto_f16_to_f32.argtypes = [C.c_uint16]
+    l.qto_f32_to_f16.restype = C.c_uint16
+    l.qto_f32_to_f16.argtypes = [C.c_float]
+    l.qto_f32_to_bf16.restype = C.c_uint16
+    l.qto_f32_to_bf16.argtypes = [C.c_float]
+    l.qto_bf16_to_f32.restype = C.c_float
+    l.qto_bf16_to_f32.argtypes = [C.c_uint16]
+    l.qto_rms_norm.argtypes = [_f32p, _f32p, _sz, C.c_float, _f32p]
+    l.qto_rope_cache.argtypes = [_sz, _sz, C.c_float, _f32p]
+    l.qto_rope_apply.argtypes = [_f32p, _sz, _sz, C.c_int, _f32p, _sz]
+    l.qto_vec_dot_f16.restype = C.c_float
+    l.qto_vec_dot_f16.argtypes = [_u16p, _u16p, _sz]
+    l.qto_vec_dot_f16_f32.restype = C.c_float
+    l.qto_vec_dot_f16_f32.argtypes = [_u16p, _f32p, _sz]
+    l.qto_ggml_expf_lane.restype = C.c_float
+    l.qto_ggml_expf_lane.argtypes = [C.c_float]
+    l.qto_silu.restype = C.c_float
+    l.qto_silu.argtypes = [C.c_float]
+    l.qto_swiglu.argtypes = [_f32p, _f32p, _sz, _f32p]
+    l.qto_relu2_mul.argtypes = [_f32p, _f32p, _sz, _f32p]
+    l.qto_expf_restated.restype = C.c_float
+    l.qto_expf_restated.argtypes = [C.c_float]
+    l.qto_exp2_table.restype = _u64p
+    l.qto_attend_head.argtypes = [_f32p, _u16p, _u16p, _sz, _sz, _sz, _sz, C.c_float, C.c_int, _f32p]
+    l.qto_argmax.restype = C.c_uint32
+    l.qto_argmax.argtypes = [_f32p, _sz]
+    l.qto_model_create.restype = C.c_void_p
+    l.qto_model_create.argtypes = [C.c_int] * 11 + [C.c_float, C.c_float, _u16p, _u16p, _f32p, C.POINTER(_u8p), _f32p, C.POINTER(_f32p)]
+    l.qto_model_free.argtypes = [C.c_void_p]
+    l.qto_model_forward.argtypes = [C.c_void_p, C.c_uint32, _sz, _f32p]
+
+
+_model_declared = False
+
+
+def mlib() -> C.CDLL:
+    global _model_declared
+    l = lib()
+    if not _model_declared:
+        _declare_model(l)
+        _model_declared = True
+    return l
+
+
+def f32_to_f16_bits(x) -> np.ndarray:
+    xx = _c(x, np.float32).reshape(-1)
+    l = mlib()
+    return np.array([l.qto_f32_to_f16(float(v)) for v in xx], np.uint16)
+
+
+def rms_norm(x, w, eps: float) -> np.ndarray:
+    xx, ww = _c(x, np.float32), _c(w, np.float32)
+    out = np.zeros(xx.size, np.float32)
+    mlib().qto_rms_norm(_p(xx, _f32p), _p(ww, _f32p), xx.size, eps, _p(out, _f32p))
+    return out
+
+
+def rope_cache(pos: int, n_dims: int, freq_base: float) -> np.ndarray:
+    out = np.zeros(n_dims, np.float32)
+    mlib().qto_rope_cache(pos, n_dims, freq_base, _p(out, _f32p))
+    return out
+
+
+def rope_apply(x, heads: int, head_dim: int, mode: int, cache) -> np.ndarray:
+    xx = _c(x, np.float32).copy()
+    cc = _c(cache, np.float32)
+    mlib().qto_rope_apply(_p(xx, _f32p), heads, head_dim, mode, _p(cc, _f32p), cc.size)
+    return xx
+
+
+def vec_dot_f16(x, y) -> np.float32:
+    a, b = _c(x, np.uint16), _c(y, np.uint16)
+    return np.float32(mlib().qto_vec_dot_f16(_p(a, _u16p), _p(b, _u16p), a.size))
+
+
+def vec_dot_f16_f32(x, y) -> np.float32:
+    a, b = _c(x, np.uint16), _c(y, np.float32)
+    return np.float32(mlib().qto_vec_dot_f16_f32(_p(a, _u16p), _p(b, _f32p), a.size))
+
+
+def swiglu(gate, up) -> np.ndarray:
+    g, u = _c(gate, np.float32), _c(up, np.float32)
+    out = np.zeros(g.size, np.float32)
+    mlib().qto_swiglu(_p(g, _f32p), _p(u, _f32p), g.size, _p(out, _f32p))
+    return out
+
+
+def relu2_mul(gate, up) -> np.ndarray:
+    g, u = _c(gate, np.float32), _c(up, np.float32)
+    out = np.zeros(g.size, np.float32)
+    mlib().qto_relu2_mul(_p(g, _f32p), _p(u, _f32p), g.size, _p(out, _f32p))
+    return out
+
+
+def expf_restated(x) -> np.ndarray:
+    xx = _c(x, np.float32).reshape(-1)
+    l = mlib()
+    return np.array([l.qto_expf_restated(float(v)) for v in xx], np.float32)
+
+
+def exp2_table() -> np.ndarray:
+    return np.ctypeslib.as_array(mlib().qto_exp2_table(), shape=(32,)).copy()
+
+
+def attend_head(q, k, v, stride: int, seq_len: int, max_seq_len: int, head_dim: int, scale: float, f32_values: bool) -> np.ndarray:
+    qq, kk, vv = _c(q, np.float32), _c(k, np.uint16).reshape(-1), _c(v, np.uint16).reshape(-1)
+    out = np.zeros(head_dim, np.float32)
+    mlib().qto_attend_head(_p(qq, _f32p), _p(kk, _u16p), _p(vv, _u16p), stride, seq_len, max_seq_len, head_dim, scale, int(f32_values), _p(out, _f32p))
+    return out
+
+
+def argmax(logits) -> int:
+    x = _c(logits, np.float32)
+    return int(mlib().qto_argmax(_p(x, _f32p), x.size))
+
+
+class Model:
+    """Whole-token CPU forward over a model given as numpy arrays (see quintrit_b200.synth.make_model)."""
+
+    def __init__(self, spec: dict):
+        l = mlib()
+        self.spec = spec
+        L = spec["layers"]
+        self._keep = []
+        w = (_u8p * (L * 7))()
+        for i, a in enumerate(spec["weights"]):
+            a = _c(a, np.uint8)
+            self._keep.append(a)
+            w[i] = _p(a, _u8p)
+        norms = (_f32p * (L * 4))()
+        for i, a in enumerate(spec["norms"]):
+            if a is None:
+                norms[i] = None
+            else:
+                a = _c(a, np.float32)
+                self._keep.append(a)
+                norms[i] = _p(a, _f32p)
+        scales = _c(spec["scales"], np.float32)
+        embed = _c(spec["embed"], np.uint16)
+        head = None if spec.get("lm_head") is None else _c(spec["lm_head"], np.uint16)
+        out_norm = _c(spec["out_norm"], np.float32)
+        self._keep += [scales, embed, head, out_norm, w, norms]
+        self._h = l.qto_model_create(spec["arch"], int(spec["f32_values"]), spec["hidden"], spec["inter"], L, spec["q_heads"], spec["kv_heads"],
+                                     spec["head_dim"], spec["vocab"], spec["ctx"], spec["rope_dims"], spec["eps"], spec["rope_theta"],
+                                     _p(embed, _u16p), None if head is None else _p(head, _u16p), _p(out_norm, _f32p), w, _p(scales, _f32p), norms)
+
+    def forward(self, token: int, pos: int) -> np.ndarray:
+        logits = np.zeros(self.spec["vocab"], np.float32)
+        mlib().qto_model_forward(self._h, token, pos, _p(logits, _f32p))
+        return logits
+
+    def __del__(self):
+        try:
+            mlib().qto_model_free(self._h)
+        except Exception:
+            pass
