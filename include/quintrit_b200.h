@@ -138,6 +138,58 @@ int quintrit_b200_plan_launch(quintrit_b200_plan_t* plan, void* stream);
 /* Host-buffer form: copies `activations` (act_total bytes) in, launches, copies out_total int32 back and waits. */
 int quintrit_b200_plan_run(quintrit_b200_plan_t* plan, const int8_t* activations, size_t activations_len, int32_t* out,
                            size_t out_capacity);
+/* ---- whole-token decoder: the device seam of the runtime ---- */
+typedef struct quintrit_b200_decoder quintrit_b200_decoder_t;
+
+#define QUINTRIT_B200_ARCH_LLAMA 0  /* LLaMA / Falcon3: interleaved RoPE pairs, SwiGLU (quintrit-runtime/src/config.rs:284-288, 464-467) */
+#define QUINTRIT_B200_ARCH_BITNET 1 /* BitNet b1.58: NEOX RoPE pairs, squared ReLU, attention and FFN sub-norms (config.rs:419-422) */
+
+/*
+ * Description of a model whose ternary projections are already on the device. It plays the part of GpuModel::load
+ * (quintrit-runtime/src/gpu.rs:183-260) after the GGUF has been read: dense tables are given as host pointers and copied.
+ * matrices: layers * 7 handles in the order q, k, v, o, gate, up, down; scales: their weight scales (layers * 7);
+ * norms: layers * 4 host pointers to F32 weights in the order attn_norm, ffn_norm, attn_sub_norm, ffn_sub_norm (the
+ * last two NULL unless arch is BITNET). embed / lm_head: F16 bit patterns [vocab][hidden]; lm_head NULL = tied
+ * (quintrit-runtime/src/model.rs:353). f32_values selects the attention arithmetic of files without I2_S tensors
+ * (FP32 value accumulators, quintrit-runtime/src/config.rs:425-429), 0 the FP16 accumulators of I2_S files.
+ * context_length is rounded down to a multiple of 256 (gpu.rs:141-146); head_dim must be a multiple of 32.
+ */
+typedef struct quintrit_b200_decoder_desc {
+    uint32_t struct_size;
+    uint32_t device_index;
+    int32_t arch;
+    int32_t f32_values;
+    uint32_t hidden_size, intermediate_size, num_layers, num_heads, num_kv_heads, head_dim, vocab_size, context_length, rope_dims;
+    float rms_norm_eps, rope_theta;
+    const uint16_t* embed;
+    const uint16_t* lm_head;
+    const float* output_norm;
+    const quintrit_b200_matrix_t* const* matrices;
+    const float* scales;
+    const float* const* norms;
+} quintrit_b200_decoder_desc_t;
+
+int quintrit_b200_decoder_create(const quintrit_b200_decoder_desc_t* desc, quintrit_b200_decoder_t** out_decoder);
+int quintrit_b200_decoder_free(quintrit_b200_decoder_t* decoder);
+/*
+ * One token at position `pos` (positions are fed in order; an earlier position restarts from that prefix), as
+ * GpuSession::forward (quintrit-runtime/src/gpu.rs:459-493) but from a token id: the embedding row is looked up on the
+ * device. logits (vocab_size floats) may be NULL; out_token (may be NULL) receives the greedy choice
+ * (quintrit-runtime/src/sampler.rs:73-83), computed on the device.
+ */
+int quintrit_b200_decoder_forward(quintrit_b200_decoder_t* decoder, uint32_t token, uint32_t pos, float* logits, size_t logits_capacity,
+                                  uint32_t* out_token);
+/*
+ * Feeds `prompt_len` tokens from position 0 and then decodes `max_new` tokens greedily without leaving the device
+ * (token and position live in device memory, one CUDA graph replay per token). out_tokens receives max_new ids.
+ * The generate loop of the reference is quintrit-runtime/src/engine.rs:626-700 with the CPU sampler.
+ */
+int quintrit_b200_decoder_generate(quintrit_b200_decoder_t* decoder, const uint32_t* prompt, size_t prompt_len, size_t max_new,
+                                   uint32_t* out_tokens, size_t out_capacity);
+/* Device time of one decode step in milliseconds: minimum over `blocks` blocks of `iters` graph replays at the current
+ * position, as GpuSession::time_token (quintrit-runtime/src/gpu.rs:346-370). */
+int quintrit_b200_decoder_time_token(quintrit_b200_decoder_t* decoder, uint32_t blocks, uint32_t iters, float* out_ms);
+
 /* Kernel launches issued by this library on the calling thread since the last call with reset != 0 (counting aid). */
 uint64_t quintrit_b200_launch_count(int reset);
 

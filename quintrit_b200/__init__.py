@@ -6,6 +6,9 @@ over that ABI. It mirrors the reference's GPU launcher interface (``rust/crates/
 compute call goes to the CUDA library and raises ``QuintritError`` if it is missing or the device is unusable.
 """
 from .api import (  # noqa: F401
+    ARCH_BITNET,
+    ARCH_LLAMA,
+    Decoder,
     DeviceInfo,
     Matrix,
     Plan,

@@ -37,6 +37,15 @@ class _DeviceInfoC(C.Structure):
                 ("name", C.c_char * 64)]
 
 
+class _DecoderDescC(C.Structure):
+    _fields_ = [("struct_size", C.c_uint32), ("device_index", C.c_uint32), ("arch", C.c_int32), ("f32_values", C.c_int32),
+                ("hidden_size", C.c_uint32), ("intermediate_size", C.c_uint32), ("num_layers", C.c_uint32), ("num_heads", C.c_uint32),
+                ("num_kv_heads", C.c_uint32), ("head_dim", C.c_uint32), ("vocab_size", C.c_uint32), ("context_length", C.c_uint32),
+                ("rope_dims", C.c_uint32), ("rms_norm_eps", C.c_float), ("rope_theta", C.c_float), ("embed", C.POINTER(C.c_uint16)),
+                ("lm_head", C.POINTER(C.c_uint16)), ("output_norm", _f32p), ("matrices", C.POINTER(C.c_void_p)), ("scales", _f32p),
+                ("norms", C.POINTER(_f32p))]
+
+
 @dataclass
 class DeviceInfo:
     index: int
@@ -85,6 +94,11 @@ def load_library(build_if_missing: bool = True) -> C.CDLL:
     l.quintrit_b200_plan_buffers.argtypes = [C.c_void_p, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p)]
     l.quintrit_b200_plan_launch.argtypes = [C.c_void_p, C.c_void_p]
     l.quintrit_b200_plan_run.argtypes = [C.c_void_p, _i8p, _sz, _i32p, _sz]
+    l.quintrit_b200_decoder_create.argtypes = [C.POINTER(_DecoderDescC), C.POINTER(C.c_void_p)]
+    l.quintrit_b200_decoder_free.argtypes = [C.c_void_p]
+    l.quintrit_b200_decoder_forward.argtypes = [C.c_void_p, C.c_uint32, C.c_uint32, _f32p, _sz, C.POINTER(C.c_uint32)]
+    l.quintrit_b200_decoder_generate.argtypes = [C.c_void_p, C.POINTER(C.c_uint32), _sz, _sz, C.POINTER(C.c_uint32), _sz]
+    l.quintrit_b200_decoder_time_token.argtypes = [C.c_void_p, C.c_uint32, C.c_uint32, C.POINTER(C.c_float)]
     l.quintrit_b200_launch_count.restype = C.c_uint64
     l.quintrit_b200_launch_count.argtypes = [C.c_int]
     _lib = l
@@ -241,6 +255,91 @@ class Plan:
         if self._h:
             load_library().quintrit_b200_plan_free(self._h)
             self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+ARCH_LLAMA, ARCH_BITNET = 0, 1
+
+
+class Decoder:
+    """Whole-token decoder on the device: ``GpuModel`` + ``GpuSession`` of ``rust/crates/quintrit-runtime/src/gpu.rs``.
+
+    ``spec`` is a dict as made by ``quintrit_b200.synth.make_model``: dimensions, ``weights`` (layers * 7 planar byte
+    arrays in the order q, k, v, o, gate, up, down, or ``(source, payload)`` pairs for GGUF encodings), ``scales``,
+    ``norms`` (layers * 4, None where absent), ``embed`` / ``lm_head`` as F16 bit patterns, ``out_norm``.
+    """
+
+    def __init__(self, spec: dict, device: int = 0):
+        self.spec = spec
+        L, H, I, hd = spec["layers"], spec["hidden"], spec["inter"], spec["head_dim"]
+        qd, kvd = spec["q_heads"] * hd, spec["kv_heads"] * hd
+        shapes = [(qd, H), (kvd, H), (kvd, H), (H, qd), (I, H), (I, H), (H, I)]
+        self.matrices = []
+        for i, w in enumerate(spec["weights"]):
+            rows, cols = shapes[i % 7]
+            if isinstance(w, tuple):
+                self.matrices.append(Matrix(w[1], rows, cols, source=w[0], device=device))
+            else:
+                self.matrices.append(Matrix(w, rows, cols, device=device))
+        keep = []
+        mats = (C.c_void_p * (L * 7))(*[m.handle for m in self.matrices])
+        norms = (_f32p * (L * 4))()
+        for i, a in enumerate(spec["norms"]):
+            if a is not None:
+                a = np.ascontiguousarray(a, np.float32)
+                keep.append(a)
+                norms[i] = _p(a, _f32p)
+        scales = np.ascontiguousarray(spec["scales"], np.float32)
+        embed = np.ascontiguousarray(spec["embed"], np.uint16)
+        head = None if spec.get("lm_head") is None else np.ascontiguousarray(spec["lm_head"], np.uint16)
+        out_norm = np.ascontiguousarray(spec["out_norm"], np.float32)
+        d = _DecoderDescC()
+        d.struct_size = C.sizeof(_DecoderDescC)
+        d.device_index, d.arch, d.f32_values = device, spec["arch"], int(spec["f32_values"])
+        d.hidden_size, d.intermediate_size, d.num_layers = H, I, L
+        d.num_heads, d.num_kv_heads, d.head_dim = spec["q_heads"], spec["kv_heads"], hd
+        d.vocab_size, d.context_length, d.rope_dims = spec["vocab"], spec["ctx"], spec["rope_dims"]
+        d.rms_norm_eps, d.rope_theta = spec["eps"], spec["rope_theta"]
+        d.embed = _p(embed, C.POINTER(C.c_uint16))
+        d.lm_head = None if head is None else _p(head, C.POINTER(C.c_uint16))
+        d.output_norm = _p(out_norm, _f32p)
+        d.matrices, d.scales, d.norms = mats, _p(scales, _f32p), norms
+        h = C.c_void_p()
+        _check(load_library().quintrit_b200_decoder_create(C.byref(d), C.byref(h)))
+        self._h = h
+        self.vocab = spec["vocab"]
+
+    def forward(self, token: int, pos: int, want_logits: bool = True):
+        """Returns (logits or None, greedy token)."""
+        logits = np.zeros(self.vocab, np.float32) if want_logits else None
+        tok = C.c_uint32(0)
+        _check(load_library().quintrit_b200_decoder_forward(self._h, token, pos, None if logits is None else _p(logits, _f32p),
+                                                            0 if logits is None else logits.size, C.byref(tok)))
+        return logits, tok.value
+
+    def generate(self, prompt, max_new: int) -> np.ndarray:
+        p = np.ascontiguousarray(prompt, np.uint32)
+        out = np.zeros(max_new, np.uint32)
+        _check(load_library().quintrit_b200_decoder_generate(self._h, _p(p, C.POINTER(C.c_uint32)), p.size, max_new,
+                                                             _p(out, C.POINTER(C.c_uint32)), out.size))
+        return out
+
+    def time_token(self, blocks: int = 5, iters: int = 50) -> float:
+        ms = C.c_float(0)
+        _check(load_library().quintrit_b200_decoder_time_token(self._h, blocks, iters, C.byref(ms)))
+        return ms.value
+
+    def free(self) -> None:
+        if self._h:
+            load_library().quintrit_b200_decoder_free(self._h)
+            self._h = C.c_void_p()
+        for m in self.matrices:
+            m.free()
 
     def __del__(self):
         try:

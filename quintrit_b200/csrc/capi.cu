@@ -175,6 +175,8 @@ struct DeviceGuard {
 
 }  // namespace
 
+#include "decoder.cuh"
+
 // ---------------------------------------------------------------------------------------------------------------------
 // errors, version, devices
 // ---------------------------------------------------------------------------------------------------------------------
@@ -604,4 +606,292 @@ extern "C" uint64_t quintrit_b200_launch_count(int reset) {
     const uint64_t n = g_launches;
     if (reset) g_launches = 0;
     return n;
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// decoder
+// ---------------------------------------------------------------------------------------------------------------------
+
+namespace {
+
+// Tiles per item for a launch over `tile_pairs` (sum over its problems of row tiles x block pairs): enough items to give
+// every CTA slot one, but no item below 8 row tiles (a table build costs about as much as streaming 8 tiles).
+size_t decoder_item_tiles(size_t tile_pairs, size_t slots) {
+    const size_t override = item_tiles_override();
+    if (override) return override;
+    return std::max<size_t>(8, (tile_pairs + slots - 1) / slots);
+}
+
+int decoder_create_impl(const quintrit_b200_decoder_desc_t* desc, quintrit_b200_decoder** out) {
+    if (desc->struct_size < sizeof(quintrit_b200_decoder_desc_t))
+        return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "struct_size %u is smaller than quintrit_b200_decoder_desc_t (%zu)", desc->struct_size,
+                    sizeof(quintrit_b200_decoder_desc_t));
+    if (!desc->embed || !desc->output_norm || !desc->matrices || !desc->scales || !desc->norms)
+        return fail(QUINTRIT_ERR_NULL_POINTER, "a required pointer of the decoder description is NULL");
+    if (desc->arch != QUINTRIT_B200_ARCH_LLAMA && desc->arch != QUINTRIT_B200_ARCH_BITNET)
+        return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "unknown architecture %d", desc->arch);
+    const uint32_t H = desc->hidden_size, I = desc->intermediate_size, L = desc->num_layers, hd = desc->head_dim;
+    if (!H || !I || !L || !desc->num_heads || !desc->num_kv_heads || !hd || !desc->vocab_size)
+        return fail(QUINTRIT_ERR_MODEL, "a model dimension is zero");
+    if (hd % 32 != 0 || hd > 256) return fail(QUINTRIT_ERR_UNSUPPORTED, "head_dim %u is not supported (a multiple of 32, at most 256)", hd);
+    if (desc->num_heads % desc->num_kv_heads != 0) return fail(QUINTRIT_ERR_MODEL, "num_heads is not a multiple of num_kv_heads");
+    if (desc->rope_dims == 0 || desc->rope_dims % 2 != 0 || desc->rope_dims > hd)
+        return fail(QUINTRIT_ERR_MODEL, "rope_dims %u must be even and at most the head dimension %u", desc->rope_dims, hd);
+    const uint32_t ctx = desc->context_length / 256 * 256;  // gpu.rs:141-146
+    if (ctx == 0 || ctx > 8192) return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "context_length %u must give 256..8192 after rounding down to a multiple of 256", desc->context_length);
+    const size_t qd = size_t(desc->num_heads) * hd, kvd = size_t(desc->num_kv_heads) * hd;
+    if (std::max<size_t>({H, I, qd}) * sizeof(float) > 200 * 1024) return fail(QUINTRIT_ERR_UNSUPPORTED, "a vector of the model does not fit the shared memory of one block");
+    cudaDeviceProp prop;
+    int rc = require_b200(static_cast<int>(desc->device_index), &prop);
+    if (rc != QUINTRIT_OK) return rc;
+    const size_t shapes[7][2] = {{qd, H}, {kvd, H}, {kvd, H}, {H, qd}, {I, H}, {I, H}, {H, I}};
+    for (size_t i = 0; i < size_t(L) * 7; ++i) {
+        const quintrit_b200_matrix* m = desc->matrices[i];
+        rc = check_matrix(m);
+        if (rc != QUINTRIT_OK) return rc;
+        if (m->device != static_cast<int>(desc->device_index)) return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "matrix %zu lives on another device", i);
+        if (m->rows != shapes[i % 7][0] || m->cols != shapes[i % 7][1])
+            return fail(QUINTRIT_ERR_MODEL, "matrix %zu is %zu x %zu, the model needs %zu x %zu", i, m->rows, m->cols, shapes[i % 7][0], shapes[i % 7][1]);
+    }
+    DeviceGuard guard(static_cast<int>(desc->device_index));
+    quintrit_b200_decoder* d = new quintrit_b200_decoder();
+    *out = d;  // the caller destroys it on failure
+    d->magic = kMagicDecoder;
+    d->device = static_cast<int>(desc->device_index);
+    d->sm_count = prop.multiProcessorCount;
+    d->arch = desc->arch, d->f32_values = desc->f32_values != 0;
+    d->hidden = H, d->inter = I, d->layers = L, d->q_heads = desc->num_heads, d->kv_heads = desc->num_kv_heads, d->head_dim = hd;
+    d->vocab = desc->vocab_size, d->ctx = ctx, d->rope_dims = desc->rope_dims, d->q_dim = static_cast<int>(qd), d->kv_dim = static_cast<int>(kvd);
+    d->eps = desc->rms_norm_eps, d->rope_theta = desc->rope_theta;
+    d->scales.assign(desc->scales, desc->scales + size_t(L) * 7);
+    d->graph_ready = false;
+    d->stream = nullptr;
+    d->host_pos = 0;
+    QTB_CUDA(cudaStreamCreateWithFlags(&d->stream, cudaStreamNonBlocking));
+
+    // glibc expf table: 2^(i/32) correctly rounded (the host libm's exp2), minus i << 47
+    unsigned long long tab[32];
+    for (int i = 0; i < 32; ++i) {
+        const double v = std::exp2(static_cast<double>(i) / 32.0);
+        unsigned long long b;
+        std::memcpy(&b, &v, 8);
+        tab[i] = b - (static_cast<unsigned long long>(i) << 47);
+    }
+    QTB_CUDA(cudaMemcpyToSymbol(c_exp2_tab, tab, sizeof tab));
+    // cos / sin of every position with the host libm, chained as ops.rs:121-141 (freq_scale 1, no YaRN)
+    {
+        std::vector<float> cs(size_t(ctx) * desc->rope_dims);
+        const float theta_scale = std::pow(desc->rope_theta, -2.0f / static_cast<float>(desc->rope_dims));
+        for (uint32_t p = 0; p < ctx; ++p) {
+            float theta = static_cast<float>(p);
+            for (uint32_t i0 = 0; i0 < desc->rope_dims; i0 += 2) {
+                cs[size_t(p) * desc->rope_dims + i0] = std::cos(theta);
+                cs[size_t(p) * desc->rope_dims + i0 + 1] = std::sin(theta);
+                theta *= theta_scale;
+            }
+        }
+        if ((rc = dev_upload(d, &d->cos_sin, cs.data(), cs.size())) != QUINTRIT_OK) return rc;
+    }
+    if ((rc = dev_upload(d, &d->embed, desc->embed, size_t(d->vocab) * H)) != QUINTRIT_OK) return rc;
+    d->lm_head = d->embed;
+    if (desc->lm_head && (rc = dev_upload(d, &d->lm_head, desc->lm_head, size_t(d->vocab) * H)) != QUINTRIT_OK) return rc;
+    if ((rc = dev_upload(d, &d->out_norm, desc->output_norm, H)) != QUINTRIT_OK) return rc;
+    d->norms.assign(size_t(L) * 4, nullptr);
+    for (size_t i = 0; i < size_t(L) * 4; ++i) {
+        const size_t n = (i % 4 == 2) ? qd : (i % 4 == 3 ? I : H);
+        if (desc->norms[i] == nullptr) {
+            if (i % 4 < 2) return fail(QUINTRIT_ERR_NULL_POINTER, "norm weights %zu are NULL", i);
+            if (desc->arch == QUINTRIT_B200_ARCH_BITNET) return fail(QUINTRIT_ERR_MODEL, "a BitNet model needs its sub-norm weights (%zu)", i);
+            continue;
+        }
+        if ((rc = dev_upload(d, &d->norms[i], desc->norms[i], n)) != QUINTRIT_OK) return rc;
+    }
+    const size_t kv_elems = size_t(L) * ctx * kvd;
+    if ((rc = dev_alloc(d, &d->kc, kv_elems)) != QUINTRIT_OK) return rc;  // zero-initialised like kv_cache.rs:24-46
+    if ((rc = dev_alloc(d, &d->vc, kv_elems)) != QUINTRIT_OK) return rc;
+    if ((rc = dev_alloc(d, &d->x, H)) != QUINTRIT_OK || (rc = dev_alloc(d, &d->q, qd)) != QUINTRIT_OK ||
+        (rc = dev_alloc(d, &d->x16, H)) != QUINTRIT_OK || (rc = dev_alloc(d, &d->part_acc, size_t(d->q_heads) * 4 * hd)) != QUINTRIT_OK ||
+        (rc = dev_alloc(d, &d->part_ms, size_t(d->q_heads) * 8)) != QUINTRIT_OK || (rc = dev_alloc(d, &d->logits, d->vocab)) != QUINTRIT_OK ||
+        (rc = dev_alloc(d, &d->a8_h, H + 16)) != QUINTRIT_OK || (rc = dev_alloc(d, &d->a8_q, qd + 16)) != QUINTRIT_OK ||
+        (rc = dev_alloc(d, &d->a8_i, I + 16)) != QUINTRIT_OK || (rc = dev_alloc(d, &d->s_h, 4)) != QUINTRIT_OK ||
+        (rc = dev_alloc(d, &d->s_q, 4)) != QUINTRIT_OK || (rc = dev_alloc(d, &d->s_i, 4)) != QUINTRIT_OK ||
+        (rc = dev_alloc(d, &d->acc_qkv, qd + 2 * kvd)) != QUINTRIT_OK || (rc = dev_alloc(d, &d->acc_o, H)) != QUINTRIT_OK ||
+        (rc = dev_alloc(d, &d->acc_gu, 2 * size_t(I))) != QUINTRIT_OK || (rc = dev_alloc(d, &d->acc_down, H)) != QUINTRIT_OK ||
+        (rc = dev_alloc(d, &d->d_token, 4)) != QUINTRIT_OK || (rc = dev_alloc(d, &d->d_pos, 4)) != QUINTRIT_OK ||
+        (rc = dev_alloc(d, &d->d_history, ctx + 1)) != QUINTRIT_OK || (rc = dev_alloc(d, &d->d_counters, 4)) != QUINTRIT_OK)
+        return rc;
+
+    // work items of the four GEMV launches of every layer
+    std::vector<GemvItem> items;
+    const size_t slots = size_t(d->sm_count) * kCtasPerSm;
+    auto tiles_of = [](const quintrit_b200_matrix* m) { return m->tiles * ((m->blocks + 1) / 2); };
+    for (uint32_t l = 0; l < L; ++l) {
+        const quintrit_b200_matrix* const* m = desc->matrices + size_t(l) * 7;
+        auto begin = [&]() { d->item_first.push_back(static_cast<int>(items.size())); };
+        auto end = [&]() { d->item_count.push_back(static_cast<int>(items.size()) - d->item_first.back()); };
+        begin();  // q | k | v share the activations and stack their results
+        size_t t = decoder_item_tiles(tiles_of(m[0]) + tiles_of(m[1]) + tiles_of(m[2]), slots);
+        build_items(items, m[0]->d_w, 0, 0, m[0]->rows, m[0]->cols, m[0]->blocks, m[0]->tiles, t);
+        build_items(items, m[1]->d_w, 0, qd, m[1]->rows, m[1]->cols, m[1]->blocks, m[1]->tiles, t);
+        build_items(items, m[2]->d_w, 0, qd + kvd, m[2]->rows, m[2]->cols, m[2]->blocks, m[2]->tiles, t);
+        end();
+        begin();
+        build_items(items, m[3]->d_w, 0, 0, m[3]->rows, m[3]->cols, m[3]->blocks, m[3]->tiles, decoder_item_tiles(tiles_of(m[3]), slots));
+        end();
+        begin();  // gate | up
+        t = decoder_item_tiles(tiles_of(m[4]) + tiles_of(m[5]), slots);
+        build_items(items, m[4]->d_w, 0, 0, m[4]->rows, m[4]->cols, m[4]->blocks, m[4]->tiles, t);
+        build_items(items, m[5]->d_w, 0, I, m[5]->rows, m[5]->cols, m[5]->blocks, m[5]->tiles, t);
+        end();
+        begin();
+        build_items(items, m[6]->d_w, 0, 0, m[6]->rows, m[6]->cols, m[6]->blocks, m[6]->tiles, decoder_item_tiles(tiles_of(m[6]), slots));
+        end();
+    }
+    if ((rc = dev_upload(d, &d->d_items, items.data(), items.size())) != QUINTRIT_OK) return rc;
+
+    // one-time kernel set-up, before any stream capture
+    GemvKernel k = nullptr;
+    if ((rc = gemv_kernel_for_device(d->device, &k)) != QUINTRIT_OK) return rc;
+    const int big = static_cast<int>(std::max<size_t>({H, I, qd}) * sizeof(float));
+    QTB_CUDA(cudaFuncSetAttribute(norm_quant_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+    QTB_CUDA(cudaFuncSetAttribute(attn_finish_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+    QTB_CUDA(cudaFuncSetAttribute(act_quant_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+    QTB_CUDA(cudaFuncSetAttribute(lm_head_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+    QTB_CUDA(cudaDeviceSynchronize());
+    return QUINTRIT_OK;
+}
+
+int decoder_step(quintrit_b200_decoder* d) {
+    int rc = decoder_graph(d);
+    if (rc != QUINTRIT_OK) return rc;
+    QTB_CUDA(cudaGraphLaunch(d->graph_step, d->stream));
+    return QUINTRIT_OK;
+}
+
+int decoder_check_status(quintrit_b200_decoder* d) {
+    unsigned int flag = 0;
+    QTB_CUDA(cudaMemcpyAsync(&flag, d->d_counters + 2, sizeof flag, cudaMemcpyDeviceToHost, d->stream));
+    QTB_CUDA(cudaStreamSynchronize(d->stream));
+    if (flag != 0) return fail(QUINTRIT_ERR_DEVICE, "GEMV kernel on the CUDA device found its shared-memory table at an unexpected address");
+    return QUINTRIT_OK;
+}
+
+}  // namespace
+
+extern "C" int quintrit_b200_decoder_create(const quintrit_b200_decoder_desc_t* desc, quintrit_b200_decoder_t** out_decoder) {
+    return guard([&]() -> int {
+        if (out_decoder == nullptr) return fail(QUINTRIT_ERR_NULL_POINTER, "out_decoder is NULL");
+        *out_decoder = nullptr;
+        if (desc == nullptr) return fail(QUINTRIT_ERR_NULL_POINTER, "desc is NULL");
+        quintrit_b200_decoder* d = nullptr;
+        int rc = decoder_create_impl(desc, &d);
+        if (rc != QUINTRIT_OK) {
+            destroy_decoder(d);
+            return rc;
+        }
+        *out_decoder = d;
+        return ok();
+    });
+}
+
+extern "C" int quintrit_b200_decoder_free(quintrit_b200_decoder_t* decoder) {
+    return guard([&]() -> int {
+        if (decoder == nullptr) return ok();
+        int rc = check_decoder(decoder);
+        if (rc != QUINTRIT_OK) return rc;
+        destroy_decoder(decoder);
+        return ok();
+    });
+}
+
+extern "C" int quintrit_b200_decoder_forward(quintrit_b200_decoder_t* decoder, uint32_t token, uint32_t pos, float* logits, size_t logits_capacity,
+                                             uint32_t* out_token) {
+    return guard([&]() -> int {
+        int rc = check_decoder(decoder);
+        if (rc != QUINTRIT_OK) return rc;
+        quintrit_b200_decoder* d = decoder;
+        if (token >= static_cast<uint32_t>(d->vocab)) return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "token id %u is not below the vocabulary size %d", token, d->vocab);
+        if (pos >= static_cast<uint32_t>(d->ctx)) return fail(QUINTRIT_ERR_CONTEXT_OVERFLOW, "position %u does not fit the context window of %d tokens", pos, d->ctx);
+        if (pos > d->host_pos) return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "position %u skips positions: %u tokens are cached", pos, d->host_pos);
+        if (logits != nullptr && logits_capacity < static_cast<size_t>(d->vocab)) return fail(QUINTRIT_ERR_BUFFER_TOO_SMALL, "logits hold %zu values, the vocabulary has %d", logits_capacity, d->vocab);
+        DeviceGuard g(d->device);
+        if ((rc = decoder_set(d, token, pos)) != QUINTRIT_OK || (rc = decoder_step(d)) != QUINTRIT_OK) return rc;
+        if (logits) QTB_CUDA(cudaMemcpyAsync(logits, d->logits, size_t(d->vocab) * sizeof(float), cudaMemcpyDeviceToHost, d->stream));
+        if (out_token) QTB_CUDA(cudaMemcpyAsync(out_token, d->d_token, sizeof(uint32_t), cudaMemcpyDeviceToHost, d->stream));
+        if ((rc = decoder_check_status(d)) != QUINTRIT_OK) return rc;
+        d->host_pos = pos + 1;
+        return ok();
+    });
+}
+
+extern "C" int quintrit_b200_decoder_generate(quintrit_b200_decoder_t* decoder, const uint32_t* prompt, size_t prompt_len, size_t max_new,
+                                              uint32_t* out_tokens, size_t out_capacity) {
+    return guard([&]() -> int {
+        int rc = check_decoder(decoder);
+        if (rc != QUINTRIT_OK) return rc;
+        quintrit_b200_decoder* d = decoder;
+        if (prompt == nullptr || out_tokens == nullptr) return fail(QUINTRIT_ERR_NULL_POINTER, "prompt or out_tokens is NULL");
+        if (prompt_len == 0 || max_new == 0) return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "the prompt and the number of new tokens must not be empty");
+        if (out_capacity < max_new) return fail(QUINTRIT_ERR_BUFFER_TOO_SMALL, "out_tokens hold %zu ids, %zu are needed", out_capacity, max_new);
+        if (prompt_len + max_new - 1 > static_cast<size_t>(d->ctx))
+            return fail(QUINTRIT_ERR_CONTEXT_OVERFLOW, "%zu prompt tokens and %zu new tokens do not fit the context window of %d tokens", prompt_len, max_new, d->ctx);
+        for (size_t i = 0; i < prompt_len; ++i)
+            if (prompt[i] >= static_cast<uint32_t>(d->vocab)) return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "token id %u is not below the vocabulary size %d", prompt[i], d->vocab);
+        DeviceGuard g(d->device);
+        uint32_t* d_prompt = nullptr;
+        QTB_CUDA(cudaMalloc(&d_prompt, prompt_len * sizeof(uint32_t)));
+        cudaError_t e = cudaMemcpyAsync(d_prompt, prompt, prompt_len * sizeof(uint32_t), cudaMemcpyHostToDevice, d->stream);
+        if (e == cudaSuccess) rc = decoder_set(d, prompt[0], 0);
+        for (size_t i = 0; e == cudaSuccess && rc == QUINTRIT_OK && i < prompt_len; ++i) {
+            rc = decoder_step(d);
+            if (rc == QUINTRIT_OK && i + 1 < prompt_len)  // the next prompt token replaces the prediction
+                e = cudaMemcpyAsync(d->d_token, d_prompt + i + 1, sizeof(uint32_t), cudaMemcpyDeviceToDevice, d->stream);
+        }
+        for (size_t j = 1; e == cudaSuccess && rc == QUINTRIT_OK && j < max_new; ++j) rc = decoder_step(d);
+        if (e == cudaSuccess && rc == QUINTRIT_OK)
+            e = cudaMemcpyAsync(out_tokens, d->d_history + (prompt_len - 1), max_new * sizeof(uint32_t), cudaMemcpyDeviceToHost, d->stream);
+        if (e == cudaSuccess && rc == QUINTRIT_OK) rc = decoder_check_status(d);
+        cudaStreamSynchronize(d->stream);
+        cudaFree(d_prompt);
+        if (e != cudaSuccess) return cuda_fail(e, "generate");
+        if (rc != QUINTRIT_OK) return rc;
+        d->host_pos = static_cast<uint32_t>(prompt_len + max_new - 1);
+        return ok();
+    });
+}
+
+extern "C" int quintrit_b200_decoder_time_token(quintrit_b200_decoder_t* decoder, uint32_t blocks, uint32_t iters, float* out_ms) {
+    return guard([&]() -> int {
+        int rc = check_decoder(decoder);
+        if (rc != QUINTRIT_OK) return rc;
+        quintrit_b200_decoder* d = decoder;
+        if (out_ms == nullptr) return fail(QUINTRIT_ERR_NULL_POINTER, "out_ms is NULL");
+        if (blocks == 0 || iters == 0) return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "blocks and iters must be at least 1");
+        if (d->host_pos == 0) return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "feed at least one token before timing a step");
+        DeviceGuard g(d->device);
+        const uint32_t pos = d->host_pos - 1, token = 0;
+        cudaEvent_t e0, e1;
+        QTB_CUDA(cudaEventCreate(&e0));
+        QTB_CUDA(cudaEventCreate(&e1));
+        float best = 1e30f;
+        if ((rc = decoder_graph(d)) != QUINTRIT_OK) return rc;
+        for (uint32_t b = 0; b < blocks; ++b) {
+            cudaEventRecord(e0, d->stream);
+            for (uint32_t i = 0; i < iters; ++i) {
+                decoder_set(d, token, pos);  // the step re-decodes the last position: the cache keeps its length
+                cudaGraphLaunch(d->graph_step, d->stream);
+            }
+            cudaEventRecord(e1, d->stream);
+            cudaEventSynchronize(e1);
+            float ms = 0;
+            cudaEventElapsedTime(&ms, e0, e1);
+            best = std::min(best, ms / iters);
+        }
+        cudaEventDestroy(e0);
+        cudaEventDestroy(e1);
+        QTB_CUDA(cudaGetLastError());
+        d->host_pos = pos;  // the timed steps overwrote the last position: it has to be fed again
+        *out_ms = best;
+        return ok();
+    });
 }

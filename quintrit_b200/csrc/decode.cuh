@@ -1,0 +1,579 @@
+// Float kernels of one decoded token (everything around the ternary GEMVs), written so that every value equals the
+// reference CPU runtime's bit for bit: rust/crates/quintrit-runtime/src/{ops.rs, attention.rs, model.rs}. The existing
+// sm_80 GPU twins in the reference are rust/crates/quintrit-cuda/kernels/layer.cu:21-580.
+//
+// Rules that keep the bits: no fused multiply-add unless the reference has one (explicit __fmaf_rn / __fmul_rn /
+// __fadd_rn / __fdiv_rn / __fsqrt_rn everywhere), the reference's reduction orders for the half dot products, the host
+// libm's cos/sin/pow through a table built on the host, glibc's expf restated in double (device_expf), F16 rounding
+// after every step of the attention accumulator.
+#pragma once
+#include <cstdint>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+namespace qtb {
+
+constexpr int kRowThreads = 1024;  // one block walks a whole activation vector
+
+// ---- block reductions (all threads get the result) ------------------------------------------------------------------
+__device__ __forceinline__ double block_sum_f64(double v, double* sh) {
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    const int w = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) sh[w] = v;
+    __syncthreads();
+    double t = 0.0;
+    for (int i = 0; i < nw; ++i) t += sh[i];
+    return t;
+}
+__device__ __forceinline__ float block_max_f32(float v, float* sh) {
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    const int w = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) sh[w] = v;
+    __syncthreads();
+    float t = 0.0f;
+    for (int i = 0; i < nw; ++i) t = fmaxf(t, sh[i]);
+    return t;
+}
+
+// ---- glibc expf (ops: attention.rs:423-428 call f32::exp = the platform libm) ---------------------------------------
+// The published table algorithm of glibc's single-precision exp: N = 32 entries of 2^(i/N) (bits, minus i << 47), a
+// cubic evaluated in double. The table is filled by the host (exp2_table_bits) so that no constant list is copied.
+__device__ __constant__ unsigned long long c_exp2_tab[32];
+
+__device__ __forceinline__ float device_expf(float x) {
+    const double inv_ln2_n = 0x1.71547652b82fep0 * 32.0, shift = 0x1.8p52;
+    const double c0 = 0x1.c6af84b912394p-5 / 32.0 / 32.0 / 32.0, c1 = 0x1.ebfce50fac4f3p-3 / 32.0 / 32.0, c2 = 0x1.62e42ff0c52d6p-1 / 32.0;
+    const uint32_t ix = __float_as_uint(x), abstop = (ix >> 20) & 0x7ffu;
+    if (abstop >= 0x42bu) {
+        if (ix == 0xff800000u) return 0.0f;
+        if (abstop >= 0x7f8u) return __fadd_rn(x, x);
+        if (x > 0x1.62e42ep6f) return __uint_as_float(0x7f800000u);
+        if (x < -0x1.9fe368p6f) return 0.0f;
+    }
+    const double xd = static_cast<double>(x);
+    const double z0 = __dmul_rn(inv_ln2_n, xd);
+    double kd = __dadd_rn(z0, shift);
+    const unsigned long long ki = static_cast<unsigned long long>(__double_as_longlong(kd));
+    kd = __dsub_rn(kd, shift);
+    const double r = __dsub_rn(z0, kd);
+    const unsigned long long t = c_exp2_tab[ki & 31ull] + (ki << 47);
+    const double s = __longlong_as_double(static_cast<long long>(t));
+    const double z = __fma_rn(c0, r, c1);
+    const double r2 = __dmul_rn(r, r);
+    double y = __fma_rn(c2, r, 1.0);
+    y = __fma_rn(z, r2, y);
+    y = __dmul_rn(y, s);
+    return __double2float_rn(y);
+}
+
+// ---- ggml's vector expf, one lane (ops.rs:316-387), and SiLU (ops.rs:389-399) ---------------------------------------
+__device__ __forceinline__ float ggml_expf_lane(float x) {
+    const float r = __uint_as_float(0x4b400000u);
+    const float z = __fmaf_rn(x, __uint_as_float(0x3fb8aa3bu), r);
+    const float n = __fsub_rn(z, r);
+    const float b = __fmaf_rn(-n, __uint_as_float(0x35bfbe8eu), __fmaf_rn(-n, __uint_as_float(0x3f317200u), x));
+    const uint32_t e = __float_as_uint(z) << 23;
+    const float k = __uint_as_float(e + 0x3f800000u);
+    const bool c = fabsf(n) > 126.0f;
+    const float u = __fmul_rn(b, b);
+    const float j = __fmaf_rn(__fmaf_rn(__fmaf_rn(__uint_as_float(0x3c072010u), b, __uint_as_float(0x3d2b9f17u)), u,
+                                        __fmaf_rn(__uint_as_float(0x3e2aaf33u), b, __uint_as_float(0x3efffedbu))),
+                              u, __fmul_rn(__uint_as_float(0x3f7ffff6u), b));
+    if (!c) return __fmaf_rn(j, k, k);
+    const uint32_t g = (n <= 0.0f) ? 0x82000000u : 0u;
+    const float s1 = __uint_as_float(g + 0x7f000000u);
+    const float s2 = __uint_as_float(e - g);
+    if (fabsf(n) > 192.0f) return __fmul_rn(s1, s1);
+    return __fmul_rn(__fmaf_rn(s2, j, s2), s1);
+}
+__device__ __forceinline__ float ggml_silu(float x) {
+    return __fdiv_rn(x, __fadd_rn(1.0f, ggml_expf_lane(__fsub_rn(0.0f, x))));
+}
+
+// ---- embedding row: model.rs:308-317 ---------------------------------------------------------------------------------
+__global__ void embed_kernel(const __half* __restrict__ table, const uint32_t* __restrict__ token, int hidden, float* __restrict__ x) {
+    const size_t base = static_cast<size_t>(token[0]) * hidden;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < hidden; i += gridDim.x * blockDim.x) x[i] = __half2float(table[base + i]);
+}
+
+// Arguments of the fused "finish the previous projection, normalise, quantise" kernel.
+struct NormQuantArgs {
+    float* x;                 // residual stream (hidden), updated in place when acc_prev != nullptr
+    const int32_t* acc_prev;  // int32 sums of the previous o / down projection (hidden), or nullptr
+    const float* scale_prev;  // activation scale that projection was fed with
+    float ws_prev;            // its weight scale
+    const float* norm_w;      // RMSNorm weights (hidden)
+    float eps;
+    int n;
+    int8_t* q_out;            // int8 codes (n), or nullptr: then the normalised vector is written to y_out as F16 bits (final norm)
+    float* scale_out;         // activation scale of q_out
+    __half* y16_out;          // F16 of the normalised vector (final norm before the output head)
+    int32_t* zero_a;          // result buffers of the next projections, cleared here (the GEMV adds into them)
+    int zero_a_n;
+    int32_t* zero_b;
+    int zero_b_n;
+};
+
+// x += acc * (ws / s)  (model.rs:85, 202 after layer.rs:143-147), y = rms_norm(x) (ops.rs:62-96), codes = quantise(y)
+// (ops.rs:241-267). One block.
+__global__ void __launch_bounds__(kRowThreads) norm_quant_kernel(NormQuantArgs a) {
+    __shared__ double sh_d[32];
+    __shared__ float sh_f[32];
+    extern __shared__ float y_s[];  // n floats
+    const int tid = threadIdx.x;
+    for (int i = tid; i < a.zero_a_n; i += kRowThreads) a.zero_a[i] = 0;
+    for (int i = tid; i < a.zero_b_n; i += kRowThreads) a.zero_b[i] = 0;
+    float post = 0.0f;
+    bool has_prev = a.acc_prev != nullptr;
+    if (has_prev) {
+        const float s = a.scale_prev[0];
+        post = s > 0.0f ? __fdiv_rn(a.ws_prev, s) : 0.0f;
+        if (!(s > 0.0f)) has_prev = false;  // layer.rs:148-150: a zero activation scale gives a zero projection
+    }
+    double sum = 0.0;
+    for (int i = tid; i < a.n; i += kRowThreads) {
+        float v = a.x[i];
+        if (a.acc_prev != nullptr) {
+            const float d = has_prev ? __fmul_rn(static_cast<float>(a.acc_prev[i]), post) : 0.0f;
+            v = __fadd_rn(v, d);
+            a.x[i] = v;
+        }
+        y_s[i] = v;
+        sum += static_cast<double>(__fmul_rn(v, v));
+    }
+    sum = block_sum_f64(sum, sh_d);
+    const float mean = __double2float_rn(sum / static_cast<double>(a.n));
+    const float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, a.eps)));
+    float amax = 0.0f;
+    for (int i = tid; i < a.n; i += kRowThreads) {
+        const float y = __fmul_rn(__fmul_rn(y_s[i], inv), a.norm_w[i]);
+        y_s[i] = y;
+        amax = fmaxf(amax, fabsf(y));
+    }
+    if (a.q_out == nullptr) {
+        for (int i = tid; i < a.n; i += kRowThreads) a.y16_out[i] = __float2half_rn(y_s[i]);
+        return;
+    }
+    amax = block_max_f32(amax, sh_f);
+    const float s = amax > 0.0f ? __fdiv_rn(127.0f, amax) : 0.0f;
+    for (int i = tid; i < a.n; i += kRowThreads) {
+        float q = 0.0f;
+        if (amax > 0.0f) {
+            q = roundf(__fmul_rn(y_s[i], s));
+            q = q != q ? 0.0f : fminf(fmaxf(q, -128.0f), 127.0f);
+        }
+        a.q_out[i] = static_cast<int8_t>(q);
+    }
+    if (tid == 0) a.scale_out[0] = s;
+}
+
+// ---- q/k/v finish: post-scale, RoPE, KV append (attention.rs:171-203, ops.rs:160-221) --------------------------------
+struct RopeKvArgs {
+    const int32_t* acc;       // stacked q | k | v sums (q_dim + 2 kv_dim)
+    const float* act_scale;
+    float ws_q, ws_k, ws_v;
+    const float* cos_sin;     // [ctx][rope_dims]: cos at 2i, sin at 2i+1, built on the host with the host libm
+    const uint32_t* pos;
+    int q_dim, kv_dim, head_dim, rope_dims, neox;
+    float* q_out;             // rotated query, F32 (q_dim)
+    __half* k_cache;          // [ctx][kv_dim] of this layer
+    __half* v_cache;
+};
+
+__global__ void rope_kv_kernel(RopeKvArgs a) {
+    const float s = a.act_scale[0];
+    const bool live = s > 0.0f;
+    const float pq = live ? __fdiv_rn(a.ws_q, s) : 0.0f, pk = live ? __fdiv_rn(a.ws_k, s) : 0.0f, pv = live ? __fdiv_rn(a.ws_v, s) : 0.0f;
+    const uint32_t pos = a.pos[0];
+    const float* cs = a.cos_sin + static_cast<size_t>(pos) * a.rope_dims;
+    const int half_pairs = a.rope_dims / 2;
+    const int total_pairs = (a.q_dim + a.kv_dim) / 2;
+    for (int t = blockIdx.x * blockDim.x + threadIdx.x; t < total_pairs + a.kv_dim; t += gridDim.x * blockDim.x) {
+        if (t >= total_pairs) {  // a value element: scale and append
+            const int i = t - total_pairs;
+            const float v = live ? __fmul_rn(static_cast<float>(a.acc[a.q_dim + a.kv_dim + i]), pv) : 0.0f;
+            a.v_cache[static_cast<size_t>(pos) * a.kv_dim + i] = __float2half_rn(v);
+            continue;
+        }
+        // pair index within q|k: head h, pair p of head_dim / 2
+        const int pairs_per_head = a.head_dim / 2;
+        const int h = t / pairs_per_head, p = t % pairs_per_head;
+        const bool is_q = h * a.head_dim < a.q_dim;
+        const int base = h * a.head_dim;  // offset inside q|k
+        int i0, i1;
+        bool rot;
+        if (a.neox) {  // pairs (i, i + n_dims/2) for i < n_dims/2; the rest passes through in pairs of its own
+            if (p < half_pairs) {
+                i0 = p;
+                i1 = p + half_pairs;
+                rot = true;
+            } else {
+                i0 = a.rope_dims + 2 * (p - half_pairs);
+                i1 = i0 + 1;
+                rot = false;
+            }
+        } else {
+            i0 = 2 * p;
+            i1 = i0 + 1;
+            rot = p < half_pairs;
+        }
+        const float post = is_q ? pq : pk;
+        float x0 = live ? __fmul_rn(static_cast<float>(a.acc[base + i0]), post) : 0.0f;
+        float x1 = live ? __fmul_rn(static_cast<float>(a.acc[base + i1]), post) : 0.0f;
+        if (rot) {
+            const int ci = a.neox ? p : p;
+            const float c = cs[2 * ci], sn = cs[2 * ci + 1];
+            const float r0 = __fmaf_rn(x0, c, -__fmul_rn(x1, sn));
+            const float r1 = __fmaf_rn(x0, sn, __fmul_rn(x1, c));
+            x0 = r0;
+            x1 = r1;
+        }
+        if (is_q) {
+            a.q_out[base + i0] = x0;
+            a.q_out[base + i1] = x1;
+        } else {
+            const size_t at = static_cast<size_t>(pos) * a.kv_dim + (base - a.q_dim);
+            a.k_cache[at + i0] = __float2half_rn(x0);
+            a.k_cache[at + i1] = __float2half_rn(x1);
+        }
+    }
+}
+
+// ---- attention of one query head over one chunk of the KV axis (attention.rs:402-469) --------------------------------
+// Grid (q_heads, chunks), 256 threads. Phase A: scores in the reference's dot-product order (one warp per position,
+// lane = accumulator lane). Phase B: running maximum, then ms / vs per position and the S chain. Phase C: the value
+// accumulator, one thread per coordinate, strictly in position order (F16 after every step, or F32 for llama.cpp files).
+struct AttnArgs {
+    const float* q;           // F32 queries (q_dim)
+    const __half* k_cache;    // [ctx][kv_dim]
+    const __half* v_cache;
+    const uint32_t* pos;
+    int head_dim, kv_dim, gqa, ctx, f32_values;
+    float scale;
+    float* part_acc;          // [q_heads][4][head_dim] chunk accumulators (as F32; the F16 ones are widened exactly)
+    float* part_ms;           // [q_heads][4][2]: M and S per chunk (S = 0 marks an empty chunk)
+};
+
+constexpr int kAttnThreads = 256;
+constexpr int kAttnMaxChunk = 2048;  // positions per chunk held in shared memory (context <= 8192)
+
+__device__ __forceinline__ float dot_lane_reduce_f16(float v) {  // (a0+a2)+(a1+a3), fold 4, two horizontal adds
+    v = __fadd_rn(v, __shfl_down_sync(0xffffffffu, v, 16));
+    v = __fadd_rn(v, __shfl_down_sync(0xffffffffu, v, 8));
+    v = __fadd_rn(v, __shfl_down_sync(0xffffffffu, v, 4));
+    v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 1));
+    v = __fadd_rn(v, __shfl_down_sync(0xffffffffu, v, 2));
+    return v;  // lane 0
+}
+__device__ __forceinline__ float dot_lane_reduce_f16_f32(float v) {  // (a0+a1)+(a2+a3), lanes ((l0+l4)+(l2+l6))+((l1+l5)+(l3+l7))
+    v = __fadd_rn(v, __shfl_down_sync(0xffffffffu, v, 8));
+    v = __fadd_rn(v, __shfl_down_sync(0xffffffffu, v, 16));
+    v = __fadd_rn(v, __shfl_down_sync(0xffffffffu, v, 4));
+    v = __fadd_rn(v, __shfl_down_sync(0xffffffffu, v, 2));
+    v = __fadd_rn(v, __shfl_down_sync(0xffffffffu, v, 1));
+    return v;  // lane 0
+}
+
+__global__ void __launch_bounds__(kAttnThreads) attention_kernel(AttnArgs a) {
+    __shared__ float s_score[kAttnMaxChunk];  // scores, then vs
+    __shared__ float s_ms[kAttnMaxChunk];     // prefix maximum, then ms
+    __shared__ float s_q[256];
+    const int h = blockIdx.x, c = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int hd = a.head_dim, kvh = h / a.gqa;
+    const int seq_len = static_cast<int>(a.pos[0]) + 1;
+    int n_kv = (seq_len + 255) / 256 * 256;
+    if (n_kv < 256) n_kv = 256;
+    if (n_kv > a.ctx) n_kv = a.ctx;
+    int start = 0, end = seq_len;
+    if (n_kv >= 512) {
+        const int chunk = (n_kv + 3) / 4;
+        start = c * chunk;
+        end = min(min(start + chunk, n_kv), seq_len);
+    } else if (c > 0) {
+        start = end;  // single-chunk case: chunks 1..3 are empty
+    }
+    float* my_acc = a.part_acc + (static_cast<size_t>(h) * 4 + c) * hd;
+    float* my_ms = a.part_ms + (static_cast<size_t>(h) * 4 + c) * 2;
+    const int len = end - start;
+    if (len <= 0) {
+        if (tid == 0) {
+            my_ms[0] = -INFINITY;
+            my_ms[1] = 0.0f;
+        }
+        return;
+    }
+    // the query: F16-rounded for bitnet.cpp numerics (attention.rs:212-214), F32 for llama.cpp numerics
+    for (int d = tid; d < hd; d += kAttnThreads) {
+        const float qv = a.q[h * hd + d];
+        s_q[d] = a.f32_values ? qv : __half2float(__float2half_rn(qv));
+    }
+    __syncthreads();
+    const __half* kbase = a.k_cache + static_cast<size_t>(kvh) * hd;
+    const __half* vbase = a.v_cache + static_cast<size_t>(kvh) * hd;
+    // Phase A
+    for (int p = warp; p < len; p += kAttnThreads / 32) {
+        const __half* kr = kbase + static_cast<size_t>(start + p) * a.kv_dim;
+        float acc = 0.0f;
+        int i = 0;
+        for (; i + 32 <= hd; i += 32) acc = __fmaf_rn(__half2float(kr[i + lane]), s_q[i + lane], acc);
+        float sc;
+        if (a.f32_values) {
+            sc = dot_lane_reduce_f16_f32(acc);
+        } else {
+            sc = dot_lane_reduce_f16(acc);
+        }
+        if (lane == 0) s_score[p] = __fmul_rn(sc, a.scale);
+    }
+    __syncthreads();
+    // Phase B: s_ms[p] = max(score[0..p]) by a block-wide inclusive scan in position order
+    {
+        const int per = (len + kAttnThreads - 1) / kAttnThreads;
+        const int p0 = tid * per, p1 = min(p0 + per, len);
+        float m = -INFINITY;
+        for (int p = p0; p < p1; ++p) m = fmaxf(m, s_score[p]);
+        __shared__ float s_tm[kAttnThreads];
+        s_tm[tid] = m;
+        __syncthreads();
+        float before = -INFINITY;
+        for (int t = 0; t < tid; ++t) before = fmaxf(before, s_tm[t]);
+        float run = before;
+        for (int p = p0; p < p1; ++p) {
+            const float sc = s_score[p];
+            const float m_old = run;
+            float ms = 1.0f, vs = 1.0f;
+            if (sc > run) {
+                run = sc;
+                ms = device_expf(__fsub_rn(m_old, run));
+            } else {
+                vs = device_expf(__fsub_rn(sc, run));
+            }
+            s_ms[p] = ms;
+            s_score[p] = vs;
+        }
+        __syncthreads();
+        if (tid == 0) {
+            float S = 0.0f, M = -INFINITY;
+            for (int t = 0; t < kAttnThreads; ++t) M = fmaxf(M, s_tm[t]);
+            for (int p = 0; p < len; ++p) S = __fmaf_rn(S, s_ms[p], s_score[p]);  // attention.rs:466
+            my_ms[0] = M;
+            my_ms[1] = S;
+        }
+    }
+    // Phase C
+    for (int d = tid; d < hd; d += kAttnThreads) {
+        const __half* vr = vbase + static_cast<size_t>(start) * a.kv_dim + d;
+        if (a.f32_values) {
+            float acc = 0.0f;
+            for (int p = 0; p < len; ++p) {
+                const float ms = s_ms[p];
+                if (ms != 1.0f) acc = __fmul_rn(acc, ms);
+                acc = __fmaf_rn(__half2float(vr[static_cast<size_t>(p) * a.kv_dim]), s_score[p], acc);
+            }
+            my_acc[d] = acc;
+        } else {
+            __half acc = __float2half_rn(0.0f);
+            for (int p = 0; p < len; ++p) {
+                const float ms = s_ms[p];
+                if (ms != 1.0f) acc = __float2half_rn(__fmul_rn(__half2float(acc), ms));
+                acc = __float2half_rn(__fmaf_rn(__half2float(vr[static_cast<size_t>(p) * a.kv_dim]), s_score[p], __half2float(acc)));
+            }
+            my_acc[d] = __half2float(acc);
+        }
+    }
+}
+
+// ---- combine the KV chunks (attention.rs:497-541), optional sub-norm, quantise for the o projection -------------------
+struct AttnFinishArgs {
+    const float* part_acc;    // [q_heads][4][head_dim]
+    const float* part_ms;     // [q_heads][4][2]
+    const uint32_t* pos;
+    int q_heads, head_dim, ctx;
+    const float* sub_norm_w;  // BitNet attn_sub_norm (q_dim) or nullptr
+    float eps;
+    int8_t* q_out;
+    float* scale_out;
+    int32_t* zero_a;          // result buffer of the o projection
+    int zero_a_n;
+};
+
+__global__ void __launch_bounds__(kRowThreads) attn_finish_kernel(AttnFinishArgs a) {
+    __shared__ double sh_d[32];
+    __shared__ float sh_f[32];
+    extern __shared__ float y_s[];  // q_dim floats
+    const int tid = threadIdx.x, hd = a.head_dim, n = a.q_heads * hd;
+    for (int i = tid; i < a.zero_a_n; i += kRowThreads) a.zero_a[i] = 0;
+    const int seq_len = static_cast<int>(a.pos[0]) + 1;
+    int n_kv = (seq_len + 255) / 256 * 256;
+    if (n_kv < 256) n_kv = 256;
+    if (n_kv > a.ctx) n_kv = a.ctx;
+    for (int i = tid; i < n; i += kRowThreads) {
+        const int h = i / hd, d = i % hd;
+        const float* pa = a.part_acc + static_cast<size_t>(h) * 4 * hd + d;
+        const float* pm = a.part_ms + static_cast<size_t>(h) * 8;
+        float out;
+        if (n_kv < 512) {
+            const float S = pm[1];
+            const float s_inv = S == 0.0f ? 0.0f : __fdiv_rn(1.0f, S);
+            out = __fmul_rn(pa[0], s_inv);
+        } else {
+            float m_final = -INFINITY, s_final = 0.0f, acc = 0.0f;
+            for (int c = 0; c < 4; ++c) {
+                const float m_chunk = pm[2 * c], s_chunk = pm[2 * c + 1];
+                if (s_chunk == 0.0f) continue;  // empty or fully masked chunk
+                const float m_new = fmaxf(m_final, m_chunk);
+                const float scale_old = device_expf(__fsub_rn(m_final, m_new));
+                const float scale_new = device_expf(__fsub_rn(m_chunk, m_new));
+                acc = __fmaf_rn(acc, scale_old, __fmul_rn(pa[c * hd], scale_new));
+                s_final = __fmaf_rn(s_final, scale_old, __fmul_rn(s_chunk, scale_new));
+                m_final = m_new;
+            }
+            out = s_final != 0.0f ? __fmul_rn(acc, __fdiv_rn(1.0f, s_final)) : acc;
+        }
+        y_s[i] = out;
+    }
+    __syncthreads();
+    if (a.sub_norm_w != nullptr) {
+        double sum = 0.0;
+        for (int i = tid; i < n; i += kRowThreads) sum += static_cast<double>(__fmul_rn(y_s[i], y_s[i]));
+        sum = block_sum_f64(sum, sh_d);
+        const float mean = __double2float_rn(sum / static_cast<double>(n));
+        const float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, a.eps)));
+        for (int i = tid; i < n; i += kRowThreads) y_s[i] = __fmul_rn(__fmul_rn(y_s[i], inv), a.sub_norm_w[i]);
+    }
+    float amax = 0.0f;
+    for (int i = tid; i < n; i += kRowThreads) amax = fmaxf(amax, fabsf(y_s[i]));
+    amax = block_max_f32(amax, sh_f);
+    const float s = amax > 0.0f ? __fdiv_rn(127.0f, amax) : 0.0f;
+    for (int i = tid; i < n; i += kRowThreads) {
+        float q = 0.0f;
+        if (amax > 0.0f) {
+            q = roundf(__fmul_rn(y_s[i], s));
+            q = q != q ? 0.0f : fminf(fmaxf(q, -128.0f), 127.0f);
+        }
+        a.q_out[i] = static_cast<int8_t>(q);
+    }
+    if (tid == 0) a.scale_out[0] = s;
+}
+
+// ---- gate / up finish: post-scale, SwiGLU or relu^2 * up, optional sub-norm, quantise for the down projection ---------
+// (model.rs:150-193; ops.rs:301-308, 427-473)
+struct ActQuantArgs {
+    const int32_t* acc_gate;
+    const int32_t* acc_up;
+    const float* act_scale;
+    float ws_gate, ws_up;
+    int n, relu2;
+    const float* sub_norm_w;  // BitNet ffn_sub_norm (n) or nullptr
+    float eps;
+    int8_t* q_out;
+    float* scale_out;
+    int32_t* zero_a;          // result buffer of the down projection
+    int zero_a_n;
+};
+
+__global__ void __launch_bounds__(kRowThreads) act_quant_kernel(ActQuantArgs a) {
+    __shared__ double sh_d[32];
+    __shared__ float sh_f[32];
+    extern __shared__ float y_s[];  // n floats
+    const int tid = threadIdx.x;
+    for (int i = tid; i < a.zero_a_n; i += kRowThreads) a.zero_a[i] = 0;
+    const float s_in = a.act_scale[0];
+    const bool live = s_in > 0.0f;
+    const float pg = live ? __fdiv_rn(a.ws_gate, s_in) : 0.0f, pu = live ? __fdiv_rn(a.ws_up, s_in) : 0.0f;
+    for (int i = tid; i < a.n; i += kRowThreads) {
+        const float g = live ? __fmul_rn(static_cast<float>(a.acc_gate[i]), pg) : 0.0f;
+        const float u = live ? __fmul_rn(static_cast<float>(a.acc_up[i]), pu) : 0.0f;
+        float v;
+        if (a.relu2) {
+            const float p = g > 0.0f ? g : 0.0f;
+            v = __fmul_rn(__fmul_rn(p, p), u);
+        } else {
+            v = __fmul_rn(ggml_silu(g), u);
+        }
+        y_s[i] = v;
+    }
+    __syncthreads();
+    if (a.sub_norm_w != nullptr) {
+        double sum = 0.0;
+        for (int i = tid; i < a.n; i += kRowThreads) sum += static_cast<double>(__fmul_rn(y_s[i], y_s[i]));
+        sum = block_sum_f64(sum, sh_d);
+        const float mean = __double2float_rn(sum / static_cast<double>(a.n));
+        const float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, a.eps)));
+        for (int i = tid; i < a.n; i += kRowThreads) y_s[i] = __fmul_rn(__fmul_rn(y_s[i], inv), a.sub_norm_w[i]);
+    }
+    float amax = 0.0f;
+    for (int i = tid; i < a.n; i += kRowThreads) amax = fmaxf(amax, fabsf(y_s[i]));
+    amax = block_max_f32(amax, sh_f);
+    const float s = amax > 0.0f ? __fdiv_rn(127.0f, amax) : 0.0f;
+    for (int i = tid; i < a.n; i += kRowThreads) {
+        float q = 0.0f;
+        if (amax > 0.0f) {
+            q = roundf(__fmul_rn(y_s[i], s));
+            q = q != q ? 0.0f : fminf(fmaxf(q, -128.0f), 127.0f);
+        }
+        a.q_out[i] = static_cast<int8_t>(q);
+    }
+    if (tid == 0) a.scale_out[0] = s;
+}
+
+// ---- output head: one warp per vocabulary row, ggml_vec_dot_f16 order (model.rs:346-375, ops.rs:970-1014) --------------
+__global__ void __launch_bounds__(256) lm_head_kernel(const __half* __restrict__ w, const __half* __restrict__ x16, int hidden, int vocab,
+                                                      float* __restrict__ logits) {
+    extern __shared__ float x_s[];  // hidden floats
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) x_s[i] = __half2float(x16[i]);
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    const int np = hidden & ~31;
+    for (int row = blockIdx.x * warps + (threadIdx.x >> 5); row < vocab; row += gridDim.x * warps) {
+        const __half* wr = w + static_cast<size_t>(row) * hidden;
+        float acc = 0.0f;
+#pragma unroll 8
+        for (int i = 0; i < np; i += 32) acc = __fmaf_rn(x_s[i + lane], __half2float(wr[i + lane]), acc);
+        float sum = dot_lane_reduce_f16(acc);
+        if (lane == 0) {
+            for (int i = np; i < hidden; ++i) sum = __fadd_rn(sum, __fmul_rn(x_s[i], __half2float(wr[i])));
+            logits[row] = sum;
+        }
+    }
+}
+
+// ---- greedy sampler: first index of the strict maximum, NaN never wins (sampler.rs:73-83) ------------------------------
+__device__ __forceinline__ void argmax_merge(float& bv, unsigned int& bi, float v, unsigned int i) {
+    if (v > bv || (v == bv && i < bi)) {
+        bv = v;
+        bi = i;
+    }
+}
+__global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ logits, int n, uint32_t* __restrict__ out_token) {
+    __shared__ float sv[32];
+    __shared__ unsigned int si[32];
+    float bv = -INFINITY;
+    unsigned int bi = 0xFFFFFFFFu;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const float v = logits[i];
+        if (v > bv) {  // strict: the earlier index stays on ties
+            bv = v;
+            bi = static_cast<unsigned int>(i);
+        }
+    }
+    for (int o = 16; o > 0; o >>= 1) argmax_merge(bv, bi, __shfl_xor_sync(0xffffffffu, bv, o), __shfl_xor_sync(0xffffffffu, bi, o));
+    if ((threadIdx.x & 31) == 0) {
+        sv[threadIdx.x >> 5] = bv;
+        si[threadIdx.x >> 5] = bi;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < 32; ++w) argmax_merge(bv, bi, sv[w], si[w]);
+        out_token[0] = bi == 0xFFFFFFFFu ? 0u : bi;  // all NaN / -inf: index 0, as the reference's loop leaves it
+    }
+}
+
+// next position (the generation loop runs on the device: the token comes from argmax_kernel, the position from here)
+__global__ void advance_kernel(uint32_t* pos, uint32_t* history, const uint32_t* token) {
+    history[pos[0]] = token[0];
+    pos[0] += 1;
+}
+
+}  // namespace qtb

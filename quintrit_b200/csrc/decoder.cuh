@@ -1,0 +1,240 @@
+// Whole-token decoder on the device: buffers, launch sequence, CUDA graph, greedy generation loop. Included by capi.cu.
+// Host-side counterpart in the reference: rust/crates/quintrit-runtime/src/gpu.rs (GpuModel::load :183-260, new_session
+// :289-339, enqueue :389-453, forward :459-493, time_token :346-370).
+#pragma once
+#include <cmath>
+#include <cstring>
+#include <vector>
+
+#include "capi_common.cuh"
+#include "decode.cuh"
+#include "gemv_lut.cuh"
+
+struct quintrit_b200_decoder {
+    uint32_t magic;
+    int device, sm_count;
+    int arch, f32_values;
+    int hidden, inter, layers, q_heads, kv_heads, head_dim, vocab, ctx, rope_dims;
+    int q_dim, kv_dim;
+    float eps, rope_theta;
+    std::vector<float> scales;  // layers * 7
+    // device memory
+    std::vector<void*> allocs;
+    __half *embed, *lm_head, *kc, *vc, *x16;
+    float *out_norm, *cos_sin, *x, *q, *part_acc, *part_ms, *logits;
+    std::vector<float*> norms;  // layers * 4 (device)
+    int8_t *a8_h, *a8_q, *a8_i;
+    float *s_h, *s_q, *s_i;
+    int32_t *acc_qkv, *acc_o, *acc_gu, *acc_down;
+    uint32_t *d_token, *d_pos, *d_history;
+    unsigned int* d_counters;
+    qtb::GemvItem* d_items;
+    std::vector<int> item_first, item_count;  // layers * 4 launches: qkv, o, gate+up, down
+    cudaStream_t stream;
+    cudaGraphExec_t graph_step;               // one token: embed ... argmax (token and position read from device memory)
+    bool graph_ready;
+    uint32_t host_pos;                         // tokens in the KV cache
+};
+
+namespace qtb {
+
+constexpr uint32_t kMagicDecoder = 0x51544244u;  // "QTBD"
+
+inline int check_decoder(const quintrit_b200_decoder* d) {
+    if (d == nullptr || d->magic != kMagicDecoder) return fail(QUINTRIT_ERR_INVALID_HANDLE, "decoder handle is NULL, freed or of the wrong type");
+    return QUINTRIT_OK;
+}
+
+template <typename T>
+int dev_alloc(quintrit_b200_decoder* d, T** p, size_t count, bool zero = true) {
+    void* q = nullptr;
+    const size_t bytes = std::max<size_t>(count * sizeof(T), 16);
+    cudaError_t e = cudaMalloc(&q, bytes);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc(decoder buffer)");
+    d->allocs.push_back(q);
+    if (zero && (e = cudaMemset(q, 0, bytes)) != cudaSuccess) return cuda_fail(e, "cudaMemset(decoder buffer)");
+    *p = static_cast<T*>(q);
+    return QUINTRIT_OK;
+}
+template <typename T>
+int dev_upload(quintrit_b200_decoder* d, T** p, const void* host, size_t count) {
+    int rc = dev_alloc(d, p, count, false);
+    if (rc != QUINTRIT_OK) return rc;
+    QTB_CUDA(cudaMemcpy(*p, host, count * sizeof(T), cudaMemcpyHostToDevice));
+    return QUINTRIT_OK;
+}
+
+inline void destroy_decoder(quintrit_b200_decoder* d) {
+    if (d == nullptr) return;
+    int prev = -1;
+    cudaGetDevice(&prev);
+    cudaSetDevice(d->device);
+    if (d->graph_ready) cudaGraphExecDestroy(d->graph_step);
+    if (d->stream) cudaStreamDestroy(d->stream);
+    for (void* p : d->allocs) cudaFree(p);
+    if (prev >= 0) cudaSetDevice(prev);
+    d->magic = 0;
+    delete d;
+}
+
+// Enqueues one GEMV launch (its items were built at creation) on the decoder's stream.
+inline int decoder_gemv(quintrit_b200_decoder* d, int layer, int which, const int8_t* act, int32_t* out) {
+    const int k = layer * 4 + which;
+    return launch_gemv(d->d_items + d->item_first[k], d->item_count[k], act, out, d->d_counters, d->sm_count, d->stream);
+}
+
+#define QTB_LAUNCH_CHECK()                                   \
+    do {                                                     \
+        ++g_launches;                                        \
+        cudaError_t qtb_e_ = cudaGetLastError();             \
+        if (qtb_e_ != cudaSuccess) return cuda_fail(qtb_e_, "kernel launch"); \
+    } while (0)
+
+// The launch sequence of one token (gpu.rs:389-453 reshaped: 4 GEMV launches and 5 float kernels per layer).
+inline int enqueue_token(quintrit_b200_decoder* d, bool with_head) {
+    cudaStream_t s = d->stream;
+    const int H = d->hidden, I = d->inter, qd = d->q_dim, kvd = d->kv_dim;
+    embed_kernel<<<(H + 255) / 256, 256, 0, s>>>(d->embed, d->d_token, H, d->x);
+    QTB_LAUNCH_CHECK();
+    for (int l = 0; l < d->layers; ++l) {
+        const float* sc = d->scales.data() + l * 7;
+        NormQuantArgs n1{};
+        n1.x = d->x;
+        if (l > 0) {
+            n1.acc_prev = d->acc_down;
+            n1.scale_prev = d->s_i;
+            n1.ws_prev = d->scales[(l - 1) * 7 + 6];
+        }
+        n1.norm_w = d->norms[l * 4 + 0];
+        n1.eps = d->eps;
+        n1.n = H;
+        n1.q_out = d->a8_h;
+        n1.scale_out = d->s_h;
+        n1.zero_a = d->acc_qkv;
+        n1.zero_a_n = qd + 2 * kvd;
+        norm_quant_kernel<<<1, kRowThreads, H * sizeof(float), s>>>(n1);
+        QTB_LAUNCH_CHECK();
+        int rc = decoder_gemv(d, l, 0, d->a8_h, d->acc_qkv);
+        if (rc != QUINTRIT_OK) return rc;
+        RopeKvArgs rk{};
+        rk.acc = d->acc_qkv;
+        rk.act_scale = d->s_h;
+        rk.ws_q = sc[0], rk.ws_k = sc[1], rk.ws_v = sc[2];
+        rk.cos_sin = d->cos_sin;
+        rk.pos = d->d_pos;
+        rk.q_dim = qd, rk.kv_dim = kvd, rk.head_dim = d->head_dim, rk.rope_dims = d->rope_dims, rk.neox = d->arch == QUINTRIT_B200_ARCH_BITNET;
+        rk.q_out = d->q;
+        rk.k_cache = d->kc + static_cast<size_t>(l) * d->ctx * kvd;
+        rk.v_cache = d->vc + static_cast<size_t>(l) * d->ctx * kvd;
+        rope_kv_kernel<<<((qd + kvd) / 2 + kvd + 255) / 256, 256, 0, s>>>(rk);
+        QTB_LAUNCH_CHECK();
+        AttnArgs at{};
+        at.q = d->q;
+        at.k_cache = rk.k_cache;
+        at.v_cache = rk.v_cache;
+        at.pos = d->d_pos;
+        at.head_dim = d->head_dim, at.kv_dim = kvd, at.gqa = d->q_heads / d->kv_heads, at.ctx = d->ctx, at.f32_values = d->f32_values;
+        at.scale = 1.0f / std::sqrt(static_cast<float>(d->head_dim));  // attention.rs:46
+        at.part_acc = d->part_acc;
+        at.part_ms = d->part_ms;
+        attention_kernel<<<dim3(d->q_heads, 4), kAttnThreads, 0, s>>>(at);
+        QTB_LAUNCH_CHECK();
+        AttnFinishArgs af{};
+        af.part_acc = d->part_acc;
+        af.part_ms = d->part_ms;
+        af.pos = d->d_pos;
+        af.q_heads = d->q_heads, af.head_dim = d->head_dim, af.ctx = d->ctx;
+        af.sub_norm_w = d->norms[l * 4 + 2];
+        af.eps = d->eps;
+        af.q_out = d->a8_q;
+        af.scale_out = d->s_q;
+        af.zero_a = d->acc_o;
+        af.zero_a_n = H;
+        attn_finish_kernel<<<1, kRowThreads, qd * sizeof(float), s>>>(af);
+        QTB_LAUNCH_CHECK();
+        rc = decoder_gemv(d, l, 1, d->a8_q, d->acc_o);
+        if (rc != QUINTRIT_OK) return rc;
+        NormQuantArgs n2{};
+        n2.x = d->x;
+        n2.acc_prev = d->acc_o;
+        n2.scale_prev = d->s_q;
+        n2.ws_prev = sc[3];
+        n2.norm_w = d->norms[l * 4 + 1];
+        n2.eps = d->eps;
+        n2.n = H;
+        n2.q_out = d->a8_h;
+        n2.scale_out = d->s_h;
+        n2.zero_a = d->acc_gu;
+        n2.zero_a_n = 2 * I;
+        norm_quant_kernel<<<1, kRowThreads, H * sizeof(float), s>>>(n2);
+        QTB_LAUNCH_CHECK();
+        rc = decoder_gemv(d, l, 2, d->a8_h, d->acc_gu);
+        if (rc != QUINTRIT_OK) return rc;
+        ActQuantArgs aq{};
+        aq.acc_gate = d->acc_gu;
+        aq.acc_up = d->acc_gu + I;
+        aq.act_scale = d->s_h;
+        aq.ws_gate = sc[4], aq.ws_up = sc[5];
+        aq.n = I, aq.relu2 = d->arch == QUINTRIT_B200_ARCH_BITNET;
+        aq.sub_norm_w = d->norms[l * 4 + 3];
+        aq.eps = d->eps;
+        aq.q_out = d->a8_i;
+        aq.scale_out = d->s_i;
+        aq.zero_a = d->acc_down;
+        aq.zero_a_n = H;
+        act_quant_kernel<<<1, kRowThreads, I * sizeof(float), s>>>(aq);
+        QTB_LAUNCH_CHECK();
+        rc = decoder_gemv(d, l, 3, d->a8_i, d->acc_down);
+        if (rc != QUINTRIT_OK) return rc;
+    }
+    if (with_head) {
+        NormQuantArgs nf{};
+        nf.x = d->x;
+        nf.acc_prev = d->acc_down;
+        nf.scale_prev = d->s_i;
+        nf.ws_prev = d->scales[(d->layers - 1) * 7 + 6];
+        nf.norm_w = d->out_norm;
+        nf.eps = d->eps;
+        nf.n = H;
+        nf.y16_out = d->x16;
+        norm_quant_kernel<<<1, kRowThreads, H * sizeof(float), s>>>(nf);
+        QTB_LAUNCH_CHECK();
+        lm_head_kernel<<<d->sm_count * 8, 256, H * sizeof(float), s>>>(d->lm_head, d->x16, H, d->vocab, d->logits);
+        QTB_LAUNCH_CHECK();
+        argmax_kernel<<<1, 1024, 0, s>>>(d->logits, d->vocab, d->d_token);
+        QTB_LAUNCH_CHECK();
+    }
+    return QUINTRIT_OK;
+}
+
+// Sets the device-side position and token from host values.
+inline int decoder_set(quintrit_b200_decoder* d, uint32_t token, uint32_t pos) {
+    QTB_CUDA(cudaMemcpyAsync(d->d_token, &token, sizeof token, cudaMemcpyHostToDevice, d->stream));
+    QTB_CUDA(cudaMemcpyAsync(d->d_pos, &pos, sizeof pos, cudaMemcpyHostToDevice, d->stream));
+    return QUINTRIT_OK;
+}
+
+// Captures [one token + advance] into a graph the first time it is needed.
+inline int decoder_graph(quintrit_b200_decoder* d) {
+    if (d->graph_ready) return QUINTRIT_OK;
+    cudaGraph_t g = nullptr;
+    QTB_CUDA(cudaStreamBeginCapture(d->stream, cudaStreamCaptureModeThreadLocal));
+    int rc = enqueue_token(d, true);
+    if (rc == QUINTRIT_OK) {
+        advance_kernel<<<1, 1, 0, d->stream>>>(d->d_pos, d->d_history, d->d_token);
+        ++g_launches;
+    }
+    cudaError_t e = cudaStreamEndCapture(d->stream, &g);
+    if (rc != QUINTRIT_OK) {
+        if (g) cudaGraphDestroy(g);
+        return rc;
+    }
+    if (e != cudaSuccess) return cuda_fail(e, "cudaStreamEndCapture");
+    e = cudaGraphInstantiate(&d->graph_step, g, 0);
+    cudaGraphDestroy(g);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGraphInstantiate");
+    d->graph_ready = true;
+    return QUINTRIT_OK;
+}
+
+}  // namespace qtb

@@ -112,3 +112,36 @@ def quantize_int8_np(x: np.ndarray):
     y = x * s
     q = np.sign(y) * np.floor(np.abs(y) + np.float32(0.5))
     return np.clip(q, -128, 127).astype(np.int8), s
+
+
+def make_model(arch: int, f32_values: bool, hidden: int, inter: int, layers: int, q_heads: int, kv_heads: int, head_dim: int, vocab: int,
+               ctx: int, rope_theta: float, eps: float, config: int = 1, tied: bool = False, rope_dims: int | None = None,
+               random_norms: bool = False) -> dict:
+    """A seeded random-init model of the given shape as numpy arrays (planar velurex projections, F16 tables).
+
+    Ternary projections and their scales come from the streams documented at the top of this module; embedding and
+    output head are N(0, 0.02) rounded to F16; norm weights are 1.0 (or U(0.5, 1.5) with ``random_norms``, which
+    exercises the weight multiply in tests). ``arch`` 1 (BitNet) gets attention and FFN sub-norm weights.
+    """
+    from . import api
+
+    qd, kvd = q_heads * head_dim, kv_heads * head_dim
+    shapes = [(qd, hidden), (kvd, hidden), (kvd, hidden), (hidden, qd), (inter, hidden), (inter, hidden), (hidden, inter)]
+    weights, scales, norms = [], [], []
+
+    def norm(seed, n):
+        if not random_norms:
+            return np.ones(n, np.float32)
+        return (np.float32(0.5) + splitmix_u32(seed, 0, n).astype(np.float32) / np.float32(4294967296.0)).astype(np.float32)
+
+    for l in range(layers):
+        for p, (rows, cols) in enumerate(shapes):
+            weights.append(api.pack_planar(trits(seed_for(config, l, p, 0), rows * cols), rows, cols))
+            scales.append(weight_scale(seed_for(config, l, p, 1)))
+        norms += [norm(seed_for(config, l, 7, 0), hidden), norm(seed_for(config, l, 7, 1), hidden),
+                  norm(seed_for(config, l, 7, 2), qd) if arch == 1 else None, norm(seed_for(config, l, 7, 3), inter) if arch == 1 else None]
+    embed = (normal_f32(seed_for(config, 255, 0, 0), vocab * hidden) * np.float32(0.02)).astype(np.float16).view(np.uint16)
+    head = None if tied else (normal_f32(seed_for(config, 255, 1, 0), vocab * hidden) * np.float32(0.02)).astype(np.float16).view(np.uint16)
+    return dict(arch=arch, f32_values=f32_values, hidden=hidden, inter=inter, layers=layers, q_heads=q_heads, kv_heads=kv_heads,
+                head_dim=head_dim, vocab=vocab, ctx=ctx, rope_dims=rope_dims or head_dim, eps=eps, rope_theta=rope_theta, weights=weights,
+                scales=np.array(scales, np.float32), norms=norms, embed=embed, lm_head=head, out_norm=norm(seed_for(config, 255, 2, 0), hidden))

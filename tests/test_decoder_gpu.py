@@ -1,0 +1,85 @@
+"""GPU parity of the whole-token decoder through the C ABI against the CPU oracle: logits bit for bit, greedy tokens equal.
+
+Mirrors rust/crates/quintrit-c/tests/engine_gpu.rs:23-100 (a small synthetic model, logits bit-equal at every position,
+positions crossing the 256 / 512 padding and the split-KV borders, restart from a shorter prefix) and
+rust/crates/quintrit-runtime/tests/gpu_layers.rs:346-408 (head geometries).
+"""
+import numpy as np
+import pytest
+
+import quintrit_b200 as q
+from quintrit_b200 import synth
+
+pytestmark = pytest.mark.gpu
+
+
+def _run(spec, tokens, oracle, check_every=1):
+    dec = q.Decoder(spec)
+    ref = oracle.Model(spec)
+    for pos, tok in enumerate(tokens):
+        want = ref.forward(int(tok), pos)
+        got, greedy = dec.forward(int(tok), pos, want_logits=(pos % check_every == 0 or pos == len(tokens) - 1))
+        if got is not None:
+            assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), f"logits differ at position {pos}"
+        assert greedy == oracle.argmax(want), pos
+    return dec, ref
+
+
+@pytest.mark.parametrize("arch,f32_values,q_heads,kv_heads,head_dim", [
+    (q.ARCH_LLAMA, False, 4, 2, 64), (q.ARCH_LLAMA, True, 4, 2, 64), (q.ARCH_BITNET, False, 4, 1, 128),
+    (q.ARCH_BITNET, True, 2, 2, 128), (q.ARCH_LLAMA, False, 3, 1, 256), (q.ARCH_LLAMA, False, 4, 4, 32)])
+def test_logits_are_bit_equal_at_every_position(oracle, arch, f32_values, q_heads, kv_heads, head_dim):
+    hidden = 320 if head_dim != 256 else 512
+    spec = synth.make_model(arch, f32_values, hidden, 704, 2, q_heads, kv_heads, head_dim, 300, 256, 500000.0, 1e-5, config=9, random_norms=True)
+    rng = np.random.default_rng(1)
+    _run(spec, rng.integers(0, 300, 40), oracle)
+
+
+@pytest.mark.parametrize("f32_values", [False, True])
+def test_long_context_crosses_every_split_border(oracle, f32_values):
+    # context 1280 as the reference's engine test: 255 / 256 / 257, 511 / 512 / 513, chunk borders of 768, 1024, 1280
+    spec = synth.make_model(q.ARCH_LLAMA, f32_values, 128, 256, 1, 2, 1, 64, 264, 1280, 10000.0, 1e-6, config=11, tied=True)
+    rng = np.random.default_rng(2)
+    _run(spec, rng.integers(0, 264, 1100), oracle, check_every=1)
+
+
+def test_restart_from_a_shorter_prefix_and_generate(oracle):
+    spec = synth.make_model(q.ARCH_BITNET, False, 256, 512, 2, 4, 2, 64, 500, 512, 500000.0, 1e-5, config=12, tied=True)
+    rng = np.random.default_rng(3)
+    prompt = rng.integers(0, 500, 24)
+    dec, ref = _run(spec, prompt, oracle)
+    # rewrite positions 10.. with other tokens (engine_gpu.rs:40-45)
+    other = rng.integers(0, 500, 8)
+    for i, tok in enumerate(other):
+        want = ref.forward(int(tok), 10 + i)
+        got, _ = dec.forward(int(tok), 10 + i)
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    # greedy generation on the device equals the oracle's loop
+    ref2 = oracle.Model(spec)
+    tok = None
+    for pos, t in enumerate(prompt):
+        tok = oracle.argmax(ref2.forward(int(t), pos))
+    want_tokens = [tok]
+    for j in range(1, 48):
+        tok = oracle.argmax(ref2.forward(int(tok), len(prompt) + j - 1))
+        want_tokens.append(tok)
+    got_tokens = dec.generate(prompt, 48)
+    assert list(got_tokens) == want_tokens
+    assert dec.time_token(2, 5) > 0
+
+
+def test_invalid_decoder_calls():
+    spec = synth.make_model(q.ARCH_LLAMA, False, 128, 256, 1, 2, 1, 64, 64, 256, 10000.0, 1e-5, config=13, tied=True)
+    dec = q.Decoder(spec)
+    with pytest.raises(q.QuintritError) as e:
+        dec.forward(64, 0)
+    assert e.value.code == 2
+    with pytest.raises(q.QuintritError) as e:
+        dec.forward(1, 3)  # skips positions
+    assert e.value.code == 2
+    with pytest.raises(q.QuintritError) as e:
+        dec.generate(np.arange(10), 300)
+    assert e.value.code == 11
+    bad = dict(spec, head_dim=48, q_heads=2, kv_heads=1)
+    with pytest.raises(q.QuintritError):
+        q.Decoder(bad)
