@@ -148,6 +148,73 @@ def cpu_sweep(layers_sample: int, threads: int, reps: int = 9):
     return weights / secs / 1e9, [p[4] for p in probs], ("avx512_vbmi" if use512 else "portable")
 
 
+def run_decode(args, local_rank: int):
+    """Whole-token decode of the Falcon3-10B shape (or --decode-shape) at batch 1 on one GPU: device time per token at a
+    context of --prompt tokens, end-to-end time per token through the C ABI, and a greedy-token parity check."""
+    import torch
+
+    import quintrit_b200 as q
+
+    dev = torch.device("cuda", local_rank)
+    ctx = (args.prompt + args.steps + 64 + 255) // 256 * 256
+    t0 = time.time()
+    spec = synth.torch_model(args.decode_shape, dev, ctx, layers=args.decode_layers)
+    torch.cuda.empty_cache()
+    dec = q.Decoder(spec, device=local_rank)
+    setup_s = time.time() - t0
+    weights = sum(int(np.prod(sh)) for sh in [(spec["q_heads"] * spec["head_dim"], spec["hidden"]), (spec["kv_heads"] * spec["head_dim"], spec["hidden"]),
+                                               (spec["kv_heads"] * spec["head_dim"], spec["hidden"]), (spec["hidden"], spec["q_heads"] * spec["head_dim"]),
+                                               (spec["inter"], spec["hidden"]), (spec["inter"], spec["hidden"]), (spec["hidden"], spec["inter"])]) * spec["layers"]
+    prompt = synth.prompt_tokens(2, args.prompt, spec["vocab"])
+    # parity leg: a short prompt and a few greedy tokens against the CPU oracle (same arrays)
+    parity = None
+    if not args.no_cpu:
+        import oracle
+
+        ref = oracle.Model(spec)
+        npar, ngen = 6, 6
+        tok = None
+        t_cpu = time.time()
+        for pos in range(npar):
+            tok = oracle.argmax(ref.forward(int(prompt[pos]), pos))
+        want = [tok]
+        for j in range(1, ngen):
+            tok = oracle.argmax(ref.forward(int(tok), npar + j - 1))
+            want.append(tok)
+        cpu_tok_s = (npar + ngen - 1) / (time.time() - t_cpu)
+        got = dec.generate(prompt[:npar], ngen)
+        lg_ref = ref.forward(int(got[-1]), npar + ngen - 1)
+        lg_gpu, _ = dec.forward(int(got[-1]), npar + ngen - 1)
+        parity = {"greedy_tokens_checked": ngen, "identical": bool(list(got) == want), "logits_bit_exact": bool(np.array_equal(lg_ref.view(np.uint32), lg_gpu.view(np.uint32))),
+                  "cpu_tokens_per_s": round(cpu_tok_s, 2), "cpu_threads": os.cpu_count()}
+        del ref
+    # ingest the prompt, then time
+    first = dec.generate(prompt, 1)
+    q.launch_count(reset=True)
+    dec.time_token(1, max(3, args.warmup))
+    launches_per_token = q.launch_count() / max(3, args.warmup)
+    step_ms = dec.time_token(1, args.steps)          # exactly K steps, CUDA events on the decoder's stream
+    best_ms = dec.time_token(5, max(args.steps, 50))  # the reference's method: minimum over blocks of replays
+    # end to end: token id in from the host, greedy token out to the host, every step
+    tok, pos = int(first[0]), args.prompt
+    t1 = time.perf_counter()
+    for _ in range(args.steps):
+        _, tok = dec.forward(tok, pos, want_logits=False)
+        pos += 1
+    e2e_ms = (time.perf_counter() - t1) * 1e3 / args.steps
+    bytes_tok = weights * BYTES_PER_WEIGHT
+    out = {
+        "shape": spec["shape"], "layers": spec["layers"], "context": args.prompt, "tokens_per_s": round(1e3 / step_ms, 1), "ms_per_token": round(step_ms, 4),
+        "best_ms_per_token": round(best_ms, 4), "velurex_bytes_per_token": int(bytes_tok),
+        "roofline_nominal_8tbs_frac": round(bytes_tok / (step_ms * 1e-3) / 8e12, 4),
+        "hbm_frac_of_measured": round(bytes_tok / (step_ms * 1e-3) / 1e9 / measured_peaks()[0], 4),
+        "e2e": {"tokens_per_s": round(1e3 / e2e_ms, 1), "ms_per_token": round(e2e_ms, 4), "h2d_bytes_per_step": 8, "d2h_bytes_per_step": 8},
+        "kernel_launches_per_token": round(launches_per_token, 1), "setup_s": round(setup_s, 1), "parity_vs_cpu": parity,
+    }
+    dec.free()
+    return out
+
+
 def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     try:
@@ -211,6 +278,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         shapes.append((l, p, r1 - r0, k))
     torch.cuda.empty_cache()
     plan = q.Plan(mats)
+    out_offsets = list(plan.out_offsets)
     weights_local = sum(n * k for _, _, n, k in shapes)
     weights_total = sum(n * k for _, _, n, k in sweep_shapes(args.layers))
     act_host = torch.from_numpy(plan.pack_activations(acts)).pin_memory()
@@ -316,11 +384,18 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         "deterministic": same,
         "setup_s": round(t_setup, 1),
     }
+    if world == 1 and not args.no_decode:
+        del plan, mats
+        torch.cuda.empty_cache()
+        try:
+            line["decode"] = run_decode(args, local_rank)
+        except Exception as e:  # the sweep line must still be printed
+            line["decode"] = {"error": f"{type(e).__name__}: {e}"}
     if world == 1 and not args.no_cpu:
         threads = os.cpu_count() or 1
         sample_layers = min(args.layers, 2)
         g, cpu_out, isa = cpu_sweep(sample_layers, threads, reps=5)
-        res = plan.split_results(first)
+        res = [first[o:o + n] for o, (_, _, n, _) in zip(out_offsets, shapes)]
         n_check = len(sweep_shapes(sample_layers))
         parity = all(np.array_equal(res[i], cpu_out[i]) for i in range(n_check))
         line["cpu_baseline"] = {"value": round(g, 2), "unit": "Gweights/s", "cores": threads, "kind": "port",
@@ -339,11 +414,18 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=40)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-decode", action="store_true", help="skip the whole-token decode leg")
+    ap.add_argument("--decode-only", action="store_true", help="run only the whole-token decode leg and print its object (profiling aid)")
+    ap.add_argument("--decode-shape", default="falcon3_10b", choices=["falcon3_10b", "bitnet_2b"])
+    ap.add_argument("--decode-layers", type=int, default=None, help="fewer layers than the shape has (experiments)")
+    ap.add_argument("--prompt", type=int, default=1024, help="context length at which a decode step is timed")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    if args.impl == "reference":
+    if args.decode_only:
+        print(json.dumps({"decode": run_decode(args, local_rank)}), flush=True)
+    elif args.impl == "reference":
         run_reference(args, rank, world)
     else:
         run_ours(args, rank, world, local_rank)

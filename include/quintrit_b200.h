@@ -186,8 +186,9 @@ int quintrit_b200_decoder_forward(quintrit_b200_decoder_t* decoder, uint32_t tok
  */
 int quintrit_b200_decoder_generate(quintrit_b200_decoder_t* decoder, const uint32_t* prompt, size_t prompt_len, size_t max_new,
                                    uint32_t* out_tokens, size_t out_capacity);
-/* Device time of one decode step in milliseconds: minimum over `blocks` blocks of `iters` graph replays at the current
- * position, as GpuSession::time_token (quintrit-runtime/src/gpu.rs:346-370). */
+/* Device time of one decode step in milliseconds: minimum over `blocks` blocks of `iters` graph replays, as
+ * GpuSession::time_token (quintrit-runtime/src/gpu.rs:346-370). Every replay decodes token 0 at the first free
+ * position, so the cached prefix is not disturbed and the context length is the number of cached tokens plus one. */
 int quintrit_b200_decoder_time_token(quintrit_b200_decoder_t* decoder, uint32_t blocks, uint32_t iters, float* out_ms);
 
 /* Kernel launches issued by this library on the calling thread since the last call with reset != 0 (counting aid). */

@@ -13,6 +13,9 @@
 #include <math.h>
 #include <stdlib.h>
 #include <string.h>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
 
 /* ---- half / bfloat conversions ---------------------------------------------------------------------------------- */
 
@@ -410,6 +413,7 @@ typedef struct qto_model {
     const float* scales;     /* layers * 7 weight scales */
     const float** norms;     /* layers * 4: attn_norm, ffn_norm, attn_sub_norm, ffn_sub_norm (the last two NULL for arch 0) */
     uint16_t *kc, *vc;       /* [layer][pos][kv_head][head_dim] */
+    uint8_t** w64;           /* 64-row tiled copies for the AVX-512 GEMV (same integers, only faster), or NULL */
 } qto_model_t;
 
 qto_model_t* qto_model_create(int arch, int f32_values, int hidden, int inter, int layers, int q_heads, int kv_heads, int head_dim,
@@ -422,19 +426,39 @@ qto_model_t* qto_model_create(int arch, int f32_values, int hidden, int inter, i
     const size_t n = (size_t)layers * ctx * kv_heads * head_dim;
     m->kc = (uint16_t*)calloc(n, 2);
     m->vc = (uint16_t*)calloc(n, 2);
+    if (qto_cpu_has_avx512_vbmi()) {
+        const size_t H = (size_t)hidden, I = (size_t)inter, qd = (size_t)q_heads * head_dim, kvd = (size_t)kv_heads * head_dim;
+        const size_t shp[7][2] = {{qd, H}, {kvd, H}, {kvd, H}, {H, qd}, {I, H}, {I, H}, {H, I}};
+        m->w64 = (uint8_t**)calloc((size_t)layers * 7, sizeof(uint8_t*));
+        for (int i = 0; i < layers * 7; ++i) {
+            m->w64[i] = (uint8_t*)malloc(qto_tile64_bytes(shp[i % 7][0], shp[i % 7][1]));
+            qto_tile64(w[i], shp[i % 7][0], shp[i % 7][1], m->w64[i]);
+        }
+    }
     return m;
 }
 void qto_model_free(qto_model_t* m) {
     if (!m) return;
     free(m->kc);
     free(m->vc);
+    if (m->w64) {
+        for (int i = 0; i < m->layers * 7; ++i) free(m->w64[i]);
+        free(m->w64);
+    }
     free(m);
 }
 
 /* layer.rs:123-177: quantised input -> exact integers -> one multiply by weight_scale / act_scale */
 static void project(const qto_model_t* m, int layer, int which, size_t rows, size_t cols, const int8_t* act, float act_scale, float* out) {
     int32_t* acc = (int32_t*)malloc(rows * 4);
-    qto_cpu_gemv_portable(m->w[layer * 7 + which], rows, cols, act, acc, 8);
+    int nt = 1;
+#ifdef _OPENMP
+    nt = omp_get_max_threads();
+#endif
+    if (m->w64)
+        qto_cpu_gemv_avx512(m->w64[layer * 7 + which], rows, cols, act, acc, nt);
+    else
+        qto_cpu_gemv_portable(m->w[layer * 7 + which], rows, cols, act, acc, nt);
     qto_rescale(acc, rows, m->scales[layer * 7 + which], act_scale, out);
     free(acc);
 }

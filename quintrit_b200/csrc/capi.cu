@@ -867,9 +867,11 @@ extern "C" int quintrit_b200_decoder_time_token(quintrit_b200_decoder_t* decoder
         quintrit_b200_decoder* d = decoder;
         if (out_ms == nullptr) return fail(QUINTRIT_ERR_NULL_POINTER, "out_ms is NULL");
         if (blocks == 0 || iters == 0) return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "blocks and iters must be at least 1");
-        if (d->host_pos == 0) return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "feed at least one token before timing a step");
+        if (d->host_pos >= static_cast<uint32_t>(d->ctx)) return fail(QUINTRIT_ERR_CONTEXT_OVERFLOW, "the context window is full: no position left to time a step at");
         DeviceGuard g(d->device);
-        const uint32_t pos = d->host_pos - 1, token = 0;
+        // The timed step decodes token 0 at the first free position: the cached prefix stays as it is, and the scratch
+        // entry it writes is overwritten by the next real token.
+        const uint32_t pos = d->host_pos, token = 0;
         cudaEvent_t e0, e1;
         QTB_CUDA(cudaEventCreate(&e0));
         QTB_CUDA(cudaEventCreate(&e1));
@@ -878,7 +880,7 @@ extern "C" int quintrit_b200_decoder_time_token(quintrit_b200_decoder_t* decoder
         for (uint32_t b = 0; b < blocks; ++b) {
             cudaEventRecord(e0, d->stream);
             for (uint32_t i = 0; i < iters; ++i) {
-                decoder_set(d, token, pos);  // the step re-decodes the last position: the cache keeps its length
+                decoder_set(d, token, pos);  // every replay decodes the same position: the context length stays fixed
                 cudaGraphLaunch(d->graph_step, d->stream);
             }
             cudaEventRecord(e1, d->stream);
@@ -890,7 +892,6 @@ extern "C" int quintrit_b200_decoder_time_token(quintrit_b200_decoder_t* decoder
         cudaEventDestroy(e0);
         cudaEventDestroy(e1);
         QTB_CUDA(cudaGetLastError());
-        d->host_pos = pos;  // the timed steps overwrote the last position: it has to be fed again
         *out_ms = best;
         return ok();
     });

@@ -145,3 +145,48 @@ def make_model(arch: int, f32_values: bool, hidden: int, inter: int, layers: int
     return dict(arch=arch, f32_values=f32_values, hidden=hidden, inter=inter, layers=layers, q_heads=q_heads, kv_heads=kv_heads,
                 head_dim=head_dim, vocab=vocab, ctx=ctx, rope_dims=rope_dims or head_dim, eps=eps, rope_theta=rope_theta, weights=weights,
                 scales=np.array(scales, np.float32), norms=norms, embed=embed, lm_head=head, out_norm=norm(seed_for(config, 255, 2, 0), hidden))
+
+
+def torch_normal_f16_bits(seed: int, n: int, std: float, device, chunk: int = 1 << 24) -> np.ndarray:
+    """N(0, std) values as F16 bit patterns (numpy uint16), generated on `device` from the seeded stream by Box-Muller."""
+    import torch
+
+    out = np.empty(n, np.uint16)
+    for s0 in range(0, n, chunk):
+        m = min(chunk, n - s0)
+        u = torch_splitmix_u32(seed, 2 * s0, 2 * m, device).to(torch.float64)
+        u1 = ((u[0::2] + 1.0) / 4294967296.0).to(torch.float32)
+        u2 = (u[1::2] / 4294967296.0).to(torch.float32)
+        x = torch.sqrt(-2.0 * torch.log(u1)) * torch.cos(6.283185307179586 * u2) * std
+        out[s0:s0 + m] = x.to(torch.float16).view(torch.int16).cpu().numpy().view(np.uint16)
+    return out
+
+
+def torch_model(shape: str, device, ctx: int, f32_values: bool = False, config: int = 2, layers: int | None = None) -> dict:
+    """The Falcon3-10B-shape or BitNet-2B-shape model with seeded random-init weights, built on a torch device."""
+    if shape == "falcon3_10b":
+        arch, hidden, inter, L, qh, kvh, hd, vocab, theta, eps, tied = 0, 3072, 23040, 40, 12, 4, 256, 131072, 1000042.0, 1e-6, False
+    elif shape == "bitnet_2b":
+        arch, hidden, inter, L, qh, kvh, hd, vocab, theta, eps, tied = 1, 2560, 6912, 30, 20, 5, 128, 128256, 500000.0, 1e-5, True
+    else:
+        raise ValueError(shape)
+    L = layers or L
+    qd, kvd = qh * hd, kvh * hd
+    shapes = [(qd, hidden), (kvd, hidden), (kvd, hidden), (hidden, qd), (inter, hidden), (inter, hidden), (hidden, inter)]
+    weights, scales, norms = [], [], []
+    for l in range(L):
+        for p, (rows, cols) in enumerate(shapes):
+            weights.append(torch_planar(seed_for(config, l, p, 0), rows, cols, device).cpu().numpy())
+            scales.append(weight_scale(seed_for(config, l, p, 1)))
+        norms += [np.ones(hidden, np.float32), np.ones(hidden, np.float32), np.ones(qd, np.float32) if arch == 1 else None,
+                  np.ones(inter, np.float32) if arch == 1 else None]
+    embed = torch_normal_f16_bits(seed_for(config, 255, 0, 0), vocab * hidden, 0.02, device)
+    head = None if tied else torch_normal_f16_bits(seed_for(config, 255, 1, 0), vocab * hidden, 0.02, device)
+    return dict(arch=arch, f32_values=f32_values, hidden=hidden, inter=inter, layers=L, q_heads=qh, kv_heads=kvh, head_dim=hd, vocab=vocab,
+                ctx=ctx, rope_dims=hd, eps=eps, rope_theta=theta, weights=weights, scales=np.array(scales, np.float32), norms=norms,
+                embed=embed, lm_head=head, out_norm=np.ones(hidden, np.float32), shape=shape)
+
+
+def prompt_tokens(config: int, n: int, vocab: int) -> np.ndarray:
+    """Uniform token ids from stream 3."""
+    return (splitmix_u32(seed_for(config, 0, 0, 3), 0, n).astype(np.uint64) * np.uint64(vocab) >> np.uint64(32)).astype(np.uint32)
