@@ -23,7 +23,8 @@ uint8_t qto_pack_5trits(const int8_t t[5]) {
 static int8_t g_byte_to_trits[256][5];
 static int g_table_ready = 0;
 
-static void init_table(void) {
+/* Built when the library is loaded, so that threaded callers never race on it. */
+__attribute__((constructor)) static void init_table(void) {
     /* pack.rs:43-58: enumerate the 243 states, everything else stays zero */
     if (g_table_ready) return;
     memset(g_byte_to_trits, 0, sizeof g_byte_to_trits);
