@@ -115,6 +115,27 @@ int quintrit_b200_gemv_f32(const quintrit_b200_matrix_t* matrix, const int8_t* a
  */
 int quintrit_b200_gemv_i32_device(const quintrit_b200_matrix_t* matrix, const int8_t* d_activations, int32_t* d_out, void* stream);
 
+/*
+ * quintrit_b200_gemv_i32_device for callers that must not allocate. It has no counterpart in the reference.
+ *
+ * Who needs it: code that runs where device-memory allocation is forbidden or unaffordable - inside a region that is
+ * being captured into a CUDA graph, in a serving loop whose memory was carved up front by a pool with nothing left
+ * for cudaMalloc, or in a latency-critical thread that may not take the allocator's lock. The kernel's scratch (its
+ * work list and counters) lives in a static device array of 262400 bytes that the library carries on every GPU that
+ * loads it, instead of the buffers quintrit_b200_matrix_upload allocated for the handle. The call allocates nothing
+ * (no cudaMalloc, cudaFree or allocating library routine); inputs and outputs are the caller's: the matrix handle
+ * (its weights were placed in HBM earlier, by code that was allowed to allocate), cols int8 activations and rows int32
+ * results in device memory.
+ *
+ * Limits and rules: a matrix that needs more than 4096 work items is rejected with QUINTRIT_ERR_INVALID_SHAPE (none of
+ * the model shapes of this project comes near). All calls on one GPU share the one array: the array keeps the last
+ * call's contents, the words that must start at zero are cleared by every call, and two calls that overlap on the GPU
+ * (different streams, or threads) race - issue them in one stream or order them yourself. The first call on a device
+ * looks up the array's device address and measures the shared-memory base with a tiny kernel and a 4-byte read-back;
+ * make that first call outside any stream capture.
+ */
+int quintrit_b200_gemv_i32_noalloc(const quintrit_b200_matrix_t* matrix, const int8_t* d_activations, int32_t* d_out, void* stream);
+
 /* ---- a list of GEMVs executed as one persistent launch (one decode step's projections) ---- */
 typedef struct quintrit_b200_plan quintrit_b200_plan_t;
 

@@ -88,6 +88,7 @@ def load_library(build_if_missing: bool = True) -> C.CDLL:
     l.quintrit_b200_gemv_i32.argtypes = [C.c_void_p, _i8p, _sz, _i32p, _sz]
     l.quintrit_b200_gemv_f32.argtypes = [C.c_void_p, _i8p, _sz, C.c_float, _f32p, _sz]
     l.quintrit_b200_gemv_i32_device.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
+    l.quintrit_b200_gemv_i32_noalloc.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
     l.quintrit_b200_plan_create.argtypes = [C.POINTER(C.c_void_p), _sz, C.POINTER(C.c_void_p)]
     l.quintrit_b200_plan_free.argtypes = [C.c_void_p]
     l.quintrit_b200_plan_layout.argtypes = [C.c_void_p, _sz, C.POINTER(_sz), C.POINTER(_sz), C.POINTER(_sz), C.POINTER(_sz)]
@@ -197,6 +198,11 @@ class Matrix:
 
     def gemv_i32_device(self, d_activations: int, d_out: int, stream: int = 0) -> None:
         _check(load_library().quintrit_b200_gemv_i32_device(self._h, C.c_void_p(d_activations), C.c_void_p(d_out), C.c_void_p(stream)))
+
+    def gemv_i32_noalloc(self, d_activations: int, d_out: int, stream: int = 0) -> None:
+        """The same GEMV on device pointers through the entry point that allocates nothing (its scratch is a static
+        device array shared by all calls on the GPU: do not overlap two of these calls)."""
+        _check(load_library().quintrit_b200_gemv_i32_noalloc(self._h, C.c_void_p(d_activations), C.c_void_p(d_out), C.c_void_p(stream)))
 
     def free(self) -> None:
         if self._h:

@@ -896,3 +896,119 @@ extern "C" int quintrit_b200_decoder_time_token(quintrit_b200_decoder_t* decoder
         return ok();
     });
 }
+
+// ---------------------------------------------------------------------------------------------------------------------
+// GEMV without any allocation
+// ---------------------------------------------------------------------------------------------------------------------
+
+namespace {
+
+constexpr int kNoAllocMaxItems = 4096;
+constexpr size_t kNoAllocHeaderBytes = 256;
+constexpr size_t kNoAllocScratchBytes = kNoAllocHeaderBytes + size_t(kNoAllocMaxItems) * sizeof(GemvItem);  // 262400 bytes
+
+// Work list and counters of quintrit_b200_gemv_i32_noalloc. Every GPU that loads the library holds these 256.25 KiB
+// until the process exits. Layout: four 32-bit words (next item, CTAs done, kernel status, measured shared-memory
+// base) padded to 256 bytes, then up to kNoAllocMaxItems descriptors of 64 bytes.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
+
+// Writes the work list of one matrix into the scratch array and clears the words that must start at zero: the same
+// decomposition as build_items (block pairs x ranges of row tiles), computed on the device so that nothing is staged.
+__global__ void noalloc_prepare_kernel(unsigned char* scratch, const uint4* w, int rows, int cols, int blocks, int tiles, int chunks,
+                                       int n_items) {
+    unsigned int* words = reinterpret_cast<unsigned int*>(scratch);
+    GemvItem* items = reinterpret_cast<GemvItem*>(scratch + kNoAllocHeaderBytes);
+    if (blockIdx.x == 0 && threadIdx.x < 3) words[threadIdx.x] = 0;  // next item, CTAs done, kernel status
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n_items; i += gridDim.x * blockDim.x) {
+        const int p = i / chunks, c = i % chunks;
+        const long long t0 = static_cast<long long>(tiles) * c / chunks, t1 = static_cast<long long>(tiles) * (c + 1) / chunks;
+        const int g = 2 * p;
+        GemvItem it{};
+        it.wa = w + (static_cast<size_t>(g) * tiles + t0) * 64;
+        it.nblk = g + 1 < blocks ? 2 : 1;
+        it.wb = it.nblk == 2 ? w + (static_cast<size_t>(g + 1) * tiles + t0) * 64 : it.wa;
+        it.act_off = 0;
+        it.out_off = 0;
+        it.rows = rows;
+        it.cols = cols;
+        it.col0 = g * kBlockTrits;
+        it.tile0 = static_cast<int>(t0);
+        it.ntiles = static_cast<int>(t1 - t0);
+        items[i] = it;
+    }
+}
+
+struct NoAllocDevice {
+    bool ready = false;
+    unsigned char* scratch = nullptr;  // device address of g_noalloc_scratch on this device
+    GemvKernel kernel = nullptr;
+};
+NoAllocDevice g_noalloc[64];
+
+// Per-device set-up, run by the first call on that device (with that device current): the device address of the
+// static array, and the kernel instantiation that matches this device's shared-memory base. Allocates nothing: the
+// base is measured into the array's fourth word.
+int noalloc_setup(int dev, NoAllocDevice** out) {
+    if (dev < 0 || dev >= 64) return fail(QUINTRIT_ERR_DEVICE, "device index %d out of range", dev);
+    NoAllocDevice& s = g_noalloc[dev];
+    if (!s.ready) {
+        unsigned char* ptr = nullptr;
+        // In host code the array's name is only a handle for the symbol; the address a kernel can use comes from here.
+        cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_noalloc_scratch);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(g_noalloc_scratch)");
+        unsigned int base = 0xFFFFFFFFu;
+        smem_base_kernel<<<1, 32, 1024>>>(reinterpret_cast<unsigned int*>(ptr) + 3);
+        e = cudaGetLastError();
+        if (e == cudaSuccess) e = cudaMemcpy(&base, ptr + 12, sizeof base, cudaMemcpyDeviceToHost);
+        if (e != cudaSuccess) return cuda_fail(e, "smem_base_kernel");
+        switch (base) {
+            case 0: s.kernel = gemv_lut_kernel<0>; break;
+            case 1024: s.kernel = gemv_lut_kernel<1024>; break;
+            case 2048: s.kernel = gemv_lut_kernel<2048>; break;
+            case 3072: s.kernel = gemv_lut_kernel<3072>; break;
+            case 4096: s.kernel = gemv_lut_kernel<4096>; break;
+            default: return fail(QUINTRIT_ERR_DEVICE, "unexpected shared-memory base %u on CUDA device %d: no kernel was built for it", base, dev);
+        }
+        QTB_CUDA(cudaFuncSetAttribute(s.kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemvSmemBytes));
+        s.scratch = ptr;
+        s.ready = true;
+    }
+    *out = &s;
+    return QUINTRIT_OK;
+}
+
+}  // namespace
+
+extern "C" int quintrit_b200_gemv_i32_noalloc(const quintrit_b200_matrix_t* matrix, const int8_t* d_activations, int32_t* d_out, void* stream) {
+    return guard([&]() -> int {
+        int rc = check_matrix(matrix);
+        if (rc != QUINTRIT_OK) return rc;
+        if (d_activations == nullptr || d_out == nullptr) return fail(QUINTRIT_ERR_NULL_POINTER, "a device pointer is NULL");
+        const size_t pairs = (matrix->blocks + 1) / 2, slots = static_cast<size_t>(matrix->sm_count) * kCtasPerSm;
+        const size_t want_chunks = std::max<size_t>(1, (slots + pairs - 1) / pairs);
+        const size_t tiles_per_item = std::max<size_t>(16, (matrix->tiles + want_chunks - 1) / want_chunks);
+        const size_t chunks = std::max<size_t>(1, (matrix->tiles + tiles_per_item - 1) / tiles_per_item);
+        const size_t n_items = pairs * chunks;
+        if (n_items > static_cast<size_t>(kNoAllocMaxItems))
+            return fail(QUINTRIT_ERR_INVALID_SHAPE,
+                        "a %zu x %zu matrix needs %zu work items, the static scratch of the no-allocation entry point holds %d (%zu bytes)",
+                        matrix->rows, matrix->cols, n_items, kNoAllocMaxItems, kNoAllocScratchBytes);
+        DeviceGuard g(matrix->device);
+        NoAllocDevice* s = nullptr;
+        if ((rc = noalloc_setup(matrix->device, &s)) != QUINTRIT_OK) return rc;
+        cudaStream_t st = static_cast<cudaStream_t>(stream);
+        QTB_CUDA(cudaMemsetAsync(d_out, 0, matrix->rows * sizeof(int32_t), st));
+        noalloc_prepare_kernel<<<static_cast<unsigned>((n_items + 255) / 256), 256, 0, st>>>(
+            s->scratch, matrix->d_w, static_cast<int>(matrix->rows), static_cast<int>(matrix->cols), static_cast<int>(matrix->blocks),
+            static_cast<int>(matrix->tiles), static_cast<int>(chunks), static_cast<int>(n_items));
+        ++g_launches;
+        QTB_CUDA(cudaGetLastError());
+        const int grid = static_cast<int>(std::max<size_t>(1, std::min(n_items, slots)));
+        s->kernel<<<grid, kGemvThreads, kGemvSmemBytes, st>>>(reinterpret_cast<const GemvItem*>(s->scratch + kNoAllocHeaderBytes),
+                                                             static_cast<int>(n_items), d_activations, d_out,
+                                                             reinterpret_cast<unsigned int*>(s->scratch));
+        ++g_launches;
+        QTB_CUDA(cudaGetLastError());
+        return ok();
+    });
+}
