@@ -622,6 +622,8 @@ size_t decoder_item_tiles(size_t tile_pairs, size_t slots) {
     return std::max<size_t>(8, (tile_pairs + slots - 1) / slots);
 }
 
+int mega_setup(quintrit_b200_decoder* d, const quintrit_b200_decoder_desc_t* desc);
+
 int decoder_create_impl(const quintrit_b200_decoder_desc_t* desc, quintrit_b200_decoder** out) {
     if (desc->struct_size < sizeof(quintrit_b200_decoder_desc_t))
         return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "struct_size %u is smaller than quintrit_b200_decoder_desc_t (%zu)", desc->struct_size,
@@ -757,11 +759,111 @@ int decoder_create_impl(const quintrit_b200_decoder_desc_t* desc, quintrit_b200_
     QTB_CUDA(cudaFuncSetAttribute(attn_finish_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
     QTB_CUDA(cudaFuncSetAttribute(act_quant_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
     QTB_CUDA(cudaFuncSetAttribute(lm_head_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+    d->use_mega = false;
+    const char* mode = std::getenv("QUINTRIT_B200_DECODE");  // "kernels" keeps the one-launch-per-step path (experiments)
+    if (desc->arch == QUINTRIT_B200_ARCH_LLAMA && d->q_heads <= kMegaMaxHeads && !(mode && std::strcmp(mode, "kernels") == 0)) {
+        if ((rc = mega_setup(d, desc)) != QUINTRIT_OK) return rc;
+        d->use_mega = true;
+    }
     QTB_CUDA(cudaDeviceSynchronize());
     return QUINTRIT_OK;
 }
 
+// Work items of one GEMV phase of the single-kernel path: one round over `ctas` CTAs. The launch's problems share their
+// column count; the chunks of row tiles are shared out in proportion to the problems' row tiles.
+void mega_phase_items(std::vector<GemvItem>& items, const quintrit_b200_matrix* const* ms, const size_t* out_offs, int n, size_t ctas) {
+    const size_t pairs = (ms[0]->blocks + 1) / 2;
+    size_t total_tiles = 0;
+    for (int i = 0; i < n; ++i) total_tiles += ms[i]->tiles;
+    const size_t chunks_total = std::max<size_t>(n, ctas / pairs);
+    for (int i = 0; i < n; ++i) {
+        size_t chunks = std::max<size_t>(1, chunks_total * ms[i]->tiles / total_tiles);
+        chunks = std::min(chunks, ms[i]->tiles);
+        const size_t tiles_per_item = (ms[i]->tiles + chunks - 1) / chunks;
+        build_items(items, ms[i]->d_w, 0, out_offs[i], ms[i]->rows, ms[i]->cols, ms[i]->blocks, ms[i]->tiles, tiles_per_item);
+    }
+}
+
+template <uint32_t BASE>
+int mega_bind(quintrit_b200_decoder* d) {
+    d->mega_kernel = decode_token_kernel<BASE>;
+    QTB_CUDA(cudaFuncSetAttribute(decode_token_kernel<BASE>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(d->mega_smem)));
+    int per_sm = 0;
+    QTB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_token_kernel<BASE>, kMegaThreads, d->mega_smem));
+    if (per_sm < 1) return fail(QUINTRIT_ERR_DEVICE, "the decode kernel does not fit one CTA per multiprocessor on this CUDA device");
+    return QUINTRIT_OK;
+}
+
+// Builds the arguments of the single-kernel path (after all buffers exist).
+int mega_setup(quintrit_b200_decoder* d, const quintrit_b200_decoder_desc_t* desc) {
+    const int L = d->layers, H = d->hidden, I = d->inter, qd = d->q_dim, kvd = d->kv_dim;
+    int rc;
+    if ((rc = dev_alloc(d, &d->xa, H)) != QUINTRIT_OK || (rc = dev_alloc(d, &d->xb, H)) != QUINTRIT_OK ||
+        (rc = dev_alloc(d, &d->v_inter, I)) != QUINTRIT_OK || (rc = dev_alloc(d, &d->amax_bits, 4)) != QUINTRIT_OK ||
+        (rc = dev_alloc(d, &d->best_val, d->sm_count)) != QUINTRIT_OK || (rc = dev_alloc(d, &d->best_idx, d->sm_count)) != QUINTRIT_OK ||
+        (rc = dev_alloc(d, &d->bar, 4)) != QUINTRIT_OK)
+        return rc;
+    std::vector<GemvItem> items;
+    std::vector<MegaLayer> layers(L);
+    for (int l = 0; l < L; ++l) {
+        const quintrit_b200_matrix* const* m = desc->matrices + size_t(l) * 7;
+        MegaLayer& ly = layers[l];
+        const size_t o_qkv[3] = {0, size_t(qd), size_t(qd + kvd)}, o_zero[1] = {0}, o_gu[2] = {0, size_t(I)};
+        auto phase = [&](int k, const quintrit_b200_matrix* const* ms, const size_t* offs, int n) {
+            ly.first[k] = static_cast<int>(items.size());
+            mega_phase_items(items, ms, offs, n, d->sm_count);
+            ly.count[k] = static_cast<int>(items.size()) - ly.first[k];
+        };
+        phase(0, m, o_qkv, 3);
+        phase(1, m + 3, o_zero, 1);
+        phase(2, m + 4, o_gu, 2);
+        phase(3, m + 6, o_zero, 1);
+        ly.attn_norm = d->norms[l * 4 + 0];
+        ly.ffn_norm = d->norms[l * 4 + 1];
+        for (int k = 0; k < 7; ++k) ly.ws[k] = d->scales[l * 7 + k];
+        ly.kc = d->kc + size_t(l) * d->ctx * kvd;
+        ly.vc = d->vc + size_t(l) * d->ctx * kvd;
+    }
+    GemvItem* d_items = nullptr;
+    MegaLayer* d_layers = nullptr;
+    if ((rc = dev_upload(d, &d_items, items.data(), items.size())) != QUINTRIT_OK) return rc;
+    if ((rc = dev_upload(d, &d_layers, layers.data(), layers.size())) != QUINTRIT_OK) return rc;
+    MegaArgs& a = d->mega;
+    a.layers = d_layers, a.items = d_items;
+    a.n_layers = L, a.hidden = H, a.inter = I, a.q_heads = d->q_heads, a.kv_heads = d->kv_heads, a.head_dim = d->head_dim;
+    a.vocab = d->vocab, a.ctx = d->ctx, a.rope_dims = d->rope_dims, a.f32_values = d->f32_values;
+    a.eps = d->eps, a.attn_scale = 1.0f / std::sqrt(static_cast<float>(d->head_dim));
+    a.embed = d->embed, a.lm_head = d->lm_head, a.out_norm = d->out_norm, a.cos_sin = d->cos_sin;
+    a.xa = d->xa, a.xb = d->xb;
+    a.acc_qkv = d->acc_qkv, a.acc_o = d->acc_o, a.acc_gu = d->acc_gu, a.acc_down = d->acc_down;
+    a.v_inter = d->v_inter, a.amax_bits = d->amax_bits, a.part_acc = d->part_acc, a.part_ms = d->part_ms, a.logits = d->logits;
+    a.best_val = d->best_val, a.best_idx = d->best_idx, a.token = d->d_token, a.pos = d->d_pos, a.history = d->d_history;
+    a.bar = d->bar, a.status = d->d_counters + 2;
+    d->mega_smem = mega_smem_bytes(std::max(H, qd));
+    // the table-base constant: measured once per device like the GEMV kernel's
+    unsigned int base = 0xFFFFFFFFu;
+    smem_base_kernel<<<1, 32, 1024>>>(reinterpret_cast<unsigned int*>(d->bar));
+    QTB_CUDA(cudaGetLastError());
+    QTB_CUDA(cudaMemcpy(&base, d->bar, sizeof base, cudaMemcpyDeviceToHost));
+    QTB_CUDA(cudaMemset(d->bar, 0, 16));
+    switch (base) {
+        case 0: return mega_bind<0>(d);
+        case 1024: return mega_bind<1024>(d);
+        case 2048: return mega_bind<2048>(d);
+        case 3072: return mega_bind<3072>(d);
+        case 4096: return mega_bind<4096>(d);
+        default: return fail(QUINTRIT_ERR_DEVICE, "unexpected shared-memory base %u on CUDA device %d: no kernel was built for it", base, d->device);
+    }
+}
+
 int decoder_step(quintrit_b200_decoder* d) {
+    if (d->use_mega) {
+        QTB_CUDA(cudaMemsetAsync(d->bar, 0, sizeof(unsigned int), d->stream));
+        void* args[] = {&d->mega};
+        QTB_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(d->mega_kernel), dim3(d->sm_count), dim3(kMegaThreads), args, d->mega_smem, d->stream));
+        ++g_launches;
+        return QUINTRIT_OK;
+    }
     int rc = decoder_graph(d);
     if (rc != QUINTRIT_OK) return rc;
     QTB_CUDA(cudaGraphLaunch(d->graph_step, d->stream));
@@ -772,7 +874,8 @@ int decoder_check_status(quintrit_b200_decoder* d) {
     unsigned int flag = 0;
     QTB_CUDA(cudaMemcpyAsync(&flag, d->d_counters + 2, sizeof flag, cudaMemcpyDeviceToHost, d->stream));
     QTB_CUDA(cudaStreamSynchronize(d->stream));
-    if (flag != 0) return fail(QUINTRIT_ERR_DEVICE, "GEMV kernel on the CUDA device found its shared-memory table at an unexpected address");
+    if (flag == 2) return fail(QUINTRIT_ERR_DEVICE, "the decode kernel on the CUDA device gave up waiting at a grid barrier");
+    if (flag != 0) return fail(QUINTRIT_ERR_DEVICE, "a kernel on the CUDA device found its shared-memory table at an unexpected address");
     return QUINTRIT_OK;
 }
 
@@ -876,12 +979,12 @@ extern "C" int quintrit_b200_decoder_time_token(quintrit_b200_decoder_t* decoder
         QTB_CUDA(cudaEventCreate(&e0));
         QTB_CUDA(cudaEventCreate(&e1));
         float best = 1e30f;
-        if ((rc = decoder_graph(d)) != QUINTRIT_OK) return rc;
+        if (!d->use_mega && (rc = decoder_graph(d)) != QUINTRIT_OK) return rc;
         for (uint32_t b = 0; b < blocks; ++b) {
             cudaEventRecord(e0, d->stream);
             for (uint32_t i = 0; i < iters; ++i) {
-                decoder_set(d, token, pos);  // every replay decodes the same position: the context length stays fixed
-                cudaGraphLaunch(d->graph_step, d->stream);
+                decoder_set(d, token, pos);  // every step decodes the same position: the context length stays fixed
+                if ((rc = decoder_step(d)) != QUINTRIT_OK) return rc;
             }
             cudaEventRecord(e1, d->stream);
             cudaEventSynchronize(e1);

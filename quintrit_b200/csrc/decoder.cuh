@@ -9,6 +9,7 @@
 #include "capi_common.cuh"
 #include "decode.cuh"
 #include "gemv_lut.cuh"
+#include "megakernel.cuh"
 
 struct quintrit_b200_decoder {
     uint32_t magic;
@@ -30,6 +31,13 @@ struct quintrit_b200_decoder {
     unsigned int* d_counters;
     qtb::GemvItem* d_items;
     std::vector<int> item_first, item_count;  // layers * 4 launches: qkv, o, gate+up, down
+    // single-kernel path (LLaMA / Falcon3 architecture)
+    bool use_mega;
+    qtb::MegaArgs mega;
+    void (*mega_kernel)(qtb::MegaArgs);
+    size_t mega_smem;
+    float *xa, *xb, *v_inter, *best_val;
+    unsigned int *amax_bits, *best_idx, *bar;
     cudaStream_t stream;
     cudaGraphExec_t graph_step;               // one token: embed ... argmax (token and position read from device memory)
     bool graph_ready;

@@ -1,0 +1,578 @@
+// One decoded token as ONE cooperative persistent kernel (one CTA per SM), for the LLaMA / Falcon3 architecture.
+//
+// Why: at batch 1 a B200 streams a whole layer's weights in about 7 us, less than the cost of the 9 kernel boundaries a
+// layer has when every step is a launch of its own (the reference's graph has 363 nodes per token,
+// rust/crates/quintrit-runtime/src/gpu.rs:410-452). Here a layer is six phases separated by grid-wide barriers:
+//   A  x += down(prev) ; RMSNorm ; int8 quantise (every CTA, redundantly) ; q|k|v GEMV (split over CTAs)
+//   C  attention: RoPE of q and of the new k on the fly, KV append, one (head, KV chunk) per CTA
+//   D  chunk combine + int8 quantise (every CTA) ; o GEMV
+//   E  x += o ; RMSNorm ; quantise (every CTA) ; gate|up GEMV
+//   F1 SwiGLU on a slice per CTA, maximum through atomicMax
+//   F2 down GEMV, quantising its activations on the fly in the table fill
+// and the token ends with the final norm, the output head (rows split over CTAs), the greedy choice and pos += 1.
+// All arithmetic is the device functions of decode.cuh / gemv_lut.cuh, so the bits equal the per-kernel path and the
+// reference CPU runtime. Every wait is bounded: a barrier that does not complete sets status and the kernel returns.
+#pragma once
+#include <cooperative_groups.h>
+
+#include "decode.cuh"
+#include "gemv_lut.cuh"
+
+namespace qtb {
+
+constexpr int kMegaThreads = 512;
+constexpr int kMegaWarps = kMegaThreads / 32;
+constexpr int kMegaMaxHeads = 96;
+constexpr unsigned int kBarrierSpinLimit = 1u << 21;  // polls of ~50 ns: about 0.1 s, then the kernel gives up
+
+struct MegaLayer {
+    int first[4], count[4];   // work items of the q|k|v, o, gate|up and down launches (indices into MegaArgs::items)
+    const float* attn_norm;
+    const float* ffn_norm;
+    float ws[7];
+    __half* kc;               // [ctx][kv_dim]
+    __half* vc;
+};
+
+struct MegaArgs {
+    const MegaLayer* layers;
+    const GemvItem* items;
+    int n_layers, hidden, inter, q_heads, kv_heads, head_dim, vocab, ctx, rope_dims, f32_values;
+    float eps, attn_scale;
+    const __half* embed;
+    const __half* lm_head;
+    const float* out_norm;
+    const float* cos_sin;
+    float* xa;                // residual stream at layer starts
+    float* xb;                // residual stream after the attention block
+    int32_t *acc_qkv, *acc_o, *acc_gu, *acc_down;
+    float* v_inter;           // SwiGLU output (inter)
+    unsigned int* amax_bits;  // two slots, alternating by layer
+    float* part_acc;
+    float* part_ms;
+    float* logits;
+    float* best_val;          // per-CTA greedy candidates
+    unsigned int* best_idx;
+    uint32_t* token;
+    uint32_t* pos;
+    uint32_t* history;
+    unsigned int* bar;        // grid barrier counter, cleared by the host before every launch
+    unsigned int* status;     // 0 = fine, 1 = wrong shared-memory base, 2 = a barrier timed out
+};
+
+// Grid-wide barrier with a bounded wait. Returns false (in every thread of the CTA) if it gave up.
+__device__ __forceinline__ bool grid_barrier(unsigned int* bar, unsigned int target, unsigned int* status, int* s_flag) {
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        atomicAdd(bar, 1u);
+        int okay = 1;
+        unsigned int spins = 0;
+        while (true) {
+            unsigned int v;
+            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(bar));
+            if (v >= target) break;
+            if (++spins > kBarrierSpinLimit || *reinterpret_cast<volatile unsigned int*>(status) != 0u) {
+                atomicMax(status, 2u);
+                okay = 0;
+                break;
+            }
+            __nanosleep(32);
+        }
+        *s_flag = okay;
+    }
+    __syncthreads();
+    return *s_flag != 0;
+}
+
+// Table fill for any block size that is a multiple of 64: thread -> (column = tid & 63, part = tid >> 6).
+template <int THREADS>
+__device__ __forceinline__ void fill_table_n(int* tab, const int a[5], int tid) {
+    constexpr int parts = THREADS / 64;
+    const int col = tid & 63, part = tid >> 6;
+#pragma unroll
+    for (int ui = 0; ui < (9 + parts - 1) / parts; ++ui) {
+        const int u = part + parts * ui;
+        if (u > 8) break;
+        const int d3 = u % 3, d4 = u / 3;
+        const int tu = (d3 - 1) * a[3] + (d4 - 1) * a[4];
+        int* dst = tab + (28 * u) * 64 + col;
+#pragma unroll
+        for (int l = 0; l < 27; ++l) {
+            const int t0 = l % 3 - 1, t1 = (l / 3) % 3 - 1, t2 = l / 9 - 1;
+            dst[l * 64] = tu + t0 * a[0] + t1 * a[1] + t2 * a[2];
+        }
+    }
+}
+
+__device__ __forceinline__ int quantize_code(float y, float s) {
+    float q = roundf(__fmul_rn(y, s));
+    q = q != q ? 0.0f : fminf(fmaxf(q, -128.0f), 127.0f);
+    return static_cast<int>(q);
+}
+
+// The GEMV share of this CTA in one phase: items first + blockIdx.x, + gridDim.x, ... Activations come either from
+// shared memory as int8 codes (act_s) or from global memory as floats that are quantised here with scale `qs`.
+template <uint32_t BASE>
+__device__ __forceinline__ void mega_gemv(const GemvItem* __restrict__ items, int first, int count, int* tab, const int8_t* act_s,
+                                          const float* __restrict__ act_f, float qs, int32_t* __restrict__ out_base,
+                                          const uint32_t (&creg)[8]) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    for (int k = blockIdx.x; k < count; k += gridDim.x) {
+        const GemvItem it = items[first + k];
+        {
+            const int col = tid & 63, gb = col >> 5, j = col & 31;
+            int a[5];
+#pragma unroll
+            for (int p = 0; p < 5; ++p) {
+                const int c = it.col0 + gb * kBlockTrits + p * kBlockBytes + j;
+                int v = 0;
+                if (gb < it.nblk && c < it.cols) v = act_s != nullptr ? static_cast<int>(act_s[c]) : (qs > 0.0f ? quantize_code(act_f[c], qs) : 0);
+                a[p] = v;
+            }
+            fill_table_n<kMegaThreads>(tab, a, tid);
+        }
+        __syncthreads();
+        const uint4* wa = it.wa + lane;
+        const uint4* wb = it.wb + lane;
+        int32_t* out = out_base + it.out_off + it.tile0 * kTileRows + lane;
+        const int rows_left = it.rows - it.tile0 * kTileRows - lane;
+        TileRegs ra, rb;
+        int t = warp;
+        if (t < it.ntiles) load_tile(ra, wa, wb, it.nblk, t, 0);
+        while (t < it.ntiles) {
+            const int t1 = t + kMegaWarps;
+            if (t1 < it.ntiles) load_tile(rb, wa, wb, it.nblk, t1, 0);
+            {
+                const int acc = tile_sum<BASE>(ra, it.nblk, creg);
+                if (t * kTileRows < rows_left) atomicAdd(out + t * kTileRows, acc);
+            }
+            if (t1 >= it.ntiles) break;
+            const int t2 = t1 + kMegaWarps;
+            if (t2 < it.ntiles) load_tile(ra, wa, wb, it.nblk, t2, 0);
+            {
+                const int acc = tile_sum<BASE>(rb, it.nblk, creg);
+                if (t1 * kTileRows < rows_left) atomicAdd(out + t1 * kTileRows, acc);
+            }
+            t = t2;
+        }
+        __syncthreads();  // the table is rewritten by the next item
+    }
+}
+
+// RMSNorm + int8 quantisation of n values held in y_s (overwritten with the normalised values); every thread returns the
+// activation scale. Same arithmetic as norm_quant_kernel.
+__device__ __forceinline__ float mega_norm_quant(float* y_s, const float* __restrict__ norm_w, int n, float eps, int8_t* a8, double* sh_d,
+                                                 float* sh_f) {
+    const int tid = threadIdx.x;
+    double sum = 0.0;
+    for (int i = tid; i < n; i += kMegaThreads) sum += static_cast<double>(__fmul_rn(y_s[i], y_s[i]));
+    sum = block_sum_f64(sum, sh_d);
+    const float mean = __double2float_rn(sum / static_cast<double>(n));
+    const float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, eps)));
+    float amax = 0.0f;
+    for (int i = tid; i < n; i += kMegaThreads) {
+        const float y = __fmul_rn(__fmul_rn(y_s[i], inv), norm_w[i]);
+        y_s[i] = y;
+        amax = fmaxf(amax, fabsf(y));
+    }
+    amax = block_max_f32(amax, sh_f);
+    const float s = amax > 0.0f ? __fdiv_rn(127.0f, amax) : 0.0f;
+    if (a8 != nullptr)
+        for (int i = tid; i < n; i += kMegaThreads) a8[i] = static_cast<int8_t>(amax > 0.0f ? quantize_code(y_s[i], s) : 0);
+    __syncthreads();
+    return s;
+}
+
+// One (query head, KV chunk) of the attention of one layer: attention_kernel with the RoPE of q and of the new key, the
+// post-scaling and the KV append folded in (rope_kv_kernel), so that no barrier is needed between them.
+__device__ __forceinline__ void mega_attention_unit(const MegaArgs& a, const MegaLayer& ly, int h, int c, float s_in, unsigned char* scratch) {
+    float* s_score = reinterpret_cast<float*>(scratch);            // kAttnMaxChunk floats
+    float* s_ms = s_score + kAttnMaxChunk;                         // kAttnMaxChunk floats
+    float* s_q = s_ms + kAttnMaxChunk;                             // 256 floats
+    float* s_tm = s_q + 256;                                       // kMegaThreads floats
+    __half* s_kcur = reinterpret_cast<__half*>(s_tm + kMegaThreads);  // 256 halves
+    __half* s_vcur = s_kcur + 256;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int hd = a.head_dim, gqa = a.q_heads / a.kv_heads, kvh = h / gqa;
+    const int qd = a.q_heads * hd, kvd = a.kv_heads * hd;
+    const int pos = static_cast<int>(a.pos[0]), seq_len = pos + 1;
+    int n_kv = (seq_len + 255) / 256 * 256;
+    if (n_kv < 256) n_kv = 256;
+    if (n_kv > a.ctx) n_kv = a.ctx;
+    int start = 0, end = seq_len;
+    if (n_kv >= 512) {
+        const int chunk = (n_kv + 3) / 4;
+        start = c * chunk;
+        end = min(min(start + chunk, n_kv), seq_len);
+    } else if (c > 0) {
+        start = end;
+    }
+    float* my_acc = a.part_acc + (static_cast<size_t>(h) * 4 + c) * hd;
+    float* my_ms = a.part_ms + (static_cast<size_t>(h) * 4 + c) * 2;
+    const int len = end - start;
+    if (len <= 0) {
+        if (tid == 0) {
+            my_ms[0] = -INFINITY;
+            my_ms[1] = 0.0f;
+        }
+        return;
+    }
+    const bool live = s_in > 0.0f;
+    const float pq = live ? __fdiv_rn(ly.ws[0], s_in) : 0.0f, pk = live ? __fdiv_rn(ly.ws[1], s_in) : 0.0f, pv = live ? __fdiv_rn(ly.ws[2], s_in) : 0.0f;
+    const float* cs = a.cos_sin + static_cast<size_t>(pos) * a.rope_dims;
+    const bool has_cur = pos >= start && pos < end;
+    // q of this head (pairs 2p, 2p+1), and the new key / value of its KV head when the chunk holds the current position
+    for (int p = tid; p < hd / 2; p += kMegaThreads) {
+        const bool rot = p < a.rope_dims / 2;
+        float c0 = 1.0f, sn = 0.0f;
+        if (rot) {
+            c0 = cs[2 * p];
+            sn = cs[2 * p + 1];
+        }
+        {
+            float x0 = live ? __fmul_rn(static_cast<float>(a.acc_qkv[h * hd + 2 * p]), pq) : 0.0f;
+            float x1 = live ? __fmul_rn(static_cast<float>(a.acc_qkv[h * hd + 2 * p + 1]), pq) : 0.0f;
+            if (rot) {
+                const float r0 = __fmaf_rn(x0, c0, -__fmul_rn(x1, sn)), r1 = __fmaf_rn(x0, sn, __fmul_rn(x1, c0));
+                x0 = r0;
+                x1 = r1;
+            }
+            s_q[2 * p] = a.f32_values ? x0 : __half2float(__float2half_rn(x0));
+            s_q[2 * p + 1] = a.f32_values ? x1 : __half2float(__float2half_rn(x1));
+        }
+        if (has_cur) {
+            float x0 = live ? __fmul_rn(static_cast<float>(a.acc_qkv[qd + kvh * hd + 2 * p]), pk) : 0.0f;
+            float x1 = live ? __fmul_rn(static_cast<float>(a.acc_qkv[qd + kvh * hd + 2 * p + 1]), pk) : 0.0f;
+            if (rot) {
+                const float r0 = __fmaf_rn(x0, c0, -__fmul_rn(x1, sn)), r1 = __fmaf_rn(x0, sn, __fmul_rn(x1, c0));
+                x0 = r0;
+                x1 = r1;
+            }
+            s_kcur[2 * p] = __float2half_rn(x0);
+            s_kcur[2 * p + 1] = __float2half_rn(x1);
+            const float v0 = live ? __fmul_rn(static_cast<float>(a.acc_qkv[qd + kvd + kvh * hd + 2 * p]), pv) : 0.0f;
+            const float v1 = live ? __fmul_rn(static_cast<float>(a.acc_qkv[qd + kvd + kvh * hd + 2 * p + 1]), pv) : 0.0f;
+            s_vcur[2 * p] = __float2half_rn(v0);
+            s_vcur[2 * p + 1] = __float2half_rn(v1);
+        }
+    }
+    __syncthreads();
+    const __half* kbase = ly.kc + static_cast<size_t>(kvh) * hd;
+    const __half* vbase = ly.vc + static_cast<size_t>(kvh) * hd;
+    if (has_cur && h % gqa == 0) {  // append to the cache (kv_cache.rs:124-138); one unit per KV head does it
+        for (int d = tid; d < hd; d += kMegaThreads) {
+            const_cast<__half*>(kbase)[static_cast<size_t>(pos) * kvd + d] = s_kcur[d];
+            const_cast<__half*>(vbase)[static_cast<size_t>(pos) * kvd + d] = s_vcur[d];
+        }
+    }
+    // scores: one warp per position, lane = accumulator lane of the reference's dot product, four positions in flight
+    for (int p0 = warp * 4; p0 < len; p0 += kMegaWarps * 4) {
+        float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int p = p0 + u;
+            if (p < len) {
+                const int gp = start + p;
+                const __half* kr = gp == pos ? s_kcur : kbase + static_cast<size_t>(gp) * kvd;
+                for (int i = 0; i + 32 <= hd; i += 32) acc[u] = __fmaf_rn(__half2float(kr[i + lane]), s_q[i + lane], acc[u]);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int p = p0 + u;
+            if (p < len) {
+                const float sc = a.f32_values ? dot_lane_reduce_f16_f32(acc[u]) : dot_lane_reduce_f16(acc[u]);
+                if (lane == 0) s_score[p] = __fmul_rn(sc, a.attn_scale);
+            }
+        }
+    }
+    __syncthreads();
+    {
+        const int per = (len + kMegaThreads - 1) / kMegaThreads;
+        const int p0 = min(tid * per, len), p1 = min(p0 + per, len);
+        float m = -INFINITY;
+        for (int p = p0; p < p1; ++p) m = fmaxf(m, s_score[p]);
+        s_tm[tid] = m;
+        __syncthreads();
+        float run = -INFINITY;
+        for (int t = 0; t < tid; ++t) run = fmaxf(run, s_tm[t]);
+        for (int p = p0; p < p1; ++p) {
+            const float sc = s_score[p];
+            const float m_old = run;
+            float ms = 1.0f, vs = 1.0f;
+            if (sc > run) {
+                run = sc;
+                ms = device_expf(__fsub_rn(m_old, run));
+            } else {
+                vs = device_expf(__fsub_rn(sc, run));
+            }
+            s_ms[p] = ms;
+            s_score[p] = vs;
+        }
+        __syncthreads();
+        if (tid == 0) {
+            float S = 0.0f, M = -INFINITY;
+            for (int t = 0; t < kMegaThreads; ++t) M = fmaxf(M, s_tm[t]);
+            for (int p = 0; p < len; ++p) S = __fmaf_rn(S, s_ms[p], s_score[p]);
+            my_ms[0] = M;
+            my_ms[1] = S;
+        }
+    }
+    for (int d = tid; d < hd; d += kMegaThreads) {
+        const __half* vr = vbase + static_cast<size_t>(start) * kvd + d;
+        const int pcur = pos - start;  // index of the current position inside the chunk, if it is in it
+        if (a.f32_values) {
+            float acc = 0.0f;
+            for (int p = 0; p < len; ++p) {
+                const float ms = s_ms[p];
+                if (ms != 1.0f) acc = __fmul_rn(acc, ms);
+                const __half v = p == pcur ? s_vcur[d] : vr[static_cast<size_t>(p) * kvd];
+                acc = __fmaf_rn(__half2float(v), s_score[p], acc);
+            }
+            my_acc[d] = acc;
+        } else {
+            __half acc = __float2half_rn(0.0f);
+            for (int p = 0; p < len; ++p) {
+                const float ms = s_ms[p];
+                if (ms != 1.0f) acc = __float2half_rn(__fmul_rn(__half2float(acc), ms));
+                const __half v = p == pcur ? s_vcur[d] : vr[static_cast<size_t>(p) * kvd];
+                acc = __float2half_rn(__fmaf_rn(__half2float(v), s_score[p], __half2float(acc)));
+            }
+            my_acc[d] = __half2float(acc);
+        }
+    }
+    __syncthreads();  // the scratch is reused
+}
+
+// Shared-memory plan of the megakernel (bytes from the dynamic base): table | attention scratch | y (floats) | a8 | small
+constexpr int kMegaAttnScratch = (2 * kAttnMaxChunk + 256 + kMegaThreads) * 4 + 2 * 256 * 2;
+__host__ __device__ constexpr size_t mega_smem_bytes(int maxvec) {
+    return static_cast<size_t>(kTableBytes) + kMegaAttnScratch + static_cast<size_t>(maxvec) * 4 + (static_cast<size_t>(maxvec) + 15) / 16 * 16 + 4096;
+}
+
+template <uint32_t BASE>
+__global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(MegaArgs a) {
+    extern __shared__ __align__(1024) unsigned char smem[];
+    const int maxvec = max(a.hidden, a.q_heads * a.head_dim);
+    int* tab = reinterpret_cast<int*>(smem);
+    unsigned char* attn_scratch = smem + kTableBytes;
+    float* y_s = reinterpret_cast<float*>(attn_scratch + kMegaAttnScratch);
+    int8_t* a8 = reinterpret_cast<int8_t*>(y_s + maxvec);
+    unsigned char* small = reinterpret_cast<unsigned char*>(a8) + (maxvec + 15) / 16 * 16;
+    double* sh_d = reinterpret_cast<double*>(small);       // 32 doubles
+    float* sh_f = reinterpret_cast<float*>(small + 256);   // 32 floats
+    float* s_pair = reinterpret_cast<float*>(small + 384); // chunk-combine factors: q_heads * (4 * 2 + 1) floats (q_heads <= kMegaMaxHeads)
+    int* s_flag = reinterpret_cast<int*>(small + 4000);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, cta = blockIdx.x, G = gridDim.x;
+    if (static_cast<uint32_t>(__cvta_generic_to_shared(smem)) != BASE) {
+        if (tid == 0) atomicMax(a.status, 1u);
+        return;
+    }
+    for (int i = tid; i < 13 * 64; i += kMegaThreads) {
+        const int k = i >> 6;
+        tab[(k < 9 ? 28 * k + 27 : 243 + k) * 64 + (i & 63)] = 0;
+    }
+    uint32_t creg[8];
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+        uint32_t v = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) v |= static_cast<uint32_t>(((lane + 4 * q + j) & 31) * 4) << (8 * j);
+        asm volatile("mov.b32 %0, %1;" : "=r"(creg[q]) : "r"(v));
+    }
+    const int H = a.hidden, I = a.inter, hd = a.head_dim, qd = a.q_heads * hd, kvd = a.kv_heads * hd;
+    unsigned int bar_target = 0;
+#define MEGA_BARRIER()                                                   \
+    do {                                                                 \
+        bar_target += static_cast<unsigned int>(G);                      \
+        if (!grid_barrier(a.bar, bar_target, a.status, s_flag)) return;  \
+    } while (0)
+
+    float s_down_prev = 0.0f;  // activation scale of the previous layer's down projection
+    for (int l = 0; l < a.n_layers; ++l) {
+        const MegaLayer ly = a.layers[l];
+        // ---- phase A: residual (or embedding), norm, quantise, q|k|v ----
+        if (l == 0) {
+            const size_t base = static_cast<size_t>(a.token[0]) * H;
+            for (int i = tid; i < H; i += kMegaThreads) y_s[i] = __half2float(a.embed[base + i]);
+        } else {
+            const float post = s_down_prev > 0.0f ? __fdiv_rn(a.layers[l - 1].ws[6], s_down_prev) : 0.0f;
+            for (int i = tid; i < H; i += kMegaThreads) {
+                const float d = s_down_prev > 0.0f ? __fmul_rn(static_cast<float>(a.acc_down[i]), post) : 0.0f;
+                y_s[i] = __fadd_rn(a.xb[i], d);
+            }
+        }
+        __syncthreads();
+        if (cta == 0)
+            for (int i = tid; i < H; i += kMegaThreads) a.xa[i] = y_s[i];
+        const float s_h = mega_norm_quant(y_s, ly.attn_norm, H, a.eps, a8, sh_d, sh_f);
+        mega_gemv<BASE>(a.items, ly.first[0], ly.count[0], tab, a8, nullptr, 0.0f, a.acc_qkv, creg);
+        MEGA_BARRIER();
+        // ---- phase C: attention units; spare CTAs clear buffers that are idle now ----
+        for (int u = cta; u < a.q_heads * 4; u += G) mega_attention_unit(a, ly, u >> 2, u & 3, s_h, attn_scratch);
+        if (cta == G - 1) {
+            for (int i = tid; i < H; i += kMegaThreads) a.acc_down[i] = 0;  // read by every CTA in phase A, rewritten in F2
+            if (tid == 0) a.amax_bits[(l + 1) & 1] = 0u;
+        }
+        MEGA_BARRIER();
+        // ---- phase D: combine the chunks, quantise, o ----
+        {
+            const int pos = static_cast<int>(a.pos[0]), seq_len = pos + 1;
+            int n_kv = (seq_len + 255) / 256 * 256;
+            if (n_kv < 256) n_kv = 256;
+            if (n_kv > a.ctx) n_kv = a.ctx;
+            // per head: the factor of every chunk and the final 1/S, in the order of attention.rs:510-541
+            if (tid < a.q_heads) {
+                const float* pm = a.part_ms + static_cast<size_t>(tid) * 8;
+                float* pr = s_pair + tid * 8;  // [c][0] = scale_old, [c][1] = scale_new (negative scale_old marks a skipped chunk)
+                if (n_kv < 512) {
+                    const float S = pm[1];
+                    pr[0] = S == 0.0f ? 0.0f : __fdiv_rn(1.0f, S);
+                } else {
+                    float m_final = -INFINITY, s_final = 0.0f;
+                    for (int c = 0; c < 4; ++c) {
+                        const float m_chunk = pm[2 * c], s_chunk = pm[2 * c + 1];
+                        if (s_chunk == 0.0f) {
+                            pr[2 * c] = -1.0f;
+                            continue;
+                        }
+                        const float m_new = fmaxf(m_final, m_chunk);
+                        const float so = device_expf(__fsub_rn(m_final, m_new)), sn = device_expf(__fsub_rn(m_chunk, m_new));
+                        pr[2 * c] = so;
+                        pr[2 * c + 1] = sn;
+                        s_final = __fmaf_rn(s_final, so, __fmul_rn(s_chunk, sn));
+                        m_final = m_new;
+                    }
+                    s_pair[a.q_heads * 8 + tid] = s_final;
+                }
+            }
+            __syncthreads();
+            for (int i = tid; i < qd; i += kMegaThreads) {
+                const int h = i / hd, d = i % hd;
+                const float* pa = a.part_acc + static_cast<size_t>(h) * 4 * hd + d;
+                const float* pr = s_pair + h * 8;
+                float out;
+                if (n_kv < 512) {
+                    out = __fmul_rn(pa[0], pr[0]);
+                } else {
+                    float acc = 0.0f;
+                    for (int c = 0; c < 4; ++c) {
+                        if (pr[2 * c] < 0.0f) continue;
+                        acc = __fmaf_rn(acc, pr[2 * c], __fmul_rn(pa[c * hd], pr[2 * c + 1]));
+                    }
+                    const float s_final = s_pair[a.q_heads * 8 + h];
+                    out = s_final != 0.0f ? __fmul_rn(acc, __fdiv_rn(1.0f, s_final)) : acc;
+                }
+                y_s[i] = out;
+            }
+            __syncthreads();
+        }
+        float amax = 0.0f;
+        for (int i = tid; i < qd; i += kMegaThreads) amax = fmaxf(amax, fabsf(y_s[i]));
+        amax = block_max_f32(amax, sh_f);
+        const float s_q = amax > 0.0f ? __fdiv_rn(127.0f, amax) : 0.0f;
+        for (int i = tid; i < qd; i += kMegaThreads) a8[i] = static_cast<int8_t>(amax > 0.0f ? quantize_code(y_s[i], s_q) : 0);
+        __syncthreads();
+        mega_gemv<BASE>(a.items, ly.first[1], ly.count[1], tab, a8, nullptr, 0.0f, a.acc_o, creg);
+        MEGA_BARRIER();
+        // ---- phase E: residual, norm, quantise, gate|up ----
+        {
+            const float post = s_q > 0.0f ? __fdiv_rn(ly.ws[3], s_q) : 0.0f;
+            for (int i = tid; i < H; i += kMegaThreads) {
+                const float d = s_q > 0.0f ? __fmul_rn(static_cast<float>(a.acc_o[i]), post) : 0.0f;
+                y_s[i] = __fadd_rn(a.xa[i], d);
+            }
+            __syncthreads();
+            if (cta == 0)
+                for (int i = tid; i < H; i += kMegaThreads) a.xb[i] = y_s[i];
+            if (cta == G - 1)
+                for (int i = tid; i < qd + 2 * kvd; i += kMegaThreads) a.acc_qkv[i] = 0;  // consumed in phase C
+        }
+        const float s_f = mega_norm_quant(y_s, ly.ffn_norm, H, a.eps, a8, sh_d, sh_f);
+        mega_gemv<BASE>(a.items, ly.first[2], ly.count[2], tab, a8, nullptr, 0.0f, a.acc_gu, creg);
+        MEGA_BARRIER();
+        // ---- phase F1: SwiGLU on a slice, maximum of |v| ----
+        {
+            const float pg = s_f > 0.0f ? __fdiv_rn(ly.ws[4], s_f) : 0.0f, pu = s_f > 0.0f ? __fdiv_rn(ly.ws[5], s_f) : 0.0f;
+            float m = 0.0f;
+            for (int i = cta * kMegaThreads + tid; i < I; i += G * kMegaThreads) {
+                const float g = s_f > 0.0f ? __fmul_rn(static_cast<float>(a.acc_gu[i]), pg) : 0.0f;
+                const float u = s_f > 0.0f ? __fmul_rn(static_cast<float>(a.acc_gu[I + i]), pu) : 0.0f;
+                const float v = __fmul_rn(ggml_silu(g), u);
+                a.v_inter[i] = v;
+                m = fmaxf(m, fabsf(v));
+            }
+            m = block_max_f32(m, sh_f);
+            if (tid == 0 && m > 0.0f) atomicMax(a.amax_bits + (l & 1), __float_as_uint(m));  // non-negative floats order like their bits
+            if (cta == G - 1)
+                for (int i = tid; i < H; i += kMegaThreads) a.acc_o[i] = 0;  // consumed in phase E
+        }
+        MEGA_BARRIER();
+        // ---- phase F2: down, quantising v on the fly ----
+        {
+            const float vmax = __uint_as_float(*reinterpret_cast<volatile unsigned int*>(a.amax_bits + (l & 1)));
+            s_down_prev = vmax > 0.0f ? __fdiv_rn(127.0f, vmax) : 0.0f;
+            mega_gemv<BASE>(a.items, ly.first[3], ly.count[3], tab, nullptr, a.v_inter, s_down_prev, a.acc_down, creg);
+            for (int i = cta * kMegaThreads + tid; i < 2 * I; i += G * kMegaThreads) a.acc_gu[i] = 0;  // consumed in phase F1
+        }
+        MEGA_BARRIER();
+    }
+    // ---- final norm (model.rs:326-331), output head, greedy choice ----
+    {
+        const float post = s_down_prev > 0.0f ? __fdiv_rn(a.layers[a.n_layers - 1].ws[6], s_down_prev) : 0.0f;
+        for (int i = tid; i < H; i += kMegaThreads) {
+            const float d = s_down_prev > 0.0f ? __fmul_rn(static_cast<float>(a.acc_down[i]), post) : 0.0f;
+            y_s[i] = __fadd_rn(a.xb[i], d);
+        }
+        __syncthreads();
+        mega_norm_quant(y_s, a.out_norm, H, a.eps, nullptr, sh_d, sh_f);
+        for (int i = tid; i < H; i += kMegaThreads) y_s[i] = __half2float(__float2half_rn(y_s[i]));  // model.rs:347-349
+        __syncthreads();
+        float bv = -INFINITY;
+        unsigned int bi = 0xFFFFFFFFu;
+        const int np = H & ~31;
+        for (int row = cta * kMegaWarps + warp; row < a.vocab; row += G * kMegaWarps) {
+            const __half* wr = a.lm_head + static_cast<size_t>(row) * H;
+            float acc = 0.0f;
+#pragma unroll 8
+            for (int i = 0; i < np; i += 32) acc = __fmaf_rn(y_s[i + lane], __half2float(wr[i + lane]), acc);
+            float sum = dot_lane_reduce_f16(acc);
+            if (lane == 0) {
+                for (int i = np; i < H; ++i) sum = __fadd_rn(sum, __fmul_rn(y_s[i], __half2float(wr[i])));
+                a.logits[row] = sum;
+                argmax_merge(bv, bi, sum, static_cast<unsigned int>(row));
+            }
+        }
+        float* s_bv = reinterpret_cast<float*>(attn_scratch);
+        unsigned int* s_bi = reinterpret_cast<unsigned int*>(attn_scratch + 256);
+        if (lane == 0) {
+            s_bv[warp] = bv;
+            s_bi[warp] = bi;
+        }
+        __syncthreads();
+        if (tid == 0) {
+            for (int w = 1; w < kMegaWarps; ++w) argmax_merge(bv, bi, s_bv[w], s_bi[w]);
+            a.best_val[cta] = bv;
+            a.best_idx[cta] = bi;
+        }
+    }
+    MEGA_BARRIER();
+    if (cta == 0) {
+        for (int i = tid; i < H; i += kMegaThreads) a.acc_down[i] = 0;
+        if (tid == 0) {
+            float bv = -INFINITY;
+            unsigned int bi = 0xFFFFFFFFu;
+            for (int c = 0; c < G; ++c) argmax_merge(bv, bi, *reinterpret_cast<volatile float*>(a.best_val + c), *reinterpret_cast<volatile unsigned int*>(a.best_idx + c));
+            const uint32_t tok = bi == 0xFFFFFFFFu ? 0u : bi;
+            a.token[0] = tok;
+            a.history[a.pos[0]] = tok;
+            a.pos[0] += 1;
+            a.amax_bits[0] = 0u;
+            a.amax_bits[1] = 0u;
+        }
+    }
+#undef MEGA_BARRIER
+}
+
+}  // namespace qtb
