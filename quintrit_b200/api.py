@@ -100,6 +100,7 @@ def load_library(build_if_missing: bool = True) -> C.CDLL:
     l.quintrit_b200_decoder_forward.argtypes = [C.c_void_p, C.c_uint32, C.c_uint32, _f32p, _sz, C.POINTER(C.c_uint32)]
     l.quintrit_b200_decoder_generate.argtypes = [C.c_void_p, C.POINTER(C.c_uint32), _sz, _sz, C.POINTER(C.c_uint32), _sz]
     l.quintrit_b200_decoder_time_token.argtypes = [C.c_void_p, C.c_uint32, C.c_uint32, C.POINTER(C.c_float)]
+    l.quintrit_b200_decoder_trace_step.argtypes = [C.c_void_p, C.POINTER(C.c_uint64), _sz, C.POINTER(_sz)]
     l.quintrit_b200_launch_count.restype = C.c_uint64
     l.quintrit_b200_launch_count.argtypes = [C.c_int]
     _lib = l
@@ -333,6 +334,14 @@ class Decoder:
         out = np.zeros(max_new, np.uint32)
         _check(load_library().quintrit_b200_decoder_generate(self._h, _p(p, C.POINTER(C.c_uint32)), p.size, max_new,
                                                              _p(out, C.POINTER(C.c_uint32)), out.size))
+        return out
+
+    def trace_step(self) -> np.ndarray:
+        """Global-timer stamps (ns) of one decode step at every phase boundary (single-kernel path only)."""
+        n = _sz(0)
+        load_library().quintrit_b200_decoder_trace_step(self._h, None, 0, C.byref(n))
+        out = np.zeros(n.value, np.uint64)
+        _check(load_library().quintrit_b200_decoder_trace_step(self._h, _p(out, C.POINTER(C.c_uint64)), out.size, C.byref(n)))
         return out
 
     def time_token(self, blocks: int = 5, iters: int = 50) -> float:

@@ -801,7 +801,7 @@ int mega_setup(quintrit_b200_decoder* d, const quintrit_b200_decoder_desc_t* des
     if ((rc = dev_alloc(d, &d->xa, H)) != QUINTRIT_OK || (rc = dev_alloc(d, &d->xb, H)) != QUINTRIT_OK ||
         (rc = dev_alloc(d, &d->v_inter, I)) != QUINTRIT_OK || (rc = dev_alloc(d, &d->amax_bits, 4)) != QUINTRIT_OK ||
         (rc = dev_alloc(d, &d->best_val, d->sm_count)) != QUINTRIT_OK || (rc = dev_alloc(d, &d->best_idx, d->sm_count)) != QUINTRIT_OK ||
-        (rc = dev_alloc(d, &d->bar, 4)) != QUINTRIT_OK)
+        (rc = dev_alloc(d, &d->bar, 4)) != QUINTRIT_OK || (rc = dev_alloc(d, &d->trace, size_t(L) * 13 + 8)) != QUINTRIT_OK)
         return rc;
     std::vector<GemvItem> items;
     std::vector<MegaLayer> layers(L);
@@ -838,7 +838,7 @@ int mega_setup(quintrit_b200_decoder* d, const quintrit_b200_decoder_desc_t* des
     a.acc_qkv = d->acc_qkv, a.acc_o = d->acc_o, a.acc_gu = d->acc_gu, a.acc_down = d->acc_down;
     a.v_inter = d->v_inter, a.amax_bits = d->amax_bits, a.part_acc = d->part_acc, a.part_ms = d->part_ms, a.logits = d->logits;
     a.best_val = d->best_val, a.best_idx = d->best_idx, a.token = d->d_token, a.pos = d->d_pos, a.history = d->d_history;
-    a.bar = d->bar, a.status = d->d_counters + 2;
+    a.bar = d->bar, a.status = d->d_counters + 2, a.trace = nullptr;
     d->mega_smem = mega_smem_bytes(std::max(H, qd));
     // the table-base constant: measured once per device like the GEMV kernel's
     unsigned int base = 0xFFFFFFFFu;
@@ -1113,5 +1113,27 @@ extern "C" int quintrit_b200_gemv_i32_noalloc(const quintrit_b200_matrix_t* matr
         ++g_launches;
         QTB_CUDA(cudaGetLastError());
         return ok();
+    });
+}
+
+extern "C" int quintrit_b200_decoder_trace_step(quintrit_b200_decoder_t* decoder, uint64_t* out_ns, size_t capacity, size_t* out_count) {
+    return guard([&]() -> int {
+        int rc = check_decoder(decoder);
+        if (rc != QUINTRIT_OK) return rc;
+        quintrit_b200_decoder* d = decoder;
+        if (out_count == nullptr) return fail(QUINTRIT_ERR_NULL_POINTER, "out_count is NULL");
+        if (!d->use_mega) return fail(QUINTRIT_ERR_UNSUPPORTED, "phase tracing is available for the single-kernel decode path only");
+        const size_t n = size_t(d->layers) * 13 + 4;
+        *out_count = n;
+        if (out_ns == nullptr || capacity < n) return fail(QUINTRIT_ERR_BUFFER_TOO_SMALL, "out_ns holds %zu values, %zu are needed", capacity, n);
+        if (d->host_pos >= static_cast<uint32_t>(d->ctx)) return fail(QUINTRIT_ERR_CONTEXT_OVERFLOW, "the context window is full");
+        DeviceGuard g(d->device);
+        d->mega.trace = d->trace;
+        rc = decoder_set(d, 0, d->host_pos);
+        if (rc == QUINTRIT_OK) rc = decoder_step(d);
+        d->mega.trace = nullptr;
+        if (rc != QUINTRIT_OK) return rc;
+        QTB_CUDA(cudaMemcpyAsync(out_ns, d->trace, n * sizeof(uint64_t), cudaMemcpyDeviceToHost, d->stream));
+        return decoder_check_status(d) == QUINTRIT_OK ? ok() : quintrit_last_error_code();
     });
 }

@@ -58,7 +58,14 @@ struct MegaArgs {
     uint32_t* history;
     unsigned int* bar;        // grid barrier counter, cleared by the host before every launch
     unsigned int* status;     // 0 = fine, 1 = wrong shared-memory base, 2 = a barrier timed out
+    unsigned long long* trace; // optional: CTA 0 stores the global timer at every phase boundary (7 per layer + 3)
 };
+
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
 
 // Grid-wide barrier with a bounded wait. Returns false (in every thread of the CTA) if it gave up.
 __device__ __forceinline__ bool grid_barrier(unsigned int* bar, unsigned int target, unsigned int* status, int* s_flag) {
@@ -389,6 +396,12 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(MegaArgs 
         if (!grid_barrier(a.bar, bar_target, a.status, s_flag)) return;  \
     } while (0)
 
+    int trace_n = 0;
+#define MEGA_TRACE()                                                                       \
+    do {                                                                                   \
+        if (a.trace != nullptr && cta == 0 && tid == 0) a.trace[trace_n++] = global_timer_ns(); \
+    } while (0)
+    MEGA_TRACE();
     float s_down_prev = 0.0f;  // activation scale of the previous layer's down projection
     for (int l = 0; l < a.n_layers; ++l) {
         const MegaLayer ly = a.layers[l];
@@ -407,15 +420,20 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(MegaArgs 
         if (cta == 0)
             for (int i = tid; i < H; i += kMegaThreads) a.xa[i] = y_s[i];
         const float s_h = mega_norm_quant(y_s, ly.attn_norm, H, a.eps, a8, sh_d, sh_f);
+        MEGA_TRACE();  // 1: norm done
         mega_gemv<BASE>(a.items, ly.first[0], ly.count[0], tab, a8, nullptr, 0.0f, a.acc_qkv, creg);
+        MEGA_TRACE();  // 2: q|k|v streamed (this CTA)
         MEGA_BARRIER();
+        MEGA_TRACE();  // 3
         // ---- phase C: attention units; spare CTAs clear buffers that are idle now ----
         for (int u = cta; u < a.q_heads * 4; u += G) mega_attention_unit(a, ly, u >> 2, u & 3, s_h, attn_scratch);
         if (cta == G - 1) {
             for (int i = tid; i < H; i += kMegaThreads) a.acc_down[i] = 0;  // read by every CTA in phase A, rewritten in F2
             if (tid == 0) a.amax_bits[(l + 1) & 1] = 0u;
         }
+        MEGA_TRACE();  // 4: attention unit done (this CTA)
         MEGA_BARRIER();
+        MEGA_TRACE();  // 5
         // ---- phase D: combine the chunks, quantise, o ----
         {
             const int pos = static_cast<int>(a.pos[0]), seq_len = pos + 1;
@@ -474,8 +492,10 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(MegaArgs 
         const float s_q = amax > 0.0f ? __fdiv_rn(127.0f, amax) : 0.0f;
         for (int i = tid; i < qd; i += kMegaThreads) a8[i] = static_cast<int8_t>(amax > 0.0f ? quantize_code(y_s[i], s_q) : 0);
         __syncthreads();
+        MEGA_TRACE();  // 6: combine + quantise done
         mega_gemv<BASE>(a.items, ly.first[1], ly.count[1], tab, a8, nullptr, 0.0f, a.acc_o, creg);
         MEGA_BARRIER();
+        MEGA_TRACE();  // 7
         // ---- phase E: residual, norm, quantise, gate|up ----
         {
             const float post = s_q > 0.0f ? __fdiv_rn(ly.ws[3], s_q) : 0.0f;
@@ -490,8 +510,11 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(MegaArgs 
                 for (int i = tid; i < qd + 2 * kvd; i += kMegaThreads) a.acc_qkv[i] = 0;  // consumed in phase C
         }
         const float s_f = mega_norm_quant(y_s, ly.ffn_norm, H, a.eps, a8, sh_d, sh_f);
+        MEGA_TRACE();  // 8: norm done
         mega_gemv<BASE>(a.items, ly.first[2], ly.count[2], tab, a8, nullptr, 0.0f, a.acc_gu, creg);
+        MEGA_TRACE();  // 9: gate|up streamed (this CTA)
         MEGA_BARRIER();
+        MEGA_TRACE();  // 10
         // ---- phase F1: SwiGLU on a slice, maximum of |v| ----
         {
             const float pg = s_f > 0.0f ? __fdiv_rn(ly.ws[4], s_f) : 0.0f, pu = s_f > 0.0f ? __fdiv_rn(ly.ws[5], s_f) : 0.0f;
@@ -509,14 +532,17 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(MegaArgs 
                 for (int i = tid; i < H; i += kMegaThreads) a.acc_o[i] = 0;  // consumed in phase E
         }
         MEGA_BARRIER();
+        MEGA_TRACE();  // 11
         // ---- phase F2: down, quantising v on the fly ----
         {
             const float vmax = __uint_as_float(*reinterpret_cast<volatile unsigned int*>(a.amax_bits + (l & 1)));
             s_down_prev = vmax > 0.0f ? __fdiv_rn(127.0f, vmax) : 0.0f;
             mega_gemv<BASE>(a.items, ly.first[3], ly.count[3], tab, nullptr, a.v_inter, s_down_prev, a.acc_down, creg);
+            MEGA_TRACE();  // 12: down streamed (this CTA)
             for (int i = cta * kMegaThreads + tid; i < 2 * I; i += G * kMegaThreads) a.acc_gu[i] = 0;  // consumed in phase F1
         }
         MEGA_BARRIER();
+        MEGA_TRACE();  // 13 = 0 of the next layer
     }
     // ---- final norm (model.rs:326-331), output head, greedy choice ----
     {
@@ -557,7 +583,9 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(MegaArgs 
             a.best_idx[cta] = bi;
         }
     }
+    MEGA_TRACE();  // head done (this CTA)
     MEGA_BARRIER();
+    MEGA_TRACE();
     if (cta == 0) {
         for (int i = tid; i < H; i += kMegaThreads) a.acc_down[i] = 0;
         if (tid == 0) {
@@ -573,6 +601,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(MegaArgs 
         }
     }
 #undef MEGA_BARRIER
+#undef MEGA_TRACE
 }
 
 }  // namespace qtb
