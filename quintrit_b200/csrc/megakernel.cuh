@@ -120,11 +120,24 @@ __device__ __forceinline__ int quantize_code(float y, float s) {
 
 // The GEMV share of this CTA in one phase: items first + blockIdx.x, + gridDim.x, ... Activations come either from
 // shared memory as int8 codes (act_s) or from global memory as floats that are quantised here with scale `qs`.
+// Column bytes of the diagonal walk: word q, byte j -> ((lane + 4 q + j) mod 32) * 4 (see gemv_lut_kernel).
+__device__ __forceinline__ void make_column_words(uint32_t (&creg)[8], int lane) {
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+        uint32_t v = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) v |= static_cast<uint32_t>(((lane + 4 * q + j) & 31) * 4) << (8 * j);
+        asm volatile("mov.b32 %0, %1;" : "=r"(creg[q]) : "r"(v));
+    }
+}
+
+// Not inlined: each phase gets its own register allocation instead of competing inside one huge function.
 template <uint32_t BASE>
-__device__ __forceinline__ void mega_gemv(const GemvItem* __restrict__ items, int first, int count, int* tab, const int8_t* act_s,
-                                          const float* __restrict__ act_f, float qs, int32_t* __restrict__ out_base,
-                                          const uint32_t (&creg)[8]) {
+__device__ __noinline__ void mega_gemv(const GemvItem* __restrict__ items, int first, int count, int* tab, const int8_t* act_s,
+                                       const float* __restrict__ act_f, float qs, int32_t* __restrict__ out_base) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    uint32_t creg[8];
+    make_column_words(creg, lane);
     for (int k = blockIdx.x; k < count; k += gridDim.x) {
         const GemvItem it = items[first + k];
         {
@@ -144,24 +157,32 @@ __device__ __forceinline__ void mega_gemv(const GemvItem* __restrict__ items, in
         const uint4* wb = it.wb + lane;
         int32_t* out = out_base + it.out_off + it.tile0 * kTileRows + lane;
         const int rows_left = it.rows - it.tile0 * kTileRows - lane;
-        TileRegs ra, rb;
+        // three row tiles in flight per warp
+        TileRegs ra, rb, rc;
+        const int n = it.ntiles, W = kMegaWarps;
         int t = warp;
-        if (t < it.ntiles) load_tile(ra, wa, wb, it.nblk, t, 0);
-        while (t < it.ntiles) {
-            const int t1 = t + kMegaWarps;
-            if (t1 < it.ntiles) load_tile(rb, wa, wb, it.nblk, t1, 0);
+        if (t < n) load_tile(ra, wa, wb, it.nblk, t, 0);
+        if (t + W < n) load_tile(rb, wa, wb, it.nblk, t + W, 0);
+        if (t + 2 * W < n) load_tile(rc, wa, wb, it.nblk, t + 2 * W, 0);
+        while (t < n) {
             {
                 const int acc = tile_sum<BASE>(ra, it.nblk, creg);
                 if (t * kTileRows < rows_left) atomicAdd(out + t * kTileRows, acc);
             }
-            if (t1 >= it.ntiles) break;
-            const int t2 = t1 + kMegaWarps;
-            if (t2 < it.ntiles) load_tile(ra, wa, wb, it.nblk, t2, 0);
+            if (t + 3 * W < n) load_tile(ra, wa, wb, it.nblk, t + 3 * W, 0);
+            if (t + W >= n) break;
             {
                 const int acc = tile_sum<BASE>(rb, it.nblk, creg);
-                if (t1 * kTileRows < rows_left) atomicAdd(out + t1 * kTileRows, acc);
+                if ((t + W) * kTileRows < rows_left) atomicAdd(out + (t + W) * kTileRows, acc);
             }
-            t = t2;
+            if (t + 4 * W < n) load_tile(rb, wa, wb, it.nblk, t + 4 * W, 0);
+            if (t + 2 * W >= n) break;
+            {
+                const int acc = tile_sum<BASE>(rc, it.nblk, creg);
+                if ((t + 2 * W) * kTileRows < rows_left) atomicAdd(out + (t + 2 * W) * kTileRows, acc);
+            }
+            if (t + 5 * W < n) load_tile(rc, wa, wb, it.nblk, t + 5 * W, 0);
+            t += 3 * W;
         }
         __syncthreads();  // the table is rewritten by the next item
     }
@@ -191,15 +212,42 @@ __device__ __forceinline__ float mega_norm_quant(float* y_s, const float* __rest
     return s;
 }
 
+// 16-byte asynchronous copy global -> shared (bypasses registers; completion through cp.async.wait_group).
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst))), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+constexpr int kAttnBlockPos = 32;  // positions staged in shared memory at a time
+constexpr int kAttnStages = 4;     // blocks in flight (a ring of kAttnStages buffers)
+
+// Copies rows [p0, p0 + 32) of a KV chunk (head_dim halves each, row stride kvd halves) into `dst` ([32][hd] halves),
+// 16 bytes per thread and copy; rows at or beyond `len` are skipped, the row of the current position (if `cur` is
+// inside the block) comes from shared memory afterwards.
+__device__ __forceinline__ void stage_rows(__half* dst, const __half* src, int p0, int len, int hd, int kvd) {
+    const int vec_per_row = hd / 8;  // 16-byte pieces per row
+    for (int v = threadIdx.x; v < kAttnBlockPos * vec_per_row; v += kMegaThreads) {
+        const int r = v / vec_per_row, c = v % vec_per_row;
+        if (p0 + r < len) cp_async16(dst + r * hd + c * 8, src + static_cast<size_t>(p0 + r) * kvd + c * 8);
+    }
+}
+
 // One (query head, KV chunk) of the attention of one layer: attention_kernel with the RoPE of q and of the new key, the
-// post-scaling and the KV append folded in (rope_kv_kernel), so that no barrier is needed between them.
-__device__ __forceinline__ void mega_attention_unit(const MegaArgs& a, const MegaLayer& ly, int h, int c, float s_in, unsigned char* scratch) {
+// post-scaling and the KV append folded in (rope_kv_kernel), so that no barrier is needed between them. K and V rows
+// are staged through shared memory in blocks of 32 positions with asynchronous copies, double-buffered, so the strictly
+// sequential value accumulation never waits for global memory.
+__device__ __noinline__ void mega_attention_unit(const MegaArgs& a, const MegaLayer& ly, int h, int c, float s_in, unsigned char* scratch) {
     float* s_score = reinterpret_cast<float*>(scratch);            // kAttnMaxChunk floats
     float* s_ms = s_score + kAttnMaxChunk;                         // kAttnMaxChunk floats
     float* s_q = s_ms + kAttnMaxChunk;                             // 256 floats
     float* s_tm = s_q + 256;                                       // kMegaThreads floats
     __half* s_kcur = reinterpret_cast<__half*>(s_tm + kMegaThreads);  // 256 halves
     __half* s_vcur = s_kcur + 256;
+    __half* s_stage = s_vcur + 256;                                // kAttnStages x [32][256] halves
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int hd = a.head_dim, gqa = a.q_heads / a.kv_heads, kvh = h / gqa;
     const int qd = a.q_heads * hd, kvd = a.kv_heads * hd;
@@ -225,11 +273,21 @@ __device__ __forceinline__ void mega_attention_unit(const MegaArgs& a, const Meg
         }
         return;
     }
+    const __half* kbase = ly.kc + static_cast<size_t>(kvh) * hd + static_cast<size_t>(start) * kvd;
+    const __half* vbase = ly.vc + static_cast<size_t>(kvh) * hd + static_cast<size_t>(start) * kvd;
+    const bool has_cur = pos >= start && pos < end;
+    const int pcur = pos - start;            // index of the current position inside the chunk (valid if has_cur)
+    const int len_old = has_cur ? pcur : len;  // rows that come from the cache (the current position is the last one)
+    const int nblk = (len + kAttnBlockPos - 1) / kAttnBlockPos;
+    // the first K blocks are on their way while q and the new key are prepared
+    for (int b = 0; b < kAttnStages - 1; ++b) {
+        if (b < nblk) stage_rows(s_stage + b * kAttnBlockPos * 256, kbase, b * kAttnBlockPos, len_old, hd, kvd);
+        cp_async_commit();
+    }
+
     const bool live = s_in > 0.0f;
     const float pq = live ? __fdiv_rn(ly.ws[0], s_in) : 0.0f, pk = live ? __fdiv_rn(ly.ws[1], s_in) : 0.0f, pv = live ? __fdiv_rn(ly.ws[2], s_in) : 0.0f;
     const float* cs = a.cos_sin + static_cast<size_t>(pos) * a.rope_dims;
-    const bool has_cur = pos >= start && pos < end;
-    // q of this head (pairs 2p, 2p+1), and the new key / value of its KV head when the chunk holds the current position
     for (int p = tid; p < hd / 2; p += kMegaThreads) {
         const bool rot = p < a.rope_dims / 2;
         float c0 = 1.0f, sn = 0.0f;
@@ -265,45 +323,64 @@ __device__ __forceinline__ void mega_attention_unit(const MegaArgs& a, const Meg
         }
     }
     __syncthreads();
-    const __half* kbase = ly.kc + static_cast<size_t>(kvh) * hd;
-    const __half* vbase = ly.vc + static_cast<size_t>(kvh) * hd;
     if (has_cur && h % gqa == 0) {  // append to the cache (kv_cache.rs:124-138); one unit per KV head does it
         for (int d = tid; d < hd; d += kMegaThreads) {
-            const_cast<__half*>(kbase)[static_cast<size_t>(pos) * kvd + d] = s_kcur[d];
-            const_cast<__half*>(vbase)[static_cast<size_t>(pos) * kvd + d] = s_vcur[d];
+            const_cast<__half*>(kbase)[static_cast<size_t>(pcur) * kvd + d] = s_kcur[d];
+            const_cast<__half*>(vbase)[static_cast<size_t>(pcur) * kvd + d] = s_vcur[d];
         }
     }
-    // scores: one warp per position, lane = accumulator lane of the reference's dot product, four positions in flight
-    for (int p0 = warp * 4; p0 < len; p0 += kMegaWarps * 4) {
-        float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            const int p = p0 + u;
-            if (p < len) {
-                const int gp = start + p;
-                const __half* kr = gp == pos ? s_kcur : kbase + static_cast<size_t>(gp) * kvd;
-                for (int i = 0; i + 32 <= hd; i += 32) acc[u] = __fmaf_rn(__half2float(kr[i + lane]), s_q[i + lane], acc[u]);
+    // ---- scores: block by block; one warp per position, lane = accumulator lane of the reference's dot product ----
+    for (int b = 0; b < nblk; ++b) {
+        __half* buf = s_stage + (b % kAttnStages) * kAttnBlockPos * 256;
+        const int nb = b + kAttnStages - 1;
+        if (nb < nblk) stage_rows(s_stage + (nb % kAttnStages) * kAttnBlockPos * 256, kbase, nb * kAttnBlockPos, len_old, hd, kvd);
+        cp_async_commit();
+        cp_async_wait<kAttnStages - 1>();
+        __syncthreads();
+        {
+            // a warp takes rows warp and warp + 16 of the block; both dot products run interleaved
+            static_assert(kAttnBlockPos == 2 * kMegaWarps, "two positions per warp and block");
+            const int pA = b * kAttnBlockPos + warp, pB = pA + kMegaWarps;
+            const __half* krA = (has_cur && pA == pcur) ? s_kcur : buf + warp * hd;
+            const __half* krB = (has_cur && pB == pcur) ? s_kcur : buf + (warp + kMegaWarps) * hd;
+            float accA = 0.0f, accB = 0.0f;
+#pragma unroll 4
+            for (int i = 0; i + 32 <= hd; i += 32) {
+                const float qv = s_q[i + lane];
+                accA = __fmaf_rn(__half2float(krA[i + lane]), qv, accA);
+                accB = __fmaf_rn(__half2float(krB[i + lane]), qv, accB);
+            }
+            const float scA = a.f32_values ? dot_lane_reduce_f16_f32(accA) : dot_lane_reduce_f16(accA);
+            const float scB = a.f32_values ? dot_lane_reduce_f16_f32(accB) : dot_lane_reduce_f16(accB);
+            if (lane == 0) {
+                if (pA < len) s_score[pA] = __fmul_rn(scA, a.attn_scale);
+                if (pB < len) s_score[pB] = __fmul_rn(scB, a.attn_scale);
             }
         }
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            const int p = p0 + u;
-            if (p < len) {
-                const float sc = a.f32_values ? dot_lane_reduce_f16_f32(acc[u]) : dot_lane_reduce_f16(acc[u]);
-                if (lane == 0) s_score[p] = __fmul_rn(sc, a.attn_scale);
-            }
-        }
+        __syncthreads();  // the buffer is refilled two blocks later
     }
-    __syncthreads();
+    // the first V blocks are on their way while the softmax factors are computed
+    for (int b = 0; b < kAttnStages - 1; ++b) {
+        if (b < nblk) stage_rows(s_stage + b * kAttnBlockPos * 256, vbase, b * kAttnBlockPos, len_old, hd, kvd);
+        cp_async_commit();
+    }
     {
+        // running maximum in position order: maximum of the thread's own positions, an exclusive scan over the threads
+        // (shuffles inside a warp, a short loop over the earlier warps), then ms / vs per position (attention.rs:448-462)
         const int per = (len + kMegaThreads - 1) / kMegaThreads;
         const int p0 = min(tid * per, len), p1 = min(p0 + per, len);
         float m = -INFINITY;
         for (int p = p0; p < p1; ++p) m = fmaxf(m, s_score[p]);
-        s_tm[tid] = m;
+        float incl = m;
+        for (int o = 1; o < 32; o <<= 1) {
+            const float t = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl = fmaxf(incl, t);
+        }
+        if (lane == 31) s_tm[warp] = incl;
         __syncthreads();
-        float run = -INFINITY;
-        for (int t = 0; t < tid; ++t) run = fmaxf(run, s_tm[t]);
+        float run = __shfl_up_sync(0xffffffffu, incl, 1);
+        if (lane == 0) run = -INFINITY;
+        for (int w = 0; w < warp; ++w) run = fmaxf(run, s_tm[w]);
         for (int p = p0; p < p1; ++p) {
             const float sc = s_score[p];
             const float m_old = run;
@@ -318,42 +395,69 @@ __device__ __forceinline__ void mega_attention_unit(const MegaArgs& a, const Meg
             s_score[p] = vs;
         }
         __syncthreads();
-        if (tid == 0) {
+    }
+    // ---- values: warps 0..hd/32-1 run the chain, one thread per coordinate, strictly in position order; the last warp
+    // computes M and S meanwhile; every thread helps staging ----
+    const bool chain = tid < hd;
+    float acc32 = 0.0f;
+    __half acc16 = __float2half_rn(0.0f);
+    for (int b = 0; b < nblk; ++b) {
+        const __half* buf = s_stage + (b % kAttnStages) * kAttnBlockPos * 256;
+        const int nb = b + kAttnStages - 1;
+        if (nb < nblk) stage_rows(s_stage + (nb % kAttnStages) * kAttnBlockPos * 256, vbase, nb * kAttnBlockPos, len_old, hd, kvd);
+        cp_async_commit();
+        cp_async_wait<kAttnStages - 1>();
+        __syncthreads();
+        if (chain) {
+            // Groups of eight positions: the factors and the values of a group are fetched from shared memory into
+            // registers before its eight dependent steps run, so the chain itself never waits for a load.
+            const int pe = min(kAttnBlockPos, len - b * kAttnBlockPos);
+            const int pb = b * kAttnBlockPos;
+            for (int g0 = 0; g0 < pe; g0 += 8) {
+                float msr[8], vsr[8];
+                __half vr[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const int r = min(g0 + j, pe - 1), p = pb + r;
+                    msr[j] = s_ms[p];
+                    vsr[j] = s_score[p];
+                    vr[j] = (has_cur && p == pcur) ? s_vcur[tid] : buf[r * hd + tid];
+                }
+                if (a.f32_values) {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        if (g0 + j < pe) {
+                            if (msr[j] != 1.0f) acc32 = __fmul_rn(acc32, msr[j]);
+                            acc32 = __fmaf_rn(__half2float(vr[j]), vsr[j], acc32);
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        if (g0 + j < pe) {
+                            if (msr[j] != 1.0f) acc16 = __float2half_rn(__fmul_rn(__half2float(acc16), msr[j]));
+                            acc16 = __float2half_rn(__fmaf_rn(__half2float(vr[j]), vsr[j], __half2float(acc16)));
+                        }
+                    }
+                }
+            }
+        } else if (b == 0 && tid == kMegaThreads - 1) {
             float S = 0.0f, M = -INFINITY;
-            for (int t = 0; t < kMegaThreads; ++t) M = fmaxf(M, s_tm[t]);
-            for (int p = 0; p < len; ++p) S = __fmaf_rn(S, s_ms[p], s_score[p]);
+            for (int w = 0; w < kMegaWarps; ++w) M = fmaxf(M, s_tm[w]);
+#pragma unroll 8
+            for (int p = 0; p < len; ++p) S = __fmaf_rn(S, s_ms[p], s_score[p]);  // attention.rs:466
             my_ms[0] = M;
             my_ms[1] = S;
         }
+        __syncthreads();
     }
-    for (int d = tid; d < hd; d += kMegaThreads) {
-        const __half* vr = vbase + static_cast<size_t>(start) * kvd + d;
-        const int pcur = pos - start;  // index of the current position inside the chunk, if it is in it
-        if (a.f32_values) {
-            float acc = 0.0f;
-            for (int p = 0; p < len; ++p) {
-                const float ms = s_ms[p];
-                if (ms != 1.0f) acc = __fmul_rn(acc, ms);
-                const __half v = p == pcur ? s_vcur[d] : vr[static_cast<size_t>(p) * kvd];
-                acc = __fmaf_rn(__half2float(v), s_score[p], acc);
-            }
-            my_acc[d] = acc;
-        } else {
-            __half acc = __float2half_rn(0.0f);
-            for (int p = 0; p < len; ++p) {
-                const float ms = s_ms[p];
-                if (ms != 1.0f) acc = __float2half_rn(__fmul_rn(__half2float(acc), ms));
-                const __half v = p == pcur ? s_vcur[d] : vr[static_cast<size_t>(p) * kvd];
-                acc = __float2half_rn(__fmaf_rn(__half2float(v), s_score[p], __half2float(acc)));
-            }
-            my_acc[d] = __half2float(acc);
-        }
-    }
+    cp_async_wait<0>();
+    if (chain) my_acc[tid] = a.f32_values ? acc32 : __half2float(acc16);
     __syncthreads();  // the scratch is reused
 }
 
 // Shared-memory plan of the megakernel (bytes from the dynamic base): table | attention scratch | y (floats) | a8 | small
-constexpr int kMegaAttnScratch = (2 * kAttnMaxChunk + 256 + kMegaThreads) * 4 + 2 * 256 * 2;
+constexpr int kMegaAttnScratch = (2 * kAttnMaxChunk + 256 + kMegaThreads) * 4 + 2 * 256 * 2 + kAttnStages * kAttnBlockPos * 256 * 2;
 __host__ __device__ constexpr size_t mega_smem_bytes(int maxvec) {
     return static_cast<size_t>(kTableBytes) + kMegaAttnScratch + static_cast<size_t>(maxvec) * 4 + (static_cast<size_t>(maxvec) + 15) / 16 * 16 + 4096;
 }
@@ -379,14 +483,6 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(MegaArgs 
     for (int i = tid; i < 13 * 64; i += kMegaThreads) {
         const int k = i >> 6;
         tab[(k < 9 ? 28 * k + 27 : 243 + k) * 64 + (i & 63)] = 0;
-    }
-    uint32_t creg[8];
-#pragma unroll
-    for (int q = 0; q < 8; ++q) {
-        uint32_t v = 0;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) v |= static_cast<uint32_t>(((lane + 4 * q + j) & 31) * 4) << (8 * j);
-        asm volatile("mov.b32 %0, %1;" : "=r"(creg[q]) : "r"(v));
     }
     const int H = a.hidden, I = a.inter, hd = a.head_dim, qd = a.q_heads * hd, kvd = a.kv_heads * hd;
     unsigned int bar_target = 0;
@@ -421,7 +517,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(MegaArgs 
             for (int i = tid; i < H; i += kMegaThreads) a.xa[i] = y_s[i];
         const float s_h = mega_norm_quant(y_s, ly.attn_norm, H, a.eps, a8, sh_d, sh_f);
         MEGA_TRACE();  // 1: norm done
-        mega_gemv<BASE>(a.items, ly.first[0], ly.count[0], tab, a8, nullptr, 0.0f, a.acc_qkv, creg);
+        mega_gemv<BASE>(a.items, ly.first[0], ly.count[0], tab, a8, nullptr, 0.0f, a.acc_qkv);
         MEGA_TRACE();  // 2: q|k|v streamed (this CTA)
         MEGA_BARRIER();
         MEGA_TRACE();  // 3
@@ -493,7 +589,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(MegaArgs 
         for (int i = tid; i < qd; i += kMegaThreads) a8[i] = static_cast<int8_t>(amax > 0.0f ? quantize_code(y_s[i], s_q) : 0);
         __syncthreads();
         MEGA_TRACE();  // 6: combine + quantise done
-        mega_gemv<BASE>(a.items, ly.first[1], ly.count[1], tab, a8, nullptr, 0.0f, a.acc_o, creg);
+        mega_gemv<BASE>(a.items, ly.first[1], ly.count[1], tab, a8, nullptr, 0.0f, a.acc_o);
         MEGA_BARRIER();
         MEGA_TRACE();  // 7
         // ---- phase E: residual, norm, quantise, gate|up ----
@@ -511,7 +607,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(MegaArgs 
         }
         const float s_f = mega_norm_quant(y_s, ly.ffn_norm, H, a.eps, a8, sh_d, sh_f);
         MEGA_TRACE();  // 8: norm done
-        mega_gemv<BASE>(a.items, ly.first[2], ly.count[2], tab, a8, nullptr, 0.0f, a.acc_gu, creg);
+        mega_gemv<BASE>(a.items, ly.first[2], ly.count[2], tab, a8, nullptr, 0.0f, a.acc_gu);
         MEGA_TRACE();  // 9: gate|up streamed (this CTA)
         MEGA_BARRIER();
         MEGA_TRACE();  // 10
@@ -537,7 +633,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(MegaArgs 
         {
             const float vmax = __uint_as_float(*reinterpret_cast<volatile unsigned int*>(a.amax_bits + (l & 1)));
             s_down_prev = vmax > 0.0f ? __fdiv_rn(127.0f, vmax) : 0.0f;
-            mega_gemv<BASE>(a.items, ly.first[3], ly.count[3], tab, nullptr, a.v_inter, s_down_prev, a.acc_down, creg);
+            mega_gemv<BASE>(a.items, ly.first[3], ly.count[3], tab, nullptr, a.v_inter, s_down_prev, a.acc_down);
             MEGA_TRACE();  // 12: down streamed (this CTA)
             for (int i = cta * kMegaThreads + tid; i < 2 * I; i += G * kMegaThreads) a.acc_gu[i] = 0;  // consumed in phase F1
         }
@@ -558,18 +654,52 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(MegaArgs 
         float bv = -INFINITY;
         unsigned int bi = 0xFFFFFFFFu;
         const int np = H & ~31;
-        for (int row = cta * kMegaWarps + warp; row < a.vocab; row += G * kMegaWarps) {
-            const __half* wr = a.lm_head + static_cast<size_t>(row) * H;
-            float acc = 0.0f;
-#pragma unroll 8
-            for (int i = 0; i < np; i += 32) acc = __fmaf_rn(y_s[i + lane], __half2float(wr[i + lane]), acc);
-            float sum = dot_lane_reduce_f16(acc);
-            if (lane == 0) {
-                for (int i = np; i < H; ++i) sum = __fadd_rn(sum, __fmul_rn(y_s[i], __half2float(wr[i])));
-                a.logits[row] = sum;
-                argmax_merge(bv, bi, sum, static_cast<unsigned int>(row));
+        // Every warp walks its rows in segments of kHeadSeg halves that arrive through a private ring of shared-memory
+        // buffers (asynchronous copies, three segments ahead); the table is not needed any more and gives up its space.
+        constexpr int kHeadSeg = 1024, kHeadStages = 4;
+        __half* ring = reinterpret_cast<__half*>(smem) + warp * kHeadStages * kHeadSeg;
+        const int nseg = (np + kHeadSeg - 1) / kHeadSeg;
+        const int first_row = cta * kMegaWarps + warp, row_stride = G * kMegaWarps;
+        const int nrows = first_row < a.vocab ? (a.vocab - first_row + row_stride - 1) / row_stride : 0;
+        const int total = nrows * nseg;
+        auto issue = [&](int q) {
+            if (q < total) {
+                const int row = first_row + (q / nseg) * row_stride, sg = q % nseg;
+                const __half* src = a.lm_head + static_cast<size_t>(row) * H + sg * kHeadSeg;
+                __half* dst = ring + (q % kHeadStages) * kHeadSeg;
+                const int nvec = min(kHeadSeg, np - sg * kHeadSeg) / 8;
+                for (int v = lane; v < nvec; v += 32) cp_async16(dst + v * 8, src + v * 8);
             }
+            cp_async_commit();
+        };
+        __syncthreads();  // every warp is done with the table and the scratch
+        for (int q = 0; q < kHeadStages - 1; ++q) issue(q);
+        float acc = 0.0f;
+        for (int q = 0; q < total; ++q) {
+            issue(q + kHeadStages - 1);
+            cp_async_wait<kHeadStages - 1>();
+            __syncwarp();
+            const int sg = q % nseg;
+            const __half* buf = ring + (q % kHeadStages) * kHeadSeg;
+            const float* xs = y_s + sg * kHeadSeg;
+            const int cnt = min(kHeadSeg, np - sg * kHeadSeg);
+#pragma unroll 8
+            for (int i = 0; i < cnt; i += 32) acc = __fmaf_rn(xs[i + lane], __half2float(buf[i + lane]), acc);
+            if (sg == nseg - 1) {
+                const int row = first_row + (q / nseg) * row_stride;
+                float sum = dot_lane_reduce_f16(acc);
+                if (lane == 0) {
+                    const __half* wr = a.lm_head + static_cast<size_t>(row) * H;
+                    for (int i = np; i < H; ++i) sum = __fadd_rn(sum, __fmul_rn(y_s[i], __half2float(wr[i])));
+                    a.logits[row] = sum;
+                    argmax_merge(bv, bi, sum, static_cast<unsigned int>(row));
+                }
+                acc = 0.0f;
+            }
+            __syncwarp();  // the buffer is refilled three segments later
         }
+        cp_async_wait<0>();
+        __syncthreads();
         float* s_bv = reinterpret_cast<float*>(attn_scratch);
         unsigned int* s_bi = reinterpret_cast<unsigned int*>(attn_scratch + 256);
         if (lane == 0) {
