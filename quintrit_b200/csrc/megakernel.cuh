@@ -236,6 +236,43 @@ __device__ __forceinline__ void stage_rows(__half* dst, const __half* src, int p
     }
 }
 
+// One staged block of the value accumulation for one coordinate (attention.rs:448-470): n positions in order, value of
+// position r at col[r * hd], factors ms[r] / vs[r]. The running sum is rounded to half precision after every operation
+// unless F32. Groups of eight positions are fetched into registers first; a group whose rescale factors are all 1 (every
+// group but the few where the running maximum moved) runs the bare multiply-add chain.
+template <bool F32>
+__device__ __noinline__ float value_chain(const __half* col, int hd, const float* ms, const float* vs, int n, float acc) {
+    auto rnd = [](float x) { return F32 ? x : __half2float(__float2half_rn(x)); };
+    int r = 0;
+    for (; r + 8 <= n; r += 8) {
+        float m[8], w[8], v[8];
+        bool moved = false;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            m[j] = ms[r + j];
+            w[j] = vs[r + j];
+            v[j] = __half2float(col[(r + j) * hd]);
+            moved |= m[j] != 1.0f;
+        }
+        if (!moved) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc = rnd(__fmaf_rn(v[j], w[j], acc));
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                if (m[j] != 1.0f) acc = rnd(__fmul_rn(acc, m[j]));
+                acc = rnd(__fmaf_rn(v[j], w[j], acc));
+            }
+        }
+    }
+    for (; r < n; ++r) {
+        const float m = ms[r];
+        if (m != 1.0f) acc = rnd(__fmul_rn(acc, m));
+        acc = rnd(__fmaf_rn(__half2float(col[r * hd]), vs[r], acc));
+    }
+    return acc;
+}
+
 // One (query head, KV chunk) of the attention of one layer: attention_kernel with the RoPE of q and of the new key, the
 // post-scaling and the KV append folded in (rope_kv_kernel), so that no barrier is needed between them. K and V rows
 // are staged through shared memory in blocks of 32 positions with asynchronous copies, double-buffered, so the strictly
@@ -400,7 +437,6 @@ __device__ __noinline__ void mega_attention_unit(const MegaArgs& a, const MegaLa
     // computes M and S meanwhile; every thread helps staging ----
     const bool chain = tid < hd;
     float acc32 = 0.0f;
-    __half acc16 = __float2half_rn(0.0f);
     for (int b = 0; b < nblk; ++b) {
         const __half* buf = s_stage + (b % kAttnStages) * kAttnBlockPos * 256;
         const int nb = b + kAttnStages - 1;
@@ -409,38 +445,11 @@ __device__ __noinline__ void mega_attention_unit(const MegaArgs& a, const MegaLa
         cp_async_wait<kAttnStages - 1>();
         __syncthreads();
         if (chain) {
-            // Groups of eight positions: the factors and the values of a group are fetched from shared memory into
-            // registers before its eight dependent steps run, so the chain itself never waits for a load.
-            const int pe = min(kAttnBlockPos, len - b * kAttnBlockPos);
-            const int pb = b * kAttnBlockPos;
-            for (int g0 = 0; g0 < pe; g0 += 8) {
-                float msr[8], vsr[8];
-                __half vr[8];
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    const int r = min(g0 + j, pe - 1), p = pb + r;
-                    msr[j] = s_ms[p];
-                    vsr[j] = s_score[p];
-                    vr[j] = (has_cur && p == pcur) ? s_vcur[tid] : buf[r * hd + tid];
-                }
-                if (a.f32_values) {
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        if (g0 + j < pe) {
-                            if (msr[j] != 1.0f) acc32 = __fmul_rn(acc32, msr[j]);
-                            acc32 = __fmaf_rn(__half2float(vr[j]), vsr[j], acc32);
-                        }
-                    }
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        if (g0 + j < pe) {
-                            if (msr[j] != 1.0f) acc16 = __float2half_rn(__fmul_rn(__half2float(acc16), msr[j]));
-                            acc16 = __float2half_rn(__fmaf_rn(__half2float(vr[j]), vsr[j], __half2float(acc16)));
-                        }
-                    }
-                }
-            }
+            const int pb = b * kAttnBlockPos, pe = min(kAttnBlockPos, len - pb);
+            // the row of the current position is not in the cache yet: each thread patches its own coordinate
+            if (has_cur && pcur >= pb && pcur < pb + pe) const_cast<__half*>(buf)[(pcur - pb) * hd + tid] = s_vcur[tid];
+            acc32 = a.f32_values ? value_chain<true>(buf + tid, hd, s_ms + pb, s_score + pb, pe, acc32)
+                                 : value_chain<false>(buf + tid, hd, s_ms + pb, s_score + pb, pe, acc32);
         } else if (b == 0 && tid == kMegaThreads - 1) {
             float S = 0.0f, M = -INFINITY;
             for (int w = 0; w < kMegaWarps; ++w) M = fmaxf(M, s_tm[w]);
@@ -452,7 +461,7 @@ __device__ __noinline__ void mega_attention_unit(const MegaArgs& a, const MegaLa
         __syncthreads();
     }
     cp_async_wait<0>();
-    if (chain) my_acc[tid] = a.f32_values ? acc32 : __half2float(acc16);
+    if (chain) my_acc[tid] = acc32;
     __syncthreads();  // the scratch is reused
 }
 
