@@ -761,7 +761,9 @@ int decoder_create_impl(const quintrit_b200_decoder_desc_t* desc, quintrit_b200_
     QTB_CUDA(cudaFuncSetAttribute(lm_head_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
     d->use_mega = false;
     const char* mode = std::getenv("QUINTRIT_B200_DECODE");  // "kernels" keeps the one-launch-per-step path (experiments)
-    if (desc->arch == QUINTRIT_B200_ARCH_LLAMA && d->q_heads <= kMegaMaxHeads && !(mode && std::strcmp(mode, "kernels") == 0)) {
+    // the single-kernel path stages KV rows with a piece permutation that needs a power-of-two head_dim of at least 64
+    const bool staged_ok = hd >= 64 && (hd & (hd - 1)) == 0;
+    if (desc->arch == QUINTRIT_B200_ARCH_LLAMA && staged_ok && d->q_heads <= kMegaMaxHeads && !(mode && std::strcmp(mode, "kernels") == 0)) {
         if ((rc = mega_setup(d, desc)) != QUINTRIT_OK) return rc;
         d->use_mega = true;
     }

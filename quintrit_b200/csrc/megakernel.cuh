@@ -222,36 +222,85 @@ __device__ __forceinline__ void cp_async_wait() {
     asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
-constexpr int kAttnBlockPos = 32;  // positions staged in shared memory at a time
-constexpr int kAttnStages = 4;     // blocks in flight (a ring of kAttnStages buffers)
+constexpr int kAttnBlockPos = 128;                          // positions staged in shared memory at a time
+constexpr int kAttnBlockBytes = kAttnBlockPos * 256 * 2;    // one staged block (head_dim <= 256 halves per row)
 
-// Copies rows [p0, p0 + 32) of a KV chunk (head_dim halves each, row stride kvd halves) into `dst` ([32][hd] halves),
-// 16 bytes per thread and copy; rows at or beyond `len` are skipped, the row of the current position (if `cur` is
-// inside the block) comes from shared memory afterwards.
-__device__ __forceinline__ void stage_rows(__half* dst, const __half* src, int p0, int len, int hd, int kvd) {
-    const int vec_per_row = hd / 8;  // 16-byte pieces per row
-    for (int v = threadIdx.x; v < kAttnBlockPos * vec_per_row; v += kMegaThreads) {
-        const int r = v / vec_per_row, c = v % vec_per_row;
-        if (p0 + r < len) cp_async16(dst + r * hd + c * 8, src + static_cast<size_t>(p0 + r) * kvd + c * 8);
+// Byte offset of 16-byte piece `c` of row `r` inside a staged block. The pieces of a row are permuted by the low three
+// bits of the row number, so that 8 threads reading the same piece of 8 consecutive rows, or one row's consecutive
+// pieces, always touch 8 different 16-byte bank groups (head_dim >= 64, i.e. at least 8 pieces per row).
+__device__ __forceinline__ int staged_offset(int r, int c, int row_bytes) { return r * row_bytes + ((c ^ (r & 7)) << 4); }
+
+// Copies rows [p0, p0 + 128) of a KV chunk (head_dim halves each, row stride kvd halves) into a staged block with
+// asynchronous 16-byte copies; rows at or beyond `len` are skipped (the row of the current position is patched in from
+// shared memory by the consumer).
+__device__ __forceinline__ void stage_rows(unsigned char* dst, const __half* src, int p0, int len, int hd, int kvd) {
+    const int shift = 31 - __clz(hd >> 3);  // head_dim is a power of two: pieces per row = 1 << shift
+    const int row_bytes = hd * 2;
+    for (int v = threadIdx.x; v < (kAttnBlockPos << shift); v += kMegaThreads) {
+        const int r = v >> shift, c = v & ((1 << shift) - 1);
+        if (p0 + r < len) cp_async16(dst + staged_offset(r, c, row_bytes), src + static_cast<size_t>(p0 + r) * kvd + c * 8);
     }
 }
 
-// One staged block of the value accumulation for one coordinate (attention.rs:448-470): n positions in order, value of
-// position r at col[r * hd], factors ms[r] / vs[r]. The running sum is rounded to half precision after every operation
-// unless F32. Groups of eight positions are fetched into registers first; a group whose rescale factors are all 1 (every
-// group but the few where the running maximum moved) runs the bare multiply-add chain.
+// Score of one staged key row against the query, by ONE thread: the 32 accumulator lanes of the reference's dot product
+// (ggml_vec_dot_f16: element e goes to lane e mod 32, lanes are summed by a fixed tree) live in 32 registers, so the
+// 32 chains run interleaved and the tree needs no shuffles.
 template <bool F32>
-__device__ __noinline__ float value_chain(const __half* col, int hd, const float* ms, const float* vs, int n, float acc) {
+__device__ __forceinline__ float key_score(const unsigned char* buf, int r, int hd, const float* s_q) {
+    float acc[32];
+#pragma unroll
+    for (int l = 0; l < 32; ++l) acc[l] = 0.0f;
+    const int row_bytes = hd * 2;
+    const unsigned char* row = buf + r * row_bytes;
+    const int sw = r & 7;
+    for (int i = 0; i < hd; i += 32) {
+#pragma unroll
+        for (int cc = 0; cc < 4; ++cc) {
+            const uint4 kk = *reinterpret_cast<const uint4*>(row + ((((i >> 3) + cc) ^ sw) << 4));
+            const float4 q0 = *reinterpret_cast<const float4*>(s_q + i + 8 * cc), q1 = *reinterpret_cast<const float4*>(s_q + i + 8 * cc + 4);
+            const __half2 h0 = *reinterpret_cast<const __half2*>(&kk.x), h1 = *reinterpret_cast<const __half2*>(&kk.y);
+            const __half2 h2 = *reinterpret_cast<const __half2*>(&kk.z), h3 = *reinterpret_cast<const __half2*>(&kk.w);
+            acc[8 * cc + 0] = __fmaf_rn(__low2float(h0), q0.x, acc[8 * cc + 0]);
+            acc[8 * cc + 1] = __fmaf_rn(__high2float(h0), q0.y, acc[8 * cc + 1]);
+            acc[8 * cc + 2] = __fmaf_rn(__low2float(h1), q0.z, acc[8 * cc + 2]);
+            acc[8 * cc + 3] = __fmaf_rn(__high2float(h1), q0.w, acc[8 * cc + 3]);
+            acc[8 * cc + 4] = __fmaf_rn(__low2float(h2), q1.x, acc[8 * cc + 4]);
+            acc[8 * cc + 5] = __fmaf_rn(__high2float(h2), q1.y, acc[8 * cc + 5]);
+            acc[8 * cc + 6] = __fmaf_rn(__low2float(h3), q1.z, acc[8 * cc + 6]);
+            acc[8 * cc + 7] = __fmaf_rn(__high2float(h3), q1.w, acc[8 * cc + 7]);
+        }
+    }
+    if (F32) {  // ggml_vec_dot_f16 summed as (a0+a1)+(a2+a3), then ((l0+l4)+(l2+l6))+((l1+l5)+(l3+l7)): dot_lane_reduce_f16_f32
+#pragma unroll
+        for (int l = 0; l < 8; ++l) acc[l] = __fadd_rn(__fadd_rn(acc[l], acc[l + 8]), __fadd_rn(acc[l + 16], acc[l + 24]));
+    } else {    // (a0+a2)+(a1+a3): dot_lane_reduce_f16
+#pragma unroll
+        for (int l = 0; l < 8; ++l) acc[l] = __fadd_rn(__fadd_rn(acc[l], acc[l + 16]), __fadd_rn(acc[l + 8], acc[l + 24]));
+    }
+#pragma unroll
+    for (int l = 0; l < 4; ++l) acc[l] = __fadd_rn(acc[l], acc[l + 4]);
+    if (F32) return __fadd_rn(__fadd_rn(acc[0], acc[2]), __fadd_rn(acc[1], acc[3]));
+    return __fadd_rn(__fadd_rn(acc[0], acc[1]), __fadd_rn(acc[2], acc[3]));
+}
+
+// One staged block of the value accumulation for one coordinate d (attention.rs:448-470): n positions in order, factors
+// ms[r] / vs[r]. The running sum is rounded to half precision after every operation unless F32. Groups of eight
+// positions are fetched into registers first; a group whose rescale factors are all 1 (every group but the few where
+// the running maximum moved) runs the bare multiply-add chain.
+template <bool F32>
+__device__ __noinline__ float value_chain(const unsigned char* buf, int row_bytes, int d, const float* ms, const float* vs, int n, float acc) {
     auto rnd = [](float x) { return F32 ? x : __half2float(__float2half_rn(x)); };
+    const int piece = d >> 3, within = (d & 7) * 2;
     int r = 0;
-    for (; r + 8 <= n; r += 8) {
+    for (; r + 8 <= n; r += 8) {  // r is a multiple of 8: row r + j has its pieces permuted by j
         float m[8], w[8], v[8];
         bool moved = false;
+        const unsigned char* rows = buf + r * row_bytes + within;
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
             m[j] = ms[r + j];
             w[j] = vs[r + j];
-            v[j] = __half2float(col[(r + j) * hd]);
+            v[j] = __half2float(*reinterpret_cast<const __half*>(rows + j * row_bytes + ((piece ^ j) << 4)));
             moved |= m[j] != 1.0f;
         }
         if (!moved) {
@@ -268,26 +317,30 @@ __device__ __noinline__ float value_chain(const __half* col, int hd, const float
     for (; r < n; ++r) {
         const float m = ms[r];
         if (m != 1.0f) acc = rnd(__fmul_rn(acc, m));
-        acc = rnd(__fmaf_rn(__half2float(col[r * hd]), vs[r], acc));
+        acc = rnd(__fmaf_rn(__half2float(*reinterpret_cast<const __half*>(buf + staged_offset(r, piece, row_bytes) + within)), vs[r], acc));
     }
     return acc;
 }
 
 // One (query head, KV chunk) of the attention of one layer: attention_kernel with the RoPE of q and of the new key, the
-// post-scaling and the KV append folded in (rope_kv_kernel), so that no barrier is needed between them. K and V rows
-// are staged through shared memory in blocks of 32 positions with asynchronous copies, double-buffered, so the strictly
-// sequential value accumulation never waits for global memory.
-__device__ __noinline__ void mega_attention_unit(const MegaArgs& a, const MegaLayer& ly, int h, int c, float s_in, unsigned char* scratch) {
-    float* s_score = reinterpret_cast<float*>(scratch);            // kAttnMaxChunk floats
+// post-scaling and the KV append folded in (rope_kv_kernel), so that no barrier is needed between them. K and then V
+// rows pass through two 64 KiB shared-memory blocks of 128 positions filled by asynchronous copies (block j + 2 is
+// requested when block j has been consumed), so neither the scores nor the strictly sequential value accumulation wait
+// for global memory. `smem` is the CTA's dynamic shared memory from its start: the first block overlays the GEMV table,
+// whose zero rows are restored before returning.
+__device__ __noinline__ void mega_attention_unit(const MegaArgs& a, const MegaLayer& ly, int h, int c, float s_in, unsigned char* smem) {
+    unsigned char* s_blk = smem;                                    // 2 x kAttnBlockBytes
+    float* s_score = reinterpret_cast<float*>(smem + 2 * kAttnBlockBytes);  // kAttnMaxChunk floats
     float* s_ms = s_score + kAttnMaxChunk;                         // kAttnMaxChunk floats
     float* s_q = s_ms + kAttnMaxChunk;                             // 256 floats
     float* s_tm = s_q + 256;                                       // kMegaThreads floats
     __half* s_kcur = reinterpret_cast<__half*>(s_tm + kMegaThreads);  // 256 halves
     __half* s_vcur = s_kcur + 256;
-    __half* s_stage = s_vcur + 256;                                // kAttnStages x [32][256] halves
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int hd = a.head_dim, gqa = a.q_heads / a.kv_heads, kvh = h / gqa;
-    const int qd = a.q_heads * hd, kvd = a.kv_heads * hd;
+    const int qd = a.q_heads * hd, kvd = a.kv_heads * hd, row_bytes = hd * 2;
+    const bool f32v = a.f32_values != 0;
+    const float attn_scale = a.attn_scale;
     const int pos = static_cast<int>(a.pos[0]), seq_len = pos + 1;
     int n_kv = (seq_len + 255) / 256 * 256;
     if (n_kv < 256) n_kv = 256;
@@ -316,11 +369,17 @@ __device__ __noinline__ void mega_attention_unit(const MegaArgs& a, const MegaLa
     const int pcur = pos - start;            // index of the current position inside the chunk (valid if has_cur)
     const int len_old = has_cur ? pcur : len;  // rows that come from the cache (the current position is the last one)
     const int nblk = (len + kAttnBlockPos - 1) / kAttnBlockPos;
-    // the first K blocks are on their way while q and the new key are prepared
-    for (int b = 0; b < kAttnStages - 1; ++b) {
-        if (b < nblk) stage_rows(s_stage + b * kAttnBlockPos * 256, kbase, b * kAttnBlockPos, len_old, hd, kvd);
+    // Staging jobs 0..nblk-1 are the K blocks, nblk..2*nblk-1 the V blocks; job j uses block j & 1 and one copy group.
+    auto issue = [&](int j) {
+        if (j < nblk)
+            stage_rows(s_blk + (j & 1) * kAttnBlockBytes, kbase, j * kAttnBlockPos, len_old, hd, kvd);
+        else if (j < 2 * nblk)
+            stage_rows(s_blk + (j & 1) * kAttnBlockBytes, vbase, (j - nblk) * kAttnBlockPos, len_old, hd, kvd);
         cp_async_commit();
-    }
+    };
+    __syncthreads();  // every thread is done with the table the first block overlays
+    issue(0);
+    issue(1);
 
     const bool live = s_in > 0.0f;
     const float pq = live ? __fdiv_rn(ly.ws[0], s_in) : 0.0f, pk = live ? __fdiv_rn(ly.ws[1], s_in) : 0.0f, pv = live ? __fdiv_rn(ly.ws[2], s_in) : 0.0f;
@@ -340,8 +399,8 @@ __device__ __noinline__ void mega_attention_unit(const MegaArgs& a, const MegaLa
                 x0 = r0;
                 x1 = r1;
             }
-            s_q[2 * p] = a.f32_values ? x0 : __half2float(__float2half_rn(x0));
-            s_q[2 * p + 1] = a.f32_values ? x1 : __half2float(__float2half_rn(x1));
+            s_q[2 * p] = f32v ? x0 : __half2float(__float2half_rn(x0));
+            s_q[2 * p + 1] = f32v ? x1 : __half2float(__float2half_rn(x1));
         }
         if (has_cur) {
             float x0 = live ? __fmul_rn(static_cast<float>(a.acc_qkv[qd + kvh * hd + 2 * p]), pk) : 0.0f;
@@ -366,40 +425,24 @@ __device__ __noinline__ void mega_attention_unit(const MegaArgs& a, const MegaLa
             const_cast<__half*>(vbase)[static_cast<size_t>(pcur) * kvd + d] = s_vcur[d];
         }
     }
-    // ---- scores: block by block; one warp per position, lane = accumulator lane of the reference's dot product ----
+    // The row of the current position is not in the cache when its block is staged: it is written into the block.
+    auto patch_current = [&](unsigned char* blk, int pb, const __half* cur) {
+        if (has_cur && pcur >= pb && pcur < pb + kAttnBlockPos && tid < hd)
+            *reinterpret_cast<__half*>(blk + staged_offset(pcur - pb, tid >> 3, row_bytes) + (tid & 7) * 2) = cur[tid];
+    };
+    // ---- scores: one thread per staged row ----
     for (int b = 0; b < nblk; ++b) {
-        __half* buf = s_stage + (b % kAttnStages) * kAttnBlockPos * 256;
-        const int nb = b + kAttnStages - 1;
-        if (nb < nblk) stage_rows(s_stage + (nb % kAttnStages) * kAttnBlockPos * 256, kbase, nb * kAttnBlockPos, len_old, hd, kvd);
-        cp_async_commit();
-        cp_async_wait<kAttnStages - 1>();
+        unsigned char* blk = s_blk + (b & 1) * kAttnBlockBytes;
+        cp_async_wait<1>();
+        patch_current(blk, b * kAttnBlockPos, s_kcur);
         __syncthreads();
-        {
-            // a warp takes rows warp and warp + 16 of the block; both dot products run interleaved
-            static_assert(kAttnBlockPos == 2 * kMegaWarps, "two positions per warp and block");
-            const int pA = b * kAttnBlockPos + warp, pB = pA + kMegaWarps;
-            const __half* krA = (has_cur && pA == pcur) ? s_kcur : buf + warp * hd;
-            const __half* krB = (has_cur && pB == pcur) ? s_kcur : buf + (warp + kMegaWarps) * hd;
-            float accA = 0.0f, accB = 0.0f;
-#pragma unroll 4
-            for (int i = 0; i + 32 <= hd; i += 32) {
-                const float qv = s_q[i + lane];
-                accA = __fmaf_rn(__half2float(krA[i + lane]), qv, accA);
-                accB = __fmaf_rn(__half2float(krB[i + lane]), qv, accB);
-            }
-            const float scA = a.f32_values ? dot_lane_reduce_f16_f32(accA) : dot_lane_reduce_f16(accA);
-            const float scB = a.f32_values ? dot_lane_reduce_f16_f32(accB) : dot_lane_reduce_f16(accB);
-            if (lane == 0) {
-                if (pA < len) s_score[pA] = __fmul_rn(scA, a.attn_scale);
-                if (pB < len) s_score[pB] = __fmul_rn(scB, a.attn_scale);
-            }
+        const int p = b * kAttnBlockPos + tid;
+        if (tid < kAttnBlockPos && p < len) {
+            const float sc = f32v ? key_score<true>(blk, tid, hd, s_q) : key_score<false>(blk, tid, hd, s_q);
+            s_score[p] = __fmul_rn(sc, attn_scale);
         }
-        __syncthreads();  // the buffer is refilled two blocks later
-    }
-    // the first V blocks are on their way while the softmax factors are computed
-    for (int b = 0; b < kAttnStages - 1; ++b) {
-        if (b < nblk) stage_rows(s_stage + b * kAttnBlockPos * 256, vbase, b * kAttnBlockPos, len_old, hd, kvd);
-        cp_async_commit();
+        __syncthreads();  // the block is refilled now
+        issue(b + 2);
     }
     {
         // running maximum in position order: maximum of the thread's own positions, an exclusive scan over the threads
@@ -431,42 +474,46 @@ __device__ __noinline__ void mega_attention_unit(const MegaArgs& a, const MegaLa
             s_ms[p] = ms;
             s_score[p] = vs;
         }
-        __syncthreads();
     }
-    // ---- values: warps 0..hd/32-1 run the chain, one thread per coordinate, strictly in position order; the last warp
-    // computes M and S meanwhile; every thread helps staging ----
-    const bool chain = tid < hd;
-    float acc32 = 0.0f;
+    // ---- values: threads 0..hd-1 run the chain, one coordinate each, strictly in position order; the last thread
+    // accumulates S over the same positions meanwhile ----
+    float acc = 0.0f, S = 0.0f;
     for (int b = 0; b < nblk; ++b) {
-        const __half* buf = s_stage + (b % kAttnStages) * kAttnBlockPos * 256;
-        const int nb = b + kAttnStages - 1;
-        if (nb < nblk) stage_rows(s_stage + (nb % kAttnStages) * kAttnBlockPos * 256, vbase, nb * kAttnBlockPos, len_old, hd, kvd);
-        cp_async_commit();
-        cp_async_wait<kAttnStages - 1>();
-        __syncthreads();
-        if (chain) {
-            const int pb = b * kAttnBlockPos, pe = min(kAttnBlockPos, len - pb);
-            // the row of the current position is not in the cache yet: each thread patches its own coordinate
-            if (has_cur && pcur >= pb && pcur < pb + pe) const_cast<__half*>(buf)[(pcur - pb) * hd + tid] = s_vcur[tid];
-            acc32 = a.f32_values ? value_chain<true>(buf + tid, hd, s_ms + pb, s_score + pb, pe, acc32)
-                                 : value_chain<false>(buf + tid, hd, s_ms + pb, s_score + pb, pe, acc32);
-        } else if (b == 0 && tid == kMegaThreads - 1) {
-            float S = 0.0f, M = -INFINITY;
-            for (int w = 0; w < kMegaWarps; ++w) M = fmaxf(M, s_tm[w]);
+        unsigned char* blk = s_blk + ((nblk + b) & 1) * kAttnBlockBytes;
+        cp_async_wait<1>();
+        const int pb = b * kAttnBlockPos, pe = min(kAttnBlockPos, len - pb);
+        patch_current(blk, pb, s_vcur);  // a thread patches the coordinate it reads itself
+        __syncthreads();                 // the block has landed for every thread; (b == 0) the factors are written
+        if (tid < hd) {
+            acc = f32v ? value_chain<true>(blk, row_bytes, tid, s_ms + pb, s_score + pb, pe, acc)
+                       : value_chain<false>(blk, row_bytes, tid, s_ms + pb, s_score + pb, pe, acc);
+        } else if (tid == kMegaThreads - 1) {
 #pragma unroll 8
-            for (int p = 0; p < len; ++p) S = __fmaf_rn(S, s_ms[p], s_score[p]);  // attention.rs:466
-            my_ms[0] = M;
-            my_ms[1] = S;
+            for (int p = pb; p < pb + pe; ++p) S = __fmaf_rn(S, s_ms[p], s_score[p]);  // attention.rs:466
         }
         __syncthreads();
+        issue(nblk + b + 2);
     }
     cp_async_wait<0>();
-    if (chain) my_acc[tid] = acc32;
+    if (tid < hd) my_acc[tid] = acc;
+    if (tid == kMegaThreads - 1) {
+        float M = -INFINITY;
+        for (int w = 0; w < kMegaWarps; ++w) M = fmaxf(M, s_tm[w]);
+        my_ms[0] = M;
+        my_ms[1] = S;
+    }
+    // the zero rows of the table (the 13 byte values that are no velurex code) were overwritten by the first block
+    for (int i = tid; i < 13 * 64; i += kMegaThreads) {
+        const int k = i >> 6;
+        reinterpret_cast<int*>(smem)[(k < 9 ? 28 * k + 27 : 243 + k) * 64 + (i & 63)] = 0;
+    }
     __syncthreads();  // the scratch is reused
 }
 
-// Shared-memory plan of the megakernel (bytes from the dynamic base): table | attention scratch | y (floats) | a8 | small
-constexpr int kMegaAttnScratch = (2 * kAttnMaxChunk + 256 + kMegaThreads) * 4 + 2 * 256 * 2 + kAttnStages * kAttnBlockPos * 256 * 2;
+// Shared-memory plan of the megakernel (bytes from the dynamic base): table | attention scratch | y (floats) | a8 | small.
+// The attention unit uses the table and its scratch together: two staged blocks, then its small arrays.
+constexpr int kMegaAttnScratch = 2 * kAttnBlockBytes - kTableBytes + (2 * kAttnMaxChunk + 256 + kMegaThreads) * 4 + 2 * 256 * 2;
+static_assert(kTableBytes <= kAttnBlockBytes, "the first staged block covers the table");
 __host__ __device__ constexpr size_t mega_smem_bytes(int maxvec) {
     return static_cast<size_t>(kTableBytes) + kMegaAttnScratch + static_cast<size_t>(maxvec) * 4 + (static_cast<size_t>(maxvec) + 15) / 16 * 16 + 4096;
 }
@@ -531,7 +578,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(MegaArgs 
         MEGA_BARRIER();
         MEGA_TRACE();  // 3
         // ---- phase C: attention units; spare CTAs clear buffers that are idle now ----
-        for (int u = cta; u < a.q_heads * 4; u += G) mega_attention_unit(a, ly, u >> 2, u & 3, s_h, attn_scratch);
+        for (int u = cta; u < a.q_heads * 4; u += G) mega_attention_unit(a, ly, u >> 2, u & 3, s_h, smem);
         if (cta == G - 1) {
             for (int i = tid; i < H; i += kMegaThreads) a.acc_down[i] = 0;  // read by every CTA in phase A, rewritten in F2
             if (tid == 0) a.amax_bits[(l + 1) & 1] = 0u;
