@@ -30,6 +30,10 @@ from quintrit_b200 import synth  # noqa: E402
 
 CONFIG_ID = 0
 BYTES_PER_WEIGHT = 0.2  # 1.60 bits per weight: the algorithmic bytes of a velurex GEMV
+# DRAM bytes per weight that ncu counted for gemv_lut_kernel (dram__bytes_read.sum + dram__bytes_write.sum of the 12-layer
+# capture summarised in profiles/gemv_lut_kernel_falcon3_12layer_sweep.md, divided by its 2 850 029 568 weights); traffic
+# grows in proportion to the weights streamed, so a launch's traffic is this figure times its weights.
+NCU_TRAFFIC_BYTES_PER_WEIGHT = (590_314_496 + 4_031_488) / 2_850_029_568
 
 
 def sweep_shapes(layers: int):
@@ -374,7 +378,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         "tokens_per_s_gemv_only": round(1e3 / ms_per_step, 1),
         "roofline_nominal_8tbs_frac": round(weights_total * BYTES_PER_WEIGHT / (ms_per_step * 1e-3) / (world * 8e12), 4),
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 4),
-                     "traffic": None, "peak_kind": peak_kind, "kernel": "gemv_lut_kernel", "launch_ms": round(kernel_ms, 4)},
+                     "traffic": int(weights_local * NCU_TRAFFIC_BYTES_PER_WEIGHT), "traffic_source": "ncu capture of the 12-layer case, scaled by weights", "peak_kind": peak_kind, "kernel": "gemv_lut_kernel", "launch_ms": round(kernel_ms, 4)},
         "e2e": {"value": round(e2e_value, 1), "unit": "Gweights/s", "h2d_bytes_per_step": int(plan.act_total), "d2h_bytes_per_step": int(plan.out_total * 4),
                 "ms_per_step": round(e2e_ms / args.steps, 4)},
         "sustained": {"value": round(weights_total / (sustained_ms * 1e-3) / 1e9, 1), "unit": "Gweights/s", "ms_per_step": round(sustained_ms, 4),
