@@ -841,7 +841,7 @@ int mega_setup(quintrit_b200_decoder* d, const quintrit_b200_decoder_desc_t* des
     a.v_inter = d->v_inter, a.amax_bits = d->amax_bits, a.part_acc = d->part_acc, a.part_ms = d->part_ms, a.logits = d->logits;
     a.best_val = d->best_val, a.best_idx = d->best_idx, a.token = d->d_token, a.pos = d->d_pos, a.history = d->d_history;
     a.bar = d->bar, a.status = d->d_counters + 2, a.trace = nullptr;
-    d->mega_smem = mega_smem_bytes(std::max(H, qd));
+    d->mega_smem = mega_smem_bytes(std::max(H, qd), H, L);
     // the table-base constant: measured once per device like the GEMV kernel's
     unsigned int base = 0xFFFFFFFFu;
     smem_base_kernel<<<1, 32, 1024>>>(reinterpret_cast<unsigned int*>(d->bar));

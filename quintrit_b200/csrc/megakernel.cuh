@@ -190,7 +190,7 @@ __device__ __noinline__ void mega_gemv(const GemvItem* __restrict__ items, int f
 
 // RMSNorm + int8 quantisation of n values held in y_s (overwritten with the normalised values); every thread returns the
 // activation scale. Same arithmetic as norm_quant_kernel.
-__device__ __forceinline__ float mega_norm_quant(float* y_s, const float* __restrict__ norm_w, int n, float eps, int8_t* a8, double* sh_d,
+__device__ __forceinline__ float mega_norm_quant(float* y_s, const float* norm_w, int n, float eps, int8_t* a8, double* sh_d,
                                                  float* sh_f) {
     const int tid = threadIdx.x;
     double sum = 0.0;
@@ -220,6 +220,37 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() {
     asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+__device__ __forceinline__ void cp_async4(void* smem_dst, const void* gsrc) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst))), "l"(gsrc) : "memory");
+}
+// Requests the n norm weights that the next norm needs (one copy group); they land while other phases run.
+__device__ __forceinline__ void request_norm_weights(float* w_s, const float* __restrict__ w, int n) {
+    for (int i = threadIdx.x; i < n; i += kMegaThreads) cp_async4(w_s + i, w + i);
+    cp_async_commit();
+}
+__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
+
+// y_s[i] = x[i] + acc[i] * post (the rescaled projection added to the residual stream), all loads of a thread issued
+// before the first use. acc was accumulated with atomics by other SMs: it is read from L2 (ld.cg).
+__device__ __forceinline__ void residual_add(float* y_s, const float* x, const int32_t* acc, float post, bool live, int n) {
+    constexpr int kPer = 8;
+    for (int i0 = threadIdx.x; i0 < n; i0 += kPer * kMegaThreads) {
+        int av[kPer];
+        float xv[kPer];
+#pragma unroll
+        for (int k = 0; k < kPer; ++k) {
+            const int i = i0 + k * kMegaThreads;
+            av[k] = i < n ? __ldcg(acc + i) : 0;
+            xv[k] = i < n ? __ldcg(x + i) : 0.0f;
+        }
+#pragma unroll
+        for (int k = 0; k < kPer; ++k) {
+            const int i = i0 + k * kMegaThreads;
+            if (i < n) y_s[i] = __fadd_rn(xv[k], live ? __fmul_rn(static_cast<float>(av[k]), post) : 0.0f);
+        }
+    }
 }
 
 constexpr int kAttnBlockPos = 128;                          // positions staged in shared memory at a time
@@ -514,8 +545,10 @@ __device__ __noinline__ void mega_attention_unit(const MegaArgs& a, const MegaLa
 // The attention unit uses the table and its scratch together: two staged blocks, then its small arrays.
 constexpr int kMegaAttnScratch = 2 * kAttnBlockBytes - kTableBytes + (2 * kAttnMaxChunk + 256 + kMegaThreads) * 4 + 2 * 256 * 2;
 static_assert(kTableBytes <= kAttnBlockBytes, "the first staged block covers the table");
-__host__ __device__ constexpr size_t mega_smem_bytes(int maxvec) {
-    return static_cast<size_t>(kTableBytes) + kMegaAttnScratch + static_cast<size_t>(maxvec) * 4 + (static_cast<size_t>(maxvec) + 15) / 16 * 16 + 4096;
+// After the small arrays: the norm weights of the next norm (hidden floats) and a copy of every layer's descriptor.
+__host__ __device__ constexpr size_t mega_smem_bytes(int maxvec, int hidden, int layers) {
+    return static_cast<size_t>(kTableBytes) + kMegaAttnScratch + static_cast<size_t>(maxvec) * 4 + (static_cast<size_t>(maxvec) + 15) / 16 * 16 + 4096 +
+           (static_cast<size_t>(hidden) * 4 + 15) / 16 * 16 + static_cast<size_t>(layers) * sizeof(MegaLayer);
 }
 
 template <uint32_t BASE>
@@ -531,6 +564,8 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(MegaArgs 
     float* sh_f = reinterpret_cast<float*>(small + 256);   // 32 floats
     float* s_pair = reinterpret_cast<float*>(small + 384); // chunk-combine factors: q_heads * (4 * 2 + 1) floats (q_heads <= kMegaMaxHeads)
     int* s_flag = reinterpret_cast<int*>(small + 4000);
+    float* w_s = reinterpret_cast<float*>(small + 4096);   // weights of the next norm
+    MegaLayer* s_layers = reinterpret_cast<MegaLayer*>(small + 4096 + (static_cast<size_t>(a.hidden) * 4 + 15) / 16 * 16);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, cta = blockIdx.x, G = gridDim.x;
     if (static_cast<uint32_t>(__cvta_generic_to_shared(smem)) != BASE) {
         if (tid == 0) atomicMax(a.status, 1u);
@@ -541,6 +576,10 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(MegaArgs 
         tab[(k < 9 ? 28 * k + 27 : 243 + k) * 64 + (i & 63)] = 0;
     }
     const int H = a.hidden, I = a.inter, hd = a.head_dim, qd = a.q_heads * hd, kvd = a.kv_heads * hd;
+    request_norm_weights(w_s, a.layers != nullptr && a.n_layers > 0 ? a.layers[0].attn_norm : a.out_norm, H);
+    for (int i = tid; i < a.n_layers * static_cast<int>(sizeof(MegaLayer) / 4); i += kMegaThreads)
+        reinterpret_cast<uint32_t*>(s_layers)[i] = reinterpret_cast<const uint32_t*>(a.layers)[i];
+    __syncthreads();
     unsigned int bar_target = 0;
 #define MEGA_BARRIER()                                                   \
     do {                                                                 \
@@ -556,22 +595,23 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(MegaArgs 
     MEGA_TRACE();
     float s_down_prev = 0.0f;  // activation scale of the previous layer's down projection
     for (int l = 0; l < a.n_layers; ++l) {
-        const MegaLayer ly = a.layers[l];
+        const MegaLayer& ly = s_layers[l];
         // ---- phase A: residual (or embedding), norm, quantise, q|k|v ----
+        if (tid < 2 && cta + tid * G < ly.count[0]) prefetch_l2(a.items + ly.first[0] + cta + tid * G);
         if (l == 0) {
             const size_t base = static_cast<size_t>(a.token[0]) * H;
             for (int i = tid; i < H; i += kMegaThreads) y_s[i] = __half2float(a.embed[base + i]);
         } else {
-            const float post = s_down_prev > 0.0f ? __fdiv_rn(a.layers[l - 1].ws[6], s_down_prev) : 0.0f;
-            for (int i = tid; i < H; i += kMegaThreads) {
-                const float d = s_down_prev > 0.0f ? __fmul_rn(static_cast<float>(a.acc_down[i]), post) : 0.0f;
-                y_s[i] = __fadd_rn(a.xb[i], d);
-            }
+            const float post = s_down_prev > 0.0f ? __fdiv_rn(s_layers[l - 1].ws[6], s_down_prev) : 0.0f;
+            residual_add(y_s, a.xb, a.acc_down, post, s_down_prev > 0.0f, H);
         }
+        cp_async_wait<0>();  // the norm weights requested one phase ago
         __syncthreads();
         if (cta == 0)
             for (int i = tid; i < H; i += kMegaThreads) a.xa[i] = y_s[i];
-        const float s_h = mega_norm_quant(y_s, ly.attn_norm, H, a.eps, a8, sh_d, sh_f);
+        const float s_h = mega_norm_quant(y_s, w_s, H, a.eps, a8, sh_d, sh_f);
+        request_norm_weights(w_s, ly.ffn_norm, H);
+        if (tid < 2 && cta + tid * G < ly.count[1]) prefetch_l2(a.items + ly.first[1] + cta + tid * G);
         MEGA_TRACE();  // 1: norm done
         mega_gemv<BASE>(a.items, ly.first[0], ly.count[0], tab, a8, nullptr, 0.0f, a.acc_qkv);
         MEGA_TRACE();  // 2: q|k|v streamed (this CTA)
@@ -651,17 +691,18 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(MegaArgs 
         // ---- phase E: residual, norm, quantise, gate|up ----
         {
             const float post = s_q > 0.0f ? __fdiv_rn(ly.ws[3], s_q) : 0.0f;
-            for (int i = tid; i < H; i += kMegaThreads) {
-                const float d = s_q > 0.0f ? __fmul_rn(static_cast<float>(a.acc_o[i]), post) : 0.0f;
-                y_s[i] = __fadd_rn(a.xa[i], d);
-            }
+            residual_add(y_s, a.xa, a.acc_o, post, s_q > 0.0f, H);
+            cp_async_wait<0>();  // the norm weights requested in phase A
             __syncthreads();
             if (cta == 0)
                 for (int i = tid; i < H; i += kMegaThreads) a.xb[i] = y_s[i];
             if (cta == G - 1)
                 for (int i = tid; i < qd + 2 * kvd; i += kMegaThreads) a.acc_qkv[i] = 0;  // consumed in phase C
         }
-        const float s_f = mega_norm_quant(y_s, ly.ffn_norm, H, a.eps, a8, sh_d, sh_f);
+        if (tid < 2 && cta + tid * G < ly.count[2]) prefetch_l2(a.items + ly.first[2] + cta + tid * G);
+        const float s_f = mega_norm_quant(y_s, w_s, H, a.eps, a8, sh_d, sh_f);
+        request_norm_weights(w_s, l + 1 < a.n_layers ? s_layers[l + 1].attn_norm : a.out_norm, H);
+        if (tid < 2 && cta + tid * G < ly.count[3]) prefetch_l2(a.items + ly.first[3] + cta + tid * G);
         MEGA_TRACE();  // 8: norm done
         mega_gemv<BASE>(a.items, ly.first[2], ly.count[2], tab, a8, nullptr, 0.0f, a.acc_gu);
         MEGA_TRACE();  // 9: gate|up streamed (this CTA)
@@ -698,13 +739,11 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(MegaArgs 
     }
     // ---- final norm (model.rs:326-331), output head, greedy choice ----
     {
-        const float post = s_down_prev > 0.0f ? __fdiv_rn(a.layers[a.n_layers - 1].ws[6], s_down_prev) : 0.0f;
-        for (int i = tid; i < H; i += kMegaThreads) {
-            const float d = s_down_prev > 0.0f ? __fmul_rn(static_cast<float>(a.acc_down[i]), post) : 0.0f;
-            y_s[i] = __fadd_rn(a.xb[i], d);
-        }
+        const float post = s_down_prev > 0.0f ? __fdiv_rn(s_layers[a.n_layers - 1].ws[6], s_down_prev) : 0.0f;
+        residual_add(y_s, a.xb, a.acc_down, post, s_down_prev > 0.0f, H);
+        cp_async_wait<0>();
         __syncthreads();
-        mega_norm_quant(y_s, a.out_norm, H, a.eps, nullptr, sh_d, sh_f);
+        mega_norm_quant(y_s, w_s, H, a.eps, nullptr, sh_d, sh_f);
         for (int i = tid; i < H; i += kMegaThreads) y_s[i] = __half2float(__float2half_rn(y_s[i]));  // model.rs:347-349
         __syncthreads();
         float bv = -INFINITY;
