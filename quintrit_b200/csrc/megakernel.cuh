@@ -22,7 +22,7 @@ namespace qtb {
 
 constexpr int kMegaThreads = 512;
 constexpr int kMegaWarps = kMegaThreads / 32;
-constexpr int kMegaMaxHeads = 96;
+constexpr int kMegaMaxHeads = 64;
 constexpr unsigned int kBarrierSpinLimit = 1u << 21;  // polls of ~50 ns: about 0.1 s, then the kernel gives up
 
 struct MegaLayer {
@@ -562,7 +562,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(MegaArgs 
     unsigned char* small = reinterpret_cast<unsigned char*>(a8) + (maxvec + 15) / 16 * 16;
     double* sh_d = reinterpret_cast<double*>(small);       // 32 doubles
     float* sh_f = reinterpret_cast<float*>(small + 256);   // 32 floats
-    float* s_pair = reinterpret_cast<float*>(small + 384); // chunk-combine factors: q_heads * (4 * 2 + 1) floats (q_heads <= kMegaMaxHeads)
+    float* s_pair = reinterpret_cast<float*>(small + 384); // chunk-combine factors: q_heads * (4 * 2 + 4) floats (q_heads <= kMegaMaxHeads)
     int* s_flag = reinterpret_cast<int*>(small + 4000);
     float* w_s = reinterpret_cast<float*>(small + 4096);   // weights of the next norm
     MegaLayer* s_layers = reinterpret_cast<MegaLayer*>(small + 4096 + (static_cast<size_t>(a.hidden) * 4 + 15) / 16 * 16);
@@ -632,49 +632,62 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(MegaArgs 
             int n_kv = (seq_len + 255) / 256 * 256;
             if (n_kv < 256) n_kv = 256;
             if (n_kv > a.ctx) n_kv = a.ctx;
-            // per head: the factor of every chunk and the final 1/S, in the order of attention.rs:510-541
-            if (tid < a.q_heads) {
-                const float* pm = a.part_ms + static_cast<size_t>(tid) * 8;
-                float* pr = s_pair + tid * 8;  // [c][0] = scale_old, [c][1] = scale_new (negative scale_old marks a skipped chunk)
-                if (n_kv < 512) {
-                    const float S = pm[1];
-                    pr[0] = S == 0.0f ? 0.0f : __fdiv_rn(1.0f, S);
-                } else {
-                    float m_final = -INFINITY, s_final = 0.0f;
-                    for (int c = 0; c < 4; ++c) {
-                        const float m_chunk = pm[2 * c], s_chunk = pm[2 * c + 1];
-                        if (s_chunk == 0.0f) {
-                            pr[2 * c] = -1.0f;
-                            continue;
-                        }
-                        const float m_new = fmaxf(m_final, m_chunk);
-                        const float so = device_expf(__fsub_rn(m_final, m_new)), sn = device_expf(__fsub_rn(m_chunk, m_new));
-                        pr[2 * c] = so;
-                        pr[2 * c + 1] = sn;
-                        s_final = __fmaf_rn(s_final, so, __fmul_rn(s_chunk, sn));
-                        m_final = m_new;
-                    }
-                    s_pair[a.q_heads * 8 + tid] = s_final;
+            // per head: the factors of every chunk in the order of attention.rs:510-541. The running maximum before chunk c is
+            // the maximum of the earlier non-empty chunks, so the eight exponentials of a head are independent: one thread each.
+            if (n_kv < 512) {
+                if (tid < a.q_heads) {
+                    const float S = __ldcg(a.part_ms + static_cast<size_t>(tid) * 8 + 1);
+                    s_pair[tid * 8] = S == 0.0f ? 0.0f : __fdiv_rn(1.0f, S);
                 }
+            } else if (tid < a.q_heads * 8) {
+                const int h = tid >> 3, c = (tid >> 1) & 3, which = tid & 1;
+                float pm[8];
+#pragma unroll
+                for (int k = 0; k < 8; ++k) pm[k] = __ldcg(a.part_ms + static_cast<size_t>(h) * 8 + k);
+                float m_before = -INFINITY;
+#pragma unroll
+                for (int k = 0; k < 4; ++k)
+                    if (k < c && pm[2 * k + 1] != 0.0f) m_before = fmaxf(m_before, pm[2 * k]);
+                const float m_chunk = pm[2 * c], s_chunk = pm[2 * c + 1];
+                const float m_new = fmaxf(m_before, m_chunk);
+                float f = device_expf(__fsub_rn(which == 0 ? m_before : m_chunk, m_new));
+                if (s_chunk == 0.0f) f = which == 0 ? -1.0f : 0.0f;  // a negative scale_old marks a skipped chunk
+                s_pair[h * 8 + 2 * c + which] = f;                    // [c][0] = scale_old, [c][1] = scale_new
+                if (which == 0) s_pair[a.q_heads * 8 + h * 4 + c] = s_chunk;
             }
             __syncthreads();
-            for (int i = tid; i < qd; i += kMegaThreads) {
-                const int h = i / hd, d = i % hd;
-                const float* pa = a.part_acc + static_cast<size_t>(h) * 4 * hd + d;
-                const float* pr = s_pair + h * 8;
-                float out;
-                if (n_kv < 512) {
-                    out = __fmul_rn(pa[0], pr[0]);
-                } else {
-                    float acc = 0.0f;
-                    for (int c = 0; c < 4; ++c) {
-                        if (pr[2 * c] < 0.0f) continue;
-                        acc = __fmaf_rn(acc, pr[2 * c], __fmul_rn(pa[c * hd], pr[2 * c + 1]));
-                    }
-                    const float s_final = s_pair[a.q_heads * 8 + h];
-                    out = s_final != 0.0f ? __fmul_rn(acc, __fdiv_rn(1.0f, s_final)) : acc;
+            // every chunk value of a thread's coordinates is requested before the first is used
+            for (int i0 = tid; i0 < qd; i0 += 4 * kMegaThreads) {
+                float pv[4][4];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const int i = i0 + k * kMegaThreads;
+                    const int h = i / hd, d = i - h * hd;
+                    const float* pa = a.part_acc + static_cast<size_t>(h) * 4 * hd + d;
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) pv[k][c] = (i < qd && (c == 0 || n_kv >= 512)) ? __ldcg(pa + c * hd) : 0.0f;
                 }
-                y_s[i] = out;
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const int i = i0 + k * kMegaThreads;
+                    if (i >= qd) continue;
+                    const int h = i / hd;
+                    const float* pr = s_pair + h * 8;
+                    float out;
+                    if (n_kv < 512) {
+                        out = __fmul_rn(pv[k][0], pr[0]);
+                    } else {
+                        float acc = 0.0f, s_final = 0.0f;
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) {
+                            if (pr[2 * c] < 0.0f) continue;
+                            acc = __fmaf_rn(acc, pr[2 * c], __fmul_rn(pv[k][c], pr[2 * c + 1]));
+                            s_final = __fmaf_rn(s_final, pr[2 * c], __fmul_rn(s_pair[a.q_heads * 8 + h * 4 + c], pr[2 * c + 1]));
+                        }
+                        out = s_final != 0.0f ? __fmul_rn(acc, __fdiv_rn(1.0f, s_final)) : acc;
+                    }
+                    y_s[i] = out;
+                }
             }
             __syncthreads();
         }
