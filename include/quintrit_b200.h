@@ -215,8 +215,8 @@ int quintrit_b200_decoder_time_token(quintrit_b200_decoder_t* decoder, uint32_t 
 /*
  * Profiling aid (the reference's counterpart is its ATTN_STOP phase cut, quintrit-cuda/kernels/layer.cu:296-297): runs one
  * decode step like quintrit_b200_decoder_time_token and returns the device's global timer (ns) as sampled by CTA 0 at
- * every phase boundary of the single-kernel path: 13 stamps per layer (norm, q|k|v, barrier, attention, barrier,
- * combine, o + barrier, norm, gate|up, barrier, SwiGLU + barrier, down, barrier) after one at the start, then two
+ * every phase boundary of the single-kernel path: 14 stamps per layer (norm, q|k|v, barrier, scores, barrier + values,
+ * barrier, combine, o + barrier, norm, gate|up, barrier, SwiGLU + barrier, down, barrier) after one at the start, then two
  * around the output head. *out_count receives the number of stamps (also on QUINTRIT_ERR_BUFFER_TOO_SMALL).
  */
 int quintrit_b200_decoder_trace_step(quintrit_b200_decoder_t* decoder, uint64_t* out_ns, size_t capacity, size_t* out_count);

@@ -762,7 +762,12 @@ int decoder_create_impl(const quintrit_b200_decoder_desc_t* desc, quintrit_b200_
     d->use_mega = false;
     const char* mode = std::getenv("QUINTRIT_B200_DECODE");  // "kernels" keeps the one-launch-per-step path (experiments)
     // the single-kernel path stages KV rows with a piece permutation that needs a power-of-two head_dim of at least 64
-    const bool staged_ok = hd >= 64 && (hd & (hd - 1)) == 0;
+    // and one values unit of the longest chunk must fit the shared memory of an SM next to the activation vectors
+    const int gqa_n = d->q_heads / d->kv_heads;
+    const size_t mega_bytes = mega_smem_bytes(mega_attn_region(d->ctx, gqa_n, hd), static_cast<int>(std::max<size_t>(H, qd)), static_cast<int>(H), static_cast<int>(L));
+    int smem_optin = 0;
+    QTB_CUDA(cudaDeviceGetAttribute(&smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, d->device));
+    const bool staged_ok = hd >= 64 && (hd & (hd - 1)) == 0 && gqa_n <= 16 && mega_bytes <= static_cast<size_t>(smem_optin);
     if (desc->arch == QUINTRIT_B200_ARCH_LLAMA && staged_ok && d->q_heads <= kMegaMaxHeads && !(mode && std::strcmp(mode, "kernels") == 0)) {
         if ((rc = mega_setup(d, desc)) != QUINTRIT_OK) return rc;
         d->use_mega = true;
@@ -803,7 +808,8 @@ int mega_setup(quintrit_b200_decoder* d, const quintrit_b200_decoder_desc_t* des
     if ((rc = dev_alloc(d, &d->xa, H)) != QUINTRIT_OK || (rc = dev_alloc(d, &d->xb, H)) != QUINTRIT_OK ||
         (rc = dev_alloc(d, &d->v_inter, I)) != QUINTRIT_OK || (rc = dev_alloc(d, &d->amax_bits, 4)) != QUINTRIT_OK ||
         (rc = dev_alloc(d, &d->best_val, d->sm_count)) != QUINTRIT_OK || (rc = dev_alloc(d, &d->best_idx, d->sm_count)) != QUINTRIT_OK ||
-        (rc = dev_alloc(d, &d->bar, 4)) != QUINTRIT_OK || (rc = dev_alloc(d, &d->trace, size_t(L) * 13 + 8)) != QUINTRIT_OK)
+        (rc = dev_alloc(d, &d->bar, 4)) != QUINTRIT_OK || (rc = dev_alloc(d, &d->trace, size_t(L) * 14 + 8)) != QUINTRIT_OK ||
+        (rc = dev_alloc(d, &d->scores, size_t(d->q_heads) * d->ctx)) != QUINTRIT_OK)
         return rc;
     std::vector<GemvItem> items;
     std::vector<MegaLayer> layers(L);
@@ -839,9 +845,10 @@ int mega_setup(quintrit_b200_decoder* d, const quintrit_b200_decoder_desc_t* des
     a.xa = d->xa, a.xb = d->xb;
     a.acc_qkv = d->acc_qkv, a.acc_o = d->acc_o, a.acc_gu = d->acc_gu, a.acc_down = d->acc_down;
     a.v_inter = d->v_inter, a.amax_bits = d->amax_bits, a.part_acc = d->part_acc, a.part_ms = d->part_ms, a.logits = d->logits;
+    a.scores = d->scores, a.attn_region = static_cast<unsigned int>(mega_attn_region(d->ctx, d->q_heads / d->kv_heads, d->head_dim));
     a.best_val = d->best_val, a.best_idx = d->best_idx, a.token = d->d_token, a.pos = d->d_pos, a.history = d->d_history;
     a.bar = d->bar, a.status = d->d_counters + 2, a.trace = nullptr;
-    d->mega_smem = mega_smem_bytes(std::max(H, qd), H, L);
+    d->mega_smem = mega_smem_bytes(a.attn_region, std::max(H, qd), H, L);
     // the table-base constant: measured once per device like the GEMV kernel's
     unsigned int base = 0xFFFFFFFFu;
     smem_base_kernel<<<1, 32, 1024>>>(reinterpret_cast<unsigned int*>(d->bar));
@@ -1125,7 +1132,7 @@ extern "C" int quintrit_b200_decoder_trace_step(quintrit_b200_decoder_t* decoder
         quintrit_b200_decoder* d = decoder;
         if (out_count == nullptr) return fail(QUINTRIT_ERR_NULL_POINTER, "out_count is NULL");
         if (!d->use_mega) return fail(QUINTRIT_ERR_UNSUPPORTED, "phase tracing is available for the single-kernel decode path only");
-        const size_t n = size_t(d->layers) * 13 + 4;
+        const size_t n = size_t(d->layers) * 14 + 4;
         *out_count = n;
         if (out_ns == nullptr || capacity < n) return fail(QUINTRIT_ERR_BUFFER_TOO_SMALL, "out_ns holds %zu values, %zu are needed", capacity, n);
         if (d->host_pos >= static_cast<uint32_t>(d->ctx)) return fail(QUINTRIT_ERR_CONTEXT_OVERFLOW, "the context window is full");

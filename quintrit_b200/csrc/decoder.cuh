@@ -23,6 +23,7 @@ struct quintrit_b200_decoder {
     std::vector<void*> allocs;
     __half *embed, *lm_head, *kc, *vc, *x16;
     float *out_norm, *cos_sin, *x, *q, *part_acc, *part_ms, *logits;
+    float* scores = nullptr;  // single-kernel path: attention scores of the current token, [q_heads][ctx]
     std::vector<float*> norms;  // layers * 4 (device)
     int8_t *a8_h, *a8_q, *a8_i;
     float *s_h, *s_q, *s_i;

@@ -48,8 +48,10 @@ struct MegaArgs {
     int32_t *acc_qkv, *acc_o, *acc_gu, *acc_down;
     float* v_inter;           // SwiGLU output (inter)
     unsigned int* amax_bits;  // two slots, alternating by layer
+    float* scores;            // [q_heads][ctx] attention scores of the current token
     float* part_acc;
     float* part_ms;
+    unsigned int attn_region; // bytes of shared memory before the activation vector (mega_attn_region)
     float* logits;
     float* best_val;          // per-CTA greedy candidates
     unsigned int* best_idx;
@@ -58,7 +60,7 @@ struct MegaArgs {
     uint32_t* history;
     unsigned int* bar;        // grid barrier counter, cleared by the host before every launch
     unsigned int* status;     // 0 = fine, 1 = wrong shared-memory base, 2 = a barrier timed out
-    unsigned long long* trace; // optional: CTA 0 stores the global timer at every phase boundary (7 per layer + 3)
+    unsigned long long* trace; // optional: CTA 0 stores the global timer at every phase boundary (14 per layer + 3)
 };
 
 __device__ __forceinline__ unsigned long long global_timer_ns() {
@@ -314,24 +316,23 @@ __device__ __forceinline__ float key_score(const unsigned char* buf, int r, int 
     return __fadd_rn(__fadd_rn(acc[0], acc[1]), __fadd_rn(acc[2], acc[3]));
 }
 
-// One staged block of the value accumulation for one coordinate d (attention.rs:448-470): n positions in order, factors
-// ms[r] / vs[r]. The running sum is rounded to half precision after every operation unless F32. Groups of eight
-// positions are fetched into registers first; a group whose rescale factors are all 1 (every group but the few where
-// the running maximum moved) runs the bare multiply-add chain.
+// One staged run of the value accumulation for one coordinate (attention.rs:448-470): n positions in order, the value of
+// position r at col[r * stride], factors ms[r] / vs[r]. The running sum is rounded to half precision after every
+// operation unless F32. Groups of eight positions are fetched into registers first; a group whose rescale factors are
+// all 1 (every group but the few where the running maximum moved) runs the bare multiply-add chain. Kept small: the
+// registers of a call chain add up (kernel + phase + unit + this), and beyond the budget every function of the kernel spills.
 template <bool F32>
-__device__ __noinline__ float value_chain(const unsigned char* buf, int row_bytes, int d, const float* ms, const float* vs, int n, float acc) {
+__device__ __noinline__ float value_chain(const __half* col, int stride, const float* ms, const float* vs, int n, float acc) {
     auto rnd = [](float x) { return F32 ? x : __half2float(__float2half_rn(x)); };
-    const int piece = d >> 3, within = (d & 7) * 2;
     int r = 0;
-    for (; r + 8 <= n; r += 8) {  // r is a multiple of 8: row r + j has its pieces permuted by j
+    for (; r + 8 <= n; r += 8) {
         float m[8], w[8], v[8];
         bool moved = false;
-        const unsigned char* rows = buf + r * row_bytes + within;
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
             m[j] = ms[r + j];
             w[j] = vs[r + j];
-            v[j] = __half2float(*reinterpret_cast<const __half*>(rows + j * row_bytes + ((piece ^ j) << 4)));
+            v[j] = __half2float(col[(r + j) * stride]);
             moved |= m[j] != 1.0f;
         }
         if (!moved) {
@@ -346,142 +347,182 @@ __device__ __noinline__ float value_chain(const unsigned char* buf, int row_byte
         }
     }
     for (; r < n; ++r) {
-        const float m = ms[r];
-        if (m != 1.0f) acc = rnd(__fmul_rn(acc, m));
-        acc = rnd(__fmaf_rn(__half2float(*reinterpret_cast<const __half*>(buf + staged_offset(r, piece, row_bytes) + within)), vs[r], acc));
+        const float mr = ms[r];
+        if (mr != 1.0f) acc = rnd(__fmul_rn(acc, mr));
+        acc = rnd(__fmaf_rn(__half2float(col[r * stride]), vs[r], acc));
     }
     return acc;
 }
 
-// One (query head, KV chunk) of the attention of one layer: attention_kernel with the RoPE of q and of the new key, the
-// post-scaling and the KV append folded in (rope_kv_kernel), so that no barrier is needed between them. K and then V
-// rows pass through two 64 KiB shared-memory blocks of 128 positions filled by asynchronous copies (block j + 2 is
-// requested when block j has been consumed), so neither the scores nor the strictly sequential value accumulation wait
-// for global memory. `smem` is the CTA's dynamic shared memory from its start: the first block overlays the GEMV table,
-// whose zero rows are restored before returning.
-__device__ __noinline__ void mega_attention_unit(const MegaArgs& a, const MegaLayer& ly, int h, int c, float s_in, unsigned char* smem) {
-    unsigned char* s_blk = smem;                                    // 2 x kAttnBlockBytes
-    float* s_score = reinterpret_cast<float*>(smem + 2 * kAttnBlockBytes);  // kAttnMaxChunk floats
-    float* s_ms = s_score + kAttnMaxChunk;                         // kAttnMaxChunk floats
-    float* s_q = s_ms + kAttnMaxChunk;                             // 256 floats
-    float* s_tm = s_q + 256;                                       // kMegaThreads floats
-    __half* s_kcur = reinterpret_cast<__half*>(s_tm + kMegaThreads);  // 256 halves
-    __half* s_vcur = s_kcur + 256;
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int hd = a.head_dim, gqa = a.q_heads / a.kv_heads, kvh = h / gqa;
+// KV geometry of the current token (attention.rs:392-396, 483-542): the padded KV axis and the chunk split.
+struct KvSplit {
+    int pos, seq_len, n_kv, chunk;  // chunk = positions per chunk (n_kv when there is a single chunk)
+    bool split;
+};
+__device__ __forceinline__ KvSplit kv_split(const MegaArgs& a) {
+    KvSplit s;
+    s.pos = static_cast<int>(a.pos[0]);
+    s.seq_len = s.pos + 1;
+    s.n_kv = (s.seq_len + 255) / 256 * 256;
+    if (s.n_kv < 256) s.n_kv = 256;
+    if (s.n_kv > a.ctx) s.n_kv = a.ctx;
+    s.split = s.n_kv >= 512;
+    s.chunk = s.split ? (s.n_kv + 3) / 4 : s.n_kv;
+    return s;
+}
+
+// Attention, first half: the scores of `rows` consecutive positions from r0 of one KV head against the query heads that
+// share it (rope_kv_kernel + phase A of attention_kernel). The key rows are staged once in shared memory (asynchronous
+// 16-byte copies) and used by every query head of the group; the unit that holds the current position computes the new
+// key and value rows, appends them to the cache and scores the new key from shared memory. Scores go to
+// a.scores[head][position]. `smem` is the CTA's dynamic shared memory from its start: the staged block overlays the GEMV
+// table, whose zero rows are restored before returning.
+__device__ __noinline__ void mega_scores_unit(const MegaArgs& a, const MegaLayer& ly, int kvh, int r0, int rows, float s_in, unsigned char* smem) {
+    const int tid = threadIdx.x;
+    const int hd = a.head_dim, gqa = a.q_heads / a.kv_heads;
     const int qd = a.q_heads * hd, kvd = a.kv_heads * hd, row_bytes = hd * 2;
+    unsigned char* blk = smem;                                               // kAttnBlockBytes
+    float* s_q = reinterpret_cast<float*>(smem + kAttnBlockBytes);           // gqa x head_dim floats
+    __half* s_kcur = reinterpret_cast<__half*>(s_q + gqa * hd);              // head_dim halves
+    __half* s_vcur = s_kcur + hd;
     const bool f32v = a.f32_values != 0;
     const float attn_scale = a.attn_scale;
-    const int pos = static_cast<int>(a.pos[0]), seq_len = pos + 1;
-    int n_kv = (seq_len + 255) / 256 * 256;
-    if (n_kv < 256) n_kv = 256;
-    if (n_kv > a.ctx) n_kv = a.ctx;
-    int start = 0, end = seq_len;
-    if (n_kv >= 512) {
-        const int chunk = (n_kv + 3) / 4;
-        start = c * chunk;
-        end = min(min(start + chunk, n_kv), seq_len);
-    } else if (c > 0) {
-        start = end;
-    }
-    float* my_acc = a.part_acc + (static_cast<size_t>(h) * 4 + c) * hd;
-    float* my_ms = a.part_ms + (static_cast<size_t>(h) * 4 + c) * 2;
-    const int len = end - start;
-    if (len <= 0) {
-        if (tid == 0) {
-            my_ms[0] = -INFINITY;
-            my_ms[1] = 0.0f;
-        }
-        return;
-    }
-    const __half* kbase = ly.kc + static_cast<size_t>(kvh) * hd + static_cast<size_t>(start) * kvd;
-    const __half* vbase = ly.vc + static_cast<size_t>(kvh) * hd + static_cast<size_t>(start) * kvd;
-    const bool has_cur = pos >= start && pos < end;
-    const int pcur = pos - start;            // index of the current position inside the chunk (valid if has_cur)
-    const int len_old = has_cur ? pcur : len;  // rows that come from the cache (the current position is the last one)
-    const int nblk = (len + kAttnBlockPos - 1) / kAttnBlockPos;
-    // Staging jobs 0..nblk-1 are the K blocks, nblk..2*nblk-1 the V blocks; job j uses block j & 1 and one copy group.
-    auto issue = [&](int j) {
-        if (j < nblk)
-            stage_rows(s_blk + (j & 1) * kAttnBlockBytes, kbase, j * kAttnBlockPos, len_old, hd, kvd);
-        else if (j < 2 * nblk)
-            stage_rows(s_blk + (j & 1) * kAttnBlockBytes, vbase, (j - nblk) * kAttnBlockPos, len_old, hd, kvd);
-        cp_async_commit();
-    };
-    __syncthreads();  // every thread is done with the table the first block overlays
-    issue(0);
-    issue(1);
+    const int pos = static_cast<int>(a.pos[0]);
+    const bool has_cur = pos >= r0 && pos < r0 + rows;
+    const int len_old = has_cur ? pos - r0 : rows;  // rows that come from the cache
+    const __half* kbase = ly.kc + static_cast<size_t>(kvh) * hd + static_cast<size_t>(r0) * kvd;
+    __syncthreads();  // every thread is done with the table the block overlays
+    stage_rows(blk, kbase, 0, len_old, hd, kvd);
+    cp_async_commit();
 
     const bool live = s_in > 0.0f;
     const float pq = live ? __fdiv_rn(ly.ws[0], s_in) : 0.0f, pk = live ? __fdiv_rn(ly.ws[1], s_in) : 0.0f, pv = live ? __fdiv_rn(ly.ws[2], s_in) : 0.0f;
     const float* cs = a.cos_sin + static_cast<size_t>(pos) * a.rope_dims;
-    for (int p = tid; p < hd / 2; p += kMegaThreads) {
+    const int half = hd / 2;
+    // rotated, rescaled query heads (and the new key / value rows): all integer results are read before the first use
+    for (int idx = tid; idx < (gqa + (has_cur ? 1 : 0)) * half; idx += kMegaThreads) {
+        const int g = idx / half, p = idx - g * half;
+        const bool is_q = g < gqa;
+        const int src = is_q ? (kvh * gqa + g) * hd + 2 * p : qd + kvh * hd + 2 * p;
+        const int i0 = __ldcg(a.acc_qkv + src), i1 = __ldcg(a.acc_qkv + src + 1);
+        int j0 = 0, j1 = 0;
+        if (!is_q) {
+            j0 = __ldcg(a.acc_qkv + src + kvd);
+            j1 = __ldcg(a.acc_qkv + src + kvd + 1);
+        }
         const bool rot = p < a.rope_dims / 2;
         float c0 = 1.0f, sn = 0.0f;
         if (rot) {
             c0 = cs[2 * p];
             sn = cs[2 * p + 1];
         }
-        {
-            float x0 = live ? __fmul_rn(static_cast<float>(a.acc_qkv[h * hd + 2 * p]), pq) : 0.0f;
-            float x1 = live ? __fmul_rn(static_cast<float>(a.acc_qkv[h * hd + 2 * p + 1]), pq) : 0.0f;
-            if (rot) {
-                const float r0 = __fmaf_rn(x0, c0, -__fmul_rn(x1, sn)), r1 = __fmaf_rn(x0, sn, __fmul_rn(x1, c0));
-                x0 = r0;
-                x1 = r1;
-            }
-            s_q[2 * p] = f32v ? x0 : __half2float(__float2half_rn(x0));
-            s_q[2 * p + 1] = f32v ? x1 : __half2float(__float2half_rn(x1));
+        const float post = is_q ? pq : pk;
+        float x0 = live ? __fmul_rn(static_cast<float>(i0), post) : 0.0f, x1 = live ? __fmul_rn(static_cast<float>(i1), post) : 0.0f;
+        if (rot) {
+            const float y0 = __fmaf_rn(x0, c0, -__fmul_rn(x1, sn)), y1 = __fmaf_rn(x0, sn, __fmul_rn(x1, c0));
+            x0 = y0;
+            x1 = y1;
         }
-        if (has_cur) {
-            float x0 = live ? __fmul_rn(static_cast<float>(a.acc_qkv[qd + kvh * hd + 2 * p]), pk) : 0.0f;
-            float x1 = live ? __fmul_rn(static_cast<float>(a.acc_qkv[qd + kvh * hd + 2 * p + 1]), pk) : 0.0f;
-            if (rot) {
-                const float r0 = __fmaf_rn(x0, c0, -__fmul_rn(x1, sn)), r1 = __fmaf_rn(x0, sn, __fmul_rn(x1, c0));
-                x0 = r0;
-                x1 = r1;
-            }
+        if (is_q) {
+            s_q[g * hd + 2 * p] = f32v ? x0 : __half2float(__float2half_rn(x0));
+            s_q[g * hd + 2 * p + 1] = f32v ? x1 : __half2float(__float2half_rn(x1));
+        } else {
             s_kcur[2 * p] = __float2half_rn(x0);
             s_kcur[2 * p + 1] = __float2half_rn(x1);
-            const float v0 = live ? __fmul_rn(static_cast<float>(a.acc_qkv[qd + kvd + kvh * hd + 2 * p]), pv) : 0.0f;
-            const float v1 = live ? __fmul_rn(static_cast<float>(a.acc_qkv[qd + kvd + kvh * hd + 2 * p + 1]), pv) : 0.0f;
-            s_vcur[2 * p] = __float2half_rn(v0);
-            s_vcur[2 * p + 1] = __float2half_rn(v1);
+            s_vcur[2 * p] = __float2half_rn(live ? __fmul_rn(static_cast<float>(j0), pv) : 0.0f);
+            s_vcur[2 * p + 1] = __float2half_rn(live ? __fmul_rn(static_cast<float>(j1), pv) : 0.0f);
         }
     }
     __syncthreads();
-    if (has_cur && h % gqa == 0) {  // append to the cache (kv_cache.rs:124-138); one unit per KV head does it
-        for (int d = tid; d < hd; d += kMegaThreads) {
-            const_cast<__half*>(kbase)[static_cast<size_t>(pcur) * kvd + d] = s_kcur[d];
-            const_cast<__half*>(vbase)[static_cast<size_t>(pcur) * kvd + d] = s_vcur[d];
-        }
+    if (has_cur && tid < hd) {  // append to the cache (kv_cache.rs:124-138) and put the new key into the staged block
+        const size_t at = static_cast<size_t>(pos) * kvd + static_cast<size_t>(kvh) * hd + tid;
+        ly.kc[at] = s_kcur[tid];
+        ly.vc[at] = s_vcur[tid];
+        *reinterpret_cast<__half*>(blk + staged_offset(pos - r0, tid >> 3, row_bytes) + (tid & 7) * 2) = s_kcur[tid];
     }
-    // The row of the current position is not in the cache when its block is staged: it is written into the block.
-    auto patch_current = [&](unsigned char* blk, int pb, const __half* cur) {
-        if (has_cur && pcur >= pb && pcur < pb + kAttnBlockPos && tid < hd)
-            *reinterpret_cast<__half*>(blk + staged_offset(pcur - pb, tid >> 3, row_bytes) + (tid & 7) * 2) = cur[tid];
-    };
-    // ---- scores: one thread per staged row ----
-    for (int b = 0; b < nblk; ++b) {
-        unsigned char* blk = s_blk + (b & 1) * kAttnBlockBytes;
-        cp_async_wait<1>();
-        patch_current(blk, b * kAttnBlockPos, s_kcur);
-        __syncthreads();
-        const int p = b * kAttnBlockPos + tid;
-        if (tid < kAttnBlockPos && p < len) {
-            const float sc = f32v ? key_score<true>(blk, tid, hd, s_q) : key_score<false>(blk, tid, hd, s_q);
-            s_score[p] = __fmul_rn(sc, attn_scale);
-        }
-        __syncthreads();  // the block is refilled now
-        issue(b + 2);
+    cp_async_wait<0>();
+    __syncthreads();
+    for (int t = tid; t < rows * gqa; t += kMegaThreads) {
+        const int g = t / rows, r = t - g * rows;
+        const float sc = f32v ? key_score<true>(blk, r, hd, s_q + g * hd) : key_score<false>(blk, r, hd, s_q + g * hd);
+        a.scores[static_cast<size_t>(kvh * gqa + g) * a.ctx + r0 + r] = __fmul_rn(sc, attn_scale);
     }
+    __syncthreads();
+    for (int i = tid; i < 13 * 64; i += kMegaThreads) {  // the zero rows of the table (byte values that are no velurex code)
+        const int k = i >> 6;
+        reinterpret_cast<int*>(smem)[(k < 9 ? 28 * k + 27 : 243 + k) * 64 + (i & 63)] = 0;
+    }
+    __syncthreads();
+}
+
+constexpr int kAttnSlice = 32;  // coordinates of a head that one values unit accumulates (one warp per query head)
+
+// Shared memory a values unit needs for chunks of `len` positions and `gqa` query heads per KV head.
+__host__ __device__ constexpr size_t values_unit_bytes(int len, int gqa) {
+    return (static_cast<size_t>(len) * kAttnSlice * 2 + 15) / 16 * 16 + static_cast<size_t>(2) * gqa * len * 4 + (kMegaWarps + 16) * 4;
+}
+
+// Attention, second half: for one KV head, one chunk of positions and one slice of 32 coordinates, the softmax factors of
+// every query head of the group (phase B of attention_kernel, recomputed by every slice) and the value accumulation
+// (phase C). The V slice of the whole chunk is staged in shared memory in four copy groups; warp g runs the chains of
+// query head g, one coordinate per lane, strictly in position order. Slice 0 also produces M and S of each head.
+__device__ __noinline__ void mega_values_unit(const MegaArgs& a, const MegaLayer& ly, int kvh, int c, int slice, unsigned char* smem) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int hd = a.head_dim, gqa = a.q_heads / a.kv_heads, kvd = a.kv_heads * hd;
+    const bool f32v = a.f32_values != 0;
+    const KvSplit ks = kv_split(a);
+    int start = 0, end = ks.seq_len;
+    if (ks.split) {
+        start = c * ks.chunk;
+        end = min(min(start + ks.chunk, ks.n_kv), ks.seq_len);
+    } else if (c > 0) {
+        start = end;
+    }
+    const int len = end - start;
+    if (len <= 0) {
+        if (slice == 0 && tid < gqa) {
+            float* my_ms = a.part_ms + (static_cast<size_t>(kvh * gqa + tid) * 4 + c) * 2;
+            my_ms[0] = -INFINITY;
+            my_ms[1] = 0.0f;
+        }
+        return;
+    }
+    __half* vbuf = reinterpret_cast<__half*>(smem);                                   // [len][32] halves
+    float* f_ms = reinterpret_cast<float*>(smem + (static_cast<size_t>(len) * kAttnSlice * 2 + 15) / 16 * 16);  // [gqa][len]
+    float* f_vs = f_ms + gqa * len;                                                   // [gqa][len]: scores, then vs
+    float* s_tm = f_vs + gqa * len;                                                   // kMegaWarps floats
+    float* s_M = s_tm + kMegaWarps;                                                   // up to 16 heads
+    __syncthreads();  // every thread is done with the table the slice overlays
     {
-        // running maximum in position order: maximum of the thread's own positions, an exclusive scan over the threads
-        // (shuffles inside a warp, a short loop over the earlier warps), then ms / vs per position (attention.rs:448-462)
-        const int per = (len + kMegaThreads - 1) / kMegaThreads;
-        const int p0 = min(tid * per, len), p1 = min(p0 + per, len);
+        // the V slice in four groups of rows, so that the chain can start when the first quarter has landed
+        const __half* vsrc = ly.vc + static_cast<size_t>(start) * kvd + static_cast<size_t>(kvh) * hd + slice * kAttnSlice;
+        const int q_rows = (len + 3) / 4;
+        for (int q = 0; q < 4; ++q) {
+            const int ra = min(q * q_rows, len), rb = min(ra + q_rows, len);
+            for (int v = ra * 4 + tid; v < rb * 4; v += kMegaThreads) {
+                const int r = v >> 2, pc = v & 3;
+                cp_async16(vbuf + r * kAttnSlice + pc * 8, vsrc + static_cast<size_t>(r) * kvd + pc * 8);
+            }
+            cp_async_commit();
+        }
+    }
+    for (int idx = tid; idx < gqa * len; idx += kMegaThreads) {
+        const int g = idx / len, p = idx - g * len;
+        f_vs[idx] = __ldcg(a.scores + static_cast<size_t>(kvh * gqa + g) * a.ctx + start + p);
+    }
+    __syncthreads();
+    // softmax factors: four groups of 128 threads take one head each; running maximum in position order by a scan over
+    // the group's threads (attention.rs:448-462)
+    for (int g0 = 0; g0 < gqa; g0 += 4) {
+        const int g = g0 + (tid >> 7), gt = tid & 127, gw = gt >> 5;  // head, thread and warp inside the group
+        const bool active = g < gqa;
+        const int per = (len + 127) / 128;
+        const int p0 = min(gt * per, len), p1 = min(p0 + per, len);
+        float* sc_g = f_vs + (active ? g : 0) * len;
+        float* ms_g = f_ms + (active ? g : 0) * len;
         float m = -INFINITY;
-        for (int p = p0; p < p1; ++p) m = fmaxf(m, s_score[p]);
+        if (active)
+            for (int p = p0; p < p1; ++p) m = fmaxf(m, sc_g[p]);
         float incl = m;
         for (int o = 1; o < 32; o <<= 1) {
             const float t = __shfl_up_sync(0xffffffffu, incl, o);
@@ -491,353 +532,475 @@ __device__ __noinline__ void mega_attention_unit(const MegaArgs& a, const MegaLa
         __syncthreads();
         float run = __shfl_up_sync(0xffffffffu, incl, 1);
         if (lane == 0) run = -INFINITY;
-        for (int w = 0; w < warp; ++w) run = fmaxf(run, s_tm[w]);
-        for (int p = p0; p < p1; ++p) {
-            const float sc = s_score[p];
-            const float m_old = run;
-            float ms = 1.0f, vs = 1.0f;
-            if (sc > run) {
-                run = sc;
-                ms = device_expf(__fsub_rn(m_old, run));
-            } else {
-                vs = device_expf(__fsub_rn(sc, run));
+        for (int w = 0; w < gw; ++w) run = fmaxf(run, s_tm[(warp - gw) + w]);
+        if (active) {
+            for (int p = p0; p < p1; ++p) {
+                const float sc = sc_g[p];
+                const float m_old = run;
+                float ms = 1.0f, vs = 1.0f;
+                if (sc > run) {
+                    run = sc;
+                    ms = device_expf(__fsub_rn(m_old, run));
+                } else {
+                    vs = device_expf(__fsub_rn(sc, run));
+                }
+                ms_g[p] = ms;
+                sc_g[p] = vs;
             }
-            s_ms[p] = ms;
-            s_score[p] = vs;
-        }
-    }
-    // ---- values: threads 0..hd-1 run the chain, one coordinate each, strictly in position order; the last thread
-    // accumulates S over the same positions meanwhile ----
-    float acc = 0.0f, S = 0.0f;
-    for (int b = 0; b < nblk; ++b) {
-        unsigned char* blk = s_blk + ((nblk + b) & 1) * kAttnBlockBytes;
-        cp_async_wait<1>();
-        const int pb = b * kAttnBlockPos, pe = min(kAttnBlockPos, len - pb);
-        patch_current(blk, pb, s_vcur);  // a thread patches the coordinate it reads itself
-        __syncthreads();                 // the block has landed for every thread; (b == 0) the factors are written
-        if (tid < hd) {
-            acc = f32v ? value_chain<true>(blk, row_bytes, tid, s_ms + pb, s_score + pb, pe, acc)
-                       : value_chain<false>(blk, row_bytes, tid, s_ms + pb, s_score + pb, pe, acc);
-        } else if (tid == kMegaThreads - 1) {
-#pragma unroll 8
-            for (int p = pb; p < pb + pe; ++p) S = __fmaf_rn(S, s_ms[p], s_score[p]);  // attention.rs:466
+            if (gt == 0) s_M[g] = fmaxf(fmaxf(s_tm[warp], s_tm[warp + 1]), fmaxf(s_tm[warp + 2], s_tm[warp + 3]));
         }
         __syncthreads();
-        issue(nblk + b + 2);
     }
-    cp_async_wait<0>();
-    if (tid < hd) my_acc[tid] = acc;
-    if (tid == kMegaThreads - 1) {
-        float M = -INFINITY;
-        for (int w = 0; w < kMegaWarps; ++w) M = fmaxf(M, s_tm[w]);
-        my_ms[0] = M;
-        my_ms[1] = S;
+    // values: warp g < gqa runs head g (heads beyond the warp count take further rounds); with slice 0, lane 0 of warp
+    // kMegaWarps - 1 - g accumulates S of head g over the same positions meanwhile
+    const int q_rows = (len + 3) / 4;
+    for (int g0 = 0; g0 < gqa; g0 += kMegaWarps / 2) {
+        const int g = g0 + warp;
+        const bool chain = warp < kMegaWarps / 2 && g < gqa;
+        const int gs = g0 + (kMegaWarps - 1 - warp);
+        const bool sums = slice == 0 && warp >= kMegaWarps / 2 && gs < gqa && lane == 0;
+        float acc = 0.0f, S = 0.0f;
+        for (int q = 0; q < 4; ++q) {
+            if (g0 == 0) {
+                if (q == 0) cp_async_wait<3>();
+                if (q == 1) cp_async_wait<2>();
+                if (q == 2) cp_async_wait<1>();
+                if (q == 3) cp_async_wait<0>();
+                __syncthreads();
+            }
+            const int ra = min(q * q_rows, len), rb = min(ra + q_rows, len);
+            if (chain) {
+                acc = f32v ? value_chain<true>(vbuf + ra * kAttnSlice + lane, kAttnSlice, f_ms + g * len + ra, f_vs + g * len + ra, rb - ra, acc)
+                           : value_chain<false>(vbuf + ra * kAttnSlice + lane, kAttnSlice, f_ms + g * len + ra, f_vs + g * len + ra, rb - ra, acc);
+            } else if (sums) {
+#pragma unroll 8
+                for (int p = ra; p < rb; ++p) S = __fmaf_rn(S, f_ms[gs * len + p], f_vs[gs * len + p]);  // attention.rs:466
+            }
+        }
+        if (chain) a.part_acc[(static_cast<size_t>(kvh * gqa + g) * 4 + c) * hd + slice * kAttnSlice + lane] = acc;
+        if (sums) {
+            float* my_ms = a.part_ms + (static_cast<size_t>(kvh * gqa + gs) * 4 + c) * 2;
+            my_ms[0] = s_M[gs];
+            my_ms[1] = S;
+        }
     }
-    // the zero rows of the table (the 13 byte values that are no velurex code) were overwritten by the first block
-    for (int i = tid; i < 13 * 64; i += kMegaThreads) {
+    __syncthreads();
+    for (int i = tid; i < 13 * 64; i += kMegaThreads) {  // the zero rows of the table (byte values that are no velurex code)
         const int k = i >> 6;
         reinterpret_cast<int*>(smem)[(k < 9 ? 28 * k + 27 : 243 + k) * 64 + (i & 63)] = 0;
     }
-    __syncthreads();  // the scratch is reused
+    __syncthreads();
 }
 
-// Shared-memory plan of the megakernel (bytes from the dynamic base): table | attention scratch | y (floats) | a8 | small.
-// The attention unit uses the table and its scratch together: two staged blocks, then its small arrays.
-constexpr int kMegaAttnScratch = 2 * kAttnBlockBytes - kTableBytes + (2 * kAttnMaxChunk + 256 + kMegaThreads) * 4 + 2 * 256 * 2;
-static_assert(kTableBytes <= kAttnBlockBytes, "the first staged block covers the table");
+// Shared-memory plan of the token kernel (bytes from the dynamic base): attention region (its first 64 KiB double as the
+// GEMV table) | y (floats) | a8 | small. The attention region holds whichever is largest: a scores unit (staged key block,
+// the group's queries, the new key/value rows), a values unit for the longest chunk, or the lm_head rings.
+__host__ __device__ constexpr size_t mega_attn_region(int ctx, int gqa, int head_dim) {
+    const int len_max = ctx < 512 ? ctx : (ctx + 3) / 4;
+    size_t need = static_cast<size_t>(kAttnBlockBytes) + static_cast<size_t>(gqa) * head_dim * 4 + static_cast<size_t>(head_dim) * 4 + 64;
+    const size_t vals = values_unit_bytes(len_max, gqa), head = static_cast<size_t>(kMegaWarps) * 4 * 1024 * 2 + 1024;
+    if (vals > need) need = vals;
+    if (head > need) need = head;
+    return (need + 1023) / 1024 * 1024;
+}
 // After the small arrays: the norm weights of the next norm (hidden floats) and a copy of every layer's descriptor.
-__host__ __device__ constexpr size_t mega_smem_bytes(int maxvec, int hidden, int layers) {
-    return static_cast<size_t>(kTableBytes) + kMegaAttnScratch + static_cast<size_t>(maxvec) * 4 + (static_cast<size_t>(maxvec) + 15) / 16 * 16 + 4096 +
+__host__ __device__ constexpr size_t mega_smem_bytes(size_t attn_region, int maxvec, int hidden, int layers) {
+    return attn_region + static_cast<size_t>(maxvec) * 4 + (static_cast<size_t>(maxvec) + 15) / 16 * 16 + 4096 +
            (static_cast<size_t>(hidden) * 4 + 15) / 16 * 16 + static_cast<size_t>(layers) * sizeof(MegaLayer);
 }
 
-template <uint32_t BASE>
-__global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(MegaArgs a) {
-    extern __shared__ __align__(1024) unsigned char smem[];
+// ---- the token kernel ---------------------------------------------------------------------------------------------------
+// Every phase is its own non-inlined function and the kernel body keeps almost nothing alive across the calls (scalars
+// that outlive a phase sit in shared memory), so each phase gets the whole register file to itself.
+
+// Views into the dynamic shared memory; recomputed inside every phase from the kernel arguments.
+struct MegaSmem {
+    int* tab;
+    float* y;        // activation vector (max(hidden, q_dim) floats)
+    int8_t* a8;      // its int8 codes
+    double* sh_d;    // 32 doubles
+    float* sh_f;     // 32 floats
+    float* pair;     // chunk-combine factors: q_heads * (4 * 2 + 4) floats (q_heads <= kMegaMaxHeads)
+    float* scale;    // [0] attention-input scale, [1] o-input scale, [2] ffn-input scale, [3] down-input scale (previous layer)
+    int* flag;
+    float* w;        // weights of the next norm
+    MegaLayer* layers;
+};
+__device__ __forceinline__ MegaSmem mega_smem_views(unsigned char* smem, const MegaArgs& a) {
+    MegaSmem v;
     const int maxvec = max(a.hidden, a.q_heads * a.head_dim);
-    int* tab = reinterpret_cast<int*>(smem);
-    unsigned char* attn_scratch = smem + kTableBytes;
-    float* y_s = reinterpret_cast<float*>(attn_scratch + kMegaAttnScratch);
-    int8_t* a8 = reinterpret_cast<int8_t*>(y_s + maxvec);
-    unsigned char* small = reinterpret_cast<unsigned char*>(a8) + (maxvec + 15) / 16 * 16;
-    double* sh_d = reinterpret_cast<double*>(small);       // 32 doubles
-    float* sh_f = reinterpret_cast<float*>(small + 256);   // 32 floats
-    float* s_pair = reinterpret_cast<float*>(small + 384); // chunk-combine factors: q_heads * (4 * 2 + 4) floats (q_heads <= kMegaMaxHeads)
-    int* s_flag = reinterpret_cast<int*>(small + 4000);
-    float* w_s = reinterpret_cast<float*>(small + 4096);   // weights of the next norm
-    MegaLayer* s_layers = reinterpret_cast<MegaLayer*>(small + 4096 + (static_cast<size_t>(a.hidden) * 4 + 15) / 16 * 16);
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, cta = blockIdx.x, G = gridDim.x;
+    v.tab = reinterpret_cast<int*>(smem);
+    v.y = reinterpret_cast<float*>(smem + a.attn_region);
+    v.a8 = reinterpret_cast<int8_t*>(v.y + maxvec);
+    unsigned char* small = reinterpret_cast<unsigned char*>(v.a8) + (maxvec + 15) / 16 * 16;
+    v.sh_d = reinterpret_cast<double*>(small);
+    v.sh_f = reinterpret_cast<float*>(small + 256);
+    v.pair = reinterpret_cast<float*>(small + 384);
+    v.scale = reinterpret_cast<float*>(small + 3968);
+    v.flag = reinterpret_cast<int*>(small + 4000);
+    v.w = reinterpret_cast<float*>(small + 4096);
+    v.layers = reinterpret_cast<MegaLayer*>(small + 4096 + (static_cast<size_t>(a.hidden) * 4 + 15) / 16 * 16);
+    return v;
+}
+
+__device__ __forceinline__ void prefetch_items(const MegaArgs& a, const MegaLayer& ly, int k) {
+    const int tid = threadIdx.x, G = gridDim.x, cta = blockIdx.x;
+    if (tid < 2 && cta + tid * G < ly.count[k]) prefetch_l2(a.items + ly.first[k] + cta + tid * G);
+}
+
+// Phase A (which = 0) and phase E (which = 1): residual (or embedding), RMSNorm, int8 codes for the projection that follows.
+__device__ __noinline__ void phase_norm(const MegaArgs& a, int l, int which, unsigned char* smem) {
+    const MegaSmem v = mega_smem_views(smem, a);
+    const int tid = threadIdx.x, cta = blockIdx.x, G = gridDim.x, H = a.hidden;
+    const MegaLayer& ly = v.layers[l];
+    prefetch_items(a, ly, which == 0 ? 0 : 2);
+    if (which == 0) {
+        if (l == 0) {
+            const size_t base = static_cast<size_t>(a.token[0]) * H;
+            for (int i = tid; i < H; i += kMegaThreads) v.y[i] = __half2float(a.embed[base + i]);
+        } else {
+            const float s_prev = v.scale[3];
+            const float post = s_prev > 0.0f ? __fdiv_rn(v.layers[l - 1].ws[6], s_prev) : 0.0f;
+            residual_add(v.y, a.xb, a.acc_down, post, s_prev > 0.0f, H);
+        }
+    } else {
+        const float s_q = v.scale[1];
+        const float post = s_q > 0.0f ? __fdiv_rn(ly.ws[3], s_q) : 0.0f;
+        residual_add(v.y, a.xa, a.acc_o, post, s_q > 0.0f, H);
+    }
+    cp_async_wait<0>();  // the norm weights requested one phase ago
+    __syncthreads();
+    if (cta == 0) {
+        float* keep = which == 0 ? a.xa : a.xb;
+        for (int i = tid; i < H; i += kMegaThreads) keep[i] = v.y[i];
+    }
+    if (which == 1 && cta == G - 1) {
+        const int n = (a.q_heads + 2 * a.kv_heads) * a.head_dim;
+        for (int i = tid; i < n; i += kMegaThreads) a.acc_qkv[i] = 0;  // consumed by the scores phase
+    }
+    const float s = mega_norm_quant(v.y, v.w, H, a.eps, v.a8, v.sh_d, v.sh_f);
+    if (tid == 0) v.scale[which == 0 ? 0 : 2] = s;
+    if (which == 0)
+        request_norm_weights(v.w, ly.ffn_norm, H);
+    else
+        request_norm_weights(v.w, l + 1 < a.n_layers ? v.layers[l + 1].attn_norm : a.out_norm, H);
+    prefetch_items(a, ly, which == 0 ? 1 : 3);
+    __syncthreads();
+}
+
+// Phase C1: scores, key rows shared out evenly over the CTAs; a spare CTA clears buffers that are idle now.
+__device__ __noinline__ void phase_scores(const MegaArgs& a, int l, unsigned char* smem) {
+    const MegaSmem v = mega_smem_views(smem, a);
+    const int tid = threadIdx.x, cta = blockIdx.x, G = gridDim.x;
+    const MegaLayer& ly = v.layers[l];
+    const KvSplit ks = kv_split(a);
+    int R = (a.kv_heads * ks.seq_len + G - 1) / G;
+    R = max(16, min(R, kAttnBlockPos));
+    const int per_head = (ks.seq_len + R - 1) / R;
+    const float s_h = v.scale[0];
+    for (int u = cta; u < a.kv_heads * per_head; u += G) {
+        const int kvh = u / per_head, r0 = (u - kvh * per_head) * R;
+        mega_scores_unit(a, ly, kvh, r0, min(R, ks.seq_len - r0), s_h, smem);
+    }
+    if (cta == G - 1) {
+        for (int i = tid; i < a.hidden; i += kMegaThreads) a.acc_down[i] = 0;  // read by every CTA in phase A, rewritten by down
+        if (tid == 0) a.amax_bits[(l + 1) & 1] = 0u;
+    }
+}
+
+// Phase C2: softmax factors and value accumulation per (KV head, chunk, 32-coordinate slice).
+__device__ __noinline__ void phase_values(const MegaArgs& a, int l, unsigned char* smem) {
+    const MegaSmem v = mega_smem_views(smem, a);
+    const int cta = blockIdx.x, G = gridDim.x;
+    const KvSplit ks = kv_split(a);
+    const int nchunks = ks.split ? 4 : 1, slices = a.head_dim / kAttnSlice;
+    for (int u = cta; u < a.kv_heads * nchunks * slices; u += G) {
+        const int slice = u % slices, c = (u / slices) % nchunks, kvh = u / (slices * nchunks);
+        mega_values_unit(a, v.layers[l], kvh, c, slice, smem);
+    }
+}
+
+// Phase D: combine the chunks of every head (attention.rs:497-541), int8 codes for the o projection.
+__device__ __noinline__ void phase_combine(const MegaArgs& a, unsigned char* smem) {
+    const MegaSmem v = mega_smem_views(smem, a);
+    const int tid = threadIdx.x, hd = a.head_dim, qd = a.q_heads * hd;
+    float* s_pair = v.pair;
+    const KvSplit ks = kv_split(a);
+    // per head: the factors of every chunk in the order of attention.rs:510-541. The running maximum before chunk c is
+    // the maximum of the earlier non-empty chunks, so the eight exponentials of a head are independent: one thread each.
+    if (!ks.split) {
+        if (tid < a.q_heads) {
+            const float S = __ldcg(a.part_ms + static_cast<size_t>(tid) * 8 + 1);
+            s_pair[tid * 8] = S == 0.0f ? 0.0f : __fdiv_rn(1.0f, S);
+        }
+    } else if (tid < a.q_heads * 8) {
+        const int h = tid >> 3, c = (tid >> 1) & 3, which = tid & 1;
+        float pm[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) pm[k] = __ldcg(a.part_ms + static_cast<size_t>(h) * 8 + k);
+        float m_before = -INFINITY;
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+            if (k < c && pm[2 * k + 1] != 0.0f) m_before = fmaxf(m_before, pm[2 * k]);
+        const float m_chunk = pm[2 * c], s_chunk = pm[2 * c + 1];
+        const float m_new = fmaxf(m_before, m_chunk);
+        float f = device_expf(__fsub_rn(which == 0 ? m_before : m_chunk, m_new));
+        if (s_chunk == 0.0f) f = which == 0 ? -1.0f : 0.0f;  // a negative scale_old marks a skipped chunk
+        s_pair[h * 8 + 2 * c + which] = f;                    // [c][0] = scale_old, [c][1] = scale_new
+        if (which == 0) s_pair[a.q_heads * 8 + h * 4 + c] = s_chunk;
+    }
+    // every chunk value of a thread's coordinates is requested before the factors are needed
+    float amax = 0.0f;
+    for (int base = 0; base < qd; base += 4 * kMegaThreads) {  // uniform trip count: the loop holds a barrier
+        const int i0 = base + tid;
+        float pv[4][4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int i = i0 + k * kMegaThreads;
+            const int h = i / hd, d = i - h * hd;
+            const float* pa = a.part_acc + static_cast<size_t>(h) * 4 * hd + d;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) pv[k][c] = (i < qd && (c == 0 || ks.split)) ? __ldcg(pa + c * hd) : 0.0f;
+        }
+        if (base == 0) __syncthreads();  // the factors are written
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int i = i0 + k * kMegaThreads;
+            if (i >= qd) continue;
+            const int h = i / hd;
+            const float* pr = s_pair + h * 8;
+            float out;
+            if (!ks.split) {
+                out = __fmul_rn(pv[k][0], pr[0]);
+            } else {
+                float acc = 0.0f, s_final = 0.0f;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    if (pr[2 * c] < 0.0f) continue;
+                    acc = __fmaf_rn(acc, pr[2 * c], __fmul_rn(pv[k][c], pr[2 * c + 1]));
+                    s_final = __fmaf_rn(s_final, pr[2 * c], __fmul_rn(s_pair[a.q_heads * 8 + h * 4 + c], pr[2 * c + 1]));
+                }
+                out = s_final != 0.0f ? __fmul_rn(acc, __fdiv_rn(1.0f, s_final)) : acc;
+            }
+            v.y[i] = out;
+            amax = fmaxf(amax, fabsf(out));
+        }
+    }
+    amax = block_max_f32(amax, v.sh_f);
+    const float s_q = amax > 0.0f ? __fdiv_rn(127.0f, amax) : 0.0f;
+    for (int i = tid; i < qd; i += kMegaThreads) v.a8[i] = static_cast<int8_t>(amax > 0.0f ? quantize_code(v.y[i], s_q) : 0);
+    if (tid == 0) v.scale[1] = s_q;
+    __syncthreads();
+}
+
+// Phase F1: SwiGLU on this CTA's slice of the intermediate vector, maximum of |v| for the down projection's scale.
+__device__ __noinline__ void phase_swiglu(const MegaArgs& a, int l, unsigned char* smem) {
+    const MegaSmem v = mega_smem_views(smem, a);
+    const int tid = threadIdx.x, cta = blockIdx.x, G = gridDim.x, I = a.inter;
+    const MegaLayer& ly = v.layers[l];
+    const float s_f = v.scale[2];
+    const float pg = s_f > 0.0f ? __fdiv_rn(ly.ws[4], s_f) : 0.0f, pu = s_f > 0.0f ? __fdiv_rn(ly.ws[5], s_f) : 0.0f;
+    float m = 0.0f;
+    for (int i0 = cta * kMegaThreads + tid; i0 < I; i0 += 2 * G * kMegaThreads) {
+        const int i1 = i0 + G * kMegaThreads;
+        const int g0 = __ldcg(a.acc_gu + i0), u0 = __ldcg(a.acc_gu + I + i0);
+        const int g1 = i1 < I ? __ldcg(a.acc_gu + i1) : 0, u1 = i1 < I ? __ldcg(a.acc_gu + I + i1) : 0;
+        {
+            const float g = s_f > 0.0f ? __fmul_rn(static_cast<float>(g0), pg) : 0.0f, u = s_f > 0.0f ? __fmul_rn(static_cast<float>(u0), pu) : 0.0f;
+            const float x = __fmul_rn(ggml_silu(g), u);
+            a.v_inter[i0] = x;
+            m = fmaxf(m, fabsf(x));
+        }
+        if (i1 < I) {
+            const float g = s_f > 0.0f ? __fmul_rn(static_cast<float>(g1), pg) : 0.0f, u = s_f > 0.0f ? __fmul_rn(static_cast<float>(u1), pu) : 0.0f;
+            const float x = __fmul_rn(ggml_silu(g), u);
+            a.v_inter[i1] = x;
+            m = fmaxf(m, fabsf(x));
+        }
+    }
+    m = block_max_f32(m, v.sh_f);
+    if (tid == 0 && m > 0.0f) atomicMax(a.amax_bits + (l & 1), __float_as_uint(m));  // non-negative floats order like their bits
+    if (cta == G - 1)
+        for (int i = tid; i < a.hidden; i += kMegaThreads) a.acc_o[i] = 0;  // consumed in phase E
+}
+
+// Final norm (model.rs:326-331), output head, greedy candidate of this CTA.
+__device__ __noinline__ void phase_head(const MegaArgs& a, unsigned char* smem) {
+    const MegaSmem v = mega_smem_views(smem, a);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, cta = blockIdx.x, G = gridDim.x, H = a.hidden;
+    float* y_s = v.y;
+    {
+        const float s_prev = v.scale[3];
+        const float post = s_prev > 0.0f ? __fdiv_rn(v.layers[a.n_layers - 1].ws[6], s_prev) : 0.0f;
+        residual_add(y_s, a.xb, a.acc_down, post, s_prev > 0.0f, H);
+    }
+    cp_async_wait<0>();
+    __syncthreads();
+    mega_norm_quant(y_s, v.w, H, a.eps, nullptr, v.sh_d, v.sh_f);
+    for (int i = tid; i < H; i += kMegaThreads) y_s[i] = __half2float(__float2half_rn(y_s[i]));  // model.rs:347-349
+    __syncthreads();
+    float bv = -INFINITY;
+    unsigned int bi = 0xFFFFFFFFu;
+    const int np = H & ~31;
+    // Every warp walks its rows in segments of kHeadSeg halves that arrive through a private ring of shared-memory
+    // buffers (asynchronous copies, three segments ahead); the table is not needed any more and gives up its space.
+    constexpr int kHeadSeg = 1024, kHeadStages = 4;
+    __half* ring = reinterpret_cast<__half*>(smem) + warp * kHeadStages * kHeadSeg;
+    const int nseg = (np + kHeadSeg - 1) / kHeadSeg;
+    const int first_row = cta * kMegaWarps + warp, row_stride = G * kMegaWarps;
+    const int nrows = first_row < a.vocab ? (a.vocab - first_row + row_stride - 1) / row_stride : 0;
+    const int total = nrows * nseg;
+    auto issue = [&](int q) {
+        if (q < total) {
+            const int row = first_row + (q / nseg) * row_stride, sg = q % nseg;
+            const __half* src = a.lm_head + static_cast<size_t>(row) * H + sg * kHeadSeg;
+            __half* dst = ring + (q % kHeadStages) * kHeadSeg;
+            const int nvec = min(kHeadSeg, np - sg * kHeadSeg) / 8;
+            for (int x = lane; x < nvec; x += 32) cp_async16(dst + x * 8, src + x * 8);
+        }
+        cp_async_commit();
+    };
+    for (int q = 0; q < kHeadStages - 1; ++q) issue(q);
+    float acc = 0.0f;
+    for (int q = 0; q < total; ++q) {
+        issue(q + kHeadStages - 1);
+        cp_async_wait<kHeadStages - 1>();
+        __syncwarp();
+        const int sg = q % nseg;
+        const __half* buf = ring + (q % kHeadStages) * kHeadSeg;
+        const float* xs = y_s + sg * kHeadSeg;
+        const int cnt = min(kHeadSeg, np - sg * kHeadSeg);
+#pragma unroll 8
+        for (int i = 0; i < cnt; i += 32) acc = __fmaf_rn(xs[i + lane], __half2float(buf[i + lane]), acc);
+        if (sg == nseg - 1) {
+            const int row = first_row + (q / nseg) * row_stride;
+            float sum = dot_lane_reduce_f16(acc);
+            if (lane == 0) {
+                const __half* wr = a.lm_head + static_cast<size_t>(row) * H;
+                for (int i = np; i < H; ++i) sum = __fadd_rn(sum, __fmul_rn(y_s[i], __half2float(wr[i])));
+                a.logits[row] = sum;
+                argmax_merge(bv, bi, sum, static_cast<unsigned int>(row));
+            }
+            acc = 0.0f;
+        }
+        __syncwarp();  // the buffer is refilled three segments later
+    }
+    cp_async_wait<0>();
+    __syncthreads();
+    float* s_bv = v.sh_f;  // 32 floats: one candidate per warp
+    unsigned int* s_bi = reinterpret_cast<unsigned int*>(v.sh_d);
+    if (lane == 0) {
+        s_bv[warp] = bv;
+        s_bi[warp] = bi;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        for (int w = 1; w < kMegaWarps; ++w) argmax_merge(bv, bi, s_bv[w], s_bi[w]);
+        a.best_val[cta] = bv;
+        a.best_idx[cta] = bi;
+    }
+}
+
+// Last step, CTA 0 after the final barrier: the greedy token (lowest index among equal maxima), position advance, clean-up.
+__device__ __noinline__ void phase_finish(const MegaArgs& a) {
+    const int tid = threadIdx.x, G = gridDim.x;
+    for (int i = tid; i < a.hidden; i += kMegaThreads) a.acc_down[i] = 0;
+    if (tid == 0) {
+        float bv = -INFINITY;
+        unsigned int bi = 0xFFFFFFFFu;
+        for (int c = 0; c < G; ++c) argmax_merge(bv, bi, __ldcg(a.best_val + c), __ldcg(a.best_idx + c));
+        const uint32_t tok = bi == 0xFFFFFFFFu ? 0u : bi;
+        a.token[0] = tok;
+        a.history[a.pos[0]] = tok;
+        a.pos[0] += 1;
+        a.amax_bits[0] = 0u;
+        a.amax_bits[1] = 0u;
+    }
+}
+
+template <uint32_t BASE>
+__global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const __grid_constant__ MegaArgs a) {
+    extern __shared__ __align__(1024) unsigned char smem[];
+    const int tid = threadIdx.x, cta = blockIdx.x, G = gridDim.x;
     if (static_cast<uint32_t>(__cvta_generic_to_shared(smem)) != BASE) {
         if (tid == 0) atomicMax(a.status, 1u);
         return;
     }
-    for (int i = tid; i < 13 * 64; i += kMegaThreads) {
-        const int k = i >> 6;
-        tab[(k < 9 ? 28 * k + 27 : 243 + k) * 64 + (i & 63)] = 0;
+    {
+        const MegaSmem v = mega_smem_views(smem, a);
+        for (int i = tid; i < 13 * 64; i += kMegaThreads) {  // byte values that are no velurex code look up zero
+            const int k = i >> 6;
+            v.tab[(k < 9 ? 28 * k + 27 : 243 + k) * 64 + (i & 63)] = 0;
+        }
+        request_norm_weights(v.w, a.n_layers > 0 ? a.layers[0].attn_norm : a.out_norm, a.hidden);
+        for (int i = tid; i < a.n_layers * static_cast<int>(sizeof(MegaLayer) / 4); i += kMegaThreads)
+            reinterpret_cast<uint32_t*>(v.layers)[i] = reinterpret_cast<const uint32_t*>(a.layers)[i];
+        if (tid < 4) v.scale[tid] = 0.0f;
+        __syncthreads();
     }
-    const int H = a.hidden, I = a.inter, hd = a.head_dim, qd = a.q_heads * hd, kvd = a.kv_heads * hd;
-    request_norm_weights(w_s, a.layers != nullptr && a.n_layers > 0 ? a.layers[0].attn_norm : a.out_norm, H);
-    for (int i = tid; i < a.n_layers * static_cast<int>(sizeof(MegaLayer) / 4); i += kMegaThreads)
-        reinterpret_cast<uint32_t*>(s_layers)[i] = reinterpret_cast<const uint32_t*>(a.layers)[i];
-    __syncthreads();
     unsigned int bar_target = 0;
-#define MEGA_BARRIER()                                                   \
-    do {                                                                 \
-        bar_target += static_cast<unsigned int>(G);                      \
-        if (!grid_barrier(a.bar, bar_target, a.status, s_flag)) return;  \
+#define MEGA_BARRIER()                                                                                   \
+    do {                                                                                                 \
+        bar_target += static_cast<unsigned int>(G);                                                      \
+        if (!grid_barrier(a.bar, bar_target, a.status, mega_smem_views(smem, a).flag)) return;           \
     } while (0)
-
     int trace_n = 0;
-#define MEGA_TRACE()                                                                       \
-    do {                                                                                   \
+#define MEGA_TRACE()                                                                            \
+    do {                                                                                        \
         if (a.trace != nullptr && cta == 0 && tid == 0) a.trace[trace_n++] = global_timer_ns(); \
     } while (0)
+#define MEGA_GEMV(k, acts, actf, qs, out)                                                                                        \
+    do {                                                                                                                         \
+        const MegaSmem v = mega_smem_views(smem, a);                                                                             \
+        mega_gemv<BASE>(a.items, v.layers[l].first[k], v.layers[l].count[k], v.tab, acts, actf, qs, out);                         \
+    } while (0)
     MEGA_TRACE();
-    float s_down_prev = 0.0f;  // activation scale of the previous layer's down projection
     for (int l = 0; l < a.n_layers; ++l) {
-        const MegaLayer& ly = s_layers[l];
-        // ---- phase A: residual (or embedding), norm, quantise, q|k|v ----
-        if (tid < 2 && cta + tid * G < ly.count[0]) prefetch_l2(a.items + ly.first[0] + cta + tid * G);
-        if (l == 0) {
-            const size_t base = static_cast<size_t>(a.token[0]) * H;
-            for (int i = tid; i < H; i += kMegaThreads) y_s[i] = __half2float(a.embed[base + i]);
-        } else {
-            const float post = s_down_prev > 0.0f ? __fdiv_rn(s_layers[l - 1].ws[6], s_down_prev) : 0.0f;
-            residual_add(y_s, a.xb, a.acc_down, post, s_down_prev > 0.0f, H);
-        }
-        cp_async_wait<0>();  // the norm weights requested one phase ago
-        __syncthreads();
-        if (cta == 0)
-            for (int i = tid; i < H; i += kMegaThreads) a.xa[i] = y_s[i];
-        const float s_h = mega_norm_quant(y_s, w_s, H, a.eps, a8, sh_d, sh_f);
-        request_norm_weights(w_s, ly.ffn_norm, H);
-        if (tid < 2 && cta + tid * G < ly.count[1]) prefetch_l2(a.items + ly.first[1] + cta + tid * G);
+        phase_norm(a, l, 0, smem);
         MEGA_TRACE();  // 1: norm done
-        mega_gemv<BASE>(a.items, ly.first[0], ly.count[0], tab, a8, nullptr, 0.0f, a.acc_qkv);
+        MEGA_GEMV(0, v.a8, nullptr, 0.0f, a.acc_qkv);
         MEGA_TRACE();  // 2: q|k|v streamed (this CTA)
         MEGA_BARRIER();
         MEGA_TRACE();  // 3
-        // ---- phase C: attention units; spare CTAs clear buffers that are idle now ----
-        for (int u = cta; u < a.q_heads * 4; u += G) mega_attention_unit(a, ly, u >> 2, u & 3, s_h, smem);
-        if (cta == G - 1) {
-            for (int i = tid; i < H; i += kMegaThreads) a.acc_down[i] = 0;  // read by every CTA in phase A, rewritten in F2
-            if (tid == 0) a.amax_bits[(l + 1) & 1] = 0u;
-        }
-        MEGA_TRACE();  // 4: attention unit done (this CTA)
+        phase_scores(a, l, smem);
+        MEGA_TRACE();  // 4: scores done (this CTA)
         MEGA_BARRIER();
-        MEGA_TRACE();  // 5
-        // ---- phase D: combine the chunks, quantise, o ----
-        {
-            const int pos = static_cast<int>(a.pos[0]), seq_len = pos + 1;
-            int n_kv = (seq_len + 255) / 256 * 256;
-            if (n_kv < 256) n_kv = 256;
-            if (n_kv > a.ctx) n_kv = a.ctx;
-            // per head: the factors of every chunk in the order of attention.rs:510-541. The running maximum before chunk c is
-            // the maximum of the earlier non-empty chunks, so the eight exponentials of a head are independent: one thread each.
-            if (n_kv < 512) {
-                if (tid < a.q_heads) {
-                    const float S = __ldcg(a.part_ms + static_cast<size_t>(tid) * 8 + 1);
-                    s_pair[tid * 8] = S == 0.0f ? 0.0f : __fdiv_rn(1.0f, S);
-                }
-            } else if (tid < a.q_heads * 8) {
-                const int h = tid >> 3, c = (tid >> 1) & 3, which = tid & 1;
-                float pm[8];
-#pragma unroll
-                for (int k = 0; k < 8; ++k) pm[k] = __ldcg(a.part_ms + static_cast<size_t>(h) * 8 + k);
-                float m_before = -INFINITY;
-#pragma unroll
-                for (int k = 0; k < 4; ++k)
-                    if (k < c && pm[2 * k + 1] != 0.0f) m_before = fmaxf(m_before, pm[2 * k]);
-                const float m_chunk = pm[2 * c], s_chunk = pm[2 * c + 1];
-                const float m_new = fmaxf(m_before, m_chunk);
-                float f = device_expf(__fsub_rn(which == 0 ? m_before : m_chunk, m_new));
-                if (s_chunk == 0.0f) f = which == 0 ? -1.0f : 0.0f;  // a negative scale_old marks a skipped chunk
-                s_pair[h * 8 + 2 * c + which] = f;                    // [c][0] = scale_old, [c][1] = scale_new
-                if (which == 0) s_pair[a.q_heads * 8 + h * 4 + c] = s_chunk;
-            }
-            __syncthreads();
-            // every chunk value of a thread's coordinates is requested before the first is used
-            for (int i0 = tid; i0 < qd; i0 += 4 * kMegaThreads) {
-                float pv[4][4];
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    const int i = i0 + k * kMegaThreads;
-                    const int h = i / hd, d = i - h * hd;
-                    const float* pa = a.part_acc + static_cast<size_t>(h) * 4 * hd + d;
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) pv[k][c] = (i < qd && (c == 0 || n_kv >= 512)) ? __ldcg(pa + c * hd) : 0.0f;
-                }
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    const int i = i0 + k * kMegaThreads;
-                    if (i >= qd) continue;
-                    const int h = i / hd;
-                    const float* pr = s_pair + h * 8;
-                    float out;
-                    if (n_kv < 512) {
-                        out = __fmul_rn(pv[k][0], pr[0]);
-                    } else {
-                        float acc = 0.0f, s_final = 0.0f;
-#pragma unroll
-                        for (int c = 0; c < 4; ++c) {
-                            if (pr[2 * c] < 0.0f) continue;
-                            acc = __fmaf_rn(acc, pr[2 * c], __fmul_rn(pv[k][c], pr[2 * c + 1]));
-                            s_final = __fmaf_rn(s_final, pr[2 * c], __fmul_rn(s_pair[a.q_heads * 8 + h * 4 + c], pr[2 * c + 1]));
-                        }
-                        out = s_final != 0.0f ? __fmul_rn(acc, __fdiv_rn(1.0f, s_final)) : acc;
-                    }
-                    y_s[i] = out;
-                }
-            }
-            __syncthreads();
-        }
-        float amax = 0.0f;
-        for (int i = tid; i < qd; i += kMegaThreads) amax = fmaxf(amax, fabsf(y_s[i]));
-        amax = block_max_f32(amax, sh_f);
-        const float s_q = amax > 0.0f ? __fdiv_rn(127.0f, amax) : 0.0f;
-        for (int i = tid; i < qd; i += kMegaThreads) a8[i] = static_cast<int8_t>(amax > 0.0f ? quantize_code(y_s[i], s_q) : 0);
-        __syncthreads();
-        MEGA_TRACE();  // 6: combine + quantise done
-        mega_gemv<BASE>(a.items, ly.first[1], ly.count[1], tab, a8, nullptr, 0.0f, a.acc_o);
+        phase_values(a, l, smem);
+        MEGA_TRACE();  // 5: values done (this CTA)
         MEGA_BARRIER();
-        MEGA_TRACE();  // 7
-        // ---- phase E: residual, norm, quantise, gate|up ----
-        {
-            const float post = s_q > 0.0f ? __fdiv_rn(ly.ws[3], s_q) : 0.0f;
-            residual_add(y_s, a.xa, a.acc_o, post, s_q > 0.0f, H);
-            cp_async_wait<0>();  // the norm weights requested in phase A
-            __syncthreads();
-            if (cta == 0)
-                for (int i = tid; i < H; i += kMegaThreads) a.xb[i] = y_s[i];
-            if (cta == G - 1)
-                for (int i = tid; i < qd + 2 * kvd; i += kMegaThreads) a.acc_qkv[i] = 0;  // consumed in phase C
-        }
-        if (tid < 2 && cta + tid * G < ly.count[2]) prefetch_l2(a.items + ly.first[2] + cta + tid * G);
-        const float s_f = mega_norm_quant(y_s, w_s, H, a.eps, a8, sh_d, sh_f);
-        request_norm_weights(w_s, l + 1 < a.n_layers ? s_layers[l + 1].attn_norm : a.out_norm, H);
-        if (tid < 2 && cta + tid * G < ly.count[3]) prefetch_l2(a.items + ly.first[3] + cta + tid * G);
-        MEGA_TRACE();  // 8: norm done
-        mega_gemv<BASE>(a.items, ly.first[2], ly.count[2], tab, a8, nullptr, 0.0f, a.acc_gu);
-        MEGA_TRACE();  // 9: gate|up streamed (this CTA)
+        MEGA_TRACE();  // 6
+        phase_combine(a, smem);
+        MEGA_TRACE();  // 7: combine + quantise done
+        MEGA_GEMV(1, v.a8, nullptr, 0.0f, a.acc_o);
         MEGA_BARRIER();
-        MEGA_TRACE();  // 10
-        // ---- phase F1: SwiGLU on a slice, maximum of |v| ----
-        {
-            const float pg = s_f > 0.0f ? __fdiv_rn(ly.ws[4], s_f) : 0.0f, pu = s_f > 0.0f ? __fdiv_rn(ly.ws[5], s_f) : 0.0f;
-            float m = 0.0f;
-            for (int i = cta * kMegaThreads + tid; i < I; i += G * kMegaThreads) {
-                const float g = s_f > 0.0f ? __fmul_rn(static_cast<float>(a.acc_gu[i]), pg) : 0.0f;
-                const float u = s_f > 0.0f ? __fmul_rn(static_cast<float>(a.acc_gu[I + i]), pu) : 0.0f;
-                const float v = __fmul_rn(ggml_silu(g), u);
-                a.v_inter[i] = v;
-                m = fmaxf(m, fabsf(v));
-            }
-            m = block_max_f32(m, sh_f);
-            if (tid == 0 && m > 0.0f) atomicMax(a.amax_bits + (l & 1), __float_as_uint(m));  // non-negative floats order like their bits
-            if (cta == G - 1)
-                for (int i = tid; i < H; i += kMegaThreads) a.acc_o[i] = 0;  // consumed in phase E
-        }
+        MEGA_TRACE();  // 8
+        phase_norm(a, l, 1, smem);
+        MEGA_TRACE();  // 9: norm done
+        MEGA_GEMV(2, v.a8, nullptr, 0.0f, a.acc_gu);
+        MEGA_TRACE();  // 10: gate|up streamed (this CTA)
         MEGA_BARRIER();
         MEGA_TRACE();  // 11
-        // ---- phase F2: down, quantising v on the fly ----
+        phase_swiglu(a, l, smem);
+        MEGA_BARRIER();
+        MEGA_TRACE();  // 12
         {
-            const float vmax = __uint_as_float(*reinterpret_cast<volatile unsigned int*>(a.amax_bits + (l & 1)));
-            s_down_prev = vmax > 0.0f ? __fdiv_rn(127.0f, vmax) : 0.0f;
-            mega_gemv<BASE>(a.items, ly.first[3], ly.count[3], tab, nullptr, a.v_inter, s_down_prev, a.acc_down);
-            MEGA_TRACE();  // 12: down streamed (this CTA)
-            for (int i = cta * kMegaThreads + tid; i < 2 * I; i += G * kMegaThreads) a.acc_gu[i] = 0;  // consumed in phase F1
+            // down, quantising v on the fly with the scale from the maximum every CTA contributed to
+            const float vmax = __uint_as_float(__ldcg(a.amax_bits + (l & 1)));
+            const float s_down = vmax > 0.0f ? __fdiv_rn(127.0f, vmax) : 0.0f;
+            if (tid == 0) mega_smem_views(smem, a).scale[3] = s_down;
+            MEGA_GEMV(3, nullptr, a.v_inter, s_down, a.acc_down);
+            MEGA_TRACE();  // 13: down streamed (this CTA)
+            for (int i = cta * kMegaThreads + tid; i < 2 * a.inter; i += G * kMegaThreads) a.acc_gu[i] = 0;  // consumed by SwiGLU
         }
         MEGA_BARRIER();
-        MEGA_TRACE();  // 13 = 0 of the next layer
+        MEGA_TRACE();  // 14 = 0 of the next layer
     }
-    // ---- final norm (model.rs:326-331), output head, greedy choice ----
-    {
-        const float post = s_down_prev > 0.0f ? __fdiv_rn(s_layers[a.n_layers - 1].ws[6], s_down_prev) : 0.0f;
-        residual_add(y_s, a.xb, a.acc_down, post, s_down_prev > 0.0f, H);
-        cp_async_wait<0>();
-        __syncthreads();
-        mega_norm_quant(y_s, w_s, H, a.eps, nullptr, sh_d, sh_f);
-        for (int i = tid; i < H; i += kMegaThreads) y_s[i] = __half2float(__float2half_rn(y_s[i]));  // model.rs:347-349
-        __syncthreads();
-        float bv = -INFINITY;
-        unsigned int bi = 0xFFFFFFFFu;
-        const int np = H & ~31;
-        // Every warp walks its rows in segments of kHeadSeg halves that arrive through a private ring of shared-memory
-        // buffers (asynchronous copies, three segments ahead); the table is not needed any more and gives up its space.
-        constexpr int kHeadSeg = 1024, kHeadStages = 4;
-        __half* ring = reinterpret_cast<__half*>(smem) + warp * kHeadStages * kHeadSeg;
-        const int nseg = (np + kHeadSeg - 1) / kHeadSeg;
-        const int first_row = cta * kMegaWarps + warp, row_stride = G * kMegaWarps;
-        const int nrows = first_row < a.vocab ? (a.vocab - first_row + row_stride - 1) / row_stride : 0;
-        const int total = nrows * nseg;
-        auto issue = [&](int q) {
-            if (q < total) {
-                const int row = first_row + (q / nseg) * row_stride, sg = q % nseg;
-                const __half* src = a.lm_head + static_cast<size_t>(row) * H + sg * kHeadSeg;
-                __half* dst = ring + (q % kHeadStages) * kHeadSeg;
-                const int nvec = min(kHeadSeg, np - sg * kHeadSeg) / 8;
-                for (int v = lane; v < nvec; v += 32) cp_async16(dst + v * 8, src + v * 8);
-            }
-            cp_async_commit();
-        };
-        __syncthreads();  // every warp is done with the table and the scratch
-        for (int q = 0; q < kHeadStages - 1; ++q) issue(q);
-        float acc = 0.0f;
-        for (int q = 0; q < total; ++q) {
-            issue(q + kHeadStages - 1);
-            cp_async_wait<kHeadStages - 1>();
-            __syncwarp();
-            const int sg = q % nseg;
-            const __half* buf = ring + (q % kHeadStages) * kHeadSeg;
-            const float* xs = y_s + sg * kHeadSeg;
-            const int cnt = min(kHeadSeg, np - sg * kHeadSeg);
-#pragma unroll 8
-            for (int i = 0; i < cnt; i += 32) acc = __fmaf_rn(xs[i + lane], __half2float(buf[i + lane]), acc);
-            if (sg == nseg - 1) {
-                const int row = first_row + (q / nseg) * row_stride;
-                float sum = dot_lane_reduce_f16(acc);
-                if (lane == 0) {
-                    const __half* wr = a.lm_head + static_cast<size_t>(row) * H;
-                    for (int i = np; i < H; ++i) sum = __fadd_rn(sum, __fmul_rn(y_s[i], __half2float(wr[i])));
-                    a.logits[row] = sum;
-                    argmax_merge(bv, bi, sum, static_cast<unsigned int>(row));
-                }
-                acc = 0.0f;
-            }
-            __syncwarp();  // the buffer is refilled three segments later
-        }
-        cp_async_wait<0>();
-        __syncthreads();
-        float* s_bv = reinterpret_cast<float*>(attn_scratch);
-        unsigned int* s_bi = reinterpret_cast<unsigned int*>(attn_scratch + 256);
-        if (lane == 0) {
-            s_bv[warp] = bv;
-            s_bi[warp] = bi;
-        }
-        __syncthreads();
-        if (tid == 0) {
-            for (int w = 1; w < kMegaWarps; ++w) argmax_merge(bv, bi, s_bv[w], s_bi[w]);
-            a.best_val[cta] = bv;
-            a.best_idx[cta] = bi;
-        }
-    }
+    phase_head(a, smem);
     MEGA_TRACE();  // head done (this CTA)
     MEGA_BARRIER();
     MEGA_TRACE();
-    if (cta == 0) {
-        for (int i = tid; i < H; i += kMegaThreads) a.acc_down[i] = 0;
-        if (tid == 0) {
-            float bv = -INFINITY;
-            unsigned int bi = 0xFFFFFFFFu;
-            for (int c = 0; c < G; ++c) argmax_merge(bv, bi, *reinterpret_cast<volatile float*>(a.best_val + c), *reinterpret_cast<volatile unsigned int*>(a.best_idx + c));
-            const uint32_t tok = bi == 0xFFFFFFFFu ? 0u : bi;
-            a.token[0] = tok;
-            a.history[a.pos[0]] = tok;
-            a.pos[0] += 1;
-            a.amax_bits[0] = 0u;
-            a.amax_bits[1] = 0u;
-        }
-    }
+    if (cta == 0) phase_finish(a);
+#undef MEGA_GEMV
 #undef MEGA_BARRIER
 #undef MEGA_TRACE
 }
