@@ -217,7 +217,8 @@ int quintrit_b200_decoder_time_token(quintrit_b200_decoder_t* decoder, uint32_t 
  * decode step like quintrit_b200_decoder_time_token and returns the device's global timer (ns) as sampled by CTA 0 at
  * every phase boundary of the single-kernel path: 14 stamps per layer (norm, q|k|v, barrier, scores, barrier + values,
  * barrier, combine, o + barrier, norm, gate|up, barrier, SwiGLU + barrier, down, barrier) after one at the start, then two
- * around the output head. *out_count receives the number of stamps (also on QUINTRIT_ERR_BUFFER_TOO_SMALL).
+ * around the output head, then 32 slots that stay zero unless the library was built with -DQTB_FINE_TRACE (stamps inside
+ * phases). *out_count receives the number of values (also on QUINTRIT_ERR_BUFFER_TOO_SMALL).
  */
 int quintrit_b200_decoder_trace_step(quintrit_b200_decoder_t* decoder, uint64_t* out_ns, size_t capacity, size_t* out_count);
 

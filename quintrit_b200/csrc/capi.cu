@@ -808,7 +808,7 @@ int mega_setup(quintrit_b200_decoder* d, const quintrit_b200_decoder_desc_t* des
     if ((rc = dev_alloc(d, &d->xa, H)) != QUINTRIT_OK || (rc = dev_alloc(d, &d->xb, H)) != QUINTRIT_OK ||
         (rc = dev_alloc(d, &d->v_inter, I)) != QUINTRIT_OK || (rc = dev_alloc(d, &d->amax_bits, 4)) != QUINTRIT_OK ||
         (rc = dev_alloc(d, &d->best_val, d->sm_count)) != QUINTRIT_OK || (rc = dev_alloc(d, &d->best_idx, d->sm_count)) != QUINTRIT_OK ||
-        (rc = dev_alloc(d, &d->bar, 4)) != QUINTRIT_OK || (rc = dev_alloc(d, &d->trace, size_t(L) * 14 + 8)) != QUINTRIT_OK ||
+        (rc = dev_alloc(d, &d->bar, 4)) != QUINTRIT_OK || (rc = dev_alloc(d, &d->trace, size_t(L) * 14 + 4 + 32)) != QUINTRIT_OK ||
         (rc = dev_alloc(d, &d->scores, size_t(d->q_heads) * d->ctx)) != QUINTRIT_OK)
         return rc;
     std::vector<GemvItem> items;
@@ -1132,7 +1132,7 @@ extern "C" int quintrit_b200_decoder_trace_step(quintrit_b200_decoder_t* decoder
         quintrit_b200_decoder* d = decoder;
         if (out_count == nullptr) return fail(QUINTRIT_ERR_NULL_POINTER, "out_count is NULL");
         if (!d->use_mega) return fail(QUINTRIT_ERR_UNSUPPORTED, "phase tracing is available for the single-kernel decode path only");
-        const size_t n = size_t(d->layers) * 14 + 4;
+        const size_t n = size_t(d->layers) * 14 + 4 + 32;  // phase stamps, then 32 optional fine stamps (zero unless built with QTB_FINE_TRACE)
         *out_count = n;
         if (out_ns == nullptr || capacity < n) return fail(QUINTRIT_ERR_BUFFER_TOO_SMALL, "out_ns holds %zu values, %zu are needed", capacity, n);
         if (d->host_pos >= static_cast<uint32_t>(d->ctx)) return fail(QUINTRIT_ERR_CONTEXT_OVERFLOW, "the context window is full");

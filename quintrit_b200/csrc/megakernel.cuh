@@ -69,6 +69,20 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
     return t;
 }
 
+// Optional fine-grained stamps for investigations (-DQTB_FINE_TRACE): CTA 0 stores the global timer in one of 32 extra slots
+// behind the phase stamps (every layer overwrites them, so the last layer's remain). Compiled out otherwise.
+#ifdef QTB_FINE_TRACE
+#define QTB_FINE(a, k)                                                                         \
+    do {                                                                                       \
+        if ((a).trace != nullptr && blockIdx.x == 0 && threadIdx.x == 0 && (k) < 32)           \
+            (a).trace[(a).n_layers * 14 + 4 + (k)] = global_timer_ns();                        \
+    } while (0)
+#else
+#define QTB_FINE(a, k) \
+    do {               \
+    } while (0)
+#endif
+
 // Grid-wide barrier with a bounded wait. Returns false (in every thread of the CTA) if it gave up.
 __device__ __forceinline__ bool grid_barrier(unsigned int* bar, unsigned int target, unsigned int* status, int* s_flag) {
     __syncthreads();
@@ -316,39 +330,54 @@ __device__ __forceinline__ float key_score(const unsigned char* buf, int r, int 
     return __fadd_rn(__fadd_rn(acc[0], acc[1]), __fadd_rn(acc[2], acc[3]));
 }
 
-// One staged run of the value accumulation for one coordinate (attention.rs:448-470): n positions in order, the value of
-// position r at col[r * stride], factors ms[r] / vs[r]. The running sum is rounded to half precision after every
-// operation unless F32. Groups of eight positions are fetched into registers first; a group whose rescale factors are
-// all 1 (every group but the few where the running maximum moved) runs the bare multiply-add chain. Kept small: the
-// registers of a call chain add up (kernel + phase + unit + this), and beyond the budget every function of the kernel spills.
+// One staged run of the value accumulation for one coordinate (attention.rs:448-470): n positions in order (n starts on a
+// multiple of 8 positions of the chunk), the value of position r at col[r * stride], factors ms[r] / vs[r]. The running
+// sum is rounded to half precision after every operation unless F32. Arguments are byte offsets into the dynamic shared
+// memory. Kept small on purpose: the registers of a call chain (kernel + phase + unit + this) add up, and beyond the
+// budget of 128 every function of the kernel starts to spill.
+// The dynamic shared memory of the CTA as the compiler knows it (shared state space, 32-bit addressing): loads through a
+// pointer that came in as a function argument are generic loads, which cost registers and latency in the chains below.
+__device__ __forceinline__ unsigned char* dyn_smem() {
+    extern __shared__ __align__(1024) unsigned char dyn_smem_base[];
+    return dyn_smem_base;
+}
+
 template <bool F32>
-__device__ __noinline__ float value_chain(const __half* col, int stride, const float* ms, const float* vs, int n, float acc) {
+__device__ __noinline__ float value_chain(uint32_t col_off, int stride, uint32_t ms_off, uint32_t vs_off, uint32_t next_off, int g0, int n, float acc) {
     auto rnd = [](float x) { return F32 ? x : __half2float(__float2half_rn(x)); };
-    int r = 0;
-    for (; r + 8 <= n; r += 8) {
-        float m[8], w[8], v[8];
-        bool moved = false;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            m[j] = ms[r + j];
-            w[j] = vs[r + j];
-            v[j] = __half2float(col[(r + j) * stride]);
-            moved |= m[j] != 1.0f;
-        }
-        if (!moved) {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) acc = rnd(__fmaf_rn(v[j], w[j], acc));
-        } else {
+    unsigned char* base = dyn_smem();
+    const __half* col = reinterpret_cast<const __half*>(base + col_off);
+    const float* ms = reinterpret_cast<const float*>(base + ms_off);
+    const float* vs = reinterpret_cast<const float*>(base + vs_off);
+    const unsigned short* next = reinterpret_cast<const unsigned short*>(base + next_off);
+    // `next` holds, for every group of 8 positions from the first one of this run, the index (relative to the chunk's first
+    // group, like g0) of the first group at or after it whose running maximum moved. Up to there the loop is branch-free,
+    // so the loads of later groups overlap the dependent steps of earlier ones.
+    const int full = n >> 3;
+    int grp = 0;
+    while (grp < full) {
+        const int e = min(static_cast<int>(next[grp]) - g0, full);
+        for (; grp < e; ++grp) {
+            float w[8], v[8];
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
-                if (m[j] != 1.0f) acc = rnd(__fmul_rn(acc, m[j]));
-                acc = rnd(__fmaf_rn(v[j], w[j], acc));
+                w[j] = vs[grp * 8 + j];
+                v[j] = __half2float(col[(grp * 8 + j) * stride]);
             }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc = rnd(__fmaf_rn(v[j], w[j], acc));
+        }
+        if (grp < full) {  // ms = 1 leaves the sum unchanged bit for bit, so the reference's test for it needs no branch
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                acc = rnd(__fmul_rn(acc, ms[grp * 8 + j]));
+                acc = rnd(__fmaf_rn(__half2float(col[(grp * 8 + j) * stride]), vs[grp * 8 + j], acc));
+            }
+            ++grp;
         }
     }
-    for (; r < n; ++r) {
-        const float mr = ms[r];
-        if (mr != 1.0f) acc = rnd(__fmul_rn(acc, mr));
+    for (int r = full * 8; r < n; ++r) {
+        acc = rnd(__fmul_rn(acc, ms[r]));
         acc = rnd(__fmaf_rn(__half2float(col[r * stride]), vs[r], acc));
     }
     return acc;
@@ -459,7 +488,8 @@ constexpr int kAttnSlice = 32;  // coordinates of a head that one values unit ac
 
 // Shared memory a values unit needs for chunks of `len` positions and `gqa` query heads per KV head.
 __host__ __device__ constexpr size_t values_unit_bytes(int len, int gqa) {
-    return (static_cast<size_t>(len) * kAttnSlice * 2 + 15) / 16 * 16 + static_cast<size_t>(2) * gqa * len * 4 + (kMegaWarps + 16) * 4;
+    return (static_cast<size_t>(len) * kAttnSlice * 2 + 15) / 16 * 16 + static_cast<size_t>(2) * gqa * len * 4 + (kMegaWarps + 16) * 4 +
+           (static_cast<size_t>(gqa) * ((len + 7) / 8 + 1) * 3 + 15) / 16 * 16;
 }
 
 // Attention, second half: for one KV head, one chunk of positions and one slice of 32 coordinates, the softmax factors of
@@ -492,6 +522,9 @@ __device__ __noinline__ void mega_values_unit(const MegaArgs& a, const MegaLayer
     float* f_vs = f_ms + gqa * len;                                                   // [gqa][len]: scores, then vs
     float* s_tm = f_vs + gqa * len;                                                   // kMegaWarps floats
     float* s_M = s_tm + kMegaWarps;                                                   // up to 16 heads
+    const int ngroups = (len + 7) / 8;
+    unsigned short* s_next = reinterpret_cast<unsigned short*>(s_M + 16);             // [gqa][ngroups + 1]: first group >= g whose maximum moved
+    unsigned char* s_moved = reinterpret_cast<unsigned char*>(s_next + gqa * (ngroups + 1));  // [gqa][ngroups]: any ms != 1 in the group of 8
     __syncthreads();  // every thread is done with the table the slice overlays
     {
         // the V slice in four groups of rows, so that the chain can start when the first quarter has landed
@@ -511,6 +544,7 @@ __device__ __noinline__ void mega_values_unit(const MegaArgs& a, const MegaLayer
         f_vs[idx] = __ldcg(a.scores + static_cast<size_t>(kvh * gqa + g) * a.ctx + start + p);
     }
     __syncthreads();
+    QTB_FINE(a, 2);
     // softmax factors: four groups of 128 threads take one head each; running maximum in position order by a scan over
     // the group's threads (attention.rs:448-462)
     for (int g0 = 0; g0 < gqa; g0 += 4) {
@@ -551,9 +585,30 @@ __device__ __noinline__ void mega_values_unit(const MegaArgs& a, const MegaLayer
         }
         __syncthreads();
     }
+    {
+        // one flag per head and group of 8 positions: does any rescale factor of the group differ from 1?
+        for (int idx = tid; idx < gqa * ngroups; idx += kMegaThreads) {
+            const int g = idx / ngroups, p0 = (idx - g * ngroups) * 8;
+            bool any = false;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) any |= p0 + j < len && f_ms[g * len + p0 + j] != 1.0f;
+            s_moved[idx] = any ? 1 : 0;
+        }
+        __syncthreads();
+        if (tid < gqa) {  // backward scan: the chain runs branch-free from a group to the next one whose maximum moved
+            unsigned short nxt = static_cast<unsigned short>(ngroups);
+            s_next[tid * (ngroups + 1) + ngroups] = nxt;
+            for (int grp = ngroups - 1; grp >= 0; --grp) {
+                if (s_moved[tid * ngroups + grp]) nxt = static_cast<unsigned short>(grp);
+                s_next[tid * (ngroups + 1) + grp] = nxt;
+            }
+        }
+        __syncthreads();
+    }
+    QTB_FINE(a, 3);
     // values: warp g < gqa runs head g (heads beyond the warp count take further rounds); with slice 0, lane 0 of warp
     // kMegaWarps - 1 - g accumulates S of head g over the same positions meanwhile
-    const int q_rows = (len + 3) / 4;
+    const int q_rows = ((len + 3) / 4 + 7) / 8 * 8;  // chain quarters start on multiples of 8 positions, like the flags
     for (int g0 = 0; g0 < gqa; g0 += kMegaWarps / 2) {
         const int g = g0 + warp;
         const bool chain = warp < kMegaWarps / 2 && g < gqa;
@@ -562,21 +617,26 @@ __device__ __noinline__ void mega_values_unit(const MegaArgs& a, const MegaLayer
         float acc = 0.0f, S = 0.0f;
         for (int q = 0; q < 4; ++q) {
             if (g0 == 0) {
-                if (q == 0) cp_async_wait<3>();
-                if (q == 1) cp_async_wait<2>();
-                if (q == 2) cp_async_wait<1>();
-                if (q == 3) cp_async_wait<0>();
-                __syncthreads();
+                // the copy groups hold ceil(len / 4) rows each, a chain quarter up to 7 more: the first quarter needs two
+                // groups, the others everything
+                if (q == 0) cp_async_wait<2>();
+                if (q == 1) cp_async_wait<0>();
+                if (q <= 1) __syncthreads();
             }
             const int ra = min(q * q_rows, len), rb = min(ra + q_rows, len);
             if (chain) {
-                acc = f32v ? value_chain<true>(vbuf + ra * kAttnSlice + lane, kAttnSlice, f_ms + g * len + ra, f_vs + g * len + ra, rb - ra, acc)
-                           : value_chain<false>(vbuf + ra * kAttnSlice + lane, kAttnSlice, f_ms + g * len + ra, f_vs + g * len + ra, rb - ra, acc);
+                const uint32_t o_col = static_cast<uint32_t>(reinterpret_cast<const unsigned char*>(vbuf + ra * kAttnSlice + lane) - smem);
+                const uint32_t o_ms = static_cast<uint32_t>(reinterpret_cast<const unsigned char*>(f_ms + g * len + ra) - smem);
+                const uint32_t o_vs = static_cast<uint32_t>(reinterpret_cast<const unsigned char*>(f_vs + g * len + ra) - smem);
+                const uint32_t o_nx = static_cast<uint32_t>(reinterpret_cast<const unsigned char*>(s_next + g * (ngroups + 1) + (ra >> 3)) - smem);
+                acc = f32v ? value_chain<true>(o_col, kAttnSlice, o_ms, o_vs, o_nx, ra >> 3, rb - ra, acc)
+                           : value_chain<false>(o_col, kAttnSlice, o_ms, o_vs, o_nx, ra >> 3, rb - ra, acc);
             } else if (sums) {
 #pragma unroll 8
                 for (int p = ra; p < rb; ++p) S = __fmaf_rn(S, f_ms[gs * len + p], f_vs[gs * len + p]);  // attention.rs:466
             }
         }
+        QTB_FINE(a, 12);
         if (chain) a.part_acc[(static_cast<size_t>(kvh * gqa + g) * 4 + c) * hd + slice * kAttnSlice + lane] = acc;
         if (sums) {
             float* my_ms = a.part_ms + (static_cast<size_t>(kvh * gqa + gs) * 4 + c) * 2;
