@@ -75,11 +75,12 @@ int quintrit_b200_pack_planar(const int8_t* trits, size_t trits_len, size_t rows
 typedef struct quintrit_b200_matrix quintrit_b200_matrix_t;
 
 /* Source encodings accepted by quintrit_b200_matrix_upload; the numbers are the GGML type ids of
- * quintrit-format/src/gguf.rs (I2_S 36, TQ1_0 34, TQ2_0 35), 0 stands for planar velurex bytes. */
+ * quintrit-format/src/gguf.rs (I2_S 36, TQ1_0 34, TQ2_0 35, Q2_0 42), 0 stands for planar velurex bytes. */
 #define QUINTRIT_B200_SRC_PLANAR 0
 #define QUINTRIT_B200_SRC_TQ1_0 34
 #define QUINTRIT_B200_SRC_TQ2_0 35
 #define QUINTRIT_B200_SRC_I2_S 36
+#define QUINTRIT_B200_SRC_Q2_0 42 /* blocks of 64 weights: f16 scale + 16 code bytes; gives a block-scaled matrix (below) */
 
 /*
  * Copies an encoded rows x cols ternary matrix from host memory to the device and transcodes it THERE into the
@@ -96,6 +97,26 @@ int quintrit_b200_matrix_free(quintrit_b200_matrix_t* matrix);
 int quintrit_b200_matrix_info(const quintrit_b200_matrix_t* matrix, size_t* out_rows, size_t* out_cols, size_t* out_device_bytes);
 /* Reads the matrix back as planar bytes (inverse of the device transcode; for tests and round trips). */
 int quintrit_b200_matrix_download_planar(const quintrit_b200_matrix_t* matrix, uint8_t* out, size_t out_capacity);
+
+/*
+ * Block-scaled matrices (source QUINTRIT_B200_SRC_Q2_0). Replaces BlockScaledLayer::from_q2_0 / forward_q8 of
+ * quintrit-runtime/src/layer.rs:420-507 (decode_q2_0_packed of quintrit-format/src/decoders/q2_0.rs:34-101, then
+ * quintrit-core/src/block_scaled.rs:175-260), which the reference runs on the CPU only. The upload transcodes the payload
+ * on the device to planar velurex bytes and keeps one f32 scale per 64 weights; a weight with the code 3 gives
+ * QUINTRIT_ERR_FORMAT. Such a matrix is served by the entry points below (and by matrix_free / matrix_info /
+ * matrix_download_planar); the integer GEMV entry points return QUINTRIT_ERR_UNSUPPORTED for it.
+ */
+/* The rows * cols / 64 weight scales, row-major (q2_0.rs:83-101). */
+int quintrit_b200_matrix_scales(const quintrit_b200_matrix_t* matrix, float* out, size_t out_capacity);
+/* Q8_0 activation blocks on the device: codes and one scale per 32 values, as quantize_q8_0 of
+ * quintrit-runtime/src/ops.rs:879-910 (d = f16(amax / 127), round to nearest even). n must be a multiple of 32. */
+int quintrit_b200_quantize_q8_0(uint32_t device_index, const float* x, size_t n, int8_t* out_codes, float* out_scales);
+/* out = W x for f32 activations: Q8_0 quantisation followed by the Q2_0 x Q8_0 dot product of every row, bit for bit the
+ * floats of quantize_q8_0 + BlockScaledLayer::forward_q8 (host buffers; copies and waits). */
+int quintrit_b200_gemv_block_scaled(const quintrit_b200_matrix_t* matrix, const float* x, size_t x_len, float* out, size_t out_capacity);
+/* The same for activations that are Q8_0 blocks already: BlockScaledLayer::forward_q8 (layer.rs:476-487). */
+int quintrit_b200_gemv_block_scaled_q8(const quintrit_b200_matrix_t* matrix, const int8_t* codes, size_t codes_len, const float* scales,
+                                       size_t scales_len, float* out, size_t out_capacity);
 
 /*
  * Exact integer GEMV with host buffers: out[i] = sum_j W[i][j] * activations[j]. Replaces quintrit_gemv_i32

@@ -301,6 +301,12 @@ def _declare_model(l: C.CDLL) -> None:
     l.qto_model_create.argtypes = [C.c_int] * 11 + [C.c_float, C.c_float, _u16p, _u16p, _f32p, C.POINTER(_u8p), _f32p, C.POINTER(_f32p)]
     l.qto_model_free.argtypes = [C.c_void_p]
     l.qto_model_forward.argtypes = [C.c_void_p, C.c_uint32, _sz, _f32p]
+    l.qto_quantize_q8_0.argtypes = [_f32p, _sz, _i8p, _f32p]
+    l.qto_block_scaled_dot_row.restype = C.c_float
+    l.qto_block_scaled_dot_row.argtypes = [_u8p, _f32p, _i8p, _f32p, _sz]
+    l.qto_block_scaled_dot_trits.restype = C.c_float
+    l.qto_block_scaled_dot_trits.argtypes = [_i8p, _f32p, _i8p, _f32p, _sz]
+    l.qto_gemv_block_scaled.argtypes = [_u8p, _f32p, _i8p, _f32p, _sz, _sz, _f32p]
 
 
 _model_declared = False
@@ -427,3 +433,29 @@ class Model:
             mlib().qto_model_free(self._h)
         except Exception:
             pass
+
+
+def quantize_q8_0(x):
+    """(codes int8[n], block scales f32[n/32]) of ops.rs:898-910; n must be a multiple of 32."""
+    xx = _c(x, np.float32).reshape(-1)
+    assert xx.size % 32 == 0
+    qs, d = np.zeros(xx.size, np.int8), np.zeros(xx.size // 32, np.float32)
+    mlib().qto_quantize_q8_0(_p(xx, _f32p), xx.size, _p(qs, _i8p), _p(d, _f32p))
+    return qs, d
+
+
+def block_scaled_dot_row(row, w_scales, acts, a_scales, cols: int) -> np.float32:
+    r, ws, a, sc = _c(row, np.uint8), _c(w_scales, np.float32), _c(acts, np.int8), _c(a_scales, np.float32)
+    return np.float32(mlib().qto_block_scaled_dot_row(_p(r, _u8p), _p(ws, _f32p), _p(a, _i8p), _p(sc, _f32p), cols))
+
+
+def block_scaled_dot_trits(trits, w_scales, acts, a_scales, cols: int) -> np.float32:
+    t, ws, a, sc = _c(trits, np.int8), _c(w_scales, np.float32), _c(acts, np.int8), _c(a_scales, np.float32)
+    return np.float32(mlib().qto_block_scaled_dot_trits(_p(t, _i8p), _p(ws, _f32p), _p(a, _i8p), _p(sc, _f32p), cols))
+
+
+def gemv_block_scaled(planar, w_scales, acts, a_scales, rows: int, cols: int) -> np.ndarray:
+    pl, ws, a, sc = _c(planar, np.uint8), _c(w_scales, np.float32), _c(acts, np.int8), _c(a_scales, np.float32)
+    out = np.zeros(rows, np.float32)
+    mlib().qto_gemv_block_scaled(_p(pl, _u8p), _p(ws, _f32p), _p(a, _i8p), _p(sc, _f32p), rows, cols, _p(out, _f32p))
+    return out

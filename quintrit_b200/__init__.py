@@ -15,6 +15,7 @@ from .api import (  # noqa: F401
     QuintritError,
     SRC_I2_S,
     SRC_PLANAR,
+    SRC_Q2_0,
     SRC_TQ1_0,
     SRC_TQ2_0,
     device_count,
@@ -23,6 +24,7 @@ from .api import (  # noqa: F401
     library_path,
     load_library,
     pack_planar,
+    quantize_q8_0,
     row_bytes,
     version,
 )

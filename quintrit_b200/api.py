@@ -15,7 +15,7 @@ import numpy as np
 
 from . import build as _build
 
-SRC_PLANAR, SRC_TQ1_0, SRC_TQ2_0, SRC_I2_S = 0, 34, 35, 36
+SRC_PLANAR, SRC_TQ1_0, SRC_TQ2_0, SRC_I2_S, SRC_Q2_0 = 0, 34, 35, 36, 42
 
 _u8p, _i8p, _i32p, _f32p = (C.POINTER(t) for t in (C.c_uint8, C.c_int8, C.c_int32, C.c_float))
 _sz = C.c_size_t
@@ -85,6 +85,10 @@ def load_library(build_if_missing: bool = True) -> C.CDLL:
     l.quintrit_b200_matrix_free.argtypes = [C.c_void_p]
     l.quintrit_b200_matrix_info.argtypes = [C.c_void_p, C.POINTER(_sz), C.POINTER(_sz), C.POINTER(_sz)]
     l.quintrit_b200_matrix_download_planar.argtypes = [C.c_void_p, _u8p, _sz]
+    l.quintrit_b200_matrix_scales.argtypes = [C.c_void_p, _f32p, _sz]
+    l.quintrit_b200_quantize_q8_0.argtypes = [C.c_uint32, _f32p, _sz, _i8p, _f32p]
+    l.quintrit_b200_gemv_block_scaled.argtypes = [C.c_void_p, _f32p, _sz, _f32p, _sz]
+    l.quintrit_b200_gemv_block_scaled_q8.argtypes = [C.c_void_p, _i8p, _sz, _f32p, _sz, _f32p, _sz]
     l.quintrit_b200_gemv_i32.argtypes = [C.c_void_p, _i8p, _sz, _i32p, _sz]
     l.quintrit_b200_gemv_f32.argtypes = [C.c_void_p, _i8p, _sz, C.c_float, _f32p, _sz]
     l.quintrit_b200_gemv_i32_device.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
@@ -177,6 +181,26 @@ class Matrix:
     def download_planar(self) -> np.ndarray:
         out = np.zeros(self.rows * row_bytes(self.cols), np.uint8)
         _check(load_library().quintrit_b200_matrix_download_planar(self._h, _p(out, _u8p), out.size))
+        return out
+
+    def scales(self) -> np.ndarray:
+        """The per-64-weight scales of a block-scaled (Q2_0) matrix, row-major."""
+        out = np.zeros(self.rows * (self.cols // 64), np.float32)
+        _check(load_library().quintrit_b200_matrix_scales(self._h, _p(out, _f32p), out.size))
+        return out
+
+    def gemv_block_scaled(self, x) -> np.ndarray:
+        """``quantize_q8_0`` + ``BlockScaledLayer::forward_q8`` for f32 activations (Q2_0 matrices)."""
+        xx = np.ascontiguousarray(x, dtype=np.float32)
+        out = np.zeros(self.rows, np.float32)
+        _check(load_library().quintrit_b200_gemv_block_scaled(self._h, _p(xx, _f32p), xx.size, _p(out, _f32p), out.size))
+        return out
+
+    def gemv_block_scaled_q8(self, codes, scales) -> np.ndarray:
+        """``BlockScaledLayer::forward_q8`` for activations that are Q8_0 blocks already."""
+        q, d = np.ascontiguousarray(codes, dtype=np.int8), np.ascontiguousarray(scales, dtype=np.float32)
+        out = np.zeros(self.rows, np.float32)
+        _check(load_library().quintrit_b200_gemv_block_scaled_q8(self._h, _p(q, _i8p), q.size, _p(d, _f32p), d.size, _p(out, _f32p), out.size))
         return out
 
     def gemv_i32(self, activations) -> np.ndarray:
@@ -361,3 +385,11 @@ class Decoder:
             self.free()
         except Exception:
             pass
+
+
+def quantize_q8_0(x, device: int = 0):
+    """Q8_0 activation blocks computed on the device: (codes int8[n], scales f32[n / 32])."""
+    xx = np.ascontiguousarray(x, dtype=np.float32).reshape(-1)
+    q, d = np.zeros(xx.size, np.int8), np.zeros(xx.size // 32, np.float32)
+    _check(load_library().quintrit_b200_quantize_q8_0(device, _p(xx, _f32p), xx.size, _p(q, _i8p), _p(d, _f32p)))
+    return q, d

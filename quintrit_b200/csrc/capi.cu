@@ -10,6 +10,7 @@
 #include "capi_common.cuh"
 #include "gemv_lut.cuh"
 #include "transcode.cuh"
+#include "block_scaled.cuh"
 
 using namespace qtb;
 
@@ -27,6 +28,12 @@ struct quintrit_b200_matrix {
     int8_t* d_act;
     int32_t* d_out;
     float* d_outf;
+    // block-scaled (Q2_0) matrices: planar bytes and one f32 scale per 64 weights instead of the stream layout
+    bool block_scaled = false;
+    uint8_t* d_planar = nullptr;
+    float* d_wscales = nullptr;
+    float* d_x = nullptr;    // cols floats: activations of one call
+    float* d_as = nullptr;   // cols / 32 activation block scales
 };
 
 struct quintrit_b200_plan {
@@ -47,8 +54,10 @@ namespace {
 
 const char* kVersion = "0.1.0";
 
-int check_matrix(const quintrit_b200_matrix* m) {
+int check_matrix(const quintrit_b200_matrix* m, bool any_kind = false) {
     if (m == nullptr || m->magic != kMagicMatrix) return fail(QUINTRIT_ERR_INVALID_HANDLE, "matrix handle is NULL, freed or of the wrong type");
+    if (m->block_scaled && !any_kind)
+        return fail(QUINTRIT_ERR_UNSUPPORTED, "a block-scaled (Q2_0) matrix is not supported by this call: use quintrit_b200_gemv_block_scaled");
     return QUINTRIT_OK;
 }
 int check_plan(const quintrit_b200_plan* p) {
@@ -278,6 +287,10 @@ void destroy_matrix(quintrit_b200_matrix* m) {
     cudaFree(m->d_act);
     cudaFree(m->d_out);
     cudaFree(m->d_outf);
+    cudaFree(m->d_planar);
+    cudaFree(m->d_wscales);
+    cudaFree(m->d_x);
+    cudaFree(m->d_as);
     m->magic = 0;
     delete m;
 }
@@ -288,6 +301,7 @@ size_t source_bytes(int32_t source, size_t rows, size_t cols) {
         case kSrcI2S: return rows * cols / 4;
         case kSrcTq2: return rows * cols / 256 * 66;
         case kSrcTq1: return rows * cols / 256 * 54;
+        case kSrcQ2: return rows * cols / 64 * 18;
         default: return 0;
     }
 }
@@ -302,8 +316,9 @@ extern "C" int quintrit_b200_matrix_upload(uint32_t device_index, int32_t source
         if (data == nullptr) return fail(QUINTRIT_ERR_NULL_POINTER, "data is NULL");
         if (rows == 0 || cols == 0 || rows > (size_t(1) << 31)) return fail(QUINTRIT_ERR_INVALID_SHAPE, "rows and cols must be at least 1");
         if (cols > 131072) return fail(QUINTRIT_ERR_INVALID_SHAPE, "cols %zu exceeds 131072", cols);
-        if (source != kSrcPlanar && source != kSrcI2S && source != kSrcTq1 && source != kSrcTq2)
+        if (source != kSrcPlanar && source != kSrcI2S && source != kSrcTq1 && source != kSrcTq2 && source != kSrcQ2)
             return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "unknown source encoding %d", source);
+        if (source == kSrcQ2 && cols % 64 != 0) return fail(QUINTRIT_ERR_FORMAT, "a Q2_0 row of %zu weights is not a multiple of the block size 64", cols);
         if (source == kSrcI2S && cols % 128 != 0) return fail(QUINTRIT_ERR_FORMAT, "an I2_S row of %zu weights is not a multiple of 128", cols);
         if ((source == kSrcTq1 || source == kSrcTq2) && (rows * cols) % 256 != 0)
             return fail(QUINTRIT_ERR_FORMAT, "a TQ tensor of %zu weights is not a multiple of 256", rows * cols);
@@ -329,6 +344,45 @@ extern "C" int quintrit_b200_matrix_upload(uint32_t device_index, int32_t source
         };
         cudaError_t e;
         uint8_t* d_src = nullptr;
+        if (source == kSrcQ2) {
+            // block-scaled matrix: planar velurex bytes + one f32 scale per 64 weights (q2_0.rs:34-101, pack.rs:103-131)
+            m->block_scaled = true;
+            m->w_bytes = rows * m->blocks * kBlockBytes + rows * (cols / 64) * sizeof(float);
+            unsigned long long* d_bad = nullptr;
+            unsigned long long bad = ~0ull;
+            if ((e = cudaMalloc(&m->d_planar, rows * m->blocks * kBlockBytes)) != cudaSuccess) return bail(e, "cudaMalloc(planar weights)");
+            if ((e = cudaMalloc(&m->d_wscales, rows * (cols / 64) * sizeof(float))) != cudaSuccess) return bail(e, "cudaMalloc(weight scales)");
+            if ((e = cudaMalloc(&m->d_x, cols * sizeof(float))) != cudaSuccess) return bail(e, "cudaMalloc(activations)");
+            if ((e = cudaMalloc(&m->d_as, cols / 32 * sizeof(float))) != cudaSuccess) return bail(e, "cudaMalloc(activation scales)");
+            if ((e = cudaMalloc(&m->d_act, cols)) != cudaSuccess) return bail(e, "cudaMalloc(activation codes)");
+            if ((e = cudaMalloc(&m->d_outf, rows * sizeof(float))) != cudaSuccess) return bail(e, "cudaMalloc(results f32)");
+            if ((e = cudaMalloc(&d_src, need)) != cudaSuccess) return bail(e, "cudaMalloc(staging)");
+            if ((e = cudaMalloc(&d_bad, sizeof bad)) != cudaSuccess) {
+                cudaFree(d_src);
+                return bail(e, "cudaMalloc(flag)");
+            }
+            e = cudaMemcpy(d_src, data, need, cudaMemcpyHostToDevice);
+            if (e == cudaSuccess) e = cudaMemcpy(d_bad, &bad, sizeof bad, cudaMemcpyHostToDevice);
+            if (e == cudaSuccess) {
+                const size_t nb = rows * m->blocks * kBlockBytes, ns = rows * (cols / 64);
+                q2_0_to_planar_kernel<<<static_cast<int>(std::min<size_t>((nb + 255) / 256, 148 * 16)), 256>>>(d_src, m->d_planar, rows, cols, m->blocks, d_bad);
+                q2_0_scales_kernel<<<static_cast<int>(std::min<size_t>((ns + 255) / 256, 148 * 16)), 256>>>(d_src, m->d_wscales, ns);
+                g_launches += 2;
+                e = cudaGetLastError();
+            }
+            if (e == cudaSuccess) e = cudaMemcpy(&bad, d_bad, sizeof bad, cudaMemcpyDeviceToHost);
+            cudaFree(d_src);
+            cudaFree(d_bad);
+            if (e != cudaSuccess) return bail(e, "Q2_0 transcode");
+            if (bad != ~0ull) {
+                destroy_matrix(m);
+                return fail(QUINTRIT_ERR_FORMAT, "Q2_0 weight %llu uses code 3 (+2), which is not ternary", bad);
+            }
+            QTB_CUDA(cudaFuncSetAttribute(gemv_block_scaled_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          static_cast<int>(block_scaled_smem_bytes(131072))));
+            *out_matrix = m;
+            return ok();
+        }
         if ((e = cudaMalloc(&m->d_w, m->w_bytes)) != cudaSuccess) return bail(e, "cudaMalloc(weights)");
         if ((e = cudaMalloc(&d_src, need)) != cudaSuccess) return bail(e, "cudaMalloc(staging)");
         if ((e = cudaMemcpy(d_src, data, need, cudaMemcpyHostToDevice)) != cudaSuccess) {
@@ -374,7 +428,7 @@ extern "C" int quintrit_b200_matrix_upload(uint32_t device_index, int32_t source
 extern "C" int quintrit_b200_matrix_free(quintrit_b200_matrix_t* matrix) {
     return guard([&]() -> int {
         if (matrix == nullptr) return ok();
-        int rc = check_matrix(matrix);
+        int rc = check_matrix(matrix, true);
         if (rc != QUINTRIT_OK) return rc;
         destroy_matrix(matrix);
         return ok();
@@ -383,7 +437,7 @@ extern "C" int quintrit_b200_matrix_free(quintrit_b200_matrix_t* matrix) {
 
 extern "C" int quintrit_b200_matrix_info(const quintrit_b200_matrix_t* matrix, size_t* out_rows, size_t* out_cols, size_t* out_device_bytes) {
     return guard([&]() -> int {
-        int rc = check_matrix(matrix);
+        int rc = check_matrix(matrix, true);
         if (rc != QUINTRIT_OK) return rc;
         if (out_rows) *out_rows = matrix->rows;
         if (out_cols) *out_cols = matrix->cols;
@@ -394,12 +448,16 @@ extern "C" int quintrit_b200_matrix_info(const quintrit_b200_matrix_t* matrix, s
 
 extern "C" int quintrit_b200_matrix_download_planar(const quintrit_b200_matrix_t* matrix, uint8_t* out, size_t out_capacity) {
     return guard([&]() -> int {
-        int rc = check_matrix(matrix);
+        int rc = check_matrix(matrix, true);
         if (rc != QUINTRIT_OK) return rc;
         if (out == nullptr) return fail(QUINTRIT_ERR_NULL_POINTER, "out is NULL");
         const size_t need = matrix->rows * matrix->blocks * kBlockBytes;
         if (out_capacity < need) return fail(QUINTRIT_ERR_BUFFER_TOO_SMALL, "out holds %zu bytes, %zu are needed", out_capacity, need);
         DeviceGuard g(matrix->device);
+        if (matrix->block_scaled) {
+            QTB_CUDA(cudaMemcpy(out, matrix->d_planar, need, cudaMemcpyDeviceToHost));
+            return ok();
+        }
         uint8_t* d_planar = nullptr;
         QTB_CUDA(cudaMalloc(&d_planar, need));
         const int grid = static_cast<int>(std::min<size_t>((need + 255) / 256, 148 * 16));
@@ -464,6 +522,104 @@ extern "C" int quintrit_b200_gemv_i32(const quintrit_b200_matrix_t* matrix, cons
 extern "C" int quintrit_b200_gemv_f32(const quintrit_b200_matrix_t* matrix, const int8_t* activations, size_t activations_len, float scale,
                                       float* out, size_t out_capacity) {
     return guard([&]() -> int { return gemv_host(matrix, activations, activations_len, out, out_capacity, true, scale); });
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// block-scaled (Q2_0 x Q8_0) projection
+// ---------------------------------------------------------------------------------------------------------------------
+
+namespace {
+int check_block_scaled(const quintrit_b200_matrix* m) {
+    int rc = check_matrix(m, true);
+    if (rc != QUINTRIT_OK) return rc;
+    if (!m->block_scaled) return fail(QUINTRIT_ERR_UNSUPPORTED, "the matrix was not uploaded from a Q2_0 payload: it has no block scales");
+    return QUINTRIT_OK;
+}
+int launch_block_scaled(const quintrit_b200_matrix* m) {
+    const int grid = static_cast<int>(std::min<size_t>((m->rows + 31) / 32, static_cast<size_t>(m->sm_count) * 8));
+    gemv_block_scaled_kernel<<<grid, kBsThreads, block_scaled_smem_bytes(m->cols)>>>(m->d_planar, m->d_wscales, m->d_act, m->d_as, m->rows, m->cols, m->d_outf);
+    ++g_launches;
+    QTB_CUDA(cudaGetLastError());
+    return QUINTRIT_OK;
+}
+}  // namespace
+
+extern "C" int quintrit_b200_matrix_scales(const quintrit_b200_matrix_t* matrix, float* out, size_t out_capacity) {
+    return guard([&]() -> int {
+        int rc = check_block_scaled(matrix);
+        if (rc != QUINTRIT_OK) return rc;
+        if (out == nullptr) return fail(QUINTRIT_ERR_NULL_POINTER, "out is NULL");
+        const size_t need = matrix->rows * (matrix->cols / 64);
+        if (out_capacity < need) return fail(QUINTRIT_ERR_BUFFER_TOO_SMALL, "out holds %zu values, %zu are needed", out_capacity, need);
+        DeviceGuard g(matrix->device);
+        QTB_CUDA(cudaMemcpy(out, matrix->d_wscales, need * sizeof(float), cudaMemcpyDeviceToHost));
+        return ok();
+    });
+}
+
+extern "C" int quintrit_b200_quantize_q8_0(uint32_t device_index, const float* x, size_t n, int8_t* out_codes, float* out_scales) {
+    return guard([&]() -> int {
+        if (x == nullptr || out_codes == nullptr || out_scales == nullptr) return fail(QUINTRIT_ERR_NULL_POINTER, "a pointer is NULL");
+        if (n == 0 || n % 32 != 0) return fail(QUINTRIT_ERR_INVALID_SHAPE, "Q8_0 quantization needs whole blocks of 32 values, got %zu", n);
+        cudaDeviceProp prop;
+        int rc = require_b200(static_cast<int>(device_index), &prop);
+        if (rc != QUINTRIT_OK) return rc;
+        DeviceGuard g(static_cast<int>(device_index));
+        float *d_x = nullptr, *d_d = nullptr;
+        int8_t* d_q = nullptr;
+        cudaError_t e = cudaMalloc(&d_x, n * sizeof(float));
+        if (e == cudaSuccess) e = cudaMalloc(&d_d, n / 32 * sizeof(float));
+        if (e == cudaSuccess) e = cudaMalloc(&d_q, n);
+        if (e == cudaSuccess) e = cudaMemcpy(d_x, x, n * sizeof(float), cudaMemcpyHostToDevice);
+        if (e == cudaSuccess) {
+            quantize_q8_0_kernel<<<static_cast<int>(std::min<size_t>((n / 32 + 7) / 8, 148 * 8)), 256>>>(d_x, n, d_q, d_d);
+            ++g_launches;
+            e = cudaGetLastError();
+        }
+        if (e == cudaSuccess) e = cudaMemcpy(out_codes, d_q, n, cudaMemcpyDeviceToHost);
+        if (e == cudaSuccess) e = cudaMemcpy(out_scales, d_d, n / 32 * sizeof(float), cudaMemcpyDeviceToHost);
+        cudaFree(d_x);
+        cudaFree(d_d);
+        cudaFree(d_q);
+        if (e != cudaSuccess) return cuda_fail(e, "quantize_q8_0");
+        return ok();
+    });
+}
+
+extern "C" int quintrit_b200_gemv_block_scaled(const quintrit_b200_matrix_t* matrix, const float* x, size_t x_len, float* out, size_t out_capacity) {
+    return guard([&]() -> int {
+        int rc = check_block_scaled(matrix);
+        if (rc != QUINTRIT_OK) return rc;
+        if (x == nullptr || out == nullptr) return fail(QUINTRIT_ERR_NULL_POINTER, "a pointer is NULL");
+        if (x_len != matrix->cols) return fail(QUINTRIT_ERR_INVALID_SHAPE, "%zu activations for %zu columns", x_len, matrix->cols);
+        if (out_capacity < matrix->rows) return fail(QUINTRIT_ERR_BUFFER_TOO_SMALL, "out holds %zu values, %zu are needed", out_capacity, matrix->rows);
+        DeviceGuard g(matrix->device);
+        QTB_CUDA(cudaMemcpy(matrix->d_x, x, x_len * sizeof(float), cudaMemcpyHostToDevice));
+        quantize_q8_0_kernel<<<static_cast<int>(std::min<size_t>((x_len / 32 + 7) / 8, 148 * 8)), 256>>>(matrix->d_x, x_len, matrix->d_act, matrix->d_as);
+        ++g_launches;
+        QTB_CUDA(cudaGetLastError());
+        if ((rc = launch_block_scaled(matrix)) != QUINTRIT_OK) return rc;
+        QTB_CUDA(cudaMemcpy(out, matrix->d_outf, matrix->rows * sizeof(float), cudaMemcpyDeviceToHost));
+        return ok();
+    });
+}
+
+extern "C" int quintrit_b200_gemv_block_scaled_q8(const quintrit_b200_matrix_t* matrix, const int8_t* codes, size_t codes_len, const float* scales,
+                                                  size_t scales_len, float* out, size_t out_capacity) {
+    return guard([&]() -> int {
+        int rc = check_block_scaled(matrix);
+        if (rc != QUINTRIT_OK) return rc;
+        if (codes == nullptr || scales == nullptr || out == nullptr) return fail(QUINTRIT_ERR_NULL_POINTER, "a pointer is NULL");
+        if (codes_len != matrix->cols) return fail(QUINTRIT_ERR_INVALID_SHAPE, "%zu activation codes for %zu columns", codes_len, matrix->cols);
+        if (scales_len != matrix->cols / 32) return fail(QUINTRIT_ERR_INVALID_SHAPE, "%zu activation scales, %zu are needed", scales_len, matrix->cols / 32);
+        if (out_capacity < matrix->rows) return fail(QUINTRIT_ERR_BUFFER_TOO_SMALL, "out holds %zu values, %zu are needed", out_capacity, matrix->rows);
+        DeviceGuard g(matrix->device);
+        QTB_CUDA(cudaMemcpy(matrix->d_act, codes, codes_len, cudaMemcpyHostToDevice));
+        QTB_CUDA(cudaMemcpy(matrix->d_as, scales, scales_len * sizeof(float), cudaMemcpyHostToDevice));
+        if ((rc = launch_block_scaled(matrix)) != QUINTRIT_OK) return rc;
+        QTB_CUDA(cudaMemcpy(out, matrix->d_outf, matrix->rows * sizeof(float), cudaMemcpyDeviceToHost));
+        return ok();
+    });
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
