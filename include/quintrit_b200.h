@@ -213,6 +213,47 @@ typedef struct quintrit_b200_decoder_desc {
 
 int quintrit_b200_decoder_create(const quintrit_b200_decoder_desc_t* desc, quintrit_b200_decoder_t** out_decoder);
 int quintrit_b200_decoder_free(quintrit_b200_decoder_t* decoder);
+
+/* Options of quintrit_b200_decoder_open_gguf: the struct of quintrit.h:502-507 (same fields and meaning; no flag is
+ * defined here, so flags must be 0; the context is capped at 8192 instead of 7936). */
+typedef struct quintrit_gpu_options {
+    uint32_t struct_size;    /* set to sizeof(quintrit_gpu_options_t) */
+    uint32_t device_index;   /* GPU to use (quintrit_cuda_device_info_t::index) */
+    uint32_t context_length; /* largest context window in tokens; 0 = min(4096, the model's maximum) */
+    uint32_t flags;          /* must be 0 */
+} quintrit_gpu_options_t;
+
+/*
+ * Loads a GGUF model onto a GPU and returns a decoder for it: the device half of quintrit_model_open_gpu
+ * (quintrit.h:515-527; quintrit-c/src/runtime.rs, GpuModel::load quintrit-runtime/src/gpu.rs:183-260) without the
+ * tokenizer - prompts are token ids. The hyperparameters are derived like ModelConfig::from_gguf
+ * (quintrit-runtime/src/config.rs:257-455); the ternary payloads (I2_S, TQ1_0, TQ2_0) are copied as the file stores
+ * them and transcoded on the device; files without I2_S tensors use the FP32-accumulator attention. `options` may be
+ * NULL (GPU 0, default context). A path that is not a regular file gives QUINTRIT_ERR_IO, a malformed file
+ * QUINTRIT_ERR_FORMAT, a missing or mis-shaped tensor QUINTRIT_ERR_MODEL, and Q2_0, mixture-of-experts, hybrid and
+ * query/key-norm models QUINTRIT_ERR_UNSUPPORTED. On failure *out_decoder is NULL. The decoder owns the weights.
+ */
+int quintrit_b200_decoder_open_gguf(const char* path, const quintrit_gpu_options_t* options, quintrit_b200_decoder_t** out_decoder);
+
+/* Shape of a decoder (the part of quintrit_model_info, quintrit.h:410-420, that concerns the device). */
+typedef struct quintrit_b200_decoder_info {
+    uint32_t struct_size; /* set to sizeof(quintrit_b200_decoder_info_t) before the call */
+    int32_t arch;
+    int32_t f32_values;
+    uint32_t hidden_size, intermediate_size, num_layers, num_heads, num_kv_heads, head_dim, vocab_size, context_length, rope_dims;
+    uint32_t device_index;
+    uint32_t single_kernel; /* 1 if tokens are decoded by the one-kernel-per-token path */
+} quintrit_b200_decoder_info_t;
+int quintrit_b200_decoder_info(const quintrit_b200_decoder_t* decoder, quintrit_b200_decoder_info_t* out_info);
+
+/*
+ * The directory of a GGUF file as text, read on the host only (no GPU needed): "version", the hyperparameters one per
+ * line as quintrit_b200_decoder_open_gguf derives them, then "tensor <name> type=<ggml id> shape=<d0>x<d1>.. bytes=<n>"
+ * per tensor in file order. *out_needed receives the length including the final NUL (also with
+ * QUINTRIT_ERR_BUFFER_TOO_SMALL, e.g. when out is NULL). The reference's counterpart is GgufFile::open
+ * (quintrit-format/src/gguf.rs:190-313) as used by the `inspect` tools.
+ */
+int quintrit_b200_gguf_describe(const char* path, char* out, size_t out_capacity, size_t* out_needed);
 /*
  * One token at position `pos` (positions are fed in order; an earlier position restarts from that prefix), as
  * GpuSession::forward (quintrit-runtime/src/gpu.rs:459-493) but from a token id: the embedding row is looked up on the

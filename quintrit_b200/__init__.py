@@ -20,6 +20,7 @@ from .api import (  # noqa: F401
     SRC_TQ2_0,
     device_count,
     device_info,
+    gguf_describe,
     launch_count,
     library_path,
     load_library,

@@ -37,6 +37,16 @@ class _DeviceInfoC(C.Structure):
                 ("name", C.c_char * 64)]
 
 
+class _GpuOptionsC(C.Structure):
+    _fields_ = [("struct_size", C.c_uint32), ("device_index", C.c_uint32), ("context_length", C.c_uint32), ("flags", C.c_uint32)]
+
+
+class _DecoderInfoC(C.Structure):
+    _fields_ = [("struct_size", C.c_uint32), ("arch", C.c_int32), ("f32_values", C.c_int32)] + [
+        (n, C.c_uint32) for n in ("hidden_size", "intermediate_size", "num_layers", "num_heads", "num_kv_heads", "head_dim", "vocab_size",
+                                  "context_length", "rope_dims", "device_index", "single_kernel")]
+
+
 class _DecoderDescC(C.Structure):
     _fields_ = [("struct_size", C.c_uint32), ("device_index", C.c_uint32), ("arch", C.c_int32), ("f32_values", C.c_int32),
                 ("hidden_size", C.c_uint32), ("intermediate_size", C.c_uint32), ("num_layers", C.c_uint32), ("num_heads", C.c_uint32),
@@ -101,6 +111,9 @@ def load_library(build_if_missing: bool = True) -> C.CDLL:
     l.quintrit_b200_plan_run.argtypes = [C.c_void_p, _i8p, _sz, _i32p, _sz]
     l.quintrit_b200_decoder_create.argtypes = [C.POINTER(_DecoderDescC), C.POINTER(C.c_void_p)]
     l.quintrit_b200_decoder_free.argtypes = [C.c_void_p]
+    l.quintrit_b200_decoder_open_gguf.argtypes = [C.c_char_p, C.POINTER(_GpuOptionsC), C.POINTER(C.c_void_p)]
+    l.quintrit_b200_decoder_info.argtypes = [C.c_void_p, C.POINTER(_DecoderInfoC)]
+    l.quintrit_b200_gguf_describe.argtypes = [C.c_char_p, C.c_char_p, _sz, C.POINTER(_sz)]
     l.quintrit_b200_decoder_forward.argtypes = [C.c_void_p, C.c_uint32, C.c_uint32, _f32p, _sz, C.POINTER(C.c_uint32)]
     l.quintrit_b200_decoder_generate.argtypes = [C.c_void_p, C.POINTER(C.c_uint32), _sz, _sz, C.POINTER(C.c_uint32), _sz]
     l.quintrit_b200_decoder_time_token.argtypes = [C.c_void_p, C.c_uint32, C.c_uint32, C.POINTER(C.c_float)]
@@ -345,6 +358,24 @@ class Decoder:
         self._h = h
         self.vocab = spec["vocab"]
 
+    @classmethod
+    def open(cls, path: str, device: int = 0, context: int = 0, flags: int = 0) -> "Decoder":
+        """Loads a GGUF model file onto the GPU (``quintrit_model_open_gpu`` without the tokenizer)."""
+        self = cls.__new__(cls)
+        self.spec, self.matrices = None, []
+        opts = _GpuOptionsC(C.sizeof(_GpuOptionsC), device, context, flags)
+        h = C.c_void_p()
+        _check(load_library().quintrit_b200_decoder_open_gguf(str(path).encode(), C.byref(opts), C.byref(h)))
+        self._h = h
+        self.vocab = self.info()["vocab_size"]
+        return self
+
+    def info(self) -> dict:
+        i = _DecoderInfoC()
+        i.struct_size = C.sizeof(_DecoderInfoC)
+        _check(load_library().quintrit_b200_decoder_info(self._h, C.byref(i)))
+        return {n: getattr(i, n) for n, _ in _DecoderInfoC._fields_ if n != "struct_size"}
+
     def forward(self, token: int, pos: int, want_logits: bool = True):
         """Returns (logits or None, greedy token)."""
         logits = np.zeros(self.vocab, np.float32) if want_logits else None
@@ -393,3 +424,29 @@ def quantize_q8_0(x, device: int = 0):
     q, d = np.zeros(xx.size, np.int8), np.zeros(xx.size // 32, np.float32)
     _check(load_library().quintrit_b200_quantize_q8_0(device, _p(xx, _f32p), xx.size, _p(q, _i8p), _p(d, _f32p)))
     return q, d
+
+
+def gguf_describe(path: str) -> dict:
+    """Hyperparameters and tensor directory of a GGUF file as the library reads them (host only, no GPU)."""
+    n = _sz(0)
+    lib = load_library()
+    rc = lib.quintrit_b200_gguf_describe(str(path).encode(), None, 0, C.byref(n))
+    if rc != 4:  # QUINTRIT_ERR_BUFFER_TOO_SMALL carries the size; anything else is the real outcome
+        _check(rc)
+    buf = C.create_string_buffer(n.value)
+    _check(lib.quintrit_b200_gguf_describe(str(path).encode(), buf, n.value, C.byref(n)))
+    out, tensors = {}, []
+    for line in buf.value.decode().splitlines():
+        key, _, rest = line.partition(" ")
+        if key == "tensor":
+            name, *fields = rest.split(" ")
+            t = {"name": name, "inside_file": "outside-file" not in fields}
+            for f in fields:
+                if "=" in f:
+                    k, v = f.split("=")
+                    t[k] = tuple(int(x) for x in v.split("x")) if k == "shape" else int(v)
+            tensors.append(t)
+        else:
+            out[key] = rest
+    out["tensors"] = tensors
+    return out

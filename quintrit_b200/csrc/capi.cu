@@ -185,6 +185,7 @@ struct DeviceGuard {
 }  // namespace
 
 #include "decoder.cuh"
+#include "gguf.hpp"
 
 // ---------------------------------------------------------------------------------------------------------------------
 // errors, version, devices
@@ -1062,12 +1063,291 @@ extern "C" int quintrit_b200_decoder_create(const quintrit_b200_decoder_desc_t* 
     });
 }
 
+// ---- decoder from a GGUF file ---------------------------------------------------------------------------------------------
+namespace {
+
+struct GgufModelShape {
+    std::string arch;
+    int arch_id = QUINTRIT_B200_ARCH_LLAMA;
+    uint64_t vocab = 0, hidden = 0, inter = 0, layers = 0, heads = 0, kv_heads = 0, head_dim = 0, ctx_train = 0, rope_dims = 0;
+    float eps = 1e-5f, theta = 500000.0f;
+    bool has_i2s = false, has_q2 = false, tied = false;
+};
+
+uint64_t meta_usize(const GgufFile& g, const std::string& key, uint64_t fallback, bool allow_array_max = false) {
+    const GgufValue* v = g.find(key);
+    if (v == nullptr) return fallback;
+    if (v->type == 9) return allow_array_max && v->count > 0 ? v->max_u : fallback;
+    return v->is_int() ? v->u : fallback;
+}
+float meta_f32(const GgufFile& g, const std::string& key, float fallback) {
+    const GgufValue* v = g.find(key);
+    if (v == nullptr) return fallback;
+    if (v->type == 6 || v->type == 12) return static_cast<float>(v->f);
+    return fallback;
+}
+std::string meta_str(const GgufFile& g, const std::string& key, const char* fallback) {
+    const GgufValue* v = g.find(key);
+    return v != nullptr && v->type == 8 ? v->s : std::string(fallback);
+}
+// The hyperparameters as ModelConfig::from_gguf derives them (quintrit-runtime/src/config.rs:257-455): keys are prefixed
+// with general.architecture, missing ones take the reference's defaults, head_dim = attention.key_length or hidden / heads.
+int read_shape(const GgufFile& g, GgufModelShape* out) {
+    GgufModelShape& m = *out;
+    m.arch = meta_str(g, "general.architecture", "bitnet-b1.58");
+    const std::string a = m.arch;
+    if (a == "qwen3" || a == "qwen35" || a == "nemotron_h_moe")
+        return fail(QUINTRIT_ERR_UNSUPPORTED, "architecture '%s' is not supported by the GPU decoder (hybrid, mixture-of-experts and query/key-norm models run on the CPU only)", a.c_str());
+    m.arch_id = (a == "bitnet-b1.58" || a == "bitnet") ? QUINTRIT_B200_ARCH_BITNET : QUINTRIT_B200_ARCH_LLAMA;
+    const GgufTensor* embd = g.tensor("token_embd.weight");
+    uint64_t vocab_fallback = 128256;
+    if (embd != nullptr && embd->shape.size() >= 2) vocab_fallback = embd->shape[1];
+    m.vocab = meta_usize(g, a + ".vocab_size", vocab_fallback);
+    m.hidden = meta_usize(g, a + ".embedding_length", 2560);
+    m.inter = meta_usize(g, a + ".feed_forward_length", 6912, true);
+    m.layers = meta_usize(g, a + ".block_count", 30);
+    m.heads = meta_usize(g, a + ".attention.head_count", 20, true);
+    m.kv_heads = meta_usize(g, a + ".attention.head_count_kv", 5, true);
+    m.eps = meta_f32(g, a + ".attention.layer_norm_rms_epsilon", 1e-5f);
+    m.theta = meta_f32(g, a + ".rope.freq_base", 500000.0f);
+    m.ctx_train = meta_usize(g, a + ".context_length", 4096);
+    if (!m.vocab || !m.hidden || !m.inter || !m.layers || !m.heads || !m.kv_heads || !m.ctx_train || m.vocab > (1u << 24) || m.hidden > (1u << 20) ||
+        m.inter > (1u << 22) || m.layers > 4096 || m.heads > 4096)
+        return fail(QUINTRIT_ERR_MODEL, "the hyperparameters of the file are zero or implausibly large");
+    m.head_dim = meta_usize(g, a + ".attention.key_length", m.hidden / m.heads);
+    if (m.head_dim == 0 || m.head_dim % 2 != 0 || m.head_dim > 4096)
+        return fail(QUINTRIT_ERR_MODEL, "metadata '%s.attention.key_length' = %llu must be even and in 2..=4096", a.c_str(), static_cast<unsigned long long>(m.head_dim));
+    m.rope_dims = meta_usize(g, a + ".rope.dimension_count", m.head_dim);
+    if (m.rope_dims == 0 || m.rope_dims % 2 != 0 || m.rope_dims > m.head_dim)
+        return fail(QUINTRIT_ERR_MODEL, "metadata '%s.rope.dimension_count' = %llu must be even and at most the head dimension %llu", a.c_str(),
+                    static_cast<unsigned long long>(m.rope_dims), static_cast<unsigned long long>(m.head_dim));
+    const std::string scaling = meta_str(g, a + ".rope.scaling.type", "none");
+    if (scaling != "none") return fail(QUINTRIT_ERR_UNSUPPORTED, "RoPE scaling '%s' is not supported by the GPU decoder", scaling.c_str());
+    for (const auto& kv : g.tensors) {
+        m.has_i2s |= kv.second.type == kGgmlI2S;
+        m.has_q2 |= kv.second.type == kGgmlQ2;
+    }
+    m.tied = g.tensor("output.weight") == nullptr;
+    return QUINTRIT_OK;
+}
+
+// One ternary projection: payload view, GGML type and per-tensor scale (gguf.rs:343-358: the f32 behind an I2_S payload, or
+// the f16 scale every TQ block repeats - quintrit-format/src/decoders/mod.rs:121-138 rejects a tensor whose blocks differ).
+int projection(const GgufFile& g, const std::string& name, uint64_t rows, uint64_t cols, const uint8_t** data, uint64_t* len, int32_t* source,
+               float* scale) {
+    const GgufTensor* t = g.tensor(name);
+    if (t == nullptr) return fail(QUINTRIT_ERR_MODEL, "Missing %s", name.c_str());
+    if (t->type != kGgmlI2S && t->type != kGgmlTq1 && t->type != kGgmlTq2)
+        return fail(QUINTRIT_ERR_UNSUPPORTED, "%s has GGML type %u; the GPU decoder needs I2_S, TQ1_0 or TQ2_0 projections", name.c_str(), t->type);
+    if (t->shape.size() != 2 || t->shape[0] != cols || t->shape[1] != rows)
+        return fail(QUINTRIT_ERR_MODEL, "%s does not have the shape %llu x %llu", name.c_str(), static_cast<unsigned long long>(rows), static_cast<unsigned long long>(cols));
+    *data = g.data(*t, len);
+    if (*data == nullptr) return fail(QUINTRIT_ERR_FORMAT, "the payload of %s does not lie inside the file", name.c_str());
+    *source = static_cast<int32_t>(t->type);
+    if (t->type == kGgmlI2S) {
+        if (!g.trailing_scale(*t, scale)) return fail(QUINTRIT_ERR_FORMAT, "the scale of %s does not lie inside the file", name.c_str());
+        return QUINTRIT_OK;
+    }
+    const size_t block = t->type == kGgmlTq1 ? 54 : 66, at = block - 2;
+    uint16_t first = 0;
+    std::memcpy(&first, *data + at, 2);
+    for (uint64_t b = 1; b < *len / block; ++b) {
+        uint16_t h = 0;
+        std::memcpy(&h, *data + b * block + at, 2);
+        if (h != first) return fail(QUINTRIT_ERR_UNSUPPORTED, "%s has block scales that differ; only tensors with one scale are ternary projections", name.c_str());
+    }
+    *scale = __half2float(__ushort_as_half(first));
+    return QUINTRIT_OK;
+}
+
+int open_gguf_impl(const char* path, const quintrit_gpu_options_t* options, quintrit_b200_decoder** out) {
+    uint32_t device = 0, want_ctx = 0;
+    if (options != nullptr) {
+        if (options->struct_size < sizeof(quintrit_gpu_options_t))
+            return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "struct_size %u is smaller than quintrit_gpu_options_t (%zu)", options->struct_size, sizeof(quintrit_gpu_options_t));
+        if (options->flags != 0) return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "unknown flag bits 0x%x", options->flags);
+        device = options->device_index;
+        want_ctx = options->context_length;
+    }
+    GgufFile g;
+    std::string why;
+    const int rc_open = g.open(path, why);
+    if (rc_open == 1) return fail(QUINTRIT_ERR_IO, "%s", why.c_str());
+    if (rc_open != 0) return fail(QUINTRIT_ERR_FORMAT, "%s", why.c_str());
+    GgufModelShape m;
+    int rc = read_shape(g, &m);
+    if (rc != QUINTRIT_OK) return rc;
+    if (m.has_q2) return fail(QUINTRIT_ERR_UNSUPPORTED, "block-scaled (Q2_0) models are not supported by the GPU decoder yet (the projection alone is: quintrit_b200_gemv_block_scaled)");
+    // context: the model's maximum, at most 4096 by default (quintrit.h:502-507), rounded down to a multiple of 256
+    uint64_t ctx = std::min<uint64_t>(m.ctx_train, want_ctx != 0 ? want_ctx : 4096);
+    ctx = std::min<uint64_t>(ctx, 8192) / 256 * 256;
+    if (ctx == 0) return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "the context window is smaller than 256 positions");
+    const uint64_t qd = m.heads * m.head_dim, kvd = m.kv_heads * m.head_dim;
+
+    auto dense_f16 = [&](const char* name, uint64_t n, const uint16_t** outp) -> int {
+        const GgufTensor* t = g.tensor(name);
+        if (t == nullptr) return fail(QUINTRIT_ERR_MODEL, "Missing %s tensor", name);
+        if (t->type != kGgmlF16) return fail(QUINTRIT_ERR_UNSUPPORTED, "%s is not F16; the GPU decoder needs an F16 embedding and head", name);
+        uint64_t len = 0;
+        const uint8_t* p = g.data(*t, &len);
+        if (p == nullptr || len != n * 2) return fail(QUINTRIT_ERR_MODEL, "%s has %llu values, expected %llu", name, static_cast<unsigned long long>(len / 2), static_cast<unsigned long long>(n));
+        *outp = reinterpret_cast<const uint16_t*>(p);
+        return QUINTRIT_OK;
+    };
+    std::vector<std::vector<float>> f32_store;
+    auto dense_f32 = [&](const std::string& name, uint64_t n, const float** outp) -> int {
+        const GgufTensor* t = g.tensor(name);
+        if (t == nullptr || t->type != kGgmlF32) return fail(QUINTRIT_ERR_MODEL, "Missing %s", name.c_str());
+        uint64_t len = 0;
+        const uint8_t* p = g.data(*t, &len);
+        if (p == nullptr || len != n * 4) return fail(QUINTRIT_ERR_MODEL, "%s does not hold %llu values", name.c_str(), static_cast<unsigned long long>(n));
+        f32_store.emplace_back(n);
+        std::memcpy(f32_store.back().data(), p, n * 4);  // tensor payloads are not necessarily 4-byte aligned in memory
+        *outp = f32_store.back().data();
+        return QUINTRIT_OK;
+    };
+
+    std::vector<quintrit_b200_matrix*> mats;
+    auto release = [&]() {
+        for (quintrit_b200_matrix* x : mats) destroy_matrix(x);
+    };
+    std::vector<float> scales;
+    std::vector<const float*> norms;
+    const char* proj_names[7] = {"attn_q", "attn_k", "attn_v", "attn_output", "ffn_gate", "ffn_up", "ffn_down"};
+    const uint64_t shapes[7][2] = {{qd, m.hidden}, {kvd, m.hidden}, {kvd, m.hidden}, {m.hidden, qd}, {m.inter, m.hidden}, {m.inter, m.hidden}, {m.hidden, m.inter}};
+    f32_store.reserve(m.layers * 4 + 1);
+    for (uint64_t l = 0; l < m.layers && rc == QUINTRIT_OK; ++l) {
+        const std::string prefix = "blk." + std::to_string(l) + ".";
+        for (int k = 0; k < 7 && rc == QUINTRIT_OK; ++k) {
+            const uint8_t* data = nullptr;
+            uint64_t len = 0;
+            int32_t source = 0;
+            float scale = 0.0f;
+            rc = projection(g, prefix + proj_names[k] + ".weight", shapes[k][0], shapes[k][1], &data, &len, &source, &scale);
+            if (rc != QUINTRIT_OK) break;
+            quintrit_b200_matrix_t* h = nullptr;
+            rc = quintrit_b200_matrix_upload(device, source, data, len, shapes[k][0], shapes[k][1], &h);
+            if (rc != QUINTRIT_OK) break;
+            mats.push_back(h);
+            scales.push_back(scale);
+        }
+        const char* norm_names[4] = {"attn_norm", "ffn_norm", "attn_sub_norm", "ffn_sub_norm"};
+        const uint64_t norm_len[4] = {m.hidden, m.hidden, m.hidden, m.inter};
+        for (int k = 0; k < 4 && rc == QUINTRIT_OK; ++k) {
+            const float* p = nullptr;
+            if (k < 2 || m.arch_id == QUINTRIT_B200_ARCH_BITNET) rc = dense_f32(prefix + norm_names[k] + ".weight", norm_len[k], &p);
+            norms.push_back(p);
+        }
+    }
+    const uint16_t *embed = nullptr, *head = nullptr;
+    const float* out_norm = nullptr;
+    if (rc == QUINTRIT_OK) rc = dense_f16("token_embd.weight", m.vocab * m.hidden, &embed);
+    if (rc == QUINTRIT_OK && !m.tied) rc = dense_f16("output.weight", m.vocab * m.hidden, &head);
+    if (rc == QUINTRIT_OK) rc = dense_f32("output_norm.weight", m.hidden, &out_norm);
+    if (rc != QUINTRIT_OK) {
+        release();
+        return rc;
+    }
+    quintrit_b200_decoder_desc_t desc;
+    std::memset(&desc, 0, sizeof desc);
+    desc.struct_size = sizeof desc;
+    desc.device_index = device;
+    desc.arch = m.arch_id;
+    desc.f32_values = m.has_i2s ? 0 : 1;  // config.rs:425-429: files with I2_S tensors use the F16-accumulator attention
+    desc.hidden_size = static_cast<uint32_t>(m.hidden), desc.intermediate_size = static_cast<uint32_t>(m.inter);
+    desc.num_layers = static_cast<uint32_t>(m.layers), desc.num_heads = static_cast<uint32_t>(m.heads), desc.num_kv_heads = static_cast<uint32_t>(m.kv_heads);
+    desc.head_dim = static_cast<uint32_t>(m.head_dim), desc.vocab_size = static_cast<uint32_t>(m.vocab), desc.context_length = static_cast<uint32_t>(ctx);
+    desc.rope_dims = static_cast<uint32_t>(m.rope_dims), desc.rms_norm_eps = m.eps, desc.rope_theta = m.theta;
+    desc.embed = embed, desc.lm_head = head, desc.output_norm = out_norm;
+    desc.matrices = reinterpret_cast<const quintrit_b200_matrix_t* const*>(mats.data());
+    desc.scales = scales.data();
+    desc.norms = norms.data();
+    quintrit_b200_decoder* d = nullptr;
+    rc = decoder_create_impl(&desc, &d);
+    if (rc != QUINTRIT_OK) {
+        destroy_decoder(d);
+        release();
+        return rc;
+    }
+    for (quintrit_b200_matrix* x : mats) d->owned_matrices.push_back(x);
+    *out = d;
+    return QUINTRIT_OK;
+}
+
+}  // namespace
+
+extern "C" int quintrit_b200_decoder_open_gguf(const char* path, const quintrit_gpu_options_t* options, quintrit_b200_decoder_t** out_decoder) {
+    return guard([&]() -> int {
+        if (out_decoder == nullptr) return fail(QUINTRIT_ERR_NULL_POINTER, "out_decoder is NULL");
+        *out_decoder = nullptr;
+        if (path == nullptr) return fail(QUINTRIT_ERR_NULL_POINTER, "path is NULL");
+        quintrit_b200_decoder* d = nullptr;
+        const int rc = open_gguf_impl(path, options, &d);
+        if (rc != QUINTRIT_OK) return rc;
+        *out_decoder = d;
+        return ok();
+    });
+}
+
+extern "C" int quintrit_b200_decoder_info(const quintrit_b200_decoder_t* decoder, quintrit_b200_decoder_info_t* out_info) {
+    return guard([&]() -> int {
+        int rc = check_decoder(decoder);
+        if (rc != QUINTRIT_OK) return rc;
+        if (out_info == nullptr) return fail(QUINTRIT_ERR_NULL_POINTER, "out_info is NULL");
+        if (out_info->struct_size < sizeof(quintrit_b200_decoder_info_t))
+            return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "struct_size %u is smaller than quintrit_b200_decoder_info_t (%zu)", out_info->struct_size, sizeof(quintrit_b200_decoder_info_t));
+        const quintrit_b200_decoder* d = decoder;
+        out_info->arch = d->arch, out_info->f32_values = d->f32_values ? 1 : 0;
+        out_info->hidden_size = d->hidden, out_info->intermediate_size = d->inter, out_info->num_layers = d->layers;
+        out_info->num_heads = d->q_heads, out_info->num_kv_heads = d->kv_heads, out_info->head_dim = d->head_dim;
+        out_info->vocab_size = d->vocab, out_info->context_length = d->ctx, out_info->rope_dims = d->rope_dims;
+        out_info->device_index = static_cast<uint32_t>(d->device), out_info->single_kernel = d->use_mega ? 1 : 0;
+        return ok();
+    });
+}
+
+// A GGUF file's directory as text, without touching a GPU: one line per hyperparameter, then one line per tensor
+// ("tensor <name> type=<id> shape=<d0>x<d1>... bytes=<n>"). *out_needed receives the length including the final NUL.
+extern "C" int quintrit_b200_gguf_describe(const char* path, char* out, size_t out_capacity, size_t* out_needed) {
+    return guard([&]() -> int {
+        if (path == nullptr || out_needed == nullptr) return fail(QUINTRIT_ERR_NULL_POINTER, "a pointer is NULL");
+        GgufFile g;
+        std::string why;
+        const int rc_open = g.open(path, why);
+        if (rc_open == 1) return fail(QUINTRIT_ERR_IO, "%s", why.c_str());
+        if (rc_open != 0) return fail(QUINTRIT_ERR_FORMAT, "%s", why.c_str());
+        GgufModelShape m;
+        int rc = read_shape(g, &m);
+        if (rc != QUINTRIT_OK) return rc;
+        std::string text = "version " + std::to_string(g.version) + "\narchitecture " + m.arch + "\nvocab_size " + std::to_string(m.vocab) + "\nhidden_size " +
+                           std::to_string(m.hidden) + "\nintermediate_size " + std::to_string(m.inter) + "\nnum_layers " + std::to_string(m.layers) + "\nnum_heads " +
+                           std::to_string(m.heads) + "\nnum_kv_heads " + std::to_string(m.kv_heads) + "\nhead_dim " + std::to_string(m.head_dim) + "\nrope_dims " +
+                           std::to_string(m.rope_dims) + "\ncontext_length " + std::to_string(m.ctx_train) + "\ntied " + (m.tied ? "1" : "0") + "\nf32_values " +
+                           (m.has_i2s ? "0" : "1") + "\n";
+        char num[64];
+        std::snprintf(num, sizeof num, "rms_norm_eps %.9g\nrope_theta %.9g\n", static_cast<double>(m.eps), static_cast<double>(m.theta));
+        text += num;
+        for (const std::string& name : g.order) {
+            const GgufTensor& t = g.tensors.at(name);
+            text += "tensor " + name + " type=" + std::to_string(t.type) + " shape=";
+            for (size_t i = 0; i < t.shape.size(); ++i) text += (i ? "x" : "") + std::to_string(t.shape[i]);
+            text += " bytes=" + std::to_string(t.byte_len()) + (g.data(t) != nullptr ? "" : " outside-file") + "\n";
+        }
+        *out_needed = text.size() + 1;
+        if (out == nullptr || out_capacity < text.size() + 1) return fail(QUINTRIT_ERR_BUFFER_TOO_SMALL, "out holds %zu bytes, %zu are needed", out_capacity, text.size() + 1);
+        std::memcpy(out, text.c_str(), text.size() + 1);
+        return ok();
+    });
+}
+
 extern "C" int quintrit_b200_decoder_free(quintrit_b200_decoder_t* decoder) {
     return guard([&]() -> int {
         if (decoder == nullptr) return ok();
         int rc = check_decoder(decoder);
         if (rc != QUINTRIT_OK) return rc;
+        const std::vector<void*> owned = decoder->owned_matrices;
         destroy_decoder(decoder);
+        for (void* m : owned) destroy_matrix(static_cast<quintrit_b200_matrix*>(m));
         return ok();
     });
 }

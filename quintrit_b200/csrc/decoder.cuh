@@ -21,6 +21,7 @@ struct quintrit_b200_decoder {
     std::vector<float> scales;  // layers * 7
     // device memory
     std::vector<void*> allocs;
+    std::vector<void*> owned_matrices;  // matrix handles created by the GGUF loader; released with the decoder
     __half *embed, *lm_head, *kc, *vc, *x16;
     float *out_norm, *cos_sin, *x, *q, *part_acc, *part_ms, *logits;
     float* scores = nullptr;  // single-kernel path: attention scores of the current token, [q_heads][ctx]

@@ -1,0 +1,119 @@
+"""Models loaded from synthetic GGUF files through quintrit_b200_decoder_open_gguf against the CPU oracle built from the
+same tensors: logits bit for bit and identical greedy tokens for each ternary encoding (I2_S -> FP16-accumulator
+attention, TQ1_0 / TQ2_0 -> FP32 accumulators, as rust/crates/quintrit-runtime/src/config.rs:425-429 selects), a BitNet
+file with sub-norms and a tied head, and the loader's rejections (rust/crates/quintrit-runtime/src/gpu.rs:149-181)."""
+import struct
+
+import numpy as np
+import pytest
+
+import oracle
+import quintrit_b200 as q
+from quintrit_b200 import gguf_io, synth
+
+pytestmark = pytest.mark.gpu
+
+
+def _model(arch, f32_values, config, tied=False):
+    spec = synth.make_model(arch, f32_values, 256, 512, 2, 4, 2, 64, 300, 512, 500000.0, 1e-5, config=config, random_norms=True, tied=tied)
+    shapes = [(256, 256), (128, 256), (128, 256), (256, 256), (512, 256), (512, 256), (256, 512)]
+    trits = [synth.trits(synth.seed_for(config, l, p, 0), r * c).reshape(r, c) for l in range(2) for p, (r, c) in enumerate(shapes)]
+    return spec, trits
+
+
+@pytest.mark.parametrize("encoding,f32_values", [(gguf_io.GGML_I2_S, False), (gguf_io.GGML_TQ2_0, True), (gguf_io.GGML_TQ1_0, True)])
+def test_llama_file_decodes_like_the_oracle(tmp_path, encoding, f32_values):
+    spec, trits = _model(q.ARCH_LLAMA, f32_values, 11)
+    if encoding != gguf_io.GGML_I2_S:
+        spec["scales"] = np.float32(np.float16(spec["scales"]))  # the tensor scale is the f16 of every block
+    path = tmp_path / "model.gguf"
+    gguf_io.write_model_gguf(path, spec, trits, encoding)
+    dec = q.Decoder.open(path)
+    info = dec.info()
+    assert (info["hidden_size"], info["num_layers"], info["num_heads"], info["num_kv_heads"], info["head_dim"], info["vocab_size"]) == (256, 2, 4, 2, 64, 300)
+    assert info["f32_values"] == int(f32_values) and info["context_length"] == 512 and info["arch"] == q.ARCH_LLAMA
+    ref = oracle.Model(spec)
+    tokens = synth.prompt_tokens(3, 12, spec["vocab"])
+    for pos, tok in enumerate(tokens):
+        want = ref.forward(int(tok), pos)
+        got, greedy = dec.forward(int(tok), pos)
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), (encoding, pos)
+        assert greedy == oracle.argmax(want)
+    # generate from the file-backed decoder = greedy loop of the oracle
+    out = dec.generate(tokens[:4], 5)
+    ref2 = oracle.Model(spec)
+    for pos, tok in enumerate(tokens[:4]):
+        last = ref2.forward(int(tok), pos)
+    want_tokens = []
+    for i in range(5):
+        t = oracle.argmax(last)
+        want_tokens.append(t)
+        last = ref2.forward(t, 4 + i)
+    assert list(out) == want_tokens
+    dec.free()
+
+
+def test_bitnet_file_with_sub_norms_and_tied_head(tmp_path):
+    spec, trits = _model(q.ARCH_BITNET, False, 12, tied=True)
+    path = tmp_path / "bitnet.gguf"
+    gguf_io.write_model_gguf(path, spec, trits, gguf_io.GGML_I2_S, architecture="bitnet-b1.58")
+    dec = q.Decoder.open(path, context=256)
+    assert dec.info()["arch"] == q.ARCH_BITNET and dec.info()["context_length"] == 256
+    spec = dict(spec, ctx=256)
+    ref = oracle.Model(spec)
+    for pos, tok in enumerate(synth.prompt_tokens(4, 6, spec["vocab"])):
+        want = ref.forward(int(tok), pos)
+        got, _ = dec.forward(int(tok), pos)
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), pos
+    dec.free()
+
+
+def test_rejections(tmp_path):
+    spec, trits = _model(q.ARCH_LLAMA, False, 13)
+
+    def code(path, **kw):
+        with pytest.raises(q.QuintritError) as e:
+            q.Decoder.open(path, **kw)
+        return e.value.code, str(e.value)
+
+    assert code(tmp_path / "nope.gguf")[0] == 7
+    junk = tmp_path / "junk.gguf"
+    junk.write_bytes(b"not a model" * 10)
+    assert code(junk)[0] == 8
+    good = tmp_path / "good.gguf"
+    gguf_io.write_model_gguf(good, spec, trits, gguf_io.GGML_I2_S)
+    assert code(good, flags=1)[0] == 2                      # unknown flag bits
+    assert code(good, context=100)[0] == 2                  # below 256 positions
+    # a file with a Q2_0 tensor is refused like the reference's GPU loader refuses it
+    q2 = tmp_path / "q2.gguf"
+    meta = {"general.architecture": "llama", "llama.embedding_length": 256, "llama.attention.head_count": 4, "llama.vocab_size": 300}
+    gguf_io.write_gguf(q2, meta, [("blk.0.attn_q.weight", (256, 256), gguf_io.GGML_Q2_0,
+                                   gguf_io.encode_q2_0(trits[0], np.ones(256 * 256 // 64, np.float16)).tobytes())])
+    c, msg = code(q2)
+    assert c == 6 and "Q2_0" in msg
+    # a missing projection names the tensor
+    miss = tmp_path / "miss.gguf"
+    gguf_io.write_gguf(miss, dict(meta, **{"llama.block_count": 1, "llama.feed_forward_length": 512, "llama.attention.head_count_kv": 2,
+                                          "llama.attention.key_length": 64, "llama.context_length": 512}), [])
+    c, msg = code(miss)
+    assert c == 10 and "blk.0.attn_q.weight" in msg
+    # payloads cut off: format error, not a crash
+    raw = good.read_bytes()
+    cut = tmp_path / "cut.gguf"
+    cut.write_bytes(raw[: len(raw) // 2])
+    assert code(cut)[0] in (8, 10)
+    # TQ tensor whose blocks disagree on the scale is not a ternary projection (decoders/mod.rs:121-138)
+    spec2 = dict(spec, scales=np.float32(np.float16(spec["scales"])))
+    tq = tmp_path / "tq.gguf"
+    gguf_io.write_model_gguf(tq, spec2, trits, gguf_io.GGML_TQ2_0)
+    data = bytearray(tq.read_bytes())
+    d = q.gguf_describe(tq)
+    first = next(t for t in d["tensors"] if t["name"] == "blk.0.attn_q.weight")
+    # find the payload: the second block's scale bytes sit 66 + 64 bytes into it; locate it through the known first block
+    blk = gguf_io.encode_tq2_0(trits[0], int(np.float16(spec2["scales"][0]).view(np.uint16))).tobytes()
+    at = bytes(data).find(blk[:132])
+    assert at > 0 and first["bytes"] == len(blk)
+    data[at + 66 + 64] ^= 0x01
+    tq.write_bytes(bytes(data))
+    c, msg = code(tq)
+    assert c == 6 and "block scales" in msg

@@ -8,32 +8,15 @@ import numpy as np
 import pytest
 
 
+from quintrit_b200.gguf_io import encode_tq1_0 as _enc1, encode_tq2_0 as _enc2
+
+
 def encode_tq2_0(trits, d_bits=0x3800):
-    """256 trits per block: four 2-bit planes of 32 per group of 32 bytes, plane 0 in the low bits, then the f16 scale."""
-    t = np.asarray(trits, np.int64).reshape(-1, 2, 4, 32) + 1
-    q = (t << (2 * np.arange(4)).reshape(1, 1, 4, 1)).sum(axis=2).astype(np.uint8)  # [blocks, 2, 32]
-    blocks = np.zeros((q.shape[0], 66), np.uint8)
-    blocks[:, :64] = q.reshape(-1, 64)
-    blocks[:, 64] = d_bits & 0xFF
-    blocks[:, 65] = d_bits >> 8
-    return blocks
+    return _enc2(trits, d_bits).reshape(-1, 66)
 
 
 def encode_tq1_0(trits, d_bits=0x3800):
-    """256 trits per block as base-3 fractions (first trit most significant), rounded up: q = ceil(v * 256 / 243)."""
-    t = np.asarray(trits, np.int64).reshape(-1, 256) + 1
-    nb = t.shape[0]
-    blocks = np.zeros((nb, 54), np.uint8)
-    ceil = lambda v: (v * 256 + 242) // 243
-    a = t[:, :160].reshape(nb, 5, 32)
-    blocks[:, :32] = ceil(sum(a[:, n] * 3 ** (4 - n) for n in range(5)))
-    b = t[:, 160:240].reshape(nb, 5, 16)
-    blocks[:, 32:48] = ceil(sum(b[:, n] * 3 ** (4 - n) for n in range(5)))
-    c = t[:, 240:].reshape(nb, 4, 4)
-    blocks[:, 48:52] = ceil(sum(c[:, n] * 3 ** (3 - n) for n in range(4)) * 3)
-    blocks[:, 52] = d_bits & 0xFF
-    blocks[:, 53] = d_bits >> 8
-    return blocks
+    return _enc1(trits, d_bits).reshape(-1, 54)
 
 
 def _trits(n, seed):
