@@ -227,6 +227,65 @@ def measured_peaks():
         return 6650.0, "fallback"
 
 
+def run_decode_tp(args, rank: int, world: int, local_rank: int, dist):
+    """Whole-token decode of the Falcon3-10B shape split over `world` GPUs (tensor parallel: every rank streams 1/world of
+    every projection; slices are exchanged inside the token kernel over NVLink peer stores). Every rank calls this; rank 0
+    returns the result object. Parity: the group's greedy tokens against a one-GPU decoder of the whole model on rank 0."""
+    import torch
+
+    import quintrit_b200 as q
+
+    dev = torch.device("cuda", local_rank)
+    ctx = (args.prompt + args.steps + 64 + 255) // 256 * 256
+    shape = {"falcon3_10b": (12, 4, 3072, 23040, 131072), "bitnet_2b": (20, 5, 2560, 6912, 128256)}[args.decode_shape]
+    if args.decode_shape != "falcon3_10b" or shape[1] % world or shape[2] % world or shape[3] % world or shape[4] % world:
+        return {"tp_world": world, "skipped": f"{world} ranks do not divide the KV heads ({shape[1]}) of {args.decode_shape}"} if rank == 0 else None
+    npar, ngen = 6, 6
+    short = synth.prompt_tokens(2, npar, shape[4])
+    want = None
+    if rank == 0:  # the one-GPU answer for the same seeded model
+        full = synth.torch_model(args.decode_shape, dev, ctx, layers=args.decode_layers)
+        one = q.Decoder(full, device=local_rank)
+        want = [int(t) for t in one.generate(short, ngen)]
+        one.free()
+        del full, one
+        torch.cuda.empty_cache()
+    dist.barrier()
+    t0 = time.time()
+    spec = synth.torch_model(args.decode_shape, dev, ctx, layers=args.decode_layers, tp=(rank, world))
+    dec = q.Decoder(spec, device=local_rank)
+    handles = [None] * world
+    dist.all_gather_object(handles, dec.tp_handle())
+    dec.tp_attach(handles)
+    dist.barrier()  # every rank has mapped every box before the first token kernel starts
+    setup_s = time.time() - t0
+    got = [int(t) for t in dec.generate(short, ngen)]
+    gathered = [None] * world
+    dist.all_gather_object(gathered, got)
+    prompt = synth.prompt_tokens(2, args.prompt, spec["vocab"])
+    dec.generate(prompt, 1)
+    dist.barrier()
+    dec.time_token(1, max(3, args.warmup))
+    dist.barrier()
+    step_ms = dec.time_token(1, args.steps)
+    best_ms = dec.time_token(5, max(args.steps, 50))
+    t = torch.tensor([step_ms, best_ms], device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    step_ms, best_ms = t.tolist()
+    dist.barrier()
+    dec.free()
+    if rank != 0:
+        return None
+    weights = sum(n * k for _, _, n, k in sweep_shapes(spec["layers"]))
+    bytes_tok = weights * BYTES_PER_WEIGHT
+    return {"shape": spec["shape"], "layers": spec["layers"], "context": args.prompt, "tp_world": world, "tokens_per_s": round(1e3 / step_ms, 1),
+            "ms_per_token": round(step_ms, 4), "best_ms_per_token": round(best_ms, 4), "velurex_bytes_per_token": int(bytes_tok),
+            "roofline_nominal_8tbs_frac": round(bytes_tok / (step_ms * 1e-3) / (world * 8e12), 4), "exchanges_per_token": 4 * spec["layers"] + 1,
+            "transport": "peer stores into every rank's box inside the token kernel, flags with release/acquire at system scope",
+            "parity": {"greedy_tokens_checked": ngen, "all_ranks_agree": all(g == got for g in gathered), "identical_to_one_gpu": got == want},
+            "setup_s": round(setup_s, 1)}
+
+
 def run_reference(args, rank: int, world: int):
     """--impl reference: the CPU path, timed on the host cores (rank 0 only)."""
     if rank != 0:
@@ -267,7 +326,9 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     if world > 1:
         import torch.distributed as dist  # noqa: F811
 
-        dist.init_process_group("nccl", device_id=dev)
+        import datetime
+
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=180))  # a rank that fell out does not hang the others forever
 
     # ---- build the sweep: weights generated on the device, transcoded by the library ----
     t_setup = time.time()
@@ -358,6 +419,14 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         ok = torch.tensor([1 if same else 0], device=dev)
         dist.all_reduce(ok, op=dist.ReduceOp.MIN)
         same = bool(ok.item())
+    decode_tp = None
+    if dist is not None and not args.no_decode:
+        del plan, mats
+        torch.cuda.empty_cache()
+        try:
+            decode_tp = run_decode_tp(args, rank, world, local_rank, dist)
+        except Exception as e:  # the sweep line must still be printed
+            decode_tp = {"tp_world": world, "error": f"{type(e).__name__}: {e}"}
     if rank != 0:
         if dist is not None:
             dist.destroy_process_group()
@@ -388,6 +457,8 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         "deterministic": same,
         "setup_s": round(t_setup, 1),
     }
+    if decode_tp is not None:
+        line["decode"] = decode_tp
     if world == 1 and not args.no_decode:
         del plan, mats
         torch.cuda.empty_cache()

@@ -209,10 +209,32 @@ typedef struct quintrit_b200_decoder_desc {
     const quintrit_b200_matrix_t* const* matrices;
     const float* scales;
     const float* const* norms;
+    /* Tensor parallelism (fields added after the first version of the struct; a smaller struct_size means one GPU).
+     * tp_world in {1, 2, 4, 8} ranks, one process and one GPU each, share the model: the dimensions above stay those of
+     * the whole model, and this rank supplies its rows of every projection - q / k / v for its num_heads / tp_world query
+     * heads and num_kv_heads / tp_world KV heads, rows [tp_rank * n / tp_world, (tp_rank + 1) * n / tp_world) of o, gate,
+     * up and down - and, if lm_head is not NULL, its vocab_size / tp_world rows of the head (embed stays whole). After
+     * creation the ranks exchange quintrit_b200_decoder_tp_handle and call quintrit_b200_decoder_tp_attach. */
+    uint32_t tp_rank, tp_world;
 } quintrit_b200_decoder_desc_t;
 
 int quintrit_b200_decoder_create(const quintrit_b200_decoder_desc_t* desc, quintrit_b200_decoder_t** out_decoder);
 int quintrit_b200_decoder_free(quintrit_b200_decoder_t* decoder);
+
+/*
+ * Tensor-parallel group set-up (no counterpart in the reference, whose GPU decoder runs on one GPU): every rank's decoder
+ * owns an exchange box in device memory into which the other ranks' kernels write their slices of the vectors every rank
+ * needs whole (attention output, o and down results, SwiGLU output, greedy candidates) over NVLink peer stores.
+ * quintrit_b200_decoder_tp_handle writes the 64-byte inter-process handle of this rank's box; the caller gathers the
+ * handles of all ranks in rank order (any host transport: the benchmark uses torch.distributed) and passes the
+ * tp_world * 64 bytes to quintrit_b200_decoder_tp_attach, which maps the peers' boxes. All ranks must then make the same
+ * sequence of forward / generate / time_token calls; a rank that does not show up within two seconds makes the others
+ * return QUINTRIT_ERR_DEVICE instead of waiting forever. quintrit_b200_decoder_forward returns this rank's
+ * vocab_size / tp_world logits (rows tp_rank * vocab_size / tp_world onward); the greedy token is the global one.
+ */
+#define QUINTRIT_B200_TP_HANDLE_BYTES 64
+int quintrit_b200_decoder_tp_handle(const quintrit_b200_decoder_t* decoder, uint8_t* out_handle, size_t out_capacity);
+int quintrit_b200_decoder_tp_attach(quintrit_b200_decoder_t* decoder, const uint8_t* handles, size_t handles_len);
 
 /* Options of quintrit_b200_decoder_open_gguf: the struct of quintrit.h:502-507 (same fields and meaning; no flag is
  * defined here, so flags must be 0; the context is capped at 8192 instead of 7936). */

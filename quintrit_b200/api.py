@@ -53,7 +53,7 @@ class _DecoderDescC(C.Structure):
                 ("num_kv_heads", C.c_uint32), ("head_dim", C.c_uint32), ("vocab_size", C.c_uint32), ("context_length", C.c_uint32),
                 ("rope_dims", C.c_uint32), ("rms_norm_eps", C.c_float), ("rope_theta", C.c_float), ("embed", C.POINTER(C.c_uint16)),
                 ("lm_head", C.POINTER(C.c_uint16)), ("output_norm", _f32p), ("matrices", C.POINTER(C.c_void_p)), ("scales", _f32p),
-                ("norms", C.POINTER(_f32p))]
+                ("norms", C.POINTER(_f32p)), ("tp_rank", C.c_uint32), ("tp_world", C.c_uint32)]
 
 
 @dataclass
@@ -111,6 +111,8 @@ def load_library(build_if_missing: bool = True) -> C.CDLL:
     l.quintrit_b200_plan_run.argtypes = [C.c_void_p, _i8p, _sz, _i32p, _sz]
     l.quintrit_b200_decoder_create.argtypes = [C.POINTER(_DecoderDescC), C.POINTER(C.c_void_p)]
     l.quintrit_b200_decoder_free.argtypes = [C.c_void_p]
+    l.quintrit_b200_decoder_tp_handle.argtypes = [C.c_void_p, _u8p, _sz]
+    l.quintrit_b200_decoder_tp_attach.argtypes = [C.c_void_p, _u8p, _sz]
     l.quintrit_b200_decoder_open_gguf.argtypes = [C.c_char_p, C.POINTER(_GpuOptionsC), C.POINTER(C.c_void_p)]
     l.quintrit_b200_decoder_info.argtypes = [C.c_void_p, C.POINTER(_DecoderInfoC)]
     l.quintrit_b200_gguf_describe.argtypes = [C.c_char_p, C.c_char_p, _sz, C.POINTER(_sz)]
@@ -322,7 +324,9 @@ class Decoder:
         self.spec = spec
         L, H, I, hd = spec["layers"], spec["hidden"], spec["inter"], spec["head_dim"]
         qd, kvd = spec["q_heads"] * hd, spec["kv_heads"] * hd
-        shapes = [(qd, H), (kvd, H), (kvd, H), (H, qd), (I, H), (I, H), (H, I)]
+        self.tp_rank, self.tp_world = spec.get("tp_rank", 0), spec.get("tp_world", 1)
+        w = self.tp_world  # a rank of a tensor-parallel group holds its rows of every projection (synth.shard_spec)
+        shapes = [(qd // w, H), (kvd // w, H), (kvd // w, H), (H // w, qd), (I // w, H), (I // w, H), (H // w, I)]
         self.matrices = []
         for i, w in enumerate(spec["weights"]):
             rows, cols = shapes[i % 7]
@@ -353,10 +357,22 @@ class Decoder:
         d.lm_head = None if head is None else _p(head, C.POINTER(C.c_uint16))
         d.output_norm = _p(out_norm, _f32p)
         d.matrices, d.scales, d.norms = mats, _p(scales, _f32p), norms
+        d.tp_rank, d.tp_world = self.tp_rank, self.tp_world
         h = C.c_void_p()
         _check(load_library().quintrit_b200_decoder_create(C.byref(d), C.byref(h)))
         self._h = h
-        self.vocab = spec["vocab"]
+        self.vocab = spec["vocab"] // self.tp_world  # logits returned by forward(): this rank's rows of the vocabulary
+
+    def tp_handle(self) -> bytes:
+        """The 64-byte inter-process handle of this rank's exchange box (tensor-parallel decoders)."""
+        out = np.zeros(64, np.uint8)
+        _check(load_library().quintrit_b200_decoder_tp_handle(self._h, _p(out, _u8p), out.size))
+        return out.tobytes()
+
+    def tp_attach(self, handles) -> None:
+        """Maps the boxes of all ranks; `handles` are the tp_handle() bytes of every rank in rank order."""
+        raw = np.frombuffer(b"".join(handles), np.uint8).copy()
+        _check(load_library().quintrit_b200_decoder_tp_attach(self._h, _p(raw, _u8p), raw.size))
 
     @classmethod
     def open(cls, path: str, device: int = 0, context: int = 0, flags: int = 0) -> "Decoder":

@@ -789,21 +789,37 @@ int decoder_create_impl(const quintrit_b200_decoder_desc_t* desc, quintrit_b200_
         return fail(QUINTRIT_ERR_NULL_POINTER, "a required pointer of the decoder description is NULL");
     if (desc->arch != QUINTRIT_B200_ARCH_LLAMA && desc->arch != QUINTRIT_B200_ARCH_BITNET)
         return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "unknown architecture %d", desc->arch);
-    const uint32_t H = desc->hidden_size, I = desc->intermediate_size, L = desc->num_layers, hd = desc->head_dim;
-    if (!H || !I || !L || !desc->num_heads || !desc->num_kv_heads || !hd || !desc->vocab_size)
+    // tensor parallelism: the fields exist only in descriptions of the newer size
+    uint32_t tp_rank = 0, tp_world = 1;
+    if (desc->struct_size >= offsetof(quintrit_b200_decoder_desc_t, tp_world) + sizeof(uint32_t) && desc->tp_world != 0) {
+        tp_rank = desc->tp_rank, tp_world = desc->tp_world;
+    }
+    if (tp_world != 1 && tp_world != 2 && tp_world != 4 && tp_world != 8) return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "tp_world %u must be 1, 2, 4 or 8", tp_world);
+    if (tp_rank >= tp_world) return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "tp_rank %u is not below tp_world %u", tp_rank, tp_world);
+    const uint32_t H = desc->hidden_size, I_full = desc->intermediate_size, L = desc->num_layers, hd = desc->head_dim;
+    if (!H || !I_full || !L || !desc->num_heads || !desc->num_kv_heads || !hd || !desc->vocab_size)
         return fail(QUINTRIT_ERR_MODEL, "a model dimension is zero");
+    if (tp_world > 1) {
+        if (desc->arch != QUINTRIT_B200_ARCH_LLAMA) return fail(QUINTRIT_ERR_UNSUPPORTED, "tensor parallelism is available for the LLaMA / Falcon3 architecture only");
+        if (desc->num_kv_heads % tp_world || H % tp_world || I_full % tp_world || desc->vocab_size % tp_world)
+            return fail(QUINTRIT_ERR_UNSUPPORTED, "tp_world %u must divide the KV heads (%u), the hidden size, the FFN size and the vocabulary", tp_world,
+                        desc->num_kv_heads);
+    }
+    const uint32_t I = I_full / tp_world;  // this rank's rows of gate and up
     if (hd % 32 != 0 || hd > 256) return fail(QUINTRIT_ERR_UNSUPPORTED, "head_dim %u is not supported (a multiple of 32, at most 256)", hd);
     if (desc->num_heads % desc->num_kv_heads != 0) return fail(QUINTRIT_ERR_MODEL, "num_heads is not a multiple of num_kv_heads");
     if (desc->rope_dims == 0 || desc->rope_dims % 2 != 0 || desc->rope_dims > hd)
         return fail(QUINTRIT_ERR_MODEL, "rope_dims %u must be even and at most the head dimension %u", desc->rope_dims, hd);
     const uint32_t ctx = desc->context_length / 256 * 256;  // gpu.rs:141-146
     if (ctx == 0 || ctx > 8192) return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "context_length %u must give 256..8192 after rounding down to a multiple of 256", desc->context_length);
-    const size_t qd = size_t(desc->num_heads) * hd, kvd = size_t(desc->num_kv_heads) * hd;
-    if (std::max<size_t>({H, I, qd}) * sizeof(float) > 200 * 1024) return fail(QUINTRIT_ERR_UNSUPPORTED, "a vector of the model does not fit the shared memory of one block");
+    const size_t qd_full = size_t(desc->num_heads) * hd;
+    const size_t qd = qd_full / tp_world, kvd = size_t(desc->num_kv_heads) * hd / tp_world;  // this rank's query and KV widths
+    const uint32_t vocab_local = desc->vocab_size / tp_world;
+    if (std::max<size_t>({H, I_full, qd_full}) * sizeof(float) > 200 * 1024) return fail(QUINTRIT_ERR_UNSUPPORTED, "a vector of the model does not fit the shared memory of one block");
     cudaDeviceProp prop;
     int rc = require_b200(static_cast<int>(desc->device_index), &prop);
     if (rc != QUINTRIT_OK) return rc;
-    const size_t shapes[7][2] = {{qd, H}, {kvd, H}, {kvd, H}, {H, qd}, {I, H}, {I, H}, {H, I}};
+    const size_t shapes[7][2] = {{qd, H}, {kvd, H}, {kvd, H}, {H / tp_world, qd_full}, {I, H}, {I, H}, {H / tp_world, I_full}};
     for (size_t i = 0; i < size_t(L) * 7; ++i) {
         const quintrit_b200_matrix* m = desc->matrices[i];
         rc = check_matrix(m);
@@ -819,8 +835,10 @@ int decoder_create_impl(const quintrit_b200_decoder_desc_t* desc, quintrit_b200_
     d->device = static_cast<int>(desc->device_index);
     d->sm_count = prop.multiProcessorCount;
     d->arch = desc->arch, d->f32_values = desc->f32_values != 0;
-    d->hidden = H, d->inter = I, d->layers = L, d->q_heads = desc->num_heads, d->kv_heads = desc->num_kv_heads, d->head_dim = hd;
-    d->vocab = desc->vocab_size, d->ctx = ctx, d->rope_dims = desc->rope_dims, d->q_dim = static_cast<int>(qd), d->kv_dim = static_cast<int>(kvd);
+    d->hidden = H, d->inter = I, d->layers = L, d->q_heads = desc->num_heads / tp_world, d->kv_heads = desc->num_kv_heads / tp_world, d->head_dim = hd;
+    d->tp_rank = static_cast<int>(tp_rank), d->tp_world = static_cast<int>(tp_world);
+    d->q_dim_full = static_cast<int>(qd_full), d->inter_full = static_cast<int>(I_full), d->vocab_full = static_cast<int>(desc->vocab_size);
+    d->vocab = vocab_local, d->ctx = ctx, d->rope_dims = desc->rope_dims, d->q_dim = static_cast<int>(qd), d->kv_dim = static_cast<int>(kvd);
     d->eps = desc->rms_norm_eps, d->rope_theta = desc->rope_theta;
     d->scales.assign(desc->scales, desc->scales + size_t(L) * 7);
     d->graph_ready = false;
@@ -851,9 +869,9 @@ int decoder_create_impl(const quintrit_b200_decoder_desc_t* desc, quintrit_b200_
         }
         if ((rc = dev_upload(d, &d->cos_sin, cs.data(), cs.size())) != QUINTRIT_OK) return rc;
     }
-    if ((rc = dev_upload(d, &d->embed, desc->embed, size_t(d->vocab) * H)) != QUINTRIT_OK) return rc;
-    d->lm_head = d->embed;
-    if (desc->lm_head && (rc = dev_upload(d, &d->lm_head, desc->lm_head, size_t(d->vocab) * H)) != QUINTRIT_OK) return rc;
+    if ((rc = dev_upload(d, &d->embed, desc->embed, size_t(desc->vocab_size) * H)) != QUINTRIT_OK) return rc;
+    d->lm_head = d->embed + size_t(tp_rank) * vocab_local * H;  // tied head: this rank's rows of the embedding
+    if (desc->lm_head && (rc = dev_upload(d, &d->lm_head, desc->lm_head, size_t(vocab_local) * H)) != QUINTRIT_OK) return rc;
     if ((rc = dev_upload(d, &d->out_norm, desc->output_norm, H)) != QUINTRIT_OK) return rc;
     d->norms.assign(size_t(L) * 4, nullptr);
     for (size_t i = 0; i < size_t(L) * 4; ++i) {
@@ -921,7 +939,7 @@ int decoder_create_impl(const quintrit_b200_decoder_desc_t* desc, quintrit_b200_
     // the single-kernel path stages KV rows with a piece permutation that needs a power-of-two head_dim of at least 64
     // and one values unit of the longest chunk must fit the shared memory of an SM next to the activation vectors
     const int gqa_n = d->q_heads / d->kv_heads;
-    const size_t mega_bytes = mega_smem_bytes(mega_attn_region(d->ctx, gqa_n, hd), static_cast<int>(std::max<size_t>(H, qd)), static_cast<int>(H), static_cast<int>(L));
+    const size_t mega_bytes = mega_smem_bytes(mega_attn_region(d->ctx, gqa_n, hd), static_cast<int>(std::max<size_t>(H, qd_full)), static_cast<int>(H), static_cast<int>(L));
     int smem_optin = 0;
     QTB_CUDA(cudaDeviceGetAttribute(&smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, d->device));
     const bool staged_ok = hd >= 64 && (hd & (hd - 1)) == 0 && gqa_n <= 16 && mega_bytes <= static_cast<size_t>(smem_optin);
@@ -929,6 +947,7 @@ int decoder_create_impl(const quintrit_b200_decoder_desc_t* desc, quintrit_b200_
         if ((rc = mega_setup(d, desc)) != QUINTRIT_OK) return rc;
         d->use_mega = true;
     }
+    if (tp_world > 1 && !d->use_mega) return fail(QUINTRIT_ERR_UNSUPPORTED, "tensor parallelism needs the single-kernel decode path, which does not take this model");
     QTB_CUDA(cudaDeviceSynchronize());
     return QUINTRIT_OK;
 }
@@ -962,6 +981,18 @@ int mega_bind(quintrit_b200_decoder* d) {
 int mega_setup(quintrit_b200_decoder* d, const quintrit_b200_decoder_desc_t* desc) {
     const int L = d->layers, H = d->hidden, I = d->inter, qd = d->q_dim, kvd = d->kv_dim;
     int rc;
+    // Tensor parallelism: the vectors every rank needs whole live in one allocation (the "box") that the peers map.
+    const auto up256 = [](size_t n) { return (n + 255) / 256 * 256; };
+    const size_t off_acc_o = 0, off_acc_down = up256(off_acc_o + size_t(H) * 4), off_y = up256(off_acc_down + size_t(H) * 4),
+                 off_v = up256(off_y + size_t(d->q_dim_full) * 4), off_amax = up256(off_v + size_t(d->inter_full) * 4), off_best = off_amax + 256,
+                 off_flags = off_best + 256, box_bytes = off_flags + 256;
+    if (d->tp_world > 1) {
+        if ((rc = dev_alloc(d, &d->tp_box, box_bytes)) != QUINTRIT_OK || (rc = dev_alloc(d, &d->tp_seq, 4)) != QUINTRIT_OK) return rc;
+        d->tp_box_bytes = box_bytes;
+        d->acc_o = reinterpret_cast<int32_t*>(d->tp_box + off_acc_o);  // replaces the private buffers allocated for one GPU
+        d->acc_down = reinterpret_cast<int32_t*>(d->tp_box + off_acc_down);
+    }
+    const size_t slice_off = size_t(d->tp_rank) * (H / d->tp_world);  // first row of this rank in the o and down results
     if ((rc = dev_alloc(d, &d->xa, H)) != QUINTRIT_OK || (rc = dev_alloc(d, &d->xb, H)) != QUINTRIT_OK ||
         (rc = dev_alloc(d, &d->v_inter, I)) != QUINTRIT_OK || (rc = dev_alloc(d, &d->amax_bits, 4)) != QUINTRIT_OK ||
         (rc = dev_alloc(d, &d->best_val, d->sm_count)) != QUINTRIT_OK || (rc = dev_alloc(d, &d->best_idx, d->sm_count)) != QUINTRIT_OK ||
@@ -973,7 +1004,7 @@ int mega_setup(quintrit_b200_decoder* d, const quintrit_b200_decoder_desc_t* des
     for (int l = 0; l < L; ++l) {
         const quintrit_b200_matrix* const* m = desc->matrices + size_t(l) * 7;
         MegaLayer& ly = layers[l];
-        const size_t o_qkv[3] = {0, size_t(qd), size_t(qd + kvd)}, o_zero[1] = {0}, o_gu[2] = {0, size_t(I)};
+        const size_t o_qkv[3] = {0, size_t(qd), size_t(qd + kvd)}, o_zero[1] = {slice_off}, o_gu[2] = {0, size_t(I)};
         auto phase = [&](int k, const quintrit_b200_matrix* const* ms, const size_t* offs, int n) {
             ly.first[k] = static_cast<int>(items.size());
             mega_phase_items(items, ms, offs, n, d->sm_count);
@@ -1003,9 +1034,17 @@ int mega_setup(quintrit_b200_decoder* d, const quintrit_b200_decoder_desc_t* des
     a.acc_qkv = d->acc_qkv, a.acc_o = d->acc_o, a.acc_gu = d->acc_gu, a.acc_down = d->acc_down;
     a.v_inter = d->v_inter, a.amax_bits = d->amax_bits, a.part_acc = d->part_acc, a.part_ms = d->part_ms, a.logits = d->logits;
     a.scores = d->scores, a.attn_region = static_cast<unsigned int>(mega_attn_region(d->ctx, d->q_heads / d->kv_heads, d->head_dim));
+    a.tp_rank = d->tp_rank, a.tp_world = d->tp_world, a.tp_seq = d->tp_seq;
+    for (int p = 0; p < 8; ++p) a.tp_box[p] = nullptr;
+    a.tp_box[d->tp_rank] = d->tp_box;
+    a.box_acc_o = static_cast<unsigned int>(off_acc_o), a.box_acc_down = static_cast<unsigned int>(off_acc_down), a.box_y = static_cast<unsigned int>(off_y);
+    a.box_v = static_cast<unsigned int>(off_v), a.box_amax = static_cast<unsigned int>(off_amax), a.box_best = static_cast<unsigned int>(off_best);
+    a.box_flags = static_cast<unsigned int>(off_flags);
+    a.q_dim_full = d->q_dim_full, a.inter_full = d->inter_full, a.vocab_base = d->tp_rank * d->vocab, a.h_slice = H / d->tp_world;
+    if (d->tp_world > 1) a.v_inter = reinterpret_cast<float*>(d->tp_box + off_v);
     a.best_val = d->best_val, a.best_idx = d->best_idx, a.token = d->d_token, a.pos = d->d_pos, a.history = d->d_history;
     a.bar = d->bar, a.status = d->d_counters + 2, a.trace = nullptr;
-    d->mega_smem = mega_smem_bytes(a.attn_region, std::max(H, qd), H, L);
+    d->mega_smem = mega_smem_bytes(a.attn_region, std::max(H, d->q_dim_full), H, L);
     // the table-base constant: measured once per device like the GEMV kernel's
     unsigned int base = 0xFFFFFFFFu;
     smem_base_kernel<<<1, 32, 1024>>>(reinterpret_cast<unsigned int*>(d->bar));
@@ -1023,6 +1062,7 @@ int mega_setup(quintrit_b200_decoder* d, const quintrit_b200_decoder_desc_t* des
 }
 
 int decoder_step(quintrit_b200_decoder* d) {
+    if (d->tp_world > 1 && !d->tp_attached) return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "the tensor-parallel group is not attached yet (quintrit_b200_decoder_tp_attach)");
     if (d->use_mega) {
         QTB_CUDA(cudaMemsetAsync(d->bar, 0, sizeof(unsigned int), d->stream));
         void* args[] = {&d->mega};
@@ -1300,7 +1340,7 @@ extern "C" int quintrit_b200_decoder_info(const quintrit_b200_decoder_t* decoder
         out_info->arch = d->arch, out_info->f32_values = d->f32_values ? 1 : 0;
         out_info->hidden_size = d->hidden, out_info->intermediate_size = d->inter, out_info->num_layers = d->layers;
         out_info->num_heads = d->q_heads, out_info->num_kv_heads = d->kv_heads, out_info->head_dim = d->head_dim;
-        out_info->vocab_size = d->vocab, out_info->context_length = d->ctx, out_info->rope_dims = d->rope_dims;
+        out_info->vocab_size = d->vocab_full, out_info->context_length = d->ctx, out_info->rope_dims = d->rope_dims;
         out_info->device_index = static_cast<uint32_t>(d->device), out_info->single_kernel = d->use_mega ? 1 : 0;
         return ok();
     });
@@ -1340,6 +1380,55 @@ extern "C" int quintrit_b200_gguf_describe(const char* path, char* out, size_t o
     });
 }
 
+extern "C" int quintrit_b200_decoder_tp_handle(const quintrit_b200_decoder_t* decoder, uint8_t* out_handle, size_t out_capacity) {
+    return guard([&]() -> int {
+        int rc = check_decoder(decoder);
+        if (rc != QUINTRIT_OK) return rc;
+        if (out_handle == nullptr) return fail(QUINTRIT_ERR_NULL_POINTER, "out_handle is NULL");
+        if (out_capacity < QUINTRIT_B200_TP_HANDLE_BYTES) return fail(QUINTRIT_ERR_BUFFER_TOO_SMALL, "out_handle holds %zu bytes, %d are needed", out_capacity, QUINTRIT_B200_TP_HANDLE_BYTES);
+        if (decoder->tp_world <= 1) return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "the decoder was not created as a rank of a tensor-parallel group");
+        static_assert(sizeof(cudaIpcMemHandle_t) == QUINTRIT_B200_TP_HANDLE_BYTES, "handle size");
+        DeviceGuard g(decoder->device);
+        cudaIpcMemHandle_t h;
+        QTB_CUDA(cudaIpcGetMemHandle(&h, decoder->tp_box));
+        std::memcpy(out_handle, &h, sizeof h);
+        return ok();
+    });
+}
+
+extern "C" int quintrit_b200_decoder_tp_attach(quintrit_b200_decoder_t* decoder, const uint8_t* handles, size_t handles_len) {
+    return guard([&]() -> int {
+        int rc = check_decoder(decoder);
+        if (rc != QUINTRIT_OK) return rc;
+        quintrit_b200_decoder* d = decoder;
+        if (handles == nullptr) return fail(QUINTRIT_ERR_NULL_POINTER, "handles is NULL");
+        if (d->tp_world <= 1) return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "the decoder was not created as a rank of a tensor-parallel group");
+        if (handles_len != size_t(d->tp_world) * QUINTRIT_B200_TP_HANDLE_BYTES)
+            return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "%zu handle bytes for %d ranks (%d each)", handles_len, d->tp_world, QUINTRIT_B200_TP_HANDLE_BYTES);
+        if (d->tp_attached) return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "the tensor-parallel group is attached already");
+        DeviceGuard g(d->device);
+        for (int p = 0; p < d->tp_world; ++p) {
+            if (p == d->tp_rank) continue;
+            cudaIpcMemHandle_t h;
+            std::memcpy(&h, handles + size_t(p) * QUINTRIT_B200_TP_HANDLE_BYTES, sizeof h);
+            void* ptr = nullptr;
+            const cudaError_t e = cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess);
+            if (e != cudaSuccess) {
+                for (void*& q : d->tp_peer)
+                    if (q != nullptr) {
+                        cudaIpcCloseMemHandle(q);
+                        q = nullptr;
+                    }
+                return cuda_fail(e, "cudaIpcOpenMemHandle(peer box)");
+            }
+            d->tp_peer[p] = ptr;
+            d->mega.tp_box[p] = static_cast<unsigned char*>(ptr);
+        }
+        d->tp_attached = true;
+        return ok();
+    });
+}
+
 extern "C" int quintrit_b200_decoder_free(quintrit_b200_decoder_t* decoder) {
     return guard([&]() -> int {
         if (decoder == nullptr) return ok();
@@ -1358,7 +1447,7 @@ extern "C" int quintrit_b200_decoder_forward(quintrit_b200_decoder_t* decoder, u
         int rc = check_decoder(decoder);
         if (rc != QUINTRIT_OK) return rc;
         quintrit_b200_decoder* d = decoder;
-        if (token >= static_cast<uint32_t>(d->vocab)) return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "token id %u is not below the vocabulary size %d", token, d->vocab);
+        if (token >= static_cast<uint32_t>(d->vocab_full)) return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "token id %u is not below the vocabulary size %d", token, d->vocab_full);
         if (pos >= static_cast<uint32_t>(d->ctx)) return fail(QUINTRIT_ERR_CONTEXT_OVERFLOW, "position %u does not fit the context window of %d tokens", pos, d->ctx);
         if (pos > d->host_pos) return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "position %u skips positions: %u tokens are cached", pos, d->host_pos);
         if (logits != nullptr && logits_capacity < static_cast<size_t>(d->vocab)) return fail(QUINTRIT_ERR_BUFFER_TOO_SMALL, "logits hold %zu values, the vocabulary has %d", logits_capacity, d->vocab);
@@ -1384,7 +1473,7 @@ extern "C" int quintrit_b200_decoder_generate(quintrit_b200_decoder_t* decoder, 
         if (prompt_len + max_new - 1 > static_cast<size_t>(d->ctx))
             return fail(QUINTRIT_ERR_CONTEXT_OVERFLOW, "%zu prompt tokens and %zu new tokens do not fit the context window of %d tokens", prompt_len, max_new, d->ctx);
         for (size_t i = 0; i < prompt_len; ++i)
-            if (prompt[i] >= static_cast<uint32_t>(d->vocab)) return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "token id %u is not below the vocabulary size %d", prompt[i], d->vocab);
+            if (prompt[i] >= static_cast<uint32_t>(d->vocab_full)) return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "token id %u is not below the vocabulary size %d", prompt[i], d->vocab_full);
         DeviceGuard g(d->device);
         uint32_t* d_prompt = nullptr;
         QTB_CUDA(cudaMalloc(&d_prompt, prompt_len * sizeof(uint32_t)));

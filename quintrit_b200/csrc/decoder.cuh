@@ -45,6 +45,14 @@ struct quintrit_b200_decoder {
     cudaGraphExec_t graph_step;               // one token: embed ... argmax (token and position read from device memory)
     bool graph_ready;
     uint32_t host_pos;                         // tokens in the KV cache
+    // tensor parallelism: this rank's share of a model split over tp_world GPUs (1 = none)
+    int tp_rank = 0, tp_world = 1;
+    int q_dim_full = 0, inter_full = 0, vocab_full = 0;
+    unsigned char* tp_box = nullptr;           // the exchange box of this rank (one allocation, shared with the peers)
+    size_t tp_box_bytes = 0;
+    unsigned int* tp_seq = nullptr;
+    bool tp_attached = false;
+    void* tp_peer[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};  // peer boxes opened through IPC
 };
 
 namespace qtb {
@@ -80,6 +88,8 @@ inline void destroy_decoder(quintrit_b200_decoder* d) {
     int prev = -1;
     cudaGetDevice(&prev);
     cudaSetDevice(d->device);
+    for (void* q : d->tp_peer)
+        if (q != nullptr) cudaIpcCloseMemHandle(q);
     if (d->graph_ready) cudaGraphExecDestroy(d->graph_step);
     if (d->stream) cudaStreamDestroy(d->stream);
     for (void* p : d->allocs) cudaFree(p);

@@ -61,6 +61,15 @@ struct MegaArgs {
     unsigned int* bar;        // grid barrier counter, cleared by the host before every launch
     unsigned int* status;     // 0 = fine, 1 = wrong shared-memory base, 2 = a barrier timed out
     unsigned long long* trace; // optional: CTA 0 stores the global timer at every phase boundary (14 per layer + 3)
+    // Tensor parallelism over tp_world GPUs (1 = none). q_heads, kv_heads, inter and vocab above are this rank's shares; the
+    // vectors that every rank needs whole (o and down results, attention output, SwiGLU output) live in a "box" of which
+    // every rank has one; ranks write their slices straight into the boxes of all ranks over NVLink and announce them
+    // with a sequence number in the destination's flag word.
+    int tp_rank, tp_world;
+    unsigned char* tp_box[8];  // the boxes as mapped into this process, own box at [tp_rank]
+    unsigned int* tp_seq;      // exchanges completed by earlier launches (the same on every rank)
+    unsigned int box_acc_o, box_acc_down, box_y, box_v, box_amax, box_best, box_flags;  // byte offsets inside a box
+    int q_dim_full, inter_full, vocab_base, h_slice;  // whole attention width and FFN width, first vocabulary row and hidden / world
 };
 
 __device__ __forceinline__ unsigned long long global_timer_ns() {
@@ -106,6 +115,58 @@ __device__ __forceinline__ bool grid_barrier(unsigned int* bar, unsigned int tar
     }
     __syncthreads();
     return *s_flag != 0;
+}
+
+// ---- exchanges between the GPUs of a tensor-parallel group ------------------------------------------------------------
+constexpr unsigned long long kTpWaitLimitNs = 2000000000ull;  // a peer that does not show up within 2 s is given up on
+
+// Called by every thread of the publishing CTA after its stores to the boxes: makes them visible system-wide, then writes
+// the sequence number into flag [tp_rank] of every box (the own one included).
+__device__ __forceinline__ void tp_publish(const MegaArgs& a, unsigned int seq) {
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x < a.tp_world) {
+        unsigned int* flag = reinterpret_cast<unsigned int*>(a.tp_box[threadIdx.x] + a.box_flags) + a.tp_rank;
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(seq) : "memory");
+    }
+}
+
+// Waits until every rank has announced exchange `seq` in this rank's box. Bounded: after kTpWaitLimitNs (or when the
+// status word is set already) the kernel's status becomes 3 and the function returns false in every thread of the CTA.
+__device__ __noinline__ bool tp_wait(const MegaArgs& a, unsigned int seq, int* s_flag) {
+    if (threadIdx.x == 0) {
+        int okay = 1;
+        const unsigned long long t0 = global_timer_ns();
+        const unsigned int* flags = reinterpret_cast<const unsigned int*>(a.tp_box[a.tp_rank] + a.box_flags);
+        for (int r = 0; r < a.tp_world && okay; ++r) {
+            while (true) {
+                unsigned int v;
+                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + r) : "memory");
+                if (static_cast<int>(v - seq) >= 0) break;
+                if (global_timer_ns() - t0 > kTpWaitLimitNs || *reinterpret_cast<volatile unsigned int*>(a.status) != 0u) {
+                    atomicMax(a.status, 3u);
+                    okay = 0;
+                    break;
+                }
+                __nanosleep(64);
+            }
+        }
+        *s_flag = okay;
+    }
+    __syncthreads();
+    return *s_flag != 0;
+}
+
+// CTA 0 after a grid barrier: copies this rank's slice [tp_rank * n, + n) of a 32-bit vector at byte offset `off` of the
+// own box into the same place of every other box, then announces `seq`.
+__device__ __noinline__ void tp_push_slice(const MegaArgs& a, unsigned int off, int n, unsigned int seq) {
+    const uint32_t* src = reinterpret_cast<const uint32_t*>(a.tp_box[a.tp_rank] + off) + a.tp_rank * n;
+    for (int p = 0; p < a.tp_world; ++p) {
+        if (p == a.tp_rank) continue;
+        uint32_t* dst = reinterpret_cast<uint32_t*>(a.tp_box[p] + off) + a.tp_rank * n;
+        for (int i = threadIdx.x; i < n; i += kMegaThreads) dst[i] = __ldcg(src + i);
+    }
+    tp_publish(a, seq);
 }
 
 // Table fill for any block size that is a multiple of 64: thread -> (column = tid & 63, part = tid >> 6).
@@ -688,7 +749,7 @@ struct MegaSmem {
 };
 __device__ __forceinline__ MegaSmem mega_smem_views(unsigned char* smem, const MegaArgs& a) {
     MegaSmem v;
-    const int maxvec = max(a.hidden, a.q_heads * a.head_dim);
+    const int maxvec = max(a.hidden, a.q_dim_full);
     v.tab = reinterpret_cast<int*>(smem);
     v.y = reinterpret_cast<float*>(smem + a.attn_region);
     v.a8 = reinterpret_cast<int8_t*>(v.y + maxvec);
@@ -709,11 +770,14 @@ __device__ __forceinline__ void prefetch_items(const MegaArgs& a, const MegaLaye
 }
 
 // Phase A (which = 0) and phase E (which = 1): residual (or embedding), RMSNorm, int8 codes for the projection that follows.
-__device__ __noinline__ void phase_norm(const MegaArgs& a, int l, int which, unsigned char* smem) {
+__device__ __noinline__ bool phase_norm(const MegaArgs& a, int l, int which, unsigned int seq_base, unsigned char* smem) {
     const MegaSmem v = mega_smem_views(smem, a);
     const int tid = threadIdx.x, cta = blockIdx.x, G = gridDim.x, H = a.hidden;
     const MegaLayer& ly = v.layers[l];
     prefetch_items(a, ly, which == 0 ? 0 : 2);
+    if (a.tp_world > 1 && (which == 1 || l > 0)) {  // the down results of the previous layer / the o results of this one
+        if (!tp_wait(a, seq_base + 4u * l + (which == 1 ? 2u : 0u), v.flag)) return false;
+    }
     if (which == 0) {
         if (l == 0) {
             const size_t base = static_cast<size_t>(a.token[0]) * H;
@@ -746,6 +810,7 @@ __device__ __noinline__ void phase_norm(const MegaArgs& a, int l, int which, uns
         request_norm_weights(v.w, l + 1 < a.n_layers ? v.layers[l + 1].attn_norm : a.out_norm, H);
     prefetch_items(a, ly, which == 0 ? 1 : 3);
     __syncthreads();
+    return true;
 }
 
 // Phase C1: scores, key rows shared out evenly over the CTAs; a spare CTA clears buffers that are idle now.
@@ -781,7 +846,7 @@ __device__ __noinline__ void phase_values(const MegaArgs& a, int l, unsigned cha
 }
 
 // Phase D: combine the chunks of every head (attention.rs:497-541), int8 codes for the o projection.
-__device__ __noinline__ void phase_combine(const MegaArgs& a, unsigned char* smem) {
+__device__ __noinline__ bool phase_combine(const MegaArgs& a, unsigned int seq, unsigned char* smem) {
     const MegaSmem v = mega_smem_views(smem, a);
     const int tid = threadIdx.x, hd = a.head_dim, qd = a.q_heads * hd;
     float* s_pair = v.pair;
@@ -846,11 +911,34 @@ __device__ __noinline__ void phase_combine(const MegaArgs& a, unsigned char* sme
             amax = fmaxf(amax, fabsf(out));
         }
     }
+    int n_all = qd;
+    if (a.tp_world > 1) {
+        // this rank's heads are a slice of the attention output: CTA 0 writes it into every box, then every CTA takes the
+        // whole vector from the own box once all ranks have announced theirs
+        __syncthreads();
+        if (blockIdx.x == 0) {
+            for (int p = 0; p < a.tp_world; ++p) {
+                float* dst = reinterpret_cast<float*>(a.tp_box[p] + a.box_y) + a.tp_rank * qd;
+                for (int i = tid; i < qd; i += kMegaThreads) dst[i] = v.y[i];
+            }
+            tp_publish(a, seq);
+        }
+        if (!tp_wait(a, seq, v.flag)) return false;
+        n_all = a.q_dim_full;
+        const float* all = reinterpret_cast<const float*>(a.tp_box[a.tp_rank] + a.box_y);
+        amax = 0.0f;
+        for (int i = tid; i < n_all; i += kMegaThreads) {
+            const float y = __ldcg(all + i);
+            v.y[i] = y;
+            amax = fmaxf(amax, fabsf(y));
+        }
+    }
     amax = block_max_f32(amax, v.sh_f);
     const float s_q = amax > 0.0f ? __fdiv_rn(127.0f, amax) : 0.0f;
-    for (int i = tid; i < qd; i += kMegaThreads) v.a8[i] = static_cast<int8_t>(amax > 0.0f ? quantize_code(v.y[i], s_q) : 0);
+    for (int i = tid; i < n_all; i += kMegaThreads) v.a8[i] = static_cast<int8_t>(amax > 0.0f ? quantize_code(v.y[i], s_q) : 0);
     if (tid == 0) v.scale[1] = s_q;
     __syncthreads();
+    return true;
 }
 
 // Phase F1: SwiGLU on this CTA's slice of the intermediate vector, maximum of |v| for the down projection's scale.
@@ -861,6 +949,15 @@ __device__ __noinline__ void phase_swiglu(const MegaArgs& a, int l, unsigned cha
     const float s_f = v.scale[2];
     const float pg = s_f > 0.0f ? __fdiv_rn(ly.ws[4], s_f) : 0.0f, pu = s_f > 0.0f ? __fdiv_rn(ly.ws[5], s_f) : 0.0f;
     float m = 0.0f;
+    // with tensor parallelism this rank's slice of the intermediate vector goes into the box of every rank
+    const int first = a.tp_world > 1 ? a.tp_rank * I : 0;
+    auto store = [&](int i, float x) {
+        if (a.tp_world > 1) {
+            for (int p = 0; p < a.tp_world; ++p) reinterpret_cast<float*>(a.tp_box[p] + a.box_v)[first + i] = x;
+        } else {
+            a.v_inter[i] = x;
+        }
+    };
     for (int i0 = cta * kMegaThreads + tid; i0 < I; i0 += 2 * G * kMegaThreads) {
         const int i1 = i0 + G * kMegaThreads;
         const int g0 = __ldcg(a.acc_gu + i0), u0 = __ldcg(a.acc_gu + I + i0);
@@ -868,16 +965,17 @@ __device__ __noinline__ void phase_swiglu(const MegaArgs& a, int l, unsigned cha
         {
             const float g = s_f > 0.0f ? __fmul_rn(static_cast<float>(g0), pg) : 0.0f, u = s_f > 0.0f ? __fmul_rn(static_cast<float>(u0), pu) : 0.0f;
             const float x = __fmul_rn(ggml_silu(g), u);
-            a.v_inter[i0] = x;
+            store(i0, x);
             m = fmaxf(m, fabsf(x));
         }
         if (i1 < I) {
             const float g = s_f > 0.0f ? __fmul_rn(static_cast<float>(g1), pg) : 0.0f, u = s_f > 0.0f ? __fmul_rn(static_cast<float>(u1), pu) : 0.0f;
             const float x = __fmul_rn(ggml_silu(g), u);
-            a.v_inter[i1] = x;
+            store(i1, x);
             m = fmaxf(m, fabsf(x));
         }
     }
+    if (a.tp_world > 1) __threadfence_system();  // the stores to the other boxes precede the barrier that follows
     m = block_max_f32(m, v.sh_f);
     if (tid == 0 && m > 0.0f) atomicMax(a.amax_bits + (l & 1), __float_as_uint(m));  // non-negative floats order like their bits
     if (cta == G - 1)
@@ -885,10 +983,11 @@ __device__ __noinline__ void phase_swiglu(const MegaArgs& a, int l, unsigned cha
 }
 
 // Final norm (model.rs:326-331), output head, greedy candidate of this CTA.
-__device__ __noinline__ void phase_head(const MegaArgs& a, unsigned char* smem) {
+__device__ __noinline__ bool phase_head(const MegaArgs& a, unsigned int seq_base, unsigned char* smem) {
     const MegaSmem v = mega_smem_views(smem, a);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, cta = blockIdx.x, G = gridDim.x, H = a.hidden;
     float* y_s = v.y;
+    if (a.tp_world > 1 && !tp_wait(a, seq_base + 4u * a.n_layers, v.flag)) return false;  // the last layer's down results
     {
         const float s_prev = v.scale[3];
         const float post = s_prev > 0.0f ? __fdiv_rn(v.layers[a.n_layers - 1].ws[6], s_prev) : 0.0f;
@@ -939,7 +1038,7 @@ __device__ __noinline__ void phase_head(const MegaArgs& a, unsigned char* smem) 
                 const __half* wr = a.lm_head + static_cast<size_t>(row) * H;
                 for (int i = np; i < H; ++i) sum = __fadd_rn(sum, __fmul_rn(y_s[i], __half2float(wr[i])));
                 a.logits[row] = sum;
-                argmax_merge(bv, bi, sum, static_cast<unsigned int>(row));
+                argmax_merge(bv, bi, sum, static_cast<unsigned int>(row + a.vocab_base));
             }
             acc = 0.0f;
         }
@@ -959,16 +1058,45 @@ __device__ __noinline__ void phase_head(const MegaArgs& a, unsigned char* smem) 
         a.best_val[cta] = bv;
         a.best_idx[cta] = bi;
     }
+    return true;
 }
 
 // Last step, CTA 0 after the final barrier: the greedy token (lowest index among equal maxima), position advance, clean-up.
-__device__ __noinline__ void phase_finish(const MegaArgs& a) {
+// With tensor parallelism every rank first tells every other rank the best row of its vocabulary slice.
+__device__ __noinline__ void phase_finish(const MegaArgs& a, unsigned int seq_base, int* s_flag) {
     const int tid = threadIdx.x, G = gridDim.x;
     for (int i = tid; i < a.hidden; i += kMegaThreads) a.acc_down[i] = 0;
+    __shared__ float s_best_v;
+    __shared__ unsigned int s_best_i;
     if (tid == 0) {
         float bv = -INFINITY;
         unsigned int bi = 0xFFFFFFFFu;
         for (int c = 0; c < G; ++c) argmax_merge(bv, bi, __ldcg(a.best_val + c), __ldcg(a.best_idx + c));
+        s_best_v = bv;
+        s_best_i = bi;
+    }
+    if (a.tp_world > 1) {
+        const unsigned int seq = seq_base + 4u * a.n_layers + 1u;
+        __syncthreads();
+        if (tid < a.tp_world) {
+            unsigned int* dst = reinterpret_cast<unsigned int*>(a.tp_box[tid] + a.box_best) + 2 * a.tp_rank;
+            dst[0] = __float_as_uint(s_best_v);
+            dst[1] = s_best_i;
+        }
+        tp_publish(a, seq);
+        if (!tp_wait(a, seq, s_flag)) return;
+        if (tid == 0) {
+            const unsigned int* all = reinterpret_cast<const unsigned int*>(a.tp_box[a.tp_rank] + a.box_best);
+            float bv = -INFINITY;
+            unsigned int bi = 0xFFFFFFFFu;
+            for (int r = 0; r < a.tp_world; ++r) argmax_merge(bv, bi, __uint_as_float(__ldcg(all + 2 * r)), __ldcg(all + 2 * r + 1));
+            s_best_v = bv;
+            s_best_i = bi;
+            *a.tp_seq = seq;
+        }
+    }
+    if (tid == 0) {
+        const unsigned int bi = s_best_i;
         const uint32_t tok = bi == 0xFFFFFFFFu ? 0u : bi;
         a.token[0] = tok;
         a.history[a.pos[0]] = tok;
@@ -1015,8 +1143,10 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const __g
         mega_gemv<BASE>(a.items, v.layers[l].first[k], v.layers[l].count[k], v.tab, acts, actf, qs, out);                         \
     } while (0)
     MEGA_TRACE();
+    const bool tp = a.tp_world > 1;
+    const unsigned int seq_base = tp ? __ldcg(a.tp_seq) : 0u;  // exchange numbers of this launch: seq_base + 4 l + 1..4, then + 4 L + 1
     for (int l = 0; l < a.n_layers; ++l) {
-        phase_norm(a, l, 0, smem);
+        if (!phase_norm(a, l, 0, seq_base, smem)) return;
         MEGA_TRACE();  // 1: norm done
         MEGA_GEMV(0, v.a8, nullptr, 0.0f, a.acc_qkv);
         MEGA_TRACE();  // 2: q|k|v streamed (this CTA)
@@ -1029,12 +1159,13 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const __g
         MEGA_TRACE();  // 5: values done (this CTA)
         MEGA_BARRIER();
         MEGA_TRACE();  // 6
-        phase_combine(a, smem);
+        if (!phase_combine(a, seq_base + 4u * l + 1u, smem)) return;
         MEGA_TRACE();  // 7: combine + quantise done
         MEGA_GEMV(1, v.a8, nullptr, 0.0f, a.acc_o);
         MEGA_BARRIER();
+        if (tp && cta == 0) tp_push_slice(a, a.box_acc_o, a.h_slice, seq_base + 4u * l + 2u);
         MEGA_TRACE();  // 8
-        phase_norm(a, l, 1, smem);
+        if (!phase_norm(a, l, 1, seq_base, smem)) return;
         MEGA_TRACE();  // 9: norm done
         MEGA_GEMV(2, v.a8, nullptr, 0.0f, a.acc_gu);
         MEGA_TRACE();  // 10: gate|up streamed (this CTA)
@@ -1045,7 +1176,19 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const __g
         MEGA_TRACE();  // 12
         {
             // down, quantising v on the fly with the scale from the maximum every CTA contributed to
-            const float vmax = __uint_as_float(__ldcg(a.amax_bits + (l & 1)));
+            float vmax = __uint_as_float(__ldcg(a.amax_bits + (l & 1)));
+            if (tp) {
+                // every rank tells every other rank the maximum of its slice; the scale comes from the maximum of all
+                const unsigned int seq = seq_base + 4u * l + 3u;
+                if (cta == 0) {
+                    if (tid < a.tp_world) reinterpret_cast<float*>(a.tp_box[tid] + a.box_amax)[a.tp_rank] = vmax;
+                    tp_publish(a, seq);
+                }
+                if (!tp_wait(a, seq, mega_smem_views(smem, a).flag)) return;
+                const float* all = reinterpret_cast<const float*>(a.tp_box[a.tp_rank] + a.box_amax);
+                vmax = 0.0f;
+                for (int r = 0; r < a.tp_world; ++r) vmax = fmaxf(vmax, __ldcg(all + r));
+            }
             const float s_down = vmax > 0.0f ? __fdiv_rn(127.0f, vmax) : 0.0f;
             if (tid == 0) mega_smem_views(smem, a).scale[3] = s_down;
             MEGA_GEMV(3, nullptr, a.v_inter, s_down, a.acc_down);
@@ -1053,13 +1196,14 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const __g
             for (int i = cta * kMegaThreads + tid; i < 2 * a.inter; i += G * kMegaThreads) a.acc_gu[i] = 0;  // consumed by SwiGLU
         }
         MEGA_BARRIER();
+        if (tp && cta == 0) tp_push_slice(a, a.box_acc_down, a.h_slice, seq_base + 4u * l + 4u);
         MEGA_TRACE();  // 14 = 0 of the next layer
     }
-    phase_head(a, smem);
+    if (!phase_head(a, seq_base, smem)) return;
     MEGA_TRACE();  // head done (this CTA)
     MEGA_BARRIER();
     MEGA_TRACE();
-    if (cta == 0) phase_finish(a);
+    if (cta == 0) phase_finish(a, seq_base, mega_smem_views(smem, a).flag);
 #undef MEGA_GEMV
 #undef MEGA_BARRIER
 #undef MEGA_TRACE

@@ -162,7 +162,7 @@ def torch_normal_f16_bits(seed: int, n: int, std: float, device, chunk: int = 1 
     return out
 
 
-def torch_model(shape: str, device, ctx: int, f32_values: bool = False, config: int = 2, layers: int | None = None) -> dict:
+def torch_model(shape: str, device, ctx: int, f32_values: bool = False, config: int = 2, layers: int | None = None, tp=None) -> dict:
     """The Falcon3-10B-shape or BitNet-2B-shape model with seeded random-init weights, built on a torch device."""
     if shape == "falcon3_10b":
         arch, hidden, inter, L, qh, kvh, hd, vocab, theta, eps, tied = 0, 3072, 23040, 40, 12, 4, 256, 131072, 1000042.0, 1e-6, False
@@ -176,17 +176,51 @@ def torch_model(shape: str, device, ctx: int, f32_values: bool = False, config: 
     weights, scales, norms = [], [], []
     for l in range(L):
         for p, (rows, cols) in enumerate(shapes):
-            weights.append(torch_planar(seed_for(config, l, p, 0), rows, cols, device).cpu().numpy())
+            if tp is None:
+                w = torch_planar(seed_for(config, l, p, 0), rows, cols, device)
+            else:  # only this rank's rows (see shard_spec)
+                n = rows // tp[1]
+                w = torch_planar(seed_for(config, l, p, 0), n, cols, device, row0=tp[0] * n)
+            weights.append(w.cpu().numpy().reshape(-1))
             scales.append(weight_scale(seed_for(config, l, p, 1)))
         norms += [np.ones(hidden, np.float32), np.ones(hidden, np.float32), np.ones(qd, np.float32) if arch == 1 else None,
                   np.ones(inter, np.float32) if arch == 1 else None]
     embed = torch_normal_f16_bits(seed_for(config, 255, 0, 0), vocab * hidden, 0.02, device)
     head = None if tied else torch_normal_f16_bits(seed_for(config, 255, 1, 0), vocab * hidden, 0.02, device)
-    return dict(arch=arch, f32_values=f32_values, hidden=hidden, inter=inter, layers=L, q_heads=qh, kv_heads=kvh, head_dim=hd, vocab=vocab,
+    spec = dict(arch=arch, f32_values=f32_values, hidden=hidden, inter=inter, layers=L, q_heads=qh, kv_heads=kvh, head_dim=hd, vocab=vocab,
                 ctx=ctx, rope_dims=hd, eps=eps, rope_theta=theta, weights=weights, scales=np.array(scales, np.float32), norms=norms,
                 embed=embed, lm_head=head, out_norm=np.ones(hidden, np.float32), shape=shape)
+    if tp is not None:
+        spec.update(tp_rank=tp[0], tp_world=tp[1])
+        if head is not None:
+            v = vocab // tp[1]
+            spec["lm_head"] = np.ascontiguousarray(head.reshape(vocab, hidden)[tp[0] * v:(tp[0] + 1) * v]).reshape(-1)
+    return spec
 
 
 def prompt_tokens(config: int, n: int, vocab: int) -> np.ndarray:
     """Uniform token ids from stream 3."""
     return (splitmix_u32(seed_for(config, 0, 0, 3), 0, n).astype(np.uint64) * np.uint64(vocab) >> np.uint64(32)).astype(np.uint32)
+
+
+def shard_spec(spec: dict, rank: int, world: int) -> dict:
+    """The share of `spec` (planar numpy projections) that rank `rank` of a tensor-parallel group of `world` GPUs holds:
+    its rows of every projection - q / k / v rows of its heads, rows [rank * n / world, (rank + 1) * n / world) of o,
+    gate, up and down - and its rows of the output head. Dimensions stay those of the whole model."""
+    from . import api
+
+    H, I, hd = spec["hidden"], spec["inter"], spec["head_dim"]
+    qd, kvd = spec["q_heads"] * hd, spec["kv_heads"] * hd
+    assert spec["kv_heads"] % world == 0 and H % world == 0 and I % world == 0 and spec["vocab"] % world == 0
+    shapes = [(qd, H), (kvd, H), (kvd, H), (H, qd), (I, H), (I, H), (H, I)]
+    weights = []
+    for i, w in enumerate(spec["weights"]):
+        rows, cols = shapes[i % 7]
+        rb = api.row_bytes(cols)
+        n = rows // world
+        weights.append(np.ascontiguousarray(np.asarray(w, np.uint8).reshape(rows, rb)[rank * n:(rank + 1) * n]).reshape(-1))
+    out = dict(spec, weights=weights, tp_rank=rank, tp_world=world)
+    if spec.get("lm_head") is not None:
+        v = spec["vocab"] // world
+        out["lm_head"] = np.ascontiguousarray(np.asarray(spec["lm_head"], np.uint16).reshape(spec["vocab"], H)[rank * v:(rank + 1) * v]).reshape(-1)
+    return out
