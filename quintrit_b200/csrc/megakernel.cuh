@@ -1063,11 +1063,14 @@ __device__ __noinline__ bool phase_head(const MegaArgs& a, unsigned int seq_base
 
 // Last step, CTA 0 after the final barrier: the greedy token (lowest index among equal maxima), position advance, clean-up.
 // With tensor parallelism every rank first tells every other rank the best row of its vocabulary slice.
-__device__ __noinline__ void phase_finish(const MegaArgs& a, unsigned int seq_base, int* s_flag) {
+__device__ __noinline__ void phase_finish(const MegaArgs& a, unsigned int seq_base, unsigned char* smem) {
+    const MegaSmem v = mega_smem_views(smem, a);
     const int tid = threadIdx.x, G = gridDim.x;
+    int* s_flag = v.flag;
+    // no static shared memory anywhere in this kernel: it would move the dynamic base the table addresses are built on
+    float& s_best_v = v.sh_f[0];
+    unsigned int& s_best_i = reinterpret_cast<unsigned int*>(v.sh_f)[1];
     for (int i = tid; i < a.hidden; i += kMegaThreads) a.acc_down[i] = 0;
-    __shared__ float s_best_v;
-    __shared__ unsigned int s_best_i;
     if (tid == 0) {
         float bv = -INFINITY;
         unsigned int bi = 0xFFFFFFFFu;
@@ -1203,7 +1206,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const __g
     MEGA_TRACE();  // head done (this CTA)
     MEGA_BARRIER();
     MEGA_TRACE();
-    if (cta == 0) phase_finish(a, seq_base, mega_smem_views(smem, a).flag);
+    if (cta == 0) phase_finish(a, seq_base, smem);
 #undef MEGA_GEMV
 #undef MEGA_BARRIER
 #undef MEGA_TRACE
