@@ -420,6 +420,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         dist.all_reduce(ok, op=dist.ReduceOp.MIN)
         same = bool(ok.item())
     decode_tp = None
+    h2d_bytes, d2h_bytes = int(plan.act_total), int(plan.out_total * 4)
     if dist is not None and not args.no_decode:
         del plan, mats
         torch.cuda.empty_cache()
@@ -448,7 +449,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         "roofline_nominal_8tbs_frac": round(weights_total * BYTES_PER_WEIGHT / (ms_per_step * 1e-3) / (world * 8e12), 4),
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 4),
                      "traffic": int(weights_local * NCU_TRAFFIC_BYTES_PER_WEIGHT), "traffic_source": "ncu capture of the 12-layer case, scaled by weights", "peak_kind": peak_kind, "kernel": "gemv_lut_kernel", "launch_ms": round(kernel_ms, 4)},
-        "e2e": {"value": round(e2e_value, 1), "unit": "Gweights/s", "h2d_bytes_per_step": int(plan.act_total), "d2h_bytes_per_step": int(plan.out_total * 4),
+        "e2e": {"value": round(e2e_value, 1), "unit": "Gweights/s", "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes,
                 "ms_per_step": round(e2e_ms / args.steps, 4)},
         "sustained": {"value": round(weights_total / (sustained_ms * 1e-3) / 1e9, 1), "unit": "Gweights/s", "ms_per_step": round(sustained_ms, 4),
                       "steps": sus_steps, "hbm_frac": round(weights_local * BYTES_PER_WEIGHT / (sustained_ms * 1e-3) / 1e9 / peak, 4)},
