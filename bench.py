@@ -281,7 +281,7 @@ def run_decode_tp(args, rank: int, world: int, local_rank: int, dist):
     return {"shape": spec["shape"], "layers": spec["layers"], "context": args.prompt, "tp_world": world, "tokens_per_s": round(1e3 / step_ms, 1),
             "ms_per_token": round(step_ms, 4), "best_ms_per_token": round(best_ms, 4), "velurex_bytes_per_token": int(bytes_tok),
             "roofline_nominal_8tbs_frac": round(bytes_tok / (step_ms * 1e-3) / (world * 8e12), 4), "exchanges_per_token": 4 * spec["layers"] + 1,
-            "transport": "peer stores into every rank's box inside the token kernel, flags with release/acquire at system scope",
+            "transport": "8-byte (value, sequence) peer stores into every rank's box inside the token kernel, polled by the readers",
             "parity": {"greedy_tokens_checked": ngen, "all_ranks_agree": all(g == got for g in gathered), "identical_to_one_gpu": got == want},
             "setup_s": round(setup_s, 1)}
 

@@ -983,14 +983,14 @@ int mega_setup(quintrit_b200_decoder* d, const quintrit_b200_decoder_desc_t* des
     int rc;
     // Tensor parallelism: the vectors every rank needs whole live in one allocation (the "box") that the peers map.
     const auto up256 = [](size_t n) { return (n + 255) / 256 * 256; };
-    const size_t off_acc_o = 0, off_acc_down = up256(off_acc_o + size_t(H) * 4), off_y = up256(off_acc_down + size_t(H) * 4),
-                 off_v = up256(off_y + size_t(d->q_dim_full) * 4), off_amax = up256(off_v + size_t(d->inter_full) * 4), off_best = off_amax + 256,
-                 off_flags = off_best + 256, box_bytes = off_flags + 256;
+    // pair buffers (8 bytes per value) for the o and down results, the attention output, the partial maxima and the greedy
+    // candidates; the SwiGLU output travels as plain floats
+    const size_t off_acc_o = 0, off_acc_down = up256(off_acc_o + size_t(H) * 8), off_y = up256(off_acc_down + size_t(H) * 8),
+                 off_v = up256(off_y + size_t(d->q_dim_full) * 8), off_amax = up256(off_v + size_t(d->inter_full) * 4), off_best = off_amax + 256,
+                 box_bytes = off_best + 256;
     if (d->tp_world > 1) {
         if ((rc = dev_alloc(d, &d->tp_box, box_bytes)) != QUINTRIT_OK || (rc = dev_alloc(d, &d->tp_seq, 4)) != QUINTRIT_OK) return rc;
         d->tp_box_bytes = box_bytes;
-        d->acc_o = reinterpret_cast<int32_t*>(d->tp_box + off_acc_o);  // replaces the private buffers allocated for one GPU
-        d->acc_down = reinterpret_cast<int32_t*>(d->tp_box + off_acc_down);
     }
     const size_t slice_off = size_t(d->tp_rank) * (H / d->tp_world);  // first row of this rank in the o and down results
     if ((rc = dev_alloc(d, &d->xa, H)) != QUINTRIT_OK || (rc = dev_alloc(d, &d->xb, H)) != QUINTRIT_OK ||
@@ -1039,7 +1039,6 @@ int mega_setup(quintrit_b200_decoder* d, const quintrit_b200_decoder_desc_t* des
     a.tp_box[d->tp_rank] = d->tp_box;
     a.box_acc_o = static_cast<unsigned int>(off_acc_o), a.box_acc_down = static_cast<unsigned int>(off_acc_down), a.box_y = static_cast<unsigned int>(off_y);
     a.box_v = static_cast<unsigned int>(off_v), a.box_amax = static_cast<unsigned int>(off_amax), a.box_best = static_cast<unsigned int>(off_best);
-    a.box_flags = static_cast<unsigned int>(off_flags);
     a.q_dim_full = d->q_dim_full, a.inter_full = d->inter_full, a.vocab_base = d->tp_rank * d->vocab, a.h_slice = H / d->tp_world;
     if (d->tp_world > 1) a.v_inter = reinterpret_cast<float*>(d->tp_box + off_v);
     a.best_val = d->best_val, a.best_idx = d->best_idx, a.token = d->d_token, a.pos = d->d_pos, a.history = d->d_history;

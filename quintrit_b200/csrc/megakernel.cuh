@@ -63,12 +63,12 @@ struct MegaArgs {
     unsigned long long* trace; // optional: CTA 0 stores the global timer at every phase boundary (14 per layer + 3)
     // Tensor parallelism over tp_world GPUs (1 = none). q_heads, kv_heads, inter and vocab above are this rank's shares; the
     // vectors that every rank needs whole (o and down results, attention output, SwiGLU output) live in a "box" of which
-    // every rank has one; ranks write their slices straight into the boxes of all ranks over NVLink and announce them
-    // with a sequence number in the destination's flag word.
+    // every rank has one; ranks write their slices straight into the boxes of all ranks over NVLink as (value, sequence
+    // number) pairs that the readers poll.
     int tp_rank, tp_world;
     unsigned char* tp_box[8];  // the boxes as mapped into this process, own box at [tp_rank]
     unsigned int* tp_seq;      // exchanges completed by earlier launches (the same on every rank)
-    unsigned int box_acc_o, box_acc_down, box_y, box_v, box_amax, box_best, box_flags;  // byte offsets inside a box
+    unsigned int box_acc_o, box_acc_down, box_y, box_v, box_amax, box_best;  // byte offsets inside a box (pair buffers; box_v: plain floats)
     int q_dim_full, inter_full, vocab_base, h_slice;  // whole attention width and FFN width, first vocabulary row and hidden / world
 };
 
@@ -111,6 +111,7 @@ __device__ __forceinline__ bool grid_barrier(unsigned int* bar, unsigned int tar
             }
             __nanosleep(32);
         }
+        if (*reinterpret_cast<volatile unsigned int*>(status) != 0u) okay = 0;  // e.g. an exchange that timed out
         *s_flag = okay;
     }
     __syncthreads();
@@ -118,55 +119,43 @@ __device__ __forceinline__ bool grid_barrier(unsigned int* bar, unsigned int tar
 }
 
 // ---- exchanges between the GPUs of a tensor-parallel group ------------------------------------------------------------
+// Every exchanged 32-bit value travels as an 8-byte pair (value, sequence number of the exchange) written with one store
+// into the destination rank's box; the reader polls the pair until it carries the number it waits for. An aligned 8-byte
+// store arrives as a unit, so no fence and no separate flag are needed and the latency is one NVLink hop. (The same idea
+// as the low-latency protocol of collective libraries.) Sequence numbers grow from launch to launch, and a buffer is
+// rewritten four exchanges later at the earliest, after the writer has seen results that depend on the reader having
+// finished with it.
 constexpr unsigned long long kTpWaitLimitNs = 2000000000ull;  // a peer that does not show up within 2 s is given up on
 
-// Called by every thread of the publishing CTA after its stores to the boxes: makes them visible system-wide, then writes
-// the sequence number into flag [tp_rank] of every box (the own one included).
-__device__ __forceinline__ void tp_publish(const MegaArgs& a, unsigned int seq) {
-    __threadfence_system();
-    __syncthreads();
-    if (threadIdx.x < a.tp_world) {
-        unsigned int* flag = reinterpret_cast<unsigned int*>(a.tp_box[threadIdx.x] + a.box_flags) + a.tp_rank;
-        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(seq) : "memory");
-    }
+__device__ __forceinline__ void ll_store(uint2* p, uint32_t value, uint32_t seq) {
+    asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(value), "r"(seq) : "memory");
 }
 
-// Waits until every rank has announced exchange `seq` in this rank's box. Bounded: after kTpWaitLimitNs (or when the
-// status word is set already) the kernel's status becomes 3 and the function returns false in every thread of the CTA.
-__device__ __noinline__ bool tp_wait(const MegaArgs& a, unsigned int seq, int* s_flag) {
-    if (threadIdx.x == 0) {
-        int okay = 1;
-        const unsigned long long t0 = global_timer_ns();
-        const unsigned int* flags = reinterpret_cast<const unsigned int*>(a.tp_box[a.tp_rank] + a.box_flags);
-        for (int r = 0; r < a.tp_world && okay; ++r) {
-            while (true) {
-                unsigned int v;
-                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + r) : "memory");
-                if (static_cast<int>(v - seq) >= 0) break;
-                if (global_timer_ns() - t0 > kTpWaitLimitNs || *reinterpret_cast<volatile unsigned int*>(a.status) != 0u) {
-                    atomicMax(a.status, 3u);
-                    okay = 0;
-                    break;
-                }
-                __nanosleep(64);
+// Value of a pair once it carries `seq`. Bounded: after kTpWaitLimitNs (or when the status word is set already) the
+// kernel's status becomes 3 and 0 is returned; the next grid barrier then ends the kernel.
+__device__ __forceinline__ uint32_t ll_load(const uint2* p, uint32_t seq, unsigned int* status) {
+    uint32_t value, got;
+    unsigned long long t0 = 0;
+    for (unsigned int spins = 0;; ++spins) {
+        asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(value), "=r"(got) : "l"(p) : "memory");
+        if (got == seq) return value;
+        if ((spins & 255u) == 255u) {
+            const unsigned long long now = global_timer_ns();
+            if (t0 == 0) t0 = now;
+            if (now - t0 > kTpWaitLimitNs || *reinterpret_cast<volatile unsigned int*>(status) != 0u) {
+                atomicMax(status, 3u);
+                return 0u;
             }
         }
-        *s_flag = okay;
     }
-    __syncthreads();
-    return *s_flag != 0;
 }
 
-// CTA 0 after a grid barrier: copies this rank's slice [tp_rank * n, + n) of a 32-bit vector at byte offset `off` of the
-// own box into the same place of every other box, then announces `seq`.
-__device__ __noinline__ void tp_push_slice(const MegaArgs& a, unsigned int off, int n, unsigned int seq) {
-    const uint32_t* src = reinterpret_cast<const uint32_t*>(a.tp_box[a.tp_rank] + off) + a.tp_rank * n;
-    for (int p = 0; p < a.tp_world; ++p) {
-        if (p == a.tp_rank) continue;
-        uint32_t* dst = reinterpret_cast<uint32_t*>(a.tp_box[p] + off) + a.tp_rank * n;
-        for (int i = threadIdx.x; i < n; i += kMegaThreads) dst[i] = __ldcg(src + i);
-    }
-    tp_publish(a, seq);
+// After a grid barrier, CTA p < tp_world: sends this rank's slice [tp_rank * n, + n) of the local 32-bit vector `src` to
+// rank p's pair buffer at byte offset `off` of its box.
+__device__ __noinline__ void tp_push_slice(const MegaArgs& a, const uint32_t* src, unsigned int off, int n, unsigned int seq) {
+    uint2* dst = reinterpret_cast<uint2*>(a.tp_box[blockIdx.x] + off) + a.tp_rank * n;
+    src += a.tp_rank * n;
+    for (int i = threadIdx.x; i < n; i += kMegaThreads) ll_store(dst + i, __ldcg(src + i), seq);
 }
 
 // Table fill for any block size that is a multiple of 64: thread -> (column = tid & 63, part = tid >> 6).
@@ -327,6 +316,16 @@ __device__ __forceinline__ void residual_add(float* y_s, const float* x, const i
             const int i = i0 + k * kMegaThreads;
             if (i < n) y_s[i] = __fadd_rn(xv[k], live ? __fmul_rn(static_cast<float>(av[k]), post) : 0.0f);
         }
+    }
+}
+
+// residual_add whose projection results arrive as (value, sequence) pairs from every rank of a tensor-parallel group.
+__device__ __forceinline__ void residual_add_ll(float* y_s, const float* x, const uint2* acc, unsigned int seq, unsigned int* status, float post,
+                                                bool live, int n) {
+    for (int i = threadIdx.x; i < n; i += kMegaThreads) {
+        const float xv = __ldcg(x + i);
+        const int av = static_cast<int>(ll_load(acc + i, seq, status));
+        y_s[i] = __fadd_rn(xv, live ? __fmul_rn(static_cast<float>(av), post) : 0.0f);
     }
 }
 
@@ -775,9 +774,7 @@ __device__ __noinline__ bool phase_norm(const MegaArgs& a, int l, int which, uns
     const int tid = threadIdx.x, cta = blockIdx.x, G = gridDim.x, H = a.hidden;
     const MegaLayer& ly = v.layers[l];
     prefetch_items(a, ly, which == 0 ? 0 : 2);
-    if (a.tp_world > 1 && (which == 1 || l > 0)) {  // the down results of the previous layer / the o results of this one
-        if (!tp_wait(a, seq_base + 4u * l + (which == 1 ? 2u : 0u), v.flag)) return false;
-    }
+
     if (which == 0) {
         if (l == 0) {
             const size_t base = static_cast<size_t>(a.token[0]) * H;
@@ -785,12 +782,20 @@ __device__ __noinline__ bool phase_norm(const MegaArgs& a, int l, int which, uns
         } else {
             const float s_prev = v.scale[3];
             const float post = s_prev > 0.0f ? __fdiv_rn(v.layers[l - 1].ws[6], s_prev) : 0.0f;
-            residual_add(v.y, a.xb, a.acc_down, post, s_prev > 0.0f, H);
+            if (a.tp_world > 1)  // the down results of the previous layer, from every rank
+                residual_add_ll(v.y, a.xb, reinterpret_cast<const uint2*>(a.tp_box[a.tp_rank] + a.box_acc_down), seq_base + 4u * l, a.status, post,
+                                s_prev > 0.0f, H);
+            else
+                residual_add(v.y, a.xb, a.acc_down, post, s_prev > 0.0f, H);
         }
     } else {
         const float s_q = v.scale[1];
         const float post = s_q > 0.0f ? __fdiv_rn(ly.ws[3], s_q) : 0.0f;
-        residual_add(v.y, a.xa, a.acc_o, post, s_q > 0.0f, H);
+        if (a.tp_world > 1)  // the o results of this layer, from every rank
+            residual_add_ll(v.y, a.xa, reinterpret_cast<const uint2*>(a.tp_box[a.tp_rank] + a.box_acc_o), seq_base + 4u * l + 2u, a.status, post,
+                            s_q > 0.0f, H);
+        else
+            residual_add(v.y, a.xa, a.acc_o, post, s_q > 0.0f, H);
     }
     cp_async_wait<0>();  // the norm weights requested one phase ago
     __syncthreads();
@@ -913,22 +918,19 @@ __device__ __noinline__ bool phase_combine(const MegaArgs& a, unsigned int seq, 
     }
     int n_all = qd;
     if (a.tp_world > 1) {
-        // this rank's heads are a slice of the attention output: CTA 0 writes it into every box, then every CTA takes the
-        // whole vector from the own box once all ranks have announced theirs
+        // this rank's heads are a slice of the attention output: CTA p sends it to rank p, then every CTA takes the whole
+        // vector from the own box as the pairs arrive
         __syncthreads();
-        if (blockIdx.x == 0) {
-            for (int p = 0; p < a.tp_world; ++p) {
-                float* dst = reinterpret_cast<float*>(a.tp_box[p] + a.box_y) + a.tp_rank * qd;
-                for (int i = tid; i < qd; i += kMegaThreads) dst[i] = v.y[i];
-            }
-            tp_publish(a, seq);
+        if (blockIdx.x < a.tp_world) {
+            uint2* dst = reinterpret_cast<uint2*>(a.tp_box[blockIdx.x] + a.box_y) + a.tp_rank * qd;
+            for (int i = tid; i < qd; i += kMegaThreads) ll_store(dst + i, __float_as_uint(v.y[i]), seq);
         }
-        if (!tp_wait(a, seq, v.flag)) return false;
+        __syncthreads();
         n_all = a.q_dim_full;
-        const float* all = reinterpret_cast<const float*>(a.tp_box[a.tp_rank] + a.box_y);
+        const uint2* all = reinterpret_cast<const uint2*>(a.tp_box[a.tp_rank] + a.box_y);
         amax = 0.0f;
         for (int i = tid; i < n_all; i += kMegaThreads) {
-            const float y = __ldcg(all + i);
+            const float y = __uint_as_float(ll_load(all + i, seq, a.status));
             v.y[i] = y;
             amax = fmaxf(amax, fabsf(y));
         }
@@ -987,11 +989,14 @@ __device__ __noinline__ bool phase_head(const MegaArgs& a, unsigned int seq_base
     const MegaSmem v = mega_smem_views(smem, a);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, cta = blockIdx.x, G = gridDim.x, H = a.hidden;
     float* y_s = v.y;
-    if (a.tp_world > 1 && !tp_wait(a, seq_base + 4u * a.n_layers, v.flag)) return false;  // the last layer's down results
     {
         const float s_prev = v.scale[3];
         const float post = s_prev > 0.0f ? __fdiv_rn(v.layers[a.n_layers - 1].ws[6], s_prev) : 0.0f;
-        residual_add(y_s, a.xb, a.acc_down, post, s_prev > 0.0f, H);
+        if (a.tp_world > 1)  // the last layer's down results, from every rank
+            residual_add_ll(y_s, a.xb, reinterpret_cast<const uint2*>(a.tp_box[a.tp_rank] + a.box_acc_down), seq_base + 4u * a.n_layers, a.status, post,
+                            s_prev > 0.0f, H);
+        else
+            residual_add(y_s, a.xb, a.acc_down, post, s_prev > 0.0f, H);
     }
     cp_async_wait<0>();
     __syncthreads();
@@ -1066,7 +1071,6 @@ __device__ __noinline__ bool phase_head(const MegaArgs& a, unsigned int seq_base
 __device__ __noinline__ void phase_finish(const MegaArgs& a, unsigned int seq_base, unsigned char* smem) {
     const MegaSmem v = mega_smem_views(smem, a);
     const int tid = threadIdx.x, G = gridDim.x;
-    int* s_flag = v.flag;
     // no static shared memory anywhere in this kernel: it would move the dynamic base the table addresses are built on
     float& s_best_v = v.sh_f[0];
     unsigned int& s_best_i = reinterpret_cast<unsigned int*>(v.sh_f)[1];
@@ -1082,17 +1086,19 @@ __device__ __noinline__ void phase_finish(const MegaArgs& a, unsigned int seq_ba
         const unsigned int seq = seq_base + 4u * a.n_layers + 1u;
         __syncthreads();
         if (tid < a.tp_world) {
-            unsigned int* dst = reinterpret_cast<unsigned int*>(a.tp_box[tid] + a.box_best) + 2 * a.tp_rank;
-            dst[0] = __float_as_uint(s_best_v);
-            dst[1] = s_best_i;
+            uint2* dst = reinterpret_cast<uint2*>(a.tp_box[tid] + a.box_best) + 2 * a.tp_rank;
+            ll_store(dst, __float_as_uint(s_best_v), seq);
+            ll_store(dst + 1, s_best_i, seq);
         }
-        tp_publish(a, seq);
-        if (!tp_wait(a, seq, s_flag)) return;
+        __syncthreads();
         if (tid == 0) {
-            const unsigned int* all = reinterpret_cast<const unsigned int*>(a.tp_box[a.tp_rank] + a.box_best);
+            const uint2* all = reinterpret_cast<const uint2*>(a.tp_box[a.tp_rank] + a.box_best);
             float bv = -INFINITY;
             unsigned int bi = 0xFFFFFFFFu;
-            for (int r = 0; r < a.tp_world; ++r) argmax_merge(bv, bi, __uint_as_float(__ldcg(all + 2 * r)), __ldcg(all + 2 * r + 1));
+            for (int r = 0; r < a.tp_world; ++r) {
+                const float rv = __uint_as_float(ll_load(all + 2 * r, seq, a.status));
+                argmax_merge(bv, bi, rv, ll_load(all + 2 * r + 1, seq, a.status));
+            }
             s_best_v = bv;
             s_best_i = bi;
             *a.tp_seq = seq;
@@ -1166,7 +1172,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const __g
         MEGA_TRACE();  // 7: combine + quantise done
         MEGA_GEMV(1, v.a8, nullptr, 0.0f, a.acc_o);
         MEGA_BARRIER();
-        if (tp && cta == 0) tp_push_slice(a, a.box_acc_o, a.h_slice, seq_base + 4u * l + 2u);
+        if (tp && cta < a.tp_world) tp_push_slice(a, reinterpret_cast<const uint32_t*>(a.acc_o), a.box_acc_o, a.h_slice, seq_base + 4u * l + 2u);
         MEGA_TRACE();  // 8
         if (!phase_norm(a, l, 1, seq_base, smem)) return;
         MEGA_TRACE();  // 9: norm done
@@ -1183,14 +1189,11 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const __g
             if (tp) {
                 // every rank tells every other rank the maximum of its slice; the scale comes from the maximum of all
                 const unsigned int seq = seq_base + 4u * l + 3u;
-                if (cta == 0) {
-                    if (tid < a.tp_world) reinterpret_cast<float*>(a.tp_box[tid] + a.box_amax)[a.tp_rank] = vmax;
-                    tp_publish(a, seq);
-                }
-                if (!tp_wait(a, seq, mega_smem_views(smem, a).flag)) return;
-                const float* all = reinterpret_cast<const float*>(a.tp_box[a.tp_rank] + a.box_amax);
+                if (cta < a.tp_world && tid == 0) __threadfence_system();  // behind the SwiGLU stores of every CTA of this rank
+                if (cta < a.tp_world && tid == 0) ll_store(reinterpret_cast<uint2*>(a.tp_box[cta] + a.box_amax) + a.tp_rank, __float_as_uint(vmax), seq);
+                const uint2* all = reinterpret_cast<const uint2*>(a.tp_box[a.tp_rank] + a.box_amax);
                 vmax = 0.0f;
-                for (int r = 0; r < a.tp_world; ++r) vmax = fmaxf(vmax, __ldcg(all + r));
+                for (int r = 0; r < a.tp_world; ++r) vmax = fmaxf(vmax, __uint_as_float(ll_load(all + r, seq, a.status)));
             }
             const float s_down = vmax > 0.0f ? __fdiv_rn(127.0f, vmax) : 0.0f;
             if (tid == 0) mega_smem_views(smem, a).scale[3] = s_down;
@@ -1199,7 +1202,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const __g
             for (int i = cta * kMegaThreads + tid; i < 2 * a.inter; i += G * kMegaThreads) a.acc_gu[i] = 0;  // consumed by SwiGLU
         }
         MEGA_BARRIER();
-        if (tp && cta == 0) tp_push_slice(a, a.box_acc_down, a.h_slice, seq_base + 4u * l + 4u);
+        if (tp && cta < a.tp_world) tp_push_slice(a, reinterpret_cast<const uint32_t*>(a.acc_down), a.box_acc_down, a.h_slice, seq_base + 4u * l + 4u);
         MEGA_TRACE();  // 14 = 0 of the next layer
     }
     if (!phase_head(a, seq_base, smem)) return;
