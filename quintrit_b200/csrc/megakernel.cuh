@@ -319,13 +319,34 @@ __device__ __forceinline__ void residual_add(float* y_s, const float* x, const i
     }
 }
 
+// One try at a pair: the value and whether it carries `seq` yet.
+__device__ __forceinline__ uint2 ll_peek(const uint2* p) {
+    uint2 r;
+    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(r.x), "=r"(r.y) : "l"(p) : "memory");
+    return r;
+}
+
 // residual_add whose projection results arrive as (value, sequence) pairs from every rank of a tensor-parallel group.
+// All pairs of a thread are requested before the first is examined; only those that have not arrived yet are polled.
 __device__ __forceinline__ void residual_add_ll(float* y_s, const float* x, const uint2* acc, unsigned int seq, unsigned int* status, float post,
                                                 bool live, int n) {
-    for (int i = threadIdx.x; i < n; i += kMegaThreads) {
-        const float xv = __ldcg(x + i);
-        const int av = static_cast<int>(ll_load(acc + i, seq, status));
-        y_s[i] = __fadd_rn(xv, live ? __fmul_rn(static_cast<float>(av), post) : 0.0f);
+    constexpr int kPer = 8;
+    for (int i0 = threadIdx.x; i0 < n; i0 += kPer * kMegaThreads) {
+        uint2 pr[kPer];
+        float xv[kPer];
+#pragma unroll
+        for (int k = 0; k < kPer; ++k) {
+            const int i = i0 + k * kMegaThreads;
+            pr[k] = i < n ? ll_peek(acc + i) : make_uint2(0u, seq);
+            xv[k] = i < n ? __ldcg(x + i) : 0.0f;
+        }
+#pragma unroll
+        for (int k = 0; k < kPer; ++k) {
+            const int i = i0 + k * kMegaThreads;
+            if (i >= n) continue;
+            const int av = static_cast<int>(pr[k].y == seq ? pr[k].x : ll_load(acc + i, seq, status));
+            y_s[i] = __fadd_rn(xv[k], live ? __fmul_rn(static_cast<float>(av), post) : 0.0f);
+        }
     }
 }
 
@@ -929,10 +950,18 @@ __device__ __noinline__ bool phase_combine(const MegaArgs& a, unsigned int seq, 
         n_all = a.q_dim_full;
         const uint2* all = reinterpret_cast<const uint2*>(a.tp_box[a.tp_rank] + a.box_y);
         amax = 0.0f;
-        for (int i = tid; i < n_all; i += kMegaThreads) {
-            const float y = __uint_as_float(ll_load(all + i, seq, a.status));
-            v.y[i] = y;
-            amax = fmaxf(amax, fabsf(y));
+        for (int i0 = tid; i0 < n_all; i0 += 8 * kMegaThreads) {
+            uint2 pr[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) pr[k] = i0 + k * kMegaThreads < n_all ? ll_peek(all + i0 + k * kMegaThreads) : make_uint2(0u, seq);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const int i = i0 + k * kMegaThreads;
+                if (i >= n_all) continue;
+                const float y = __uint_as_float(pr[k].y == seq ? pr[k].x : ll_load(all + i, seq, a.status));
+                v.y[i] = y;
+                amax = fmaxf(amax, fabsf(y));
+            }
         }
     }
     amax = block_max_f32(amax, v.sh_f);
