@@ -216,6 +216,11 @@ typedef struct quintrit_b200_decoder_desc {
      * up and down - and, if lm_head is not NULL, its vocab_size / tp_world rows of the head (embed stays whole). After
      * creation the ranks exchange quintrit_b200_decoder_tp_handle and call quintrit_b200_decoder_tp_attach. */
     uint32_t tp_rank, tp_world;
+    /* 0: embed / lm_head hold F16 bit patterns (the reference's dense path, quintrit-runtime/src/model.rs:308-375);
+     * 1: BF16 bit patterns, with the reference's BF16 projection arithmetic (quintrit-runtime/src/hybrid.rs:327-333, 364-367:
+     * the row widened with bf16_to_f32, the normalised vector rounded with f32_to_bf16, rows through ggml_vec_dot_bf16,
+     * ops.rs:650-712). The hidden size must be a multiple of 32 either way. */
+    uint32_t table_dtype;
 } quintrit_b200_decoder_desc_t;
 
 int quintrit_b200_decoder_create(const quintrit_b200_decoder_desc_t* desc, quintrit_b200_decoder_t** out_decoder);
@@ -265,6 +270,7 @@ typedef struct quintrit_b200_decoder_info {
     uint32_t hidden_size, intermediate_size, num_layers, num_heads, num_kv_heads, head_dim, vocab_size, context_length, rope_dims;
     uint32_t device_index;
     uint32_t single_kernel; /* 1 if tokens are decoded by the one-kernel-per-token path */
+    uint32_t table_dtype;   /* 0 = F16 embedding and head, 1 = BF16 */
 } quintrit_b200_decoder_info_t;
 int quintrit_b200_decoder_info(const quintrit_b200_decoder_t* decoder, quintrit_b200_decoder_info_t* out_info);
 

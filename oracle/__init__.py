@@ -301,6 +301,11 @@ def _declare_model(l: C.CDLL) -> None:
     l.qto_model_create.argtypes = [C.c_int] * 11 + [C.c_float, C.c_float, _u16p, _u16p, _f32p, C.POINTER(_u8p), _f32p, C.POINTER(_f32p)]
     l.qto_model_free.argtypes = [C.c_void_p]
     l.qto_model_forward.argtypes = [C.c_void_p, C.c_uint32, _sz, _f32p]
+    l.qto_model_set_bf16_tables.argtypes = [C.c_void_p, C.c_int]
+    l.qto_vec_dot_bf16.restype = C.c_float
+    l.qto_vec_dot_bf16.argtypes = [_u16p, _u16p, _sz]
+    l.qto_f32_to_bf16.restype = C.c_uint16
+    l.qto_f32_to_bf16.argtypes = [C.c_float]
     l.qto_quantize_q8_0.argtypes = [_f32p, _sz, _i8p, _f32p]
     l.qto_block_scaled_dot_row.restype = C.c_float
     l.qto_block_scaled_dot_row.argtypes = [_u8p, _f32p, _i8p, _f32p, _sz]
@@ -422,6 +427,8 @@ class Model:
         self._h = l.qto_model_create(spec["arch"], int(spec["f32_values"]), spec["hidden"], spec["inter"], L, spec["q_heads"], spec["kv_heads"],
                                      spec["head_dim"], spec["vocab"], spec["ctx"], spec["rope_dims"], spec["eps"], spec["rope_theta"],
                                      _p(embed, _u16p), None if head is None else _p(head, _u16p), _p(out_norm, _f32p), w, _p(scales, _f32p), norms)
+        if spec.get("bf16_tables"):
+            l.qto_model_set_bf16_tables(self._h, 1)
 
     def forward(self, token: int, pos: int) -> np.ndarray:
         logits = np.zeros(self.spec["vocab"], np.float32)
@@ -459,3 +466,15 @@ def gemv_block_scaled(planar, w_scales, acts, a_scales, rows: int, cols: int) ->
     out = np.zeros(rows, np.float32)
     mlib().qto_gemv_block_scaled(_p(pl, _u8p), _p(ws, _f32p), _p(a, _i8p), _p(sc, _f32p), rows, cols, _p(out, _f32p))
     return out
+
+
+def vec_dot_bf16(x, y) -> np.float32:
+    """ggml_vec_dot_bf16 (ops.rs:688-712) of two vectors given as BF16 bit patterns."""
+    xx, yy = _c(x, np.uint16), _c(y, np.uint16)
+    return np.float32(mlib().qto_vec_dot_bf16(_p(xx, _u16p), _p(yy, _u16p), xx.size))
+
+
+def f32_to_bf16_bits(x) -> np.ndarray:
+    xx = _c(x, np.float32).reshape(-1)
+    l = mlib()
+    return np.array([l.qto_f32_to_bf16(float(v)) for v in xx], np.uint16)

@@ -387,6 +387,27 @@ void qto_attend_head(const float* q, const uint16_t* k, const uint16_t* v, size_
     free(acc);
 }
 
+/* rust/crates/quintrit-runtime/src/ops.rs:688-712 (ggml_vec_dot_bf16_scalar): four accumulators of eight lanes take
+ * acc + x*y with the product and the sum rounded separately (no FMA); (a0+a2)+(a1+a3); g_l = a_{l+4} + a_l;
+ * (g0+g2)+(g1+g3); the tail beyond whole groups of 32 is added in double precision. */
+float qto_vec_dot_bf16(const uint16_t* x, const uint16_t* y, size_t n) {
+    float acc[4][8] = {{0}};
+    size_t i = 0;
+    for (; i + 32 <= n; i += 32)
+        for (int j = 0; j < 4; ++j)
+            for (int l = 0; l < 8; ++l) {
+                const size_t k = i + 8 * (size_t)j + (size_t)l;
+                const float prod = qto_bf16_to_f32(x[k]) * qto_bf16_to_f32(y[k]);
+                acc[j][l] = acc[j][l] + prod;
+            }
+    float a[8];
+    for (int l = 0; l < 8; ++l) a[l] = (acc[0][l] + acc[2][l]) + (acc[1][l] + acc[3][l]);
+    const float g0 = a[4] + a[0], g1 = a[5] + a[1], g2 = a[6] + a[2], g3 = a[7] + a[3];
+    double sum = (double)((g0 + g2) + (g1 + g3));
+    for (; i < n; ++i) sum += (double)(qto_bf16_to_f32(x[i]) * qto_bf16_to_f32(y[i]));
+    return (float)sum;
+}
+
 /* rust/crates/quintrit-runtime/src/sampler.rs:73-83: first index of the strict maximum; NaN never wins */
 uint32_t qto_argmax(const float* logits, size_t n) {
     size_t best = 0;
@@ -414,6 +435,7 @@ typedef struct qto_model {
     const float** norms;     /* layers * 4: attn_norm, ffn_norm, attn_sub_norm, ffn_sub_norm (the last two NULL for arch 0) */
     uint16_t *kc, *vc;       /* [layer][pos][kv_head][head_dim] */
     uint8_t** w64;           /* 64-row tiled copies for the AVX-512 GEMV (same integers, only faster), or NULL */
+    int bf16_tables;         /* embedding and output head are BF16 instead of F16 (qto_model_set_bf16_tables) */
 } qto_model_t;
 
 qto_model_t* qto_model_create(int arch, int f32_values, int hidden, int inter, int layers, int q_heads, int kv_heads, int head_dim,
@@ -437,6 +459,8 @@ qto_model_t* qto_model_create(int arch, int f32_values, int hidden, int inter, i
     }
     return m;
 }
+void qto_model_set_bf16_tables(qto_model_t* m, int on) { m->bf16_tables = on != 0; }
+
 void qto_model_free(qto_model_t* m) {
     if (!m) return;
     free(m->kc);
@@ -481,7 +505,8 @@ void qto_model_forward(qto_model_t* m, uint32_t token, size_t pos, float* logits
     float* cache = (float*)malloc((size_t)m->rope_dims * 4);
     const float scale = 1.0f / sqrtf((float)m->head_dim); /* attention.rs:46 */
 
-    for (size_t i = 0; i < H; ++i) x[i] = qto_f16_to_f32(m->embed[(size_t)token * H + i]); /* model.rs:308-317 */
+    /* model.rs:308-317; BF16 tables: hybrid.rs:364-367 (bf16_to_f32 of the row) */
+    for (size_t i = 0; i < H; ++i) x[i] = m->bf16_tables ? qto_bf16_to_f32(m->embed[(size_t)token * H + i]) : qto_f16_to_f32(m->embed[(size_t)token * H + i]);
     for (int l = 0; l < m->layers; ++l) {
         const float** nw = m->norms + l * 4;
         qto_rms_norm(x, nw[0], H, m->eps, xn);
@@ -530,9 +555,10 @@ void qto_model_forward(qto_model_t* m, uint32_t token, size_t pos, float* logits
     }
     qto_rms_norm(x, m->out_norm, H, m->eps, xn); /* model.rs:326-331 */
     uint16_t* x16 = (uint16_t*)malloc(H * 2);
-    for (size_t i = 0; i < H; ++i) x16[i] = qto_f32_to_f16(xn[i]);
+    for (size_t i = 0; i < H; ++i) x16[i] = m->bf16_tables ? qto_f32_to_bf16(xn[i]) : qto_f32_to_f16(xn[i]); /* hybrid.rs:327-333 for BF16 */
     const uint16_t* head = m->lm_head ? m->lm_head : m->embed;
 #pragma omp parallel for schedule(static)
-    for (long t = 0; t < (long)m->vocab; ++t) logits[t] = qto_vec_dot_f16(x16, head + (size_t)t * H, H); /* model.rs:346-375 */
+    for (long t = 0; t < (long)m->vocab; ++t) /* model.rs:346-375 */
+        logits[t] = m->bf16_tables ? qto_vec_dot_bf16(x16, head + (size_t)t * H, H) : qto_vec_dot_f16(x16, head + (size_t)t * H, H);
     free(x16), free(x), free(xn), free(q), free(k), free(v), free(att), free(gate), free(up), free(inter), free(delta), free(a8), free(cache);
 }

@@ -44,7 +44,7 @@ class _GpuOptionsC(C.Structure):
 class _DecoderInfoC(C.Structure):
     _fields_ = [("struct_size", C.c_uint32), ("arch", C.c_int32), ("f32_values", C.c_int32)] + [
         (n, C.c_uint32) for n in ("hidden_size", "intermediate_size", "num_layers", "num_heads", "num_kv_heads", "head_dim", "vocab_size",
-                                  "context_length", "rope_dims", "device_index", "single_kernel")]
+                                  "context_length", "rope_dims", "device_index", "single_kernel", "table_dtype")]
 
 
 class _DecoderDescC(C.Structure):
@@ -53,7 +53,7 @@ class _DecoderDescC(C.Structure):
                 ("num_kv_heads", C.c_uint32), ("head_dim", C.c_uint32), ("vocab_size", C.c_uint32), ("context_length", C.c_uint32),
                 ("rope_dims", C.c_uint32), ("rms_norm_eps", C.c_float), ("rope_theta", C.c_float), ("embed", C.POINTER(C.c_uint16)),
                 ("lm_head", C.POINTER(C.c_uint16)), ("output_norm", _f32p), ("matrices", C.POINTER(C.c_void_p)), ("scales", _f32p),
-                ("norms", C.POINTER(_f32p)), ("tp_rank", C.c_uint32), ("tp_world", C.c_uint32)]
+                ("norms", C.POINTER(_f32p)), ("tp_rank", C.c_uint32), ("tp_world", C.c_uint32), ("table_dtype", C.c_uint32)]
 
 
 @dataclass
@@ -358,6 +358,7 @@ class Decoder:
         d.output_norm = _p(out_norm, _f32p)
         d.matrices, d.scales, d.norms = mats, _p(scales, _f32p), norms
         d.tp_rank, d.tp_world = self.tp_rank, self.tp_world
+        d.table_dtype = 1 if spec.get("bf16_tables") else 0
         h = C.c_void_p()
         _check(load_library().quintrit_b200_decoder_create(C.byref(d), C.byref(h)))
         self._h = h

@@ -796,6 +796,9 @@ int decoder_create_impl(const quintrit_b200_decoder_desc_t* desc, quintrit_b200_
     }
     if (tp_world != 1 && tp_world != 2 && tp_world != 4 && tp_world != 8) return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "tp_world %u must be 1, 2, 4 or 8", tp_world);
     if (tp_rank >= tp_world) return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "tp_rank %u is not below tp_world %u", tp_rank, tp_world);
+    uint32_t table_dtype = 0;
+    if (desc->struct_size >= offsetof(quintrit_b200_decoder_desc_t, table_dtype) + sizeof(uint32_t)) table_dtype = desc->table_dtype;
+    if (table_dtype > 1) return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "table_dtype %u is not 0 (F16) or 1 (BF16)", table_dtype);
     const uint32_t H = desc->hidden_size, I_full = desc->intermediate_size, L = desc->num_layers, hd = desc->head_dim;
     if (!H || !I_full || !L || !desc->num_heads || !desc->num_kv_heads || !hd || !desc->vocab_size)
         return fail(QUINTRIT_ERR_MODEL, "a model dimension is zero");
@@ -807,6 +810,7 @@ int decoder_create_impl(const quintrit_b200_decoder_desc_t* desc, quintrit_b200_
     }
     const uint32_t I = I_full / tp_world;  // this rank's rows of gate and up
     if (hd % 32 != 0 || hd > 256) return fail(QUINTRIT_ERR_UNSUPPORTED, "head_dim %u is not supported (a multiple of 32, at most 256)", hd);
+    if (H % 32 != 0) return fail(QUINTRIT_ERR_UNSUPPORTED, "the hidden size %u must be a multiple of 32", H);  // as gpu.rs:171-173
     if (desc->num_heads % desc->num_kv_heads != 0) return fail(QUINTRIT_ERR_MODEL, "num_heads is not a multiple of num_kv_heads");
     if (desc->rope_dims == 0 || desc->rope_dims % 2 != 0 || desc->rope_dims > hd)
         return fail(QUINTRIT_ERR_MODEL, "rope_dims %u must be even and at most the head dimension %u", desc->rope_dims, hd);
@@ -837,6 +841,7 @@ int decoder_create_impl(const quintrit_b200_decoder_desc_t* desc, quintrit_b200_
     d->arch = desc->arch, d->f32_values = desc->f32_values != 0;
     d->hidden = H, d->inter = I, d->layers = L, d->q_heads = desc->num_heads / tp_world, d->kv_heads = desc->num_kv_heads / tp_world, d->head_dim = hd;
     d->tp_rank = static_cast<int>(tp_rank), d->tp_world = static_cast<int>(tp_world);
+    d->bf16_tables = table_dtype == 1;
     d->q_dim_full = static_cast<int>(qd_full), d->inter_full = static_cast<int>(I_full), d->vocab_full = static_cast<int>(desc->vocab_size);
     d->vocab = vocab_local, d->ctx = ctx, d->rope_dims = desc->rope_dims, d->q_dim = static_cast<int>(qd), d->kv_dim = static_cast<int>(kvd);
     d->eps = desc->rms_norm_eps, d->rope_theta = desc->rope_theta;
@@ -1034,6 +1039,7 @@ int mega_setup(quintrit_b200_decoder* d, const quintrit_b200_decoder_desc_t* des
     a.acc_qkv = d->acc_qkv, a.acc_o = d->acc_o, a.acc_gu = d->acc_gu, a.acc_down = d->acc_down;
     a.v_inter = d->v_inter, a.amax_bits = d->amax_bits, a.part_acc = d->part_acc, a.part_ms = d->part_ms, a.logits = d->logits;
     a.scores = d->scores, a.attn_region = static_cast<unsigned int>(mega_attn_region(d->ctx, d->q_heads / d->kv_heads, d->head_dim));
+    a.bf16_tables = d->bf16_tables ? 1 : 0;
     a.tp_rank = d->tp_rank, a.tp_world = d->tp_world, a.tp_seq = d->tp_seq;
     for (int p = 0; p < 8; ++p) a.tp_box[p] = nullptr;
     a.tp_box[d->tp_rank] = d->tp_box;
@@ -1223,10 +1229,13 @@ int open_gguf_impl(const char* path, const quintrit_gpu_options_t* options, quin
     if (ctx == 0) return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "the context window is smaller than 256 positions");
     const uint64_t qd = m.heads * m.head_dim, kvd = m.kv_heads * m.head_dim;
 
+    uint32_t table_type = kGgmlF16;
+    if (const GgufTensor* e = g.tensor("token_embd.weight"))
+        if (e->type == kGgmlBF16) table_type = kGgmlBF16;
     auto dense_f16 = [&](const char* name, uint64_t n, const uint16_t** outp) -> int {
         const GgufTensor* t = g.tensor(name);
         if (t == nullptr) return fail(QUINTRIT_ERR_MODEL, "Missing %s tensor", name);
-        if (t->type != kGgmlF16) return fail(QUINTRIT_ERR_UNSUPPORTED, "%s is not F16; the GPU decoder needs an F16 embedding and head", name);
+        if (t->type != table_type) return fail(QUINTRIT_ERR_UNSUPPORTED, "%s is not %s; the GPU decoder needs an embedding and a head that are both F16 or both BF16", name, table_type == kGgmlF16 ? "F16" : "BF16");
         uint64_t len = 0;
         const uint8_t* p = g.data(*t, &len);
         if (p == nullptr || len != n * 2) return fail(QUINTRIT_ERR_MODEL, "%s has %llu values, expected %llu", name, static_cast<unsigned long long>(len / 2), static_cast<unsigned long long>(n));
@@ -1298,6 +1307,7 @@ int open_gguf_impl(const char* path, const quintrit_gpu_options_t* options, quin
     desc.head_dim = static_cast<uint32_t>(m.head_dim), desc.vocab_size = static_cast<uint32_t>(m.vocab), desc.context_length = static_cast<uint32_t>(ctx);
     desc.rope_dims = static_cast<uint32_t>(m.rope_dims), desc.rms_norm_eps = m.eps, desc.rope_theta = m.theta;
     desc.embed = embed, desc.lm_head = head, desc.output_norm = out_norm;
+    desc.table_dtype = table_type == kGgmlBF16 ? 1u : 0u;
     desc.matrices = reinterpret_cast<const quintrit_b200_matrix_t* const*>(mats.data());
     desc.scales = scales.data();
     desc.norms = norms.data();
@@ -1341,6 +1351,7 @@ extern "C" int quintrit_b200_decoder_info(const quintrit_b200_decoder_t* decoder
         out_info->num_heads = d->q_heads, out_info->num_kv_heads = d->kv_heads, out_info->head_dim = d->head_dim;
         out_info->vocab_size = d->vocab_full, out_info->context_length = d->ctx, out_info->rope_dims = d->rope_dims;
         out_info->device_index = static_cast<uint32_t>(d->device), out_info->single_kernel = d->use_mega ? 1 : 0;
+        out_info->table_dtype = d->bf16_tables ? 1 : 0;
         return ok();
     });
 }

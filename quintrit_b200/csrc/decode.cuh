@@ -92,10 +92,29 @@ __device__ __forceinline__ float ggml_silu(float x) {
     return __fdiv_rn(x, __fadd_rn(1.0f, ggml_expf_lane(__fsub_rn(0.0f, x))));
 }
 
+// ---- BF16 tables (ops.rs:650-664): widening is a shift; narrowing rounds to nearest even and keeps a NaN quiet --------
+__device__ __forceinline__ float bf16_bits_to_float(unsigned short h) { return __uint_as_float(static_cast<uint32_t>(h) << 16); }
+__device__ __forceinline__ unsigned short float_to_bf16_bits(float f) {
+    const uint32_t u = __float_as_uint(f);
+    if ((u & 0x7FFFFFFFu) > 0x7F800000u) return static_cast<unsigned short>((u >> 16) | 64u);
+    return static_cast<unsigned short>((u + (0x7FFFu + ((u >> 16) & 1u))) >> 16);
+}
+// A table entry (F16 or BF16 bit pattern) as float.
+__device__ __forceinline__ float table_to_float(__half h, bool bf16) { return bf16 ? bf16_bits_to_float(__half_as_ushort(h)) : __half2float(h); }
+// ggml_vec_dot_bf16's reduction of the 32 lanes (ops.rs:702-708): (a0+a2)+(a1+a3), g_l = a_{l+4}+a_l, (g0+g2)+(g1+g3).
+__device__ __forceinline__ float dot_lane_reduce_bf16(float v) {
+    v = __fadd_rn(v, __shfl_down_sync(0xffffffffu, v, 16));
+    v = __fadd_rn(v, __shfl_down_sync(0xffffffffu, v, 8));
+    v = __fadd_rn(__shfl_down_sync(0xffffffffu, v, 4), v);
+    v = __fadd_rn(v, __shfl_down_sync(0xffffffffu, v, 2));
+    v = __fadd_rn(v, __shfl_down_sync(0xffffffffu, v, 1));
+    return v;  // lane 0
+}
+
 // ---- embedding row: model.rs:308-317 ---------------------------------------------------------------------------------
-__global__ void embed_kernel(const __half* __restrict__ table, const uint32_t* __restrict__ token, int hidden, float* __restrict__ x) {
+__global__ void embed_kernel(const __half* __restrict__ table, const uint32_t* __restrict__ token, int hidden, float* __restrict__ x, bool bf16) {
     const size_t base = static_cast<size_t>(token[0]) * hidden;
-    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < hidden; i += gridDim.x * blockDim.x) x[i] = __half2float(table[base + i]);
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < hidden; i += gridDim.x * blockDim.x) x[i] = table_to_float(table[base + i], bf16);
 }
 
 // Arguments of the fused "finish the previous projection, normalise, quantise" kernel.
@@ -109,7 +128,8 @@ struct NormQuantArgs {
     int n;
     int8_t* q_out;            // int8 codes (n), or nullptr: then the normalised vector is written to y_out as F16 bits (final norm)
     float* scale_out;         // activation scale of q_out
-    __half* y16_out;          // F16 of the normalised vector (final norm before the output head)
+    __half* y16_out;          // F16 (or BF16 bits, y16_bf16) of the normalised vector (final norm before the output head)
+    bool y16_bf16;
     int32_t* zero_a;          // result buffers of the next projections, cleared here (the GEMV adds into them)
     int zero_a_n;
     int32_t* zero_b;
@@ -153,7 +173,7 @@ __global__ void __launch_bounds__(kRowThreads) norm_quant_kernel(NormQuantArgs a
         amax = fmaxf(amax, fabsf(y));
     }
     if (a.q_out == nullptr) {
-        for (int i = tid; i < a.n; i += kRowThreads) a.y16_out[i] = __float2half_rn(y_s[i]);
+        for (int i = tid; i < a.n; i += kRowThreads) a.y16_out[i] = a.y16_bf16 ? __ushort_as_half(float_to_bf16_bits(y_s[i])) : __float2half_rn(y_s[i]);
         return;
     }
     amax = block_max_f32(amax, sh_f);
@@ -520,22 +540,24 @@ __global__ void __launch_bounds__(kRowThreads) act_quant_kernel(ActQuantArgs a) 
 
 // ---- output head: one warp per vocabulary row, ggml_vec_dot_f16 order (model.rs:346-375, ops.rs:970-1014) --------------
 __global__ void __launch_bounds__(256) lm_head_kernel(const __half* __restrict__ w, const __half* __restrict__ x16, int hidden, int vocab,
-                                                      float* __restrict__ logits) {
+                                                      float* __restrict__ logits, bool bf16) {
     extern __shared__ float x_s[];  // hidden floats
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) x_s[i] = __half2float(x16[i]);
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) x_s[i] = table_to_float(x16[i], bf16);
     __syncthreads();
     const int lane = threadIdx.x & 31, warps = blockDim.x >> 5;
-    const int np = hidden & ~31;
+    const int np = hidden & ~31;  // hidden is a multiple of 32 (checked at creation): no scalar tail
     for (int row = blockIdx.x * warps + (threadIdx.x >> 5); row < vocab; row += gridDim.x * warps) {
         const __half* wr = w + static_cast<size_t>(row) * hidden;
         float acc = 0.0f;
+        if (bf16) {  // ggml_vec_dot_bf16: product and sum rounded separately (ops.rs:694-700)
 #pragma unroll 8
-        for (int i = 0; i < np; i += 32) acc = __fmaf_rn(x_s[i + lane], __half2float(wr[i + lane]), acc);
-        float sum = dot_lane_reduce_f16(acc);
-        if (lane == 0) {
-            for (int i = np; i < hidden; ++i) sum = __fadd_rn(sum, __fmul_rn(x_s[i], __half2float(wr[i])));
-            logits[row] = sum;
+            for (int i = 0; i < np; i += 32) acc = __fadd_rn(acc, __fmul_rn(x_s[i + lane], bf16_bits_to_float(__half_as_ushort(wr[i + lane]))));
+        } else {
+#pragma unroll 8
+            for (int i = 0; i < np; i += 32) acc = __fmaf_rn(x_s[i + lane], __half2float(wr[i + lane]), acc);
         }
+        const float sum = bf16 ? dot_lane_reduce_bf16(acc) : dot_lane_reduce_f16(acc);
+        if (lane == 0) logits[row] = sum;
     }
 }
 

@@ -46,6 +46,7 @@ struct quintrit_b200_decoder {
     bool graph_ready;
     uint32_t host_pos;                         // tokens in the KV cache
     // tensor parallelism: this rank's share of a model split over tp_world GPUs (1 = none)
+    bool bf16_tables = false;                  // embedding and output head hold BF16 instead of F16 bit patterns
     int tp_rank = 0, tp_world = 1;
     int q_dim_full = 0, inter_full = 0, vocab_full = 0;
     unsigned char* tp_box = nullptr;           // the exchange box of this rank (one allocation, shared with the peers)
@@ -115,7 +116,7 @@ inline int decoder_gemv(quintrit_b200_decoder* d, int layer, int which, const in
 inline int enqueue_token(quintrit_b200_decoder* d, bool with_head) {
     cudaStream_t s = d->stream;
     const int H = d->hidden, I = d->inter, qd = d->q_dim, kvd = d->kv_dim;
-    embed_kernel<<<(H + 255) / 256, 256, 0, s>>>(d->embed, d->d_token, H, d->x);
+    embed_kernel<<<(H + 255) / 256, 256, 0, s>>>(d->embed, d->d_token, H, d->x, d->bf16_tables);
     QTB_LAUNCH_CHECK();
     for (int l = 0; l < d->layers; ++l) {
         const float* sc = d->scales.data() + l * 7;
@@ -218,9 +219,10 @@ inline int enqueue_token(quintrit_b200_decoder* d, bool with_head) {
         nf.eps = d->eps;
         nf.n = H;
         nf.y16_out = d->x16;
+        nf.y16_bf16 = d->bf16_tables;
         norm_quant_kernel<<<1, kRowThreads, H * sizeof(float), s>>>(nf);
         QTB_LAUNCH_CHECK();
-        lm_head_kernel<<<d->sm_count * 8, 256, H * sizeof(float), s>>>(d->lm_head, d->x16, H, d->vocab, d->logits);
+        lm_head_kernel<<<d->sm_count * 8, 256, H * sizeof(float), s>>>(d->lm_head, d->x16, H, d->vocab, d->logits, d->bf16_tables);
         QTB_LAUNCH_CHECK();
         argmax_kernel<<<1, 1024, 0, s>>>(d->logits, d->vocab, d->d_token);
         QTB_LAUNCH_CHECK();

@@ -65,6 +65,7 @@ struct MegaArgs {
     // vectors that every rank needs whole (o and down results, attention output, SwiGLU output) live in a "box" of which
     // every rank has one; ranks write their slices straight into the boxes of all ranks over NVLink as (value, sequence
     // number) pairs that the readers poll.
+    int bf16_tables;           // embedding and output head hold BF16 instead of F16 bit patterns
     int tp_rank, tp_world;
     unsigned char* tp_box[8];  // the boxes as mapped into this process, own box at [tp_rank]
     unsigned int* tp_seq;      // exchanges completed by earlier launches (the same on every rank)
@@ -799,7 +800,7 @@ __device__ __noinline__ bool phase_norm(const MegaArgs& a, int l, int which, uns
     if (which == 0) {
         if (l == 0) {
             const size_t base = static_cast<size_t>(a.token[0]) * H;
-            for (int i = tid; i < H; i += kMegaThreads) v.y[i] = __half2float(a.embed[base + i]);
+            for (int i = tid; i < H; i += kMegaThreads) v.y[i] = table_to_float(a.embed[base + i], a.bf16_tables != 0);
         } else {
             const float s_prev = v.scale[3];
             const float post = s_prev > 0.0f ? __fdiv_rn(v.layers[l - 1].ws[6], s_prev) : 0.0f;
@@ -1030,7 +1031,9 @@ __device__ __noinline__ bool phase_head(const MegaArgs& a, unsigned int seq_base
     cp_async_wait<0>();
     __syncthreads();
     mega_norm_quant(y_s, v.w, H, a.eps, nullptr, v.sh_d, v.sh_f);
-    for (int i = tid; i < H; i += kMegaThreads) y_s[i] = __half2float(__float2half_rn(y_s[i]));  // model.rs:347-349
+    const bool bf16 = a.bf16_tables != 0;
+    for (int i = tid; i < H; i += kMegaThreads)  // model.rs:347-349; BF16 tables: hybrid.rs:327-333
+        y_s[i] = bf16 ? bf16_bits_to_float(float_to_bf16_bits(y_s[i])) : __half2float(__float2half_rn(y_s[i]));
     __syncthreads();
     float bv = -INFINITY;
     unsigned int bi = 0xFFFFFFFFu;
@@ -1063,14 +1066,17 @@ __device__ __noinline__ bool phase_head(const MegaArgs& a, unsigned int seq_base
         const __half* buf = ring + (q % kHeadStages) * kHeadSeg;
         const float* xs = y_s + sg * kHeadSeg;
         const int cnt = min(kHeadSeg, np - sg * kHeadSeg);
+        if (bf16) {  // ggml_vec_dot_bf16: product and sum rounded separately
 #pragma unroll 8
-        for (int i = 0; i < cnt; i += 32) acc = __fmaf_rn(xs[i + lane], __half2float(buf[i + lane]), acc);
+            for (int i = 0; i < cnt; i += 32) acc = __fadd_rn(acc, __fmul_rn(xs[i + lane], bf16_bits_to_float(__half_as_ushort(buf[i + lane]))));
+        } else {
+#pragma unroll 8
+            for (int i = 0; i < cnt; i += 32) acc = __fmaf_rn(xs[i + lane], __half2float(buf[i + lane]), acc);
+        }
         if (sg == nseg - 1) {
             const int row = first_row + (q / nseg) * row_stride;
-            float sum = dot_lane_reduce_f16(acc);
+            const float sum = bf16 ? dot_lane_reduce_bf16(acc) : dot_lane_reduce_f16(acc);  // hidden is a multiple of 32: no tail
             if (lane == 0) {
-                const __half* wr = a.lm_head + static_cast<size_t>(row) * H;
-                for (int i = np; i < H; ++i) sum = __fadd_rn(sum, __fmul_rn(y_s[i], __half2float(wr[i])));
                 a.logits[row] = sum;
                 argmax_merge(bv, bi, sum, static_cast<unsigned int>(row + a.vocab_base));
             }

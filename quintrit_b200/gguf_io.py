@@ -15,7 +15,7 @@ import struct
 
 import numpy as np
 
-GGML_F32, GGML_F16, GGML_TQ1_0, GGML_TQ2_0, GGML_I2_S, GGML_Q2_0 = 0, 1, 34, 35, 36, 42
+GGML_F32, GGML_F16, GGML_BF16, GGML_TQ1_0, GGML_TQ2_0, GGML_I2_S, GGML_Q2_0 = 0, 1, 30, 34, 35, 36, 42
 ALIGNMENT = 32
 
 
@@ -129,7 +129,8 @@ def write_model_gguf(path, spec: dict, trits: list, encoding: int = GGML_I2_S, a
         f"{architecture}.attention.layer_norm_rms_epsilon": float(spec["eps"]), f"{architecture}.rope.freq_base": float(spec["rope_theta"]),
         f"{architecture}.rope.dimension_count": spec["rope_dims"], f"{architecture}.context_length": spec["ctx"],
     }
-    tensors = [("token_embd.weight", (H, spec["vocab"]), GGML_F16, np.ascontiguousarray(spec["embed"], np.uint16).tobytes())]
+    table_type = GGML_BF16 if spec.get("bf16_tables") else GGML_F16
+    tensors = [("token_embd.weight", (H, spec["vocab"]), table_type, np.ascontiguousarray(spec["embed"], np.uint16).tobytes())]
     norm_names = ["attn_norm", "ffn_norm", "attn_sub_norm", "ffn_sub_norm"]
     for l in range(L):
         for k in range(7):
@@ -150,5 +151,5 @@ def write_model_gguf(path, spec: dict, trits: list, encoding: int = GGML_I2_S, a
                 tensors.append((f"blk.{l}.{norm_names[k]}.weight", (len(w),), GGML_F32, np.ascontiguousarray(w, np.float32).tobytes()))
     tensors.append(("output_norm.weight", (H,), GGML_F32, np.ascontiguousarray(spec["out_norm"], np.float32).tobytes()))
     if spec.get("lm_head") is not None:
-        tensors.append(("output.weight", (H, spec["vocab"]), GGML_F16, np.ascontiguousarray(spec["lm_head"], np.uint16).tobytes()))
+        tensors.append(("output.weight", (H, spec["vocab"]), table_type, np.ascontiguousarray(spec["lm_head"], np.uint16).tobytes()))
     write_gguf(path, meta, tensors)

@@ -116,7 +116,7 @@ def quantize_int8_np(x: np.ndarray):
 
 def make_model(arch: int, f32_values: bool, hidden: int, inter: int, layers: int, q_heads: int, kv_heads: int, head_dim: int, vocab: int,
                ctx: int, rope_theta: float, eps: float, config: int = 1, tied: bool = False, rope_dims: int | None = None,
-               random_norms: bool = False) -> dict:
+               random_norms: bool = False, bf16_tables: bool = False) -> dict:
     """A seeded random-init model of the given shape as numpy arrays (planar velurex projections, F16 tables).
 
     Ternary projections and their scales come from the streams documented at the top of this module; embedding and
@@ -140,9 +140,16 @@ def make_model(arch: int, f32_values: bool, hidden: int, inter: int, layers: int
             scales.append(weight_scale(seed_for(config, l, p, 1)))
         norms += [norm(seed_for(config, l, 7, 0), hidden), norm(seed_for(config, l, 7, 1), hidden),
                   norm(seed_for(config, l, 7, 2), qd) if arch == 1 else None, norm(seed_for(config, l, 7, 3), inter) if arch == 1 else None]
-    embed = (normal_f32(seed_for(config, 255, 0, 0), vocab * hidden) * np.float32(0.02)).astype(np.float16).view(np.uint16)
-    head = None if tied else (normal_f32(seed_for(config, 255, 1, 0), vocab * hidden) * np.float32(0.02)).astype(np.float16).view(np.uint16)
-    return dict(arch=arch, f32_values=f32_values, hidden=hidden, inter=inter, layers=layers, q_heads=q_heads, kv_heads=kv_heads,
+    def table(seed):  # N(0, 0.02) as F16 bits, or as BF16 bits rounded to nearest even
+        x = normal_f32(seed, vocab * hidden) * np.float32(0.02)
+        if not bf16_tables:
+            return x.astype(np.float16).view(np.uint16)
+        u = x.view(np.uint32)
+        return ((u + (np.uint32(0x7FFF) + ((u >> np.uint32(16)) & np.uint32(1)))) >> np.uint32(16)).astype(np.uint16)
+
+    embed = table(seed_for(config, 255, 0, 0))
+    head = None if tied else table(seed_for(config, 255, 1, 0))
+    return dict(bf16_tables=bf16_tables, arch=arch, f32_values=f32_values, hidden=hidden, inter=inter, layers=layers, q_heads=q_heads, kv_heads=kv_heads,
                 head_dim=head_dim, vocab=vocab, ctx=ctx, rope_dims=rope_dims or head_dim, eps=eps, rope_theta=rope_theta, weights=weights,
                 scales=np.array(scales, np.float32), norms=norms, embed=embed, lm_head=head, out_norm=norm(seed_for(config, 255, 2, 0), hidden))
 

@@ -83,3 +83,14 @@ def test_invalid_decoder_calls():
     bad = dict(spec, head_dim=48, q_heads=2, kv_heads=1)
     with pytest.raises(q.QuintritError):
         q.Decoder(bad)
+
+
+@pytest.mark.parametrize("arch", [q.ARCH_LLAMA, q.ARCH_BITNET])
+def test_bf16_embedding_and_head(oracle, arch):
+    """BF16 tables with the reference's BF16 projection arithmetic (hybrid.rs:327-333, ops.rs:650-712): the single-kernel path
+    (LLaMA) and the one-kernel-per-step path (BitNet) against the oracle."""
+    spec = synth.make_model(arch, False, 320, 704, 2, 4, 2, 64, 300, 256, 500000.0, 1e-5, config=17, random_norms=True, bf16_tables=True,
+                            tied=(arch == q.ARCH_BITNET))
+    dec, _ = _run(spec, synth.prompt_tokens(6, 10, spec["vocab"]), oracle)
+    assert dec.info()["table_dtype"] == 1
+    dec.free()

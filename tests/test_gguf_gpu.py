@@ -117,3 +117,20 @@ def test_rejections(tmp_path):
     tq.write_bytes(bytes(data))
     c, msg = code(tq)
     assert c == 6 and "block scales" in msg
+
+
+def test_bf16_tables_from_a_file(tmp_path):
+    spec = synth.make_model(q.ARCH_LLAMA, False, 256, 512, 2, 4, 2, 64, 300, 512, 500000.0, 1e-5, config=14, random_norms=True, bf16_tables=True)
+    shapes = [(256, 256), (128, 256), (128, 256), (256, 256), (512, 256), (512, 256), (256, 512)]
+    trits = [synth.trits(synth.seed_for(14, l, p, 0), r * c).reshape(r, c) for l in range(2) for p, (r, c) in enumerate(shapes)]
+    path = tmp_path / "bf16.gguf"
+    gguf_io.write_model_gguf(path, spec, trits, gguf_io.GGML_I2_S)
+    assert any(t["name"] == "output.weight" and t["type"] == 30 for t in q.gguf_describe(path)["tensors"])
+    dec = q.Decoder.open(path)
+    assert dec.info()["table_dtype"] == 1
+    ref = oracle.Model(spec)
+    for pos, tok in enumerate(synth.prompt_tokens(8, 6, spec["vocab"])):
+        want = ref.forward(int(tok), pos)
+        got, _ = dec.forward(int(tok), pos)
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), pos
+    dec.free()

@@ -157,3 +157,28 @@ def test_attention_matches_softmax_across_padding_and_chunk_borders(oracle):
 def test_argmax_takes_the_first_maximum(oracle):
     assert oracle.argmax(np.float32([1, 5, 5, 2])) == 1
     assert oracle.argmax(np.float32([np.nan, -1, np.nan])) == 1
+
+
+def test_vec_dot_bf16_follows_the_documented_order(oracle):
+    """rust/crates/quintrit-runtime/src/ops.rs:688-712: 4 x 8 lanes, product and sum rounded separately (no FMA),
+    (a0+a2)+(a1+a3), g_l = a_{l+4}+a_l, (g0+g2)+(g1+g3), tail in double."""
+    rng = np.random.default_rng(4)
+    for n in (32, 64, 320, 3072, 45, 100):
+        x = oracle.f32_to_bf16_bits(rng.standard_normal(n).astype(np.float32))
+        y = oracle.f32_to_bf16_bits((rng.standard_normal(n) * 0.02).astype(np.float32))
+        xf = (x.astype(np.uint32) << 16).view(np.float32)
+        yf = (y.astype(np.uint32) << 16).view(np.float32)
+        acc = np.zeros((4, 8), np.float32)
+        full = n // 32 * 32
+        for i in range(0, full, 32):
+            prod = (xf[i:i + 32] * yf[i:i + 32]).astype(np.float32).reshape(4, 8)
+            acc = (acc + prod).astype(np.float32)
+        a = ((acc[0] + acc[2]).astype(np.float32) + (acc[1] + acc[3]).astype(np.float32)).astype(np.float32)
+        g = (a[4:] + a[:4]).astype(np.float32)
+        s = np.float64(np.float32(np.float32(g[0] + g[2]) + np.float32(g[1] + g[3])))
+        for k in range(full, n):
+            s += np.float64(np.float32(xf[k] * yf[k]))
+        want = np.float32(s)
+        assert oracle.vec_dot_bf16(x, y).view(np.uint32) == want.view(np.uint32), n
+    ones = np.full(64, 0x3F80, np.uint16)
+    assert oracle.vec_dot_bf16(ones, ones) == np.float32(64.0)
