@@ -1085,6 +1085,7 @@ int decoder_check_status(quintrit_b200_decoder* d) {
     unsigned int flag = 0;
     QTB_CUDA(cudaMemcpyAsync(&flag, d->d_counters + 2, sizeof flag, cudaMemcpyDeviceToHost, d->stream));
     QTB_CUDA(cudaStreamSynchronize(d->stream));
+    if (flag == 3) return fail(QUINTRIT_ERR_DEVICE, "the decode kernel on the CUDA device gave up waiting for another rank of the tensor-parallel group");
     if (flag == 2) return fail(QUINTRIT_ERR_DEVICE, "the decode kernel on the CUDA device gave up waiting at a grid barrier");
     if (flag != 0) return fail(QUINTRIT_ERR_DEVICE, "a kernel on the CUDA device found its shared-memory table at an unexpected address");
     return QUINTRIT_OK;

@@ -23,7 +23,7 @@ namespace qtb {
 constexpr int kMegaThreads = 512;
 constexpr int kMegaWarps = kMegaThreads / 32;
 constexpr int kMegaMaxHeads = 64;
-constexpr unsigned int kBarrierSpinLimit = 1u << 21;  // polls of ~50 ns: about 0.1 s, then the kernel gives up
+constexpr unsigned int kBarrierSpinLimit = 1u << 21;  // polls of one L2 round trip each (~0.7 us): about 1.5 s, then the kernel gives up
 
 struct MegaLayer {
     int first[4], count[4];   // work items of the q|k|v, o, gate|up and down launches (indices into MegaArgs::items)
@@ -93,26 +93,37 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
     } while (0)
 #endif
 
-// Grid-wide barrier with a bounded wait. Returns false (in every thread of the CTA) if it gave up.
+// Grid-wide barrier with a bounded wait. Returns false (in every thread of the CTA) if it gave up or if any thread of the
+// grid reported a failure. The barrier counter doubles as the failure signal: whoever gives up (here or in an exchange
+// between GPUs) adds kBarFail to it, which releases every waiter at once and is recognised by its size, so the polling
+// loop reads one word only. The host clears the counter before every launch; legitimate targets stay far below kBarFail.
+constexpr unsigned int kBarFail = 1u << 30;
+
+__device__ __forceinline__ void report_failure(unsigned int* bar, unsigned int* status, unsigned int code) {
+    atomicMax(status, code);
+    atomicAdd(bar, kBarFail);
+}
+
 __device__ __forceinline__ bool grid_barrier(unsigned int* bar, unsigned int target, unsigned int* status, int* s_flag) {
     __syncthreads();
     if (threadIdx.x == 0) {
         __threadfence();
         atomicAdd(bar, 1u);
         int okay = 1;
-        unsigned int spins = 0;
-        while (true) {
+        for (unsigned int spins = 0;; ++spins) {
             unsigned int v;
             asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(bar));
-            if (v >= target) break;
-            if (++spins > kBarrierSpinLimit || *reinterpret_cast<volatile unsigned int*>(status) != 0u) {
-                atomicMax(status, 2u);
+            if (v >= kBarFail) {
                 okay = 0;
                 break;
             }
-            __nanosleep(32);
+            if (v >= target) break;
+            if (spins > kBarrierSpinLimit) {
+                report_failure(bar, status, 2u);
+                okay = 0;
+                break;
+            }
         }
-        if (*reinterpret_cast<volatile unsigned int*>(status) != 0u) okay = 0;  // e.g. an exchange that timed out
         *s_flag = okay;
     }
     __syncthreads();
@@ -132,9 +143,9 @@ __device__ __forceinline__ void ll_store(uint2* p, uint32_t value, uint32_t seq)
     asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(value), "r"(seq) : "memory");
 }
 
-// Value of a pair once it carries `seq`. Bounded: after kTpWaitLimitNs (or when the status word is set already) the
-// kernel's status becomes 3 and 0 is returned; the next grid barrier then ends the kernel.
-__device__ __forceinline__ uint32_t ll_load(const uint2* p, uint32_t seq, unsigned int* status) {
+// Value of a pair once it carries `seq`. Bounded: after kTpWaitLimitNs the kernel's status becomes 3, the failure is
+// signalled through the barrier counter (the next grid barrier ends the kernel) and 0 is returned.
+__device__ __forceinline__ uint32_t ll_load(const uint2* p, uint32_t seq, const MegaArgs& a) {
     uint32_t value, got;
     unsigned long long t0 = 0;
     for (unsigned int spins = 0;; ++spins) {
@@ -143,8 +154,8 @@ __device__ __forceinline__ uint32_t ll_load(const uint2* p, uint32_t seq, unsign
         if ((spins & 255u) == 255u) {
             const unsigned long long now = global_timer_ns();
             if (t0 == 0) t0 = now;
-            if (now - t0 > kTpWaitLimitNs || *reinterpret_cast<volatile unsigned int*>(status) != 0u) {
-                atomicMax(status, 3u);
+            if (now - t0 > kTpWaitLimitNs || *reinterpret_cast<volatile unsigned int*>(a.bar) >= kBarFail) {
+                report_failure(a.bar, a.status, 3u);
                 return 0u;
             }
         }
@@ -329,7 +340,7 @@ __device__ __forceinline__ uint2 ll_peek(const uint2* p) {
 
 // residual_add whose projection results arrive as (value, sequence) pairs from every rank of a tensor-parallel group.
 // All pairs of a thread are requested before the first is examined; only those that have not arrived yet are polled.
-__device__ __forceinline__ void residual_add_ll(float* y_s, const float* x, const uint2* acc, unsigned int seq, unsigned int* status, float post,
+__device__ __forceinline__ void residual_add_ll(float* y_s, const float* x, const uint2* acc, unsigned int seq, const MegaArgs& a, float post,
                                                 bool live, int n) {
     constexpr int kPer = 8;
     for (int i0 = threadIdx.x; i0 < n; i0 += kPer * kMegaThreads) {
@@ -345,7 +356,7 @@ __device__ __forceinline__ void residual_add_ll(float* y_s, const float* x, cons
         for (int k = 0; k < kPer; ++k) {
             const int i = i0 + k * kMegaThreads;
             if (i >= n) continue;
-            const int av = static_cast<int>(pr[k].y == seq ? pr[k].x : ll_load(acc + i, seq, status));
+            const int av = static_cast<int>(pr[k].y == seq ? pr[k].x : ll_load(acc + i, seq, a));
             y_s[i] = __fadd_rn(xv[k], live ? __fmul_rn(static_cast<float>(av), post) : 0.0f);
         }
     }
@@ -805,7 +816,7 @@ __device__ __noinline__ bool phase_norm(const MegaArgs& a, int l, int which, uns
             const float s_prev = v.scale[3];
             const float post = s_prev > 0.0f ? __fdiv_rn(v.layers[l - 1].ws[6], s_prev) : 0.0f;
             if (a.tp_world > 1)  // the down results of the previous layer, from every rank
-                residual_add_ll(v.y, a.xb, reinterpret_cast<const uint2*>(a.tp_box[a.tp_rank] + a.box_acc_down), seq_base + 4u * l, a.status, post,
+                residual_add_ll(v.y, a.xb, reinterpret_cast<const uint2*>(a.tp_box[a.tp_rank] + a.box_acc_down), seq_base + 4u * l, a, post,
                                 s_prev > 0.0f, H);
             else
                 residual_add(v.y, a.xb, a.acc_down, post, s_prev > 0.0f, H);
@@ -814,7 +825,7 @@ __device__ __noinline__ bool phase_norm(const MegaArgs& a, int l, int which, uns
         const float s_q = v.scale[1];
         const float post = s_q > 0.0f ? __fdiv_rn(ly.ws[3], s_q) : 0.0f;
         if (a.tp_world > 1)  // the o results of this layer, from every rank
-            residual_add_ll(v.y, a.xa, reinterpret_cast<const uint2*>(a.tp_box[a.tp_rank] + a.box_acc_o), seq_base + 4u * l + 2u, a.status, post,
+            residual_add_ll(v.y, a.xa, reinterpret_cast<const uint2*>(a.tp_box[a.tp_rank] + a.box_acc_o), seq_base + 4u * l + 2u, a, post,
                             s_q > 0.0f, H);
         else
             residual_add(v.y, a.xa, a.acc_o, post, s_q > 0.0f, H);
@@ -959,7 +970,7 @@ __device__ __noinline__ bool phase_combine(const MegaArgs& a, unsigned int seq, 
             for (int k = 0; k < 8; ++k) {
                 const int i = i0 + k * kMegaThreads;
                 if (i >= n_all) continue;
-                const float y = __uint_as_float(pr[k].y == seq ? pr[k].x : ll_load(all + i, seq, a.status));
+                const float y = __uint_as_float(pr[k].y == seq ? pr[k].x : ll_load(all + i, seq, a));
                 v.y[i] = y;
                 amax = fmaxf(amax, fabsf(y));
             }
@@ -1023,7 +1034,7 @@ __device__ __noinline__ bool phase_head(const MegaArgs& a, unsigned int seq_base
         const float s_prev = v.scale[3];
         const float post = s_prev > 0.0f ? __fdiv_rn(v.layers[a.n_layers - 1].ws[6], s_prev) : 0.0f;
         if (a.tp_world > 1)  // the last layer's down results, from every rank
-            residual_add_ll(y_s, a.xb, reinterpret_cast<const uint2*>(a.tp_box[a.tp_rank] + a.box_acc_down), seq_base + 4u * a.n_layers, a.status, post,
+            residual_add_ll(y_s, a.xb, reinterpret_cast<const uint2*>(a.tp_box[a.tp_rank] + a.box_acc_down), seq_base + 4u * a.n_layers, a, post,
                             s_prev > 0.0f, H);
         else
             residual_add(y_s, a.xb, a.acc_down, post, s_prev > 0.0f, H);
@@ -1131,8 +1142,8 @@ __device__ __noinline__ void phase_finish(const MegaArgs& a, unsigned int seq_ba
             float bv = -INFINITY;
             unsigned int bi = 0xFFFFFFFFu;
             for (int r = 0; r < a.tp_world; ++r) {
-                const float rv = __uint_as_float(ll_load(all + 2 * r, seq, a.status));
-                argmax_merge(bv, bi, rv, ll_load(all + 2 * r + 1, seq, a.status));
+                const float rv = __uint_as_float(ll_load(all + 2 * r, seq, a));
+                argmax_merge(bv, bi, rv, ll_load(all + 2 * r + 1, seq, a));
             }
             s_best_v = bv;
             s_best_i = bi;
@@ -1228,7 +1239,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const __g
                 if (cta < a.tp_world && tid == 0) ll_store(reinterpret_cast<uint2*>(a.tp_box[cta] + a.box_amax) + a.tp_rank, __float_as_uint(vmax), seq);
                 const uint2* all = reinterpret_cast<const uint2*>(a.tp_box[a.tp_rank] + a.box_amax);
                 vmax = 0.0f;
-                for (int r = 0; r < a.tp_world; ++r) vmax = fmaxf(vmax, __uint_as_float(ll_load(all + r, seq, a.status)));
+                for (int r = 0; r < a.tp_world; ++r) vmax = fmaxf(vmax, __uint_as_float(ll_load(all + r, seq, a)));
             }
             const float s_down = vmax > 0.0f ? __fdiv_rn(127.0f, vmax) : 0.0f;
             if (tid == 0) mega_smem_views(smem, a).scale[3] = s_down;
