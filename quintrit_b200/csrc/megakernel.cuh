@@ -218,6 +218,15 @@ __device__ __noinline__ void mega_gemv(const GemvItem* __restrict__ items, int f
     make_column_words(creg, lane);
     for (int k = blockIdx.x; k < count; k += gridDim.x) {
         const GemvItem it = items[first + k];
+        // the first three row tiles of this warp do not depend on the table: they are requested before it is built
+        const uint4* wa = it.wa + lane;
+        const uint4* wb = it.wb + lane;
+        TileRegs ra, rb, rc;
+        const int n = it.ntiles, W = kMegaWarps;
+        int t = warp;
+        if (t < n) load_tile(ra, wa, wb, it.nblk, t, 0);
+        if (t + W < n) load_tile(rb, wa, wb, it.nblk, t + W, 0);
+        if (t + 2 * W < n) load_tile(rc, wa, wb, it.nblk, t + 2 * W, 0);
         {
             const int col = tid & 63, gb = col >> 5, j = col & 31;
             int a[5];
@@ -231,18 +240,9 @@ __device__ __noinline__ void mega_gemv(const GemvItem* __restrict__ items, int f
             fill_table_n<kMegaThreads>(tab, a, tid);
         }
         __syncthreads();
-        const uint4* wa = it.wa + lane;
-        const uint4* wb = it.wb + lane;
         int32_t* out = out_base + it.out_off + it.tile0 * kTileRows + lane;
         const int rows_left = it.rows - it.tile0 * kTileRows - lane;
-        // three row tiles in flight per warp
-        TileRegs ra, rb, rc;
-        const int n = it.ntiles, W = kMegaWarps;
-        int t = warp;
-        if (t < n) load_tile(ra, wa, wb, it.nblk, t, 0);
-        if (t + W < n) load_tile(rb, wa, wb, it.nblk, t + W, 0);
-        if (t + 2 * W < n) load_tile(rc, wa, wb, it.nblk, t + 2 * W, 0);
-        while (t < n) {
+        while (t < n) {  // three row tiles in flight per warp
             {
                 const int acc = tile_sum<BASE>(ra, it.nblk, creg);
                 if (t * kTileRows < rows_left) atomicAdd(out + t * kTileRows, acc);
