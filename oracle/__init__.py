@@ -302,6 +302,7 @@ def _declare_model(l: C.CDLL) -> None:
     l.qto_model_free.argtypes = [C.c_void_p]
     l.qto_model_forward.argtypes = [C.c_void_p, C.c_uint32, _sz, _f32p]
     l.qto_model_set_bf16_tables.argtypes = [C.c_void_p, C.c_int]
+    l.qto_model_set_block_scales.argtypes = [C.c_void_p, C.POINTER(_f32p)]
     l.qto_vec_dot_bf16.restype = C.c_float
     l.qto_vec_dot_bf16.argtypes = [_u16p, _u16p, _sz]
     l.qto_f32_to_bf16.restype = C.c_uint16
@@ -429,6 +430,14 @@ class Model:
                                      _p(embed, _u16p), None if head is None else _p(head, _u16p), _p(out_norm, _f32p), w, _p(scales, _f32p), norms)
         if spec.get("bf16_tables"):
             l.qto_model_set_bf16_tables(self._h, 1)
+        if spec.get("block_scales") is not None:  # Q2_0 model: layers * 7 arrays of per-64-weight scales
+            bsc = (_f32p * (L * 7))()
+            for i, a in enumerate(spec["block_scales"]):
+                a = _c(a, np.float32)
+                self._keep.append(a)
+                bsc[i] = _p(a, _f32p)
+            self._keep.append(bsc)
+            l.qto_model_set_block_scales(self._h, bsc)
 
     def forward(self, token: int, pos: int) -> np.ndarray:
         logits = np.zeros(self.spec["vocab"], np.float32)

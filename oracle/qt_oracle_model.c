@@ -422,6 +422,10 @@ uint32_t qto_argmax(const float* logits, size_t n) {
 
 /* ---- whole-token forward: model.rs:64-203, 282-377; attention.rs:115-260 ------------------------------------------ */
 
+void qto_quantize_q8_0(const float* x, size_t n, int8_t* qs, float* d);
+void qto_gemv_block_scaled(const uint8_t* planar, const float* w_scales, const int8_t* acts, const float* a_scales, size_t rows, size_t cols,
+                           float* out);
+
 typedef struct qto_model {
     int arch;     /* 0 = llama / falcon3 (interleaved RoPE, SwiGLU), 1 = bitnet (NEOX RoPE, relu^2, sub-norms) */
     int f32_values; /* attention accumulators: 0 = F16 (I2_S files), 1 = F32 (TQ1_0 / TQ2_0 files) */
@@ -436,6 +440,7 @@ typedef struct qto_model {
     uint16_t *kc, *vc;       /* [layer][pos][kv_head][head_dim] */
     uint8_t** w64;           /* 64-row tiled copies for the AVX-512 GEMV (same integers, only faster), or NULL */
     int bf16_tables;         /* embedding and output head are BF16 instead of F16 (qto_model_set_bf16_tables) */
+    const float** block_scales; /* layers * 7 arrays of rows * cols / 64 weight scales: Q2_0 projections (qto_model_set_block_scales) */
 } qto_model_t;
 
 qto_model_t* qto_model_create(int arch, int f32_values, int hidden, int inter, int layers, int q_heads, int kv_heads, int head_dim,
@@ -460,6 +465,8 @@ qto_model_t* qto_model_create(int arch, int f32_values, int hidden, int inter, i
     return m;
 }
 void qto_model_set_bf16_tables(qto_model_t* m, int on) { m->bf16_tables = on != 0; }
+/* Q2_0 models: every projection is block-scaled (attention.rs:262-344, model.rs:209-229); the tensor scales are unused */
+void qto_model_set_block_scales(qto_model_t* m, const float** scales) { m->block_scales = scales; }
 
 void qto_model_free(qto_model_t* m) {
     if (!m) return;
@@ -487,6 +494,11 @@ static void project(const qto_model_t* m, int layer, int which, size_t rows, siz
     free(acc);
 }
 
+/* attention.rs:276-280, 342-343; model.rs:211-228: the input quantised to Q8_0 blocks, then the Q2_0 x Q8_0 dot of every row */
+static void project_q8(const qto_model_t* m, int layer, int which, size_t rows, size_t cols, const int8_t* qs, const float* d, float* out) {
+    qto_gemv_block_scaled(m->w[layer * 7 + which], m->block_scales[layer * 7 + which], qs, d, rows, cols, out);
+}
+
 void qto_model_forward(qto_model_t* m, uint32_t token, size_t pos, float* logits) {
     const size_t H = (size_t)m->hidden, I = (size_t)m->inter, hd = (size_t)m->head_dim;
     const size_t qd = (size_t)m->q_heads * hd, kvd = (size_t)m->kv_heads * hd;
@@ -502,6 +514,8 @@ void qto_model_forward(qto_model_t* m, uint32_t token, size_t pos, float* logits
     float* inter = (float*)malloc(I * 4);
     float* delta = (float*)malloc(H * 4);
     int8_t* a8 = (int8_t*)malloc(big > H ? big : H);
+    float* d8 = (float*)malloc(((big > H ? big : H) / 32 + 1) * 4); /* Q8_0 block scales */
+    const int bs = m->block_scales != NULL;
     float* cache = (float*)malloc((size_t)m->rope_dims * 4);
     const float scale = 1.0f / sqrtf((float)m->head_dim); /* attention.rs:46 */
 
@@ -510,10 +524,18 @@ void qto_model_forward(qto_model_t* m, uint32_t token, size_t pos, float* logits
     for (int l = 0; l < m->layers; ++l) {
         const float** nw = m->norms + l * 4;
         qto_rms_norm(x, nw[0], H, m->eps, xn);
-        float s = qto_quantize_int8(xn, H, a8);
-        project(m, l, 0, qd, H, a8, s, q);
-        project(m, l, 1, kvd, H, a8, s, k);
-        project(m, l, 2, kvd, H, a8, s, v);
+        float s = 0.0f;
+        if (bs) {
+            qto_quantize_q8_0(xn, H, a8, d8);
+            project_q8(m, l, 0, qd, H, a8, d8, q);
+            project_q8(m, l, 1, kvd, H, a8, d8, k);
+            project_q8(m, l, 2, kvd, H, a8, d8, v);
+        } else {
+            s = qto_quantize_int8(xn, H, a8);
+            project(m, l, 0, qd, H, a8, s, q);
+            project(m, l, 1, kvd, H, a8, s, k);
+            project(m, l, 2, kvd, H, a8, s, v);
+        }
         qto_rope_cache(pos, (size_t)m->rope_dims, m->rope_theta, cache);
         qto_rope_apply(q, (size_t)m->q_heads, hd, m->arch == 1, cache, (size_t)m->rope_dims);
         qto_rope_apply(k, (size_t)m->kv_heads, hd, m->arch == 1, cache, (size_t)m->rope_dims);
@@ -528,29 +550,45 @@ void qto_model_forward(qto_model_t* m, uint32_t token, size_t pos, float* logits
             const size_t kvh = h / gqa;
             qto_attend_head(q + h * hd, kc + kvh * hd, vc + kvh * hd, kvd, pos + 1, (size_t)m->ctx, hd, scale, m->f32_values, att + h * hd);
         }
+        const float* o_in = att;
         if (nw[2]) { /* attention.rs:234-246 sub-norm (BitNet) */
             qto_rms_norm(att, nw[2], qd, m->eps, xn);
-            s = qto_quantize_int8(xn, qd, a8);
-        } else {
-            s = qto_quantize_int8(att, qd, a8);
+            o_in = xn;
         }
-        project(m, l, 3, H, qd, a8, s, delta);
+        if (bs) {
+            qto_quantize_q8_0(o_in, qd, a8, d8);
+            project_q8(m, l, 3, H, qd, a8, d8, delta);
+        } else {
+            s = qto_quantize_int8(o_in, qd, a8);
+            project(m, l, 3, H, qd, a8, s, delta);
+        }
         for (size_t i = 0; i < H; ++i) x[i] += delta[i]; /* model.rs:85 */
         qto_rms_norm(x, nw[1], H, m->eps, xn);
-        s = qto_quantize_int8(xn, H, a8);
-        project(m, l, 4, I, H, a8, s, gate);
-        project(m, l, 5, I, H, a8, s, up);
+        if (bs) {
+            qto_quantize_q8_0(xn, H, a8, d8);
+            project_q8(m, l, 4, I, H, a8, d8, gate);
+            project_q8(m, l, 5, I, H, a8, d8, up);
+        } else {
+            s = qto_quantize_int8(xn, H, a8);
+            project(m, l, 4, I, H, a8, s, gate);
+            project(m, l, 5, I, H, a8, s, up);
+        }
         if (m->arch == 1)
             qto_relu2_mul(gate, up, I, inter);
         else
             qto_swiglu(gate, up, I, inter);
+        const float* down_in = inter;
         if (nw[3]) {
             qto_rms_norm(inter, nw[3], I, m->eps, xn);
-            s = qto_quantize_int8(xn, I, a8);
-        } else {
-            s = qto_quantize_int8(inter, I, a8);
+            down_in = xn;
         }
-        project(m, l, 6, H, I, a8, s, delta);
+        if (bs) {
+            qto_quantize_q8_0(down_in, I, a8, d8);
+            project_q8(m, l, 6, H, I, a8, d8, delta);
+        } else {
+            s = qto_quantize_int8(down_in, I, a8);
+            project(m, l, 6, H, I, a8, s, delta);
+        }
         for (size_t i = 0; i < H; ++i) x[i] += delta[i];
     }
     qto_rms_norm(x, m->out_norm, H, m->eps, xn); /* model.rs:326-331 */
@@ -560,5 +598,5 @@ void qto_model_forward(qto_model_t* m, uint32_t token, size_t pos, float* logits
 #pragma omp parallel for schedule(static)
     for (long t = 0; t < (long)m->vocab; ++t) /* model.rs:346-375 */
         logits[t] = m->bf16_tables ? qto_vec_dot_bf16(x16, head + (size_t)t * H, H) : qto_vec_dot_f16(x16, head + (size_t)t * H, H);
-    free(x16), free(x), free(xn), free(q), free(k), free(v), free(att), free(gate), free(up), free(inter), free(delta), free(a8), free(cache);
+    free(x16), free(x), free(xn), free(q), free(k), free(v), free(att), free(gate), free(up), free(inter), free(delta), free(a8), free(d8), free(cache);
 }

@@ -824,10 +824,15 @@ int decoder_create_impl(const quintrit_b200_decoder_desc_t* desc, quintrit_b200_
     int rc = require_b200(static_cast<int>(desc->device_index), &prop);
     if (rc != QUINTRIT_OK) return rc;
     const size_t shapes[7][2] = {{qd, H}, {kvd, H}, {kvd, H}, {H / tp_world, qd_full}, {I, H}, {I, H}, {H / tp_world, I_full}};
+    // A model of Q2_0 projections: every matrix is block-scaled (attention.rs:262-344, model.rs:209-229); mixtures are refused.
+    bool block_scaled = false;
+    if (desc->matrices[0] != nullptr && check_matrix(desc->matrices[0], true) == QUINTRIT_OK) block_scaled = desc->matrices[0]->block_scaled;
+    if (block_scaled && tp_world > 1) return fail(QUINTRIT_ERR_UNSUPPORTED, "tensor parallelism is not available for block-scaled (Q2_0) models");
     for (size_t i = 0; i < size_t(L) * 7; ++i) {
         const quintrit_b200_matrix* m = desc->matrices[i];
-        rc = check_matrix(m);
+        rc = check_matrix(m, true);
         if (rc != QUINTRIT_OK) return rc;
+        if (m->block_scaled != block_scaled) return fail(QUINTRIT_ERR_UNSUPPORTED, "matrix %zu: block-scaled (Q2_0) and per-tensor projections cannot be mixed in one model", i);
         if (m->device != static_cast<int>(desc->device_index)) return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "matrix %zu lives on another device", i);
         if (m->rows != shapes[i % 7][0] || m->cols != shapes[i % 7][1])
             return fail(QUINTRIT_ERR_MODEL, "matrix %zu is %zu x %zu, the model needs %zu x %zu", i, m->rows, m->cols, shapes[i % 7][0], shapes[i % 7][1]);
@@ -842,6 +847,8 @@ int decoder_create_impl(const quintrit_b200_decoder_desc_t* desc, quintrit_b200_
     d->hidden = H, d->inter = I, d->layers = L, d->q_heads = desc->num_heads / tp_world, d->kv_heads = desc->num_kv_heads / tp_world, d->head_dim = hd;
     d->tp_rank = static_cast<int>(tp_rank), d->tp_world = static_cast<int>(tp_world);
     d->bf16_tables = table_dtype == 1;
+    d->block_scaled = block_scaled;
+    d->mats.assign(desc->matrices, desc->matrices + size_t(L) * 7);
     d->q_dim_full = static_cast<int>(qd_full), d->inter_full = static_cast<int>(I_full), d->vocab_full = static_cast<int>(desc->vocab_size);
     d->vocab = vocab_local, d->ctx = ctx, d->rope_dims = desc->rope_dims, d->q_dim = static_cast<int>(qd), d->kv_dim = static_cast<int>(kvd);
     d->eps = desc->rms_norm_eps, d->rope_theta = desc->rope_theta;
@@ -903,6 +910,18 @@ int decoder_create_impl(const quintrit_b200_decoder_desc_t* desc, quintrit_b200_
         (rc = dev_alloc(d, &d->d_history, ctx + 1)) != QUINTRIT_OK || (rc = dev_alloc(d, &d->d_counters, 4)) != QUINTRIT_OK)
         return rc;
 
+    if ((rc = dev_alloc(d, &d->q8_d, std::max<size_t>({H, I, qd}) / 32 + 1)) != QUINTRIT_OK) return rc;
+    if (block_scaled) {  // no work items: the block-scaled projections are plain launches; one kernel per step
+        QTB_CUDA(cudaFuncSetAttribute(gemv_block_scaled_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(block_scaled_smem_bytes(131072))));
+        const int big_bs = static_cast<int>(std::max<size_t>({H, I, qd}) * sizeof(float));
+        QTB_CUDA(cudaFuncSetAttribute(norm_quant_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, big_bs));
+        QTB_CUDA(cudaFuncSetAttribute(attn_finish_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, big_bs));
+        QTB_CUDA(cudaFuncSetAttribute(act_quant_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, big_bs));
+        QTB_CUDA(cudaFuncSetAttribute(lm_head_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, big_bs));
+        d->use_mega = false;
+        QTB_CUDA(cudaDeviceSynchronize());
+        return QUINTRIT_OK;
+    }
     // work items of the four GEMV launches of every layer
     std::vector<GemvItem> items;
     const size_t slots = size_t(d->sm_count) * kCtasPerSm;
@@ -1183,13 +1202,17 @@ int projection(const GgufFile& g, const std::string& name, uint64_t rows, uint64
                float* scale) {
     const GgufTensor* t = g.tensor(name);
     if (t == nullptr) return fail(QUINTRIT_ERR_MODEL, "Missing %s", name.c_str());
-    if (t->type != kGgmlI2S && t->type != kGgmlTq1 && t->type != kGgmlTq2)
-        return fail(QUINTRIT_ERR_UNSUPPORTED, "%s has GGML type %u; the GPU decoder needs I2_S, TQ1_0 or TQ2_0 projections", name.c_str(), t->type);
+    if (t->type != kGgmlI2S && t->type != kGgmlTq1 && t->type != kGgmlTq2 && t->type != kGgmlQ2)
+        return fail(QUINTRIT_ERR_UNSUPPORTED, "%s has GGML type %u; the GPU decoder needs I2_S, TQ1_0, TQ2_0 or Q2_0 projections", name.c_str(), t->type);
     if (t->shape.size() != 2 || t->shape[0] != cols || t->shape[1] != rows)
         return fail(QUINTRIT_ERR_MODEL, "%s does not have the shape %llu x %llu", name.c_str(), static_cast<unsigned long long>(rows), static_cast<unsigned long long>(cols));
     *data = g.data(*t, len);
     if (*data == nullptr) return fail(QUINTRIT_ERR_FORMAT, "the payload of %s does not lie inside the file", name.c_str());
     *source = static_cast<int32_t>(t->type);
+    if (t->type == kGgmlQ2) {  // one scale per 64 weights inside the payload: no tensor scale
+        *scale = 1.0f;
+        return QUINTRIT_OK;
+    }
     if (t->type == kGgmlI2S) {
         if (!g.trailing_scale(*t, scale)) return fail(QUINTRIT_ERR_FORMAT, "the scale of %s does not lie inside the file", name.c_str());
         return QUINTRIT_OK;
@@ -1223,7 +1246,7 @@ int open_gguf_impl(const char* path, const quintrit_gpu_options_t* options, quin
     GgufModelShape m;
     int rc = read_shape(g, &m);
     if (rc != QUINTRIT_OK) return rc;
-    if (m.has_q2) return fail(QUINTRIT_ERR_UNSUPPORTED, "block-scaled (Q2_0) models are not supported by the GPU decoder yet (the projection alone is: quintrit_b200_gemv_block_scaled)");
+
     // context: the model's maximum, at most 4096 by default (quintrit.h:502-507), rounded down to a multiple of 256
     uint64_t ctx = std::min<uint64_t>(m.ctx_train, want_ctx != 0 ? want_ctx : 4096);
     ctx = std::min<uint64_t>(ctx, 8192) / 256 * 256;

@@ -111,6 +111,42 @@ __device__ __forceinline__ float dot_lane_reduce_bf16(float v) {
     return v;  // lane 0
 }
 
+// ---- quantisation of a vector held in shared memory, for the projection that follows -------------------------------------
+// q8_d == nullptr: per-tensor absmax int8 (ops.rs:241-267), scale to scale_out[0]. Otherwise Q8_0 blocks for a block-scaled
+// (Q2_0) projection (ops.rs:898-910): one warp per block of 32 values, d = f16(amax / 127) to q8_d[block], codes rounded to
+// nearest even. `amax` is the thread's partial maximum of |y| (used by the per-tensor form only). n is a multiple of 32 in
+// the block form. All threads of the block must call it.
+__device__ __forceinline__ void quantize_vector(const float* y_s, int n, float amax, int8_t* q_out, float* scale_out, float* q8_d, float* sh_f) {
+    const int tid = threadIdx.x, nthreads = blockDim.x;
+    if (q8_d != nullptr) {
+        const int lane = tid & 31, warp = tid >> 5, nwarps = nthreads >> 5;
+        for (int b = warp; b < n / 32; b += nwarps) {
+            const float v = y_s[b * 32 + lane];
+            float m = fabsf(v);
+            if (m != m) m = 0.0f;  // f32::max ignores a NaN
+            for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+            if (lane == 0) q8_d[b] = __half2float(__float2half_rn(__fdiv_rn(m, 127.0f)));
+            const float id = m != 0.0f ? __fdiv_rn(127.0f, m) : 0.0f;
+            const float r = rintf(__fmul_rn(v, id));
+            int q = 0;
+            if (r == r) q = static_cast<int>(fminf(fmaxf(r, -128.0f), 127.0f));
+            q_out[b * 32 + lane] = static_cast<int8_t>(q);
+        }
+        return;
+    }
+    amax = block_max_f32(amax, sh_f);
+    const float s = amax > 0.0f ? __fdiv_rn(127.0f, amax) : 0.0f;
+    for (int i = tid; i < n; i += nthreads) {
+        float q = 0.0f;
+        if (amax > 0.0f) {
+            q = roundf(__fmul_rn(y_s[i], s));
+            q = q != q ? 0.0f : fminf(fmaxf(q, -128.0f), 127.0f);
+        }
+        q_out[i] = static_cast<int8_t>(q);
+    }
+    if (tid == 0) scale_out[0] = s;
+}
+
 // ---- embedding row: model.rs:308-317 ---------------------------------------------------------------------------------
 __global__ void embed_kernel(const __half* __restrict__ table, const uint32_t* __restrict__ token, int hidden, float* __restrict__ x, bool bf16) {
     const size_t base = static_cast<size_t>(token[0]) * hidden;
@@ -134,6 +170,10 @@ struct NormQuantArgs {
     int zero_a_n;
     int32_t* zero_b;
     int zero_b_n;
+    // block-scaled (Q2_0) models: acc_prev holds the previous projection's F32 results, added as they are (model.rs:85,
+    // attention.rs:343), and the codes are Q8_0 blocks with their scales in q8_d
+    int block_scaled;
+    float* q8_d;
 };
 
 // x += acc * (ws / s)  (model.rs:85, 202 after layer.rs:143-147), y = rms_norm(x) (ops.rs:62-96), codes = quantise(y)
@@ -147,7 +187,7 @@ __global__ void __launch_bounds__(kRowThreads) norm_quant_kernel(NormQuantArgs a
     for (int i = tid; i < a.zero_b_n; i += kRowThreads) a.zero_b[i] = 0;
     float post = 0.0f;
     bool has_prev = a.acc_prev != nullptr;
-    if (has_prev) {
+    if (has_prev && !a.block_scaled) {
         const float s = a.scale_prev[0];
         post = s > 0.0f ? __fdiv_rn(a.ws_prev, s) : 0.0f;
         if (!(s > 0.0f)) has_prev = false;  // layer.rs:148-150: a zero activation scale gives a zero projection
@@ -156,7 +196,8 @@ __global__ void __launch_bounds__(kRowThreads) norm_quant_kernel(NormQuantArgs a
     for (int i = tid; i < a.n; i += kRowThreads) {
         float v = a.x[i];
         if (a.acc_prev != nullptr) {
-            const float d = has_prev ? __fmul_rn(static_cast<float>(a.acc_prev[i]), post) : 0.0f;
+            const float d = a.block_scaled ? reinterpret_cast<const float*>(a.acc_prev)[i]
+                                           : (has_prev ? __fmul_rn(static_cast<float>(a.acc_prev[i]), post) : 0.0f);
             v = __fadd_rn(v, d);
             a.x[i] = v;
         }
@@ -176,17 +217,8 @@ __global__ void __launch_bounds__(kRowThreads) norm_quant_kernel(NormQuantArgs a
         for (int i = tid; i < a.n; i += kRowThreads) a.y16_out[i] = a.y16_bf16 ? __ushort_as_half(float_to_bf16_bits(y_s[i])) : __float2half_rn(y_s[i]);
         return;
     }
-    amax = block_max_f32(amax, sh_f);
-    const float s = amax > 0.0f ? __fdiv_rn(127.0f, amax) : 0.0f;
-    for (int i = tid; i < a.n; i += kRowThreads) {
-        float q = 0.0f;
-        if (amax > 0.0f) {
-            q = roundf(__fmul_rn(y_s[i], s));
-            q = q != q ? 0.0f : fminf(fmaxf(q, -128.0f), 127.0f);
-        }
-        a.q_out[i] = static_cast<int8_t>(q);
-    }
-    if (tid == 0) a.scale_out[0] = s;
+    __syncthreads();
+    quantize_vector(y_s, a.n, amax, a.q_out, a.scale_out, a.block_scaled ? a.q8_d : nullptr, sh_f);
 }
 
 // ---- q/k/v finish: post-scale, RoPE, KV append (attention.rs:171-203, ops.rs:160-221) --------------------------------
@@ -200,10 +232,11 @@ struct RopeKvArgs {
     float* q_out;             // rotated query, F32 (q_dim)
     __half* k_cache;          // [ctx][kv_dim] of this layer
     __half* v_cache;
+    int block_scaled;         // acc holds the F32 results of block-scaled projections: used as they are
 };
 
 __global__ void rope_kv_kernel(RopeKvArgs a) {
-    const float s = a.act_scale[0];
+    const float s = a.block_scaled ? 1.0f : a.act_scale[0];
     const bool live = s > 0.0f;
     const float pq = live ? __fdiv_rn(a.ws_q, s) : 0.0f, pk = live ? __fdiv_rn(a.ws_k, s) : 0.0f, pv = live ? __fdiv_rn(a.ws_v, s) : 0.0f;
     const uint32_t pos = a.pos[0];
@@ -213,7 +246,8 @@ __global__ void rope_kv_kernel(RopeKvArgs a) {
     for (int t = blockIdx.x * blockDim.x + threadIdx.x; t < total_pairs + a.kv_dim; t += gridDim.x * blockDim.x) {
         if (t >= total_pairs) {  // a value element: scale and append
             const int i = t - total_pairs;
-            const float v = live ? __fmul_rn(static_cast<float>(a.acc[a.q_dim + a.kv_dim + i]), pv) : 0.0f;
+            const float v = a.block_scaled ? reinterpret_cast<const float*>(a.acc)[a.q_dim + a.kv_dim + i]
+                                           : (live ? __fmul_rn(static_cast<float>(a.acc[a.q_dim + a.kv_dim + i]), pv) : 0.0f);
             a.v_cache[static_cast<size_t>(pos) * a.kv_dim + i] = __float2half_rn(v);
             continue;
         }
@@ -240,8 +274,8 @@ __global__ void rope_kv_kernel(RopeKvArgs a) {
             rot = p < half_pairs;
         }
         const float post = is_q ? pq : pk;
-        float x0 = live ? __fmul_rn(static_cast<float>(a.acc[base + i0]), post) : 0.0f;
-        float x1 = live ? __fmul_rn(static_cast<float>(a.acc[base + i1]), post) : 0.0f;
+        float x0 = a.block_scaled ? reinterpret_cast<const float*>(a.acc)[base + i0] : (live ? __fmul_rn(static_cast<float>(a.acc[base + i0]), post) : 0.0f);
+        float x1 = a.block_scaled ? reinterpret_cast<const float*>(a.acc)[base + i1] : (live ? __fmul_rn(static_cast<float>(a.acc[base + i1]), post) : 0.0f);
         if (rot) {
             const int ci = a.neox ? p : p;
             const float c = cs[2 * ci], sn = cs[2 * ci + 1];
@@ -416,6 +450,7 @@ struct AttnFinishArgs {
     float* scale_out;
     int32_t* zero_a;          // result buffer of the o projection
     int zero_a_n;
+    float* q8_d;              // block-scaled models: Q8_0 block scales of q_out (else nullptr: per-tensor int8)
 };
 
 __global__ void __launch_bounds__(kRowThreads) attn_finish_kernel(AttnFinishArgs a) {
@@ -464,17 +499,8 @@ __global__ void __launch_bounds__(kRowThreads) attn_finish_kernel(AttnFinishArgs
     }
     float amax = 0.0f;
     for (int i = tid; i < n; i += kRowThreads) amax = fmaxf(amax, fabsf(y_s[i]));
-    amax = block_max_f32(amax, sh_f);
-    const float s = amax > 0.0f ? __fdiv_rn(127.0f, amax) : 0.0f;
-    for (int i = tid; i < n; i += kRowThreads) {
-        float q = 0.0f;
-        if (amax > 0.0f) {
-            q = roundf(__fmul_rn(y_s[i], s));
-            q = q != q ? 0.0f : fminf(fmaxf(q, -128.0f), 127.0f);
-        }
-        a.q_out[i] = static_cast<int8_t>(q);
-    }
-    if (tid == 0) a.scale_out[0] = s;
+    __syncthreads();
+    quantize_vector(y_s, n, amax, a.q_out, a.scale_out, a.q8_d, sh_f);
 }
 
 // ---- gate / up finish: post-scale, SwiGLU or relu^2 * up, optional sub-norm, quantise for the down projection ---------
@@ -491,6 +517,8 @@ struct ActQuantArgs {
     float* scale_out;
     int32_t* zero_a;          // result buffer of the down projection
     int zero_a_n;
+    int block_scaled;         // acc_gate / acc_up hold F32 results of block-scaled projections; codes are Q8_0 blocks
+    float* q8_d;
 };
 
 __global__ void __launch_bounds__(kRowThreads) act_quant_kernel(ActQuantArgs a) {
@@ -499,12 +527,12 @@ __global__ void __launch_bounds__(kRowThreads) act_quant_kernel(ActQuantArgs a) 
     extern __shared__ float y_s[];  // n floats
     const int tid = threadIdx.x;
     for (int i = tid; i < a.zero_a_n; i += kRowThreads) a.zero_a[i] = 0;
-    const float s_in = a.act_scale[0];
+    const float s_in = a.block_scaled ? 1.0f : a.act_scale[0];
     const bool live = s_in > 0.0f;
     const float pg = live ? __fdiv_rn(a.ws_gate, s_in) : 0.0f, pu = live ? __fdiv_rn(a.ws_up, s_in) : 0.0f;
     for (int i = tid; i < a.n; i += kRowThreads) {
-        const float g = live ? __fmul_rn(static_cast<float>(a.acc_gate[i]), pg) : 0.0f;
-        const float u = live ? __fmul_rn(static_cast<float>(a.acc_up[i]), pu) : 0.0f;
+        const float g = a.block_scaled ? reinterpret_cast<const float*>(a.acc_gate)[i] : (live ? __fmul_rn(static_cast<float>(a.acc_gate[i]), pg) : 0.0f);
+        const float u = a.block_scaled ? reinterpret_cast<const float*>(a.acc_up)[i] : (live ? __fmul_rn(static_cast<float>(a.acc_up[i]), pu) : 0.0f);
         float v;
         if (a.relu2) {
             const float p = g > 0.0f ? g : 0.0f;
@@ -525,17 +553,8 @@ __global__ void __launch_bounds__(kRowThreads) act_quant_kernel(ActQuantArgs a) 
     }
     float amax = 0.0f;
     for (int i = tid; i < a.n; i += kRowThreads) amax = fmaxf(amax, fabsf(y_s[i]));
-    amax = block_max_f32(amax, sh_f);
-    const float s = amax > 0.0f ? __fdiv_rn(127.0f, amax) : 0.0f;
-    for (int i = tid; i < a.n; i += kRowThreads) {
-        float q = 0.0f;
-        if (amax > 0.0f) {
-            q = roundf(__fmul_rn(y_s[i], s));
-            q = q != q ? 0.0f : fminf(fmaxf(q, -128.0f), 127.0f);
-        }
-        a.q_out[i] = static_cast<int8_t>(q);
-    }
-    if (tid == 0) a.scale_out[0] = s;
+    __syncthreads();
+    quantize_vector(y_s, a.n, amax, a.q_out, a.scale_out, a.block_scaled ? a.q8_d : nullptr, sh_f);
 }
 
 // ---- output head: one warp per vocabulary row, ggml_vec_dot_f16 order (model.rs:346-375, ops.rs:970-1014) --------------

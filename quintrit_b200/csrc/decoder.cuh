@@ -46,6 +46,9 @@ struct quintrit_b200_decoder {
     bool graph_ready;
     uint32_t host_pos;                         // tokens in the KV cache
     // tensor parallelism: this rank's share of a model split over tp_world GPUs (1 = none)
+    bool block_scaled = false;                 // every projection is a block-scaled (Q2_0) matrix: Q8_0 activations, F32 results
+    std::vector<const quintrit_b200_matrix*> mats;  // the projections (layers * 7), for the block-scaled launches
+    float* q8_d = nullptr;                     // Q8_0 block scales of the current projection input
     bool bf16_tables = false;                  // embedding and output head hold BF16 instead of F16 bit patterns
     int tp_rank = 0, tp_world = 1;
     int q_dim_full = 0, inter_full = 0, vocab_full = 0;
@@ -105,6 +108,17 @@ inline int decoder_gemv(quintrit_b200_decoder* d, int layer, int which, const in
     return launch_gemv(d->d_items + d->item_first[k], d->item_count[k], act, out, d->d_counters, d->sm_count, d->stream);
 }
 
+// Block-scaled projection `which` (0..6) of a layer: out (F32) = W x for Q8_0 blocks (codes, d->q8_d).
+inline int decoder_gemv_bs(quintrit_b200_decoder* d, int layer, int which, const int8_t* codes, float* out) {
+    const quintrit_b200_matrix* m = d->mats[static_cast<size_t>(layer) * 7 + which];
+    const int grid = static_cast<int>(std::min<size_t>((m->rows + 31) / 32, static_cast<size_t>(d->sm_count) * 8));
+    gemv_block_scaled_kernel<<<grid, kBsThreads, block_scaled_smem_bytes(m->cols), d->stream>>>(m->d_planar, m->d_wscales, codes, d->q8_d, m->rows, m->cols, out);
+    ++g_launches;
+    const cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e, "block-scaled GEMV launch");
+    return QUINTRIT_OK;
+}
+
 #define QTB_LAUNCH_CHECK()                                   \
     do {                                                     \
         ++g_launches;                                        \
@@ -116,6 +130,7 @@ inline int decoder_gemv(quintrit_b200_decoder* d, int layer, int which, const in
 inline int enqueue_token(quintrit_b200_decoder* d, bool with_head) {
     cudaStream_t s = d->stream;
     const int H = d->hidden, I = d->inter, qd = d->q_dim, kvd = d->kv_dim;
+    const bool bs = d->block_scaled;  // Q2_0 model: the int32 result buffers hold F32 results, activations are Q8_0 blocks
     embed_kernel<<<(H + 255) / 256, 256, 0, s>>>(d->embed, d->d_token, H, d->x, d->bf16_tables);
     QTB_LAUNCH_CHECK();
     for (int l = 0; l < d->layers; ++l) {
@@ -133,11 +148,19 @@ inline int enqueue_token(quintrit_b200_decoder* d, bool with_head) {
         n1.q_out = d->a8_h;
         n1.scale_out = d->s_h;
         n1.zero_a = d->acc_qkv;
-        n1.zero_a_n = qd + 2 * kvd;
+        n1.zero_a_n = bs ? 0 : qd + 2 * kvd;
+        n1.block_scaled = bs, n1.q8_d = d->q8_d;
         norm_quant_kernel<<<1, kRowThreads, H * sizeof(float), s>>>(n1);
         QTB_LAUNCH_CHECK();
-        int rc = decoder_gemv(d, l, 0, d->a8_h, d->acc_qkv);
-        if (rc != QUINTRIT_OK) return rc;
+        int rc;
+        if (bs) {
+            float* f = reinterpret_cast<float*>(d->acc_qkv);
+            if ((rc = decoder_gemv_bs(d, l, 0, d->a8_h, f)) != QUINTRIT_OK || (rc = decoder_gemv_bs(d, l, 1, d->a8_h, f + qd)) != QUINTRIT_OK ||
+                (rc = decoder_gemv_bs(d, l, 2, d->a8_h, f + qd + kvd)) != QUINTRIT_OK)
+                return rc;
+        } else if ((rc = decoder_gemv(d, l, 0, d->a8_h, d->acc_qkv)) != QUINTRIT_OK) {
+            return rc;
+        }
         RopeKvArgs rk{};
         rk.acc = d->acc_qkv;
         rk.act_scale = d->s_h;
@@ -148,6 +171,7 @@ inline int enqueue_token(quintrit_b200_decoder* d, bool with_head) {
         rk.q_out = d->q;
         rk.k_cache = d->kc + static_cast<size_t>(l) * d->ctx * kvd;
         rk.v_cache = d->vc + static_cast<size_t>(l) * d->ctx * kvd;
+        rk.block_scaled = bs;
         rope_kv_kernel<<<((qd + kvd) / 2 + kvd + 255) / 256, 256, 0, s>>>(rk);
         QTB_LAUNCH_CHECK();
         AttnArgs at{};
@@ -171,10 +195,11 @@ inline int enqueue_token(quintrit_b200_decoder* d, bool with_head) {
         af.q_out = d->a8_q;
         af.scale_out = d->s_q;
         af.zero_a = d->acc_o;
-        af.zero_a_n = H;
+        af.zero_a_n = bs ? 0 : H;
+        af.q8_d = bs ? d->q8_d : nullptr;
         attn_finish_kernel<<<1, kRowThreads, qd * sizeof(float), s>>>(af);
         QTB_LAUNCH_CHECK();
-        rc = decoder_gemv(d, l, 1, d->a8_q, d->acc_o);
+        rc = bs ? decoder_gemv_bs(d, l, 3, d->a8_q, reinterpret_cast<float*>(d->acc_o)) : decoder_gemv(d, l, 1, d->a8_q, d->acc_o);
         if (rc != QUINTRIT_OK) return rc;
         NormQuantArgs n2{};
         n2.x = d->x;
@@ -187,11 +212,16 @@ inline int enqueue_token(quintrit_b200_decoder* d, bool with_head) {
         n2.q_out = d->a8_h;
         n2.scale_out = d->s_h;
         n2.zero_a = d->acc_gu;
-        n2.zero_a_n = 2 * I;
+        n2.zero_a_n = bs ? 0 : 2 * I;
+        n2.block_scaled = bs, n2.q8_d = d->q8_d;
         norm_quant_kernel<<<1, kRowThreads, H * sizeof(float), s>>>(n2);
         QTB_LAUNCH_CHECK();
-        rc = decoder_gemv(d, l, 2, d->a8_h, d->acc_gu);
-        if (rc != QUINTRIT_OK) return rc;
+        if (bs) {
+            float* f = reinterpret_cast<float*>(d->acc_gu);
+            if ((rc = decoder_gemv_bs(d, l, 4, d->a8_h, f)) != QUINTRIT_OK || (rc = decoder_gemv_bs(d, l, 5, d->a8_h, f + I)) != QUINTRIT_OK) return rc;
+        } else if ((rc = decoder_gemv(d, l, 2, d->a8_h, d->acc_gu)) != QUINTRIT_OK) {
+            return rc;
+        }
         ActQuantArgs aq{};
         aq.acc_gate = d->acc_gu;
         aq.acc_up = d->acc_gu + I;
@@ -203,10 +233,11 @@ inline int enqueue_token(quintrit_b200_decoder* d, bool with_head) {
         aq.q_out = d->a8_i;
         aq.scale_out = d->s_i;
         aq.zero_a = d->acc_down;
-        aq.zero_a_n = H;
+        aq.zero_a_n = bs ? 0 : H;
+        aq.block_scaled = bs, aq.q8_d = d->q8_d;
         act_quant_kernel<<<1, kRowThreads, I * sizeof(float), s>>>(aq);
         QTB_LAUNCH_CHECK();
-        rc = decoder_gemv(d, l, 3, d->a8_i, d->acc_down);
+        rc = bs ? decoder_gemv_bs(d, l, 6, d->a8_i, reinterpret_cast<float*>(d->acc_down)) : decoder_gemv(d, l, 3, d->a8_i, d->acc_down);
         if (rc != QUINTRIT_OK) return rc;
     }
     if (with_head) {
@@ -220,6 +251,7 @@ inline int enqueue_token(quintrit_b200_decoder* d, bool with_head) {
         nf.n = H;
         nf.y16_out = d->x16;
         nf.y16_bf16 = d->bf16_tables;
+        nf.block_scaled = bs;
         norm_quant_kernel<<<1, kRowThreads, H * sizeof(float), s>>>(nf);
         QTB_LAUNCH_CHECK();
         lm_head_kernel<<<d->sm_count * 8, 256, H * sizeof(float), s>>>(d->lm_head, d->x16, H, d->vocab, d->logits, d->bf16_tables);

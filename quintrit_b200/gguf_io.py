@@ -137,7 +137,12 @@ def write_model_gguf(path, spec: dict, trits: list, encoding: int = GGML_I2_S, a
             rows, cols = shapes[k]
             t = np.asarray(trits[l * 7 + k], np.int8).reshape(rows, cols)
             scale = np.float32(spec["scales"][l * 7 + k])
-            if encoding == GGML_I2_S:
+            if encoding == GGML_Q2_0:  # one f16 scale per 64 weights, from spec["block_scales"] (exact in f16)
+                bsc = np.asarray(spec["block_scales"][l * 7 + k], np.float32)
+                if not np.array_equal(bsc.astype(np.float16).astype(np.float32), bsc):
+                    raise ValueError("Q2_0 needs block scales that are exact in f16")
+                payload = encode_q2_0(t, bsc.astype(np.float16)).tobytes()
+            elif encoding == GGML_I2_S:
                 payload = encode_i2_s(t, rows, cols).tobytes() + struct.pack("<f", float(scale))
             else:
                 d_bits = int(np.float16(scale).view(np.uint16))

@@ -94,3 +94,43 @@ def test_bf16_embedding_and_head(oracle, arch):
     dec, _ = _run(spec, synth.prompt_tokens(6, 10, spec["vocab"]), oracle)
     assert dec.info()["table_dtype"] == 1
     dec.free()
+
+
+def _q2_0_model(arch, config):
+    """A model whose projections are Q2_0 blocks (f16 scale per 64 weights): the device gets the GGUF payloads, the oracle the
+    planar bytes and the widened scales."""
+    from quintrit_b200 import gguf_io
+
+    spec = synth.make_model(arch, True, 320, 704, 2, 4, 2, 64, 300, 256, 500000.0, 1e-5, config=config, random_norms=True, tied=(arch == q.ARCH_BITNET))
+    shapes = [(256, 320), (128, 320), (128, 320), (320, 256), (704, 320), (704, 320), (320, 704)]
+    rng = np.random.default_rng(config)
+    payloads, block_scales = [], []
+    for l in range(2):
+        for p, (r, c) in enumerate(shapes):
+            trits = synth.trits(synth.seed_for(config, l, p, 0), r * c).reshape(r, c)
+            sc = rng.uniform(0.5, 2.0, r * c // 64).astype(np.float16)
+            payloads.append((q.SRC_Q2_0, gguf_io.encode_q2_0(trits, sc)))
+            block_scales.append(sc.astype(np.float32))
+    return dict(spec, block_scales=block_scales), payloads
+
+
+@pytest.mark.parametrize("arch", [q.ARCH_LLAMA, q.ARCH_BITNET])
+def test_q2_0_model_decodes_like_the_oracle(oracle, arch):
+    """Block-scaled projections in the whole decoder (attention.rs:262-344, model.rs:209-229): Q8_0 activation blocks, F32
+    projection results, FP32-accumulator attention."""
+    spec, payloads = _q2_0_model(arch, 23)
+    dec = q.Decoder(dict(spec, weights=payloads))
+    assert dec.info()["single_kernel"] == 0
+    ref = oracle.Model(spec)
+    for pos, tok in enumerate(synth.prompt_tokens(9, 14, spec["vocab"])):
+        want = ref.forward(int(tok), pos)
+        got, greedy = dec.forward(int(tok), pos)
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), f"logits differ at position {pos}"
+        assert greedy == oracle.argmax(want)
+    dec.free()
+    # a model may not mix block-scaled and per-tensor projections
+    mixed = list(payloads)
+    mixed[3] = spec["weights"][3]
+    with pytest.raises(q.QuintritError) as e:
+        q.Decoder(dict(spec, weights=mixed))
+    assert e.value.code == 6

@@ -84,13 +84,7 @@ def test_rejections(tmp_path):
     gguf_io.write_model_gguf(good, spec, trits, gguf_io.GGML_I2_S)
     assert code(good, flags=1)[0] == 2                      # unknown flag bits
     assert code(good, context=100)[0] == 2                  # below 256 positions
-    # a file with a Q2_0 tensor is refused like the reference's GPU loader refuses it
-    q2 = tmp_path / "q2.gguf"
     meta = {"general.architecture": "llama", "llama.embedding_length": 256, "llama.attention.head_count": 4, "llama.vocab_size": 300}
-    gguf_io.write_gguf(q2, meta, [("blk.0.attn_q.weight", (256, 256), gguf_io.GGML_Q2_0,
-                                   gguf_io.encode_q2_0(trits[0], np.ones(256 * 256 // 64, np.float16)).tobytes())])
-    c, msg = code(q2)
-    assert c == 6 and "Q2_0" in msg
     # a missing projection names the tensor
     miss = tmp_path / "miss.gguf"
     gguf_io.write_gguf(miss, dict(meta, **{"llama.block_count": 1, "llama.feed_forward_length": 512, "llama.attention.head_count_kv": 2,
@@ -130,6 +124,26 @@ def test_bf16_tables_from_a_file(tmp_path):
     assert dec.info()["table_dtype"] == 1
     ref = oracle.Model(spec)
     for pos, tok in enumerate(synth.prompt_tokens(8, 6, spec["vocab"])):
+        want = ref.forward(int(tok), pos)
+        got, _ = dec.forward(int(tok), pos)
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), pos
+    dec.free()
+
+
+def test_q2_0_file(tmp_path):
+    """A whole model of Q2_0 projections from a file (the reference's GPU loader refuses these, gpu.rs:152-154; its CPU path is
+    the oracle's): logits bit for bit."""
+    spec = synth.make_model(q.ARCH_LLAMA, True, 256, 512, 2, 4, 2, 64, 300, 512, 500000.0, 1e-5, config=15, random_norms=True)
+    shapes = [(256, 256), (128, 256), (128, 256), (256, 256), (512, 256), (512, 256), (256, 512)]
+    trits = [synth.trits(synth.seed_for(15, l, p, 0), r * c).reshape(r, c) for l in range(2) for p, (r, c) in enumerate(shapes)]
+    rng = np.random.default_rng(15)
+    spec["block_scales"] = [rng.uniform(0.5, 2.0, t.size // 64).astype(np.float16).astype(np.float32) for t in trits]
+    path = tmp_path / "q2.gguf"
+    gguf_io.write_model_gguf(path, spec, trits, gguf_io.GGML_Q2_0)
+    dec = q.Decoder.open(path)
+    assert dec.info()["f32_values"] == 1 and dec.info()["single_kernel"] == 0
+    ref = oracle.Model(spec)
+    for pos, tok in enumerate(synth.prompt_tokens(8, 8, spec["vocab"])):
         want = ref.forward(int(tok), pos)
         got, _ = dec.forward(int(tok), pos)
         assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), pos
