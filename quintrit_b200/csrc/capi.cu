@@ -967,7 +967,7 @@ int decoder_create_impl(const quintrit_b200_decoder_desc_t* desc, quintrit_b200_
     int smem_optin = 0;
     QTB_CUDA(cudaDeviceGetAttribute(&smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, d->device));
     const bool staged_ok = hd >= 64 && (hd & (hd - 1)) == 0 && gqa_n <= 16 && mega_bytes <= static_cast<size_t>(smem_optin);
-    if (desc->arch == QUINTRIT_B200_ARCH_LLAMA && staged_ok && d->q_heads <= kMegaMaxHeads && !(mode && std::strcmp(mode, "kernels") == 0)) {
+    if (staged_ok && d->q_heads <= kMegaMaxHeads && !(mode && std::strcmp(mode, "kernels") == 0)) {
         if ((rc = mega_setup(d, desc)) != QUINTRIT_OK) return rc;
         d->use_mega = true;
     }
@@ -1040,6 +1040,8 @@ int mega_setup(quintrit_b200_decoder* d, const quintrit_b200_decoder_desc_t* des
         phase(3, m + 6, o_zero, 1);
         ly.attn_norm = d->norms[l * 4 + 0];
         ly.ffn_norm = d->norms[l * 4 + 1];
+        ly.attn_sub_norm = d->norms[l * 4 + 2];  // nullptr unless the model has sub-norms (BitNet)
+        ly.ffn_sub_norm = d->norms[l * 4 + 3];
         for (int k = 0; k < 7; ++k) ly.ws[k] = d->scales[l * 7 + k];
         ly.kc = d->kc + size_t(l) * d->ctx * kvd;
         ly.vc = d->vc + size_t(l) * d->ctx * kvd;
@@ -1059,6 +1061,13 @@ int mega_setup(quintrit_b200_decoder* d, const quintrit_b200_decoder_desc_t* des
     a.v_inter = d->v_inter, a.amax_bits = d->amax_bits, a.part_acc = d->part_acc, a.part_ms = d->part_ms, a.logits = d->logits;
     a.scores = d->scores, a.attn_region = static_cast<unsigned int>(mega_attn_region(d->ctx, d->q_heads / d->kv_heads, d->head_dim));
     a.bf16_tables = d->bf16_tables ? 1 : 0;
+    a.neox = d->arch == QUINTRIT_B200_ARCH_BITNET, a.relu2 = d->arch == QUINTRIT_B200_ARCH_BITNET;
+    a.sumsq_part = nullptr;
+    if (d->arch == QUINTRIT_B200_ARCH_BITNET) {
+        double* part = nullptr;
+        if ((rc = dev_alloc(d, &part, static_cast<size_t>(d->sm_count))) != QUINTRIT_OK) return rc;
+        a.sumsq_part = part;
+    }
     a.tp_rank = d->tp_rank, a.tp_world = d->tp_world, a.tp_seq = d->tp_seq;
     for (int p = 0; p < 8; ++p) a.tp_box[p] = nullptr;
     a.tp_box[d->tp_rank] = d->tp_box;

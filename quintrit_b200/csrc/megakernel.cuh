@@ -29,6 +29,8 @@ struct MegaLayer {
     int first[4], count[4];   // work items of the q|k|v, o, gate|up and down launches (indices into MegaArgs::items)
     const float* attn_norm;
     const float* ffn_norm;
+    const float* attn_sub_norm;  // BitNet: RMSNorm of the attention output before o (q_dim weights), else nullptr
+    const float* ffn_sub_norm;   // BitNet: RMSNorm of the gated activations before down (inter weights), else nullptr
     float ws[7];
     __half* kc;               // [ctx][kv_dim]
     __half* vc;
@@ -66,6 +68,9 @@ struct MegaArgs {
     // every rank has one; ranks write their slices straight into the boxes of all ranks over NVLink as (value, sequence
     // number) pairs that the readers poll.
     int bf16_tables;           // embedding and output head hold BF16 instead of F16 bit patterns
+    int neox;                  // BitNet: RoPE pairs (i, i + rope_dims / 2) instead of (2i, 2i + 1) (config.rs:464-467)
+    int relu2;                 // BitNet: relu(gate)^2 * up instead of SwiGLU (ops.rs:301-308)
+    double* sumsq_part;        // BitNet FFN sub-norm: one partial sum of squares per CTA
     int tp_rank, tp_world;
     unsigned char* tp_box[8];  // the boxes as mapped into this process, own box at [tp_rank]
     unsigned int* tp_seq;      // exchanges completed by earlier launches (the same on every rank)
@@ -525,14 +530,22 @@ __device__ __noinline__ void mega_scores_unit(const MegaArgs& a, const MegaLayer
     for (int idx = tid; idx < (gqa + (has_cur ? 1 : 0)) * half; idx += kMegaThreads) {
         const int g = idx / half, p = idx - g * half;
         const bool is_q = g < gqa;
-        const int src = is_q ? (kvh * gqa + g) * hd + 2 * p : qd + kvh * hd + 2 * p;
-        const int i0 = __ldcg(a.acc_qkv + src), i1 = __ldcg(a.acc_qkv + src + 1);
+        // the two elements of pair p: (2p, 2p + 1), or with NEOX pairing (p, p + rope_dims / 2) inside the rotated part and
+        // plain neighbours behind it (ops.rs:160-221)
+        const int hr = a.rope_dims / 2;
+        int e0 = 2 * p, e1 = 2 * p + 1;
+        if (a.neox) {
+            e0 = p < hr ? p : a.rope_dims + 2 * (p - hr);
+            e1 = p < hr ? p + hr : e0 + 1;
+        }
+        const int base = is_q ? (kvh * gqa + g) * hd : qd + kvh * hd;
+        const int i0 = __ldcg(a.acc_qkv + base + e0), i1 = __ldcg(a.acc_qkv + base + e1);
         int j0 = 0, j1 = 0;
         if (!is_q) {
-            j0 = __ldcg(a.acc_qkv + src + kvd);
-            j1 = __ldcg(a.acc_qkv + src + kvd + 1);
+            j0 = __ldcg(a.acc_qkv + base + kvd + e0);
+            j1 = __ldcg(a.acc_qkv + base + kvd + e1);
         }
-        const bool rot = p < a.rope_dims / 2;
+        const bool rot = p < hr;
         float c0 = 1.0f, sn = 0.0f;
         if (rot) {
             c0 = cs[2 * p];
@@ -546,13 +559,13 @@ __device__ __noinline__ void mega_scores_unit(const MegaArgs& a, const MegaLayer
             x1 = y1;
         }
         if (is_q) {
-            s_q[g * hd + 2 * p] = f32v ? x0 : __half2float(__float2half_rn(x0));
-            s_q[g * hd + 2 * p + 1] = f32v ? x1 : __half2float(__float2half_rn(x1));
+            s_q[g * hd + e0] = f32v ? x0 : __half2float(__float2half_rn(x0));
+            s_q[g * hd + e1] = f32v ? x1 : __half2float(__float2half_rn(x1));
         } else {
-            s_kcur[2 * p] = __float2half_rn(x0);
-            s_kcur[2 * p + 1] = __float2half_rn(x1);
-            s_vcur[2 * p] = __float2half_rn(live ? __fmul_rn(static_cast<float>(j0), pv) : 0.0f);
-            s_vcur[2 * p + 1] = __float2half_rn(live ? __fmul_rn(static_cast<float>(j1), pv) : 0.0f);
+            s_kcur[e0] = __float2half_rn(x0);
+            s_kcur[e1] = __float2half_rn(x1);
+            s_vcur[e0] = __float2half_rn(live ? __fmul_rn(static_cast<float>(j0), pv) : 0.0f);
+            s_vcur[e1] = __float2half_rn(live ? __fmul_rn(static_cast<float>(j1), pv) : 0.0f);
         }
     }
     __syncthreads();
@@ -884,7 +897,7 @@ __device__ __noinline__ void phase_values(const MegaArgs& a, int l, unsigned cha
 }
 
 // Phase D: combine the chunks of every head (attention.rs:497-541), int8 codes for the o projection.
-__device__ __noinline__ bool phase_combine(const MegaArgs& a, unsigned int seq, unsigned char* smem) {
+__device__ __noinline__ bool phase_combine(const MegaArgs& a, int l, unsigned int seq, unsigned char* smem) {
     const MegaSmem v = mega_smem_views(smem, a);
     const int tid = threadIdx.x, hd = a.head_dim, qd = a.q_heads * hd;
     float* s_pair = v.pair;
@@ -976,6 +989,19 @@ __device__ __noinline__ bool phase_combine(const MegaArgs& a, unsigned int seq, 
             }
         }
     }
+    if (const float* sub_w = v.layers[l].attn_sub_norm) {  // BitNet: RMSNorm of the attention output (attention.rs:234-246)
+        double sum = 0.0;
+        for (int i = tid; i < n_all; i += kMegaThreads) sum += static_cast<double>(__fmul_rn(v.y[i], v.y[i]));
+        sum = block_sum_f64(sum, v.sh_d);
+        const float mean = __double2float_rn(sum / static_cast<double>(n_all));
+        const float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, a.eps)));
+        amax = 0.0f;
+        for (int i = tid; i < n_all; i += kMegaThreads) {
+            const float y = __fmul_rn(__fmul_rn(v.y[i], inv), __ldg(sub_w + i));
+            v.y[i] = y;
+            amax = fmaxf(amax, fabsf(y));
+        }
+    }
     amax = block_max_f32(amax, v.sh_f);
     const float s_q = amax > 0.0f ? __fdiv_rn(127.0f, amax) : 0.0f;
     for (int i = tid; i < n_all; i += kMegaThreads) v.a8[i] = static_cast<int8_t>(amax > 0.0f ? quantize_code(v.y[i], s_q) : 0);
@@ -1001,28 +1027,62 @@ __device__ __noinline__ void phase_swiglu(const MegaArgs& a, int l, unsigned cha
             a.v_inter[i] = x;
         }
     };
+    const bool relu2 = a.relu2 != 0;
+    auto act = [&](float g, float u) {  // SwiGLU (ops.rs:427-464) or relu(gate)^2 * up (ops.rs:301-308, 467-473)
+        if (!relu2) return __fmul_rn(ggml_silu(g), u);
+        const float r = g > 0.0f ? g : 0.0f;
+        return __fmul_rn(__fmul_rn(r, r), u);
+    };
+    double sq = 0.0;  // BitNet FFN sub-norm: this thread's share of the sum of squares
     for (int i0 = cta * kMegaThreads + tid; i0 < I; i0 += 2 * G * kMegaThreads) {
         const int i1 = i0 + G * kMegaThreads;
         const int g0 = __ldcg(a.acc_gu + i0), u0 = __ldcg(a.acc_gu + I + i0);
         const int g1 = i1 < I ? __ldcg(a.acc_gu + i1) : 0, u1 = i1 < I ? __ldcg(a.acc_gu + I + i1) : 0;
         {
             const float g = s_f > 0.0f ? __fmul_rn(static_cast<float>(g0), pg) : 0.0f, u = s_f > 0.0f ? __fmul_rn(static_cast<float>(u0), pu) : 0.0f;
-            const float x = __fmul_rn(ggml_silu(g), u);
+            const float x = act(g, u);
             store(i0, x);
             m = fmaxf(m, fabsf(x));
+            sq += static_cast<double>(__fmul_rn(x, x));
         }
         if (i1 < I) {
             const float g = s_f > 0.0f ? __fmul_rn(static_cast<float>(g1), pg) : 0.0f, u = s_f > 0.0f ? __fmul_rn(static_cast<float>(u1), pu) : 0.0f;
-            const float x = __fmul_rn(ggml_silu(g), u);
+            const float x = act(g, u);
             store(i1, x);
             m = fmaxf(m, fabsf(x));
+            sq += static_cast<double>(__fmul_rn(x, x));
         }
     }
     if (a.tp_world > 1) __threadfence_system();  // the stores to the other boxes precede the barrier that follows
-    m = block_max_f32(m, v.sh_f);
-    if (tid == 0 && m > 0.0f) atomicMax(a.amax_bits + (l & 1), __float_as_uint(m));  // non-negative floats order like their bits
+    if (ly.ffn_sub_norm != nullptr) {  // the maximum is taken after the sub-norm (phase_ffn_sub_norm); here only the partial sum
+        sq = block_sum_f64(sq, v.sh_d);
+        if (tid == 0) a.sumsq_part[cta] = sq;
+    } else {
+        m = block_max_f32(m, v.sh_f);
+        if (tid == 0 && m > 0.0f) atomicMax(a.amax_bits + (l & 1), __float_as_uint(m));  // non-negative floats order like their bits
+    }
     if (cta == G - 1)
         for (int i = tid; i < a.hidden; i += kMegaThreads) a.acc_o[i] = 0;  // consumed in phase E
+}
+
+// BitNet, after phase_swiglu and a grid barrier: RMSNorm of the gated activations (model.rs:219-224). Every CTA adds the
+// per-CTA sums of squares in the same order, normalises its own slice in place and contributes to the maximum.
+__device__ __noinline__ void phase_ffn_sub_norm(const MegaArgs& a, int l, unsigned char* smem) {
+    const MegaSmem v = mega_smem_views(smem, a);
+    const int tid = threadIdx.x, cta = blockIdx.x, G = gridDim.x, I = a.inter;
+    const float* w = v.layers[l].ffn_sub_norm;
+    double sum = 0.0;
+    for (int c = 0; c < G; ++c) sum += __ldcg(a.sumsq_part + c);
+    const float mean = __double2float_rn(sum / static_cast<double>(I));
+    const float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, a.eps)));
+    float m = 0.0f;
+    for (int i = cta * kMegaThreads + tid; i < I; i += G * kMegaThreads) {
+        const float y = __fmul_rn(__fmul_rn(a.v_inter[i], inv), __ldg(w + i));
+        a.v_inter[i] = y;
+        m = fmaxf(m, fabsf(y));
+    }
+    m = block_max_f32(m, v.sh_f);
+    if (tid == 0 && m > 0.0f) atomicMax(a.amax_bits + (l & 1), __float_as_uint(m));
 }
 
 // Final norm (model.rs:326-331), output head, greedy candidate of this CTA.
@@ -1214,7 +1274,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const __g
         MEGA_TRACE();  // 5: values done (this CTA)
         MEGA_BARRIER();
         MEGA_TRACE();  // 6
-        if (!phase_combine(a, seq_base + 4u * l + 1u, smem)) return;
+        if (!phase_combine(a, l, seq_base + 4u * l + 1u, smem)) return;
         MEGA_TRACE();  // 7: combine + quantise done
         MEGA_GEMV(1, v.a8, nullptr, 0.0f, a.acc_o);
         MEGA_BARRIER();
@@ -1228,6 +1288,10 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const __g
         MEGA_TRACE();  // 11
         phase_swiglu(a, l, smem);
         MEGA_BARRIER();
+        if (a.relu2 != 0 && a.sumsq_part != nullptr && mega_smem_views(smem, a).layers[l].ffn_sub_norm != nullptr) {
+            phase_ffn_sub_norm(a, l, smem);
+            MEGA_BARRIER();
+        }
         MEGA_TRACE();  // 12
         {
             // down, quantising v on the fly with the scale from the maximum every CTA contributed to

@@ -134,3 +134,18 @@ def test_q2_0_model_decodes_like_the_oracle(oracle, arch):
     with pytest.raises(q.QuintritError) as e:
         q.Decoder(dict(spec, weights=mixed))
     assert e.value.code == 6
+
+
+@pytest.mark.parametrize("arch,f32_values", [(q.ARCH_LLAMA, False), (q.ARCH_BITNET, True)])
+def test_one_kernel_per_step_path_stays_exact(oracle, monkeypatch, arch, f32_values):
+    """Both decode paths serve both architectures; QUINTRIT_B200_DECODE=kernels selects the one-kernel-per-step path, which
+    otherwise only runs for shapes the token kernel does not take."""
+    monkeypatch.setenv("QUINTRIT_B200_DECODE", "kernels")
+    spec = synth.make_model(arch, f32_values, 320, 704, 2, 4, 2, 64, 300, 256, 500000.0, 1e-5, config=19, random_norms=True, tied=(arch == q.ARCH_BITNET))
+    dec, _ = _run(spec, synth.prompt_tokens(4, 10, spec["vocab"]), oracle)
+    assert dec.info()["single_kernel"] == 0
+    dec.free()
+    monkeypatch.delenv("QUINTRIT_B200_DECODE")
+    dec2 = q.Decoder(spec)
+    assert dec2.info()["single_kernel"] == 1
+    dec2.free()
