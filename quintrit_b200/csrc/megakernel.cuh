@@ -1071,8 +1071,21 @@ __device__ __noinline__ void phase_ffn_sub_norm(const MegaArgs& a, int l, unsign
     const MegaSmem v = mega_smem_views(smem, a);
     const int tid = threadIdx.x, cta = blockIdx.x, G = gridDim.x, I = a.inter;
     const float* w = v.layers[l].ffn_sub_norm;
-    double sum = 0.0;
-    for (int c = 0; c < G; ++c) sum += __ldcg(a.sumsq_part + c);
+    // the per-CTA partial sums: fetched by one thread each (one L2 round trip in all), then added by every thread in the
+    // same fixed order (four interleaved chains)
+    double* s_part = reinterpret_cast<double*>(v.y);  // the activation vector is not in use between SwiGLU and down
+    for (int c = tid; c < G; c += kMegaThreads) s_part[c] = __ldcg(a.sumsq_part + c);
+    __syncthreads();
+    double p0 = 0.0, p1 = 0.0, p2 = 0.0, p3 = 0.0;
+    int c = 0;
+    for (; c + 4 <= G; c += 4) {
+        p0 += s_part[c];
+        p1 += s_part[c + 1];
+        p2 += s_part[c + 2];
+        p3 += s_part[c + 3];
+    }
+    for (; c < G; ++c) p0 += s_part[c];
+    const double sum = (p0 + p1) + (p2 + p3);
     const float mean = __double2float_rn(sum / static_cast<double>(I));
     const float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, a.eps)));
     float m = 0.0f;
