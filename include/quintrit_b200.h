@@ -240,6 +240,11 @@ int quintrit_b200_decoder_free(quintrit_b200_decoder_t* decoder);
 #define QUINTRIT_B200_TP_HANDLE_BYTES 64
 int quintrit_b200_decoder_tp_handle(const quintrit_b200_decoder_t* decoder, uint8_t* out_handle, size_t out_capacity);
 int quintrit_b200_decoder_tp_attach(quintrit_b200_decoder_t* decoder, const uint8_t* handles, size_t handles_len);
+/* The same for a group whose decoders all live in this process (one thread per GPU, or several ranks on one GPU for
+ * tests): `group` holds the tp_world decoders in rank order, this decoder among them; peer access between their devices is
+ * enabled as needed. The environment variable QUINTRIT_B200_TP_WAIT_MS (read at creation) replaces the two seconds a
+ * rank waits for a silent peer. */
+int quintrit_b200_decoder_tp_attach_local(quintrit_b200_decoder_t* decoder, quintrit_b200_decoder_t* const* group, size_t group_len);
 
 /* Options of quintrit_b200_decoder_open_gguf: the struct of quintrit.h:502-507 (same fields and meaning; no flag is
  * defined here, so flags must be 0; the context is capped at 8192 instead of 7936). */

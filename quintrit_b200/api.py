@@ -113,6 +113,7 @@ def load_library(build_if_missing: bool = True) -> C.CDLL:
     l.quintrit_b200_decoder_free.argtypes = [C.c_void_p]
     l.quintrit_b200_decoder_tp_handle.argtypes = [C.c_void_p, _u8p, _sz]
     l.quintrit_b200_decoder_tp_attach.argtypes = [C.c_void_p, _u8p, _sz]
+    l.quintrit_b200_decoder_tp_attach_local.argtypes = [C.c_void_p, C.POINTER(C.c_void_p), _sz]
     l.quintrit_b200_decoder_open_gguf.argtypes = [C.c_char_p, C.POINTER(_GpuOptionsC), C.POINTER(C.c_void_p)]
     l.quintrit_b200_decoder_info.argtypes = [C.c_void_p, C.POINTER(_DecoderInfoC)]
     l.quintrit_b200_gguf_describe.argtypes = [C.c_char_p, C.c_char_p, _sz, C.POINTER(_sz)]
@@ -369,6 +370,11 @@ class Decoder:
         out = np.zeros(64, np.uint8)
         _check(load_library().quintrit_b200_decoder_tp_handle(self._h, _p(out, _u8p), out.size))
         return out.tobytes()
+
+    def tp_attach_local(self, group) -> None:
+        """Maps the boxes of a group of decoders that live in this process (rank order, this decoder among them)."""
+        hs = (C.c_void_p * len(group))(*[g._h for g in group])
+        _check(load_library().quintrit_b200_decoder_tp_attach_local(self._h, hs, len(group)))
 
     def tp_attach(self, handles) -> None:
         """Maps the boxes of all ranks; `handles` are the tp_handle() bytes of every rank in rank order."""

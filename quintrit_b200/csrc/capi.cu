@@ -1069,6 +1069,11 @@ int mega_setup(quintrit_b200_decoder* d, const quintrit_b200_decoder_desc_t* des
         a.sumsq_part = part;
     }
     a.tp_rank = d->tp_rank, a.tp_world = d->tp_world, a.tp_seq = d->tp_seq;
+    a.tp_wait_ns = kTpWaitLimitNs;
+    if (const char* ms = std::getenv("QUINTRIT_B200_TP_WAIT_MS")) {  // shorter or longer patience with a silent peer, in milliseconds
+        const long v = std::strtol(ms, nullptr, 10);
+        if (v >= 1 && v <= 600000) a.tp_wait_ns = static_cast<unsigned long long>(v) * 1000000ull;
+    }
     for (int p = 0; p < 8; ++p) a.tp_box[p] = nullptr;
     a.tp_box[d->tp_rank] = d->tp_box;
     a.box_acc_o = static_cast<unsigned int>(off_acc_o), a.box_acc_down = static_cast<unsigned int>(off_acc_down), a.box_y = static_cast<unsigned int>(off_y);
@@ -1466,6 +1471,40 @@ extern "C" int quintrit_b200_decoder_tp_attach(quintrit_b200_decoder_t* decoder,
             }
             d->tp_peer[p] = ptr;
             d->mega.tp_box[p] = static_cast<unsigned char*>(ptr);
+        }
+        d->tp_attached = true;
+        return ok();
+    });
+}
+
+extern "C" int quintrit_b200_decoder_tp_attach_local(quintrit_b200_decoder_t* decoder, quintrit_b200_decoder_t* const* group, size_t group_len) {
+    return guard([&]() -> int {
+        int rc = check_decoder(decoder);
+        if (rc != QUINTRIT_OK) return rc;
+        quintrit_b200_decoder* d = decoder;
+        if (group == nullptr) return fail(QUINTRIT_ERR_NULL_POINTER, "group is NULL");
+        if (d->tp_world <= 1) return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "the decoder was not created as a rank of a tensor-parallel group");
+        if (group_len != static_cast<size_t>(d->tp_world)) return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "%zu decoders for %d ranks", group_len, d->tp_world);
+        if (d->tp_attached) return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "the tensor-parallel group is attached already");
+        for (int p = 0; p < d->tp_world; ++p) {
+            rc = check_decoder(group[p]);
+            if (rc != QUINTRIT_OK) return rc;
+            if (group[p]->tp_world != d->tp_world || group[p]->tp_rank != p || group[p]->tp_box_bytes != d->tp_box_bytes)
+                return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "decoder %d of the group is not rank %d of the same %d-rank model", p, p, d->tp_world);
+        }
+        if (group[d->tp_rank] != d) return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "the decoder is not at its own rank in the group");
+        DeviceGuard g(d->device);
+        for (int p = 0; p < d->tp_world; ++p) {
+            if (p == d->tp_rank) continue;
+            if (group[p]->device != d->device) {
+                int can = 0;
+                QTB_CUDA(cudaDeviceCanAccessPeer(&can, d->device, group[p]->device));
+                if (!can) return fail(QUINTRIT_ERR_DEVICE, "CUDA device %d cannot access the memory of device %d", d->device, group[p]->device);
+                const cudaError_t e = cudaDeviceEnablePeerAccess(group[p]->device, 0);
+                if (e != cudaSuccess && e != cudaErrorPeerAccessAlreadyEnabled) return cuda_fail(e, "cudaDeviceEnablePeerAccess");
+                (void)cudaGetLastError();
+            }
+            d->mega.tp_box[p] = group[p]->tp_box;
         }
         d->tp_attached = true;
         return ok();

@@ -74,6 +74,7 @@ struct MegaArgs {
     int tp_rank, tp_world;
     unsigned char* tp_box[8];  // the boxes as mapped into this process, own box at [tp_rank]
     unsigned int* tp_seq;      // exchanges completed by earlier launches (the same on every rank)
+    unsigned long long tp_wait_ns;  // how long a reader waits for a peer's pair before it gives up (kTpWaitLimitNs by default)
     unsigned int box_acc_o, box_acc_down, box_y, box_v, box_amax, box_best;  // byte offsets inside a box (pair buffers; box_v: plain floats)
     int q_dim_full, inter_full, vocab_base, h_slice;  // whole attention width and FFN width, first vocabulary row and hidden / world
 };
@@ -142,13 +143,13 @@ __device__ __forceinline__ bool grid_barrier(unsigned int* bar, unsigned int tar
 // as the low-latency protocol of collective libraries.) Sequence numbers grow from launch to launch, and a buffer is
 // rewritten four exchanges later at the earliest, after the writer has seen results that depend on the reader having
 // finished with it.
-constexpr unsigned long long kTpWaitLimitNs = 2000000000ull;  // a peer that does not show up within 2 s is given up on
+constexpr unsigned long long kTpWaitLimitNs = 2000000000ull;  // default: a peer that does not show up within 2 s is given up on
 
 __device__ __forceinline__ void ll_store(uint2* p, uint32_t value, uint32_t seq) {
     asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(value), "r"(seq) : "memory");
 }
 
-// Value of a pair once it carries `seq`. Bounded: after kTpWaitLimitNs the kernel's status becomes 3, the failure is
+// Value of a pair once it carries `seq`. Bounded: after MegaArgs::tp_wait_ns the kernel's status becomes 3, the failure is
 // signalled through the barrier counter (the next grid barrier ends the kernel) and 0 is returned.
 __device__ __forceinline__ uint32_t ll_load(const uint2* p, uint32_t seq, const MegaArgs& a) {
     uint32_t value, got;
@@ -159,7 +160,7 @@ __device__ __forceinline__ uint32_t ll_load(const uint2* p, uint32_t seq, const 
         if ((spins & 255u) == 255u) {
             const unsigned long long now = global_timer_ns();
             if (t0 == 0) t0 = now;
-            if (now - t0 > kTpWaitLimitNs || *reinterpret_cast<volatile unsigned int*>(a.bar) >= kBarFail) {
+            if (now - t0 > a.tp_wait_ns || *reinterpret_cast<volatile unsigned int*>(a.bar) >= kBarFail) {
                 report_failure(a.bar, a.status, 3u);
                 return 0u;
             }

@@ -78,3 +78,36 @@ def test_two_ranks_decode_like_one_cpu_model(tmp_path, geometry):
     port = _free_port()
     mp.start_processes(_rank_main, args=(2, port, str(tmp_path), geometry), nprocs=2, join=True, start_method="spawn")
     assert (tmp_path / "rank0.ok").exists() and (tmp_path / "rank1.ok").exists()
+
+
+def test_a_silent_rank_ends_in_an_error_not_in_a_hang(monkeypatch):
+    """Failure detection without a GPU fault: rank 0 of a two-rank group decodes alone (its peer exists but never launches), so
+    the pairs it waits for never arrive. The wait is bounded (QUINTRIT_B200_TP_WAIT_MS, here 200 ms): the kernel gives up, sets
+    its status, every CTA leaves through the grid barrier, and the call returns QUINTRIT_ERR_DEVICE. The context stays usable.
+    Only one kernel runs at any time, so nothing on the GPU waits on another launch."""
+    import oracle
+    import quintrit_b200 as q
+    from quintrit_b200 import synth
+
+    monkeypatch.setenv("QUINTRIT_B200_TP_WAIT_MS", "200")
+    spec = synth.make_model(q.ARCH_LLAMA, False, 256, 512, 2, 4, 2, 64, 512, 256, 500000.0, 1e-5, config=22, random_norms=True)
+    group = [q.Decoder(synth.shard_spec(spec, r, 2), device=0) for r in range(2)]
+    for d in group:
+        d.tp_attach_local(group)
+    with pytest.raises(q.QuintritError) as e:
+        group[0].forward(1, 0)
+    assert e.value.code == 15 and "another rank" in str(e.value)
+    for d in group:
+        d.free()
+    # the device still works: a decoder of the whole model gives the oracle's logits
+    whole = q.Decoder(spec)
+    want = oracle.Model(spec).forward(1, 0)
+    got, _ = whole.forward(1, 0)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    whole.free()
+    # set-up errors of the in-process attach
+    lone = q.Decoder(spec)
+    with pytest.raises(q.QuintritError) as e:
+        lone.tp_attach_local([lone])
+    assert e.value.code == 2
+    lone.free()
