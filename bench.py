@@ -286,6 +286,31 @@ def run_decode_tp(args, rank: int, world: int, local_rank: int, dist):
             "setup_s": round(setup_s, 1)}
 
 
+def run_block_scaled(args, local_rank: int):
+    """The block-scaled (Q2_0 x Q8_0) projection on the three Falcon3-10B projection shapes through the C ABI with host
+    buffers (activations in, results out, every call). Profiling aid: the kernel's device time is read from an ncu launch
+    list of this command."""
+    import quintrit_b200 as q
+    from quintrit_b200 import gguf_io
+
+    out = []
+    for rows, cols in [(3072, 3072), (23040, 3072), (3072, 23040)]:
+        rng = np.random.default_rng(rows + cols)
+        trits = rng.integers(-1, 2, size=(rows, cols)).astype(np.int8)
+        sc = rng.uniform(0.5, 2.0, rows * cols // 64).astype(np.float16)
+        m = q.Matrix(gguf_io.encode_q2_0(trits, sc), rows, cols, q.SRC_Q2_0, device=local_rank)
+        x = rng.standard_normal(cols).astype(np.float32)
+        for _ in range(max(3, args.warmup)):
+            m.gemv_block_scaled(x)
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            m.gemv_block_scaled(x)
+        dt = (time.perf_counter() - t0) / args.steps
+        out.append({"rows": rows, "cols": cols, "us_per_call_host_buffers": round(dt * 1e6, 1), "gweights_per_s": round(rows * cols / dt / 1e9, 1)})
+        m.free()
+    return out
+
+
 def run_reference(args, rank: int, world: int):
     """--impl reference: the CPU path, timed on the host cores (rank 0 only)."""
     if rank != 0:
@@ -492,6 +517,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-decode", action="store_true", help="skip the whole-token decode leg")
     ap.add_argument("--decode-only", action="store_true", help="run only the whole-token decode leg and print its object (profiling aid)")
+    ap.add_argument("--block-scaled-only", action="store_true", help="run only the block-scaled (Q2_0) projection on the model's shapes (profiling aid)")
     ap.add_argument("--decode-shape", default="falcon3_10b", choices=["falcon3_10b", "bitnet_2b"])
     ap.add_argument("--decode-layers", type=int, default=None, help="fewer layers than the shape has (experiments)")
     ap.add_argument("--prompt", type=int, default=1024, help="context length at which a decode step is timed")
@@ -499,6 +525,9 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.block_scaled_only:
+        print(json.dumps({"block_scaled": run_block_scaled(args, local_rank)}), flush=True)
+        return
     if args.decode_only:
         print(json.dumps({"decode": run_decode(args, local_rank)}), flush=True)
     elif args.impl == "reference":
