@@ -70,8 +70,12 @@ __global__ void quantize_q8_0_kernel(const float* __restrict__ x, size_t n, int8
     }
 }
 
-// Trit tables in shared memory: for every byte value the trits of planes 0-3 as four int8 in one word, and plane 4.
-__device__ __forceinline__ void build_trit_tables(uint32_t* t0123, int8_t* t4) {
+// Trit tables in shared memory: for every byte value the trits of planes 0-3 as four int8 in one word, and plane 4 (in
+// the low byte of a word). Each table holds kBsCopies interleaved copies (entry b of copy c at index b * kBsCopies + c):
+// the 32 lanes of a warp look up unrelated bytes at the same time, and a lane that reads copy lane % kBsCopies meets at
+// most a quarter of the other lanes in its banks.
+constexpr int kBsCopies = 8;
+__device__ __forceinline__ void build_trit_tables(uint32_t* t0123, uint32_t* t4) {
     for (int b = threadIdx.x; b < 256; b += blockDim.x) {
         int t[5] = {0, 0, 0, 0, 0};
         const bool valid = b <= 250 && b % 28 != 27;
@@ -86,80 +90,122 @@ __device__ __forceinline__ void build_trit_tables(uint32_t* t0123, int8_t* t4) {
             const int d1 = r / 3, d0 = r - 3 * d1;
             t[0] = d0 - 1, t[1] = d1 - 1, t[2] = d2 - 1, t[3] = d3 - 1, t[4] = d4 - 1;
         }
-        t0123[b] = (static_cast<uint32_t>(t[0]) & 0xFFu) | ((static_cast<uint32_t>(t[1]) & 0xFFu) << 8) | ((static_cast<uint32_t>(t[2]) & 0xFFu) << 16) |
-                   ((static_cast<uint32_t>(t[3]) & 0xFFu) << 24);
-        t4[b] = static_cast<int8_t>(t[4]);
+        const uint32_t w = (static_cast<uint32_t>(t[0]) & 0xFFu) | ((static_cast<uint32_t>(t[1]) & 0xFFu) << 8) | ((static_cast<uint32_t>(t[2]) & 0xFFu) << 16) |
+                           ((static_cast<uint32_t>(t[3]) & 0xFFu) << 24);
+        for (int c = 0; c < kBsCopies; ++c) {
+            t0123[b * kBsCopies + c] = w;
+            t4[b * kBsCopies + c] = static_cast<uint32_t>(t[4]) & 0xFFu;
+        }
     }
 }
 
-constexpr int kBsThreads = 256;  // 32 rows x 8 lanes per CTA
+constexpr int kBsTableBytes = 2 * 256 * kBsCopies * 4;  // the two trit tables
+constexpr int kBsThreads = 256;                       // eight warps, one row per warp at a time
+constexpr int kBsWarps = kBsThreads / 32;
+constexpr int kBsChunkBlocks = 32;                    // 160-trit blocks a warp decodes at once (one per lane)
+constexpr int kBsChunkActs = kBsChunkBlocks * 5;      // activation blocks of such a chunk
+constexpr int kBsLaneStride = 9;                      // floats per activation block in the scratch (8 lane sums + 1: no bank conflicts)
+constexpr int kBsWarpScratch = kBsChunkActs * kBsLaneStride + kBsChunkActs;  // floats: lane sums, then the scale products
 
-// Block-scaled GEMV. Thread (row, lane j of 8) owns the values 4j..4j+3 of every 32-value activation block: per block s
-// an exact integer sum of four products (dp4a), then lane = fma(w_scale[s/2] * a_scale[s], sum, lane) into the
-// accumulator of the 64-weight block's parity, strictly in the order of s; at the end the two accumulators are added and
-// the eight lanes of a row are reduced as ((l0+l4) + (l2+l6)) + ((l1+l5) + (l3+l7)) with shuffles.
+// Block-scaled GEMV, one row per warp, in two steps per chunk of 32 weight blocks (160 activation blocks):
+//  1. lane l decodes block l of the chunk (its 32 bytes: two 16-byte loads), forms for each of its five planes the eight
+//     exact integer lane sums (dp4a of four trits with four activation codes) and the product w_scale[s/2] * a_scale[s],
+//     and leaves them in the warp's scratch - this part is order-free, so it runs 32 blocks wide;
+//  2. sixteen lanes (two accumulators x eight lanes of the reference's dot product) run the multiply-add chains over the
+//     chunk strictly in the order of s: lane = fma(product, sum, lane), blocks of 64 weights alternating between the two
+//     accumulators (block_scaled.rs:175-202).
+// At the end the two accumulators are added and the eight lanes reduced as ((l0+l4) + (l2+l6)) + ((l1+l5) + (l3+l7)).
 // Activations (int8 codes and block scales) are staged in shared memory once per CTA.
 __global__ void __launch_bounds__(kBsThreads) gemv_block_scaled_kernel(const uint8_t* __restrict__ planar, const float* __restrict__ w_scales,
                                                                         const int8_t* __restrict__ qs, const float* __restrict__ a_scales, size_t rows,
                                                                         size_t cols, float* __restrict__ out) {
     extern __shared__ __align__(16) unsigned char bs_smem[];
-    uint32_t* t0123 = reinterpret_cast<uint32_t*>(bs_smem);             // 256 words
-    int8_t* t4 = reinterpret_cast<int8_t*>(bs_smem + 1024);             // 256 bytes
-    float* s_as = reinterpret_cast<float*>(bs_smem + 1280);             // cols / 32 floats
+    uint32_t* t0123 = reinterpret_cast<uint32_t*>(bs_smem);                    // 256 x kBsCopies words
+    uint32_t* t4 = t0123 + 256 * kBsCopies;                                    // likewise
+    float* s_as = reinterpret_cast<float*>(bs_smem + kBsTableBytes);           // cols / 32 floats
     int8_t* s_q = reinterpret_cast<int8_t*>(s_as + cols / 32);          // cols codes (offset is a multiple of 4)
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    float* pf = reinterpret_cast<float*>(bs_smem + ((kBsTableBytes + (cols / 32) * 4 + cols + 15) / 16) * 16) + warp * kBsWarpScratch;
+    float* dd = pf + kBsChunkActs * kBsLaneStride;
     build_trit_tables(t0123, t4);
     for (size_t i = threadIdx.x; i < cols / 32; i += kBsThreads) s_as[i] = a_scales[i];
     for (size_t i = threadIdx.x; i < cols / 4; i += kBsThreads) reinterpret_cast<uint32_t*>(s_q)[i] = reinterpret_cast<const uint32_t*>(qs)[i];
     __syncthreads();
-    const int j = threadIdx.x & 7;
     const size_t row_bytes = (cols + kBlockTrits - 1) / kBlockTrits * kBlockBytes, sb = cols / 64, nact = cols / 32;
-    for (size_t r0 = static_cast<size_t>(blockIdx.x) * 32; r0 < rows; r0 += static_cast<size_t>(gridDim.x) * 32) {
-        const size_t r = r0 + (threadIdx.x >> 3);
-        float acc0 = 0.0f, acc1 = 0.0f;
-        if (r < rows) {
-            const uint8_t* row = planar + r * row_bytes;
-            const float* ws = w_scales + r * sb;
-            for (size_t b = 0; b * 5 < nact; ++b) {
-                const uint32_t w = *reinterpret_cast<const uint32_t*>(row + b * kBlockBytes + 4 * j);
-                const uint32_t b0 = w & 0xFFu, b1 = (w >> 8) & 0xFFu, b2 = (w >> 16) & 0xFFu, b3 = w >> 24;
-                const uint32_t x0 = t0123[b0], x1 = t0123[b1], x2 = t0123[b2], x3 = t0123[b3];
-                // transpose the 4 x 4 bytes: word p = the trits of plane p of the four weights
-                const uint32_t lo01 = __byte_perm(x0, x1, 0x5140), hi01 = __byte_perm(x0, x1, 0x7362);  // (x0.b0,x1.b0,x0.b1,x1.b1), (b2,b3)
-                const uint32_t lo23 = __byte_perm(x2, x3, 0x5140), hi23 = __byte_perm(x2, x3, 0x7362);
-                uint32_t plane[5];
-                plane[0] = __byte_perm(lo01, lo23, 0x5410);
-                plane[1] = __byte_perm(lo01, lo23, 0x7632);
-                plane[2] = __byte_perm(hi01, hi23, 0x5410);
-                plane[3] = __byte_perm(hi01, hi23, 0x7632);
-                plane[4] = (static_cast<uint32_t>(t4[b0]) & 0xFFu) | ((static_cast<uint32_t>(t4[b1]) & 0xFFu) << 8) |
-                           ((static_cast<uint32_t>(t4[b2]) & 0xFFu) << 16) | ((static_cast<uint32_t>(t4[b3]) & 0xFFu) << 24);
+    const size_t nblocks = (nact + 4) / 5;
+    const int chain_c = (lane >> 3) & 1, chain_j = lane & 7;  // lanes 0-15: accumulator and lane of the dot product
+    for (size_t r = static_cast<size_t>(blockIdx.x) * kBsWarps + warp; r < rows; r += static_cast<size_t>(gridDim.x) * kBsWarps) {
+        const uint8_t* row = planar + r * row_bytes;
+        const float* ws = w_scales + r * sb;
+        float acc = 0.0f;
+        for (size_t c0 = 0; c0 < nblocks; c0 += kBsChunkBlocks) {
+            const size_t b = c0 + lane;
+            if (b < nblocks) {
+                const uint4 lo = __ldg(reinterpret_cast<const uint4*>(row + b * kBlockBytes));
+                const uint4 hi = __ldg(reinterpret_cast<const uint4*>(row + b * kBlockBytes) + 1);
+                const uint32_t words[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
 #pragma unroll
                 for (int p = 0; p < 5; ++p) {
                     const size_t s = b * 5 + p;
-                    if (s < nact) {
-                        const int a4 = *reinterpret_cast<const int*>(s_q + s * 32 + 4 * j);
-                        const int sum = __dp4a(static_cast<int>(plane[p]), a4, 0);
-                        const float d = __fmul_rn(ws[s / 2], s_as[s]);
-                        if ((s / 2) & 1)
-                            acc1 = __fmaf_rn(d, static_cast<float>(sum), acc1);
-                        else
-                            acc0 = __fmaf_rn(d, static_cast<float>(sum), acc0);
+                    if (s < nact) dd[lane * 5 + p] = __fmul_rn(__ldg(ws + s / 2), s_as[s]);
+                }
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const uint32_t w = words[j];
+                    const uint32_t b0 = w & 0xFFu, b1 = (w >> 8) & 0xFFu, b2 = (w >> 16) & 0xFFu, b3 = w >> 24;
+                    const int cp = lane & (kBsCopies - 1);
+                    const uint32_t x0 = t0123[b0 * kBsCopies + cp], x1 = t0123[b1 * kBsCopies + cp], x2 = t0123[b2 * kBsCopies + cp], x3 = t0123[b3 * kBsCopies + cp];
+                    // transpose the 4 x 4 bytes: word p = the trits of plane p of the four weights
+                    const uint32_t lo01 = __byte_perm(x0, x1, 0x5140), hi01 = __byte_perm(x0, x1, 0x7362);
+                    const uint32_t lo23 = __byte_perm(x2, x3, 0x5140), hi23 = __byte_perm(x2, x3, 0x7362);
+                    uint32_t plane[5];
+                    plane[0] = __byte_perm(lo01, lo23, 0x5410);
+                    plane[1] = __byte_perm(lo01, lo23, 0x7632);
+                    plane[2] = __byte_perm(hi01, hi23, 0x5410);
+                    plane[3] = __byte_perm(hi01, hi23, 0x7632);
+                    plane[4] = t4[b0 * kBsCopies + cp] | (t4[b1 * kBsCopies + cp] << 8) | (t4[b2 * kBsCopies + cp] << 16) | (t4[b3 * kBsCopies + cp] << 24);
+#pragma unroll
+                    for (int p = 0; p < 5; ++p) {
+                        const size_t s = b * 5 + p;
+                        if (s < nact) {
+                            const int a4 = *reinterpret_cast<const int*>(s_q + s * 32 + 4 * j);
+                            pf[(lane * 5 + p) * kBsLaneStride + j] = static_cast<float>(__dp4a(static_cast<int>(plane[p]), a4, 0));
+                        }
                     }
                 }
             }
+            __syncwarp();
+            // the chains: activation blocks 4m + 2c and 4m + 2c + 1 of the chunk belong to accumulator c (the chunk starts
+            // on a multiple of 160 activation blocks, so the pattern of the whole row is the pattern inside the chunk)
+            const int n_s = static_cast<int>(min(static_cast<size_t>(kBsChunkActs), nact - c0 * 5));
+            if (lane < 16) {
+#pragma unroll 4
+                for (int s0 = 2 * chain_c; s0 < n_s; s0 += 4) {
+                    acc = __fmaf_rn(dd[s0], pf[s0 * kBsLaneStride + chain_j], acc);
+                    if (s0 + 1 < n_s) acc = __fmaf_rn(dd[s0 + 1], pf[(s0 + 1) * kBsLaneStride + chain_j], acc);
+                }
+            }
+            __syncwarp();  // the scratch is rewritten by the next chunk
         }
-        float l = __fadd_rn(acc0, acc1);
-        // lanes j and j + 4 first (r_j = l[j+4] + l[j]), then (r0 + r2) and (r1 + r3), then their sum
-        const float up4 = __shfl_down_sync(0xffffffffu, l, 4, 8);
-        l = __fadd_rn(up4, l);
-        const float up2 = __shfl_down_sync(0xffffffffu, l, 2, 8);
-        l = __fadd_rn(l, up2);
-        const float up1 = __shfl_down_sync(0xffffffffu, l, 1, 8);
+        // lanes 0-7 hold accumulator 0, lanes 8-15 accumulator 1
+        float l = __fadd_rn(acc, __shfl_down_sync(0xffffffffu, acc, 8));
+        const float up4 = __shfl_down_sync(0xffffffffu, l, 4);
+        l = __fadd_rn(up4, l);  // r_j = l[j + 4] + l[j]
+        const float up2 = __shfl_down_sync(0xffffffffu, l, 2);
+        l = __fadd_rn(l, up2);  // (r0 + r2), (r1 + r3)
+        const float up1 = __shfl_down_sync(0xffffffffu, l, 1);
         l = __fadd_rn(l, up1);
-        if (j == 0 && r < rows) out[r] = l;
+        if (lane == 0) out[r] = l;
     }
 }
 
-__host__ __device__ constexpr size_t block_scaled_smem_bytes(size_t cols) { return 1280 + (cols / 32) * 4 + cols; }
+__host__ __device__ constexpr size_t block_scaled_smem_bytes(size_t cols) {
+    return ((kBsTableBytes + (cols / 32) * 4 + cols + 15) / 16) * 16 + static_cast<size_t>(kBsWarps) * kBsWarpScratch * 4;
+}
+// CTAs of a launch: eight rows per CTA at a time, a few CTAs per SM.
+inline int block_scaled_grid(size_t rows, int sm_count) {
+    const size_t want = (rows + kBsWarps - 1) / kBsWarps, cap = static_cast<size_t>(sm_count) * 3;
+    return static_cast<int>(want < cap ? want : cap);
+}
 
 }  // namespace qtb

@@ -537,7 +537,7 @@ int check_block_scaled(const quintrit_b200_matrix* m) {
     return QUINTRIT_OK;
 }
 int launch_block_scaled(const quintrit_b200_matrix* m) {
-    const int grid = static_cast<int>(std::min<size_t>((m->rows + 31) / 32, static_cast<size_t>(m->sm_count) * 8));
+    const int grid = block_scaled_grid(m->rows, m->sm_count);
     gemv_block_scaled_kernel<<<grid, kBsThreads, block_scaled_smem_bytes(m->cols)>>>(m->d_planar, m->d_wscales, m->d_act, m->d_as, m->rows, m->cols, m->d_outf);
     ++g_launches;
     QTB_CUDA(cudaGetLastError());
