@@ -90,3 +90,35 @@ def test_pack_planar_matches_the_oracle_and_rejects_bad_trits(oracle):
 
 def test_device_count_never_fails():
     assert q.device_count() >= 0
+
+
+def test_header_is_plain_c99_and_a_c_program_links(tmp_path):
+    """The boundary is a C ABI: the header must compile as C99 on its own, and a C program that calls into the library must
+    link against it (no C++ or CUDA types in the signatures)."""
+    import shutil
+    import subprocess
+
+    gcc = shutil.which("gcc")
+    if gcc is None:
+        pytest.skip("no C compiler")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    header = os.path.join(root, "include", "quintrit_b200.h")
+    subprocess.run([gcc, "-std=c99", "-Wall", "-Wextra", "-pedantic", "-Werror", "-fsyntax-only", "-x", "c", header], check=True)
+    src = tmp_path / "caller.c"
+    src.write_text(
+        '#include "quintrit_b200.h"\n#include <stdio.h>\n'
+        "int main(void) {\n"
+        "    uint32_t n = 0;\n"
+        "    quintrit_gpu_options_t o = {sizeof o, 0, 0, 0};\n"
+        "    quintrit_b200_decoder_t* d = NULL;\n"
+        "    int rc = quintrit_cuda_device_count(&n);\n"
+        '    if (quintrit_b200_decoder_open_gguf("no-such-file.gguf", &o, &d) != QUINTRIT_ERR_IO || d != NULL) return 2;\n'
+        "    if (quintrit_b200_planar_row_bytes(3072) != 640) return 3;\n"
+        '    printf("%s %u %d\\n", quintrit_b200_version(), (unsigned)n, rc);\n'
+        "    return 0;\n}\n")
+    exe = tmp_path / "caller"
+    libdir = os.path.dirname(q.library_path())
+    subprocess.run([gcc, "-std=c99", "-I", os.path.join(root, "include"), str(src), "-o", str(exe), "-L", libdir, "-lquintrit_b200",
+                    f"-Wl,-rpath,{libdir}"], check=True)
+    out = subprocess.run([str(exe)], check=True, capture_output=True, text=True)
+    assert out.stdout.split()[0] == q.version()
