@@ -519,33 +519,46 @@ __device__ __noinline__ void mega_scores_unit(const MegaArgs& a, const MegaLayer
     const bool has_cur = pos >= r0 && pos < r0 + rows;
     const int len_old = has_cur ? pos - r0 : rows;  // rows that come from the cache
     const __half* kbase = ly.kc + static_cast<size_t>(kvh) * hd + static_cast<size_t>(r0) * kvd;
-    __syncthreads();  // every thread is done with the table the block overlays
-    stage_rows(blk, kbase, 0, len_old, hd, kvd);
-    cp_async_commit();
-
     const bool live = s_in > 0.0f;
     const float pq = live ? __fdiv_rn(ly.ws[0], s_in) : 0.0f, pk = live ? __fdiv_rn(ly.ws[1], s_in) : 0.0f, pv = live ? __fdiv_rn(ly.ws[2], s_in) : 0.0f;
     const float* cs = a.cos_sin + static_cast<size_t>(pos) * a.rope_dims;
-    const int half = hd / 2;
-    // rotated, rescaled query heads (and the new key / value rows): all integer results are read before the first use
-    for (int idx = tid; idx < (gqa + (has_cur ? 1 : 0)) * half; idx += kMegaThreads) {
-        const int g = idx / half, p = idx - g * half;
-        const bool is_q = g < gqa;
-        // the two elements of pair p: (2p, 2p + 1), or with NEOX pairing (p, p + rope_dims / 2) inside the rotated part and
-        // plain neighbours behind it (ops.rs:160-221)
-        const int hr = a.rope_dims / 2;
-        int e0 = 2 * p, e1 = 2 * p + 1;
+    const int half = hd / 2, hr = a.rope_dims / 2;
+    const int n_pairs = (gqa + (has_cur ? 1 : 0)) * half;
+    // Pair idx of the rotated, rescaled query heads (and of the new key / value rows): head g, pair p. Its two elements are
+    // (2p, 2p + 1), or with NEOX pairing (p, p + rope_dims / 2) inside the rotated part and plain neighbours behind it
+    // (ops.rs:160-221).
+    struct Pair {
+        int g, p, e0, e1, i0, i1, j0, j1;
+    };
+    auto fetch = [&](int idx) {
+        Pair r;
+        r.g = idx / half, r.p = idx - r.g * half;
+        r.e0 = 2 * r.p, r.e1 = 2 * r.p + 1;
         if (a.neox) {
-            e0 = p < hr ? p : a.rope_dims + 2 * (p - hr);
-            e1 = p < hr ? p + hr : e0 + 1;
+            r.e0 = r.p < hr ? r.p : a.rope_dims + 2 * (r.p - hr);
+            r.e1 = r.p < hr ? r.p + hr : r.e0 + 1;
         }
-        const int base = is_q ? (kvh * gqa + g) * hd : qd + kvh * hd;
-        const int i0 = __ldcg(a.acc_qkv + base + e0), i1 = __ldcg(a.acc_qkv + base + e1);
-        int j0 = 0, j1 = 0;
+        const bool is_q = r.g < gqa;
+        const int base = is_q ? (kvh * gqa + r.g) * hd : qd + kvh * hd;
+        r.i0 = __ldcg(a.acc_qkv + base + r.e0), r.i1 = __ldcg(a.acc_qkv + base + r.e1);
+        r.j0 = 0, r.j1 = 0;
         if (!is_q) {
-            j0 = __ldcg(a.acc_qkv + base + kvd + e0);
-            j1 = __ldcg(a.acc_qkv + base + kvd + e1);
+            r.j0 = __ldcg(a.acc_qkv + base + kvd + r.e0);
+            r.j1 = __ldcg(a.acc_qkv + base + kvd + r.e1);
         }
+        return r;
+    };
+    // the integer results of this thread's first pair are requested before the key rows are staged (the copies below keep
+    // the load/store unit busy for most of a microsecond)
+    Pair first{};
+    if (tid < n_pairs) first = fetch(tid);
+    __syncthreads();  // every thread is done with the table the block overlays
+    stage_rows(blk, kbase, 0, len_old, hd, kvd);
+    cp_async_commit();
+    for (int idx = tid; idx < n_pairs; idx += kMegaThreads) {
+        const Pair pr = idx == tid ? first : fetch(idx);
+        const int g = pr.g, p = pr.p, e0 = pr.e0, e1 = pr.e1, i0 = pr.i0, i1 = pr.i1, j0 = pr.j0, j1 = pr.j1;
+        const bool is_q = g < gqa;
         const bool rot = p < hr;
         float c0 = 1.0f, sn = 0.0f;
         if (rot) {
@@ -702,12 +715,21 @@ __device__ __noinline__ void mega_values_unit(const MegaArgs& a, const MegaLayer
             s_moved[idx] = any ? 1 : 0;
         }
         __syncthreads();
-        if (tid < gqa) {  // backward scan: the chain runs branch-free from a group to the next one whose maximum moved
-            unsigned short nxt = static_cast<unsigned short>(ngroups);
-            s_next[tid * (ngroups + 1) + ngroups] = nxt;
-            for (int grp = ngroups - 1; grp >= 0; --grp) {
-                if (s_moved[tid * ngroups + grp]) nxt = static_cast<unsigned short>(grp);
-                s_next[tid * (ngroups + 1) + grp] = nxt;
+        // For every group the first group at or after it whose maximum moved (the chain runs branch-free up to there): a
+        // suffix minimum, one warp per head, 32 groups at a time from the end with the carry of the later groups.
+        for (int g = warp; g < gqa; g += kMegaWarps) {
+            int carry = ngroups;
+            if (lane == 0) s_next[g * (ngroups + 1) + ngroups] = static_cast<unsigned short>(ngroups);
+            for (int hi = ngroups; hi > 0; hi -= 32) {
+                const int grp = hi - 32 + lane;  // lanes cover [hi - 32, hi); lanes below 0 idle
+                int v = (grp >= 0 && s_moved[g * ngroups + grp]) ? grp : ngroups;
+                for (int o = 1; o < 32; o <<= 1) {
+                    const int t = __shfl_down_sync(0xffffffffu, v, o);
+                    if (lane + o < 32) v = min(v, t);
+                }
+                v = min(v, carry);
+                if (grp >= 0) s_next[g * (ngroups + 1) + grp] = static_cast<unsigned short>(v);
+                carry = __shfl_sync(0xffffffffu, v, max(0, 32 - hi));  // the lowest covered group's value
             }
         }
         __syncthreads();
@@ -903,29 +925,6 @@ __device__ __noinline__ bool phase_combine(const MegaArgs& a, int l, unsigned in
     const int tid = threadIdx.x, hd = a.head_dim, qd = a.q_heads * hd;
     float* s_pair = v.pair;
     const KvSplit ks = kv_split(a);
-    // per head: the factors of every chunk in the order of attention.rs:510-541. The running maximum before chunk c is
-    // the maximum of the earlier non-empty chunks, so the eight exponentials of a head are independent: one thread each.
-    if (!ks.split) {
-        if (tid < a.q_heads) {
-            const float S = __ldcg(a.part_ms + static_cast<size_t>(tid) * 8 + 1);
-            s_pair[tid * 8] = S == 0.0f ? 0.0f : __fdiv_rn(1.0f, S);
-        }
-    } else if (tid < a.q_heads * 8) {
-        const int h = tid >> 3, c = (tid >> 1) & 3, which = tid & 1;
-        float pm[8];
-#pragma unroll
-        for (int k = 0; k < 8; ++k) pm[k] = __ldcg(a.part_ms + static_cast<size_t>(h) * 8 + k);
-        float m_before = -INFINITY;
-#pragma unroll
-        for (int k = 0; k < 4; ++k)
-            if (k < c && pm[2 * k + 1] != 0.0f) m_before = fmaxf(m_before, pm[2 * k]);
-        const float m_chunk = pm[2 * c], s_chunk = pm[2 * c + 1];
-        const float m_new = fmaxf(m_before, m_chunk);
-        float f = device_expf(__fsub_rn(which == 0 ? m_before : m_chunk, m_new));
-        if (s_chunk == 0.0f) f = which == 0 ? -1.0f : 0.0f;  // a negative scale_old marks a skipped chunk
-        s_pair[h * 8 + 2 * c + which] = f;                    // [c][0] = scale_old, [c][1] = scale_new
-        if (which == 0) s_pair[a.q_heads * 8 + h * 4 + c] = s_chunk;
-    }
     // every chunk value of a thread's coordinates is requested before the factors are needed
     float amax = 0.0f;
     for (int base = 0; base < qd; base += 4 * kMegaThreads) {  // uniform trip count: the loop holds a barrier
@@ -939,7 +938,33 @@ __device__ __noinline__ bool phase_combine(const MegaArgs& a, int l, unsigned in
 #pragma unroll
             for (int c = 0; c < 4; ++c) pv[k][c] = (i < qd && (c == 0 || ks.split)) ? __ldcg(pa + c * hd) : 0.0f;
         }
-        if (base == 0) __syncthreads();  // the factors are written
+        if (base == 0) {
+            // Per head: the factors of every chunk in the order of attention.rs:510-541 (computed after the loads above were
+            // issued, so that the two round trips to L2 overlap). The running maximum before chunk c is the maximum of the
+            // earlier non-empty chunks, so the eight exponentials of a head are independent: one thread each.
+            if (!ks.split) {
+                if (tid < a.q_heads) {
+                    const float S = __ldcg(a.part_ms + static_cast<size_t>(tid) * 8 + 1);
+                    s_pair[tid * 8] = S == 0.0f ? 0.0f : __fdiv_rn(1.0f, S);
+                }
+            } else if (tid < a.q_heads * 8) {
+                const int h = tid >> 3, c = (tid >> 1) & 3, which = tid & 1;
+                float pm[8];
+#pragma unroll
+                for (int k = 0; k < 8; ++k) pm[k] = __ldcg(a.part_ms + static_cast<size_t>(h) * 8 + k);
+                float m_before = -INFINITY;
+#pragma unroll
+                for (int k = 0; k < 4; ++k)
+                    if (k < c && pm[2 * k + 1] != 0.0f) m_before = fmaxf(m_before, pm[2 * k]);
+                const float m_chunk = pm[2 * c], s_chunk = pm[2 * c + 1];
+                const float m_new = fmaxf(m_before, m_chunk);
+                float f = device_expf(__fsub_rn(which == 0 ? m_before : m_chunk, m_new));
+                if (s_chunk == 0.0f) f = which == 0 ? -1.0f : 0.0f;  // a negative scale_old marks a skipped chunk
+                s_pair[h * 8 + 2 * c + which] = f;                    // [c][0] = scale_old, [c][1] = scale_new
+                if (which == 0) s_pair[a.q_heads * 8 + h * 4 + c] = s_chunk;
+            }
+            __syncthreads();  // the factors are written
+        }
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
             const int i = i0 + k * kMegaThreads;
