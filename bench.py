@@ -353,7 +353,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
 
         import datetime
 
-        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=180))  # a rank that fell out does not hang the others forever
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=90))  # a rank that fell out does not hang the others forever
 
     # ---- build the sweep: weights generated on the device, transcoded by the library ----
     t_setup = time.time()
