@@ -160,7 +160,7 @@ def run_decode(args, local_rank: int):
     import quintrit_b200 as q
 
     dev = torch.device("cuda", local_rank)
-    ctx = (args.prompt + args.steps + 64 + 255) // 256 * 256
+    ctx = (max(args.prompt + args.steps + 64, args.parity_prompt + args.parity_new + 1) + 255) // 256 * 256
     t0 = time.time()
     spec = synth.torch_model(args.decode_shape, dev, ctx, layers=args.decode_layers)
     torch.cuda.empty_cache()
@@ -176,7 +176,7 @@ def run_decode(args, local_rank: int):
         import oracle
 
         ref = oracle.Model(spec)
-        npar, ngen = 6, 6
+        npar, ngen = args.parity_prompt, args.parity_new  # BASELINE's full check is 1024 + 512 (Falcon3) / 512 + 256 (BitNet): minutes of CPU
         tok = None
         t_cpu = time.time()
         for pos in range(npar):
@@ -521,6 +521,8 @@ def main():
     ap.add_argument("--decode-shape", default="falcon3_10b", choices=["falcon3_10b", "bitnet_2b"])
     ap.add_argument("--decode-layers", type=int, default=None, help="fewer layers than the shape has (experiments)")
     ap.add_argument("--prompt", type=int, default=1024, help="context length at which a decode step is timed")
+    ap.add_argument("--parity-prompt", type=int, default=6, help="prompt tokens of the greedy-token parity check against the CPU oracle")
+    ap.add_argument("--parity-new", type=int, default=6, help="greedy tokens compared in that check")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
