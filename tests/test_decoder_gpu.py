@@ -149,3 +149,14 @@ def test_one_kernel_per_step_path_stays_exact(oracle, monkeypatch, arch, f32_val
     dec2 = q.Decoder(spec)
     assert dec2.info()["single_kernel"] == 1
     dec2.free()
+
+
+@pytest.mark.parametrize("f32_values,head_dim,q_heads,kv_heads", [(False, 256, 3, 1), (True, 128, 4, 2)])
+def test_context_of_several_thousand_positions(oracle, f32_values, head_dim, q_heads, kv_heads):
+    """Chunks of more than a thousand positions: the staged key blocks take several rounds per CTA, the V slice of a chunk no
+    longer fits one copy group comfortably, the next-moved table spans more than 32 groups. Context 3584 (the reference caps
+    its GPU sessions at 7936, gpu.rs:141-146); logits are compared at a sample of positions and at the last one."""
+    hidden = q_heads * head_dim // 2 if head_dim == 256 else 256
+    spec = synth.make_model(q.ARCH_LLAMA, f32_values, hidden, 256, 1, q_heads, kv_heads, head_dim, 264, 3584, 10000.0, 1e-6, config=29, tied=True)
+    rng = np.random.default_rng(5)
+    _run(spec, rng.integers(0, 264, 3400), oracle, check_every=211)
