@@ -30,9 +30,9 @@ from quintrit_b200 import synth  # noqa: E402
 
 CONFIG_ID = 0
 BYTES_PER_WEIGHT = 0.2  # 1.60 bits per weight: the algorithmic bytes of a velurex GEMV
-# DRAM bytes per weight that ncu counted for gemv_lut_kernel (dram__bytes_read.sum + dram__bytes_write.sum of the 12-layer
-# capture summarised in profiles/gemv_lut_kernel_falcon3_12layer_sweep.md, divided by its 2 850 029 568 weights); traffic
-# grows in proportion to the weights streamed, so a launch's traffic is this figure times its weights.
+# DRAM bytes per weight that ncu counted for gemv_lut_kernel (dram__bytes_read.sum + dram__bytes_write.sum of a capture of
+# the 12-layer case, divided by its 2 850 029 568 weights); traffic grows in proportion to the weights streamed, so a
+# launch's traffic is this figure times its weights.
 NCU_TRAFFIC_BYTES_PER_WEIGHT = (590_314_496 + 4_031_488) / 2_850_029_568
 
 
@@ -122,34 +122,57 @@ class ClockSampler:
         return out
 
 
-def cpu_sweep(layers_sample: int, threads: int, reps: int = 9):
-    """Times the CPU restatement of the reference's AVX-512 kernel (oracle/cpu_gemv.c) on the first `layers_sample`
-    layers of the sweep: best of `reps` passes, averaged over two rounds with the second in reverse order
-    (the reference's method, docs/benchmarks.md:45-59). Returns (Gweights/s, results per projection, kind)."""
-    import oracle
+class CpuSweep:
+    """The sweep on the host cores: the CPU restatement of the reference's AVX-512 kernel (oracle/cpu_gemv.c) over the first
+    `layers` layers of the sweep in the 64-row tile layout. The weights come from the oracle library's threaded generator
+    (the same seeded stream as the GPU arm's)."""
 
-    probs = []
-    use512 = oracle.cpu_has_avx512_vbmi()
-    for (l, p, n, k) in sweep_shapes(layers_sample):
-        planar = synth.torch_planar(synth.seed_for(CONFIG_ID, l, p, 0), n, k, "cpu").numpy()
-        w = oracle.tile64(planar, n, k) if use512 else planar
-        probs.append((n, k, w, activations_for(l, p, k), np.zeros(n, np.int32)))
-    weights = sum(n * k for n, k, *_ in probs)
-    fn = oracle.cpu_gemv_avx512 if use512 else oracle.cpu_gemv_portable
+    def __init__(self, layers: int):
+        import oracle
 
-    def one_pass(order):
+        self.oracle = oracle
+        self.use512 = oracle.cpu_has_avx512_vbmi()
+        self.probs = []
+        for (l, p, n, k) in sweep_shapes(layers):
+            planar = oracle.synth_planar(synth.seed_for(CONFIG_ID, l, p, 0), n, k)
+            w = oracle.tile64(planar, n, k) if self.use512 else planar
+            self.probs.append((n, k, w, activations_for(l, p, k), np.zeros(n, np.int32)))
+        self.weights = sum(n * k for n, k, *_ in self.probs)
+        self.fn = oracle.cpu_gemv_avx512 if self.use512 else oracle.cpu_gemv_portable
+        self.isa = "avx512_vbmi" if self.use512 else "portable"
+
+    def one_pass(self, threads: int, reverse: bool = False) -> float:
+        order = range(len(self.probs) - 1, -1, -1) if reverse else range(len(self.probs))
         t0 = time.perf_counter()
         for i in order:
-            n, k, w, a, o = probs[i]
-            fn(w, n, k, a, threads, out=o)
+            n, k, w, a, o = self.probs[i]
+            self.fn(w, n, k, a, threads, out=o)
         return time.perf_counter() - t0
 
-    fwd = list(range(len(probs)))
-    one_pass(fwd)
-    best1 = min(one_pass(fwd) for _ in range(reps))
-    best2 = min(one_pass(fwd[::-1]) for _ in range(reps))
-    secs = 0.5 * (best1 + best2)
-    return weights / secs / 1e9, [p[4] for p in probs], ("avx512_vbmi" if use512 else "portable")
+    def best_of(self, threads: int, reps: int = 9) -> float:
+        """Gweights/s by the reference's method (docs/benchmarks.md:45-59): best of `reps` passes, averaged over two rounds
+        with the second in reverse order."""
+        self.one_pass(threads)
+        best1 = min(self.one_pass(threads) for _ in range(reps))
+        best2 = min(self.one_pass(threads, reverse=True) for _ in range(reps))
+        return self.weights / (0.5 * (best1 + best2)) / 1e9
+
+    def results(self):
+        return [p[4] for p in self.probs]
+
+
+def pin_to_all_cores():
+    """Keeps the process (and the OpenMP threads it starts) on the cores it may use, one thread per core, no migration
+    (the reference pins its pool with QUINTRIT_POOL_PIN=1). Must run before the oracle library is first used."""
+    os.environ.setdefault("OMP_PROC_BIND", "close")
+    os.environ.setdefault("OMP_PLACES", "cores")
+    return len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+
+
+def sweep_config(layers: int, world: int, weights_total: int) -> dict:
+    """The `config` object of the sweep line; both arms print the same one."""
+    return {"workload": "falcon3_10b_gemv_sweep", "layers": layers, "projections": 7 * layers, "batch": 1, "weights": weights_total,
+            "l2": "inputs (1.9 GB of weights per pass) exceed L2", "sharding": f"rows/{world}, no collective"}
 
 
 def run_decode(args, local_rank: int):
@@ -176,7 +199,7 @@ def run_decode(args, local_rank: int):
         import oracle
 
         ref = oracle.Model(spec)
-        npar, ngen = args.parity_prompt, args.parity_new  # BASELINE's full check is 1024 + 512 (Falcon3) / 512 + 256 (BitNet): minutes of CPU
+        npar, ngen = args.parity_prompt, args.parity_new  # the full-length sequences are checked against committed fixtures by --parity-full
         tok = None
         t_cpu = time.time()
         for pos in range(npar):
@@ -311,30 +334,61 @@ def run_block_scaled(args, local_rank: int):
     return out
 
 
+def cpu_decode(shape: str, layers, prompt_len: int, tail: int = 32):
+    """The CPU oracle's whole-token decode on the host cores: the seeded prompt is ingested token by token (the reference
+    ingests prompts this way, engine.rs:626-631) and the time per token is the mean over the last `tail` positions, i.e. at
+    a context of about `prompt_len` tokens. A restatement of the reference's CPU path, not its binary."""
+    import oracle
+
+    ctx = (prompt_len + 255) // 256 * 256
+    spec = oracle.full_model(shape, "i2_s", ctx, layers=layers)
+    m = oracle.Model(spec)
+    prompt = synth.prompt_tokens(synth.full_dims(shape)["config"], prompt_len, spec["vocab"])
+    times = []
+    for pos, tok in enumerate(prompt):
+        t0 = time.perf_counter()
+        m.forward(int(tok), pos)
+        times.append(time.perf_counter() - t0)
+    ms = 1e3 * sum(times[-tail:]) / min(tail, len(times))
+    return {"shape": shape, "layers": spec["layers"], "context": prompt_len, "tokens_per_s": round(1e3 / ms, 2), "ms_per_token": round(ms, 2),
+            "method": f"mean over the last {min(tail, len(times))} of {prompt_len} prompt positions, all host threads", "kind": "port"}
+
+
 def run_reference(args, rank: int, world: int):
-    """--impl reference: the CPU path, timed on the host cores (rank 0 only)."""
+    """--impl reference: the reference's CPU path for the same workload on the host cores (rank 0 only): every step is one
+    pass over all projections of the sweep with all host threads. The reference is Rust and cannot be built where this
+    runs, so the kernel is its C restatement (kind "port")."""
     if rank != 0:
         return
-    threads = os.cpu_count() or 1
-    sample_layers = min(args.layers, 2)
-    steps = max(1, args.steps)
-    vals = []
-    kind = "port"
-    for _ in range(min(steps, 3)):
-        g, _, isa = cpu_sweep(sample_layers, threads, reps=3)
-        vals.append(g)
-    value = max(vals)
-    weights_sample = sum(n * k for _, _, n, k in sweep_shapes(sample_layers))
+    threads = pin_to_all_cores()
+    sweep = CpuSweep(args.layers)
+    for _ in range(max(3, args.warmup)):
+        sweep.one_pass(threads)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        sweep.one_pass(threads)
+    ms_per_step = (time.perf_counter() - t0) * 1e3 / args.steps
+    value = sweep.weights / (ms_per_step * 1e-3) / 1e9
+    by_threads = {str(t): round(sweep.best_of(t), 2) for t in sorted({1, min(4, threads), threads})}
+    ceiling = sweep.oracle.stream_read_gbs(1 << 30, threads, 21)
     line = {
         "impl": "reference", "metric": "gemv_gweights_per_s", "value": round(value, 2), "unit": "Gweights/s", "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(weights_sample / value / 1e6, 3), "higher_is_better": True,
+        "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": round(ms_per_step, 3), "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "int8xternary->int32", "data": "synthetic",
-        "config": {"workload": "falcon3_10b_gemv_sweep", "layers": args.layers, "projections": 7 * args.layers, "batch": 1},
-        "cpu_baseline": {"value": round(value, 2), "unit": "Gweights/s", "cores": threads, "kind": kind,
-                         "sample": f"first {sample_layers} of {args.layers} layers ({weights_sample / 1e6:.0f} M weights), {isa} kernel, "
-                                   "best of 3 passes averaged over forward and reverse order"},
+        "config": sweep_config(args.layers, args.gpus, sweep.weights),
+        "cpu_baseline": {"value": round(value, 2), "unit": "Gweights/s", "cores": threads, "kind": "port",
+                         "sample": f"all {7 * args.layers} projections ({sweep.weights / 1e9:.2f} G weights) per step, {sweep.isa} kernel, threads pinned",
+                         "best_of_9_fwd_rev_gweights_per_s_by_threads": by_threads,
+                         "host_read_ceiling_gbs": round(ceiling, 1),
+                         "share_of_read_ceiling": round(by_threads[str(threads)] * BYTES_PER_WEIGHT / ceiling, 3) if ceiling > 0 else None},
         "e2e": {"value": round(value, 2), "unit": "Gweights/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
+    if args.gpus == 1 and not args.no_decode:
+        del sweep
+        try:
+            line["decode"] = cpu_decode(args.decode_shape, args.decode_layers, args.prompt)
+        except Exception as e:  # the sweep line must still be printed
+            line["decode"] = {"error": f"{type(e).__name__}: {e}"}
     print(json.dumps(line), flush=True)
 
 
@@ -391,9 +445,20 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     for _ in range(max(3, args.warmup)):
         plan.launch(stream)
     barrier()
+    # Warm-up continues for about a second of back-to-back passes, so that the K timed steps that follow without a gap run
+    # at the clocks of sustained serving (a cold burst of a few milliseconds runs above them) and the clock samples of this
+    # window describe the state the steps were timed in.
+    sampler.mark_begin()
+    t_heat = time.time()
+    heat_steps = 0
+    while time.time() - t_heat < args.preheat:
+        for _ in range(100):
+            plan.launch(stream)
+        heat_steps += 100
+        torch.cuda.synchronize()
+    barrier()
     q.launch_count(reset=True)
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
-    sampler.mark_begin()
     ev[0].record()
     for i in range(args.steps):
         plan.launch(stream)
@@ -403,10 +468,8 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     launches = q.launch_count()
     total_ms = ev[0].elapsed_time(ev[-1])
     per_launch_ms = [ev[i].elapsed_time(ev[i + 1]) for i in range(args.steps)]
-    timed_wall = sampler.t1 - sampler.t0
 
-    # A second, untimed-by-contract phase of at least a second of back-to-back passes: the sustained rate under the
-    # power cap, and the clock samples when the timed region was too short for nvidia-smi to land one inside it.
+    # A further second of back-to-back passes, timed as one block: the long-run rate beside the K-step figure.
     sus0, sus1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t_sus = time.time()
     sus_steps = 0
@@ -419,12 +482,8 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     sus1.record()
     torch.cuda.synchronize()
     sustained_ms = sus0.elapsed_time(sus1) / sus_steps
-    clock_window = "timed_region"
-    if timed_wall < 0.3:
-        sampler.t0, clock_window = t_sus, "sustained_phase_after_timed_region"
-        sampler.mark_end()
     clocks = sampler.stop()
-    clocks["window"] = clock_window
+    clocks["window"] = f"{heat_steps} warm-up passes ({args.preheat:g} s) followed without a gap by the {args.steps} timed steps"
 
     # ---- end to end through the C ABI with host buffers: H2D activations, kernel, D2H results, every step ----
     for _ in range(2):
@@ -468,12 +527,12 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         "metric": "gemv_gweights_per_s", "value": round(value, 1), "unit": "Gweights/s", "n_gpus": world, "steps": args.steps,
         "warmup": max(3, args.warmup), "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "int8xternary->int32", "data": "synthetic",
-        "config": {"workload": "falcon3_10b_gemv_sweep", "layers": args.layers, "projections": 7 * args.layers, "batch": 1,
-                   "weights": weights_total, "l2": "inputs (1.9 GB of weights per pass) exceed L2", "sharding": f"rows/{world}, no collective"},
+        "config": sweep_config(args.layers, world, weights_total),
         "tokens_per_s_gemv_only": round(1e3 / ms_per_step, 1),
         "roofline_nominal_8tbs_frac": round(weights_total * BYTES_PER_WEIGHT / (ms_per_step * 1e-3) / (world * 8e12), 4),
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 4),
-                     "traffic": int(weights_local * NCU_TRAFFIC_BYTES_PER_WEIGHT), "traffic_source": "ncu capture of the 12-layer case, scaled by weights", "peak_kind": peak_kind, "kernel": "gemv_lut_kernel", "launch_ms": round(kernel_ms, 4)},
+                     "traffic": int(weights_local * NCU_TRAFFIC_BYTES_PER_WEIGHT), "traffic_source": "ncu capture of the 12-layer case, scaled by weights", "peak_kind": peak_kind, "kernel": "gemv_lut_kernel", "launch_ms": round(kernel_ms, 4),
+                     "launch_ms_median": round(statistics.median(per_launch_ms), 4)},
         "e2e": {"value": round(e2e_value, 1), "unit": "Gweights/s", "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes,
                 "ms_per_step": round(e2e_ms / args.steps, 4)},
         "sustained": {"value": round(weights_total / (sustained_ms * 1e-3) / 1e9, 1), "unit": "Gweights/s", "ms_per_step": round(sustained_ms, 4),
@@ -493,15 +552,15 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         except Exception as e:  # the sweep line must still be printed
             line["decode"] = {"error": f"{type(e).__name__}: {e}"}
     if world == 1 and not args.no_cpu:
-        threads = os.cpu_count() or 1
-        sample_layers = min(args.layers, 2)
-        g, cpu_out, isa = cpu_sweep(sample_layers, threads, reps=5)
+        threads = pin_to_all_cores()
+        sweep = CpuSweep(args.layers)
+        g = sweep.best_of(threads, reps=5)
         res = [first[o:o + n] for o, (_, _, n, _) in zip(out_offsets, shapes)]
-        n_check = len(sweep_shapes(sample_layers))
-        parity = all(np.array_equal(res[i], cpu_out[i]) for i in range(n_check))
+        parity = all(np.array_equal(r, c) for r, c in zip(res, sweep.results()))
         line["cpu_baseline"] = {"value": round(g, 2), "unit": "Gweights/s", "cores": threads, "kind": "port",
-                                "sample": f"first {sample_layers} of {args.layers} layers, {isa} kernel, best of 5 passes averaged over forward and reverse order"}
-        line["parity_vs_cpu"] = {"projections_checked": n_check, "bit_exact": bool(parity)}
+                                "sample": f"all {7 * args.layers} projections ({sweep.weights / 1e9:.2f} G weights) per pass, {sweep.isa} kernel, best of 5 passes averaged over forward and reverse order"}
+        line["parity_vs_cpu"] = {"projections_checked": len(res), "bit_exact": bool(parity)}
+        del sweep
     print(json.dumps(line), flush=True)
     if dist is not None:
         dist.destroy_process_group()
@@ -515,6 +574,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=40)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--preheat", type=float, default=1.0, help="seconds of untimed back-to-back passes right before the timed steps")
     ap.add_argument("--no-decode", action="store_true", help="skip the whole-token decode leg")
     ap.add_argument("--decode-only", action="store_true", help="run only the whole-token decode leg and print its object (profiling aid)")
     ap.add_argument("--block-scaled-only", action="store_true", help="run only the block-scaled (Q2_0) projection on the model's shapes (profiling aid)")

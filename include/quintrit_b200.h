@@ -152,8 +152,12 @@ int quintrit_b200_gemv_i32_device(const quintrit_b200_matrix_t* matrix, const in
  * the model shapes of this project comes near). All calls on one GPU share the one array: the array keeps the last
  * call's contents, the words that must start at zero are cleared by every call, and two calls that overlap on the GPU
  * (different streams, or threads) race - issue them in one stream or order them yourself. The first call on a device
- * looks up the array's device address and measures the shared-memory base with a tiny kernel and a 4-byte read-back;
- * make that first call outside any stream capture.
+ * looks up the array's device address and measures the shared-memory base with a tiny kernel and a 4-byte read-back
+ * (under a lock, so first calls from several host threads are safe); make that first call outside any stream capture.
+ * Because the call never waits, it does not read back the kernel's status word (the kernel's check that its table sits
+ * at the measured shared-memory base): the kernel instantiation was chosen from that measurement at set-up, and a
+ * mismatch, which would leave d_out all zero, is reported only by the entry points that wait (quintrit_b200_gemv_i32).
+ * The 4096-item limit is a guard: with cols <= 131072 no shape reaches it on a 148-multiprocessor device.
  */
 int quintrit_b200_gemv_i32_noalloc(const quintrit_b200_matrix_t* matrix, const int8_t* d_activations, int32_t* d_out, void* stream);
 
@@ -316,6 +320,16 @@ int quintrit_b200_decoder_time_token(quintrit_b200_decoder_t* decoder, uint32_t 
  * phases). *out_count receives the number of values (also on QUINTRIT_ERR_BUFFER_TOO_SMALL).
  */
 int quintrit_b200_decoder_trace_step(quintrit_b200_decoder_t* decoder, uint64_t* out_ns, size_t capacity, size_t* out_count);
+
+/*
+ * Self-test of the bounded grid barrier of the single-kernel decode path (failure detection, no counterpart in the
+ * reference, which has no device-side waits): `ctas` CTAs, all resident, wait at the barrier for an arrival that cannot
+ * come, with `spin_limit` polls of patience (1..2^20). The wait runs out, the kernel sets its status word and the failure
+ * bit releases every other waiter; nothing faults and nothing spins beyond the limit. Returns QUINTRIT_ERR_DEVICE with
+ * the message a decoder gives for the same condition; *out_released receives the number of CTAs that left through the
+ * failure path (expected: ctas). The device stays usable.
+ */
+int quintrit_b200_selftest_barrier(uint32_t device_index, uint32_t ctas, uint32_t spin_limit, uint32_t* out_released);
 
 /* Kernel launches issued by this library on the calling thread since the last call with reset != 0 (counting aid). */
 uint64_t quintrit_b200_launch_count(int reset);

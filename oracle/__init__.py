@@ -75,6 +75,11 @@ def _declare(l: C.CDLL) -> None:
     l.qto_cpu_gemv_avx512.restype = C.c_int
     l.qto_cpu_gemv_avx512.argtypes = [_u8p, _sz, _sz, _i8p, _i32p, C.c_int]
     l.qto_cpu_gemv_portable.argtypes = [_u8p, _sz, _sz, _i8p, _i32p, C.c_int]
+    l.qto_synth_planar.argtypes = [C.c_uint64, _sz, _sz, _sz, _u8p]
+    l.qto_synth_table.argtypes = [C.c_uint64, _sz, _sz, C.c_int, C.POINTER(C.c_uint16)]
+    l.qto_synth_block_scales.argtypes = [C.c_uint64, _sz, _sz, _f32p]
+    l.qto_stream_read_gbs.restype = C.c_double
+    l.qto_stream_read_gbs.argtypes = [_u8p, _sz, C.c_int, C.c_int, C.POINTER(C.c_uint64)]
 
 
 def _p(a: np.ndarray, t):
@@ -133,6 +138,61 @@ def tile32(planar, rows: int, cols: int) -> np.ndarray:
     out = np.zeros(rows * tile_row_bytes(cols), np.uint8)
     lib().qto_tile32(_p(p, _u8p), rows, cols, _p(out, _u8p))
     return out
+
+
+def synth_planar(seed: int, rows: int, cols: int, row0: int = 0) -> np.ndarray:
+    """Planar bytes of rows [row0, row0 + rows) of the seeded synthetic matrix (quintrit_b200.synth.trits + pack), threaded."""
+    out = np.zeros(rows * planar_row_bytes(cols), np.uint8)
+    lib().qto_synth_planar(seed & 0xFFFFFFFFFFFFFFFF, rows, cols, row0, _p(out, _u8p))
+    return out
+
+
+def synth_table(seed: int, n: int, bf16: bool = False, start: int = 0) -> np.ndarray:
+    """quintrit_b200.synth.table_bits_np, threaded."""
+    out = np.zeros(n, np.uint16)
+    lib().qto_synth_table(seed & 0xFFFFFFFFFFFFFFFF, n, start, int(bf16), out.ctypes.data_as(C.POINTER(C.c_uint16)))
+    return out
+
+
+def synth_block_scales(seed: int, n: int, start: int = 0) -> np.ndarray:
+    """quintrit_b200.synth.block_scales_np, threaded."""
+    out = np.zeros(n, np.float32)
+    lib().qto_synth_block_scales(seed & 0xFFFFFFFFFFFFFFFF, n, start, _p(out, _f32p))
+    return out
+
+
+def stream_read_gbs(nbytes: int = 1 << 30, threads: int = 0, reps: int = 21) -> float:
+    """Read-only streaming rate of the host cores over a buffer of `nbytes` (GB/s, best of `reps`)."""
+    buf = np.ones(nbytes, np.uint8)
+    sink = C.c_uint64(0)
+    return float(lib().qto_stream_read_gbs(_p(buf, _u8p), buf.size, threads or (os.cpu_count() or 1), reps, C.byref(sink)))
+
+
+def full_model(shape: str, variant: str, ctx: int, bf16_tables: bool = False, layers: int | None = None) -> dict:
+    """quintrit_b200.synth.full_model built by the threaded generators of this library (the same values: tests/test_synth.py)."""
+    from quintrit_b200 import synth
+
+    d = synth.full_dims(shape, layers)
+    config, H = d["config"], d["hidden"]
+    weights, scales, norms, block_scales = [], [], [], []
+    for l in range(d["layers"]):
+        for p, (rows, cols) in enumerate(d["shapes"]):
+            weights.append(synth_planar(synth.seed_for(config, l, p, 0), rows, cols))
+            scales.append(synth.full_scale(config, l, p, variant))
+            if variant == "q2_0":
+                block_scales.append(synth_block_scales(synth.seed_for(config, l, p, 1), rows * cols // 64))
+        qd = d["q_heads"] * d["head_dim"]
+        norms += [np.ones(H, np.float32), np.ones(H, np.float32), np.ones(qd, np.float32) if d["arch"] == 1 else None,
+                  np.ones(d["inter"], np.float32) if d["arch"] == 1 else None]
+    embed = synth_table(synth.seed_for(config, 255, 0, 0), d["vocab"] * H, bf16_tables)
+    head = None if d["tied"] else synth_table(synth.seed_for(config, 255, 1, 0), d["vocab"] * H, bf16_tables)
+    spec = dict(arch=d["arch"], f32_values=variant != "i2_s", hidden=H, inter=d["inter"], layers=d["layers"], q_heads=d["q_heads"], kv_heads=d["kv_heads"],
+                head_dim=d["head_dim"], vocab=d["vocab"], ctx=ctx, rope_dims=d["rope_dims"], eps=d["eps"], rope_theta=d["rope_theta"], weights=weights,
+                scales=np.array(scales, np.float32), norms=norms, embed=embed, lm_head=head, out_norm=np.ones(H, np.float32), shape=shape,
+                bf16_tables=bf16_tables)
+    if variant == "q2_0":
+        spec["block_scales"] = block_scales
+    return spec
 
 
 # ---- GEMV ----------------------------------------------------------------------------------------------------------
@@ -313,6 +373,8 @@ def _declare_model(l: C.CDLL) -> None:
     l.qto_block_scaled_dot_trits.restype = C.c_float
     l.qto_block_scaled_dot_trits.argtypes = [_i8p, _f32p, _i8p, _f32p, _sz]
     l.qto_gemv_block_scaled.argtypes = [_u8p, _f32p, _i8p, _f32p, _sz, _sz, _f32p]
+    l.qto_fast_enable.argtypes = [C.c_int]
+    l.qto_fast_available.restype = C.c_int
 
 
 _model_declared = False

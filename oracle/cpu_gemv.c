@@ -199,3 +199,34 @@ void qto_cpu_gemv_portable(const uint8_t* planar, size_t rows, size_t cols, cons
         qto_gemv_planar(planar + (size_t)r0 * qto_planar_row_bytes(cols), n, cols, act, out + r0);
     }
 }
+
+/* Read-only streaming rate of the host in GB/s: every thread sums its share of `bytes` bytes with 64-bit loads, best of
+ * `reps` passes (the reference measures its memory ceiling the same way: a 1 GiB buffer read 21 times,
+ * docs/benchmarks.md:144-146). The sum is returned through *sink so that the loads cannot be dropped. */
+double qto_stream_read_gbs(const uint8_t* buf, size_t bytes, int threads, int reps, uint64_t* sink) {
+    double best = 0.0;
+    uint64_t total = 0;
+    const size_t words = bytes / 8;
+    for (int r = 0; r < reps; ++r) {
+        uint64_t sum = 0;
+#ifdef _OPENMP
+        const double t0 = omp_get_wtime();
+#pragma omp parallel for schedule(static) reduction(+ : sum) num_threads(threads)
+#endif
+        for (long c = 0; c < (long)(words / 512); ++c) {
+            const uint64_t* p = (const uint64_t*)buf + (size_t)c * 512;
+            uint64_t s0 = 0, s1 = 0, s2 = 0, s3 = 0;
+            for (int i = 0; i < 512; i += 4) s0 += p[i], s1 += p[i + 1], s2 += p[i + 2], s3 += p[i + 3];
+            sum += (s0 + s1) + (s2 + s3);
+        }
+#ifdef _OPENMP
+        const double dt = omp_get_wtime() - t0;
+        if (dt > 0.0 && (double)bytes / dt / 1e9 > best) best = (double)bytes / dt / 1e9;
+#else
+        (void)threads;
+#endif
+        total += sum;
+    }
+    if (sink) *sink = total;
+    return best;
+}

@@ -402,3 +402,66 @@ int qto_uniform_block_scale(int ggml_type, const uint8_t* data, size_t data_len,
     *scale = qto_half_to_f32(first);
     return 1;
 }
+
+/* ---- seeded synthetic weights (benchmark and fixture input, not part of the reference) ----------------------------
+ * The counter-based SplitMix64 stream of quintrit_b200/synth.py (the numpy code there is the definition;
+ * tests/test_synth.py holds this copy to it): value i = mix(seed + (i + 1) * GAMMA), u = its high 32 bits,
+ * u < 0.3 * 2^32 -> -1, u < 0.6 * 2^32 -> +1, else 0. Writes rows [row0, row0 + rows) of the rows x cols matrix as planar
+ * velurex bytes; threaded over rows so that the 9.5 G weights of a Falcon3-10B-shape model take seconds on the host. */
+static inline uint32_t synth_u32(uint64_t seed, uint64_t i) {
+    uint64_t z = seed + (i + 1) * 0x9E3779B97F4A7C15ull;
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    z = z ^ (z >> 31);
+    return (uint32_t)(z >> 32);
+}
+
+void qto_synth_planar(uint64_t seed, size_t rows, size_t cols, size_t row0, uint8_t* out) {
+    const size_t bpr = (cols + QTO_BLOCK_TRITS - 1) / QTO_BLOCK_TRITS;
+#pragma omp parallel for schedule(static)
+    for (long rr = 0; rr < (long)rows; ++rr) {
+        const size_t r = (size_t)rr;
+        uint8_t* dst = out + r * bpr * QTO_BLOCK_BYTES;
+        const uint64_t base = (uint64_t)(row0 + r) * cols;
+        for (size_t b = 0; b < bpr; ++b)
+            for (size_t j = 0; j < QTO_BLOCK_BYTES; ++j) {
+                int8_t t[5];
+                for (size_t p = 0; p < 5; ++p) {
+                    const size_t c = b * QTO_BLOCK_TRITS + p * QTO_BLOCK_BYTES + j;
+                    int8_t v = 0;
+                    if (c < cols) {
+                        const uint32_t u = synth_u32(seed, base + c);
+                        v = u < 1288490188u ? -1 : (u < 2576980377u ? 1 : 0);
+                    }
+                    t[p] = v;
+                }
+                dst[b * QTO_BLOCK_BYTES + j] = qto_pack_5trits(t);
+            }
+    }
+}
+
+uint16_t qto_f32_to_f16(float f);
+uint16_t qto_f32_to_bf16(float f);
+
+/* Dense-table values of quintrit_b200/synth.py (table_bits_np is the definition): (u0 + u1 + u2 + u3 - 2^33) * gain with
+ * four consecutive uniforms, one double multiply, rounded to float and then to F16 or BF16 bit patterns. */
+void qto_synth_table(uint64_t seed, size_t n, size_t start, int bf16, uint16_t* out) {
+    const double gain = 0.02 * 1.7320508075688772 / 4294967296.0;
+#pragma omp parallel for schedule(static)
+    for (long ii = 0; ii < (long)n; ++ii) {
+        const uint64_t i = (uint64_t)ii + start;
+        const int64_t s = (int64_t)synth_u32(seed, 4 * i) + synth_u32(seed, 4 * i + 1) + synth_u32(seed, 4 * i + 2) + synth_u32(seed, 4 * i + 3);
+        const float x = (float)((double)(s - ((int64_t)1 << 33)) * gain);
+        out[ii] = bf16 ? qto_f32_to_bf16(x) : qto_f32_to_f16(x);
+    }
+}
+
+/* Q2_0 block scales of quintrit_b200/synth.py (block_scales_np): 0.5 + 1.5 u / 2^32, to float, to F16 and back. */
+float qto_f16_to_f32(uint16_t h);
+void qto_synth_block_scales(uint64_t seed, size_t n, size_t start, float* out) {
+#pragma omp parallel for schedule(static)
+    for (long ii = 0; ii < (long)n; ++ii) {
+        const double v = 0.5 + 1.5 * (double)synth_u32(seed, (uint64_t)ii + start) / 4294967296.0;
+        out[ii] = qto_f16_to_f32(qto_f32_to_f16((float)v));
+    }
+}

@@ -80,6 +80,9 @@ int qto_uniform_block_scale(int ggml_type, const uint8_t* data, size_t data_len,
 /* decoders/mod.rs:85-118 half_to_f32. */
 float qto_half_to_f32(uint16_t h);
 
+/* Seeded synthetic ternary matrix (the stream of quintrit_b200/synth.py) as planar bytes, rows [row0, row0 + rows). */
+void qto_synth_planar(uint64_t seed, size_t rows, size_t cols, size_t row0, uint8_t* out);
+
 /* ---- timed CPU baseline (oracle/cpu_gemv.c) ---- */
 
 /*

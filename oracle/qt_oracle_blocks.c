@@ -17,6 +17,9 @@
 
 uint16_t qto_f32_to_f16(float f);
 float qto_f16_to_f32(uint16_t h);
+int qto_fast_available(void);
+float qto_fast_block_scaled_dot_row(const uint8_t* row, const float* w_scales, const int8_t* acts, const int16_t* act_pairs, const float* a_scales,
+                                    size_t cols);
 
 /* rust/crates/quintrit-runtime/src/ops.rs:898-910 (quantize_q8_0_scalar): per block of 32 values amax (NaN ignored),
  * d = f16(amax / 127) returned as f32, codes round_ties_even(x * (127 / amax)) clamped to [-128, 127]; NaN gives 0. */
@@ -93,6 +96,15 @@ float qto_block_scaled_dot_trits(const int8_t* trits, const float* w_scales, con
 void qto_gemv_block_scaled(const uint8_t* planar, const float* w_scales, const int8_t* acts, const float* a_scales, size_t rows, size_t cols,
                            float* out) {
     const size_t rb = qto_planar_row_bytes(cols), sb = cols / 64;
+    if (qto_fast_available() && cols % 32 == 0) { /* the same lanes, eight at a time (qt_oracle_fast.c) */
+        int16_t* pairs = (int16_t*)malloc(cols / 2 * sizeof(int16_t) + 64);
+        for (size_t k = 0; k < cols / 2; ++k) pairs[k] = (int16_t)((int)acts[2 * k] + (int)acts[2 * k + 1]);
+#pragma omp parallel for schedule(static)
+        for (long r = 0; r < (long)rows; ++r)
+            out[r] = qto_fast_block_scaled_dot_row(planar + (size_t)r * rb, w_scales + (size_t)r * sb, acts, pairs, a_scales, cols);
+        free(pairs);
+        return;
+    }
 #pragma omp parallel for schedule(static)
     for (long r = 0; r < (long)rows; ++r) out[r] = qto_block_scaled_dot_row(planar + (size_t)r * rb, w_scales + (size_t)r * sb, acts, a_scales, cols);
 }

@@ -17,6 +17,16 @@
 #include <omp.h>
 #endif
 
+/* AVX2 + FMA + F16C forms of the inner loops (qt_oracle_fast.c): the same lanes, eight at a time. */
+int qto_fast_available(void);
+void qto_fast_dot_f16_groups(const uint16_t* x, const uint16_t* y, size_t n32, float acc[4][8]);
+void qto_fast_dot_f16_f32_groups(const uint16_t* x, const float* y, size_t n32, float acc[4][8]);
+void qto_fast_dot_bf16_groups(const uint16_t* x, const uint16_t* y, size_t n32, float acc[4][8]);
+void qto_fast_mad_f16(uint16_t* y, const uint16_t* x, size_t n8, float v);
+void qto_fast_scale_f16(uint16_t* y, size_t n8, float v);
+void qto_fast_mad_f16_f32(float* acc, const uint16_t* x, size_t n8, float v);
+void qto_fast_scale_f32(float* acc, size_t n8, float v);
+
 /* ---- half / bfloat conversions ---------------------------------------------------------------------------------- */
 
 float qto_f16_to_f32(uint16_t h) { return qto_half_to_f32(h); } /* ops.rs:512-539 (exact) */
@@ -108,6 +118,10 @@ float qto_vec_dot_f16(const uint16_t* x, const uint16_t* y, size_t n) {
     float acc[4][8];
     memset(acc, 0, sizeof acc);
     size_t i = 0;
+    if (qto_fast_available()) {
+        i = n / 32 * 32;
+        qto_fast_dot_f16_groups(x, y, i, acc);
+    }
     for (; i + 32 <= n; i += 32)
         for (int j = 0; j < 4; ++j)
             for (int l = 0; l < 8; ++l) {
@@ -131,6 +145,10 @@ float qto_vec_dot_f16_f32(const uint16_t* x, const float* y, size_t n) {
     float acc[4][8];
     memset(acc, 0, sizeof acc);
     size_t i = 0;
+    if (qto_fast_available()) {
+        i = n / 32 * 32;
+        qto_fast_dot_f16_f32_groups(x, y, i, acc);
+    }
     for (; i + 32 <= n; i += 32)
         for (int j = 0; j < 4; ++j)
             for (int l = 0; l < 8; ++l) {
@@ -264,6 +282,10 @@ float qto_expf_restated(float x) {
 
 static void vec_mad_f16(uint16_t* y, const uint16_t* x, size_t n, float v) {
     size_t i = 0;
+    if (qto_fast_available()) {
+        i = n / 32 * 32;
+        qto_fast_mad_f16(y, x, i, v);
+    }
     for (; i + 32 <= n; i += 32)
         for (size_t l = 0; l < 32; ++l) y[i + l] = qto_f32_to_f16(fmaf(qto_f16_to_f32(x[i + l]), v, qto_f16_to_f32(y[i + l])));
     for (; i < n; ++i) {
@@ -272,7 +294,12 @@ static void vec_mad_f16(uint16_t* y, const uint16_t* x, size_t n, float v) {
     }
 }
 static void vec_scale_f16(uint16_t* y, size_t n, float v) {
-    for (size_t i = 0; i < n; ++i) y[i] = qto_f32_to_f16(qto_f16_to_f32(y[i]) * v);
+    size_t i = 0;
+    if (qto_fast_available()) {
+        i = n / 8 * 8;
+        qto_fast_scale_f16(y, i, v);
+    }
+    for (; i < n; ++i) y[i] = qto_f32_to_f16(qto_f16_to_f32(y[i]) * v);
 }
 
 /* attention.rs:438-469 attend_range: online softmax over [p0, p1) with an F16 accumulator. K and V rows are `stride`
@@ -311,11 +338,21 @@ static void attend_range_f32(const float* q, const uint16_t* k, const uint16_t* 
         if (score > max_score) {
             max_score = score;
             ms = expf(m_old - max_score);
-            for (size_t d = 0; d < hd; ++d) vkq[d] *= ms;
+            size_t d = 0;
+            if (qto_fast_available()) {
+                d = hd / 8 * 8;
+                qto_fast_scale_f32(vkq, d, ms);
+            }
+            for (; d < hd; ++d) vkq[d] *= ms;
         } else {
             vs = expf(score - max_score);
         }
-        for (size_t d = 0; d < hd; ++d) vkq[d] = fmaf(qto_f16_to_f32(v[p * stride + d]), vs, vkq[d]);
+        size_t d = 0;
+        if (qto_fast_available()) {
+            d = hd / 8 * 8;
+            qto_fast_mad_f16_f32(vkq, v + p * stride, d, vs);
+        }
+        for (; d < hd; ++d) vkq[d] = fmaf(qto_f16_to_f32(v[p * stride + d]), vs, vkq[d]);
         s_sum = fmaf(s_sum, ms, vs);
     }
     *m_out = max_score;
@@ -393,6 +430,10 @@ void qto_attend_head(const float* q, const uint16_t* k, const uint16_t* v, size_
 float qto_vec_dot_bf16(const uint16_t* x, const uint16_t* y, size_t n) {
     float acc[4][8] = {{0}};
     size_t i = 0;
+    if (qto_fast_available()) {
+        i = n / 32 * 32;
+        qto_fast_dot_bf16_groups(x, y, i, acc);
+    }
     for (; i + 32 <= n; i += 32)
         for (int j = 0; j < 4; ++j)
             for (int l = 0; l < 8; ++l) {
@@ -546,8 +587,9 @@ void qto_model_forward(qto_model_t* m, uint32_t token, size_t pos, float* logits
             vc[pos * kvd + i] = qto_f32_to_f16(v[i]);
         }
         const size_t gqa = (size_t)(m->q_heads / m->kv_heads);
-        for (size_t h = 0; h < (size_t)m->q_heads; ++h) {
-            const size_t kvh = h / gqa;
+#pragma omp parallel for schedule(dynamic, 1) /* heads are independent (attention.rs:205-232) */
+        for (long hh = 0; hh < (long)m->q_heads; ++hh) {
+            const size_t h = (size_t)hh, kvh = h / gqa;
             qto_attend_head(q + h * hd, kc + kvh * hd, vc + kvh * hd, kvd, pos + 1, (size_t)m->ctx, hd, scale, m->f32_values, att + h * hd);
         }
         const float* o_in = att;

@@ -21,11 +21,13 @@ from .api import (  # noqa: F401
     device_count,
     device_info,
     gguf_describe,
+    last_selftest_released,
     launch_count,
     library_path,
     load_library,
     pack_planar,
     quantize_q8_0,
     row_bytes,
+    selftest_barrier,
     version,
 )

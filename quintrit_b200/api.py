@@ -121,6 +121,7 @@ def load_library(build_if_missing: bool = True) -> C.CDLL:
     l.quintrit_b200_decoder_generate.argtypes = [C.c_void_p, C.POINTER(C.c_uint32), _sz, _sz, C.POINTER(C.c_uint32), _sz]
     l.quintrit_b200_decoder_time_token.argtypes = [C.c_void_p, C.c_uint32, C.c_uint32, C.POINTER(C.c_float)]
     l.quintrit_b200_decoder_trace_step.argtypes = [C.c_void_p, C.POINTER(C.c_uint64), _sz, C.POINTER(_sz)]
+    l.quintrit_b200_selftest_barrier.argtypes = [C.c_uint32, C.c_uint32, C.c_uint32, C.POINTER(C.c_uint32)]
     l.quintrit_b200_launch_count.restype = C.c_uint64
     l.quintrit_b200_launch_count.argtypes = [C.c_int]
     _lib = l
@@ -156,6 +157,24 @@ def device_info(index: int = 0) -> DeviceInfo:
 
 def launch_count(reset: bool = False) -> int:
     return int(load_library().quintrit_b200_launch_count(1 if reset else 0))
+
+
+_selftest_released = 0
+
+
+def selftest_barrier(device: int = 0, ctas: int = 4, spin_limit: int = 5000) -> int:
+    """Runs the barrier's give-up self-test (quintrit_b200_selftest_barrier). The expected outcome is a QuintritError with
+    code 15; the number of CTAs the failure released is kept for last_selftest_released()."""
+    global _selftest_released
+    n = C.c_uint32(0)
+    rc = load_library().quintrit_b200_selftest_barrier(device, ctas, spin_limit, C.byref(n))
+    _selftest_released = n.value
+    _check(rc)
+    return n.value
+
+
+def last_selftest_released() -> int:
+    return _selftest_released
 
 
 def row_bytes(cols: int) -> int:

@@ -4,6 +4,7 @@
 // rust/crates/quintrit-cuda/src/{device.rs,gemv.rs,pack.rs} and rust/crates/quintrit-c/src/cuda.rs.
 #include <algorithm>
 #include <cstdlib>
+#include <mutex>
 #include <new>
 #include <vector>
 
@@ -123,7 +124,9 @@ using GemvKernel = void (*)(const GemvItem*, int, const int8_t*, int32_t*, unsig
 // dynamic shared memory (measured once per device with smem_base_kernel).
 int gemv_kernel_for_device(int dev, GemvKernel* out) {
     static GemvKernel chosen[64] = {};
+    static std::mutex lock;  // first calls on a device from several host threads must not race on the cache
     if (dev < 0 || dev >= 64) return fail(QUINTRIT_ERR_DEVICE, "device index %d out of range", dev);
+    std::lock_guard<std::mutex> hold(lock);
     if (chosen[dev] == nullptr) {
         unsigned int* d_base = nullptr;
         unsigned int base = 0xFFFFFFFFu;
@@ -1072,7 +1075,7 @@ int mega_setup(quintrit_b200_decoder* d, const quintrit_b200_decoder_desc_t* des
     a.tp_wait_ns = kTpWaitLimitNs;
     if (const char* ms = std::getenv("QUINTRIT_B200_TP_WAIT_MS")) {  // shorter or longer patience with a silent peer, in milliseconds
         const long v = std::strtol(ms, nullptr, 10);
-        if (v >= 1 && v <= 600000) a.tp_wait_ns = static_cast<unsigned long long>(v) * 1000000ull;
+        if (v >= 1 && v <= 10000) a.tp_wait_ns = static_cast<unsigned long long>(v) * 1000000ull;
     }
     for (int p = 0; p < 8; ++p) a.tp_box[p] = nullptr;
     a.tp_box[d->tp_rank] = d->tp_box;
@@ -1114,13 +1117,22 @@ int decoder_step(quintrit_b200_decoder* d) {
     return QUINTRIT_OK;
 }
 
+// The status word of the decode kernel as an error of the C ABI.
+int kernel_status_error(unsigned int flag) {
+    if (flag == 3) return fail(QUINTRIT_ERR_DEVICE, "the decode kernel on the CUDA device gave up waiting for another rank of the tensor-parallel group");
+    if (flag == 2) return fail(QUINTRIT_ERR_DEVICE, "the decode kernel on the CUDA device gave up waiting at a grid barrier");
+    if (flag != 0) return fail(QUINTRIT_ERR_DEVICE, "a kernel on the CUDA device found its shared-memory table at an unexpected address");
+    return QUINTRIT_OK;
+}
+
 int decoder_check_status(quintrit_b200_decoder* d) {
     unsigned int flag = 0;
     QTB_CUDA(cudaMemcpyAsync(&flag, d->d_counters + 2, sizeof flag, cudaMemcpyDeviceToHost, d->stream));
     QTB_CUDA(cudaStreamSynchronize(d->stream));
-    if (flag == 3) return fail(QUINTRIT_ERR_DEVICE, "the decode kernel on the CUDA device gave up waiting for another rank of the tensor-parallel group");
-    if (flag == 2) return fail(QUINTRIT_ERR_DEVICE, "the decode kernel on the CUDA device gave up waiting at a grid barrier");
-    if (flag != 0) return fail(QUINTRIT_ERR_DEVICE, "a kernel on the CUDA device found its shared-memory table at an unexpected address");
+    if (flag != 0) {  // the word is sticky on the device: clear it so that the decoder stays usable after the error
+        cudaMemsetAsync(d->d_counters + 2, 0, sizeof(unsigned int), d->stream);
+        return kernel_status_error(flag);
+    }
     return QUINTRIT_OK;
 }
 
@@ -1663,6 +1675,7 @@ struct NoAllocDevice {
     GemvKernel kernel = nullptr;
 };
 NoAllocDevice g_noalloc[64];
+std::mutex g_noalloc_lock;  // two host threads may make the first call on a device at the same time
 
 // Per-device set-up, run by the first call on that device (with that device current): the device address of the
 // static array, and the kernel instantiation that matches this device's shared-memory base. Allocates nothing: the
@@ -1670,6 +1683,7 @@ NoAllocDevice g_noalloc[64];
 int noalloc_setup(int dev, NoAllocDevice** out) {
     if (dev < 0 || dev >= 64) return fail(QUINTRIT_ERR_DEVICE, "device index %d out of range", dev);
     NoAllocDevice& s = g_noalloc[dev];
+    std::lock_guard<std::mutex> hold(g_noalloc_lock);
     if (!s.ready) {
         unsigned char* ptr = nullptr;
         // In host code the array's name is only a handle for the symbol; the address a kernel can use comes from here.
@@ -1729,6 +1743,37 @@ extern "C" int quintrit_b200_gemv_i32_noalloc(const quintrit_b200_matrix_t* matr
         ++g_launches;
         QTB_CUDA(cudaGetLastError());
         return ok();
+    });
+}
+
+// Runs the barrier self-test kernel: `ctas` co-resident CTAs (at most one per multiprocessor) wait for an arrival that
+// never comes, with `spin_limit` polls of patience. Expected outcome: QUINTRIT_ERR_DEVICE ("gave up waiting at a grid
+// barrier") and *out_released == ctas, i.e. every CTA saw the failure at both of its barriers and returned.
+extern "C" int quintrit_b200_selftest_barrier(uint32_t device_index, uint32_t ctas, uint32_t spin_limit, uint32_t* out_released) {
+    return guard([&]() -> int {
+        if (out_released == nullptr) return fail(QUINTRIT_ERR_NULL_POINTER, "out_released is NULL");
+        *out_released = 0;
+        cudaDeviceProp prop;
+        int rc = require_b200(static_cast<int>(device_index), &prop);
+        if (rc != QUINTRIT_OK) return rc;
+        if (ctas == 0 || ctas > static_cast<uint32_t>(prop.multiProcessorCount)) return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "ctas must be 1..%d (every CTA has to be resident)", prop.multiProcessorCount);
+        if (spin_limit == 0 || spin_limit > (1u << 20)) return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "spin_limit must be 1..2^20 polls");
+        DeviceGuard g(static_cast<int>(device_index));
+        unsigned int* d_words = nullptr;  // [0] barrier counter, [1] status, [2..] one flag per CTA
+        QTB_CUDA(cudaMalloc(&d_words, (2 + ctas) * sizeof(unsigned int)));
+        cudaError_t e = cudaMemset(d_words, 0, (2 + ctas) * sizeof(unsigned int));
+        if (e == cudaSuccess) {
+            barrier_selftest_kernel<<<ctas, 128>>>(d_words, d_words + 1, spin_limit, d_words + 2);
+            ++g_launches;
+            e = cudaGetLastError();
+        }
+        std::vector<unsigned int> host(2 + ctas, 0u);
+        if (e == cudaSuccess) e = cudaMemcpy(host.data(), d_words, host.size() * sizeof(unsigned int), cudaMemcpyDeviceToHost);
+        cudaFree(d_words);
+        if (e != cudaSuccess) return cuda_fail(e, "barrier self-test");
+        for (uint32_t i = 0; i < ctas; ++i) *out_released += host[2 + i];
+        rc = kernel_status_error(host[1]);
+        return rc == QUINTRIT_OK ? ok() : rc;
     });
 }
 

@@ -101,16 +101,19 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
 
 // Grid-wide barrier with a bounded wait. Returns false (in every thread of the CTA) if it gave up or if any thread of the
 // grid reported a failure. The barrier counter doubles as the failure signal: whoever gives up (here or in an exchange
-// between GPUs) adds kBarFail to it, which releases every waiter at once and is recognised by its size, so the polling
-// loop reads one word only. The host clears the counter before every launch; legitimate targets stay far below kBarFail.
+// between GPUs) sets the bit kBarFail in it, which releases every waiter at once and is recognised by its size, so the
+// polling loop reads one word only. Setting a bit is idempotent: however many threads report, the flag stays set (an add
+// per reporting thread would wrap the word back to a legitimate count once 4 x 2^30 has been added). The host clears the
+// counter before every launch; legitimate counts stay far below kBarFail, so arrivals after a failure leave the bit alone.
 constexpr unsigned int kBarFail = 1u << 30;
 
 __device__ __forceinline__ void report_failure(unsigned int* bar, unsigned int* status, unsigned int code) {
     atomicMax(status, code);
-    atomicAdd(bar, kBarFail);
+    atomicOr(bar, kBarFail);
 }
 
-__device__ __forceinline__ bool grid_barrier(unsigned int* bar, unsigned int target, unsigned int* status, int* s_flag) {
+__device__ __forceinline__ bool grid_barrier(unsigned int* bar, unsigned int target, unsigned int* status, int* s_flag,
+                                             unsigned int spin_limit = kBarrierSpinLimit) {
     __syncthreads();
     if (threadIdx.x == 0) {
         __threadfence();
@@ -124,7 +127,7 @@ __device__ __forceinline__ bool grid_barrier(unsigned int* bar, unsigned int tar
                 break;
             }
             if (v >= target) break;
-            if (spins > kBarrierSpinLimit) {
+            if (spins > spin_limit) {
                 report_failure(bar, status, 2u);
                 okay = 0;
                 break;
@@ -149,18 +152,21 @@ __device__ __forceinline__ void ll_store(uint2* p, uint32_t value, uint32_t seq)
     asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(value), "r"(seq) : "memory");
 }
 
-// Value of a pair once it carries `seq`. Bounded: after MegaArgs::tp_wait_ns the kernel's status becomes 3, the failure is
-// signalled through the barrier counter (the next grid barrier ends the kernel) and 0 is returned.
+// Value of a pair once it carries `seq`. Bounded: after MegaArgs::tp_wait_ns the kernel's status becomes 3, the failure
+// bit of the barrier counter is set (the next grid barrier ends the kernel) and 0 is returned. Once the bit is set, by this
+// thread or any other, every later wait of the launch returns at once: a kernel whose peer is silent runs out its patience
+// once, not once per exchange.
 __device__ __forceinline__ uint32_t ll_load(const uint2* p, uint32_t seq, const MegaArgs& a) {
     uint32_t value, got;
     unsigned long long t0 = 0;
     for (unsigned int spins = 0;; ++spins) {
         asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(value), "=r"(got) : "l"(p) : "memory");
         if (got == seq) return value;
-        if ((spins & 255u) == 255u) {
+        if ((spins & 63u) == 63u) {
+            if (*reinterpret_cast<volatile unsigned int*>(a.bar) >= kBarFail) return 0u;  // somebody gave up already
             const unsigned long long now = global_timer_ns();
             if (t0 == 0) t0 = now;
-            if (now - t0 > a.tp_wait_ns || *reinterpret_cast<volatile unsigned int*>(a.bar) >= kBarFail) {
+            if (now - t0 > a.tp_wait_ns) {
                 report_failure(a.bar, a.status, 3u);
                 return 0u;
             }
@@ -1362,6 +1368,17 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const __g
 #undef MEGA_GEMV
 #undef MEGA_BARRIER
 #undef MEGA_TRACE
+}
+
+// Self-test of the barrier's give-up path (quintrit_b200_selftest_barrier): a few CTAs, all resident, wait at a barrier
+// whose target is one arrival more than the grid can deliver, with a short poll limit. The wait runs out, status becomes
+// 2, the failure bit releases the other waiters, and a second barrier returns false at once. out[cta] = 1 for every CTA
+// whose two barriers both reported the failure. Nothing faults and nothing spins beyond the limit.
+__global__ void barrier_selftest_kernel(unsigned int* bar, unsigned int* status, unsigned int spin_limit, unsigned int* out) {
+    __shared__ int s_flag;
+    const bool first = grid_barrier(bar, gridDim.x + 1u, status, &s_flag, spin_limit);
+    const bool second = grid_barrier(bar, 2u * gridDim.x + 2u, status, &s_flag, spin_limit);
+    if (threadIdx.x == 0) out[blockIdx.x] = (!first && !second) ? 1u : 0u;
 }
 
 }  // namespace qtb

@@ -20,6 +20,9 @@ M2 = 0x94D049BB133111EB
 T_NEG = int(0.3 * 2 ** 32)
 T_POS = int(0.6 * 2 ** 32)
 PROJECTIONS = ("q", "k", "v", "o", "gate", "up", "down")
+# Packer used by make_model: None = the library's own quintrit_b200_pack_planar. The test suite installs the CPU oracle's
+# independent packer here, so that the bytes the oracle decodes in decoder tests were not produced by the code under test.
+PACKER = None
 
 
 def falcon3_10b_shapes():
@@ -136,7 +139,7 @@ def make_model(arch: int, f32_values: bool, hidden: int, inter: int, layers: int
 
     for l in range(layers):
         for p, (rows, cols) in enumerate(shapes):
-            weights.append(api.pack_planar(trits(seed_for(config, l, p, 0), rows * cols), rows, cols))
+            weights.append((PACKER or api.pack_planar)(trits(seed_for(config, l, p, 0), rows * cols), rows, cols))
             scales.append(weight_scale(seed_for(config, l, p, 1)))
         norms += [norm(seed_for(config, l, 7, 0), hidden), norm(seed_for(config, l, 7, 1), hidden),
                   norm(seed_for(config, l, 7, 2), qd) if arch == 1 else None, norm(seed_for(config, l, 7, 3), inter) if arch == 1 else None]
@@ -231,3 +234,118 @@ def shard_spec(spec: dict, rank: int, world: int) -> dict:
         v = spec["vocab"] // world
         out["lm_head"] = np.ascontiguousarray(np.asarray(spec["lm_head"], np.uint16).reshape(spec["vocab"], H)[rank * v:(rank + 1) * v]).reshape(-1)
     return out
+
+
+# ---- full-size models whose every value is the same on any machine --------------------------------------------------
+# The sequences of the full-size parity fixtures are computed on one machine (CPU) and checked on another (GPU box), so
+# nothing in these models may depend on a libm or on a device's float kernels: trits and scales come from integer
+# arithmetic and single IEEE operations, and the dense tables replace Box-Muller by a sum of four uniforms.
+
+TABLE_STD = 0.02
+_TABLE_GAIN = TABLE_STD * 1.7320508075688772 / 4294967296.0  # sum of four U[0, 2^32): mean 2^33, standard deviation 2^32 / sqrt(3)
+
+
+def _bits_from_f32(x, bf16: bool):
+    """F16 or BF16 (round to nearest even) bit patterns of a float32 numpy array."""
+    if not bf16:
+        return x.astype(np.float16).view(np.uint16)
+    u = x.view(np.uint32)
+    return ((u + (np.uint32(0x7FFF) + ((u >> np.uint32(16)) & np.uint32(1)))) >> np.uint32(16)).astype(np.uint16)
+
+
+def table_bits_np(seed: int, n: int, bf16: bool = False, start: int = 0) -> np.ndarray:
+    """Values ``start .. start + n`` of a dense table: (u0 + u1 + u2 + u3 - 2^33) * gain with four consecutive uniforms
+    of the stream, one float64 multiply (exact inputs), rounded to float32 and then to F16 / BF16. Bell-shaped with
+    standard deviation 0.02; identical on every IEEE machine (numpy definition)."""
+    u = splitmix_u32(seed, 4 * start, 4 * n).astype(np.int64).reshape(n, 4).sum(axis=1)
+    x = ((u - (1 << 33)).astype(np.float64) * _TABLE_GAIN).astype(np.float32)
+    return _bits_from_f32(x, bf16)
+
+
+def torch_table_bits(seed: int, n: int, bf16: bool, device, chunk: int = 1 << 23) -> np.ndarray:
+    """table_bits_np computed on a torch device (same integers, same single multiply)."""
+    import torch
+
+    out = np.empty(n, np.uint16)
+    for s0 in range(0, n, chunk):
+        m = min(chunk, n - s0)
+        u = torch_splitmix_u32(seed, 4 * s0, 4 * m, device).view(m, 4).sum(dim=1)
+        x = ((u - (1 << 33)).to(torch.float64) * _TABLE_GAIN).to(torch.float32)
+        h = x.to(torch.bfloat16 if bf16 else torch.float16).view(torch.int16)
+        out[s0:s0 + m] = h.cpu().numpy().view(np.uint16)
+    return out
+
+
+def block_scales_np(seed: int, n: int, start: int = 0) -> np.ndarray:
+    """Q2_0 block scales: 0.5 + 1.5 u / 2^32 (exact in float64), rounded to float32 and to F16; returned as float32."""
+    u = splitmix_u32(seed, start, n).astype(np.float64)
+    return (0.5 + 1.5 * u / 4294967296.0).astype(np.float32).astype(np.float16).astype(np.float32)
+
+
+def torch_block_scales(seed: int, n: int, device, chunk: int = 1 << 24) -> np.ndarray:
+    import torch
+
+    out = np.empty(n, np.float32)
+    for s0 in range(0, n, chunk):
+        m = min(chunk, n - s0)
+        u = torch_splitmix_u32(seed, s0, m, device).to(torch.float64)
+        out[s0:s0 + m] = (0.5 + 1.5 * u / 4294967296.0).to(torch.float32).to(torch.float16).to(torch.float32).cpu().numpy()
+    return out
+
+
+def torch_digits(seed: int, rows: int, cols: int, device, row0: int = 0):
+    """Digits trit + 1 (uint8 tensor [rows, cols]) of the seeded ternary matrix."""
+    import torch
+
+    u = torch_splitmix_u32(seed, row0 * cols, rows * cols, device).view(rows, cols)
+    return torch.where(u < T_NEG, 0, torch.where(u < T_POS, 2, 1)).to(torch.uint8)
+
+
+FULL_SHAPES = {
+    # arch, hidden, inter, layers, q heads, kv heads, head_dim, vocab, rope theta, eps, tied head, seed field, GGUF architecture, name
+    "falcon3_10b": (0, 3072, 23040, 40, 12, 4, 256, 131072, 1000042.0, 1e-6, False, 2, "llama", "falcon3-10b-shape"),
+    "bitnet_2b": (1, 2560, 6912, 30, 20, 5, 128, 128256, 500000.0, 1e-5, True, 1, "bitnet-b1.58", "bitnet-2b-shape"),
+}
+
+
+def full_dims(shape: str, layers: int | None = None) -> dict:
+    arch, hidden, inter, L, qh, kvh, hd, vocab, theta, eps, tied, config, gguf_arch, name = FULL_SHAPES[shape]
+    L = layers or L
+    qd, kvd = qh * hd, kvh * hd
+    return dict(arch=arch, hidden=hidden, inter=inter, layers=L, q_heads=qh, kv_heads=kvh, head_dim=hd, vocab=vocab, rope_theta=theta, eps=eps,
+                tied=tied, config=config, gguf_arch=gguf_arch, name=name, rope_dims=hd,
+                shapes=[(qd, hidden), (kvd, hidden), (kvd, hidden), (hidden, qd), (inter, hidden), (inter, hidden), (hidden, inter)])
+
+
+def full_scale(config: int, layer: int, projection: int, variant: str) -> np.float32:
+    """Tensor scale of a projection: U(0.5, 2) in float32; the TQ encodings store it as the F16 of every block, so their
+    variant rounds it to F16 (a Q2_0 model has block scales instead and ignores it)."""
+    s = weight_scale(seed_for(config, layer, projection, 1))
+    return np.float32(np.float16(s)) if variant == "tq" else s
+
+
+def full_model(shape: str, variant: str, device, ctx: int, bf16_tables: bool = False, layers: int | None = None) -> dict:
+    """The named full-size model as numpy arrays for a decoder description (planar velurex projections), every value
+    machine-independent. variant: "i2_s" (float32 tensor scales, FP16-accumulator attention), "tq" (F16-exact tensor
+    scales, FP32 accumulators) or "q2_0" (one F16 scale per 64 weights, FP32 accumulators)."""
+    d = full_dims(shape, layers)
+    config, H = d["config"], d["hidden"]
+    weights, scales, norms, block_scales = [], [], [], []
+    for l in range(d["layers"]):
+        for p, (rows, cols) in enumerate(d["shapes"]):
+            weights.append(torch_planar(seed_for(config, l, p, 0), rows, cols, device).cpu().numpy().reshape(-1))
+            scales.append(full_scale(config, l, p, variant))
+            if variant == "q2_0":
+                block_scales.append(torch_block_scales(seed_for(config, l, p, 1), rows * cols // 64, device))
+        qd = d["q_heads"] * d["head_dim"]
+        norms += [np.ones(H, np.float32), np.ones(H, np.float32), np.ones(qd, np.float32) if d["arch"] == 1 else None,
+                  np.ones(d["inter"], np.float32) if d["arch"] == 1 else None]
+    embed = torch_table_bits(seed_for(config, 255, 0, 0), d["vocab"] * H, bf16_tables, device)
+    head = None if d["tied"] else torch_table_bits(seed_for(config, 255, 1, 0), d["vocab"] * H, bf16_tables, device)
+    spec = dict(arch=d["arch"], f32_values=variant != "i2_s", hidden=H, inter=d["inter"], layers=d["layers"], q_heads=d["q_heads"], kv_heads=d["kv_heads"],
+                head_dim=d["head_dim"], vocab=d["vocab"], ctx=ctx, rope_dims=d["rope_dims"], eps=d["eps"], rope_theta=d["rope_theta"], weights=weights,
+                scales=np.array(scales, np.float32), norms=norms, embed=embed, lm_head=head, out_norm=np.ones(H, np.float32), shape=shape,
+                bf16_tables=bf16_tables)
+    if variant == "q2_0":
+        spec["block_scales"] = block_scales
+    return spec

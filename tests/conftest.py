@@ -18,3 +18,14 @@ def oracle():
 
     o.lib()
     return o
+
+
+@pytest.fixture(autouse=True, scope="session")
+def _oracle_packs_the_test_models():
+    """Synthetic models of the tests are packed by the oracle's packer, not by the library under test."""
+    import oracle as o
+    from quintrit_b200 import synth
+
+    synth.PACKER = o.pack_planar
+    yield
+    synth.PACKER = None

@@ -35,3 +35,28 @@ def test_distributions():
     x = synth.normal_f32(synth.seed_for(0, 0, 0, 2), 100000)
     assert abs(x.mean()) < 0.02 and abs(x.std() - 1.0) < 0.02 and np.isfinite(x).all()
     assert len({synth.seed_for(0, l, p, s) for l in range(40) for p in range(7) for s in range(3)}) == 840
+
+
+def test_the_oracle_generator_equals_the_numpy_definition(oracle):
+    for seed, rows, cols, row0 in [(synth.seed_for(2, 3, 4, 0), 33, 161, 0), (synth.seed_for(0, 0, 6, 0), 7, 3072, 5), (1, 2, 23040, 1)]:
+        want = oracle.pack_planar(synth.trits(seed, rows * cols, start=row0 * cols), rows, cols)
+        assert np.array_equal(oracle.synth_planar(seed, rows, cols, row0), want)
+
+
+def test_portable_tables_and_block_scales():
+    a = synth.table_bits_np(123, 4096, False)
+    assert np.array_equal(a, synth.torch_table_bits(123, 4096, False, "cpu"))
+    x = a.view(np.float16).astype(np.float32)
+    assert abs(x.std() - 0.02) < 0.002 and abs(x.mean()) < 0.002
+    b = synth.table_bits_np(123, 100, True, start=50)
+    assert np.array_equal(b, synth.torch_table_bits(123, 150, True, "cpu")[50:])
+    s = synth.block_scales_np(9, 1000)
+    assert np.array_equal(s, synth.torch_block_scales(9, 1000, "cpu"))
+    assert s.min() >= 0.5 and s.max() <= 2.0 and np.array_equal(s.astype(np.float16).astype(np.float32), s)
+
+
+def test_the_oracle_table_generators_equal_the_numpy_definitions(oracle):
+    for bf16 in (False, True):
+        assert np.array_equal(oracle.synth_table(77, 5000, bf16, start=3), synth.table_bits_np(77, 5000, bf16, start=3))
+    assert np.array_equal(oracle.synth_block_scales(78, 3000, start=11), synth.block_scales_np(78, 3000, start=11))
+    assert oracle.stream_read_gbs(1 << 24, reps=3) > 0.1

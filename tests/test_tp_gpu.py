@@ -94,9 +94,16 @@ def test_a_silent_rank_ends_in_an_error_not_in_a_hang(monkeypatch):
     group = [q.Decoder(synth.shard_spec(spec, r, 2), device=0) for r in range(2)]
     for d in group:
         d.tp_attach_local(group)
+    import time
+
+    group[1].info()  # nothing of rank 1 ever launches
+    t0 = time.perf_counter()
     with pytest.raises(q.QuintritError) as e:
         group[0].forward(1, 0)
+    elapsed = time.perf_counter() - t0
     assert e.value.code == 15 and "another rank" in str(e.value)
+    # the patience runs out ONCE: after the first wait gave up, every later exchange of the launch returns at once
+    assert elapsed < 0.6, f"the kernel took {elapsed:.2f} s to give up with 0.2 s of patience"
     for d in group:
         d.free()
     # the device still works: a decoder of the whole model gives the oracle's logits
@@ -111,3 +118,17 @@ def test_a_silent_rank_ends_in_an_error_not_in_a_hang(monkeypatch):
         lone.tp_attach_local([lone])
     assert e.value.code == 2
     lone.free()
+
+
+def test_a_grid_barrier_that_cannot_complete_gives_up():
+    """The barrier's give-up path, made to run out without a fault or a hang: four resident CTAs wait for a fifth arrival
+    with 5000 polls of patience. Status 2 comes back as QUINTRIT_ERR_DEVICE, every CTA was released by the failure bit and
+    saw it again at its next barrier, and the device keeps working."""
+    import quintrit_b200 as q
+
+    with pytest.raises(q.QuintritError) as e:
+        q.selftest_barrier(0, ctas=4, spin_limit=5000)
+    assert e.value.code == 15 and "grid barrier" in str(e.value)
+    assert q.last_selftest_released() == 4
+    m = q.Matrix(np.full(32 * 32, 125, np.uint8), 32, 160)
+    assert not m.gemv_i32(np.ones(160, np.int8)).any()
