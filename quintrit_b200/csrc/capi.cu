@@ -966,9 +966,16 @@ int decoder_create_impl(const quintrit_b200_decoder_desc_t* desc, quintrit_b200_
     // the single-kernel path stages KV rows with a piece permutation that needs a power-of-two head_dim of at least 64
     // and one values unit of the longest chunk must fit the shared memory of an SM next to the activation vectors
     const int gqa_n = d->q_heads / d->kv_heads;
-    const size_t mega_bytes = mega_smem_bytes(mega_attn_region(d->ctx, gqa_n, hd), static_cast<int>(std::max<size_t>(H, qd_full)), static_cast<int>(H), static_cast<int>(L));
     int smem_optin = 0;
     QTB_CUDA(cudaDeviceGetAttribute(&smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, d->device));
+    // the second form of the attention's second half (units that take all chunks of 8 coordinates) where its arrays fit
+    d->attn_v2 = tp_world == 1 && d->ctx <= static_cast<uint32_t>(kV2MaxCtx) && gqa_n <= kV2MaxGqa && qd_full <= size_t(kNormPer) * kMegaThreads && hd % kV2Dims == 0;
+    if (const char* v2 = std::getenv("QUINTRIT_B200_ATTN_V2")) d->attn_v2 = d->attn_v2 && v2[0] != '0';  // experiments: "0" keeps the first form
+    auto bytes_for = [&](bool v2) {
+        return mega_smem_bytes(mega_attn_region(d->ctx, gqa_n, hd, v2), static_cast<int>(std::max<size_t>(H, qd_full)), static_cast<int>(H), static_cast<int>(L));
+    };
+    if (d->attn_v2 && bytes_for(true) > static_cast<size_t>(smem_optin)) d->attn_v2 = false;
+    const size_t mega_bytes = bytes_for(d->attn_v2);
     const bool staged_ok = hd >= 64 && (hd & (hd - 1)) == 0 && gqa_n <= 16 && mega_bytes <= static_cast<size_t>(smem_optin);
     if (staged_ok && d->q_heads <= kMegaMaxHeads && !(mode && std::strcmp(mode, "kernels") == 0)) {
         if ((rc = mega_setup(d, desc)) != QUINTRIT_OK) return rc;
@@ -1023,8 +1030,8 @@ int mega_setup(quintrit_b200_decoder* d, const quintrit_b200_decoder_desc_t* des
     if ((rc = dev_alloc(d, &d->xa, H)) != QUINTRIT_OK || (rc = dev_alloc(d, &d->xb, H)) != QUINTRIT_OK ||
         (rc = dev_alloc(d, &d->v_inter, I)) != QUINTRIT_OK || (rc = dev_alloc(d, &d->amax_bits, 4)) != QUINTRIT_OK ||
         (rc = dev_alloc(d, &d->best_val, d->sm_count)) != QUINTRIT_OK || (rc = dev_alloc(d, &d->best_idx, d->sm_count)) != QUINTRIT_OK ||
-        (rc = dev_alloc(d, &d->bar, 4)) != QUINTRIT_OK || (rc = dev_alloc(d, &d->trace, size_t(L) * 14 + 4 + 32)) != QUINTRIT_OK ||
-        (rc = dev_alloc(d, &d->scores, size_t(d->q_heads) * d->ctx)) != QUINTRIT_OK)
+        (rc = dev_alloc(d, &d->bar, 16)) != QUINTRIT_OK || (rc = dev_alloc(d, &d->trace, size_t(L) * 14 + 4 + 32 + 2)) != QUINTRIT_OK ||
+        (rc = dev_alloc(d, &d->scores, size_t(d->q_heads) * d->ctx)) != QUINTRIT_OK || (rc = dev_alloc(d, &d->attn_out, size_t(qd))) != QUINTRIT_OK)
         return rc;
     std::vector<GemvItem> items;
     std::vector<MegaLayer> layers(L);
@@ -1048,6 +1055,10 @@ int mega_setup(quintrit_b200_decoder* d, const quintrit_b200_decoder_desc_t* des
         for (int k = 0; k < 7; ++k) ly.ws[k] = d->scales[l * 7 + k];
         ly.kc = d->kc + size_t(l) * d->ctx * kvd;
         ly.vc = d->vc + size_t(l) * d->ctx * kvd;
+        for (int k = 0; k < 7; ++k) {
+            ly.wbase[k] = reinterpret_cast<const unsigned char*>(m[k]->d_w);
+            ly.wbytes[k] = static_cast<unsigned int>(m[k]->w_bytes);
+        }
     }
     GemvItem* d_items = nullptr;
     MegaLayer* d_layers = nullptr;
@@ -1062,8 +1073,11 @@ int mega_setup(quintrit_b200_decoder* d, const quintrit_b200_decoder_desc_t* des
     a.xa = d->xa, a.xb = d->xb;
     a.acc_qkv = d->acc_qkv, a.acc_o = d->acc_o, a.acc_gu = d->acc_gu, a.acc_down = d->acc_down;
     a.v_inter = d->v_inter, a.amax_bits = d->amax_bits, a.part_acc = d->part_acc, a.part_ms = d->part_ms, a.logits = d->logits;
-    a.scores = d->scores, a.attn_region = static_cast<unsigned int>(mega_attn_region(d->ctx, d->q_heads / d->kv_heads, d->head_dim));
+    a.scores = d->scores, a.attn_region = static_cast<unsigned int>(mega_attn_region(d->ctx, d->q_heads / d->kv_heads, d->head_dim, d->attn_v2));
+    a.attn_v2 = d->attn_v2 ? 1 : 0, a.attn_out = d->attn_out;
     a.bf16_tables = d->bf16_tables ? 1 : 0;
+    a.l2_prefetch = 1;
+    if (const char* pf = std::getenv("QUINTRIT_B200_L2_PREFETCH")) a.l2_prefetch = pf[0] != '0';  // experiments: "0" keeps the cold streams
     a.neox = d->arch == QUINTRIT_B200_ARCH_BITNET, a.relu2 = d->arch == QUINTRIT_B200_ARCH_BITNET;
     a.sumsq_part = nullptr;
     if (d->arch == QUINTRIT_B200_ARCH_BITNET) {
@@ -1091,7 +1105,7 @@ int mega_setup(quintrit_b200_decoder* d, const quintrit_b200_decoder_desc_t* des
     smem_base_kernel<<<1, 32, 1024>>>(reinterpret_cast<unsigned int*>(d->bar));
     QTB_CUDA(cudaGetLastError());
     QTB_CUDA(cudaMemcpy(&base, d->bar, sizeof base, cudaMemcpyDeviceToHost));
-    QTB_CUDA(cudaMemset(d->bar, 0, 16));
+    QTB_CUDA(cudaMemset(d->bar, 0, 64));
     switch (base) {
         case 0: return mega_bind<0>(d);
         case 1024: return mega_bind<1024>(d);
@@ -1105,7 +1119,7 @@ int mega_setup(quintrit_b200_decoder* d, const quintrit_b200_decoder_desc_t* des
 int decoder_step(quintrit_b200_decoder* d) {
     if (d->tp_world > 1 && !d->tp_attached) return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "the tensor-parallel group is not attached yet (quintrit_b200_decoder_tp_attach)");
     if (d->use_mega) {
-        QTB_CUDA(cudaMemsetAsync(d->bar, 0, sizeof(unsigned int), d->stream));
+        QTB_CUDA(cudaMemsetAsync(d->bar, 0, 16 * sizeof(unsigned int), d->stream));
         void* args[] = {&d->mega};
         QTB_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(d->mega_kernel), dim3(d->sm_count), dim3(kMegaThreads), args, d->mega_smem, d->stream));
         ++g_launches;
@@ -1759,20 +1773,20 @@ extern "C" int quintrit_b200_selftest_barrier(uint32_t device_index, uint32_t ct
         if (ctas == 0 || ctas > static_cast<uint32_t>(prop.multiProcessorCount)) return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "ctas must be 1..%d (every CTA has to be resident)", prop.multiProcessorCount);
         if (spin_limit == 0 || spin_limit > (1u << 20)) return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "spin_limit must be 1..2^20 polls");
         DeviceGuard g(static_cast<int>(device_index));
-        unsigned int* d_words = nullptr;  // [0] barrier counter, [1] status, [2..] one flag per CTA
-        QTB_CUDA(cudaMalloc(&d_words, (2 + ctas) * sizeof(unsigned int)));
-        cudaError_t e = cudaMemset(d_words, 0, (2 + ctas) * sizeof(unsigned int));
+        unsigned int* d_words = nullptr;  // [0..15] barrier counters, [16] status, [17..] one flag per CTA
+        QTB_CUDA(cudaMalloc(&d_words, (17 + ctas) * sizeof(unsigned int)));
+        cudaError_t e = cudaMemset(d_words, 0, (17 + ctas) * sizeof(unsigned int));
         if (e == cudaSuccess) {
-            barrier_selftest_kernel<<<ctas, 128>>>(d_words, d_words + 1, spin_limit, d_words + 2);
+            barrier_selftest_kernel<<<ctas, 128>>>(d_words, d_words + 16, spin_limit, d_words + 17);
             ++g_launches;
             e = cudaGetLastError();
         }
-        std::vector<unsigned int> host(2 + ctas, 0u);
+        std::vector<unsigned int> host(17 + ctas, 0u);
         if (e == cudaSuccess) e = cudaMemcpy(host.data(), d_words, host.size() * sizeof(unsigned int), cudaMemcpyDeviceToHost);
         cudaFree(d_words);
         if (e != cudaSuccess) return cuda_fail(e, "barrier self-test");
-        for (uint32_t i = 0; i < ctas; ++i) *out_released += host[2 + i];
-        rc = kernel_status_error(host[1]);
+        for (uint32_t i = 0; i < ctas; ++i) *out_released += host[17 + i];
+        rc = kernel_status_error(host[16]);
         return rc == QUINTRIT_OK ? ok() : rc;
     });
 }
@@ -1789,12 +1803,22 @@ extern "C" int quintrit_b200_decoder_trace_step(quintrit_b200_decoder_t* decoder
         if (out_ns == nullptr || capacity < n) return fail(QUINTRIT_ERR_BUFFER_TOO_SMALL, "out_ns holds %zu values, %zu are needed", capacity, n);
         if (d->host_pos >= static_cast<uint32_t>(d->ctx)) return fail(QUINTRIT_ERR_CONTEXT_OVERFLOW, "the context window is full");
         DeviceGuard g(d->device);
+        QTB_CUDA(cudaMemsetAsync(d->trace, 0, (n + 2) * sizeof(uint64_t), d->stream));
         d->mega.trace = d->trace;
         rc = decoder_set(d, 0, d->host_pos);
         if (rc == QUINTRIT_OK) rc = decoder_step(d);
         d->mega.trace = nullptr;
         if (rc != QUINTRIT_OK) return rc;
-        QTB_CUDA(cudaMemcpyAsync(out_ns, d->trace, n * sizeof(uint64_t), cudaMemcpyDeviceToHost, d->stream));
-        return decoder_check_status(d) == QUINTRIT_OK ? ok() : quintrit_last_error_code();
+        // The kernel stamps the SM's cycle counter and reads the global timer once at either end: cycles become nanoseconds
+        // by the ratio of the two spans. Slot layers * 14 + 3 receives the SM clock in kHz.
+        std::vector<uint64_t> raw(n + 2);
+        QTB_CUDA(cudaMemcpyAsync(raw.data(), d->trace, (n + 2) * sizeof(uint64_t), cudaMemcpyDeviceToHost, d->stream));
+        if ((rc = decoder_check_status(d)) != QUINTRIT_OK) return rc;
+        const size_t last = size_t(d->layers) * 14 + 2;
+        const double span_ns = static_cast<double>(raw[n + 1] - raw[n]), span_cyc = static_cast<double>(raw[last] - raw[0]);
+        const double ns_per_cycle = span_cyc > 0 ? span_ns / span_cyc : 0.0;
+        for (size_t i = 0; i < n; ++i) out_ns[i] = raw[i] == 0 ? 0 : raw[n] + static_cast<uint64_t>(static_cast<double>(raw[i] - raw[0]) * ns_per_cycle);
+        out_ns[last + 1] = ns_per_cycle > 0 ? static_cast<uint64_t>(1e6 / ns_per_cycle) : 0;
+        return ok();
     });
 }

@@ -40,6 +40,8 @@ struct quintrit_b200_decoder {
     size_t mega_smem;
     float *xa, *xb, *v_inter, *best_val;
     unsigned int *amax_bits, *best_idx, *bar;
+    bool attn_v2 = false;
+    float* attn_out = nullptr;
     unsigned long long* trace;  // phase timestamps of the last traced step (13 per layer + 3)
     cudaStream_t stream;
     cudaGraphExec_t graph_step;               // one token: embed ... argmax (token and position read from device memory)

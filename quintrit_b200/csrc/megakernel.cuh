@@ -34,6 +34,8 @@ struct MegaLayer {
     float ws[7];
     __half* kc;               // [ctx][kv_dim]
     __half* vc;
+    const unsigned char* wbase[7];  // the seven weight matrices of the layer in the stream layout, for the L2 prefetches
+    unsigned int wbytes[7];
 };
 
 struct MegaArgs {
@@ -67,6 +69,9 @@ struct MegaArgs {
     // vectors that every rank needs whole (o and down results, attention output, SwiGLU output) live in a "box" of which
     // every rank has one; ranks write their slices straight into the boxes of all ranks over NVLink as (value, sequence
     // number) pairs that the readers poll.
+    int attn_v2;               // attention second half by (KV head, 8 coordinates) units that also combine the chunks
+    float* attn_out;           // their result: the attention output before the o projection's quantiser (q_dim floats)
+    int l2_prefetch;           // request the weights of later phases into L2 ahead of their streams (QUINTRIT_B200_L2_PREFETCH=0 switches it off)
     int bf16_tables;           // embedding and output head hold BF16 instead of F16 bit patterns
     int neox;                  // BitNet: RoPE pairs (i, i + rope_dims / 2) instead of (2i, 2i + 1) (config.rs:464-467)
     int relu2;                 // BitNet: relu(gate)^2 * up instead of SwiGLU (ops.rs:301-308)
@@ -91,7 +96,7 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
 #define QTB_FINE(a, k)                                                                         \
     do {                                                                                       \
         if ((a).trace != nullptr && blockIdx.x == 0 && threadIdx.x == 0 && (k) < 32)           \
-            (a).trace[(a).n_layers * 14 + 4 + (k)] = global_timer_ns();                        \
+            (a).trace[(a).n_layers * 14 + 4 + (k)] = static_cast<unsigned long long>(clock64());  \
     } while (0)
 #else
 #define QTB_FINE(a, k) \
@@ -112,13 +117,17 @@ __device__ __forceinline__ void report_failure(unsigned int* bar, unsigned int* 
     atomicOr(bar, kBarFail);
 }
 
-__device__ __forceinline__ bool grid_barrier(unsigned int* bar, unsigned int target, unsigned int* status, int* s_flag,
+// `round` counts the barriers of the launch from 1; the barrier is complete once the counter holds round * gridDim.x.
+// (Spreading the arrivals over several counters of one sector, polled with two 16-byte loads, measured slower than this
+// single word polled with one acquire load: about 2.0 us against 1.4 us per barrier.)
+__device__ __forceinline__ bool grid_barrier(unsigned int* bar, unsigned int round, unsigned int* status, int* s_flag,
                                              unsigned int spin_limit = kBarrierSpinLimit) {
     __syncthreads();
     if (threadIdx.x == 0) {
         __threadfence();
         atomicAdd(bar, 1u);
         int okay = 1;
+        const unsigned int target = round * gridDim.x;
         for (unsigned int spins = 0;; ++spins) {
             unsigned int v;
             asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(bar));
@@ -281,11 +290,15 @@ __device__ __noinline__ void mega_gemv(const GemvItem* __restrict__ items, int f
 // RMSNorm + int8 quantisation of n values held in y_s (overwritten with the normalised values); every thread returns the
 // activation scale. Same arithmetic as norm_quant_kernel.
 __device__ __forceinline__ float mega_norm_quant(float* y_s, const float* norm_w, int n, float eps, int8_t* a8, double* sh_d,
-                                                 float* sh_f) {
+                                                 float* sh_f, const MegaArgs* ta = nullptr) {
+    (void)ta;
     const int tid = threadIdx.x;
     double sum = 0.0;
     for (int i = tid; i < n; i += kMegaThreads) sum += static_cast<double>(__fmul_rn(y_s[i], y_s[i]));
     sum = block_sum_f64(sum, sh_d);
+#ifdef QTB_FINE_TRACE
+    if (ta) QTB_FINE(*ta, 18);
+#endif
     const float mean = __double2float_rn(sum / static_cast<double>(n));
     const float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, eps)));
     float amax = 0.0f;
@@ -295,6 +308,9 @@ __device__ __forceinline__ float mega_norm_quant(float* y_s, const float* norm_w
         amax = fmaxf(amax, fabsf(y));
     }
     amax = block_max_f32(amax, sh_f);
+#ifdef QTB_FINE_TRACE
+    if (ta) QTB_FINE(*ta, 19);
+#endif
     const float s = amax > 0.0f ? __fdiv_rn(127.0f, amax) : 0.0f;
     if (a8 != nullptr)
         for (int i = tid; i < n; i += kMegaThreads) a8[i] = static_cast<int8_t>(amax > 0.0f ? quantize_code(y_s[i], s) : 0);
@@ -321,6 +337,26 @@ __device__ __forceinline__ void request_norm_weights(float* w_s, const float* __
     cp_async_commit();
 }
 __device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
+
+// Asks the copy engine to bring `bytes` (a multiple of 16, from a 16-byte boundary of this GPU's own memory) into L2; nothing
+// waits for it. A decode step leaves HBM idle most of the time (the dependent phases between two weight streams take longer
+// than the streams), while a layer's weights fit L2 several times: every CTA therefore requests its share of the weights of a
+// later phase while an earlier phase runs, and the GEMV phases then read L2 instead of starting a cold HBM stream after
+// every grid barrier.
+__device__ __forceinline__ void l2_prefetch_bulk(const void* p, unsigned int bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
+}
+constexpr unsigned int kPrefetchPiece = 8192;  // bytes per request
+// This CTA's share of matrix `which` of layer `ly` (shares are whole pieces; the last CTAs may have none).
+__device__ __forceinline__ void prefetch_weights(const MegaLayer& ly, int which) {
+    const unsigned int bytes = ly.wbytes[which];
+    const unsigned int pieces = (bytes + kPrefetchPiece - 1) / kPrefetchPiece, per = (pieces + gridDim.x - 1) / gridDim.x;
+    const unsigned int p0 = blockIdx.x * per, p1 = min(p0 + per, pieces);
+    for (unsigned int q = p0 + threadIdx.x; q < p1; q += kMegaThreads) {
+        const unsigned int off = q * kPrefetchPiece;
+        l2_prefetch_bulk(ly.wbase[which] + off, min(kPrefetchPiece, bytes - off));
+    }
+}
 
 // y_s[i] = x[i] + acc[i] * post (the rescaled projection added to the residual stream), all loads of a thread issued
 // before the first use. acc was accumulated with atomics by other SMs: it is read from L2 (ld.cg).
@@ -558,6 +594,7 @@ __device__ __noinline__ void mega_scores_unit(const MegaArgs& a, const MegaLayer
     // the load/store unit busy for most of a microsecond)
     Pair first{};
     if (tid < n_pairs) first = fetch(tid);
+    QTB_FINE(a, 25);
     __syncthreads();  // every thread is done with the table the block overlays
     stage_rows(blk, kbase, 0, len_old, hd, kvd);
     cp_async_commit();
@@ -595,14 +632,17 @@ __device__ __noinline__ void mega_scores_unit(const MegaArgs& a, const MegaLayer
         ly.vc[at] = s_vcur[tid];
         *reinterpret_cast<__half*>(blk + staged_offset(pos - r0, tid >> 3, row_bytes) + (tid & 7) * 2) = s_kcur[tid];
     }
+    QTB_FINE(a, 26);
     cp_async_wait<0>();
     __syncthreads();
+    QTB_FINE(a, 27);
     for (int t = tid; t < rows * gqa; t += kMegaThreads) {
         const int g = t / rows, r = t - g * rows;
         const float sc = f32v ? key_score<true>(blk, r, hd, s_q + g * hd) : key_score<false>(blk, r, hd, s_q + g * hd);
         a.scores[static_cast<size_t>(kvh * gqa + g) * a.ctx + r0 + r] = __fmul_rn(sc, attn_scale);
     }
     __syncthreads();
+    QTB_FINE(a, 28);
     for (int i = tid; i < 13 * 64; i += kMegaThreads) {  // the zero rows of the table (byte values that are no velurex code)
         const int k = i >> 6;
         reinterpret_cast<int*>(smem)[(k < 9 ? 28 * k + 27 : 243 + k) * 64 + (i & 63)] = 0;
@@ -787,13 +827,311 @@ __device__ __noinline__ void mega_values_unit(const MegaArgs& a, const MegaLayer
     __syncthreads();
 }
 
+// ---- attention, second half, second form: one unit per (KV head, 8 coordinates) -----------------------------------------
+// The value accumulation is a chain of one dependent step per position (about 16 cycles: multiply-add, round to half,
+// widen), so its length, not the work, sets the time. A unit therefore takes ALL chunks of its coordinates at once: lane
+// (chunk, coordinate) of warp g runs the chain of query head g for that chunk, the four chunks of the reference's split
+// (attention.rs:510-533) side by side, and the unit also combines them (attention.rs:497-541) and contributes to the
+// maximum that the quantiser of the o projection needs. What is left after the next grid barrier is a load and a rounding.
+// Staging is asynchronous copies only (no registers, everything in flight at once): the unit's 16-byte piece of every
+// cached V row into [chunk][position][8 halves], the scores of its heads into one row per (head, chunk). The softmax
+// factors (attention.rs:448-462) are computed by all threads, eight consecutive positions each: maxima of the groups, a
+// barrier, the maximum before the group from the earlier groups' maxima, then one exponential per position. A word per
+// head and group of eight positions tells whether any chunk's running maximum moved there; groups without a move run
+// branch-free.
+constexpr int kV2Dims = 16;  // two coordinates per lane: their chains interleave, which hides most of a step's latency
+constexpr int kV2MaxCtx = 4096;
+constexpr int kV2MaxGqa = 12;  // chain warps + sum warps must fit the 16 warps of the CTA
+
+// Row length (floats) of the factor rows for chunks of `chunk` positions: a multiple of 8, at least `chunk`.
+__host__ __device__ constexpr int values2_clp(int chunk) { return (chunk + 7) / 8 * 8; }
+// Positions per chunk in the staged V block: odd, so that the 32-byte pieces the four chunks' lanes read at one step fall into
+// four different bank groups.
+__host__ __device__ constexpr int values2_clr(int chunk) { return values2_clp(chunk) + 1; }
+__host__ __device__ constexpr size_t values2_bytes(int ctx, int gqa) {
+    const int nch = ctx >= 512 ? 4 : 1, chunk = ctx >= 512 ? (ctx + 3) / 4 : ctx, clp = values2_clp(chunk);
+    return static_cast<size_t>(nch) * values2_clr(chunk) * kV2Dims * 2 + static_cast<size_t>(2) * gqa * nch * clp * 4 + static_cast<size_t>(gqa) * (clp / 8) * 4 +
+           static_cast<size_t>(gqa) * nch * (clp / 8) * 4 + static_cast<size_t>(gqa) * nch * 8 + 64;
+}
+
+template <bool F32>
+__device__ __forceinline__ float v2_round(float x) {
+    return F32 ? x : __half2float(__float2half_rn(x));
+}
+
+// The two chains of one lane (two neighbouring coordinates of one head and chunk): `ngr` groups of eight positions in order;
+// values (a pair of halves every 32 bytes), factors vs and ms and the move flags (one word per group) at byte offsets into
+// the dynamic shared memory. The operands of the next group are loaded while this group's eight dependent steps run, and
+// the two chains' steps alternate, so that one's latency covers the other's. Rounded to half precision after every
+// operation unless F32 (attention.rs:448-470).
+template <bool F32>
+__device__ __noinline__ float2 v2_chain(uint32_t v_off, uint32_t w_off, uint32_t m_off, uint32_t f_off, int ngr) {
+    unsigned char* base = dyn_smem();
+    const unsigned char* vrow = base + v_off;
+    const float* wrow = reinterpret_cast<const float*>(base + w_off);
+    const float* mrow = reinterpret_cast<const float*>(base + m_off);
+    const unsigned int* fl = reinterpret_cast<const unsigned int*>(base + f_off);
+    float a0 = 0.0f, a1 = 0.0f;
+    // The group after the last one is loaded too and not used: it lies in the padding or in the arrays behind the rows.
+    __half2 vn[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) vn[j] = *reinterpret_cast<const __half2*>(vrow + j * (kV2Dims * 2));
+    float4 w0n = *reinterpret_cast<const float4*>(wrow), w1n = *reinterpret_cast<const float4*>(wrow + 4);
+    unsigned int fn = fl[0];
+    for (int grp = 0; grp < ngr; ++grp) {
+        float2 v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = __half22float2(vn[j]);
+        const float w[8] = {w0n.x, w0n.y, w0n.z, w0n.w, w1n.x, w1n.y, w1n.z, w1n.w};
+        const unsigned int f = fn;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) vn[j] = *reinterpret_cast<const __half2*>(vrow + (8 * (grp + 1) + j) * (kV2Dims * 2));
+        w0n = *reinterpret_cast<const float4*>(wrow + 8 * (grp + 1));
+        w1n = *reinterpret_cast<const float4*>(wrow + 8 * (grp + 1) + 4);
+        fn = fl[grp + 1];
+        if (f == 0) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                a0 = v2_round<F32>(__fmaf_rn(v[j].x, w[j], a0));
+                a1 = v2_round<F32>(__fmaf_rn(v[j].y, w[j], a1));
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                if ((f >> j) & 1u) {  // some chunk's maximum moved here; a factor of one changes nothing
+                    const float ms = mrow[grp * 8 + j];
+                    a0 = v2_round<F32>(__fmul_rn(a0, ms));
+                    a1 = v2_round<F32>(__fmul_rn(a1, ms));
+                }
+                a0 = v2_round<F32>(__fmaf_rn(v[j].x, w[j], a0));
+                a1 = v2_round<F32>(__fmaf_rn(v[j].y, w[j], a1));
+            }
+        }
+    }
+    return make_float2(a0, a1);
+}
+
+// S of one (head, chunk): S = fma(S, ms, vs) over its positions in order (attention.rs:466), operands one group ahead.
+__device__ __noinline__ float v2_sum_chain(uint32_t m_off, uint32_t w_off, int len) {
+    unsigned char* base = dyn_smem();
+    const float* ms_row = reinterpret_cast<const float*>(base + m_off);
+    const float* vs_row = reinterpret_cast<const float*>(base + w_off);
+    float S = 0.0f;
+    const int full = len >> 3;
+    // The group after the last one is loaded too and not used: it lies in the row's padding or in the arrays behind it.
+    float4 m0 = *reinterpret_cast<const float4*>(ms_row), m1 = *reinterpret_cast<const float4*>(ms_row + 4);
+    float4 v0 = *reinterpret_cast<const float4*>(vs_row), v1 = *reinterpret_cast<const float4*>(vs_row + 4);
+    for (int g = 0; g < full; ++g) {
+        const float4 n0 = *reinterpret_cast<const float4*>(ms_row + 8 * g + 8), n1 = *reinterpret_cast<const float4*>(ms_row + 8 * g + 12);
+        const float4 u0 = *reinterpret_cast<const float4*>(vs_row + 8 * g + 8), u1 = *reinterpret_cast<const float4*>(vs_row + 8 * g + 12);
+        S = __fmaf_rn(S, m0.x, v0.x);
+        S = __fmaf_rn(S, m0.y, v0.y);
+        S = __fmaf_rn(S, m0.z, v0.z);
+        S = __fmaf_rn(S, m0.w, v0.w);
+        S = __fmaf_rn(S, m1.x, v1.x);
+        S = __fmaf_rn(S, m1.y, v1.y);
+        S = __fmaf_rn(S, m1.z, v1.z);
+        S = __fmaf_rn(S, m1.w, v1.w);
+        m0 = n0, m1 = n1, v0 = u0, v1 = u1;
+    }
+    for (int p = full * 8; p < len; ++p) S = __fmaf_rn(S, ms_row[p], vs_row[p]);
+#ifdef QTB_DEBUG_V2_PRINT
+    printf("sum_chain m_off %u w_off %u len %d full %d S %g ms0 %g vs0 %g\n", m_off, w_off, len, full, S, ms_row[0], vs_row[0]);
+#endif
+    return S;
+}
+
+#ifdef QTB_DEBUG_V2
+__device__ long long g_v2_clock[16];
+#define QTB_V2_CLOCK(k)                                  \
+    do {                                                 \
+        if (threadIdx.x == 0) g_v2_clock[k] = clock64(); \
+    } while (0)
+#else
+#define QTB_V2_CLOCK(k) \
+    do {                \
+    } while (0)
+#endif
+
+template <bool F32>
+__device__ __noinline__ void mega_values2_unit(const MegaArgs& a, const MegaLayer& ly, int l, int kvh, int slice, unsigned char* smem) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int hd = a.head_dim, gqa = a.q_heads / a.kv_heads, kvd = a.kv_heads * hd;
+    const KvSplit ks = kv_split(a);
+    const int nch = ks.split ? 4 : 1, CL = ks.chunk, clp = values2_clp(CL), clr = values2_clr(CL), seq = ks.seq_len;
+    const int ngr8 = clp / 8, npairs = gqa * nch;
+    constexpr int kPiece = kV2Dims * 2;                                                  // bytes of a cached row a unit takes
+    unsigned char* Vr = smem;                                                            // [nch][clr][16 halves]
+    float* f_ms = reinterpret_cast<float*>(smem + static_cast<size_t>(nch) * clr * kPiece);  // [gqa][nch][clp]
+    float* f_vs = f_ms + npairs * clp;                                                   // scores, then vs
+    unsigned int* s_moved = reinterpret_cast<unsigned int*>(f_vs + npairs * clp);        // [gqa][ngr8]
+    float* s_gmax = reinterpret_cast<float*>(s_moved + gqa * ngr8);                      // [gqa * nch][ngr8]: maxima of the groups
+    float* s_MS = s_gmax + npairs * ngr8;                                                // [gqa][nch][2]: M, S
+    auto chunk_len = [&](int c) {
+        if (!ks.split) return c == 0 ? seq : 0;
+        const int start = c * CL;
+        return max(0, min(min(start + CL, ks.n_kv), seq) - start);
+    };
+    int ngr = 0;  // groups of eight positions of the longest chunk: the length of every chain of this unit
+    for (int cc = 0; cc < nch; ++cc) ngr = max(ngr, (chunk_len(cc) + 7) / 8);
+    __syncthreads();  // every thread is done with the table the arrays overlay
+    QTB_FINE(a, 8);
+    QTB_V2_CLOCK(0);
+    {
+        const __half* vsrc = ly.vc + static_cast<size_t>(kvh) * hd + slice * kV2Dims;
+        for (int i = tid; i < seq * 2; i += kMegaThreads) {  // two 16-byte copies per cached row
+            const int p = i >> 1, h = i & 1, c = ks.split ? p / CL : 0;
+            cp_async16(Vr + static_cast<size_t>(c * clr + (p - c * CL)) * kPiece + h * 16, vsrc + static_cast<size_t>(p) * kvd + h * 8);
+        }
+        // the scores of a (head, chunk) are contiguous in the score buffer and 16-byte aligned (chunks start on multiples of 64)
+        for (int pair = warp; pair < npairs; pair += kMegaWarps) {
+            const int g = pair / nch, c = pair - g * nch, len = chunk_len(c);
+            const float* src = a.scores + static_cast<size_t>(kvh * gqa + g) * a.ctx + c * CL;
+            for (int q = lane; q * 4 < len; q += 32) cp_async16(f_vs + pair * clp + q * 4, src + q * 4);
+        }
+        cp_async_commit();
+        for (int i = tid; i < gqa * ngr8; i += kMegaThreads) s_moved[i] = 0u;
+        // zero values behind a chunk's end up to the common chain length (the last chunk, mostly)
+        for (int c = 0; c < nch; ++c)
+            for (int i = chunk_len(c) * 2 + tid; i < ngr * 16; i += kMegaThreads) *reinterpret_cast<uint4*>(Vr + static_cast<size_t>(c * clr) * kPiece + i * 16) = make_uint4(0u, 0u, 0u, 0u);
+        cp_async_wait<0>();
+    }
+    __syncthreads();
+    QTB_FINE(a, 2);
+    QTB_V2_CLOCK(1);
+    // softmax factors, a task = (head, chunk, group of eight positions): first the maximum of every group
+    const int ntasks = npairs * ngr;
+    for (int t = tid; t < ntasks; t += kMegaThreads) {
+        const int pair = t / ngr, grp = t - pair * ngr, len = chunk_len(pair % nch);
+        const float* sc = f_vs + pair * clp + grp * 8;
+        float m = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            if (grp * 8 + j < len) m = fmaxf(m, sc[j]);
+        s_gmax[pair * ngr8 + grp] = m;
+    }
+    __syncthreads();
+    QTB_FINE(a, 4);
+    QTB_V2_CLOCK(2);
+    // then the running maximum before the group, and per position ms = exp(m_before - score), vs = 1 where the score exceeds
+    // the maximum so far, else ms = 1, vs = exp(score - m_before); behind a chunk's end vs = 0, ms = 1 (such a step leaves a
+    // sum unchanged bit for bit)
+    for (int t = tid; t < ntasks; t += kMegaThreads) {
+        const int pair = t / ngr, grp = t - pair * ngr, len = chunk_len(pair % nch);
+        float run = -INFINITY;
+        for (int q = 0; q < grp; ++q) run = fmaxf(run, s_gmax[pair * ngr8 + q]);
+        float* sc = f_vs + pair * clp + grp * 8;
+        float* msr = f_ms + pair * clp + grp * 8;
+        float ms[8], vs[8];
+        unsigned int bits = 0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            ms[j] = 1.0f, vs[j] = 0.0f;
+            if (grp * 8 + j < len) {
+                const float s_j = sc[j];
+                vs[j] = 1.0f;
+                if (s_j > run) {
+                    ms[j] = device_expf(__fsub_rn(run, s_j));
+                    run = s_j;
+                    bits |= 1u << j;
+                } else {
+                    vs[j] = device_expf(__fsub_rn(s_j, run));
+                }
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            msr[j] = ms[j];
+            sc[j] = vs[j];
+            if (ms[j] == 1.0f) bits &= ~(1u << j);  // exp(0) = 1: a maximum that moved by nothing needs no rescale
+        }
+        if (bits) atomicOr(s_moved + (pair / nch) * ngr8 + grp, bits);
+        if (grp == ngr - 1) s_MS[pair * 2] = run;  // the maximum of the whole chunk (-inf for an empty one)
+    }
+    __syncthreads();
+    QTB_FINE(a, 3);
+    QTB_V2_CLOCK(3);
+    float2 acc = make_float2(0.0f, 0.0f);
+    if (warp < gqa) {
+        // the chains of head `warp`: lane -> (chunk, pair of coordinates)
+        const int c = lane >> 3, d = lane & 7;
+        const int row = c < nch ? c : 0;  // lanes without a chunk repeat chunk 0; their sums are not used
+        const uint32_t v_off = static_cast<uint32_t>(row * clr * kPiece + d * 4);
+        const uint32_t w_off = static_cast<uint32_t>(reinterpret_cast<const unsigned char*>(f_vs + (warp * nch + row) * clp) - smem);
+        const uint32_t m_off = static_cast<uint32_t>(reinterpret_cast<const unsigned char*>(f_ms + (warp * nch + row) * clp) - smem);
+        const uint32_t f_off = static_cast<uint32_t>(reinterpret_cast<const unsigned char*>(s_moved + warp * ngr8) - smem);
+        acc = v2_chain<F32>(v_off, w_off, m_off, f_off, ngr);
+        QTB_FINE(a, 9);
+        QTB_V2_CLOCK(4);
+    } else {
+        // S of every (head, chunk), one thread each, meanwhile
+        const int pair = (warp - gqa) * 32 + lane;
+        if (pair < npairs)
+            s_MS[pair * 2 + 1] = v2_sum_chain(static_cast<uint32_t>(reinterpret_cast<const unsigned char*>(f_ms + pair * clp) - smem),
+                                              static_cast<uint32_t>(reinterpret_cast<const unsigned char*>(f_vs + pair * clp) - smem), chunk_len(pair % nch));
+    }
+    __syncthreads();
+    QTB_FINE(a, 12);
+    QTB_V2_CLOCK(5);
+#ifdef QTB_DEBUG_V2_PRINT
+    if (tid == 0) {
+        for (int pr = 0; pr < npairs; ++pr) printf("pair %d len %d M %g S %g gmax0 %g\n", pr, chunk_len(pr % nch), s_MS[pr * 2], s_MS[pr * 2 + 1], s_gmax[pr * ngr8]);
+        for (int p = 0; p < min(48, ngr * 8); ++p) printf("p %d ms %g vs %g flag %u v0 %g\n", p, f_ms[p], f_vs[p], s_moved[p / 8], __half2float(*reinterpret_cast<const __half*>(Vr + p * kPiece)));
+    }
+    if (lane == 0 && warp < gqa) printf("warp %d acc %g %g\n", warp, acc.x, acc.y);
+#endif
+    if (warp < gqa) {
+        // combine the chunks (attention.rs:497-541); every lane of a coordinate pair computes the same values
+        const int d = lane & 7;
+        float2 part[4];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            part[c].x = __shfl_sync(0xffffffffu, acc.x, (c * 8 + d) & 31);
+            part[c].y = __shfl_sync(0xffffffffu, acc.y, (c * 8 + d) & 31);
+        }
+        const float* MS = s_MS + warp * nch * 2;
+        float2 out;
+        if (!ks.split) {
+            const float S = MS[1];
+            const float inv = S == 0.0f ? 0.0f : __fdiv_rn(1.0f, S);
+            out = make_float2(__fmul_rn(part[0].x, inv), __fmul_rn(part[0].y, inv));
+        } else {
+            float m_final = -INFINITY, s_final = 0.0f;
+            float2 sum = make_float2(0.0f, 0.0f);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const float M = MS[2 * c], S = MS[2 * c + 1];
+                if (S == 0.0f) continue;
+                const float m_new = fmaxf(m_final, M);
+                const float scale_old = device_expf(__fsub_rn(m_final, m_new)), scale_new = device_expf(__fsub_rn(M, m_new));
+                sum.x = __fmaf_rn(sum.x, scale_old, __fmul_rn(part[c].x, scale_new));
+                sum.y = __fmaf_rn(sum.y, scale_old, __fmul_rn(part[c].y, scale_new));
+                s_final = __fmaf_rn(s_final, scale_old, __fmul_rn(S, scale_new));
+                m_final = m_new;
+            }
+            const float inv = s_final != 0.0f ? __fdiv_rn(1.0f, s_final) : 0.0f;
+            out = s_final != 0.0f ? make_float2(__fmul_rn(sum.x, inv), __fmul_rn(sum.y, inv)) : sum;
+        }
+        if (lane < 8) *reinterpret_cast<float2*>(a.attn_out + (kvh * gqa + warp) * hd + slice * kV2Dims + 2 * lane) = out;
+        float m = lane < 8 ? fmaxf(fabsf(out.x), fabsf(out.y)) : 0.0f;
+        for (int o = 4; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        if (lane == 0 && m > 0.0f) atomicMax(a.amax_bits + 2 + (l & 1), __float_as_uint(m));  // non-negative floats order like their bits
+    }
+    __syncthreads();
+    for (int i = tid; i < 13 * 64; i += kMegaThreads) {  // the zero rows of the table (byte values that are no velurex code)
+        const int k = i >> 6;
+        reinterpret_cast<int*>(smem)[(k < 9 ? 28 * k + 27 : 243 + k) * 64 + (i & 63)] = 0;
+    }
+    __syncthreads();
+}
+
 // Shared-memory plan of the token kernel (bytes from the dynamic base): attention region (its first 64 KiB double as the
 // GEMV table) | y (floats) | a8 | small. The attention region holds whichever is largest: a scores unit (staged key block,
 // the group's queries, the new key/value rows), a values unit for the longest chunk, or the lm_head rings.
-__host__ __device__ constexpr size_t mega_attn_region(int ctx, int gqa, int head_dim) {
+__host__ __device__ constexpr size_t mega_attn_region(int ctx, int gqa, int head_dim, bool v2) {
     const int len_max = ctx < 512 ? ctx : (ctx + 3) / 4;
     size_t need = static_cast<size_t>(kAttnBlockBytes) + static_cast<size_t>(gqa) * head_dim * 4 + static_cast<size_t>(head_dim) * 4 + 64;
-    const size_t vals = values_unit_bytes(len_max, gqa), head = static_cast<size_t>(kMegaWarps) * 4 * 1024 * 2 + 1024;
+    const size_t vals = v2 ? values2_bytes(ctx, gqa) : values_unit_bytes(len_max, gqa), head = static_cast<size_t>(kMegaWarps) * 4 * 1024 * 2 + 1024;
     if (vals > need) need = vals;
     if (head > need) need = head;
     return (need + 1023) / 1024 * 1024;
@@ -844,46 +1182,152 @@ __device__ __forceinline__ void prefetch_items(const MegaArgs& a, const MegaLaye
 }
 
 // Phase A (which = 0) and phase E (which = 1): residual (or embedding), RMSNorm, int8 codes for the projection that follows.
-__device__ __noinline__ bool phase_norm(const MegaArgs& a, int l, int which, unsigned int seq_base, unsigned char* smem) {
-    const MegaSmem v = mega_smem_views(smem, a);
+// One block-wide reduction with a single barrier: lane 0 of every warp deposits its warp's value, everybody reads all of
+// them. `sh` must not have been read since the last __syncthreads of every thread (the phases alternate the buffers).
+__device__ __forceinline__ double block_sum_f64_once(double v, double* sh) {
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = v;
+    __syncthreads();
+    double t0 = 0.0, t1 = 0.0;
+#pragma unroll
+    for (int i = 0; i < kMegaWarps; i += 2) {  // two interleaved chains, the same order in every thread
+        t0 += sh[i];
+        t1 += sh[i + 1];
+    }
+    return t0 + t1;
+}
+__device__ __forceinline__ float block_max_f32_once(float v, float* sh) {
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float t = 0.0f;
+#pragma unroll
+    for (int i = 0; i < kMegaWarps; ++i) t = fmaxf(t, sh[i]);
+    return t;
+}
+
+constexpr int kNormPer = 8;  // elements of the residual stream a thread keeps in registers: hidden <= 8 * 512
+
+// Phase A (which = 0) and phase E (which = 1) for one GPU and hidden <= 4096: the vector never leaves the registers. Every
+// thread owns the elements tid + 512 k; all loads (projection sums and residual stream from L2, norm weights from shared
+// memory) are issued before the first use, and the two block-wide reductions (sum of squares in double, maximum) cost
+// one barrier each. Same arithmetic as mega_norm_quant.
+__device__ __forceinline__ void phase_norm_regs(const MegaArgs& a, const MegaSmem& v, int l, int which) {
     const int tid = threadIdx.x, cta = blockIdx.x, G = gridDim.x, H = a.hidden;
     const MegaLayer& ly = v.layers[l];
-    prefetch_items(a, ly, which == 0 ? 0 : 2);
-
-    if (which == 0) {
-        if (l == 0) {
-            const size_t base = static_cast<size_t>(a.token[0]) * H;
-            for (int i = tid; i < H; i += kMegaThreads) v.y[i] = table_to_float(a.embed[base + i], a.bf16_tables != 0);
-        } else {
-            const float s_prev = v.scale[3];
-            const float post = s_prev > 0.0f ? __fdiv_rn(v.layers[l - 1].ws[6], s_prev) : 0.0f;
-            if (a.tp_world > 1)  // the down results of the previous layer, from every rank
-                residual_add_ll(v.y, a.xb, reinterpret_cast<const uint2*>(a.tp_box[a.tp_rank] + a.box_acc_down), seq_base + 4u * l, a, post,
-                                s_prev > 0.0f, H);
-            else
-                residual_add(v.y, a.xb, a.acc_down, post, s_prev > 0.0f, H);
+    const bool embed = which == 0 && l == 0;
+    const float s_prev = which == 0 ? v.scale[3] : v.scale[1];
+    const float ws_prev = which == 0 ? (l > 0 ? v.layers[l - 1].ws[6] : 0.0f) : ly.ws[3];
+    const bool live = s_prev > 0.0f;
+    const float post = live ? __fdiv_rn(ws_prev, s_prev) : 0.0f;
+    const int32_t* acc = which == 0 ? a.acc_down : a.acc_o;
+    const float* x = which == 0 ? a.xb : a.xa;
+    int av[kNormPer];
+    float y[kNormPer];
+    if (embed) {
+        const size_t base = static_cast<size_t>(a.token[0]) * H;
+#pragma unroll
+        for (int k = 0; k < kNormPer; ++k) {
+            const int i = tid + k * kMegaThreads;
+            y[k] = i < H ? table_to_float(a.embed[base + i], a.bf16_tables != 0) : 0.0f;
         }
     } else {
-        const float s_q = v.scale[1];
-        const float post = s_q > 0.0f ? __fdiv_rn(ly.ws[3], s_q) : 0.0f;
-        if (a.tp_world > 1)  // the o results of this layer, from every rank
-            residual_add_ll(v.y, a.xa, reinterpret_cast<const uint2*>(a.tp_box[a.tp_rank] + a.box_acc_o), seq_base + 4u * l + 2u, a, post,
-                            s_q > 0.0f, H);
-        else
-            residual_add(v.y, a.xa, a.acc_o, post, s_q > 0.0f, H);
+#pragma unroll
+        for (int k = 0; k < kNormPer; ++k) {
+            const int i = tid + k * kMegaThreads;
+            av[k] = i < H ? __ldcg(acc + i) : 0;
+            y[k] = i < H ? __ldcg(x + i) : 0.0f;
+        }
+#pragma unroll
+        for (int k = 0; k < kNormPer; ++k) y[k] = __fadd_rn(y[k], live ? __fmul_rn(static_cast<float>(av[k]), post) : 0.0f);
     }
     cp_async_wait<0>();  // the norm weights requested one phase ago
     __syncthreads();
+    if (which == 1) QTB_FINE(a, 17);
     if (cta == 0) {
         float* keep = which == 0 ? a.xa : a.xb;
-        for (int i = tid; i < H; i += kMegaThreads) keep[i] = v.y[i];
+#pragma unroll
+        for (int k = 0; k < kNormPer; ++k)
+            if (tid + k * kMegaThreads < H) keep[tid + k * kMegaThreads] = y[k];
     }
     if (which == 1 && cta == G - 1) {
         const int n = (a.q_heads + 2 * a.kv_heads) * a.head_dim;
         for (int i = tid; i < n; i += kMegaThreads) a.acc_qkv[i] = 0;  // consumed by the scores phase
     }
-    const float s = mega_norm_quant(v.y, v.w, H, a.eps, v.a8, v.sh_d, v.sh_f);
+    double sum = 0.0;
+#pragma unroll
+    for (int k = 0; k < kNormPer; ++k) sum += static_cast<double>(__fmul_rn(y[k], y[k]));  // elements beyond H are zero
+    sum = block_sum_f64_once(sum, v.sh_d);
+    if (which == 1) QTB_FINE(a, 18);
+    const float mean = __double2float_rn(sum / static_cast<double>(H));
+    const float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, a.eps)));
+    float amax = 0.0f;
+#pragma unroll
+    for (int k = 0; k < kNormPer; ++k) {
+        const int i = tid + k * kMegaThreads;
+        y[k] = i < H ? __fmul_rn(__fmul_rn(y[k], inv), v.w[i]) : 0.0f;
+        amax = fmaxf(amax, fabsf(y[k]));
+    }
+    amax = block_max_f32_once(amax, v.sh_f);
+    if (which == 1) QTB_FINE(a, 19);
+    const float s = amax > 0.0f ? __fdiv_rn(127.0f, amax) : 0.0f;
+#pragma unroll
+    for (int k = 0; k < kNormPer; ++k) {
+        const int i = tid + k * kMegaThreads;
+        if (i < H) v.a8[i] = static_cast<int8_t>(amax > 0.0f ? quantize_code(y[k], s) : 0);
+    }
     if (tid == 0) v.scale[which == 0 ? 0 : 2] = s;
+    __syncthreads();  // the norm weights are rewritten next
+}
+
+// Phase A (which = 0) and phase E (which = 1): residual (or embedding), RMSNorm, int8 codes for the projection that follows.
+__device__ __noinline__ bool phase_norm(const MegaArgs& a, int l, int which, unsigned int seq_base, unsigned char* smem) {
+    const MegaSmem v = mega_smem_views(smem, a);
+    const int tid = threadIdx.x, cta = blockIdx.x, G = gridDim.x, H = a.hidden;
+    const MegaLayer& ly = v.layers[l];
+    prefetch_items(a, ly, which == 0 ? 0 : 2);
+    if (which == 1) QTB_FINE(a, 16);
+
+    if (a.tp_world == 1 && H <= kNormPer * kMegaThreads) {
+        phase_norm_regs(a, v, l, which);
+    } else {
+        if (which == 0) {
+            if (l == 0) {
+                const size_t base = static_cast<size_t>(a.token[0]) * H;
+                for (int i = tid; i < H; i += kMegaThreads) v.y[i] = table_to_float(a.embed[base + i], a.bf16_tables != 0);
+            } else {
+                const float s_prev = v.scale[3];
+                const float post = s_prev > 0.0f ? __fdiv_rn(v.layers[l - 1].ws[6], s_prev) : 0.0f;
+                if (a.tp_world > 1)  // the down results of the previous layer, from every rank
+                    residual_add_ll(v.y, a.xb, reinterpret_cast<const uint2*>(a.tp_box[a.tp_rank] + a.box_acc_down), seq_base + 4u * l, a, post,
+                                    s_prev > 0.0f, H);
+                else
+                    residual_add(v.y, a.xb, a.acc_down, post, s_prev > 0.0f, H);
+            }
+        } else {
+            const float s_q = v.scale[1];
+            const float post = s_q > 0.0f ? __fdiv_rn(ly.ws[3], s_q) : 0.0f;
+            if (a.tp_world > 1)  // the o results of this layer, from every rank
+                residual_add_ll(v.y, a.xa, reinterpret_cast<const uint2*>(a.tp_box[a.tp_rank] + a.box_acc_o), seq_base + 4u * l + 2u, a, post,
+                                s_q > 0.0f, H);
+            else
+                residual_add(v.y, a.xa, a.acc_o, post, s_q > 0.0f, H);
+        }
+        cp_async_wait<0>();  // the norm weights requested one phase ago
+        __syncthreads();
+        if (which == 1) QTB_FINE(a, 17);
+        if (cta == 0) {
+            float* keep = which == 0 ? a.xa : a.xb;
+            for (int i = tid; i < H; i += kMegaThreads) keep[i] = v.y[i];
+        }
+        if (which == 1 && cta == G - 1) {
+            const int n = (a.q_heads + 2 * a.kv_heads) * a.head_dim;
+            for (int i = tid; i < n; i += kMegaThreads) a.acc_qkv[i] = 0;  // consumed by the scores phase
+        }
+        const float s = mega_norm_quant(v.y, v.w, H, a.eps, v.a8, v.sh_d, v.sh_f, which == 1 ? &a : nullptr);
+        if (tid == 0) v.scale[which == 0 ? 0 : 2] = s;
+    }
+    if (which == 1) QTB_FINE(a, 20);
     if (which == 0)
         request_norm_weights(v.w, ly.ffn_norm, H);
     else
@@ -909,7 +1353,10 @@ __device__ __noinline__ void phase_scores(const MegaArgs& a, int l, unsigned cha
     }
     if (cta == G - 1) {
         for (int i = tid; i < a.hidden; i += kMegaThreads) a.acc_down[i] = 0;  // read by every CTA in phase A, rewritten by down
-        if (tid == 0) a.amax_bits[(l + 1) & 1] = 0u;
+        if (tid == 0) {
+            a.amax_bits[(l + 1) & 1] = 0u;
+            a.amax_bits[2 + ((l + 1) & 1)] = 0u;  // the attention output's maximum of the next layer
+        }
     }
 }
 
@@ -919,10 +1366,72 @@ __device__ __noinline__ void phase_values(const MegaArgs& a, int l, unsigned cha
     const int cta = blockIdx.x, G = gridDim.x;
     const KvSplit ks = kv_split(a);
     const int nchunks = ks.split ? 4 : 1, slices = a.head_dim / kAttnSlice;
+    // The value chains are pure latency (one dependent step per position) and leave the memory system idle: the o, gate, up
+    // and down weights of this layer are requested into L2 now.
+    if (a.l2_prefetch)
+        for (int k = 3; k < 7; ++k) prefetch_weights(v.layers[l], k);
     for (int u = cta; u < a.kv_heads * nchunks * slices; u += G) {
         const int slice = u % slices, c = (u / slices) % nchunks, kvh = u / (slices * nchunks);
         mega_values_unit(a, v.layers[l], kvh, c, slice, smem);
     }
+}
+
+// Phase C2, second form: one unit per (KV head, 8 coordinates); see mega_values2_unit.
+__device__ __noinline__ void phase_values2(const MegaArgs& a, int l, unsigned char* smem) {
+    const MegaSmem v = mega_smem_views(smem, a);
+    const int slices = a.head_dim / kV2Dims;
+    for (int u = blockIdx.x; u < a.kv_heads * slices; u += gridDim.x) {
+        if (a.f32_values)
+            mega_values2_unit<true>(a, v.layers[l], l, u / slices, u % slices, smem);
+        else
+            mega_values2_unit<false>(a, v.layers[l], l, u / slices, u % slices, smem);
+    }
+}
+
+// Phase D after phase_values2: the attention output is complete in a.attn_out and, without a sub-norm, so is its maximum;
+// every CTA loads the vector into registers, normalises it if the model has an attention sub-norm (attention.rs:234-246)
+// and writes the int8 codes of the o projection's input.
+__device__ __noinline__ void phase_combine2(const MegaArgs& a, int l, unsigned char* smem) {
+    const MegaSmem v = mega_smem_views(smem, a);
+    const int tid = threadIdx.x, qd = a.q_heads * a.head_dim;
+    QTB_FINE(a, 21);
+    float y[kNormPer];
+#pragma unroll
+    for (int k = 0; k < kNormPer; ++k) {
+        const int i = tid + k * kMegaThreads;
+        y[k] = i < qd ? __ldcg(a.attn_out + i) : 0.0f;
+    }
+    float amax;
+    if (const float* sub_w = v.layers[l].attn_sub_norm) {
+        float w[kNormPer];
+#pragma unroll
+        for (int k = 0; k < kNormPer; ++k) w[k] = tid + k * kMegaThreads < qd ? __ldg(sub_w + tid + k * kMegaThreads) : 0.0f;
+        double sum = 0.0;
+#pragma unroll
+        for (int k = 0; k < kNormPer; ++k) sum += static_cast<double>(__fmul_rn(y[k], y[k]));
+        sum = block_sum_f64_once(sum, v.sh_d);
+        const float mean = __double2float_rn(sum / static_cast<double>(qd));
+        const float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, a.eps)));
+        amax = 0.0f;
+#pragma unroll
+        for (int k = 0; k < kNormPer; ++k) {
+            y[k] = __fmul_rn(__fmul_rn(y[k], inv), w[k]);
+            amax = fmaxf(amax, fabsf(y[k]));
+        }
+        amax = block_max_f32_once(amax, v.sh_f);
+    } else {
+        amax = __uint_as_float(__ldcg(a.amax_bits + 2 + (l & 1)));
+    }
+    QTB_FINE(a, 23);
+    const float s_q = amax > 0.0f ? __fdiv_rn(127.0f, amax) : 0.0f;
+#pragma unroll
+    for (int k = 0; k < kNormPer; ++k) {
+        const int i = tid + k * kMegaThreads;
+        if (i < qd) v.a8[i] = static_cast<int8_t>(amax > 0.0f ? quantize_code(y[k], s_q) : 0);
+    }
+    if (tid == 0) v.scale[1] = s_q;
+    __syncthreads();
+    QTB_FINE(a, 24);
 }
 
 // Phase D: combine the chunks of every head (attention.rs:497-541), int8 codes for the o projection.
@@ -931,6 +1440,7 @@ __device__ __noinline__ bool phase_combine(const MegaArgs& a, int l, unsigned in
     const int tid = threadIdx.x, hd = a.head_dim, qd = a.q_heads * hd;
     float* s_pair = v.pair;
     const KvSplit ks = kv_split(a);
+    QTB_FINE(a, 21);
     // every chunk value of a thread's coordinates is requested before the factors are needed
     float amax = 0.0f;
     for (int base = 0; base < qd; base += 4 * kMegaThreads) {  // uniform trip count: the loop holds a barrier
@@ -970,6 +1480,7 @@ __device__ __noinline__ bool phase_combine(const MegaArgs& a, int l, unsigned in
                 if (which == 0) s_pair[a.q_heads * 8 + h * 4 + c] = s_chunk;
             }
             __syncthreads();  // the factors are written
+            QTB_FINE(a, 22);
         }
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
@@ -994,6 +1505,7 @@ __device__ __noinline__ bool phase_combine(const MegaArgs& a, int l, unsigned in
             amax = fmaxf(amax, fabsf(out));
         }
     }
+    QTB_FINE(a, 23);
     int n_all = qd;
     if (a.tp_world > 1) {
         // this rank's heads are a slice of the attention output: CTA p sends it to rank p, then every CTA takes the whole
@@ -1039,6 +1551,7 @@ __device__ __noinline__ bool phase_combine(const MegaArgs& a, int l, unsigned in
     for (int i = tid; i < n_all; i += kMegaThreads) v.a8[i] = static_cast<int8_t>(amax > 0.0f ? quantize_code(v.y[i], s_q) : 0);
     if (tid == 0) v.scale[1] = s_q;
     __syncthreads();
+    QTB_FINE(a, 24);
     return true;
 }
 
@@ -1202,6 +1715,8 @@ __device__ __noinline__ bool phase_head(const MegaArgs& a, unsigned int seq_base
     }
     cp_async_wait<0>();
     __syncthreads();
+    if (a.l2_prefetch && a.n_layers > 0)  // the next token starts with the first layer's attention projections
+        for (int k = 0; k < 3; ++k) prefetch_weights(v.layers[0], k);
     float* s_bv = v.sh_f;  // 32 floats: one candidate per warp
     unsigned int* s_bi = reinterpret_cast<unsigned int*>(v.sh_d);
     if (lane == 0) {
@@ -1263,6 +1778,8 @@ __device__ __noinline__ void phase_finish(const MegaArgs& a, unsigned int seq_ba
         a.pos[0] += 1;
         a.amax_bits[0] = 0u;
         a.amax_bits[1] = 0u;
+        a.amax_bits[2] = 0u;
+        a.amax_bits[3] = 0u;
     }
 }
 
@@ -1285,23 +1802,27 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const __g
             reinterpret_cast<uint32_t*>(v.layers)[i] = reinterpret_cast<const uint32_t*>(a.layers)[i];
         if (tid < 4) v.scale[tid] = 0.0f;
         __syncthreads();
+        if (a.l2_prefetch && a.n_layers > 0)
+            for (int k = 0; k < 3; ++k) prefetch_weights(v.layers[0], k);  // the first layer's q, k and v
     }
-    unsigned int bar_target = 0;
+    unsigned int bar_round = 0;
 #define MEGA_BARRIER()                                                                                   \
     do {                                                                                                 \
-        bar_target += static_cast<unsigned int>(G);                                                      \
-        if (!grid_barrier(a.bar, bar_target, a.status, mega_smem_views(smem, a).flag)) return;           \
+        if (!grid_barrier(a.bar, ++bar_round, a.status, mega_smem_views(smem, a).flag)) return;          \
     } while (0)
     int trace_n = 0;
 #define MEGA_TRACE()                                                                            \
     do {                                                                                        \
-        if (a.trace != nullptr && cta == 0 && tid == 0) a.trace[trace_n++] = global_timer_ns(); \
+        if (a.trace != nullptr && cta == 0 && tid == 0) a.trace[trace_n++] = static_cast<unsigned long long>(clock64()); \
     } while (0)
 #define MEGA_GEMV(k, acts, actf, qs, out)                                                                                        \
     do {                                                                                                                         \
         const MegaSmem v = mega_smem_views(smem, a);                                                                             \
         mega_gemv<BASE>(a.items, v.layers[l].first[k], v.layers[l].count[k], v.tab, acts, actf, qs, out);                         \
     } while (0)
+    // Stamps are the SM's cycle counter (reading it costs a few cycles; the global timer costs most of a microsecond per
+    // read); the global timer is read once at either end so that the host can convert cycles to nanoseconds.
+    if (a.trace != nullptr && cta == 0 && tid == 0) a.trace[a.n_layers * 14 + 4 + 32] = global_timer_ns();
     MEGA_TRACE();
     const bool tp = a.tp_world > 1;
     const unsigned int seq_base = tp ? __ldcg(a.tp_seq) : 0u;  // exchange numbers of this launch: seq_base + 4 l + 1..4, then + 4 L + 1
@@ -1315,11 +1836,19 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const __g
         phase_scores(a, l, smem);
         MEGA_TRACE();  // 4: scores done (this CTA)
         MEGA_BARRIER();
-        phase_values(a, l, smem);
-        MEGA_TRACE();  // 5: values done (this CTA)
-        MEGA_BARRIER();
-        MEGA_TRACE();  // 6
-        if (!phase_combine(a, l, seq_base + 4u * l + 1u, smem)) return;
+        if (a.attn_v2) {
+            phase_values2(a, l, smem);
+            MEGA_TRACE();  // 5: values and chunk combine done (this CTA)
+            MEGA_BARRIER();
+            MEGA_TRACE();  // 6
+            phase_combine2(a, l, smem);
+        } else {
+            phase_values(a, l, smem);
+            MEGA_TRACE();  // 5: values done (this CTA)
+            MEGA_BARRIER();
+            MEGA_TRACE();  // 6
+            if (!phase_combine(a, l, seq_base + 4u * l + 1u, smem)) return;
+        }
         MEGA_TRACE();  // 7: combine + quantise done
         MEGA_GEMV(1, v.a8, nullptr, 0.0f, a.acc_o);
         MEGA_BARRIER();
@@ -1352,6 +1881,8 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const __g
             }
             const float s_down = vmax > 0.0f ? __fdiv_rn(127.0f, vmax) : 0.0f;
             if (tid == 0) mega_smem_views(smem, a).scale[3] = s_down;
+            if (a.l2_prefetch && l + 1 < a.n_layers)  // the next layer's q, k and v while down streams from L2
+                for (int k = 0; k < 3; ++k) prefetch_weights(mega_smem_views(smem, a).layers[l + 1], k);
             MEGA_GEMV(3, nullptr, a.v_inter, s_down, a.acc_down);
             MEGA_TRACE();  // 13: down streamed (this CTA)
             for (int i = cta * kMegaThreads + tid; i < 2 * a.inter; i += G * kMegaThreads) a.acc_gu[i] = 0;  // consumed by SwiGLU
@@ -1364,6 +1895,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const __g
     MEGA_TRACE();  // head done (this CTA)
     MEGA_BARRIER();
     MEGA_TRACE();
+    if (a.trace != nullptr && cta == 0 && tid == 0) a.trace[a.n_layers * 14 + 4 + 33] = global_timer_ns();
     if (cta == 0) phase_finish(a, seq_base, smem);
 #undef MEGA_GEMV
 #undef MEGA_BARRIER
@@ -1371,13 +1903,13 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const __g
 }
 
 // Self-test of the barrier's give-up path (quintrit_b200_selftest_barrier): a few CTAs, all resident, wait at a barrier
-// whose target is one arrival more than the grid can deliver, with a short poll limit. The wait runs out, status becomes
+// whose target is twice the arrivals the grid can deliver, with a short poll limit. The wait runs out, status becomes
 // 2, the failure bit releases the other waiters, and a second barrier returns false at once. out[cta] = 1 for every CTA
 // whose two barriers both reported the failure. Nothing faults and nothing spins beyond the limit.
 __global__ void barrier_selftest_kernel(unsigned int* bar, unsigned int* status, unsigned int spin_limit, unsigned int* out) {
     __shared__ int s_flag;
-    const bool first = grid_barrier(bar, gridDim.x + 1u, status, &s_flag, spin_limit);
-    const bool second = grid_barrier(bar, 2u * gridDim.x + 2u, status, &s_flag, spin_limit);
+    const bool first = grid_barrier(bar, 2u, status, &s_flag, spin_limit);   // round 2 at the first barrier: twice the arrivals there are
+    const bool second = grid_barrier(bar, 4u, status, &s_flag, spin_limit);
     if (threadIdx.x == 0) out[blockIdx.x] = (!first && !second) ? 1u : 0u;
 }
 

@@ -95,7 +95,7 @@ def _value(v) -> bytes:
 def write_gguf(path, metadata: dict, tensors) -> None:
     """`tensors`: iterable of (name, dims innermost first, ggml type, payload bytes). Payloads start on multiples of 32
     bytes inside the data section; a payload may be longer than the tensor's nominal size (the scale behind I2_S)."""
-    tensors = list(tensors)
+    tensors = [(name, dims, ggml_type, memoryview(payload).cast("B")) for name, dims, ggml_type, payload in tensors]  # bytes or contiguous arrays
     head = bytearray(b"GGUF") + struct.pack("<IQQ", 3, len(tensors), len(metadata))
     for key, value in metadata.items():
         head += _string(key) + _value(value)
@@ -109,8 +109,8 @@ def write_gguf(path, metadata: dict, tensors) -> None:
     with open(path, "wb") as f:
         f.write(head)
         for _, _, _, payload in tensors:
-            raw = bytes(payload)
-            f.write(raw + b"\0" * (-len(raw) % ALIGNMENT))
+            f.write(payload)
+            f.write(b"\0" * (-len(payload) % ALIGNMENT))
 
 
 def write_model_gguf(path, spec: dict, trits: list, encoding: int = GGML_I2_S, architecture: str = "llama", name: str = "synthetic") -> None:
@@ -158,3 +158,90 @@ def write_model_gguf(path, spec: dict, trits: list, encoding: int = GGML_I2_S, a
     if spec.get("lm_head") is not None:
         tensors.append(("output.weight", (H, spec["vocab"]), table_type, np.ascontiguousarray(spec["lm_head"], np.uint16).tobytes()))
     write_gguf(path, meta, tensors)
+
+
+# ---- the same encodings on a torch device, and full-size model files -------------------------------------------------
+
+def torch_encode(encoding: int, digits, d_bits: int = 0x3800, block_scales=None):
+    """Payload (uint8 tensor on the digits' device) of a [rows, cols] tensor of digits trit + 1 in `encoding`; the same bytes
+    as the numpy encoders above. d_bits: the F16 scale every TQ block carries; block_scales: float tensor, one per 64 weights."""
+    import torch
+
+    rows, cols = digits.shape
+    d = digits.to(torch.int32)
+    if encoding == GGML_I2_S:
+        t = d.view(rows, cols // 128, 4, 32)
+        return ((t[:, :, 0] << 6) | (t[:, :, 1] << 4) | (t[:, :, 2] << 2) | t[:, :, 3]).to(torch.uint8).reshape(-1)
+    if encoding == GGML_TQ2_0:
+        t = d.view(-1, 2, 4, 32)
+        q = (t[:, :, 0] | (t[:, :, 1] << 2) | (t[:, :, 2] << 4) | (t[:, :, 3] << 6)).to(torch.uint8).reshape(-1, 64)
+        blocks = torch.empty((q.shape[0], 66), dtype=torch.uint8, device=digits.device)
+        blocks[:, :64] = q
+        blocks[:, 64], blocks[:, 65] = d_bits & 0xFF, d_bits >> 8
+        return blocks.reshape(-1)
+    if encoding == GGML_TQ1_0:
+        t = d.view(-1, 256)
+        nb = t.shape[0]
+        blocks = torch.empty((nb, 54), dtype=torch.uint8, device=digits.device)
+        a, b, c = t[:, :160].reshape(nb, 5, 32), t[:, 160:240].reshape(nb, 5, 16), t[:, 240:].reshape(nb, 4, 4)
+        blocks[:, :32] = ((sum(a[:, n] * 3 ** (4 - n) for n in range(5)) * 256 + 242) // 243).to(torch.uint8)
+        blocks[:, 32:48] = ((sum(b[:, n] * 3 ** (4 - n) for n in range(5)) * 256 + 242) // 243).to(torch.uint8)
+        blocks[:, 48:52] = ((sum(c[:, n] * 3 ** (3 - n) for n in range(4)) * 3 * 256 + 242) // 243).to(torch.uint8)
+        blocks[:, 52], blocks[:, 53] = d_bits & 0xFF, d_bits >> 8
+        return blocks.reshape(-1)
+    if encoding == GGML_Q2_0:
+        t = d.view(-1, 16, 4)
+        out = torch.empty((t.shape[0], 18), dtype=torch.uint8, device=digits.device)
+        out[:, :2] = block_scales.to(torch.float16).view(torch.uint8).reshape(-1, 2)
+        out[:, 2:] = (t[:, :, 0] | (t[:, :, 1] << 2) | (t[:, :, 2] << 4) | (t[:, :, 3] << 6)).to(torch.uint8)
+        return out.reshape(-1)
+    raise ValueError(f"no encoder for GGML type {encoding}")
+
+
+def write_full_model_gguf(path, shape: str, encoding: int, device, ctx: int, bf16_tables: bool = False, layers: int | None = None) -> dict:
+    """Writes the named full-size model (quintrit_b200.synth.full_model: "falcon3_10b" or "bitnet_2b", every value
+    machine-independent) as a GGUF file with its projections in `encoding`, building and encoding every tensor on `device`.
+    I2_S files carry float32 tensor scales, TQ1_0 / TQ2_0 files the same scales rounded to F16 in every block, Q2_0 files one
+    F16 scale per 64 weights. Returns the model's dimensions."""
+    import torch
+
+    from . import synth
+
+    d = synth.full_dims(shape, layers)
+    variant = {GGML_I2_S: "i2_s", GGML_TQ1_0: "tq", GGML_TQ2_0: "tq", GGML_Q2_0: "q2_0"}[encoding]
+    a, H, L = d["gguf_arch"], d["hidden"], d["layers"]
+    meta = {
+        "general.architecture": a, "general.name": d["name"], "general.alignment": ALIGNMENT,
+        f"{a}.vocab_size": d["vocab"], f"{a}.embedding_length": H, f"{a}.feed_forward_length": d["inter"], f"{a}.block_count": L,
+        f"{a}.attention.head_count": d["q_heads"], f"{a}.attention.head_count_kv": d["kv_heads"], f"{a}.attention.key_length": d["head_dim"],
+        f"{a}.attention.layer_norm_rms_epsilon": float(d["eps"]), f"{a}.rope.freq_base": float(d["rope_theta"]),
+        f"{a}.rope.dimension_count": d["rope_dims"], f"{a}.context_length": ctx,
+    }
+    config = d["config"]
+    table_type = GGML_BF16 if bf16_tables else GGML_F16
+    tensors = [("token_embd.weight", (H, d["vocab"]), table_type, synth.torch_table_bits(synth.seed_for(config, 255, 0, 0), d["vocab"] * H, bf16_tables, device).data)]
+    names = ["attn_q", "attn_k", "attn_v", "attn_output", "ffn_gate", "ffn_up", "ffn_down"]
+    ones = lambda n: np.ones(n, np.float32).data  # noqa: E731
+    qd = d["q_heads"] * d["head_dim"]
+    for l in range(L):
+        for k, (rows, cols) in enumerate(d["shapes"]):
+            digits = synth.torch_digits(synth.seed_for(config, l, k, 0), rows, cols, device)
+            scale = synth.full_scale(config, l, k, variant)
+            if encoding == GGML_Q2_0:
+                bsc = torch.from_numpy(synth.torch_block_scales(synth.seed_for(config, l, k, 1), rows * cols // 64, device)).to(device)
+                payload = torch_encode(encoding, digits, block_scales=bsc).cpu().numpy().data
+            elif encoding == GGML_I2_S:
+                payload = memoryview(torch_encode(encoding, digits).cpu().numpy().tobytes() + struct.pack("<f", float(scale)))
+            else:
+                payload = torch_encode(encoding, digits, d_bits=int(np.float16(scale).view(np.uint16))).cpu().numpy().data
+            tensors.append((f"blk.{l}.{names[k]}.weight", (cols, rows), encoding, payload))
+        tensors.append((f"blk.{l}.attn_norm.weight", (H,), GGML_F32, ones(H)))
+        tensors.append((f"blk.{l}.ffn_norm.weight", (H,), GGML_F32, ones(H)))
+        if d["arch"] == 1:
+            tensors.append((f"blk.{l}.attn_sub_norm.weight", (qd,), GGML_F32, ones(qd)))
+            tensors.append((f"blk.{l}.ffn_sub_norm.weight", (d["inter"],), GGML_F32, ones(d["inter"])))
+    tensors.append(("output_norm.weight", (H,), GGML_F32, ones(H)))
+    if not d["tied"]:
+        tensors.append(("output.weight", (H, d["vocab"]), table_type, synth.torch_table_bits(synth.seed_for(config, 255, 1, 0), d["vocab"] * H, bf16_tables, device).data))
+    write_gguf(path, meta, tensors)
+    return d
