@@ -969,7 +969,8 @@ int decoder_create_impl(const quintrit_b200_decoder_desc_t* desc, quintrit_b200_
     int smem_optin = 0;
     QTB_CUDA(cudaDeviceGetAttribute(&smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, d->device));
     // the second form of the attention's second half (units that take all chunks of 8 coordinates) where its arrays fit
-    d->attn_v2 = tp_world == 1 && d->ctx <= static_cast<uint32_t>(kV2MaxCtx) && gqa_n <= kV2MaxGqa && qd_full <= size_t(kNormPer) * kMegaThreads && hd % kV2Dims == 0;
+    d->attn_v2 = tp_world == 1 && d->ctx <= static_cast<uint32_t>(kV2MaxCtx) && gqa_n <= kV2MaxGqa && qd_full <= size_t(kNormPer) * kMegaThreads && hd % kV2Dims == 0 &&
+                 d->kv_heads * (hd / kV2Dims) < static_cast<uint32_t>(d->sm_count);  // some CTAs must stay free to compute the softmax factors
     if (const char* v2 = std::getenv("QUINTRIT_B200_ATTN_V2")) d->attn_v2 = d->attn_v2 && v2[0] != '0';  // experiments: "0" keeps the first form
     auto bytes_for = [&](bool v2) {
         return mega_smem_bytes(mega_attn_region(d->ctx, gqa_n, hd, v2), static_cast<int>(std::max<size_t>(H, qd_full)), static_cast<int>(H), static_cast<int>(L));
@@ -1033,6 +1034,11 @@ int mega_setup(quintrit_b200_decoder* d, const quintrit_b200_decoder_desc_t* des
         (rc = dev_alloc(d, &d->bar, 16)) != QUINTRIT_OK || (rc = dev_alloc(d, &d->trace, size_t(L) * 14 + 4 + 32 + 2)) != QUINTRIT_OK ||
         (rc = dev_alloc(d, &d->scores, size_t(d->q_heads) * d->ctx)) != QUINTRIT_OK || (rc = dev_alloc(d, &d->attn_out, size_t(qd))) != QUINTRIT_OK)
         return rc;
+    const int fac_stride = values2_clp(d->ctx >= 512 ? (d->ctx + 3) / 4 : d->ctx);
+    if (d->attn_v2 && ((rc = dev_alloc(d, &d->fac, size_t(2) * d->q_heads * 4 * fac_stride)) != QUINTRIT_OK ||
+                       (rc = dev_alloc(d, &d->fac_flags, size_t(d->q_heads) * 4 * (fac_stride / 8))) != QUINTRIT_OK ||
+                       (rc = dev_alloc(d, &d->fac_M, size_t(d->q_heads) * 4)) != QUINTRIT_OK || (rc = dev_alloc(d, &d->fac_done, size_t(d->kv_heads))) != QUINTRIT_OK))
+        return rc;
     std::vector<GemvItem> items;
     std::vector<MegaLayer> layers(L);
     for (int l = 0; l < L; ++l) {
@@ -1075,6 +1081,7 @@ int mega_setup(quintrit_b200_decoder* d, const quintrit_b200_decoder_desc_t* des
     a.v_inter = d->v_inter, a.amax_bits = d->amax_bits, a.part_acc = d->part_acc, a.part_ms = d->part_ms, a.logits = d->logits;
     a.scores = d->scores, a.attn_region = static_cast<unsigned int>(mega_attn_region(d->ctx, d->q_heads / d->kv_heads, d->head_dim, d->attn_v2));
     a.attn_v2 = d->attn_v2 ? 1 : 0, a.attn_out = d->attn_out;
+    a.fac = d->fac, a.fac_flags = d->fac_flags, a.fac_M = d->fac_M, a.fac_done = d->fac_done, a.fac_stride = fac_stride;
     a.bf16_tables = d->bf16_tables ? 1 : 0;
     a.l2_prefetch = 1;
     if (const char* pf = std::getenv("QUINTRIT_B200_L2_PREFETCH")) a.l2_prefetch = pf[0] != '0';  // experiments: "0" keeps the cold streams

@@ -42,6 +42,8 @@ struct quintrit_b200_decoder {
     unsigned int *amax_bits, *best_idx, *bar;
     bool attn_v2 = false;
     float* attn_out = nullptr;
+    float *fac = nullptr, *fac_M = nullptr;
+    unsigned int *fac_flags = nullptr, *fac_done = nullptr;
     unsigned long long* trace;  // phase timestamps of the last traced step (13 per layer + 3)
     cudaStream_t stream;
     cudaGraphExec_t graph_step;               // one token: embed ... argmax (token and position read from device memory)

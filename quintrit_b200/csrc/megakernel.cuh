@@ -71,6 +71,15 @@ struct MegaArgs {
     // number) pairs that the readers poll.
     int attn_v2;               // attention second half by (KV head, 8 coordinates) units that also combine the chunks
     float* attn_out;           // their result: the attention output before the o projection's quantiser (q_dim floats)
+    // Softmax factors of the current token, computed once per (head, chunk) by the CTAs that have no values unit and read by
+    // every unit of the head's group: rows of fac_stride floats, ms rows of all (head, chunk slot) first, then the vs rows;
+    // one word of move flags per (head, chunk slot, group of eight positions); the maximum of every (head, chunk slot);
+    // fac_done[kv head] counts the (head, chunk) tasks finished since the token began.
+    float* fac;
+    unsigned int* fac_flags;
+    float* fac_M;
+    unsigned int* fac_done;
+    int fac_stride;
     int l2_prefetch;           // request the weights of later phases into L2 ahead of their streams (QUINTRIT_B200_L2_PREFETCH=0 switches it off)
     int bf16_tables;           // embedding and output head hold BF16 instead of F16 bit patterns
     int neox;                  // BitNet: RoPE pairs (i, i + rope_dims / 2) instead of (2i, 2i + 1) (config.rs:464-467)
@@ -839,9 +848,10 @@ __device__ __noinline__ void mega_values_unit(const MegaArgs& a, const MegaLayer
 // barrier, the maximum before the group from the earlier groups' maxima, then one exponential per position. A word per
 // head and group of eight positions tells whether any chunk's running maximum moved there; groups without a move run
 // branch-free.
-constexpr int kV2Dims = 16;  // two coordinates per lane: their chains interleave, which hides most of a step's latency
+constexpr int kV2Dims = 16;      // coordinates per unit: two warps of eight coordinates x four chunks per query head
+constexpr int kV2WarpsPerHead = kV2Dims / 8;
 constexpr int kV2MaxCtx = 4096;
-constexpr int kV2MaxGqa = 12;  // chain warps + sum warps must fit the 16 warps of the CTA
+constexpr int kV2MaxGqa = 7;     // chain warps (two per head) + the warp of the sum chains must fit the 16 warps of the CTA
 
 // Row length (floats) of the factor rows for chunks of `chunk` positions: a multiple of 8, at least `chunk`.
 __host__ __device__ constexpr int values2_clp(int chunk) { return (chunk + 7) / 8 * 8; }
@@ -851,7 +861,7 @@ __host__ __device__ constexpr int values2_clr(int chunk) { return values2_clp(ch
 __host__ __device__ constexpr size_t values2_bytes(int ctx, int gqa) {
     const int nch = ctx >= 512 ? 4 : 1, chunk = ctx >= 512 ? (ctx + 3) / 4 : ctx, clp = values2_clp(chunk);
     return static_cast<size_t>(nch) * values2_clr(chunk) * kV2Dims * 2 + static_cast<size_t>(2) * gqa * nch * clp * 4 + static_cast<size_t>(gqa) * (clp / 8) * 4 +
-           static_cast<size_t>(gqa) * nch * (clp / 8) * 4 + static_cast<size_t>(gqa) * nch * 8 + 64;
+           static_cast<size_t>(gqa) * 8 * 4 + static_cast<size_t>(gqa) * nch * 8 + 64;
 }
 
 template <bool F32>
@@ -859,56 +869,64 @@ __device__ __forceinline__ float v2_round(float x) {
     return F32 ? x : __half2float(__float2half_rn(x));
 }
 
-// The two chains of one lane (two neighbouring coordinates of one head and chunk): `ngr` groups of eight positions in order;
-// values (a pair of halves every 32 bytes), factors vs and ms and the move flags (one word per group) at byte offsets into
-// the dynamic shared memory. The operands of the next group are loaded while this group's eight dependent steps run, and
-// the two chains' steps alternate, so that one's latency covers the other's. Rounded to half precision after every
-// operation unless F32 (attention.rs:448-470).
+// The chain of one lane: `ngr` groups of eight positions in order; values (one half every 32 bytes), factors vs and ms and
+// the table of next groups with a move (16 bits per group) at byte offsets into the dynamic shared memory. The operands of the next group are
+// loaded while this group's eight dependent steps run. One chain per lane and more warps, rather than several chains per
+// lane: a warp issues an instruction every three to four cycles here, so the instructions per step, not the latency of a
+// step (16 cycles), set the pace. Rounded to half precision after every operation unless F32 (attention.rs:448-470).
 template <bool F32>
-__device__ __noinline__ float2 v2_chain(uint32_t v_off, uint32_t w_off, uint32_t m_off, uint32_t f_off, int ngr) {
+__device__ __noinline__ float v2_chain(uint32_t v_off, uint32_t w_off, uint32_t m_off, uint32_t f_off, int ngr) {
     unsigned char* base = dyn_smem();
     const unsigned char* vrow = base + v_off;
     const float* wrow = reinterpret_cast<const float*>(base + w_off);
     const float* mrow = reinterpret_cast<const float*>(base + m_off);
-    const unsigned int* fl = reinterpret_cast<const unsigned int*>(base + f_off);
-    float a0 = 0.0f, a1 = 0.0f;
+    const unsigned char* fl = base + f_off;
+    float acc = 0.0f;
     // The group after the last one is loaded too and not used: it lies in the padding or in the arrays behind the rows.
-    __half2 vn[8];
+    __half vn[8];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) vn[j] = *reinterpret_cast<const __half2*>(vrow + j * (kV2Dims * 2));
+    for (int j = 0; j < 8; ++j) vn[j] = *reinterpret_cast<const __half*>(vrow + j * (kV2Dims * 2));
     float4 w0n = *reinterpret_cast<const float4*>(wrow), w1n = *reinterpret_cast<const float4*>(wrow + 4);
-    unsigned int fn = fl[0];
-    for (int grp = 0; grp < ngr; ++grp) {
-        float2 v[8];
+    // `nx[g]` is the first group at or after g in which some chunk's running maximum moved (ngr if none). Up to there the loop
+    // has no branch but its own, so the compiler overlaps the loads of the next group with the eight dependent steps.
+    const unsigned short* nx = reinterpret_cast<const unsigned short*>(fl);
+    int grp = 0;
+    while (grp < ngr) {
+        const int stop = min(static_cast<int>(nx[grp]), ngr);
+        for (; grp < stop; ++grp) {
+            float v[8];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) v[j] = __half22float2(vn[j]);
-        const float w[8] = {w0n.x, w0n.y, w0n.z, w0n.w, w1n.x, w1n.y, w1n.z, w1n.w};
-        const unsigned int f = fn;
+            for (int j = 0; j < 8; ++j) v[j] = __half2float(vn[j]);
+            const float w[8] = {w0n.x, w0n.y, w0n.z, w0n.w, w1n.x, w1n.y, w1n.z, w1n.w};
 #pragma unroll
-        for (int j = 0; j < 8; ++j) vn[j] = *reinterpret_cast<const __half2*>(vrow + (8 * (grp + 1) + j) * (kV2Dims * 2));
-        w0n = *reinterpret_cast<const float4*>(wrow + 8 * (grp + 1));
-        w1n = *reinterpret_cast<const float4*>(wrow + 8 * (grp + 1) + 4);
-        fn = fl[grp + 1];
-        if (f == 0) {
+            for (int j = 0; j < 8; ++j) vn[j] = *reinterpret_cast<const __half*>(vrow + (8 * (grp + 1) + j) * (kV2Dims * 2));
+            w0n = *reinterpret_cast<const float4*>(wrow + 8 * (grp + 1));
+            w1n = *reinterpret_cast<const float4*>(wrow + 8 * (grp + 1) + 4);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc = v2_round<F32>(__fmaf_rn(v[j], w[j], acc));
+        }
+        if (grp < ngr) {
+            // a group with a move: its rescale factors are loaded once; the multiply of a position is skipped where this lane's
+            // chunk did not move (a factor of one would change nothing, but cost a step's latency)
+            float v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = __half2float(vn[j]);
+            const float w[8] = {w0n.x, w0n.y, w0n.z, w0n.w, w1n.x, w1n.y, w1n.z, w1n.w};
+            const float4 m0 = *reinterpret_cast<const float4*>(mrow + grp * 8), m1 = *reinterpret_cast<const float4*>(mrow + grp * 8 + 4);
+            const float m[8] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
+#pragma unroll
+            for (int j = 0; j < 8; ++j) vn[j] = *reinterpret_cast<const __half*>(vrow + (8 * (grp + 1) + j) * (kV2Dims * 2));
+            w0n = *reinterpret_cast<const float4*>(wrow + 8 * (grp + 1));
+            w1n = *reinterpret_cast<const float4*>(wrow + 8 * (grp + 1) + 4);
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
-                a0 = v2_round<F32>(__fmaf_rn(v[j].x, w[j], a0));
-                a1 = v2_round<F32>(__fmaf_rn(v[j].y, w[j], a1));
+                if (m[j] != 1.0f) acc = v2_round<F32>(__fmul_rn(acc, m[j]));
+                acc = v2_round<F32>(__fmaf_rn(v[j], w[j], acc));
             }
-        } else {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                if ((f >> j) & 1u) {  // some chunk's maximum moved here; a factor of one changes nothing
-                    const float ms = mrow[grp * 8 + j];
-                    a0 = v2_round<F32>(__fmul_rn(a0, ms));
-                    a1 = v2_round<F32>(__fmul_rn(a1, ms));
-                }
-                a0 = v2_round<F32>(__fmaf_rn(v[j].x, w[j], a0));
-                a1 = v2_round<F32>(__fmaf_rn(v[j].y, w[j], a1));
-            }
+            ++grp;
         }
     }
-    return make_float2(a0, a1);
+    return acc;
 }
 
 // S of one (head, chunk): S = fma(S, ms, vs) over its positions in order (attention.rs:466), operands one group ahead.
@@ -935,17 +953,107 @@ __device__ __noinline__ float v2_sum_chain(uint32_t m_off, uint32_t w_off, int l
         m0 = n0, m1 = n1, v0 = u0, v1 = u1;
     }
     for (int p = full * 8; p < len; ++p) S = __fmaf_rn(S, ms_row[p], vs_row[p]);
-#ifdef QTB_DEBUG_V2_PRINT
-    printf("sum_chain m_off %u w_off %u len %d full %d S %g ms0 %g vs0 %g\n", m_off, w_off, len, full, S, ms_row[0], vs_row[0]);
-#endif
     return S;
+}
+
+// One helper task of the values phase: the softmax factors of head `h`, chunk `c` (attention.rs:448-462), two consecutive
+// positions per thread. The running maximum before a position comes from a scan over the block; then one exponential per
+// position: ms = exp(m_before - score), vs = 1 where the score exceeds the maximum so far, else ms = 1, vs = exp(score -
+// m_before). Positions behind the chunk's end up to the common chain length get vs = 0, ms = 1: such a step leaves a sum
+// unchanged bit for bit. Rows, move flags (bit j of a word: the maximum moved at position 8 group + j, and by a factor other
+// than one) and the chunk's maximum go to global memory; the count of finished tasks of the KV head is raised last.
+__device__ __noinline__ void v2_factors_task(const MegaArgs& a, int h, int c, unsigned char* smem) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const KvSplit ks = kv_split(a);
+    const int nch = ks.split ? 4 : 1, CL = ks.chunk, seq = ks.seq_len;
+    auto chunk_len = [&](int cc) {
+        if (!ks.split) return cc == 0 ? seq : 0;
+        const int start = cc * CL;
+        return max(0, min(min(start + CL, ks.n_kv), seq) - start);
+    };
+    int ngr = 0;
+    for (int cc = 0; cc < nch; ++cc) ngr = max(ngr, (chunk_len(cc) + 7) / 8);
+    const int len = chunk_len(c), slot = h * 4 + c;
+    const float* src = a.scores + static_cast<size_t>(h) * a.ctx + c * CL;
+    float* ms_out = a.fac + static_cast<size_t>(slot) * a.fac_stride;
+    float* vs_out = a.fac + static_cast<size_t>(a.q_heads * 4 + slot) * a.fac_stride;
+    unsigned int* fl_out = a.fac_flags + static_cast<size_t>(slot) * (a.fac_stride / 8);
+    float* s_wt = reinterpret_cast<float*>(smem);  // one maximum per warp
+    // chunks of up to 512 positions: one position per thread; up to 1024: two consecutive ones
+    const bool two = ngr * 8 > kMegaThreads;
+    const int p0 = two ? 2 * tid : tid, p1 = p0 + 1;
+    const float s0 = p0 < len ? __ldcg(src + p0) : -INFINITY, s1 = two && p1 < len ? __ldcg(src + p1) : -INFINITY;
+    float incl = fmaxf(s0, s1);
+    for (int o = 1; o < 32; o <<= 1) {
+        const float t = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl = fmaxf(incl, t);
+    }
+    float before = __shfl_up_sync(0xffffffffu, incl, 1);
+    if (lane == 0) before = -INFINITY;
+    __syncthreads();  // the table region is free
+    if (lane == 31) s_wt[warp] = incl;
+    __syncthreads();
+    float total = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kMegaWarps; ++w) {
+        const float t = s_wt[w];
+        if (w < warp) before = fmaxf(before, t);
+        total = fmaxf(total, t);
+    }
+    auto factor = [&](int p, float sc, float m_before, float& ms, float& vs) {
+        ms = 1.0f, vs = 0.0f;
+        bool moved = false;
+        if (p < len) {
+            vs = 1.0f;
+            if (sc > m_before) {
+                ms = device_expf(__fsub_rn(m_before, sc));
+                moved = ms != 1.0f;  // exp(0) = 1: a maximum that moved by nothing needs no rescale
+            } else {
+                vs = device_expf(__fsub_rn(sc, m_before));
+            }
+        }
+        return moved;
+    };
+    float ms0, vs0, ms1 = 1.0f, vs1 = 0.0f;
+    const bool mv0 = factor(p0, s0, before, ms0, vs0);
+    bool mv1 = false;
+    if (two) mv1 = factor(p1, s1, fmaxf(before, s0), ms1, vs1);
+    const unsigned int b0 = __ballot_sync(0xffffffffu, mv0), b1 = __ballot_sync(0xffffffffu, mv1);
+    if (two) {
+        if (p0 < ngr * 8) {
+            *reinterpret_cast<float2*>(ms_out + p0) = make_float2(ms0, ms1);
+            *reinterpret_cast<float2*>(vs_out + p0) = make_float2(vs0, vs1);
+        }
+        if ((lane & 3) == 0) {  // four lanes = eight positions = one group
+            unsigned int bits = 0;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) bits |= (((b0 >> (lane + i)) & 1u) << (2 * i)) | (((b1 >> (lane + i)) & 1u) << (2 * i + 1));
+            const int grp = warp * 8 + (lane >> 2);
+            if (grp < ngr) fl_out[grp] = bits;
+        }
+    } else {
+        if (p0 < ngr * 8) {
+            ms_out[p0] = ms0;
+            vs_out[p0] = vs0;
+        }
+        if ((lane & 7) == 0) {  // eight lanes = one group
+            const int grp = warp * 4 + (lane >> 3);
+            if (grp < ngr) fl_out[grp] = (b0 >> lane) & 0xFFu;
+        }
+    }
+    if (tid == 0) a.fac_M[slot] = total;
+    __syncthreads();
+    if (tid == 0) {
+        __threadfence();
+        atomicAdd(a.fac_done + h / (a.q_heads / a.kv_heads), 1u);
+    }
 }
 
 #ifdef QTB_DEBUG_V2
 __device__ long long g_v2_clock[16];
 #define QTB_V2_CLOCK(k)                                  \
     do {                                                 \
-        if (threadIdx.x == 0) g_v2_clock[k] = clock64(); \
+        if (threadIdx.x == 0 && blockIdx.x == 0) g_v2_clock[k] = clock64(); \
     } while (0)
 #else
 #define QTB_V2_CLOCK(k) \
@@ -964,9 +1072,10 @@ __device__ __noinline__ void mega_values2_unit(const MegaArgs& a, const MegaLaye
     unsigned char* Vr = smem;                                                            // [nch][clr][16 halves]
     float* f_ms = reinterpret_cast<float*>(smem + static_cast<size_t>(nch) * clr * kPiece);  // [gqa][nch][clp]
     float* f_vs = f_ms + npairs * clp;                                                   // scores, then vs
-    unsigned int* s_moved = reinterpret_cast<unsigned int*>(f_vs + npairs * clp);        // [gqa][ngr8]
-    float* s_gmax = reinterpret_cast<float*>(s_moved + gqa * ngr8);                      // [gqa * nch][ngr8]: maxima of the groups
-    float* s_MS = s_gmax + npairs * ngr8;                                                // [gqa][nch][2]: M, S
+    unsigned short* s_next = reinterpret_cast<unsigned short*>(f_vs + npairs * clp);     // [gqa][ngr8 + 2]: next group with a move
+    float* s_scale = reinterpret_cast<float*>(s_next + gqa * (ngr8 + 2) + ((gqa * (ngr8 + 2)) & 1));  // [gqa][4][2]: chunk-combine factors
+    float* s_MS = s_scale + gqa * 8;                                                     // [gqa][nch][2]: M, S
+    int* s_ok = reinterpret_cast<int*>(s_MS + npairs * 2);
     auto chunk_len = [&](int c) {
         if (!ks.split) return c == 0 ? seq : 0;
         const int start = c * CL;
@@ -983,89 +1092,95 @@ __device__ __noinline__ void mega_values2_unit(const MegaArgs& a, const MegaLaye
             const int p = i >> 1, h = i & 1, c = ks.split ? p / CL : 0;
             cp_async16(Vr + static_cast<size_t>(c * clr + (p - c * CL)) * kPiece + h * 16, vsrc + static_cast<size_t>(p) * kvd + h * 8);
         }
-        // the scores of a (head, chunk) are contiguous in the score buffer and 16-byte aligned (chunks start on multiples of 64)
-        for (int pair = warp; pair < npairs; pair += kMegaWarps) {
-            const int g = pair / nch, c = pair - g * nch, len = chunk_len(c);
-            const float* src = a.scores + static_cast<size_t>(kvh * gqa + g) * a.ctx + c * CL;
-            for (int q = lane; q * 4 < len; q += 32) cp_async16(f_vs + pair * clp + q * 4, src + q * 4);
-        }
         cp_async_commit();
-        for (int i = tid; i < gqa * ngr8; i += kMegaThreads) s_moved[i] = 0u;
         // zero values behind a chunk's end up to the common chain length (the last chunk, mostly)
         for (int c = 0; c < nch; ++c)
             for (int i = chunk_len(c) * 2 + tid; i < ngr * 16; i += kMegaThreads) *reinterpret_cast<uint4*>(Vr + static_cast<size_t>(c * clr) * kPiece + i * 16) = make_uint4(0u, 0u, 0u, 0u);
-        cp_async_wait<0>();
-    }
-    __syncthreads();
-    QTB_FINE(a, 2);
-    QTB_V2_CLOCK(1);
-    // softmax factors, a task = (head, chunk, group of eight positions): first the maximum of every group
-    const int ntasks = npairs * ngr;
-    for (int t = tid; t < ntasks; t += kMegaThreads) {
-        const int pair = t / ngr, grp = t - pair * ngr, len = chunk_len(pair % nch);
-        const float* sc = f_vs + pair * clp + grp * 8;
-        float m = -INFINITY;
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-            if (grp * 8 + j < len) m = fmaxf(m, sc[j]);
-        s_gmax[pair * ngr8 + grp] = m;
-    }
-    __syncthreads();
-    QTB_FINE(a, 4);
-    QTB_V2_CLOCK(2);
-    // then the running maximum before the group, and per position ms = exp(m_before - score), vs = 1 where the score exceeds
-    // the maximum so far, else ms = 1, vs = exp(score - m_before); behind a chunk's end vs = 0, ms = 1 (such a step leaves a
-    // sum unchanged bit for bit)
-    for (int t = tid; t < ntasks; t += kMegaThreads) {
-        const int pair = t / ngr, grp = t - pair * ngr, len = chunk_len(pair % nch);
-        float run = -INFINITY;
-        for (int q = 0; q < grp; ++q) run = fmaxf(run, s_gmax[pair * ngr8 + q]);
-        float* sc = f_vs + pair * clp + grp * 8;
-        float* msr = f_ms + pair * clp + grp * 8;
-        float ms[8], vs[8];
-        unsigned int bits = 0;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            ms[j] = 1.0f, vs[j] = 0.0f;
-            if (grp * 8 + j < len) {
-                const float s_j = sc[j];
-                vs[j] = 1.0f;
-                if (s_j > run) {
-                    ms[j] = device_expf(__fsub_rn(run, s_j));
-                    run = s_j;
-                    bits |= 1u << j;
-                } else {
-                    vs[j] = device_expf(__fsub_rn(s_j, run));
+        // The factors of this group's heads come from the helper CTAs of this phase (v2_factors_task): wait, bounded, until
+        // all (head, chunk) tasks of the KV head have been counted.
+        if (tid == 0) {
+            const unsigned int target = static_cast<unsigned int>(l + 1) * static_cast<unsigned int>(npairs);
+            int okay = 1;
+            for (unsigned int spins = 0;; ++spins) {
+                unsigned int v;
+                asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(a.fac_done + kvh));
+                if (v >= target) break;
+                if (spins > kBarrierSpinLimit || *reinterpret_cast<volatile unsigned int*>(a.bar) >= kBarFail) {
+                    report_failure(a.bar, a.status, 2u);
+                    okay = 0;
+                    break;
                 }
             }
+            *s_ok = okay;
         }
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            msr[j] = ms[j];
-            sc[j] = vs[j];
-            if (ms[j] == 1.0f) bits &= ~(1u << j);  // exp(0) = 1: a maximum that moved by nothing needs no rescale
+    }
+    __syncthreads();
+    if (*s_ok == 0) return;  // the grid barrier that follows ends the kernel
+    QTB_FINE(a, 2);
+    QTB_V2_CLOCK(1);
+    {
+        const int rows4 = a.q_heads * 4, fl_stride = a.fac_stride / 8;
+        for (int pair = warp; pair < npairs; pair += kMegaWarps) {
+            const int g = pair / nch, c = pair - g * nch, slot = (kvh * gqa + g) * 4 + c;
+            const float* ms_src = a.fac + static_cast<size_t>(slot) * a.fac_stride;
+            const float* vs_src = a.fac + static_cast<size_t>(rows4 + slot) * a.fac_stride;
+            for (int q = lane; q < ngr * 2; q += 32) {
+                cp_async16(f_ms + pair * clp + q * 4, ms_src + q * 4);
+                cp_async16(f_vs + pair * clp + q * 4, vs_src + q * 4);
+            }
         }
-        if (bits) atomicOr(s_moved + (pair / nch) * ngr8 + grp, bits);
-        if (grp == ngr - 1) s_MS[pair * 2] = run;  // the maximum of the whole chunk (-inf for an empty one)
+        cp_async_commit();
+        // For every head and group the first group at or after it in which any chunk moved (the chain runs branch-free up to
+        // there): one warp per head, 32 groups at a time from the end with the carry of the later groups.
+        for (int g = warp; g < gqa; g += kMegaWarps) {
+            unsigned short* nx = s_next + g * (ngr8 + 2);
+            int carry = ngr;
+            if (lane == 0) nx[ngr] = static_cast<unsigned short>(ngr);
+            for (int hi = (ngr + 31) / 32 * 32; hi > 0; hi -= 32) {
+                const int grp = hi - 32 + lane;
+                unsigned int bits = 0;
+                if (grp < ngr)
+                    for (int c = 0; c < nch; ++c) bits |= __ldcg(a.fac_flags + static_cast<size_t>((kvh * gqa + g) * 4 + c) * fl_stride + grp);
+                const unsigned int any = __ballot_sync(0xffffffffu, bits != 0u);
+                const unsigned int later = any >> lane;  // bit 0: this group
+                const int nxt = later ? hi - 32 + lane + (__ffs(later) - 1) : carry;
+                if (grp < ngr) nx[grp] = static_cast<unsigned short>(nxt);
+                carry = __shfl_sync(0xffffffffu, nxt, 0);
+            }
+        }
+        if (tid < npairs) s_MS[tid * 2] = __ldcg(a.fac_M + (kvh * gqa + tid / nch) * 4 + tid % nch);
+        if (ks.split && tid < gqa * 8) {
+            // The factors that fold chunk c into the running result (attention.rs:510-541): the maximum before the chunk is
+            // that of the earlier non-empty chunks, so the eight exponentials of a head are independent: one thread each.
+            const int g = tid >> 3, c = (tid >> 1) & 3, which = tid & 1;
+            const float* Mg = a.fac_M + (kvh * gqa + g) * 4;
+            float m_before = -INFINITY;
+            for (int k = 0; k < c; ++k)
+                if (chunk_len(k) > 0) m_before = fmaxf(m_before, __ldcg(Mg + k));
+            const float M = __ldcg(Mg + c), m_new = fmaxf(m_before, M);
+            s_scale[tid] = device_expf(__fsub_rn(which == 0 ? m_before : M, m_new));
+        }
+        cp_async_wait<0>();
     }
     __syncthreads();
     QTB_FINE(a, 3);
     QTB_V2_CLOCK(3);
-    float2 acc = make_float2(0.0f, 0.0f);
-    if (warp < gqa) {
-        // the chains of head `warp`: lane -> (chunk, pair of coordinates)
+    float acc = 0.0f;
+    const int head = warp / kV2WarpsPerHead, part8 = warp % kV2WarpsPerHead;  // chain warps: (query head, eight of the unit's coordinates)
+    if (warp < gqa * kV2WarpsPerHead) {
+        // lane -> (chunk, coordinate)
         const int c = lane >> 3, d = lane & 7;
         const int row = c < nch ? c : 0;  // lanes without a chunk repeat chunk 0; their sums are not used
-        const uint32_t v_off = static_cast<uint32_t>(row * clr * kPiece + d * 4);
-        const uint32_t w_off = static_cast<uint32_t>(reinterpret_cast<const unsigned char*>(f_vs + (warp * nch + row) * clp) - smem);
-        const uint32_t m_off = static_cast<uint32_t>(reinterpret_cast<const unsigned char*>(f_ms + (warp * nch + row) * clp) - smem);
-        const uint32_t f_off = static_cast<uint32_t>(reinterpret_cast<const unsigned char*>(s_moved + warp * ngr8) - smem);
+        const uint32_t v_off = static_cast<uint32_t>(row * clr * kPiece + (part8 * 8 + d) * 2);
+        const uint32_t w_off = static_cast<uint32_t>(reinterpret_cast<const unsigned char*>(f_vs + (head * nch + row) * clp) - smem);
+        const uint32_t m_off = static_cast<uint32_t>(reinterpret_cast<const unsigned char*>(f_ms + (head * nch + row) * clp) - smem);
+        const uint32_t f_off = static_cast<uint32_t>(reinterpret_cast<const unsigned char*>(s_next + head * (ngr8 + 2)) - smem);
         acc = v2_chain<F32>(v_off, w_off, m_off, f_off, ngr);
         QTB_FINE(a, 9);
         QTB_V2_CLOCK(4);
     } else {
         // S of every (head, chunk), one thread each, meanwhile
-        const int pair = (warp - gqa) * 32 + lane;
+        const int pair = (warp - gqa * kV2WarpsPerHead) * 32 + lane;
         if (pair < npairs)
             s_MS[pair * 2 + 1] = v2_sum_chain(static_cast<uint32_t>(reinterpret_cast<const unsigned char*>(f_ms + pair * clp) - smem),
                                               static_cast<uint32_t>(reinterpret_cast<const unsigned char*>(f_vs + pair * clp) - smem), chunk_len(pair % nch));
@@ -1073,47 +1188,42 @@ __device__ __noinline__ void mega_values2_unit(const MegaArgs& a, const MegaLaye
     __syncthreads();
     QTB_FINE(a, 12);
     QTB_V2_CLOCK(5);
-#ifdef QTB_DEBUG_V2_PRINT
-    if (tid == 0) {
-        for (int pr = 0; pr < npairs; ++pr) printf("pair %d len %d M %g S %g gmax0 %g\n", pr, chunk_len(pr % nch), s_MS[pr * 2], s_MS[pr * 2 + 1], s_gmax[pr * ngr8]);
-        for (int p = 0; p < min(48, ngr * 8); ++p) printf("p %d ms %g vs %g flag %u v0 %g\n", p, f_ms[p], f_vs[p], s_moved[p / 8], __half2float(*reinterpret_cast<const __half*>(Vr + p * kPiece)));
-    }
-    if (lane == 0 && warp < gqa) printf("warp %d acc %g %g\n", warp, acc.x, acc.y);
-#endif
-    if (warp < gqa) {
-        // combine the chunks (attention.rs:497-541); every lane of a coordinate pair computes the same values
+    if (warp < gqa * kV2WarpsPerHead) {
+        // combine the chunks (attention.rs:497-541); every lane of a coordinate computes the same value
         const int d = lane & 7;
-        float2 part[4];
+        float part[4];
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-            part[c].x = __shfl_sync(0xffffffffu, acc.x, (c * 8 + d) & 31);
-            part[c].y = __shfl_sync(0xffffffffu, acc.y, (c * 8 + d) & 31);
-        }
-        const float* MS = s_MS + warp * nch * 2;
-        float2 out;
+        for (int c = 0; c < 4; ++c) part[c] = __shfl_sync(0xffffffffu, acc, (c * 8 + d) & 31);
+        const float* MS = s_MS + head * nch * 2;
+        float out;
         if (!ks.split) {
             const float S = MS[1];
-            const float inv = S == 0.0f ? 0.0f : __fdiv_rn(1.0f, S);
-            out = make_float2(__fmul_rn(part[0].x, inv), __fmul_rn(part[0].y, inv));
+            out = __fmul_rn(part[0], S == 0.0f ? 0.0f : __fdiv_rn(1.0f, S));
         } else {
-            float m_final = -INFINITY, s_final = 0.0f;
-            float2 sum = make_float2(0.0f, 0.0f);
+            // A chunk is skipped when its S is zero (attention.rs:519), which happens exactly when it is empty; the factors in
+            // s_scale were computed on that assumption. Should an S ever be zero otherwise, the factors are recomputed here.
+            bool regular = true;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) regular &= (MS[2 * c + 1] == 0.0f) == (chunk_len(c) == 0);
+            float m_final = -INFINITY, s_final = 0.0f, sum = 0.0f;
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 const float M = MS[2 * c], S = MS[2 * c + 1];
                 if (S == 0.0f) continue;
                 const float m_new = fmaxf(m_final, M);
-                const float scale_old = device_expf(__fsub_rn(m_final, m_new)), scale_new = device_expf(__fsub_rn(M, m_new));
-                sum.x = __fmaf_rn(sum.x, scale_old, __fmul_rn(part[c].x, scale_new));
-                sum.y = __fmaf_rn(sum.y, scale_old, __fmul_rn(part[c].y, scale_new));
+                float scale_old = s_scale[head * 8 + 2 * c], scale_new = s_scale[head * 8 + 2 * c + 1];
+                if (!regular) {
+                    scale_old = device_expf(__fsub_rn(m_final, m_new));
+                    scale_new = device_expf(__fsub_rn(M, m_new));
+                }
+                sum = __fmaf_rn(sum, scale_old, __fmul_rn(part[c], scale_new));
                 s_final = __fmaf_rn(s_final, scale_old, __fmul_rn(S, scale_new));
                 m_final = m_new;
             }
-            const float inv = s_final != 0.0f ? __fdiv_rn(1.0f, s_final) : 0.0f;
-            out = s_final != 0.0f ? make_float2(__fmul_rn(sum.x, inv), __fmul_rn(sum.y, inv)) : sum;
+            out = s_final != 0.0f ? __fmul_rn(sum, __fdiv_rn(1.0f, s_final)) : sum;
         }
-        if (lane < 8) *reinterpret_cast<float2*>(a.attn_out + (kvh * gqa + warp) * hd + slice * kV2Dims + 2 * lane) = out;
-        float m = lane < 8 ? fmaxf(fabsf(out.x), fabsf(out.y)) : 0.0f;
+        if (lane < 8) a.attn_out[(kvh * gqa + head) * hd + slice * kV2Dims + part8 * 8 + lane] = out;
+        float m = lane < 8 ? fabsf(out) : 0.0f;
         for (int o = 4; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
         if (lane == 0 && m > 0.0f) atomicMax(a.amax_bits + 2 + (l & 1), __float_as_uint(m));  // non-negative floats order like their bits
     }
@@ -1379,12 +1489,29 @@ __device__ __noinline__ void phase_values(const MegaArgs& a, int l, unsigned cha
 // Phase C2, second form: one unit per (KV head, 8 coordinates); see mega_values2_unit.
 __device__ __noinline__ void phase_values2(const MegaArgs& a, int l, unsigned char* smem) {
     const MegaSmem v = mega_smem_views(smem, a);
-    const int slices = a.head_dim / kV2Dims;
-    for (int u = blockIdx.x; u < a.kv_heads * slices; u += gridDim.x) {
+    const int slices = a.head_dim / kV2Dims, units = a.kv_heads * slices, G = gridDim.x, cta = blockIdx.x;
+    if (cta < units) {  // the host chose this form only if units < gridDim.x
         if (a.f32_values)
-            mega_values2_unit<true>(a, v.layers[l], l, u / slices, u % slices, smem);
+            mega_values2_unit<true>(a, v.layers[l], l, cta / slices, cta % slices, smem);
         else
-            mega_values2_unit<false>(a, v.layers[l], l, u / slices, u % slices, smem);
+            mega_values2_unit<false>(a, v.layers[l], l, cta / slices, cta % slices, smem);
+        return;
+    }
+    // helpers: the factor tasks, interleaved over the KV heads so that every head's first tasks start at once
+    const KvSplit ks = kv_split(a);
+    const int nch = ks.split ? 4 : 1, tasks = a.q_heads * nch;
+    int done = 0;
+    for (int t = cta - units; t < tasks; t += G - units) {
+        v2_factors_task(a, t / nch, t % nch, smem);
+        ++done;
+    }
+    if (done) {
+        __syncthreads();
+        for (int i = threadIdx.x; i < 13 * 64; i += kMegaThreads) {  // the zero rows of the table the tasks wrote over
+            const int k = i >> 6;
+            reinterpret_cast<int*>(smem)[(k < 9 ? 28 * k + 27 : 243 + k) * 64 + (i & 63)] = 0;
+        }
+        __syncthreads();
     }
 }
 
@@ -1780,6 +1907,8 @@ __device__ __noinline__ void phase_finish(const MegaArgs& a, unsigned int seq_ba
         a.amax_bits[1] = 0u;
         a.amax_bits[2] = 0u;
         a.amax_bits[3] = 0u;
+        if (a.attn_v2)
+            for (int k = 0; k < a.kv_heads; ++k) a.fac_done[k] = 0u;
     }
 }
 
