@@ -9,6 +9,9 @@
  * QUINTRIT_ERR_DEVICE or QUINTRIT_ERR_UNSUPPORTED.
  *
  * Plain C99: pointers and sizes only.
+ *
+ * The library also exports every function of quintrit.h itself (see quintrit_b200_runtime.h). A program that includes
+ * the reference's quintrit.h includes it BEFORE this header: the declarations both share are then taken from there.
  */
 #ifndef QUINTRIT_B200_H
 #define QUINTRIT_B200_H
@@ -41,15 +44,22 @@ extern "C" {
 
 #define QUINTRIT_B200_ABI_VERSION 1
 
+/* Kernel id of this library's device GEMV for the kernel-level functions of quintrit.h:112-224 (planar rows, tile_rows 1).
+ * QUINTRIT_KERNEL_AUTO (0) resolves to it; the reference's ids 1..3 are its CPU kernels, which this library does not have. */
+#define QUINTRIT_KERNEL_B200 16
+
 /* ---- errors and version: replaces quintrit.h:91-110 (quintrit-c/src/error.rs:64-81, 149-157) ---- */
+#ifndef QUINTRIT_H
 const char* quintrit_status_string(int status);
 int quintrit_last_error_code(void);
 const char* quintrit_last_error_message(void);
+#endif
 const char* quintrit_b200_version(void);
 uint32_t quintrit_b200_abi_version(void);
 
 /* ---- devices: same names, struct and meaning as quintrit.h:490-513 (quintrit-c/src/cuda.rs:20-104), except that
  * `supported` is 1 only for compute capability 10.0 (the kernels are built for sm_100a alone). ---- */
+#ifndef QUINTRIT_H
 typedef struct quintrit_cuda_device_info {
     uint32_t struct_size;
     uint32_t index;
@@ -64,6 +74,7 @@ typedef struct quintrit_cuda_device_info {
 
 int quintrit_cuda_device_count(uint32_t* out_count);
 int quintrit_cuda_device_info(uint32_t index, quintrit_cuda_device_info_t* out_info);
+#endif
 
 /* ---- host-side layout helpers: replace quintrit-cuda/src/pack.rs:24-48 (blocks_per_row, row_bytes, pack_planar),
  * i.e. quintrit-core/src/pack.rs:103-131. A trit outside {-1,0,1} gives QUINTRIT_ERR_INVALID_VALUE (as
@@ -252,12 +263,14 @@ int quintrit_b200_decoder_tp_attach_local(quintrit_b200_decoder_t* decoder, quin
 
 /* Options of quintrit_b200_decoder_open_gguf: the struct of quintrit.h:502-507 (same fields and meaning; no flag is
  * defined here, so flags must be 0; the context is capped at 8192 instead of 7936). */
+#ifndef QUINTRIT_H
 typedef struct quintrit_gpu_options {
     uint32_t struct_size;    /* set to sizeof(quintrit_gpu_options_t) */
     uint32_t device_index;   /* GPU to use (quintrit_cuda_device_info_t::index) */
-    uint32_t context_length; /* largest context window in tokens; 0 = min(4096, the model's maximum) */
-    uint32_t flags;          /* must be 0 */
+    uint32_t context_length; /* largest context window in tokens; 0 = min(4096, the model's maximum); at most 7936 */
+    uint32_t flags;          /* 0, or QUINTRIT_MODEL_OPEN_VERBOSE (accepted, no effect: the library never prints) */
 } quintrit_gpu_options_t;
+#endif
 
 /*
  * Loads a GGUF model onto a GPU and returns a decoder for it: the device half of quintrit_model_open_gpu
@@ -266,8 +279,8 @@ typedef struct quintrit_gpu_options {
  * (quintrit-runtime/src/config.rs:257-455); the ternary payloads (I2_S, TQ1_0, TQ2_0) are copied as the file stores
  * them and transcoded on the device; files without I2_S tensors use the FP32-accumulator attention. `options` may be
  * NULL (GPU 0, default context). A path that is not a regular file gives QUINTRIT_ERR_IO, a malformed file
- * QUINTRIT_ERR_FORMAT, a missing or mis-shaped tensor QUINTRIT_ERR_MODEL, and Q2_0, mixture-of-experts, hybrid and
- * query/key-norm models QUINTRIT_ERR_UNSUPPORTED. On failure *out_decoder is NULL. The decoder owns the weights.
+ * QUINTRIT_ERR_FORMAT, a missing or mis-shaped tensor QUINTRIT_ERR_MODEL, and mixture-of-experts, hybrid and
+ * query/key-norm models QUINTRIT_ERR_UNSUPPORTED (a file whose projections are all Q2_0 runs through the block-scaled kernels). On failure *out_decoder is NULL. The decoder owns the weights.
  */
 int quintrit_b200_decoder_open_gguf(const char* path, const quintrit_gpu_options_t* options, quintrit_b200_decoder_t** out_decoder);
 
@@ -330,6 +343,37 @@ int quintrit_b200_decoder_trace_step(quintrit_b200_decoder_t* decoder, uint64_t*
  * failure path (expected: ctas). The device stays usable.
  */
 int quintrit_b200_selftest_barrier(uint32_t device_index, uint32_t ctas, uint32_t spin_limit, uint32_t* out_released);
+
+/* ---- token-id entry points on a session of the runtime level (quintrit_model_open_gpu -> quintrit_session_create; the
+ * handles are those of quintrit.h / quintrit_b200_runtime.h). They are what a server that tokenizes elsewhere binds, and what
+ * the parity tests drive: the same decoder as quintrit_session_generate, without text. ---- */
+struct quintrit_session;
+/* Feeds `count` token ids (each below the vocabulary size); flags: 0 restarts the session at position 0,
+ * QUINTRIT_GENERATE_KEEP_CONTEXT (1) continues after the cached tokens. The logits of the last position are kept for
+ * quintrit_session_logits. QUINTRIT_ERR_CONTEXT_OVERFLOW if the tokens do not fit, QUINTRIT_ERR_BUSY if another thread
+ * uses the session. */
+int quintrit_session_feed_tokens(struct quintrit_session* session, const uint32_t* tokens, size_t count, uint32_t flags);
+/* Copies the logits of the last position fed (vocab_size floats); QUINTRIT_ERR_INVALID_ARGUMENT if there are none. */
+int quintrit_session_logits(struct quintrit_session* session, float* out, size_t capacity);
+/* Greedy decoding from position 0 without leaving the device between tokens (quintrit_b200_decoder_generate on the
+ * session's decoder): out receives max_new ids, *out_count their number. */
+int quintrit_session_generate_tokens(struct quintrit_session* session, const uint32_t* prompt, size_t prompt_len, size_t max_new, uint32_t* out,
+                                     size_t out_capacity, size_t* out_count);
+
+/* ---- the tokenizer of a GGUF file on its own (byte-level BPE as quintrit-runtime/src/tokenizer.rs builds it; no GPU needed):
+ * for a front end that tokenizes on another host and for tests. The runtime level uses the same object. ---- */
+typedef struct quintrit_b200_tokenizer quintrit_b200_tokenizer_t;
+int quintrit_b200_tokenizer_open(const char* path, quintrit_b200_tokenizer_t** out_tokenizer);
+int quintrit_b200_tokenizer_free(quintrit_b200_tokenizer_t* tokenizer);
+int quintrit_b200_tokenizer_info(const quintrit_b200_tokenizer_t* tokenizer, uint64_t* out_vocab, int64_t* out_bos, int64_t* out_eos);
+/* As quintrit_model_tokenize (quintrit.h:433-437): flags 0 or QUINTRIT_TOKENIZE_ADD_BOS (1); *out_count always receives the count. */
+int quintrit_b200_tokenizer_encode(const quintrit_b200_tokenizer_t* tokenizer, const char* text, size_t text_len, uint32_t flags, uint32_t* out,
+                                   size_t capacity, size_t* out_count);
+/* As quintrit_model_detokenize (quintrit.h:439-443). streaming != 0 decodes token by token as the generation loop emits text
+ * (a token that ends inside a UTF-8 character adds nothing until the character is complete); out_piece_ends, if not NULL,
+ * receives the text length after every token and after the final flush (count + 1 values). */
+int quintrit_b200_tokenizer_decode(const quintrit_b200_tokenizer_t* tokenizer, const uint32_t* tokens, size_t count, int streaming, char* out,
+                                   size_t capacity, size_t* out_len, size_t* out_piece_ends);
 
 /* Kernel launches issued by this library on the calling thread since the last call with reset != 0 (counting aid). */
 uint64_t quintrit_b200_launch_count(int reset);

@@ -817,8 +817,10 @@ int decoder_create_impl(const quintrit_b200_decoder_desc_t* desc, quintrit_b200_
     if (desc->num_heads % desc->num_kv_heads != 0) return fail(QUINTRIT_ERR_MODEL, "num_heads is not a multiple of num_kv_heads");
     if (desc->rope_dims == 0 || desc->rope_dims % 2 != 0 || desc->rope_dims > hd)
         return fail(QUINTRIT_ERR_MODEL, "rope_dims %u must be even and at most the head dimension %u", desc->rope_dims, hd);
-    const uint32_t ctx = desc->context_length / 256 * 256;  // gpu.rs:141-146
-    if (ctx == 0 || ctx > 8192) return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "context_length %u must give 256..8192 after rounding down to a multiple of 256", desc->context_length);
+    // gpu.rs:141-146: rounded down to a multiple of 256 from 256 on; a smaller window is kept as it is (a multiple of 8 here)
+    const uint32_t ctx = desc->context_length >= 256 ? desc->context_length / 256 * 256 : desc->context_length;
+    if (ctx == 0 || ctx > 8192 || ctx % 8 != 0)
+        return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "context_length %u must be a multiple of 8 below 256, or give 256..8192 after rounding down to a multiple of 256", desc->context_length);
     const size_t qd_full = size_t(desc->num_heads) * hd;
     const size_t qd = qd_full / tp_world, kvd = size_t(desc->num_kv_heads) * hd / tp_world;  // this rank's query and KV widths
     const uint32_t vocab_local = desc->vocab_size / tp_world;
@@ -1276,33 +1278,53 @@ int projection(const GgufFile& g, const std::string& name, uint64_t rows, uint64
     return QUINTRIT_OK;
 }
 
-int open_gguf_impl(const char* path, const quintrit_gpu_options_t* options, quintrit_b200_decoder** out) {
-    uint32_t device = 0, want_ctx = 0;
-    if (options != nullptr) {
-        if (options->struct_size < sizeof(quintrit_gpu_options_t))
-            return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "struct_size %u is smaller than quintrit_gpu_options_t (%zu)", options->struct_size, sizeof(quintrit_gpu_options_t));
-        if (options->flags != 0) return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "unknown flag bits 0x%x", options->flags);
-        device = options->device_index;
-        want_ctx = options->context_length;
+// A model file as the decoder needs it: the mapped file, the hyperparameters, the ternary projections transcoded on the
+// device (owned here), their scales, and views of the dense tensors inside the mapping.
+struct GgufModel {
+    GgufFile file;
+    GgufModelShape shape;
+    uint32_t device = 0;
+    std::vector<quintrit_b200_matrix*> mats;
+    std::vector<float> scales;
+    std::vector<std::vector<float>> f32_store;
+    std::vector<const float*> norms;
+    const uint16_t* embed = nullptr;
+    const uint16_t* head = nullptr;
+    const float* out_norm = nullptr;
+    uint32_t table_type = kGgmlF16;
+    GgufModel() = default;
+    GgufModel(const GgufModel&) = delete;
+    GgufModel& operator=(const GgufModel&) = delete;
+    ~GgufModel() {
+        for (quintrit_b200_matrix* x : mats) destroy_matrix(x);
     }
-    GgufFile g;
+    // Largest context a decoder of this model may have: the model's maximum, at most `limit` (0: 4096) and 7936, rounded down to
+    // a multiple of 256 when it reaches 256 (gpu.rs:141-146).
+    uint32_t context_for(uint32_t limit) const {
+        uint64_t want = std::min<uint64_t>(shape.ctx_train, limit != 0 ? limit : 4096);
+        want = std::min<uint64_t>(want, 7936);
+        return static_cast<uint32_t>(want >= 256 ? want / 256 * 256 : want);
+    }
+};
+
+// Reads the file, checks what the decoder needs and places the ternary projections on GPU `device` (the loading half of
+// GpuModel::load, gpu.rs:183-260).
+int load_gguf_model(const char* path, uint32_t device, GgufModel* out) {
+    GgufModel& md = *out;
+    GgufFile& g = md.file;
+    GgufModelShape& m = md.shape;
+    md.device = device;
     std::string why;
     const int rc_open = g.open(path, why);
     if (rc_open == 1) return fail(QUINTRIT_ERR_IO, "%s", why.c_str());
     if (rc_open != 0) return fail(QUINTRIT_ERR_FORMAT, "%s", why.c_str());
-    GgufModelShape m;
     int rc = read_shape(g, &m);
     if (rc != QUINTRIT_OK) return rc;
-
-    // context: the model's maximum, at most 4096 by default (quintrit.h:502-507), rounded down to a multiple of 256
-    uint64_t ctx = std::min<uint64_t>(m.ctx_train, want_ctx != 0 ? want_ctx : 4096);
-    ctx = std::min<uint64_t>(ctx, 8192) / 256 * 256;
-    if (ctx == 0) return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "the context window is smaller than 256 positions");
     const uint64_t qd = m.heads * m.head_dim, kvd = m.kv_heads * m.head_dim;
 
-    uint32_t table_type = kGgmlF16;
     if (const GgufTensor* e = g.tensor("token_embd.weight"))
-        if (e->type == kGgmlBF16) table_type = kGgmlBF16;
+        if (e->type == kGgmlBF16) md.table_type = kGgmlBF16;
+    const uint32_t table_type = md.table_type;
     auto dense_f16 = [&](const char* name, uint64_t n, const uint16_t** outp) -> int {
         const GgufTensor* t = g.tensor(name);
         if (t == nullptr) return fail(QUINTRIT_ERR_MODEL, "Missing %s tensor", name);
@@ -1313,28 +1335,21 @@ int open_gguf_impl(const char* path, const quintrit_gpu_options_t* options, quin
         *outp = reinterpret_cast<const uint16_t*>(p);
         return QUINTRIT_OK;
     };
-    std::vector<std::vector<float>> f32_store;
     auto dense_f32 = [&](const std::string& name, uint64_t n, const float** outp) -> int {
         const GgufTensor* t = g.tensor(name);
         if (t == nullptr || t->type != kGgmlF32) return fail(QUINTRIT_ERR_MODEL, "Missing %s", name.c_str());
         uint64_t len = 0;
         const uint8_t* p = g.data(*t, &len);
         if (p == nullptr || len != n * 4) return fail(QUINTRIT_ERR_MODEL, "%s does not hold %llu values", name.c_str(), static_cast<unsigned long long>(n));
-        f32_store.emplace_back(n);
-        std::memcpy(f32_store.back().data(), p, n * 4);  // tensor payloads are not necessarily 4-byte aligned in memory
-        *outp = f32_store.back().data();
+        md.f32_store.emplace_back(n);
+        std::memcpy(md.f32_store.back().data(), p, n * 4);  // tensor payloads are not necessarily 4-byte aligned in memory
+        *outp = md.f32_store.back().data();
         return QUINTRIT_OK;
     };
 
-    std::vector<quintrit_b200_matrix*> mats;
-    auto release = [&]() {
-        for (quintrit_b200_matrix* x : mats) destroy_matrix(x);
-    };
-    std::vector<float> scales;
-    std::vector<const float*> norms;
     const char* proj_names[7] = {"attn_q", "attn_k", "attn_v", "attn_output", "ffn_gate", "ffn_up", "ffn_down"};
     const uint64_t shapes[7][2] = {{qd, m.hidden}, {kvd, m.hidden}, {kvd, m.hidden}, {m.hidden, qd}, {m.inter, m.hidden}, {m.inter, m.hidden}, {m.hidden, m.inter}};
-    f32_store.reserve(m.layers * 4 + 1);
+    md.f32_store.reserve(m.layers * 4 + 1);
     for (uint64_t l = 0; l < m.layers && rc == QUINTRIT_OK; ++l) {
         const std::string prefix = "blk." + std::to_string(l) + ".";
         for (int k = 0; k < 7 && rc == QUINTRIT_OK; ++k) {
@@ -1347,49 +1362,69 @@ int open_gguf_impl(const char* path, const quintrit_gpu_options_t* options, quin
             quintrit_b200_matrix_t* h = nullptr;
             rc = quintrit_b200_matrix_upload(device, source, data, len, shapes[k][0], shapes[k][1], &h);
             if (rc != QUINTRIT_OK) break;
-            mats.push_back(h);
-            scales.push_back(scale);
+            md.mats.push_back(h);
+            md.scales.push_back(scale);
         }
         const char* norm_names[4] = {"attn_norm", "ffn_norm", "attn_sub_norm", "ffn_sub_norm"};
         const uint64_t norm_len[4] = {m.hidden, m.hidden, m.hidden, m.inter};
         for (int k = 0; k < 4 && rc == QUINTRIT_OK; ++k) {
             const float* p = nullptr;
             if (k < 2 || m.arch_id == QUINTRIT_B200_ARCH_BITNET) rc = dense_f32(prefix + norm_names[k] + ".weight", norm_len[k], &p);
-            norms.push_back(p);
+            md.norms.push_back(p);
         }
     }
-    const uint16_t *embed = nullptr, *head = nullptr;
-    const float* out_norm = nullptr;
-    if (rc == QUINTRIT_OK) rc = dense_f16("token_embd.weight", m.vocab * m.hidden, &embed);
-    if (rc == QUINTRIT_OK && !m.tied) rc = dense_f16("output.weight", m.vocab * m.hidden, &head);
-    if (rc == QUINTRIT_OK) rc = dense_f32("output_norm.weight", m.hidden, &out_norm);
-    if (rc != QUINTRIT_OK) {
-        release();
-        return rc;
-    }
+    if (rc == QUINTRIT_OK) rc = dense_f16("token_embd.weight", m.vocab * m.hidden, &md.embed);
+    if (rc == QUINTRIT_OK && !m.tied) rc = dense_f16("output.weight", m.vocab * m.hidden, &md.head);
+    if (rc == QUINTRIT_OK) rc = dense_f32("output_norm.weight", m.hidden, &md.out_norm);
+    return rc;
+}
+
+// A decoder (KV cache, buffers, copies of the dense tables) over a loaded model; the model keeps the projections.
+int decoder_from_model(const GgufModel& md, uint32_t ctx, quintrit_b200_decoder** out) {
+    const GgufModelShape& m = md.shape;
     quintrit_b200_decoder_desc_t desc;
     std::memset(&desc, 0, sizeof desc);
     desc.struct_size = sizeof desc;
-    desc.device_index = device;
+    desc.device_index = md.device;
     desc.arch = m.arch_id;
     desc.f32_values = m.has_i2s ? 0 : 1;  // config.rs:425-429: files with I2_S tensors use the F16-accumulator attention
     desc.hidden_size = static_cast<uint32_t>(m.hidden), desc.intermediate_size = static_cast<uint32_t>(m.inter);
     desc.num_layers = static_cast<uint32_t>(m.layers), desc.num_heads = static_cast<uint32_t>(m.heads), desc.num_kv_heads = static_cast<uint32_t>(m.kv_heads);
-    desc.head_dim = static_cast<uint32_t>(m.head_dim), desc.vocab_size = static_cast<uint32_t>(m.vocab), desc.context_length = static_cast<uint32_t>(ctx);
+    desc.head_dim = static_cast<uint32_t>(m.head_dim), desc.vocab_size = static_cast<uint32_t>(m.vocab), desc.context_length = ctx;
     desc.rope_dims = static_cast<uint32_t>(m.rope_dims), desc.rms_norm_eps = m.eps, desc.rope_theta = m.theta;
-    desc.embed = embed, desc.lm_head = head, desc.output_norm = out_norm;
-    desc.table_dtype = table_type == kGgmlBF16 ? 1u : 0u;
-    desc.matrices = reinterpret_cast<const quintrit_b200_matrix_t* const*>(mats.data());
-    desc.scales = scales.data();
-    desc.norms = norms.data();
+    desc.embed = md.embed, desc.lm_head = md.head, desc.output_norm = md.out_norm;
+    desc.table_dtype = md.table_type == kGgmlBF16 ? 1u : 0u;
+    desc.matrices = reinterpret_cast<const quintrit_b200_matrix_t* const*>(md.mats.data());
+    desc.scales = md.scales.data();
+    desc.norms = md.norms.data();
     quintrit_b200_decoder* d = nullptr;
-    rc = decoder_create_impl(&desc, &d);
+    const int rc = decoder_create_impl(&desc, &d);
     if (rc != QUINTRIT_OK) {
         destroy_decoder(d);
-        release();
         return rc;
     }
-    for (quintrit_b200_matrix* x : mats) d->owned_matrices.push_back(x);
+    *out = d;
+    return QUINTRIT_OK;
+}
+
+int open_gguf_impl(const char* path, const quintrit_gpu_options_t* options, quintrit_b200_decoder** out) {
+    uint32_t device = 0, want_ctx = 0;
+    if (options != nullptr) {
+        if (options->struct_size < sizeof(quintrit_gpu_options_t))
+            return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "struct_size %u is smaller than quintrit_gpu_options_t (%zu)", options->struct_size, sizeof(quintrit_gpu_options_t));
+        if (options->flags & ~1u) return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "unknown flag bits 0x%x", options->flags);
+        device = options->device_index;
+        want_ctx = options->context_length;
+    }
+    GgufModel md;
+    int rc = load_gguf_model(path, device, &md);
+    if (rc != QUINTRIT_OK) return rc;
+    const uint32_t ctx = md.context_for(want_ctx);
+    if (ctx == 0) return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "the context window of the model is empty");
+    quintrit_b200_decoder* d = nullptr;
+    if ((rc = decoder_from_model(md, ctx, &d)) != QUINTRIT_OK) return rc;
+    for (quintrit_b200_matrix* x : md.mats) d->owned_matrices.push_back(x);  // the decoder takes the projections over
+    md.mats.clear();
     *out = d;
     return QUINTRIT_OK;
 }
@@ -1829,3 +1864,5 @@ extern "C" int quintrit_b200_decoder_trace_step(quintrit_b200_decoder_t* decoder
         return ok();
     });
 }
+
+#include "runtime.cuh"

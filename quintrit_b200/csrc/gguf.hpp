@@ -31,6 +31,8 @@ struct GgufValue {
     uint32_t elem_type = 0; // arrays
     uint64_t count = 0;
     uint64_t max_u = 0;     // arrays of integers: the largest element (per-layer head counts, config.rs:502-512)
+    std::vector<std::string> strs;  // arrays of strings (tokenizer.ggml.tokens, tokenizer.ggml.merges)
+    std::vector<int64_t> ints;      // arrays of integers (tokenizer.ggml.token_type)
     bool is_int() const { return type <= 5 || type == 7 || type == 10 || type == 11; }
 };
 
@@ -135,6 +137,8 @@ class GgufFile {
         return true;
     }
 
+    uint64_t data_start() const { return data_start_; }
+
     uint32_t version = 0;
     std::map<std::string, GgufValue> metadata;
     std::map<std::string, GgufTensor> tensors;
@@ -195,9 +199,10 @@ class GgufFile {
         if (v->type == 9) {
             if (depth > 0 || !read(&v->elem_type) || !read(&v->count)) return false;  // nested arrays are not used by model files
             if (v->elem_type == 8) {
-                std::string tmp;
+                if (v->count > (size_ - pos_) / 8) return false;  // every string has an 8-byte length
+                v->strs.resize(static_cast<size_t>(v->count));
                 for (uint64_t i = 0; i < v->count; ++i)
-                    if (!read_string(&tmp)) return false;
+                    if (!read_string(&v->strs[static_cast<size_t>(i)])) return false;
                 return true;
             }
             const size_t n = scalar_size(v->elem_type);
@@ -207,6 +212,7 @@ class GgufFile {
             for (uint64_t i = 0; i < v->count; ++i) {
                 if (!read_scalar(v->elem_type, &e)) return false;
                 if (e.is_int() && e.u > v->max_u) v->max_u = e.u;
+                if (e.is_int()) v->ints.push_back(static_cast<int64_t>(e.u));
             }
             return true;
         }

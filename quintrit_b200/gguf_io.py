@@ -83,7 +83,9 @@ def _value(v) -> bytes:
         return struct.pack("<If", 6, float(v))
     if isinstance(v, str):
         return struct.pack("<I", 8) + _string(v)
-    if isinstance(v, (list, tuple)) and v:
+    if isinstance(v, (list, tuple)) and not v:  # an empty array of strings (a tokenizer without merges)
+        return struct.pack("<IIQ", 9, 8, 0)
+    if isinstance(v, (list, tuple)):
         bodies = [_value(x) for x in v]
         kinds = {b[:4] for b in bodies}
         if len(kinds) != 1:
@@ -113,10 +115,12 @@ def write_gguf(path, metadata: dict, tensors) -> None:
             f.write(b"\0" * (-len(payload) % ALIGNMENT))
 
 
-def write_model_gguf(path, spec: dict, trits: list, encoding: int = GGML_I2_S, architecture: str = "llama", name: str = "synthetic") -> None:
+def write_model_gguf(path, spec: dict, trits: list, encoding: int = GGML_I2_S, architecture: str = "llama", name: str = "synthetic",
+                     extra_metadata: dict | None = None) -> None:
     """Writes the model `spec` (dimensions, scales, norms, embed, lm_head, out_norm as in synth.make_model) with the
     ternary projections `trits` (layers * 7 arrays [rows, cols], order q, k, v, o, gate, up, down) in `encoding`.
-    TQ encodings store the tensor scale as the f16 of every block, so the scales must be exactly representable in f16."""
+    TQ encodings store the tensor scale as the f16 of every block, so the scales must be exactly representable in f16.
+    `extra_metadata` is added to the file's key/value pairs (a tokenizer, for instance)."""
     L, H, I, hd = spec["layers"], spec["hidden"], spec["inter"], spec["head_dim"]
     qd, kvd = spec["q_heads"] * hd, spec["kv_heads"] * hd
     shapes = [(qd, H), (kvd, H), (kvd, H), (H, qd), (I, H), (I, H), (H, I)]
@@ -129,6 +133,7 @@ def write_model_gguf(path, spec: dict, trits: list, encoding: int = GGML_I2_S, a
         f"{architecture}.attention.layer_norm_rms_epsilon": float(spec["eps"]), f"{architecture}.rope.freq_base": float(spec["rope_theta"]),
         f"{architecture}.rope.dimension_count": spec["rope_dims"], f"{architecture}.context_length": spec["ctx"],
     }
+    meta.update(extra_metadata or {})
     table_type = GGML_BF16 if spec.get("bf16_tables") else GGML_F16
     tensors = [("token_embd.weight", (H, spec["vocab"]), table_type, np.ascontiguousarray(spec["embed"], np.uint16).tobytes())]
     norm_names = ["attn_norm", "ffn_norm", "attn_sub_norm", "ffn_sub_norm"]
