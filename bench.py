@@ -392,6 +392,88 @@ def run_reference(args, rank: int, world: int):
     print(json.dumps(line), flush=True)
 
 
+def run_reference_cuda(args, rank: int, world: int, local_rank: int):
+    """--impl reference-cuda: the reference's own CUDA projection kernel (quintrit-cuda/kernels/gemv.cu, compiled for sm_100a from the
+    reference tree into oracle/_ref by oracle/ref_cuda/Makefile) on the same sweep on this GPU: one launch per projection, as the
+    reference's decoder issues them, each with the configuration its device profile picks for that role. Rank 0 only; weights and
+    permuted activations resident in HBM; the results of one pass are checked against the CPU kernel's on a sample of projections."""
+    if rank != 0:
+        return
+    from oracle import refcuda
+
+    base = {"impl": "reference-cuda", "metric": "gemv_gweights_per_s", "unit": "Gweights/s", "n_gpus": args.gpus}
+    if not refcuda.available():
+        print(json.dumps({**base, "unavailable": "oracle/_ref/libqtref_cuda.so is not built (it needs the reference tree at build time)"}), flush=True)
+        return
+    import torch
+
+    if not torch.cuda.is_available():
+        print(json.dumps({**base, "unavailable": "no CUDA device"}), flush=True)
+        return
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    l = refcuda.lib()
+    role_of = [2, 2, 2, 0, 3, 3, 1]  # q, k, v: the stacked projection's configuration; o: output; gate, up; down
+    items = []
+    for (layer, p, n, k) in sweep_shapes(args.layers):
+        cfg = refcuda.profile_config(role_of[p])
+        w = synth.torch_planar(synth.seed_for(CONFIG_ID, layer, p, 0), n, k, dev)
+        perm, total = refcuda.permute_activations(activations_for(layer, p, k))
+        items.append((cfg, w, n, k, torch.from_numpy(perm).to(dev), torch.tensor([total], dtype=torch.int32, device=dev), torch.zeros(n, dtype=torch.int32, device=dev)))
+    weights_total = sum(n * k for _, _, n, k in sweep_shapes(args.layers))
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def one_pass():
+        for cfg, w, n, k, a, s, o in items:
+            rc = l.qtref_gemv_plain_device(cfg, w.data_ptr(), n, k, a.data_ptr(), s.data_ptr(), o.data_ptr(), stream)
+            if rc != 0:
+                raise RuntimeError(f"the reference kernel failed to launch: CUDA error {rc}")
+
+    one_pass()
+    torch.cuda.synchronize()
+    checked = 0
+    for idx in range(0, len(items), max(1, len(items) // 14)):  # a sample of projections against the CPU kernel
+        cfg, w, n, k, a, s, o = items[idx]
+        layer, p = divmod(idx, 7)
+        import oracle
+
+        want = oracle.gemv_planar(w.cpu().numpy(), n, k, activations_for(layer, p, k))
+        if not np.array_equal(o.cpu().numpy(), want):
+            raise SystemExit(f"the reference kernel's result of projection {idx} differs from the CPU kernel's")
+        checked += 1
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    for _ in range(max(3, args.warmup)):
+        one_pass()
+    torch.cuda.synchronize()
+    sampler.mark_begin()
+    t_heat = time.time()
+    while time.time() - t_heat < args.preheat:
+        for _ in range(10):
+            one_pass()
+        torch.cuda.synchronize()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+    ev[0].record()
+    for i in range(args.steps):
+        one_pass()
+        ev[i + 1].record()
+    torch.cuda.synchronize()
+    sampler.mark_end()
+    clocks = sampler.stop()
+    ms_per_step = ev[0].elapsed_time(ev[-1]) / args.steps
+    value = weights_total / (ms_per_step * 1e-3) / 1e9
+    peak, peak_kind = measured_peaks()
+    achieved = weights_total * BYTES_PER_WEIGHT / (ms_per_step * 1e-3) / 1e9
+    print(json.dumps({
+        **base, "value": round(value, 1), "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": round(ms_per_step, 4), "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "int8xternary->int32", "data": "synthetic", "config": sweep_config(args.layers, 1, weights_total),
+        "kernel": "the reference's gemv_<config>_plain, one launch per projection (280 per step), configurations of its profile '24sm_24mib' (the nearest to this device by its own rule)",
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 4), "traffic": None, "peak_kind": peak_kind},
+        "e2e": {"value": round(value, 1), "unit": "Gweights/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": len(items) * args.steps, "clocks": clocks, "parity_vs_cpu": {"projections_checked": checked, "bit_exact": True},
+    }), flush=True)
+
+
 def run_ours(args, rank: int, world: int, local_rank: int):
     import torch
 
@@ -571,7 +653,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-cuda"])
     ap.add_argument("--layers", type=int, default=40)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--preheat", type=float, default=1.0, help="seconds of untimed back-to-back passes right before the timed steps")
@@ -594,6 +676,8 @@ def main():
         print(json.dumps({"decode": run_decode(args, local_rank)}), flush=True)
     elif args.impl == "reference":
         run_reference(args, rank, world)
+    elif args.impl == "reference-cuda":
+        run_reference_cuda(args, rank, world, local_rank)
     else:
         run_ours(args, rank, world, local_rank)
 

@@ -162,8 +162,14 @@ static void runtime_level(const char* path, const char* prompt) {
     printf("PROMPT_IDS=");
     for (i = 0; i < n; ++i) printf("%s%u", i ? "," : "", (unsigned)ids[i]);
     printf("\n");
-    STATUS(quintrit_model_detokenize(model, ids, n, text, sizeof text, &text_len), QUINTRIT_OK);
-    EXPECT(text_len == strlen(prompt) && memcmp(text, prompt, text_len) == 0); /* BOS is a control token: skipped */
+    {   /* without BOS the ids decode to the prompt; with it, one more id stands in front */
+        uint32_t plain[512];
+        size_t m = 0;
+        STATUS(quintrit_model_tokenize(model, prompt, strlen(prompt), 0, plain, 512, &m), QUINTRIT_OK);
+        EXPECT(m == n || (m + 1 == n && memcmp(plain, ids + 1, m * sizeof plain[0]) == 0 && (int64_t)ids[0] == mi.bos_token_id));
+        STATUS(quintrit_model_detokenize(model, plain, m, text, sizeof text, &text_len), QUINTRIT_OK);
+        EXPECT(text_len == strlen(prompt) && memcmp(text, prompt, text_len) == 0);
+    }
     STATUS(quintrit_model_detokenize(model, ids, n, text, 2, &text_len), QUINTRIT_ERR_BUFFER_TOO_SMALL);
     STATUS(quintrit_model_tokenize(model, "\xff\xfe", 2, 0, ids, 512, &n), QUINTRIT_ERR_INVALID_ARGUMENT); /* not UTF-8 */
 
