@@ -101,6 +101,8 @@ def load_library(build_if_missing: bool = True) -> C.CDLL:
     l.quintrit_b200_gemv_block_scaled_q8.argtypes = [C.c_void_p, _i8p, _sz, _f32p, _sz, _f32p, _sz]
     l.quintrit_b200_gemv_i32.argtypes = [C.c_void_p, _i8p, _sz, _i32p, _sz]
     l.quintrit_b200_gemv_f32.argtypes = [C.c_void_p, _i8p, _sz, C.c_float, _f32p, _sz]
+    l.quintrit_b200_gemm_i32.argtypes = [C.c_void_p, _i8p, _sz, _sz, _i32p, _sz]
+    l.quintrit_b200_gemm_i32_device.argtypes = [C.c_void_p, C.c_void_p, _sz, C.c_void_p, C.c_void_p]
     l.quintrit_b200_gemv_i32_device.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
     l.quintrit_b200_gemv_i32_noalloc.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
     l.quintrit_b200_plan_create.argtypes = [C.POINTER(C.c_void_p), _sz, C.POINTER(C.c_void_p)]
@@ -237,6 +239,16 @@ class Matrix:
         out = np.zeros(self.rows, np.float32)
         _check(load_library().quintrit_b200_gemv_block_scaled_q8(self._h, _p(q, _i8p), q.size, _p(d, _f32p), d.size, _p(out, _f32p), out.size))
         return out
+
+    def gemm_i32(self, activations) -> np.ndarray:
+        """Batched projection on the tensor cores: activations [batch, cols] int8 -> [batch, rows] int32, every row the integers of gemv_i32."""
+        a = np.ascontiguousarray(activations, dtype=np.int8).reshape(-1, self.cols)
+        out = np.zeros((a.shape[0], self.rows), np.int32)
+        _check(load_library().quintrit_b200_gemm_i32(self._h, _p(a, _i8p), a.size, a.shape[0], _p(out, _i32p), out.size))
+        return out
+
+    def gemm_i32_device(self, d_activations: int, batch: int, d_out: int, stream: int = 0) -> None:
+        _check(load_library().quintrit_b200_gemm_i32_device(self._h, d_activations, batch, d_out, stream))
 
     def gemv_i32(self, activations) -> np.ndarray:
         a = np.ascontiguousarray(activations, dtype=np.int8)

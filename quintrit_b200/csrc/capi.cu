@@ -11,6 +11,7 @@
 #include "capi_common.cuh"
 #include "gemv_lut.cuh"
 #include "transcode.cuh"
+#include "gemm_tc.cuh"
 #include "block_scaled.cuh"
 
 using namespace qtb;
@@ -35,6 +36,13 @@ struct quintrit_b200_matrix {
     float* d_wscales = nullptr;
     float* d_x = nullptr;    // cols floats: activations of one call
     float* d_as = nullptr;   // cols / 32 activation block scales
+    // batched projection on the tensor cores (gemm_tc.cuh): block-major planar copy of the weights and call buffers, made on first use
+    uint8_t* d_gemm_w = nullptr;
+    size_t gemm_rows_padded = 0;
+    int8_t* d_gemm_act = nullptr;     // kGemmMaxN x blocks * 160, zero padded
+    int8_t* d_gemm_in = nullptr;      // host-call staging: kGemmMaxN x cols
+    int32_t* d_gemm_out = nullptr;    // host-call staging: kGemmMaxN x rows
+    unsigned int* d_gemm_status = nullptr;
 };
 
 struct quintrit_b200_plan {
@@ -295,6 +303,11 @@ void destroy_matrix(quintrit_b200_matrix* m) {
     cudaFree(m->d_wscales);
     cudaFree(m->d_x);
     cudaFree(m->d_as);
+    cudaFree(m->d_gemm_w);
+    cudaFree(m->d_gemm_act);
+    cudaFree(m->d_gemm_in);
+    cudaFree(m->d_gemm_out);
+    cudaFree(m->d_gemm_status);
     m->magic = 0;
     delete m;
 }
@@ -1861,6 +1874,154 @@ extern "C" int quintrit_b200_decoder_trace_step(quintrit_b200_decoder_t* decoder
         const double ns_per_cycle = span_cyc > 0 ? span_ns / span_cyc : 0.0;
         for (size_t i = 0; i < n; ++i) out_ns[i] = raw[i] == 0 ? 0 : raw[n] + static_cast<uint64_t>(static_cast<double>(raw[i] - raw[0]) * ns_per_cycle);
         out_ns[last + 1] = ns_per_cycle > 0 ? static_cast<uint64_t>(1e6 / ns_per_cycle) : 0;
+        return ok();
+    });
+}
+
+// ---- batched projection on the tensor cores (gemm_tc.cuh) ------------------------------------------------------------------------
+namespace {
+
+std::mutex g_gemm_lock;
+typedef CUresult (*TensorMapEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                      CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// The driver's tensor-map encoder, fetched at run time so that the library loads on a machine without a driver.
+int tensor_map_encoder(TensorMapEncodeFn* out) {
+    static TensorMapEncodeFn fn = nullptr;
+    if (fn == nullptr) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q = cudaDriverEntryPointSymbolNotFound;
+        const cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q);
+        if (e != cudaSuccess || q != cudaDriverEntryPointSuccess || p == nullptr) return fail(QUINTRIT_ERR_DEVICE, "the CUDA driver does not provide cuTensorMapEncodeTiled");
+        fn = reinterpret_cast<TensorMapEncodeFn>(p);
+    }
+    *out = fn;
+    return QUINTRIT_OK;
+}
+
+// Makes the block-major planar copy and the call buffers of a matrix the first time it is used by the batched projection.
+int gemm_prepare(quintrit_b200_matrix* m) {
+    std::lock_guard<std::mutex> hold(g_gemm_lock);
+    if (m->d_gemm_w != nullptr) return QUINTRIT_OK;
+    if (m->block_scaled) return fail(QUINTRIT_ERR_UNSUPPORTED, "the batched projection takes per-tensor ternary matrices, not block-scaled (Q2_0) ones");
+    const size_t rows_padded = (m->rows + kGemmM - 1) / kGemmM * kGemmM, k_pad = m->blocks * kBlockTrits;
+    uint8_t* w = nullptr;
+    QTB_CUDA(cudaMalloc(&w, m->blocks * rows_padded * 32));
+    const size_t pieces = m->blocks * rows_padded * 2;
+    stream_to_block_major_kernel<<<static_cast<int>(std::min<size_t>((pieces + 255) / 256, 148 * 16)), 256>>>(m->d_w, w, m->rows, rows_padded, m->blocks, m->tiles);
+    ++g_launches;
+    cudaError_t e = cudaGetLastError();
+    if (e == cudaSuccess) e = cudaMalloc(&m->d_gemm_act, size_t(kGemmMaxN) * k_pad);
+    if (e == cudaSuccess) e = cudaMalloc(&m->d_gemm_in, size_t(kGemmMaxN) * m->cols);
+    if (e == cudaSuccess) e = cudaMalloc(&m->d_gemm_out, size_t(kGemmMaxN) * m->rows * sizeof(int32_t));
+    if (e == cudaSuccess) e = cudaMalloc(&m->d_gemm_status, sizeof(unsigned int));
+    if (e == cudaSuccess) e = cudaMemset(m->d_gemm_status, 0, sizeof(unsigned int));
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_i8_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(gemm_smem_bytes(kGemmMaxN, 3)));
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) {
+        cudaFree(w);
+        return cuda_fail(e, "set-up of the batched projection");
+    }
+    m->gemm_rows_padded = rows_padded;
+    m->d_gemm_w = w;
+    return QUINTRIT_OK;
+}
+
+// One launch for up to kGemmMaxN activation vectors that are on the device ([batch][cols]); d_out is [batch][rows].
+int gemm_launch(quintrit_b200_matrix* m, const int8_t* d_act, int batch, int32_t* d_out, cudaStream_t stream) {
+    TensorMapEncodeFn encode = nullptr;
+    int rc = tensor_map_encoder(&encode);
+    if (rc != QUINTRIT_OK) return rc;
+    const int n = std::max(16, (batch + 15) / 16 * 16), k_pad = static_cast<int>(m->blocks * kBlockTrits);
+    // The TMA reads the caller's vectors in place when their pitch and address allow it (columns and vectors beyond the matrix read as zeros);
+    // otherwise they are first copied into a zero-padded matrix with a pitch of whole blocks.
+    const bool in_place = m->cols % 16 == 0 && reinterpret_cast<uintptr_t>(d_act) % 16 == 0;
+    const void* base = d_act;
+    cuuint64_t dims[2] = {static_cast<cuuint64_t>(m->cols), static_cast<cuuint64_t>(batch)};
+    if (!in_place) {
+        gemm_pad_activations_kernel<<<std::min((n * k_pad + 255) / 256, 148 * 8), 256, 0, stream>>>(d_act, m->d_gemm_act, batch, n, static_cast<int>(m->cols), k_pad);
+        ++g_launches;
+        base = m->d_gemm_act, dims[0] = static_cast<cuuint64_t>(k_pad), dims[1] = static_cast<cuuint64_t>(n);
+    }
+    CUtensorMap map;
+    const cuuint64_t strides[1] = {dims[0]};  // bytes between activation vectors: a multiple of 16 in both cases
+    const cuuint32_t box[2] = {32, static_cast<cuuint32_t>(n)}, elem[2] = {1, 1};
+    const CUresult cr = encode(&map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_32B,
+                               CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (cr != CUDA_SUCCESS) return fail(QUINTRIT_ERR_DEVICE, "cuTensorMapEncodeTiled failed with CUDA driver error %d", static_cast<int>(cr));
+    GemmArgs a;
+    a.w = m->d_gemm_w, a.out = d_out, a.status = m->d_gemm_status;
+    a.rows = static_cast<int>(m->rows), a.rows_padded = static_cast<int>(m->gemm_rows_padded), a.blocks = static_cast<int>(m->blocks);
+    a.n = n, a.batch = batch;
+    a.stages = n > 160 ? 3 : 4;
+    a.spin_limit = 1u << 22;
+    // Work items are (row tile, K part); K is split (at least four blocks a part) where the items of whole tiles would leave SMs idle: the cost of a
+    // split is the largest number of items an SM gets times the blocks of an item plus about one block for its epilogue.
+    const int m_tiles = a.rows_padded / kGemmM;
+    int ksplit = 1;
+    long best = -1;
+    for (int ks = 1; ks <= std::max(1, a.blocks / 4); ++ks) {
+        const int per = (a.blocks + ks - 1) / ks, parts = (a.blocks + per - 1) / per;
+        const long waves = (long(m_tiles) * parts + m->sm_count - 1) / m->sm_count, cost = waves * (per + 1 + (parts > 1 ? 1 : 0));
+        if (best < 0 || cost < best) best = cost, ksplit = parts;
+    }
+    if (const char* v = std::getenv("QUINTRIT_B200_GEMM_KSPLIT")) ksplit = std::max(1, std::min(std::atoi(v), a.blocks));
+    a.blocks_per_cta = (a.blocks + ksplit - 1) / ksplit;
+    ksplit = (a.blocks + a.blocks_per_cta - 1) / a.blocks_per_cta;
+    if (ksplit > 1) QTB_CUDA(cudaMemsetAsync(d_out, 0, size_t(batch) * m->rows * sizeof(int32_t), stream));
+    gemm_i8_tcgen05_kernel<<<std::min(m_tiles * ksplit, m->sm_count), kGemmThreads, gemm_smem_bytes(n, a.stages), stream>>>(map, a);
+    ++g_launches;
+    const cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e, "batched projection launch");
+    return QUINTRIT_OK;
+}
+
+int gemm_check_status(quintrit_b200_matrix* m, cudaStream_t stream) {
+    unsigned int flag = 0;
+    QTB_CUDA(cudaMemcpyAsync(&flag, m->d_gemm_status, sizeof flag, cudaMemcpyDeviceToHost, stream));
+    QTB_CUDA(cudaStreamSynchronize(stream));
+    if (flag != 0) {
+        cudaMemsetAsync(m->d_gemm_status, 0, sizeof flag, stream);
+        return fail(QUINTRIT_ERR_DEVICE, "the batched projection kernel on the CUDA device gave up waiting at a barrier");
+    }
+    return QUINTRIT_OK;
+}
+
+}  // namespace
+
+extern "C" int quintrit_b200_gemm_i32_device(quintrit_b200_matrix_t* matrix, const int8_t* d_activations, size_t batch, int32_t* d_out, void* stream) {
+    return guard([&]() -> int {
+        int rc = check_matrix(matrix, true);
+        if (rc != QUINTRIT_OK) return rc;
+        if (d_activations == nullptr || d_out == nullptr) return fail(QUINTRIT_ERR_NULL_POINTER, "a device pointer is NULL");
+        if (batch == 0 || batch > (size_t(1) << 20)) return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "batch must be in [1, 2^20]");
+        DeviceGuard g(matrix->device);
+        if ((rc = gemm_prepare(matrix)) != QUINTRIT_OK) return rc;
+        for (size_t b0 = 0; b0 < batch; b0 += kGemmMaxN) {
+            const int nb = static_cast<int>(std::min<size_t>(kGemmMaxN, batch - b0));
+            if ((rc = gemm_launch(matrix, d_activations + b0 * matrix->cols, nb, d_out + b0 * matrix->rows, static_cast<cudaStream_t>(stream))) != QUINTRIT_OK) return rc;
+        }
+        return ok();
+    });
+}
+
+extern "C" int quintrit_b200_gemm_i32(quintrit_b200_matrix_t* matrix, const int8_t* activations, size_t activations_len, size_t batch, int32_t* out, size_t out_capacity) {
+    return guard([&]() -> int {
+        int rc = check_matrix(matrix, true);
+        if (rc != QUINTRIT_OK) return rc;
+        if (activations == nullptr || out == nullptr) return fail(QUINTRIT_ERR_NULL_POINTER, "activations or out is NULL");
+        if (batch == 0 || batch > (size_t(1) << 20)) return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "batch must be in [1, 2^20]");
+        if (activations_len < batch * matrix->cols) return fail(QUINTRIT_ERR_BUFFER_TOO_SMALL, "activations hold %zu values, %zu x %zu are needed", activations_len, batch, matrix->cols);
+        if (out_capacity < batch * matrix->rows) return fail(QUINTRIT_ERR_BUFFER_TOO_SMALL, "out holds %zu values, %zu x %zu are needed", out_capacity, batch, matrix->rows);
+        DeviceGuard g(matrix->device);
+        if ((rc = gemm_prepare(matrix)) != QUINTRIT_OK) return rc;
+        for (size_t b0 = 0; b0 < batch; b0 += kGemmMaxN) {
+            const int nb = static_cast<int>(std::min<size_t>(kGemmMaxN, batch - b0));
+            QTB_CUDA(cudaMemcpyAsync(matrix->d_gemm_in, activations + b0 * matrix->cols, size_t(nb) * matrix->cols, cudaMemcpyHostToDevice, nullptr));
+            if ((rc = gemm_launch(matrix, matrix->d_gemm_in, nb, matrix->d_gemm_out, nullptr)) != QUINTRIT_OK) return rc;
+            QTB_CUDA(cudaMemcpyAsync(out + b0 * matrix->rows, matrix->d_gemm_out, size_t(nb) * matrix->rows * sizeof(int32_t), cudaMemcpyDeviceToHost, nullptr));
+            if ((rc = gemm_check_status(matrix, nullptr)) != QUINTRIT_OK) return rc;
+        }
         return ok();
     });
 }
