@@ -347,9 +347,9 @@ int quintrit_b200_selftest_barrier(uint32_t device_index, uint32_t ctas, uint32_
 /* ---- batched projection on the tensor cores: out[b][n] = sum_k trit[n][k] * act[b][k] for `batch` int8 activation vectors
  * ([batch][cols], row-major), the integers quintrit_b200_gemv_i32 gives vector by vector (so every vector may carry its own
  * activation scale, as the tokens of a prompt do: quintrit-runtime/src/layer.rs:123-177 per token). out is [batch][rows]. The
- * weights are decoded from their velurex bytes inside the kernel (tcgen05.mma.kind::i8, accumulator in tensor memory, activations
- * by TMA); the first call on a matrix makes a second device copy of its bytes in the order this kernel reads (0.2 bytes per
- * weight more). Per-tensor matrices only (not Q2_0). The _device form takes device pointers and enqueues on `stream` without
+ * kernel is tcgen05.mma.kind::i8 with the accumulator in tensor memory and the activations fetched by TMA; the first call on a
+ * matrix makes a second device copy of its weights with two bits per trit in the order this kernel reads (0.25 bytes per weight
+ * more), from which int8 operands are made with one table lookup per four weights. Per-tensor matrices only (not Q2_0). The _device form takes device pointers and enqueues on `stream` without
  * waiting; its status is reported by the next host-buffer call on the matrix. ---- */
 int quintrit_b200_gemm_i32(quintrit_b200_matrix_t* matrix, const int8_t* activations, size_t activations_len, size_t batch, int32_t* out, size_t out_capacity);
 int quintrit_b200_gemm_i32_device(quintrit_b200_matrix_t* matrix, const int8_t* d_activations, size_t batch, int32_t* d_out, void* stream);

@@ -36,13 +36,14 @@ struct quintrit_b200_matrix {
     float* d_wscales = nullptr;
     float* d_x = nullptr;    // cols floats: activations of one call
     float* d_as = nullptr;   // cols / 32 activation block scales
-    // batched projection on the tensor cores (gemm_tc.cuh): block-major planar copy of the weights and call buffers, made on first use
+    // batched projection on the tensor cores (gemm_tc.cuh): two-bit block-major copy of the weights and call buffers, made on first use
     uint8_t* d_gemm_w = nullptr;
     size_t gemm_rows_padded = 0;
-    int8_t* d_gemm_act = nullptr;     // kGemmMaxN x blocks * 160, zero padded
+    int8_t* d_gemm_act = nullptr;     // kGemmMaxN x whole 128-column blocks, zero padded
     int8_t* d_gemm_in = nullptr;      // host-call staging: kGemmMaxN x cols
     int32_t* d_gemm_out = nullptr;    // host-call staging: kGemmMaxN x rows
     unsigned int* d_gemm_status = nullptr;
+    int32_t* d_gemm_parts = nullptr;  // partial sums of a projection whose K is split: kGemmMaxParts x kGemmMaxN x rows
 };
 
 struct quintrit_b200_plan {
@@ -308,6 +309,7 @@ void destroy_matrix(quintrit_b200_matrix* m) {
     cudaFree(m->d_gemm_in);
     cudaFree(m->d_gemm_out);
     cudaFree(m->d_gemm_status);
+    cudaFree(m->d_gemm_parts);
     m->magic = 0;
     delete m;
 }
@@ -1882,6 +1884,8 @@ extern "C" int quintrit_b200_decoder_trace_step(quintrit_b200_decoder_t* decoder
 namespace {
 
 std::mutex g_gemm_lock;
+constexpr int kGemmMaxParts = 8;
+constexpr size_t kGemmSmemLimit = 227 * 1024;  // dynamic shared memory a CTA may ask for on this device
 typedef CUresult (*TensorMapEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
                                       CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
@@ -1899,24 +1903,24 @@ int tensor_map_encoder(TensorMapEncodeFn* out) {
     return QUINTRIT_OK;
 }
 
-// Makes the block-major planar copy and the call buffers of a matrix the first time it is used by the batched projection.
+// Makes the two-bit copy of the weights and the call buffers of a matrix the first time it is used by the batched projection.
 int gemm_prepare(quintrit_b200_matrix* m) {
     std::lock_guard<std::mutex> hold(g_gemm_lock);
     if (m->d_gemm_w != nullptr) return QUINTRIT_OK;
     if (m->block_scaled) return fail(QUINTRIT_ERR_UNSUPPORTED, "the batched projection takes per-tensor ternary matrices, not block-scaled (Q2_0) ones");
-    const size_t rows_padded = (m->rows + kGemmM - 1) / kGemmM * kGemmM, k_pad = m->blocks * kBlockTrits;
+    const size_t rows_padded = (m->rows + kGemmM - 1) / kGemmM * kGemmM, gblocks = (m->cols + kGemmBlockCols - 1) / kGemmBlockCols, k_pad = gblocks * kGemmBlockCols;
     uint8_t* w = nullptr;
-    QTB_CUDA(cudaMalloc(&w, m->blocks * rows_padded * 32));
-    const size_t pieces = m->blocks * rows_padded * 2;
-    stream_to_block_major_kernel<<<static_cast<int>(std::min<size_t>((pieces + 255) / 256, 148 * 16)), 256>>>(m->d_w, w, m->rows, rows_padded, m->blocks, m->tiles);
+    QTB_CUDA(cudaMalloc(&w, gblocks * rows_padded * 32));
+    const size_t bytes = gblocks * rows_padded * 32;
+    stream_to_two_bit_kernel<<<static_cast<int>(std::min<size_t>((bytes + 255) / 256, 148 * 32)), 256>>>(m->d_w, w, m->rows, m->cols, rows_padded, gblocks, m->blocks, m->tiles);
     ++g_launches;
     cudaError_t e = cudaGetLastError();
     if (e == cudaSuccess) e = cudaMalloc(&m->d_gemm_act, size_t(kGemmMaxN) * k_pad);
     if (e == cudaSuccess) e = cudaMalloc(&m->d_gemm_in, size_t(kGemmMaxN) * m->cols);
     if (e == cudaSuccess) e = cudaMalloc(&m->d_gemm_out, size_t(kGemmMaxN) * m->rows * sizeof(int32_t));
-    if (e == cudaSuccess) e = cudaMalloc(&m->d_gemm_status, sizeof(unsigned int));
-    if (e == cudaSuccess) e = cudaMemset(m->d_gemm_status, 0, sizeof(unsigned int));
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_i8_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(gemm_smem_bytes(kGemmMaxN, 3)));
+    if (e == cudaSuccess) e = cudaMalloc(&m->d_gemm_status, 4096);  // the status word; the rest is used by debug builds only
+    if (e == cudaSuccess) e = cudaMemset(m->d_gemm_status, 0, 4096);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_i8_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kGemmSmemLimit));
     if (e == cudaSuccess) e = cudaDeviceSynchronize();
     if (e != cudaSuccess) {
         cudaFree(w);
@@ -1932,45 +1936,63 @@ int gemm_launch(quintrit_b200_matrix* m, const int8_t* d_act, int batch, int32_t
     TensorMapEncodeFn encode = nullptr;
     int rc = tensor_map_encoder(&encode);
     if (rc != QUINTRIT_OK) return rc;
-    const int n = std::max(16, (batch + 15) / 16 * 16), k_pad = static_cast<int>(m->blocks * kBlockTrits);
+    const int gblocks = static_cast<int>((m->cols + kGemmBlockCols - 1) / kGemmBlockCols);
+    const int n = std::max(16, (batch + 15) / 16 * 16), k_pad = gblocks * kGemmBlockCols;
     // The TMA reads the caller's vectors in place when their pitch and address allow it (columns and vectors beyond the matrix read as zeros);
     // otherwise they are first copied into a zero-padded matrix with a pitch of whole blocks.
-    const bool in_place = m->cols % 16 == 0 && reinterpret_cast<uintptr_t>(d_act) % 16 == 0;
+    const bool in_place = m->cols % 32 == 0 && reinterpret_cast<uintptr_t>(d_act) % 16 == 0;
     const void* base = d_act;
-    cuuint64_t dims[2] = {static_cast<cuuint64_t>(m->cols), static_cast<cuuint64_t>(batch)};
+    cuuint64_t pitch = m->cols, vectors = static_cast<cuuint64_t>(batch);
     if (!in_place) {
         gemm_pad_activations_kernel<<<std::min((n * k_pad + 255) / 256, 148 * 8), 256, 0, stream>>>(d_act, m->d_gemm_act, batch, n, static_cast<int>(m->cols), k_pad);
         ++g_launches;
-        base = m->d_gemm_act, dims[0] = static_cast<cuuint64_t>(k_pad), dims[1] = static_cast<cuuint64_t>(n);
+        base = m->d_gemm_act, pitch = static_cast<cuuint64_t>(k_pad), vectors = static_cast<cuuint64_t>(n);
     }
+    // the activations as a 3-D tensor: 32 bytes of a K tile, the vectors, the K tiles of a vector; a box is 32 x n x 4 (the four tiles of a block)
     CUtensorMap map;
-    const cuuint64_t strides[1] = {dims[0]};  // bytes between activation vectors: a multiple of 16 in both cases
-    const cuuint32_t box[2] = {32, static_cast<cuuint32_t>(n)}, elem[2] = {1, 1};
-    const CUresult cr = encode(&map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_32B,
+    const cuuint64_t dims[3] = {32, vectors, pitch / 32};
+    const cuuint64_t strides[2] = {pitch, 32};  // bytes between vectors and between K tiles: multiples of 16
+    const cuuint32_t box[3] = {32, static_cast<cuuint32_t>(n), 4}, elem[3] = {1, 1, 1};
+    const CUresult cr = encode(&map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_32B,
                                CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (cr != CUDA_SUCCESS) return fail(QUINTRIT_ERR_DEVICE, "cuTensorMapEncodeTiled failed with CUDA driver error %d", static_cast<int>(cr));
     GemmArgs a;
     a.w = m->d_gemm_w, a.out = d_out, a.status = m->d_gemm_status;
-    a.rows = static_cast<int>(m->rows), a.rows_padded = static_cast<int>(m->gemm_rows_padded), a.blocks = static_cast<int>(m->blocks);
+    a.rows = static_cast<int>(m->rows), a.rows_padded = static_cast<int>(m->gemm_rows_padded), a.blocks = gblocks;
     a.n = n, a.batch = batch;
-    a.stages = n > 160 ? 3 : 4;
-    a.spin_limit = 1u << 22;
-    // Work items are (row tile, K part); K is split (at least four blocks a part) where the items of whole tiles would leave SMs idle: the cost of a
-    // split is the largest number of items an SM gets times the blocks of an item plus about one block for its epilogue.
+    a.stages = gemm_stages_for(n, kGemmSmemLimit);
+    if (const char* v = std::getenv("QUINTRIT_B200_GEMM_STAGES")) a.stages = std::max(2, std::min(std::atoi(v), a.stages));  // experiments: fewer stages (at least two: see the decode groups)
+    a.spin_limit = 1u << 16;  // polls of up to 20 us each: about a second before a wait gives up
+    // Work items are (row tile, K part); K is split (at least four blocks a part, at most kGemmMaxParts parts) where the items of whole tiles would
+    // leave SMs idle: the cost of a split is the largest number of items an SM gets times the blocks of an item plus about one block for its
+    // epilogue, plus the pass that adds the parts (its bytes at about 3 TB/s against 0.4 us a block).
     const int m_tiles = a.rows_padded / kGemmM;
     int ksplit = 1;
     long best = -1;
-    for (int ks = 1; ks <= std::max(1, a.blocks / 4); ++ks) {
+    for (int ks = 1; ks <= std::min(kGemmMaxParts, std::max(1, a.blocks / 4)); ++ks) {
         const int per = (a.blocks + ks - 1) / ks, parts = (a.blocks + per - 1) / per;
-        const long waves = (long(m_tiles) * parts + m->sm_count - 1) / m->sm_count, cost = waves * (per + 1 + (parts > 1 ? 1 : 0));
+        const long waves = (long(m_tiles) * parts + m->sm_count - 1) / m->sm_count;
+        const long add_pass = parts > 1 ? long((parts + 1) * double(batch) * double(m->rows) * 4.0 / 1.2e6) + 3 : 0;  // bytes the second kernel moves, in units of a block's time
+        const long cost = waves * (per + 1) + add_pass;
         if (best < 0 || cost < best) best = cost, ksplit = parts;
     }
-    if (const char* v = std::getenv("QUINTRIT_B200_GEMM_KSPLIT")) ksplit = std::max(1, std::min(std::atoi(v), a.blocks));
+    if (const char* v = std::getenv("QUINTRIT_B200_GEMM_KSPLIT")) ksplit = std::max(1, std::min({std::atoi(v), a.blocks, kGemmMaxParts}));
     a.blocks_per_cta = (a.blocks + ksplit - 1) / ksplit;
     ksplit = (a.blocks + a.blocks_per_cta - 1) / a.blocks_per_cta;
-    if (ksplit > 1) QTB_CUDA(cudaMemsetAsync(d_out, 0, size_t(batch) * m->rows * sizeof(int32_t), stream));
+    if (ksplit > 1) {
+        if (m->d_gemm_parts == nullptr) {
+            std::lock_guard<std::mutex> hold(g_gemm_lock);
+            if (m->d_gemm_parts == nullptr) QTB_CUDA(cudaMalloc(&m->d_gemm_parts, size_t(kGemmMaxParts) * kGemmMaxN * m->rows * sizeof(int32_t)));
+        }
+        a.out = m->d_gemm_parts;
+    }
     gemm_i8_tcgen05_kernel<<<std::min(m_tiles * ksplit, m->sm_count), kGemmThreads, gemm_smem_bytes(n, a.stages), stream>>>(map, a);
     ++g_launches;
+    if (ksplit > 1) {
+        const size_t count = size_t(batch) * m->rows;
+        gemm_reduce_parts_kernel<<<static_cast<int>(std::min<size_t>((count + 255) / 256, size_t(m->sm_count) * 8)), 256, 0, stream>>>(m->d_gemm_parts, d_out, count, ksplit);
+        ++g_launches;
+    }
     const cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "batched projection launch");
     return QUINTRIT_OK;
@@ -2025,5 +2047,12 @@ extern "C" int quintrit_b200_gemm_i32(quintrit_b200_matrix_t* matrix, const int8
         return ok();
     });
 }
+
+#ifdef QTB_GEMM_TRACE
+extern "C" int quintrit_b200_debug_gemm_trace(quintrit_b200_matrix_t* m, long long* out) {  // debug builds: 4 roles x 4 events x 16 blocks of cycle stamps
+    cudaDeviceSynchronize();
+    return cudaMemcpy(out, m->d_gemm_status + 64, 4 * 4 * 16 * sizeof(long long), cudaMemcpyDeviceToHost);
+}
+#endif
 
 #include "runtime.cuh"
