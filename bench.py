@@ -474,6 +474,51 @@ def run_reference_cuda(args, rank: int, world: int, local_rank: int):
     }), flush=True)
 
 
+def run_prefill(args, mats, shapes, dev, batch: int = 256, passes: int = 3):
+    """The batched projections of a prompt chunk on the tensor cores (quintrit_b200_gemm_i32_device, tcgen05 int8): all projections of the sweep for
+    `batch` activation vectors at once, activations resident in HBM. Reported beside the batch-1 sweep: how many tokens' worth of projections a
+    second of this kernel gives, its int8 rate, and one projection checked against the batch-1 kernel."""
+    import torch
+
+    stream = torch.cuda.current_stream().cuda_stream
+    by_cols, outs = {}, {}
+    for (_, _, n, k) in shapes:
+        if k not in by_cols:
+            by_cols[k] = torch.randint(-128, 128, (batch, k), dtype=torch.int8, device=dev)
+        if n not in outs:
+            outs[n] = torch.zeros((batch, n), dtype=torch.int32, device=dev)
+
+    def one_pass():
+        for m, (_, _, n, k) in zip(mats, shapes):
+            m.gemm_i32_device(by_cols[k].data_ptr(), batch, outs[n].data_ptr(), stream)
+
+    one_pass()  # makes the two-bit copies of the weights
+    torch.cuda.synchronize()
+    m0, (_, _, n0, k0) = mats[0], shapes[0]
+    m0.gemm_i32_device(by_cols[k0].data_ptr(), batch, outs[n0].data_ptr(), stream)
+    torch.cuda.synchronize()
+    got = outs[n0][batch - 1].cpu().numpy()
+    parity = bool(np.array_equal(got, m0.gemv_i32(by_cols[k0][batch - 1].cpu().numpy())))
+    one_pass()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(passes):
+        one_pass()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / passes
+    weights = sum(n * k for _, _, n, k in shapes)
+    tops = 2.0 * weights * batch / (ms * 1e-3) / 1e12
+    try:
+        bf16 = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops"])
+    except Exception:
+        bf16 = 1590.0
+    return {"kernel": "gemm_i8_tcgen05_kernel", "batch": batch, "projections": len(mats), "ms_per_pass": round(ms, 3), "tokens_per_s_projections_only": round(batch / (ms * 1e-3), 1),
+            "int8_tops": round(tops, 1), "peak_tops": round(2 * bf16, 1), "peak_kind": "twice the measured dense bf16 rate (int8 runs at twice the bf16 rate on this part)",
+            "tensor_frac": round(tops / (2 * bf16), 4), "bit_exact_vs_batch1": parity,
+            "note": "every vector has its own activation scale downstream; the integers equal the batch-1 kernel's vector by vector"}
+
+
 def run_ours(args, rank: int, world: int, local_rank: int):
     import torch
 
@@ -587,6 +632,12 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         same = bool(ok.item())
     decode_tp = None
     h2d_bytes, d2h_bytes = int(plan.act_total), int(plan.out_total * 4)
+    prefill = None
+    if world == 1 and not args.no_prefill:
+        try:
+            prefill = run_prefill(args, mats, shapes, dev)
+        except Exception as e:  # the sweep line must still be printed
+            prefill = {"error": f"{type(e).__name__}: {e}"}
     if dist is not None and not args.no_decode:
         del plan, mats
         torch.cuda.empty_cache()
@@ -624,6 +675,8 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         "deterministic": same,
         "setup_s": round(t_setup, 1),
     }
+    if prefill is not None:
+        line["prefill"] = prefill
     if decode_tp is not None:
         line["decode"] = decode_tp
     if world == 1 and not args.no_decode:
@@ -658,6 +711,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--preheat", type=float, default=1.0, help="seconds of untimed back-to-back passes right before the timed steps")
     ap.add_argument("--no-decode", action="store_true", help="skip the whole-token decode leg")
+    ap.add_argument("--no-prefill", action="store_true", help="skip the batched-projection (tensor core) leg")
     ap.add_argument("--decode-only", action="store_true", help="run only the whole-token decode leg and print its object (profiling aid)")
     ap.add_argument("--block-scaled-only", action="store_true", help="run only the block-scaled (Q2_0) projection on the model's shapes (profiling aid)")
     ap.add_argument("--decode-shape", default="falcon3_10b", choices=["falcon3_10b", "bitnet_2b"])

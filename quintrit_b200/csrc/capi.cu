@@ -1916,8 +1916,6 @@ int gemm_prepare(quintrit_b200_matrix* m) {
     ++g_launches;
     cudaError_t e = cudaGetLastError();
     if (e == cudaSuccess) e = cudaMalloc(&m->d_gemm_act, size_t(kGemmMaxN) * k_pad);
-    if (e == cudaSuccess) e = cudaMalloc(&m->d_gemm_in, size_t(kGemmMaxN) * m->cols);
-    if (e == cudaSuccess) e = cudaMalloc(&m->d_gemm_out, size_t(kGemmMaxN) * m->rows * sizeof(int32_t));
     if (e == cudaSuccess) e = cudaMalloc(&m->d_gemm_status, 4096);  // the status word; the rest is used by debug builds only
     if (e == cudaSuccess) e = cudaMemset(m->d_gemm_status, 0, 4096);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_i8_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kGemmSmemLimit));
@@ -2037,6 +2035,20 @@ extern "C" int quintrit_b200_gemm_i32(quintrit_b200_matrix_t* matrix, const int8
         if (out_capacity < batch * matrix->rows) return fail(QUINTRIT_ERR_BUFFER_TOO_SMALL, "out holds %zu values, %zu x %zu are needed", out_capacity, batch, matrix->rows);
         DeviceGuard g(matrix->device);
         if ((rc = gemm_prepare(matrix)) != QUINTRIT_OK) return rc;
+        if (matrix->d_gemm_in == nullptr) {  // staging of host-buffer calls, made when the first one comes
+            std::lock_guard<std::mutex> hold(g_gemm_lock);
+            if (matrix->d_gemm_in == nullptr) {
+                int32_t* o = nullptr;
+                int8_t* in = nullptr;
+                QTB_CUDA(cudaMalloc(&o, size_t(kGemmMaxN) * matrix->rows * sizeof(int32_t)));
+                const cudaError_t e = cudaMalloc(&in, size_t(kGemmMaxN) * matrix->cols);
+                if (e != cudaSuccess) {
+                    cudaFree(o);
+                    return cuda_fail(e, "cudaMalloc(batched projection staging)");
+                }
+                matrix->d_gemm_out = o, matrix->d_gemm_in = in;
+            }
+        }
         for (size_t b0 = 0; b0 < batch; b0 += kGemmMaxN) {
             const int nb = static_cast<int>(std::min<size_t>(kGemmMaxN, batch - b0));
             QTB_CUDA(cudaMemcpyAsync(matrix->d_gemm_in, activations + b0 * matrix->cols, size_t(nb) * matrix->cols, cudaMemcpyHostToDevice, nullptr));

@@ -82,8 +82,11 @@ def test_rejections(tmp_path):
     assert code(junk)[0] == 8
     good = tmp_path / "good.gguf"
     gguf_io.write_model_gguf(good, spec, trits, gguf_io.GGML_I2_S)
-    assert code(good, flags=1)[0] == 2                      # unknown flag bits
-    assert code(good, context=100)[0] == 2                  # below 256 positions
+    assert code(good, flags=2)[0] == 2                      # unknown flag bits (1 = QUINTRIT_MODEL_OPEN_VERBOSE is accepted and changes nothing)
+    assert code(good, context=100)[0] == 2                  # a window below 256 positions is kept as it is (gpu.rs:141-146) but must be a multiple of 8
+    small = q.Decoder.open(good, context=96, flags=1)
+    assert small.info()["context_length"] == 96
+    small.free()
     meta = {"general.architecture": "llama", "llama.embedding_length": 256, "llama.attention.head_count": 4, "llama.vocab_size": 300}
     # a missing projection names the tensor
     miss = tmp_path / "miss.gguf"
