@@ -48,6 +48,25 @@ def shard_rows(n: int, rank: int, world: int):
     return min(t0 * 32, n), min(t1 * 32, n)
 
 
+def shard_plan(layers: int, rank: int, world: int):
+    """What rank `rank` of `world` streams, as (layer, projection, first row, end row, columns) per work unit, and the name of the rule.
+
+    The projections of the sweep are independent objects. When the layers divide evenly, a rank takes whole layers (every layer has the same
+    weights, so the shares are equal and every matrix keeps its full height: the kernel builds one activation table per pair of 160-column blocks
+    and reuses it for all rows it streams, so short matrices cost more per weight); otherwise every projection is cut by rows. Neither
+    needs a collective."""
+    shapes = sweep_shapes(layers)
+    if world > 1 and layers % world == 0:
+        per = layers // world
+        return [(l, p, 0, n, k) for (l, p, n, k) in shapes if rank * per <= l < (rank + 1) * per], f"layers/{world}"
+    out = []
+    for (l, p, n, k) in shapes:
+        r0, r1 = shard_rows(n, rank, world)
+        if r1 > r0:
+            out.append((l, p, r0, r1, k))
+    return out, f"rows/{world}"
+
+
 def activations_for(layer: int, proj: int, cols: int) -> np.ndarray:
     x = synth.normal_f32(synth.seed_for(CONFIG_ID, layer, proj, 2), cols)
     return synth.quantize_int8_np(x)[0]
@@ -172,7 +191,7 @@ def pin_to_all_cores():
 def sweep_config(layers: int, world: int, weights_total: int) -> dict:
     """The `config` object of the sweep line; both arms print the same one."""
     return {"workload": "falcon3_10b_gemv_sweep", "layers": layers, "projections": 7 * layers, "batch": 1, "weights": weights_total,
-            "l2": "inputs (1.9 GB of weights per pass) exceed L2", "sharding": f"rows/{world}, no collective"}
+            "l2": f"inputs ({weights_total * BYTES_PER_WEIGHT / 1e9:.1f} GB of weights per pass over all GPUs) exceed L2", "sharding": f"{shard_plan(layers, 0, world)[1]}, no collective"}
 
 
 def run_decode(args, local_rank: int):
@@ -539,10 +558,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     # ---- build the sweep: weights generated on the device, transcoded by the library ----
     t_setup = time.time()
     mats, acts, shapes = [], [], []
-    for (l, p, n, k) in sweep_shapes(args.layers):
-        r0, r1 = shard_rows(n, rank, world)
-        if r1 <= r0:
-            continue
+    for (l, p, r0, r1, k) in shard_plan(args.layers, rank, world)[0]:
         planar = synth.torch_planar(synth.seed_for(CONFIG_ID, l, p, 0), r1 - r0, k, dev, row0=r0).cpu().numpy()
         mats.append(q.Matrix(planar, r1 - r0, k, device=local_rank))
         acts.append(activations_for(l, p, k))

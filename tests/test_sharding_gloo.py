@@ -85,3 +85,23 @@ def test_shards_partition_the_rows_in_whole_tiles(rows, world):
         assert r0 % 32 == 0 and r1 % 32 == 0  # only the last shard may end inside a tile
     sizes = [(b[1] - b[0] + 31) // 32 for b in bounds]
     assert max(sizes) - min(sizes) <= 1  # tiles are balanced to within one
+
+
+@pytest.mark.parametrize("layers,world", [(40, 1), (40, 2), (40, 4), (40, 8), (12, 8), (7, 2)])
+def test_shard_plan_covers_every_weight_once(layers, world):
+    """Whole layers per rank when they divide evenly (equal shares, full-height matrices), rows otherwise; either way every weight exactly once."""
+    import bench
+
+    seen = {}
+    totals = []
+    for r in range(world):
+        units, rule = bench.shard_plan(layers, r, world)
+        assert rule == (f"layers/{world}" if world > 1 and layers % world == 0 else f"rows/{world}")
+        totals.append(sum((r1 - r0) * k for _, _, r0, r1, k in units))
+        for (l, p, r0, r1, k) in units:
+            for a, b in seen.get((l, p), []):
+                assert r1 <= a or r0 >= b  # row ranges of one projection never overlap
+            seen.setdefault((l, p), []).append((r0, r1))
+    for (l, p, n, k) in bench.sweep_shapes(layers):
+        assert sum(b - a for a, b in seen[(l, p)]) == n
+    assert max(totals) <= min(totals) * 1.02 + 32 * 23040  # balanced to a tile row of the widest matrix
