@@ -344,6 +344,17 @@ int quintrit_b200_decoder_trace_step(quintrit_b200_decoder_t* decoder, uint64_t*
  */
 int quintrit_b200_selftest_barrier(uint32_t device_index, uint32_t ctas, uint32_t spin_limit, uint32_t* out_released);
 
+/*
+ * Prompt ingestion: `count` tokens at positions pos .. pos + count - 1 in chunks of up to 256, every projection of a chunk as one
+ * batched product on the tensor cores (quintrit_b200_gemm_i32). The reference ingests a prompt token by token
+ * (quintrit-c/src/runtime.rs:430-436); the result here is bit for bit that of `count` calls of quintrit_b200_decoder_forward:
+ * the KV cache, the position, and - for the last token - the logits and the greedy choice (logits and out_token may be NULL).
+ * Per-tensor ternary models on one GPU; block-scaled (Q2_0) and tensor-parallel decoders give QUINTRIT_ERR_UNSUPPORTED. The
+ * text and token entry points of the runtime level use it for prompts of 8 tokens or more.
+ */
+int quintrit_b200_decoder_prefill(quintrit_b200_decoder_t* decoder, const uint32_t* tokens, size_t count, uint32_t pos, float* logits, size_t logits_capacity,
+                                  uint32_t* out_token);
+
 /* ---- batched projection on the tensor cores: out[b][n] = sum_k trit[n][k] * act[b][k] for `batch` int8 activation vectors
  * ([batch][cols], row-major), the integers quintrit_b200_gemv_i32 gives vector by vector (so every vector may carry its own
  * activation scale, as the tokens of a prompt do: quintrit-runtime/src/layer.rs:123-177 per token). out is [batch][rows]. The

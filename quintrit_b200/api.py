@@ -120,6 +120,7 @@ def load_library(build_if_missing: bool = True) -> C.CDLL:
     l.quintrit_b200_decoder_info.argtypes = [C.c_void_p, C.POINTER(_DecoderInfoC)]
     l.quintrit_b200_gguf_describe.argtypes = [C.c_char_p, C.c_char_p, _sz, C.POINTER(_sz)]
     l.quintrit_b200_decoder_forward.argtypes = [C.c_void_p, C.c_uint32, C.c_uint32, _f32p, _sz, C.POINTER(C.c_uint32)]
+    l.quintrit_b200_decoder_prefill.argtypes = [C.c_void_p, C.POINTER(C.c_uint32), _sz, C.c_uint32, _f32p, _sz, C.POINTER(C.c_uint32)]
     l.quintrit_b200_decoder_generate.argtypes = [C.c_void_p, C.POINTER(C.c_uint32), _sz, _sz, C.POINTER(C.c_uint32), _sz]
     l.quintrit_b200_decoder_time_token.argtypes = [C.c_void_p, C.c_uint32, C.c_uint32, C.POINTER(C.c_float)]
     l.quintrit_b200_decoder_trace_step.argtypes = [C.c_void_p, C.POINTER(C.c_uint64), _sz, C.POINTER(_sz)]
@@ -423,6 +424,13 @@ class Decoder:
         self._h = h
         self.vocab = self.info()["vocab_size"]
         return self
+
+    def prefill(self, tokens, pos: int = 0):
+        """Ingests `tokens` at positions pos .. in chunks on the tensor cores; returns (logits of the last token, its greedy successor)."""
+        t = np.ascontiguousarray(tokens, dtype=np.uint32)
+        logits, nxt = np.zeros(self.vocab, np.float32), C.c_uint32(0)
+        _check(load_library().quintrit_b200_decoder_prefill(self._h, t.ctypes.data_as(C.POINTER(C.c_uint32)), t.size, pos, _p(logits, _f32p), logits.size, C.byref(nxt)))
+        return logits, nxt.value
 
     def info(self) -> dict:
         i = _DecoderInfoC()

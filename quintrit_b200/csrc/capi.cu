@@ -1930,7 +1930,8 @@ int gemm_prepare(quintrit_b200_matrix* m) {
 }
 
 // One launch for up to kGemmMaxN activation vectors that are on the device ([batch][cols]); d_out is [batch][rows].
-int gemm_launch(quintrit_b200_matrix* m, const int8_t* d_act, int batch, int32_t* d_out, cudaStream_t stream) {
+int gemm_launch(quintrit_b200_matrix* m, const int8_t* d_act, int batch, int32_t* d_out, cudaStream_t stream, int ldo = 0) {
+    if (ldo == 0) ldo = static_cast<int>(m->rows);
     TensorMapEncodeFn encode = nullptr;
     int rc = tensor_map_encoder(&encode);
     if (rc != QUINTRIT_OK) return rc;
@@ -1957,7 +1958,7 @@ int gemm_launch(quintrit_b200_matrix* m, const int8_t* d_act, int batch, int32_t
     GemmArgs a;
     a.w = m->d_gemm_w, a.out = d_out, a.status = m->d_gemm_status;
     a.rows = static_cast<int>(m->rows), a.rows_padded = static_cast<int>(m->gemm_rows_padded), a.blocks = gblocks;
-    a.n = n, a.batch = batch;
+    a.n = n, a.batch = batch, a.ldo = ldo;
     a.stages = gemm_stages_for(n, kGemmSmemLimit);
     if (const char* v = std::getenv("QUINTRIT_B200_GEMM_STAGES")) a.stages = std::max(2, std::min(std::atoi(v), a.stages));  // experiments: fewer stages (at least two: see the decode groups)
     a.spin_limit = 1u << 16;  // polls of up to 20 us each: about a second before a wait gives up
@@ -1982,13 +1983,13 @@ int gemm_launch(quintrit_b200_matrix* m, const int8_t* d_act, int batch, int32_t
             std::lock_guard<std::mutex> hold(g_gemm_lock);
             if (m->d_gemm_parts == nullptr) QTB_CUDA(cudaMalloc(&m->d_gemm_parts, size_t(kGemmMaxParts) * kGemmMaxN * m->rows * sizeof(int32_t)));
         }
-        a.out = m->d_gemm_parts;
+        a.out = m->d_gemm_parts, a.ldo = static_cast<int>(m->rows);
     }
     gemm_i8_tcgen05_kernel<<<std::min(m_tiles * ksplit, m->sm_count), kGemmThreads, gemm_smem_bytes(n, a.stages), stream>>>(map, a);
     ++g_launches;
     if (ksplit > 1) {
         const size_t count = size_t(batch) * m->rows;
-        gemm_reduce_parts_kernel<<<static_cast<int>(std::min<size_t>((count + 255) / 256, size_t(m->sm_count) * 8)), 256, 0, stream>>>(m->d_gemm_parts, d_out, count, ksplit);
+        gemm_reduce_parts_kernel<<<static_cast<int>(std::min<size_t>((count + 255) / 256, size_t(m->sm_count) * 8)), 256, 0, stream>>>(m->d_gemm_parts, d_out, count, ksplit, static_cast<int>(m->rows), ldo);
         ++g_launches;
     }
     const cudaError_t e = cudaGetLastError();
@@ -2056,6 +2057,159 @@ extern "C" int quintrit_b200_gemm_i32(quintrit_b200_matrix_t* matrix, const int8
             QTB_CUDA(cudaMemcpyAsync(out + b0 * matrix->rows, matrix->d_gemm_out, size_t(nb) * matrix->rows * sizeof(int32_t), cudaMemcpyDeviceToHost, nullptr));
             if ((rc = gemm_check_status(matrix, nullptr)) != QUINTRIT_OK) return rc;
         }
+        return ok();
+    });
+}
+
+// ---- prompt ingestion: a chunk of tokens per pass, projections on the tensor cores -------------------------------------------------
+namespace {
+
+constexpr int kPrefillMax = kGemmMaxN;
+
+int prefill_buffers(quintrit_b200_decoder* d) {
+    if (d->pf.x != nullptr) return QUINTRIT_OK;
+    const size_t B = kPrefillMax, H = d->hidden, I = d->inter, qd = d->q_dim, kvd = d->kv_dim, hd = d->head_dim;
+    int rc;
+    if ((rc = dev_alloc(d, &d->pf.tokens, B)) != QUINTRIT_OK || (rc = dev_alloc(d, &d->pf.pos, 4)) != QUINTRIT_OK || (rc = dev_alloc(d, &d->pf.x, B * H)) != QUINTRIT_OK ||
+        (rc = dev_alloc(d, &d->pf.q, B * qd)) != QUINTRIT_OK || (rc = dev_alloc(d, &d->pf.part_acc, B * d->q_heads * 4 * hd)) != QUINTRIT_OK ||
+        (rc = dev_alloc(d, &d->pf.part_ms, B * d->q_heads * 8)) != QUINTRIT_OK || (rc = dev_alloc(d, &d->pf.s_h, B)) != QUINTRIT_OK ||
+        (rc = dev_alloc(d, &d->pf.s_q, B)) != QUINTRIT_OK || (rc = dev_alloc(d, &d->pf.s_i, B)) != QUINTRIT_OK || (rc = dev_alloc(d, &d->pf.a8_h, B * H)) != QUINTRIT_OK ||
+        (rc = dev_alloc(d, &d->pf.a8_q, B * qd)) != QUINTRIT_OK || (rc = dev_alloc(d, &d->pf.a8_i, B * I)) != QUINTRIT_OK ||
+        (rc = dev_alloc(d, &d->pf.acc_qkv, B * (qd + 2 * kvd))) != QUINTRIT_OK || (rc = dev_alloc(d, &d->pf.acc_o, B * H)) != QUINTRIT_OK ||
+        (rc = dev_alloc(d, &d->pf.acc_gu, B * 2 * I)) != QUINTRIT_OK || (rc = dev_alloc(d, &d->pf.acc_down, B * H)) != QUINTRIT_OK)
+        return rc;
+    return QUINTRIT_OK;
+}
+
+// One chunk of n <= kPrefillMax tokens (already in d->pf.tokens) at positions pos0 .. pos0 + n - 1: the launch sequence of enqueue_token with a token
+// index in gridDim.z, the projections as batched products (every token keeps its own activation scale; the integers are those of the batch-1
+// kernel). With `with_head` the last token's logits and greedy choice land in d->logits / d->d_token as after a single step.
+int enqueue_prefill_chunk(quintrit_b200_decoder* d, int n, uint32_t pos0, bool with_head) {
+    cudaStream_t s = d->stream;
+    const int H = d->hidden, I = d->inter, qd = d->q_dim, kvd = d->kv_dim, hd = d->head_dim, qkv = qd + 2 * kvd;
+    QTB_CUDA(cudaMemcpyAsync(d->pf.pos, &pos0, sizeof pos0, cudaMemcpyHostToDevice, s));
+    embed_kernel<<<dim3((H + 255) / 256, n), 256, 0, s>>>(d->embed, d->pf.tokens, H, d->pf.x, d->bf16_tables);
+    QTB_LAUNCH_CHECK();
+    auto mat = [&](int l, int k) { return const_cast<quintrit_b200_matrix*>(d->mats[size_t(l) * 7 + k]); };
+    int rc;
+    for (int l = 0; l < d->layers; ++l) {
+        const float* sc = d->scales.data() + l * 7;
+        NormQuantArgs n1{};
+        n1.x = d->pf.x, n1.b_x = H;
+        if (l > 0) n1.acc_prev = d->pf.acc_down, n1.b_acc = H, n1.scale_prev = d->pf.s_i, n1.ws_prev = d->scales[(l - 1) * 7 + 6];
+        n1.norm_w = d->norms[l * 4 + 0], n1.eps = d->eps, n1.n = H;
+        n1.q_out = d->pf.a8_h, n1.b_q = H, n1.scale_out = d->pf.s_h, n1.b_scale = 1;
+        norm_quant_kernel<<<dim3(1, 1, n), kRowThreads, H * sizeof(float), s>>>(n1);
+        QTB_LAUNCH_CHECK();
+        if ((rc = gemm_launch(mat(l, 0), d->pf.a8_h, n, d->pf.acc_qkv, s, qkv)) != QUINTRIT_OK || (rc = gemm_launch(mat(l, 1), d->pf.a8_h, n, d->pf.acc_qkv + qd, s, qkv)) != QUINTRIT_OK ||
+            (rc = gemm_launch(mat(l, 2), d->pf.a8_h, n, d->pf.acc_qkv + qd + kvd, s, qkv)) != QUINTRIT_OK)
+            return rc;
+        RopeKvArgs rk{};
+        rk.acc = d->pf.acc_qkv, rk.b_acc = qkv, rk.act_scale = d->pf.s_h, rk.b_scale = 1;
+        rk.ws_q = sc[0], rk.ws_k = sc[1], rk.ws_v = sc[2];
+        rk.cos_sin = d->cos_sin, rk.pos = d->pf.pos;
+        rk.q_dim = qd, rk.kv_dim = kvd, rk.head_dim = hd, rk.rope_dims = d->rope_dims, rk.neox = d->arch == QUINTRIT_B200_ARCH_BITNET;
+        rk.q_out = d->pf.q, rk.b_q = qd;
+        rk.k_cache = d->kc + static_cast<size_t>(l) * d->ctx * kvd;
+        rk.v_cache = d->vc + static_cast<size_t>(l) * d->ctx * kvd;
+        rope_kv_kernel<<<dim3(((qd + kvd) / 2 + kvd + 255) / 256, 1, n), 256, 0, s>>>(rk);
+        QTB_LAUNCH_CHECK();
+        AttnArgs at{};
+        at.q = d->pf.q, at.b_q = qd;
+        at.k_cache = rk.k_cache, at.v_cache = rk.v_cache, at.pos = d->pf.pos;
+        at.head_dim = hd, at.kv_dim = kvd, at.gqa = d->q_heads / d->kv_heads, at.ctx = d->ctx, at.f32_values = d->f32_values;
+        at.scale = 1.0f / std::sqrt(static_cast<float>(hd));
+        at.part_acc = d->pf.part_acc, at.b_acc = d->q_heads * 4 * hd, at.part_ms = d->pf.part_ms, at.b_ms = d->q_heads * 8;
+        attention_kernel<<<dim3(d->q_heads, 4, n), kAttnThreads, 0, s>>>(at);
+        QTB_LAUNCH_CHECK();
+        AttnFinishArgs af{};
+        af.part_acc = d->pf.part_acc, af.b_acc = d->q_heads * 4 * hd, af.part_ms = d->pf.part_ms, af.b_ms = d->q_heads * 8, af.pos = d->pf.pos;
+        af.q_heads = d->q_heads, af.head_dim = hd, af.ctx = d->ctx;
+        af.sub_norm_w = d->norms[l * 4 + 2], af.eps = d->eps;
+        af.q_out = d->pf.a8_q, af.b_q = qd, af.scale_out = d->pf.s_q, af.b_scale = 1;
+        attn_finish_kernel<<<dim3(1, 1, n), kRowThreads, qd * sizeof(float), s>>>(af);
+        QTB_LAUNCH_CHECK();
+        if ((rc = gemm_launch(mat(l, 3), d->pf.a8_q, n, d->pf.acc_o, s)) != QUINTRIT_OK) return rc;
+        NormQuantArgs n2{};
+        n2.x = d->pf.x, n2.b_x = H, n2.acc_prev = d->pf.acc_o, n2.b_acc = H, n2.scale_prev = d->pf.s_q, n2.ws_prev = sc[3];
+        n2.norm_w = d->norms[l * 4 + 1], n2.eps = d->eps, n2.n = H;
+        n2.q_out = d->pf.a8_h, n2.b_q = H, n2.scale_out = d->pf.s_h, n2.b_scale = 1;
+        norm_quant_kernel<<<dim3(1, 1, n), kRowThreads, H * sizeof(float), s>>>(n2);
+        QTB_LAUNCH_CHECK();
+        if ((rc = gemm_launch(mat(l, 4), d->pf.a8_h, n, d->pf.acc_gu, s, 2 * I)) != QUINTRIT_OK || (rc = gemm_launch(mat(l, 5), d->pf.a8_h, n, d->pf.acc_gu + I, s, 2 * I)) != QUINTRIT_OK)
+            return rc;
+        ActQuantArgs aq{};
+        aq.acc_gate = d->pf.acc_gu, aq.acc_up = d->pf.acc_gu + I, aq.b_acc = 2 * I, aq.act_scale = d->pf.s_h, aq.b_scale = 1;
+        aq.ws_gate = sc[4], aq.ws_up = sc[5];
+        aq.n = I, aq.relu2 = d->arch == QUINTRIT_B200_ARCH_BITNET;
+        aq.sub_norm_w = d->norms[l * 4 + 3], aq.eps = d->eps;
+        aq.q_out = d->pf.a8_i, aq.b_q = I, aq.scale_out = d->pf.s_i;
+        act_quant_kernel<<<dim3(1, 1, n), kRowThreads, I * sizeof(float), s>>>(aq);
+        QTB_LAUNCH_CHECK();
+        if ((rc = gemm_launch(mat(l, 6), d->pf.a8_i, n, d->pf.acc_down, s)) != QUINTRIT_OK) return rc;
+    }
+    if (with_head) {  // the last token of the chunk: final norm, output head, greedy choice, as a single step ends
+        const size_t last = static_cast<size_t>(n - 1);
+        NormQuantArgs nf{};
+        nf.x = d->pf.x + last * H, nf.acc_prev = d->pf.acc_down + last * H, nf.scale_prev = d->pf.s_i + last;
+        nf.ws_prev = d->scales[(d->layers - 1) * 7 + 6], nf.norm_w = d->out_norm, nf.eps = d->eps, nf.n = H;
+        nf.y16_out = d->x16, nf.y16_bf16 = d->bf16_tables;
+        norm_quant_kernel<<<1, kRowThreads, H * sizeof(float), s>>>(nf);
+        QTB_LAUNCH_CHECK();
+        lm_head_kernel<<<d->sm_count * 8, 256, H * sizeof(float), s>>>(d->lm_head, d->x16, H, d->vocab, d->logits, d->bf16_tables);
+        QTB_LAUNCH_CHECK();
+        argmax_kernel<<<1, 1024, 0, s>>>(d->logits, d->vocab, d->d_token);
+        QTB_LAUNCH_CHECK();
+    }
+    return QUINTRIT_OK;
+}
+
+// Whether a decoder can ingest prompts in chunks: per-tensor ternary projections on one GPU (the block-scaled and tensor-parallel decoders
+// take their prompts token by token).
+bool prefill_available(const quintrit_b200_decoder* d) { return !d->block_scaled && d->tp_world == 1 && d->hidden % 32 == 0 && d->inter % 32 == 0 && d->q_dim % 32 == 0; }
+
+// Tokens at positions pos0 .. pos0 + count - 1, chunk by chunk; ends like a single step of the last token (logits, greedy token, position).
+int decoder_prefill(quintrit_b200_decoder* d, const uint32_t* tokens, size_t count, uint32_t pos0) {
+    int rc = prefill_buffers(d);
+    if (rc != QUINTRIT_OK) return rc;
+    for (int k = 0; k < d->layers * 7; ++k)
+        if ((rc = gemm_prepare(const_cast<quintrit_b200_matrix*>(d->mats[k]))) != QUINTRIT_OK) return rc;
+    for (size_t c0 = 0; c0 < count; c0 += kPrefillMax) {
+        const int n = static_cast<int>(std::min<size_t>(kPrefillMax, count - c0));
+        QTB_CUDA(cudaMemcpyAsync(d->pf.tokens, tokens + c0, size_t(n) * sizeof(uint32_t), cudaMemcpyHostToDevice, d->stream));
+        QTB_CUDA(cudaMemcpyAsync(d->d_history + pos0 + c0, d->pf.tokens, size_t(n) * sizeof(uint32_t), cudaMemcpyDeviceToDevice, d->stream));
+        if ((rc = enqueue_prefill_chunk(d, n, pos0 + static_cast<uint32_t>(c0), c0 + n == count)) != QUINTRIT_OK) return rc;
+    }
+    const uint32_t next = pos0 + static_cast<uint32_t>(count);  // the device-side position as after `count` single steps
+    QTB_CUDA(cudaMemcpyAsync(d->d_pos, &next, sizeof next, cudaMemcpyHostToDevice, d->stream));
+    return QUINTRIT_OK;
+}
+
+}  // namespace
+
+extern "C" int quintrit_b200_decoder_prefill(quintrit_b200_decoder_t* decoder, const uint32_t* tokens, size_t count, uint32_t pos, float* logits, size_t logits_capacity,
+                                             uint32_t* out_token) {
+    return guard([&]() -> int {
+        int rc = check_decoder(decoder);
+        if (rc != QUINTRIT_OK) return rc;
+        quintrit_b200_decoder* d = decoder;
+        if (tokens == nullptr) return fail(QUINTRIT_ERR_NULL_POINTER, "tokens is NULL");
+        if (count == 0) return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "no tokens to ingest");
+        if (!prefill_available(d)) return fail(QUINTRIT_ERR_UNSUPPORTED, "this decoder takes its prompt token by token (block-scaled or tensor-parallel model)");
+        if (size_t(pos) + count > static_cast<size_t>(d->ctx)) return fail(QUINTRIT_ERR_CONTEXT_OVERFLOW, "%zu tokens from position %u do not fit the context window of %d tokens", count, pos, d->ctx);
+        if (pos > d->host_pos) return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "position %u skips positions: %u tokens are cached", pos, d->host_pos);
+        for (size_t i = 0; i < count; ++i)
+            if (tokens[i] >= static_cast<uint32_t>(d->vocab_full)) return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "token id %u is not below the vocabulary size %d", tokens[i], d->vocab_full);
+        if (logits != nullptr && logits_capacity < static_cast<size_t>(d->vocab)) return fail(QUINTRIT_ERR_BUFFER_TOO_SMALL, "logits hold %zu values, the vocabulary has %d", logits_capacity, d->vocab);
+        DeviceGuard g(d->device);
+        std::vector<uint32_t> pinned(tokens, tokens + count);  // the copies below are asynchronous: keep the ids alive until the synchronisation
+        if ((rc = decoder_prefill(d, pinned.data(), count, pos)) != QUINTRIT_OK) return rc;
+        if (logits) QTB_CUDA(cudaMemcpyAsync(logits, d->logits, size_t(d->vocab) * sizeof(float), cudaMemcpyDeviceToHost, d->stream));
+        if (out_token) QTB_CUDA(cudaMemcpyAsync(out_token, d->d_token, sizeof(uint32_t), cudaMemcpyDeviceToHost, d->stream));
+        if ((rc = decoder_check_status(d)) != QUINTRIT_OK) return rc;
+        for (int k = 0; k < d->layers * 7; k += 7)  // the batched projections report through their matrices' status words; one per layer is enough to see a time-out
+            if ((rc = gemm_check_status(const_cast<quintrit_b200_matrix*>(d->mats[k]), d->stream)) != QUINTRIT_OK) return rc;
+        d->host_pos = pos + static_cast<uint32_t>(count);
         return ok();
     });
 }

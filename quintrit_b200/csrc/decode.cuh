@@ -148,8 +148,10 @@ __device__ __forceinline__ void quantize_vector(const float* y_s, int n, float a
 }
 
 // ---- embedding row: model.rs:308-317 ---------------------------------------------------------------------------------
+// A batch of tokens (prompt ingestion) runs as gridDim.y rows: token[y] -> x[y][hidden].
 __global__ void embed_kernel(const __half* __restrict__ table, const uint32_t* __restrict__ token, int hidden, float* __restrict__ x, bool bf16) {
-    const size_t base = static_cast<size_t>(token[0]) * hidden;
+    const size_t base = static_cast<size_t>(token[blockIdx.y]) * hidden;
+    x += static_cast<size_t>(blockIdx.y) * hidden;
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < hidden; i += gridDim.x * blockDim.x) x[i] = table_to_float(table[base + i], bf16);
 }
 
@@ -174,6 +176,9 @@ struct NormQuantArgs {
     // attention.rs:343), and the codes are Q8_0 blocks with their scales in q8_d
     int block_scaled;
     float* q8_d;
+    // A batch of tokens (prompt ingestion): token blockIdx.z uses x + z * b_x, acc_prev + z * b_acc, q_out + z * b_q, scale_prev + z and
+    // scale_out + z when b_scale is set. All zero for the single-token launches.
+    int b_x, b_acc, b_q, b_scale;
 };
 
 // x += acc * (ws / s)  (model.rs:85, 202 after layer.rs:143-147), y = rms_norm(x) (ops.rs:62-96), codes = quantise(y)
@@ -183,6 +188,16 @@ __global__ void __launch_bounds__(kRowThreads) norm_quant_kernel(NormQuantArgs a
     __shared__ float sh_f[32];
     extern __shared__ float y_s[];  // n floats
     const int tid = threadIdx.x;
+    if (blockIdx.z != 0) {
+        const size_t z = blockIdx.z;
+        a.x += z * a.b_x;
+        if (a.acc_prev != nullptr) a.acc_prev += z * a.b_acc;
+        if (a.q_out != nullptr) a.q_out += z * a.b_q;
+        if (a.b_scale) {
+            if (a.scale_prev != nullptr) a.scale_prev += z;
+            a.scale_out += z;
+        }
+    }
     for (int i = tid; i < a.zero_a_n; i += kRowThreads) a.zero_a[i] = 0;
     for (int i = tid; i < a.zero_b_n; i += kRowThreads) a.zero_b[i] = 0;
     float post = 0.0f;
@@ -233,13 +248,20 @@ struct RopeKvArgs {
     __half* k_cache;          // [ctx][kv_dim] of this layer
     __half* v_cache;
     int block_scaled;         // acc holds the F32 results of block-scaled projections: used as they are
+    int b_acc, b_q, b_scale;  // batch of tokens: token blockIdx.z at position pos[0] + z reads acc + z * b_acc and act_scale + z, writes q_out + z * b_q
 };
 
 __global__ void rope_kv_kernel(RopeKvArgs a) {
+    if (blockIdx.z != 0) {
+        const size_t z = blockIdx.z;
+        a.acc += z * a.b_acc;
+        a.q_out += z * a.b_q;
+        if (a.b_scale) a.act_scale += z;
+    }
     const float s = a.block_scaled ? 1.0f : a.act_scale[0];
     const bool live = s > 0.0f;
     const float pq = live ? __fdiv_rn(a.ws_q, s) : 0.0f, pk = live ? __fdiv_rn(a.ws_k, s) : 0.0f, pv = live ? __fdiv_rn(a.ws_v, s) : 0.0f;
-    const uint32_t pos = a.pos[0];
+    const uint32_t pos = a.pos[0] + blockIdx.z;
     const float* cs = a.cos_sin + static_cast<size_t>(pos) * a.rope_dims;
     const int half_pairs = a.rope_dims / 2;
     const int total_pairs = (a.q_dim + a.kv_dim) / 2;
@@ -308,6 +330,7 @@ struct AttnArgs {
     float scale;
     float* part_acc;          // [q_heads][4][head_dim] chunk accumulators (as F32; the F16 ones are widened exactly)
     float* part_ms;           // [q_heads][4][2]: M and S per chunk (S = 0 marks an empty chunk)
+    int b_q, b_acc, b_ms;     // batch of tokens: token blockIdx.z at position pos[0] + z uses q + z * b_q, part_acc + z * b_acc, part_ms + z * b_ms
 };
 
 constexpr int kAttnThreads = 256;
@@ -336,7 +359,13 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(AttnArgs a) {
     __shared__ float s_q[256];
     const int h = blockIdx.x, c = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int hd = a.head_dim, kvh = h / a.gqa;
-    const int seq_len = static_cast<int>(a.pos[0]) + 1;
+    if (blockIdx.z != 0) {
+        const size_t z = blockIdx.z;
+        a.q += z * a.b_q;
+        a.part_acc += z * a.b_acc;
+        a.part_ms += z * a.b_ms;
+    }
+    const int seq_len = static_cast<int>(a.pos[0] + blockIdx.z) + 1;
     int n_kv = (seq_len + 255) / 256 * 256;
     if (n_kv < 256) n_kv = 256;
     if (n_kv > a.ctx) n_kv = a.ctx;
@@ -451,6 +480,7 @@ struct AttnFinishArgs {
     int32_t* zero_a;          // result buffer of the o projection
     int zero_a_n;
     float* q8_d;              // block-scaled models: Q8_0 block scales of q_out (else nullptr: per-tensor int8)
+    int b_acc, b_ms, b_q, b_scale;  // batch of tokens: per-token strides of part_acc, part_ms, q_out; scale_out + z when b_scale is set
 };
 
 __global__ void __launch_bounds__(kRowThreads) attn_finish_kernel(AttnFinishArgs a) {
@@ -458,8 +488,15 @@ __global__ void __launch_bounds__(kRowThreads) attn_finish_kernel(AttnFinishArgs
     __shared__ float sh_f[32];
     extern __shared__ float y_s[];  // q_dim floats
     const int tid = threadIdx.x, hd = a.head_dim, n = a.q_heads * hd;
+    if (blockIdx.z != 0) {
+        const size_t z = blockIdx.z;
+        a.part_acc += z * a.b_acc;
+        a.part_ms += z * a.b_ms;
+        a.q_out += z * a.b_q;
+        if (a.b_scale) a.scale_out += z;
+    }
     for (int i = tid; i < a.zero_a_n; i += kRowThreads) a.zero_a[i] = 0;
-    const int seq_len = static_cast<int>(a.pos[0]) + 1;
+    const int seq_len = static_cast<int>(a.pos[0] + blockIdx.z) + 1;
     int n_kv = (seq_len + 255) / 256 * 256;
     if (n_kv < 256) n_kv = 256;
     if (n_kv > a.ctx) n_kv = a.ctx;
@@ -519,6 +556,7 @@ struct ActQuantArgs {
     int zero_a_n;
     int block_scaled;         // acc_gate / acc_up hold F32 results of block-scaled projections; codes are Q8_0 blocks
     float* q8_d;
+    int b_acc, b_q, b_scale;  // batch of tokens: per-token strides of acc_gate / acc_up and of q_out; act_scale + z and scale_out + z when b_scale is set
 };
 
 __global__ void __launch_bounds__(kRowThreads) act_quant_kernel(ActQuantArgs a) {
@@ -526,6 +564,16 @@ __global__ void __launch_bounds__(kRowThreads) act_quant_kernel(ActQuantArgs a) 
     __shared__ float sh_f[32];
     extern __shared__ float y_s[];  // n floats
     const int tid = threadIdx.x;
+    if (blockIdx.z != 0) {
+        const size_t z = blockIdx.z;
+        a.acc_gate += z * a.b_acc;
+        a.acc_up += z * a.b_acc;
+        a.q_out += z * a.b_q;
+        if (a.b_scale) {
+            a.act_scale += z;
+            a.scale_out += z;
+        }
+    }
     for (int i = tid; i < a.zero_a_n; i += kRowThreads) a.zero_a[i] = 0;
     const float s_in = a.block_scaled ? 1.0f : a.act_scale[0];
     const bool live = s_in > 0.0f;

@@ -61,6 +61,14 @@ struct quintrit_b200_decoder {
     unsigned int* tp_seq = nullptr;
     bool tp_attached = false;
     void* tp_peer[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};  // peer boxes opened through IPC
+    // prompt ingestion in chunks of up to kPrefillMax tokens (batched projections on the tensor cores): per-token rows of the step buffers, made on first use
+    struct Prefill {
+        uint32_t* tokens = nullptr;
+        uint32_t* pos = nullptr;
+        float *x = nullptr, *q = nullptr, *part_acc = nullptr, *part_ms = nullptr, *s_h = nullptr, *s_q = nullptr, *s_i = nullptr;
+        int8_t *a8_h = nullptr, *a8_q = nullptr, *a8_i = nullptr;
+        int32_t *acc_qkv = nullptr, *acc_o = nullptr, *acc_gu = nullptr, *acc_down = nullptr;
+    } pf;
 };
 
 namespace qtb {

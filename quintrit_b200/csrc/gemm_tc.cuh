@@ -56,6 +56,7 @@ struct GemmArgs {
     int32_t* out;          // [batch][rows]; with K split over several items: the partial sums [part][batch][rows] that gemm_reduce_parts_kernel adds up
     unsigned int* status;  // set to kGemmStatusTimeout when a wait ran out
     int rows, rows_padded, blocks;
+    int ldo;               // elements between the results of consecutive vectors in `out` (rows, or more when the results go into a wider row)
     int n;                 // instruction N: the batch rounded up to a multiple of 16
     int batch;             // activation vectors actually present (columns of the accumulator that are written out)
     int blocks_per_cta;    // blocks of one work item (a row tile x a K part)
@@ -99,11 +100,12 @@ __global__ void stream_to_two_bit_kernel(const uint4* __restrict__ stream, uint8
 }
 
 // out[i] = sum over the K parts of partial[part][i] (i over batch * rows): the second step of a projection whose K was split over several items
-__global__ void gemm_reduce_parts_kernel(const int32_t* __restrict__ partial, int32_t* __restrict__ out, size_t count, int parts) {
+// (partial rows are dense, `rows` apart; the results of a vector are `ldo` apart in out)
+__global__ void gemm_reduce_parts_kernel(const int32_t* __restrict__ partial, int32_t* __restrict__ out, size_t count, int parts, int rows, int ldo) {
     for (size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x; i < count; i += size_t(gridDim.x) * blockDim.x) {
         int32_t sum = 0;
         for (int p = 0; p < parts; ++p) sum += partial[size_t(p) * count + i];
-        out[i] = sum;
+        out[(i / rows) * ldo + i % rows] = sum;
     }
 }
 
@@ -385,12 +387,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_i8_tcgen05_kernel(const 
                     : "r"(taddr));
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                 if (row < a.rows) {
-                    int32_t* dst = a.out + (size_t(item % parts) * a.batch + c0) * a.rows + row;
+                    int32_t* dst = a.out + (size_t(item % parts) * a.batch + c0) * a.ldo + row;
                     const int valid = min(16, a.batch - c0);
 #pragma unroll
                     for (int i = 0; i < 16; ++i) {
                         if (i < valid) *dst = static_cast<int32_t>(v[i]);
-                        dst += a.rows;
+                        dst += a.ldo;
                     }
                 }
             }

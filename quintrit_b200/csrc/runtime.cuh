@@ -206,6 +206,17 @@ int rt_forward(quintrit_session* s, uint32_t token, uint32_t pos, bool want_logi
 int rt_feed(quintrit_session* s, const uint32_t* ids, size_t n, uint32_t pos0, bool want_logits, uint32_t* greedy) {
     quintrit_b200_decoder* d = s->dec;
     DeviceGuard g(d->device);
+    if (n >= 8 && prefill_available(d) && std::getenv("QUINTRIT_B200_NO_PREFILL") == nullptr) {
+        // a prompt goes in chunks of up to 256 tokens with the projections on the tensor cores; the result is that of n single steps
+        int rc = decoder_prefill(d, ids, n, pos0);
+        if (rc != QUINTRIT_OK) return rc;
+        if (want_logits) QTB_CUDA(cudaMemcpyAsync(s->logits.data(), d->logits, size_t(d->vocab) * sizeof(float), cudaMemcpyDeviceToHost, d->stream));
+        if (greedy) QTB_CUDA(cudaMemcpyAsync(greedy, d->d_token, sizeof(uint32_t), cudaMemcpyDeviceToHost, d->stream));
+        if ((rc = decoder_check_status(d)) != QUINTRIT_OK) return rc;
+        d->host_pos = pos0 + static_cast<uint32_t>(n);
+        s->logits_valid = want_logits;
+        return QUINTRIT_OK;
+    }
     for (size_t i = 0; i + 1 < n; ++i) {
         int rc;
         if ((rc = decoder_set(d, ids[i], pos0 + static_cast<uint32_t>(i))) != QUINTRIT_OK || (rc = decoder_step(d)) != QUINTRIT_OK) return rc;
