@@ -234,8 +234,21 @@ def run_decode(args, local_rank: int):
         parity = {"greedy_tokens_checked": ngen, "identical": bool(list(got) == want), "logits_bit_exact": bool(np.array_equal(lg_ref.view(np.uint32), lg_gpu.view(np.uint32))),
                   "cpu_tokens_per_s": round(cpu_tok_s, 2), "cpu_threads": os.cpu_count()}
         del ref
-    # ingest the prompt, then time
+    # ingest the prompt: token by token on the device (the reference's way), and in chunks on the tensor cores; both must end in the same token
+    t0 = time.perf_counter()
     first = dec.generate(prompt, 1)
+    serial_s = time.perf_counter() - t0
+    ingest = None
+    try:
+        dec.prefill(prompt[:16])  # makes the two-bit copies of the weights and the chunk buffers
+        t0 = time.perf_counter()
+        _, nxt = dec.prefill(prompt)
+        chunk_s = time.perf_counter() - t0
+        ingest = {"prompt_tokens": int(len(prompt)), "token_by_token_tokens_per_s": round(len(prompt) / serial_s, 1), "chunked_tokens_per_s": round(len(prompt) / chunk_s, 1),
+                  "chunked_ms": round(chunk_s * 1e3, 2), "chunk": 256, "same_next_token": bool(int(nxt) == int(first[0])),
+                  "kernel": "gemm_i8_tcgen05_kernel for the projections, the step kernels with a token index in the grid"}
+    except q.QuintritError as e:
+        ingest = {"error": str(e)}
     q.launch_count(reset=True)
     dec.time_token(1, max(3, args.warmup))
     launches_per_token = q.launch_count() / max(3, args.warmup)
@@ -255,7 +268,7 @@ def run_decode(args, local_rank: int):
         "roofline_nominal_8tbs_frac": round(bytes_tok / (step_ms * 1e-3) / 8e12, 4),
         "hbm_frac_of_measured": round(bytes_tok / (step_ms * 1e-3) / 1e9 / measured_peaks()[0], 4),
         "e2e": {"tokens_per_s": round(1e3 / e2e_ms, 1), "ms_per_token": round(e2e_ms, 4), "h2d_bytes_per_step": 8, "d2h_bytes_per_step": 8},
-        "kernel_launches_per_token": round(launches_per_token, 1), "setup_s": round(setup_s, 1), "parity_vs_cpu": parity,
+        "kernel_launches_per_token": round(launches_per_token, 1), "setup_s": round(setup_s, 1), "parity_vs_cpu": parity, "prompt_ingestion": ingest,
     }
     dec.free()
     return out
