@@ -18,12 +18,20 @@ _lib = None
 
 def build(force: bool = False) -> str:
     """Compiles the oracle with ``make`` (gcc, a few seconds) and returns the path of the shared object."""
-    if force or not os.path.exists(_LIB_PATH) or any(
-        os.path.getmtime(os.path.join(_HERE, f)) > os.path.getmtime(_LIB_PATH)
-        for f in os.listdir(_HERE)
-        if f.endswith((".c", ".h"))
-    ):
-        subprocess.run(["make", "-C", _HERE] + (["-B"] if force else []), check=True, capture_output=True)
+    def stale() -> bool:
+        return not os.path.exists(_LIB_PATH) or any(
+            os.path.getmtime(os.path.join(_HERE, f)) > os.path.getmtime(_LIB_PATH) for f in os.listdir(_HERE) if f.endswith((".c", ".h")))
+
+    if force or stale():
+        import fcntl
+
+        with open(os.path.join(_HERE, ".build.lock"), "w") as lock:  # several ranks may get here at once: one of them runs make
+            fcntl.flock(lock, fcntl.LOCK_EX)
+            try:
+                if force or stale():
+                    subprocess.run(["make", "-C", _HERE] + (["-B"] if force else []), check=True, capture_output=True)
+            finally:
+                fcntl.flock(lock, fcntl.LOCK_UN)
     return _LIB_PATH
 
 
