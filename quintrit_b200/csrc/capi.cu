@@ -2084,10 +2084,9 @@ int prefill_buffers(quintrit_b200_decoder* d) {
 // One chunk of n <= kPrefillMax tokens (already in d->pf.tokens) at positions pos0 .. pos0 + n - 1: the launch sequence of enqueue_token with a token
 // index in gridDim.z, the projections as batched products (every token keeps its own activation scale; the integers are those of the batch-1
 // kernel). With `with_head` the last token's logits and greedy choice land in d->logits / d->d_token as after a single step.
-int enqueue_prefill_chunk(quintrit_b200_decoder* d, int n, uint32_t pos0, bool with_head) {
+int prefill_layers(quintrit_b200_decoder* d, int n) {
     cudaStream_t s = d->stream;
     const int H = d->hidden, I = d->inter, qd = d->q_dim, kvd = d->kv_dim, hd = d->head_dim, qkv = qd + 2 * kvd;
-    QTB_CUDA(cudaMemcpyAsync(d->pf.pos, &pos0, sizeof pos0, cudaMemcpyHostToDevice, s));
     embed_kernel<<<dim3((H + 255) / 256, n), 256, 0, s>>>(d->embed, d->pf.tokens, H, d->pf.x, d->bf16_tables);
     QTB_LAUNCH_CHECK();
     auto mat = [&](int l, int k) { return const_cast<quintrit_b200_matrix*>(d->mats[size_t(l) * 7 + k]); };
@@ -2147,6 +2146,37 @@ int enqueue_prefill_chunk(quintrit_b200_decoder* d, int n, uint32_t pos0, bool w
         act_quant_kernel<<<dim3(1, 1, n), kRowThreads, I * sizeof(float), s>>>(aq);
         QTB_LAUNCH_CHECK();
         if ((rc = gemm_launch(mat(l, 6), d->pf.a8_i, n, d->pf.acc_down, s)) != QUINTRIT_OK) return rc;
+    }
+    return QUINTRIT_OK;
+}
+
+int enqueue_prefill_chunk(quintrit_b200_decoder* d, int n, uint32_t pos0, bool with_head) {
+    cudaStream_t s = d->stream;
+    const int H = d->hidden;
+    QTB_CUDA(cudaMemcpyAsync(d->pf.pos, &pos0, sizeof pos0, cudaMemcpyHostToDevice, s));
+    int rc;
+    // A full chunk is about 1200 launches; from the third full chunk on they are replayed as one CUDA graph (the first runs as it is and makes
+    // every lazy allocation, the second is captured). The position and the tokens are read from device memory, so one graph serves every chunk.
+    if (n == kPrefillMax && d->pf.graph_ready) {
+        QTB_CUDA(cudaGraphLaunch(d->pf.graph, s));
+    } else if (n == kPrefillMax && d->pf.warm && std::getenv("QUINTRIT_B200_PREFILL_GRAPH_OFF") == nullptr) {
+        cudaGraph_t g = nullptr;
+        QTB_CUDA(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
+        rc = prefill_layers(d, n);
+        const cudaError_t e = cudaStreamEndCapture(s, &g);
+        if (rc != QUINTRIT_OK) {
+            if (g) cudaGraphDestroy(g);
+            return rc;
+        }
+        if (e != cudaSuccess) return cuda_fail(e, "cudaStreamEndCapture(prompt chunk)");
+        const cudaError_t ei = cudaGraphInstantiate(&d->pf.graph, g, 0);
+        cudaGraphDestroy(g);
+        if (ei != cudaSuccess) return cuda_fail(ei, "cudaGraphInstantiate(prompt chunk)");
+        d->pf.graph_ready = true;
+        QTB_CUDA(cudaGraphLaunch(d->pf.graph, s));
+    } else {
+        if ((rc = prefill_layers(d, n)) != QUINTRIT_OK) return rc;
+        if (n == kPrefillMax) d->pf.warm = true;
     }
     if (with_head) {  // the last token of the chunk: final norm, output head, greedy choice, as a single step ends
         const size_t last = static_cast<size_t>(n - 1);

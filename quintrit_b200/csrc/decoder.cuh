@@ -68,6 +68,8 @@ struct quintrit_b200_decoder {
         float *x = nullptr, *q = nullptr, *part_acc = nullptr, *part_ms = nullptr, *s_h = nullptr, *s_q = nullptr, *s_i = nullptr;
         int8_t *a8_h = nullptr, *a8_q = nullptr, *a8_i = nullptr;
         int32_t *acc_qkv = nullptr, *acc_o = nullptr, *acc_gu = nullptr, *acc_down = nullptr;
+        bool warm = false, graph_ready = false;  // a full chunk ran once (lazy allocations done); the graph of a full chunk exists
+        cudaGraphExec_t graph = nullptr;
     } pf;
 };
 
@@ -107,6 +109,7 @@ inline void destroy_decoder(quintrit_b200_decoder* d) {
     for (void* q : d->tp_peer)
         if (q != nullptr) cudaIpcCloseMemHandle(q);
     if (d->graph_ready) cudaGraphExecDestroy(d->graph_step);
+    if (d->pf.graph_ready) cudaGraphExecDestroy(d->pf.graph);
     if (d->stream) cudaStreamDestroy(d->stream);
     for (void* p : d->allocs) cudaFree(p);
     if (prev >= 0) cudaSetDevice(prev);

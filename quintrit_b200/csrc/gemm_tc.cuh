@@ -17,9 +17,9 @@
 //     writes the row's 128 int8 operands into its lane of TENSOR MEMORY with tcgen05.st (32 columns a group). Operands that threads
 //     store to shared memory need a proxy fence before the tensor cores may read them, and that fence was measured at more than a
 //     thousand cycles a block; operands in tensor memory need none;
-//   * one thread of warp 0 fetches, per block, the tile's 4096 weight bytes (one bulk copy) and the matching four 32-byte-wide slices of
-//     the activation matrix (one 3-D TMA box, 32-byte swizzle, in place from the caller's vectors where their pitch allows it), both
-//     completing on one mbarrier;
+//   * two loader threads (warp 0 and the last warp) fetch, per block, the tile's 4096 weight bytes (one bulk copy) and the matching four
+//     32-byte-wide slices of the activation matrix (one 3-D TMA box, 32-byte swizzle, in place from the caller's vectors where their
+//     pitch allows it), both completing on one mbarrier;
 //   * one thread of warp 1 issues four MMAs (128 x N x 32, A from tensor memory, B from shared memory) per block and releases the stage
 //     and the group's operand columns with tcgen05.commit; a ring of 3 to 8 stages (as many as fit beside the batch) keeps the loads ahead;
 //   * the kernel is persistent: a CTA takes items round-robin;
@@ -44,7 +44,7 @@ namespace qtb {
 constexpr int kGemmM = 128;
 constexpr int kGemmDecodeWarps = 16;
 constexpr int kGemmGroups = 4;  // the decode warps work in groups of four; group g decodes the blocks it, it + 4, ... of the CTA's sequence on its own
-constexpr int kGemmThreads = 64 + 32 * kGemmDecodeWarps;
+constexpr int kGemmThreads = 64 + 32 * kGemmDecodeWarps + 32;  // weight loader warp, MMA warp, decode warps, activation loader warp
 constexpr int kGemmMaxStages = 8;
 constexpr int kGemmMaxN = 256;  // 256 accumulator columns + 4 x 32 operand columns fit the 512 columns of tensor memory
 constexpr int kGemmBlockCols = 128;           // columns (K) of one block of the two-bit copy: 32 bytes a row
@@ -237,7 +237,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_i8_tcgen05_kernel(const 
     }
     if (tid == 0) {
         for (int s = 0; s < S; ++s) {
-            mbar_init(loaded(s), 1);  // the loader's expect_tx arrival
+            mbar_init(loaded(s), 2);  // the expect_tx arrivals of the two loader threads
             mbar_init(empty(s), 1);   // tcgen05.commit
         }
         for (int g = 0; g < kGemmGroups; ++g) {
@@ -258,22 +258,31 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_i8_tcgen05_kernel(const 
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
 
-    if (warp == 0) {
-        // ---- loads: the weight bytes of the block (one bulk copy) and its activations (one TMA box: 32 bytes x n vectors x four K tiles) ----
+    if (warp == 0 || warp == 2 + kGemmDecodeWarps) {
+        // ---- loads, by two threads so that neither's fixed cost per block bounds the pipe: warp 0 fetches the weight bytes of a block (one bulk
+        // copy of the tile's 4096 bytes), the last warp its activations (one TMA box: 32 bytes x n vectors x four K tiles) ----
         if (lane == 0) {
+            const bool weights = warp == 0;
             int it = 0, s = 0;
             uint32_t ph = 0;  // stage and phase of the ring, advanced by hand (S is a run-time value)
             bool okay = true;
             const uint32_t b_base = smem_u32(b_tiles), raw_base = smem_u32(raw_tiles);
             for (int item = blockIdx.x; item < items && okay; item += gridDim.x) {
                 const int row0 = (item / parts) * kGemmM, kb0 = (item % parts) * per, nkb = min(per, a.blocks - kb0);
+                const uint8_t* src = a.w + (size_t(kb0) * a.rows_padded + row0) * 32;
+                const size_t pitch = size_t(a.rows_padded) * 32;
                 for (int k = 0; k < nkb; ++k, ++it) {
                     QTB_GEMM_STAMP(0, 0, it);
                     if (!(okay = mbar_wait(empty(s), ph ^ 1, abort_flag, a.spin_limit))) break;
                     QTB_GEMM_STAMP(0, 1, it);
-                    mbar_expect_tx(loaded(s), 4u * n * 32u + kGemmM * 32u);
-                    bulk_load(raw_base + s * (kGemmM * 32), a.w + (size_t(kb0 + k) * a.rows_padded + row0) * 32, kGemmM * 32, loaded(s));  // the tile's 4096 weight bytes of this block
-                    tma_load_3d(b_base + s * n * kGemmBlockCols, &act_map, 0, 0, (kb0 + k) * 4, loaded(s));  // four K tiles of 32 bytes x n vectors in one box
+                    if (weights) {
+                        mbar_expect_tx(loaded(s), kGemmM * 32u);
+                        bulk_load(raw_base + s * (kGemmM * 32), src, kGemmM * 32, loaded(s));
+                        src += pitch;
+                    } else {
+                        mbar_expect_tx(loaded(s), 4u * n * 32u);
+                        tma_load_3d(b_base + s * n * kGemmBlockCols, &act_map, 0, 0, (kb0 + k) * 4, loaded(s));
+                    }
                     QTB_GEMM_STAMP(0, 2, it);
                     if (++s == S) s = 0, ph ^= 1;
                 }
@@ -301,7 +310,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_i8_tcgen05_kernel(const 
                 for (int k = 0; k < nkb; ++k, ++it) {
                     const int g = it & (kGemmGroups - 1);
                     QTB_GEMM_STAMP(1, 0, k + 100 * j);
-                    if (!(okay = mbar_wait(a_full(g), (it / kGemmGroups) & 1, abort_flag, a.spin_limit) && mbar_wait(loaded(s), ph, abort_flag, a.spin_limit))) break;
+                    // the group's arrival also stands for the stage's loads: the group waited for them before it decoded
+                    if (!(okay = mbar_wait(a_full(g), (it / kGemmGroups) & 1, abort_flag, a.spin_limit))) break;
                     QTB_GEMM_STAMP(1, 1, k + 100 * j);
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint64_t b_desc = b_desc0 + uint64_t(s * b_stage16);

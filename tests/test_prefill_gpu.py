@@ -68,3 +68,19 @@ def test_arguments():
     with pytest.raises(q.QuintritError) as e:
         d.prefill([])
     assert e.value.code == 2
+
+
+def test_many_chunks_replay_one_graph():
+    """From the third full chunk on the launches of a chunk are replayed as a CUDA graph: 800 tokens = 3 full chunks + a tail."""
+    spec = _spec(q.ARCH_LLAMA, False, 79, ctx=1024)
+    tokens = synth.prompt_tokens(6, 800, spec["vocab"])
+    a, b = q.Decoder(spec), q.Decoder(spec)
+    for pos, t in enumerate(tokens):
+        want, want_next = a.forward(int(t), pos)
+    got, got_next = b.prefill(tokens)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32)) and got_next == want_next
+    again, _ = b.prefill(tokens)  # a second prompt on the same decoder: every full chunk is a replay now
+    assert np.array_equal(again.view(np.uint32), want.view(np.uint32))
+    la, ta = a.forward(want_next, 800)
+    lb, tb = b.forward(got_next, 800)
+    assert np.array_equal(la.view(np.uint32), lb.view(np.uint32)) and ta == tb
