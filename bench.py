@@ -749,12 +749,28 @@ def main():
     ap.add_argument("--decode-shape", default="falcon3_10b", choices=["falcon3_10b", "bitnet_2b"])
     ap.add_argument("--decode-layers", type=int, default=None, help="fewer layers than the shape has (experiments)")
     ap.add_argument("--prompt", type=int, default=1024, help="context length at which a decode step is timed")
+    ap.add_argument("--parity-full", action="store_true", help="decode the committed full-size fixtures (40 / 30 layers, 1024 + 512 / 512 + 256 tokens) from synthetic GGUF files in every encoding and compare with the CPU oracle's tokens and logits")
     ap.add_argument("--parity-prompt", type=int, default=6, help="prompt tokens of the greedy-token parity check against the CPU oracle")
     ap.add_argument("--parity-new", type=int, default=6, help="greedy tokens compared in that check")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.parity_full:
+        import tempfile
+
+        from tests.test_full_parity_gpu import CASES, check_against_fixture  # the same check the GPU test suite runs
+
+        out = []
+        with tempfile.TemporaryDirectory() as tmp:
+            for model, variant, tables, encoding in CASES:
+                if model == args.decode_shape or args.decode_shape == "falcon3_10b" and model == "bitnet_2b":  # the default runs every committed case
+                    t0 = time.time()
+                    r = check_against_fixture(model, variant, tables, encoding, tmp, device=local_rank)
+                    r["seconds"] = round(time.time() - t0, 1)
+                    out.append(r)
+        print(json.dumps({"parity_full": out}), flush=True)
+        return
     if args.block_scaled_only:
         print(json.dumps({"block_scaled": run_block_scaled(args, local_rank)}), flush=True)
         return
