@@ -203,6 +203,8 @@ def run_decode(args, local_rank: int):
 
     dev = torch.device("cuda", local_rank)
     ctx = (max(args.prompt + args.steps + 64, args.parity_prompt + args.parity_new + 1) + 255) // 256 * 256
+    if args.batch_seqs > 0:  # the sequences of the batched leg: prompts of 256 .. 2048 tokens and the generated tokens behind them
+        ctx = max(ctx, (2048 + args.batch_steps + 8 + 255) // 256 * 256)
     t0 = time.time()
     spec = synth.torch_model(args.decode_shape, dev, ctx, layers=args.decode_layers)
     torch.cuda.empty_cache()
@@ -273,8 +275,52 @@ def run_decode(args, local_rank: int):
         "e2e": {"tokens_per_s": round(1e3 / e2e_ms, 1), "ms_per_token": round(e2e_ms, 4), "h2d_bytes_per_step": 8, "d2h_bytes_per_step": 8},
         "kernel_launches_per_token": round(launches_per_token, 1), "setup_s": round(setup_s, 1), "parity_vs_cpu": parity, "prompt_ingestion": ingest,
     }
+    if args.batch_seqs > 0:
+        try:
+            out["batched_decode"] = run_batched_decode(args, dec, spec, step_ms)
+        except q.QuintritError as e:
+            out["batched_decode"] = {"error": str(e)}
     dec.free()
     return out
+
+
+def run_batched_decode(args, dec, spec, single_ms: float):
+    """Several sequences with prompts of different lengths decoded together (one batched pass over the weights per step): aggregate tokens/s of
+    the greedy steps, wall clock around the C call with the chosen tokens read back every step, and a check of two sequences against the
+    same sequences decoded alone."""
+    import quintrit_b200 as q
+
+    n_seq, steps = args.batch_seqs, args.batch_steps
+    lengths = synth.batch_lengths(3, n_seq)
+    prompts = [synth.prompt_tokens(100 + i, int(n), spec["vocab"]) for i, n in enumerate(lengths)]
+    batch = q.Batch(dec, n_seq)
+    t0 = time.perf_counter()
+    first = [batch.prefill(i, p)[1] for i, p in enumerate(prompts)]
+    ingest_s = time.perf_counter() - t0
+    check = sorted(range(n_seq), key=lambda i: lengths[i])[:2]  # the two shortest: decoded alone afterwards, token by token
+    for _ in range(3):
+        batch.step()
+    got = {i: [] for i in check}
+    t0 = time.perf_counter()
+    for k in range(steps):
+        toks, _ = batch.step()
+        for i in check:
+            got[i].append(int(toks[i]))
+    step_s = (time.perf_counter() - t0) / steps
+    batch.free()
+    same = True
+    for i in check:
+        _, tok = dec.prefill(prompts[i])
+        same = same and int(tok) == int(first[i])
+        alone = []
+        for k in range(3 + steps):
+            _, tok = dec.forward(int(tok), int(lengths[i]) + k, want_logits=False)
+            alone.append(int(tok))
+        same = same and alone[3:] == got[i]
+    return {"sequences": n_seq, "prompt_lengths": "uniform in [256, 2048] (stream 4)", "prompt_tokens_total": int(lengths.sum()), "mean_context": round(float(lengths.mean()), 1),
+            "steps": steps, "ms_per_step": round(step_s * 1e3, 3), "tokens_per_s": round(n_seq / step_s, 1), "speedup_vs_one_sequence": round(n_seq / step_s / (1e3 / single_ms), 2),
+            "prompt_ingestion_tokens_per_s": round(float(lengths.sum()) / ingest_s, 1), "sequences_checked_against_decoding_alone": len(check), "identical_tokens": bool(same),
+            "timing": "wall clock around quintrit_b200_batch_step, the chosen tokens copied to the host every step"}
 
 
 def measured_peaks():
@@ -748,6 +794,8 @@ def main():
     ap.add_argument("--block-scaled-only", action="store_true", help="run only the block-scaled (Q2_0) projection on the model's shapes (profiling aid)")
     ap.add_argument("--decode-shape", default="falcon3_10b", choices=["falcon3_10b", "bitnet_2b"])
     ap.add_argument("--decode-layers", type=int, default=None, help="fewer layers than the shape has (experiments)")
+    ap.add_argument("--batch-seqs", type=int, default=32, help="sequences of the batched-decode leg (0 skips it)")
+    ap.add_argument("--batch-steps", type=int, default=16, help="greedy steps timed in the batched-decode leg")
     ap.add_argument("--prompt", type=int, default=1024, help="context length at which a decode step is timed")
     ap.add_argument("--parity-full", action="store_true", help="decode the committed full-size fixtures (40 / 30 layers, 1024 + 512 / 512 + 256 tokens) from synthetic GGUF files in every encoding and compare with the CPU oracle's tokens and logits")
     ap.add_argument("--parity-prompt", type=int, default=6, help="prompt tokens of the greedy-token parity check against the CPU oracle")

@@ -355,6 +355,35 @@ int quintrit_b200_selftest_barrier(uint32_t device_index, uint32_t ctas, uint32_
 int quintrit_b200_decoder_prefill(quintrit_b200_decoder_t* decoder, const uint32_t* tokens, size_t count, uint32_t pos, float* logits, size_t logits_capacity,
                                   uint32_t* out_token);
 
+/* ---- several sequences decoded together (batched decode) ---------------------------------------------------------------
+ * The reference decodes one sequence per session, one token per step (quintrit-runtime/src/engine.rs:282, 626-631); nothing in
+ * it batches sequences. Here up to 256 independent sequences share one pass over the weights per step: the projections of a
+ * step are batched products on the tensor cores (quintrit_b200_gemm_i32: every token keeps its own activation scale, the
+ * integers are those of the batch-1 kernel), attention runs per sequence over that sequence's own KV cache at its own
+ * position, the output head reads every vocabulary row once for all tokens. Every sequence's logits and greedy tokens are
+ * bit for bit those of the same sequence decoded alone with quintrit_b200_decoder_forward.
+ *
+ * A batch belongs to a decoder (per-tensor ternary model on one GPU; else QUINTRIT_ERR_UNSUPPORTED): it holds one KV cache of
+ * the decoder's context length per sequence and uses the decoder's weights, stream and per-token buffers, so the decoder
+ * and its batches are used by one thread at a time, and a batch is freed before its decoder. */
+typedef struct quintrit_b200_batch quintrit_b200_batch_t;
+
+int quintrit_b200_batch_create(quintrit_b200_decoder_t* decoder, uint32_t sequences, quintrit_b200_batch_t** out_batch);
+void quintrit_b200_batch_free(quintrit_b200_batch_t* batch);
+/* Number of sequences, context length, tokens cached per sequence (any pointer may be NULL). */
+int quintrit_b200_batch_info(const quintrit_b200_batch_t* batch, uint32_t* out_sequences, uint32_t* out_context, uint32_t* out_positions, size_t positions_capacity);
+/* Drops the cached tokens of one sequence from `position` on (0 = start a new sequence in that slot). */
+int quintrit_b200_batch_rewind(quintrit_b200_batch_t* batch, uint32_t sequence, uint32_t position);
+/* Appends `count` prompt tokens to one sequence, in chunks on the tensor cores as quintrit_b200_decoder_prefill does; the last
+ * token's logits and greedy choice are returned (both may be NULL) and the choice is kept as the sequence's next input. */
+int quintrit_b200_batch_prefill(quintrit_b200_batch_t* batch, uint32_t sequence, const uint32_t* tokens, size_t count, float* logits, size_t logits_capacity,
+                                uint32_t* out_token);
+/* One step of `count` sequences: sequences[z] (distinct; NULL = all sequences in order) is fed tokens[z] (NULL = the token
+ * the sequence chose last) at its own position. out_tokens[z] receives the greedy choice, logits ([count][vocab], may be NULL)
+ * the logits; every listed sequence advances by one position. */
+int quintrit_b200_batch_step(quintrit_b200_batch_t* batch, const uint32_t* sequences, size_t count, const uint32_t* tokens, uint32_t* out_tokens, float* logits,
+                             size_t logits_capacity);
+
 /* ---- batched projection on the tensor cores: out[b][n] = sum_k trit[n][k] * act[b][k] for `batch` int8 activation vectors
  * ([batch][cols], row-major), the integers quintrit_b200_gemv_i32 gives vector by vector (so every vector may carry its own
  * activation scale, as the tokens of a prompt do: quintrit-runtime/src/layer.rs:123-177 per token). out is [batch][rows]. The

@@ -121,6 +121,14 @@ def load_library(build_if_missing: bool = True) -> C.CDLL:
     l.quintrit_b200_gguf_describe.argtypes = [C.c_char_p, C.c_char_p, _sz, C.POINTER(_sz)]
     l.quintrit_b200_decoder_forward.argtypes = [C.c_void_p, C.c_uint32, C.c_uint32, _f32p, _sz, C.POINTER(C.c_uint32)]
     l.quintrit_b200_decoder_prefill.argtypes = [C.c_void_p, C.POINTER(C.c_uint32), _sz, C.c_uint32, _f32p, _sz, C.POINTER(C.c_uint32)]
+    _u32p = C.POINTER(C.c_uint32)
+    l.quintrit_b200_batch_create.argtypes = [C.c_void_p, C.c_uint32, C.POINTER(C.c_void_p)]
+    l.quintrit_b200_batch_free.argtypes = [C.c_void_p]
+    l.quintrit_b200_batch_free.restype = None
+    l.quintrit_b200_batch_info.argtypes = [C.c_void_p, _u32p, _u32p, _u32p, _sz]
+    l.quintrit_b200_batch_rewind.argtypes = [C.c_void_p, C.c_uint32, C.c_uint32]
+    l.quintrit_b200_batch_prefill.argtypes = [C.c_void_p, C.c_uint32, _u32p, _sz, _f32p, _sz, _u32p]
+    l.quintrit_b200_batch_step.argtypes = [C.c_void_p, _u32p, _sz, _u32p, _u32p, _f32p, _sz]
     l.quintrit_b200_decoder_generate.argtypes = [C.c_void_p, C.POINTER(C.c_uint32), _sz, _sz, C.POINTER(C.c_uint32), _sz]
     l.quintrit_b200_decoder_time_token.argtypes = [C.c_void_p, C.c_uint32, C.c_uint32, C.POINTER(C.c_float)]
     l.quintrit_b200_decoder_trace_step.argtypes = [C.c_void_p, C.POINTER(C.c_uint64), _sz, C.POINTER(_sz)]
@@ -472,6 +480,59 @@ class Decoder:
             self._h = C.c_void_p()
         for m in self.matrices:
             m.free()
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+class Batch:
+    """Several sequences of one model decoded together (``quintrit_b200_batch_*``): every sequence has its own KV cache and
+    position; a step feeds one token per listed sequence through one batched pass over the weights. The decoder must
+    outlive the batch and is not used by another thread meanwhile."""
+
+    def __init__(self, decoder: "Decoder", sequences: int):
+        self._h = C.c_void_p()
+        self.decoder, self.sequences, self.vocab = decoder, sequences, decoder.vocab
+        _check(load_library().quintrit_b200_batch_create(decoder._h, sequences, C.byref(self._h)))
+
+    def positions(self) -> np.ndarray:
+        out = np.zeros(self.sequences, np.uint32)
+        _check(load_library().quintrit_b200_batch_info(self._h, None, None, out.ctypes.data_as(C.POINTER(C.c_uint32)), out.size))
+        return out
+
+    def rewind(self, sequence: int, position: int = 0) -> None:
+        _check(load_library().quintrit_b200_batch_rewind(self._h, sequence, position))
+
+    def prefill(self, sequence: int, tokens):
+        """Appends prompt tokens to one sequence; returns (logits of the last token, its greedy successor)."""
+        t = np.ascontiguousarray(tokens, dtype=np.uint32)
+        logits, nxt = np.zeros(self.vocab, np.float32), C.c_uint32(0)
+        _check(load_library().quintrit_b200_batch_prefill(self._h, sequence, t.ctypes.data_as(C.POINTER(C.c_uint32)), t.size, _p(logits, _f32p), logits.size,
+                                                          C.byref(nxt)))
+        return logits, nxt.value
+
+    def step(self, sequences=None, tokens=None, want_logits: bool = False):
+        """One token for every listed sequence (all by default), the given tokens or each sequence's last choice; returns
+        (greedy tokens, logits [count][vocab] or None)."""
+        u32p = C.POINTER(C.c_uint32)
+        sq = None if sequences is None else np.ascontiguousarray(sequences, dtype=np.uint32)
+        n = self.sequences if sq is None else sq.size
+        tk = None if tokens is None else np.ascontiguousarray(tokens, dtype=np.uint32)
+        if tk is not None and tk.size != n:
+            raise ValueError(f"{tk.size} tokens for {n} sequences")
+        out = np.zeros(n, np.uint32)
+        logits = np.zeros((n, self.vocab), np.float32) if want_logits else None
+        _check(load_library().quintrit_b200_batch_step(self._h, None if sq is None else sq.ctypes.data_as(u32p), n, None if tk is None else tk.ctypes.data_as(u32p),
+                                                       out.ctypes.data_as(u32p), None if logits is None else _p(logits, _f32p), 0 if logits is None else logits.size))
+        return out, logits
+
+    def free(self) -> None:
+        if self._h:
+            load_library().quintrit_b200_batch_free(self._h)
+            self._h = C.c_void_p()
 
     def __del__(self):
         try:

@@ -2084,7 +2084,21 @@ int prefill_buffers(quintrit_b200_decoder* d) {
 // One chunk of n <= kPrefillMax tokens (already in d->pf.tokens) at positions pos0 .. pos0 + n - 1: the launch sequence of enqueue_token with a token
 // index in gridDim.z, the projections as batched products (every token keeps its own activation scale; the integers are those of the batch-1
 // kernel). With `with_head` the last token's logits and greedy choice land in d->logits / d->d_token as after a single step.
-int prefill_layers(quintrit_b200_decoder* d, int n) {
+// Where the tokens of a batched pass sit: the KV cache they append to and read, their positions, and (for a step of several sequences) the
+// sequence of every token. The default is the decoder's own cache with consecutive positions from pf.pos[0] (a prompt chunk).
+struct BatchTarget {
+    __half *kc = nullptr, *vc = nullptr;  // [layers][ctx][kv_dim] of the first sequence
+    const uint32_t* pos = nullptr;
+    SeqIndex seq{nullptr, 0, 0};
+    bool own = true;                      // the decoder's own cache: a full chunk may be replayed as the captured graph
+};
+BatchTarget own_target(quintrit_b200_decoder* d) {
+    BatchTarget t;
+    t.kc = d->kc, t.vc = d->vc, t.pos = d->pf.pos;
+    return t;
+}
+
+int prefill_layers(quintrit_b200_decoder* d, int n, const BatchTarget& tg) {
     cudaStream_t s = d->stream;
     const int H = d->hidden, I = d->inter, qd = d->q_dim, kvd = d->kv_dim, hd = d->head_dim, qkv = qd + 2 * kvd;
     embed_kernel<<<dim3((H + 255) / 256, n), 256, 0, s>>>(d->embed, d->pf.tokens, H, d->pf.x, d->bf16_tables);
@@ -2106,23 +2120,23 @@ int prefill_layers(quintrit_b200_decoder* d, int n) {
         RopeKvArgs rk{};
         rk.acc = d->pf.acc_qkv, rk.b_acc = qkv, rk.act_scale = d->pf.s_h, rk.b_scale = 1;
         rk.ws_q = sc[0], rk.ws_k = sc[1], rk.ws_v = sc[2];
-        rk.cos_sin = d->cos_sin, rk.pos = d->pf.pos;
+        rk.cos_sin = d->cos_sin, rk.pos = tg.pos, rk.seq = tg.seq;
         rk.q_dim = qd, rk.kv_dim = kvd, rk.head_dim = hd, rk.rope_dims = d->rope_dims, rk.neox = d->arch == QUINTRIT_B200_ARCH_BITNET;
         rk.q_out = d->pf.q, rk.b_q = qd;
-        rk.k_cache = d->kc + static_cast<size_t>(l) * d->ctx * kvd;
-        rk.v_cache = d->vc + static_cast<size_t>(l) * d->ctx * kvd;
+        rk.k_cache = tg.kc + static_cast<size_t>(l) * d->ctx * kvd;
+        rk.v_cache = tg.vc + static_cast<size_t>(l) * d->ctx * kvd;
         rope_kv_kernel<<<dim3(((qd + kvd) / 2 + kvd + 255) / 256, 1, n), 256, 0, s>>>(rk);
         QTB_LAUNCH_CHECK();
         AttnArgs at{};
         at.q = d->pf.q, at.b_q = qd;
-        at.k_cache = rk.k_cache, at.v_cache = rk.v_cache, at.pos = d->pf.pos;
+        at.k_cache = rk.k_cache, at.v_cache = rk.v_cache, at.pos = tg.pos, at.seq = tg.seq;
         at.head_dim = hd, at.kv_dim = kvd, at.gqa = d->q_heads / d->kv_heads, at.ctx = d->ctx, at.f32_values = d->f32_values;
         at.scale = 1.0f / std::sqrt(static_cast<float>(hd));
         at.part_acc = d->pf.part_acc, at.b_acc = d->q_heads * 4 * hd, at.part_ms = d->pf.part_ms, at.b_ms = d->q_heads * 8;
         attention_kernel<<<dim3(d->q_heads, 4, n), kAttnThreads, 0, s>>>(at);
         QTB_LAUNCH_CHECK();
         AttnFinishArgs af{};
-        af.part_acc = d->pf.part_acc, af.b_acc = d->q_heads * 4 * hd, af.part_ms = d->pf.part_ms, af.b_ms = d->q_heads * 8, af.pos = d->pf.pos;
+        af.part_acc = d->pf.part_acc, af.b_acc = d->q_heads * 4 * hd, af.part_ms = d->pf.part_ms, af.b_ms = d->q_heads * 8, af.pos = tg.pos, af.seq = tg.seq;
         af.q_heads = d->q_heads, af.head_dim = hd, af.ctx = d->ctx;
         af.sub_norm_w = d->norms[l * 4 + 2], af.eps = d->eps;
         af.q_out = d->pf.a8_q, af.b_q = qd, af.scale_out = d->pf.s_q, af.b_scale = 1;
@@ -2150,19 +2164,19 @@ int prefill_layers(quintrit_b200_decoder* d, int n) {
     return QUINTRIT_OK;
 }
 
-int enqueue_prefill_chunk(quintrit_b200_decoder* d, int n, uint32_t pos0, bool with_head) {
+int enqueue_prefill_chunk(quintrit_b200_decoder* d, int n, uint32_t pos0, bool with_head, const BatchTarget& tg) {
     cudaStream_t s = d->stream;
     const int H = d->hidden;
     QTB_CUDA(cudaMemcpyAsync(d->pf.pos, &pos0, sizeof pos0, cudaMemcpyHostToDevice, s));
     int rc;
     // A full chunk is about 1200 launches; from the third full chunk on they are replayed as one CUDA graph (the first runs as it is and makes
     // every lazy allocation, the second is captured). The position and the tokens are read from device memory, so one graph serves every chunk.
-    if (n == kPrefillMax && d->pf.graph_ready) {
+    if (n == kPrefillMax && tg.own && d->pf.graph_ready) {
         QTB_CUDA(cudaGraphLaunch(d->pf.graph, s));
-    } else if (n == kPrefillMax && d->pf.warm && std::getenv("QUINTRIT_B200_PREFILL_GRAPH_OFF") == nullptr) {
+    } else if (n == kPrefillMax && tg.own && d->pf.warm && std::getenv("QUINTRIT_B200_PREFILL_GRAPH_OFF") == nullptr) {
         cudaGraph_t g = nullptr;
         QTB_CUDA(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
-        rc = prefill_layers(d, n);
+        rc = prefill_layers(d, n, tg);
         const cudaError_t e = cudaStreamEndCapture(s, &g);
         if (rc != QUINTRIT_OK) {
             if (g) cudaGraphDestroy(g);
@@ -2175,7 +2189,7 @@ int enqueue_prefill_chunk(quintrit_b200_decoder* d, int n, uint32_t pos0, bool w
         d->pf.graph_ready = true;
         QTB_CUDA(cudaGraphLaunch(d->pf.graph, s));
     } else {
-        if ((rc = prefill_layers(d, n)) != QUINTRIT_OK) return rc;
+        if ((rc = prefill_layers(d, n, tg)) != QUINTRIT_OK) return rc;
         if (n == kPrefillMax) d->pf.warm = true;
     }
     if (with_head) {  // the last token of the chunk: final norm, output head, greedy choice, as a single step ends
@@ -2199,19 +2213,22 @@ int enqueue_prefill_chunk(quintrit_b200_decoder* d, int n, uint32_t pos0, bool w
 bool prefill_available(const quintrit_b200_decoder* d) { return !d->block_scaled && d->tp_world == 1 && d->hidden % 32 == 0 && d->inter % 32 == 0 && d->q_dim % 32 == 0; }
 
 // Tokens at positions pos0 .. pos0 + count - 1, chunk by chunk; ends like a single step of the last token (logits, greedy token, position).
-int decoder_prefill(quintrit_b200_decoder* d, const uint32_t* tokens, size_t count, uint32_t pos0) {
+int decoder_prefill(quintrit_b200_decoder* d, const uint32_t* tokens, size_t count, uint32_t pos0, const BatchTarget* target = nullptr) {
     int rc = prefill_buffers(d);
     if (rc != QUINTRIT_OK) return rc;
     for (int k = 0; k < d->layers * 7; ++k)
         if ((rc = gemm_prepare(const_cast<quintrit_b200_matrix*>(d->mats[k]))) != QUINTRIT_OK) return rc;
+    const BatchTarget tg = target != nullptr ? *target : own_target(d);
     for (size_t c0 = 0; c0 < count; c0 += kPrefillMax) {
         const int n = static_cast<int>(std::min<size_t>(kPrefillMax, count - c0));
         QTB_CUDA(cudaMemcpyAsync(d->pf.tokens, tokens + c0, size_t(n) * sizeof(uint32_t), cudaMemcpyHostToDevice, d->stream));
-        QTB_CUDA(cudaMemcpyAsync(d->d_history + pos0 + c0, d->pf.tokens, size_t(n) * sizeof(uint32_t), cudaMemcpyDeviceToDevice, d->stream));
-        if ((rc = enqueue_prefill_chunk(d, n, pos0 + static_cast<uint32_t>(c0), c0 + n == count)) != QUINTRIT_OK) return rc;
+        if (tg.own) QTB_CUDA(cudaMemcpyAsync(d->d_history + pos0 + c0, d->pf.tokens, size_t(n) * sizeof(uint32_t), cudaMemcpyDeviceToDevice, d->stream));
+        if ((rc = enqueue_prefill_chunk(d, n, pos0 + static_cast<uint32_t>(c0), c0 + n == count, tg)) != QUINTRIT_OK) return rc;
     }
-    const uint32_t next = pos0 + static_cast<uint32_t>(count);  // the device-side position as after `count` single steps
-    QTB_CUDA(cudaMemcpyAsync(d->d_pos, &next, sizeof next, cudaMemcpyHostToDevice, d->stream));
+    if (tg.own) {
+        const uint32_t next = pos0 + static_cast<uint32_t>(count);  // the device-side position as after `count` single steps
+        QTB_CUDA(cudaMemcpyAsync(d->d_pos, &next, sizeof next, cudaMemcpyHostToDevice, d->stream));
+    }
     return QUINTRIT_OK;
 }
 
@@ -2240,6 +2257,245 @@ extern "C" int quintrit_b200_decoder_prefill(quintrit_b200_decoder_t* decoder, c
         for (int k = 0; k < d->layers * 7; k += 7)  // the batched projections report through their matrices' status words; one per layer is enough to see a time-out
             if ((rc = gemm_check_status(const_cast<quintrit_b200_matrix*>(d->mats[k]), d->stream)) != QUINTRIT_OK) return rc;
         d->host_pos = pos + static_cast<uint32_t>(count);
+        return ok();
+    });
+}
+
+// ---- several sequences decoded together: one pass of the batched projections per step ----------------------------------------------
+struct quintrit_b200_batch {
+    uint32_t magic;
+    quintrit_b200_decoder* d;              // weights, stream and the per-token buffers of the batched pass are the decoder's
+    int n_seq;
+    __half *kc = nullptr, *vc = nullptr;   // [n_seq][layers][ctx][kv_dim]
+    uint32_t *d_pos = nullptr, *d_last = nullptr, *d_slot = nullptr, *d_chosen = nullptr;
+    float* logits = nullptr;               // [n_seq][vocab] of the last step
+    __half* x16 = nullptr;                 // [n_seq][hidden]: the final norm's output
+    std::vector<uint32_t> host_pos;        // tokens cached per sequence
+    std::vector<uint32_t> staged;          // host copy of the ids given to an asynchronous copy
+    std::vector<void*> allocs;
+};
+
+namespace {
+
+constexpr uint32_t kMagicBatch = 0x51544242u;  // "QTBB"
+
+int check_batch(const quintrit_b200_batch* b) {
+    if (b == nullptr || b->magic != kMagicBatch) return fail(QUINTRIT_ERR_INVALID_HANDLE, "batch handle is NULL, freed or of the wrong type");
+    return check_decoder(b->d);
+}
+
+void destroy_batch(quintrit_b200_batch* b) {
+    if (b == nullptr) return;
+    int prev = -1;
+    cudaGetDevice(&prev);
+    cudaSetDevice(b->d->device);
+    for (void* p : b->allocs) cudaFree(p);
+    if (prev >= 0) cudaSetDevice(prev);
+    b->magic = 0;
+    delete b;
+}
+
+template <typename T>
+int batch_alloc(quintrit_b200_batch* b, T** p, size_t count) {
+    void* q = nullptr;
+    const size_t bytes = std::max<size_t>(count * sizeof(T), 16);
+    cudaError_t e = cudaMalloc(&q, bytes);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc(batch buffer)");
+    b->allocs.push_back(q);
+    if ((e = cudaMemset(q, 0, bytes)) != cudaSuccess) return cuda_fail(e, "cudaMemset(batch buffer)");
+    *p = static_cast<T*>(q);
+    return QUINTRIT_OK;
+}
+
+size_t batch_cache_stride(const quintrit_b200_decoder* d) { return static_cast<size_t>(d->layers) * d->ctx * d->kv_dim; }
+
+// The output head for the n tokens of a step: final norm per token, then every vocabulary row against all tokens, then the greedy choice per token.
+int batch_head(quintrit_b200_batch* b, int n) {
+    quintrit_b200_decoder* d = b->d;
+    cudaStream_t s = d->stream;
+    const int H = d->hidden;
+    NormQuantArgs nf{};
+    nf.x = d->pf.x, nf.b_x = H, nf.acc_prev = d->pf.acc_down, nf.b_acc = H, nf.scale_prev = d->pf.s_i, nf.b_scale = 1;
+    nf.ws_prev = d->scales[(d->layers - 1) * 7 + 6], nf.norm_w = d->out_norm, nf.eps = d->eps, nf.n = H;
+    nf.y16_out = b->x16, nf.b_y16 = H, nf.y16_bf16 = d->bf16_tables;
+    norm_quant_kernel<<<dim3(1, 1, n), kRowThreads, H * sizeof(float), s>>>(nf);
+    QTB_LAUNCH_CHECK();
+    if (H % 128 == 0 && lm_head_batch_smem(H) <= 200 * 1024) {
+        static std::mutex attr_lock;
+        static bool attr_set[64] = {};
+        {
+            std::lock_guard<std::mutex> hold(attr_lock);
+            if (!attr_set[d->device & 63]) {
+                QTB_CUDA(cudaFuncSetAttribute(lm_head_batch_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+                attr_set[d->device & 63] = true;
+            }
+        }
+        lm_head_batch_kernel<<<dim3(d->sm_count, (n + kHeadTokens - 1) / kHeadTokens), kHeadThreads, lm_head_batch_smem(H), s>>>(d->lm_head, b->x16, H, d->vocab, n, b->logits,
+                                                                                                                                  d->bf16_tables);
+        QTB_LAUNCH_CHECK();
+    } else {  // a hidden size the grouped kernel does not take: token by token
+        for (int t = 0; t < n; ++t) {
+            lm_head_kernel<<<d->sm_count * 8, 256, H * sizeof(float), s>>>(d->lm_head, b->x16 + size_t(t) * H, H, d->vocab, b->logits + size_t(t) * d->vocab, d->bf16_tables);
+            QTB_LAUNCH_CHECK();
+        }
+    }
+    argmax_kernel<<<n, 1024, 0, s>>>(b->logits, d->vocab, b->d_chosen);
+    QTB_LAUNCH_CHECK();
+    return QUINTRIT_OK;
+}
+
+int batch_gemm_status(quintrit_b200_decoder* d) {
+    int rc;
+    for (int k = 0; k < d->layers * 7; k += 7)
+        if ((rc = gemm_check_status(const_cast<quintrit_b200_matrix*>(d->mats[k]), d->stream)) != QUINTRIT_OK) return rc;
+    return QUINTRIT_OK;
+}
+
+}  // namespace
+
+extern "C" int quintrit_b200_batch_create(quintrit_b200_decoder_t* decoder, uint32_t sequences, quintrit_b200_batch_t** out_batch) {
+    return guard([&]() -> int {
+        if (out_batch == nullptr) return fail(QUINTRIT_ERR_NULL_POINTER, "out_batch is NULL");
+        *out_batch = nullptr;
+        int rc = check_decoder(decoder);
+        if (rc != QUINTRIT_OK) return rc;
+        quintrit_b200_decoder* d = decoder;
+        if (sequences == 0 || sequences > static_cast<uint32_t>(kPrefillMax)) return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "sequences must be in [1, %d], got %u", kPrefillMax, sequences);
+        if (!prefill_available(d)) return fail(QUINTRIT_ERR_UNSUPPORTED, "this decoder has no batched pass (block-scaled or tensor-parallel model)");
+        DeviceGuard g(d->device);
+        if ((rc = prefill_buffers(d)) != QUINTRIT_OK) return rc;
+        for (int k = 0; k < d->layers * 7; ++k)
+            if ((rc = gemm_prepare(const_cast<quintrit_b200_matrix*>(d->mats[k]))) != QUINTRIT_OK) return rc;
+        quintrit_b200_batch* b = new quintrit_b200_batch();
+        b->magic = kMagicBatch, b->d = d, b->n_seq = static_cast<int>(sequences);
+        b->host_pos.assign(sequences, 0);
+        const size_t n = sequences;
+        if ((rc = batch_alloc(b, &b->kc, n * batch_cache_stride(d))) != QUINTRIT_OK || (rc = batch_alloc(b, &b->vc, n * batch_cache_stride(d))) != QUINTRIT_OK ||
+            (rc = batch_alloc(b, &b->d_pos, n)) != QUINTRIT_OK || (rc = batch_alloc(b, &b->d_last, n)) != QUINTRIT_OK || (rc = batch_alloc(b, &b->d_slot, n)) != QUINTRIT_OK ||
+            (rc = batch_alloc(b, &b->d_chosen, n)) != QUINTRIT_OK || (rc = batch_alloc(b, &b->logits, n * d->vocab)) != QUINTRIT_OK ||
+            (rc = batch_alloc(b, &b->x16, n * d->hidden)) != QUINTRIT_OK) {
+            destroy_batch(b);
+            return rc;
+        }
+        *out_batch = b;
+        return ok();
+    });
+}
+
+extern "C" void quintrit_b200_batch_free(quintrit_b200_batch_t* batch) {
+    if (batch == nullptr || batch->magic != kMagicBatch) return;
+    destroy_batch(batch);
+}
+
+extern "C" int quintrit_b200_batch_info(const quintrit_b200_batch_t* batch, uint32_t* out_sequences, uint32_t* out_context, uint32_t* out_positions, size_t positions_capacity) {
+    return guard([&]() -> int {
+        int rc = check_batch(batch);
+        if (rc != QUINTRIT_OK) return rc;
+        if (out_sequences) *out_sequences = static_cast<uint32_t>(batch->n_seq);
+        if (out_context) *out_context = static_cast<uint32_t>(batch->d->ctx);
+        if (out_positions != nullptr) {
+            if (positions_capacity < static_cast<size_t>(batch->n_seq)) return fail(QUINTRIT_ERR_BUFFER_TOO_SMALL, "positions hold %zu values, the batch has %d sequences", positions_capacity, batch->n_seq);
+            std::copy(batch->host_pos.begin(), batch->host_pos.end(), out_positions);
+        }
+        return ok();
+    });
+}
+
+extern "C" int quintrit_b200_batch_rewind(quintrit_b200_batch_t* batch, uint32_t sequence, uint32_t position) {
+    return guard([&]() -> int {
+        int rc = check_batch(batch);
+        if (rc != QUINTRIT_OK) return rc;
+        if (sequence >= static_cast<uint32_t>(batch->n_seq)) return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "sequence %u of %d", sequence, batch->n_seq);
+        if (position > batch->host_pos[sequence]) return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "position %u skips positions: %u tokens are cached", position, batch->host_pos[sequence]);
+        DeviceGuard g(batch->d->device);
+        QTB_CUDA(cudaMemcpyAsync(batch->d_pos + sequence, &position, sizeof position, cudaMemcpyHostToDevice, batch->d->stream));
+        QTB_CUDA(cudaStreamSynchronize(batch->d->stream));
+        batch->host_pos[sequence] = position;
+        return ok();
+    });
+}
+
+extern "C" int quintrit_b200_batch_prefill(quintrit_b200_batch_t* batch, uint32_t sequence, const uint32_t* tokens, size_t count, float* logits, size_t logits_capacity,
+                                           uint32_t* out_token) {
+    return guard([&]() -> int {
+        int rc = check_batch(batch);
+        if (rc != QUINTRIT_OK) return rc;
+        quintrit_b200_batch* b = batch;
+        quintrit_b200_decoder* d = b->d;
+        if (tokens == nullptr) return fail(QUINTRIT_ERR_NULL_POINTER, "tokens is NULL");
+        if (count == 0) return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "no tokens to ingest");
+        if (sequence >= static_cast<uint32_t>(b->n_seq)) return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "sequence %u of %d", sequence, b->n_seq);
+        const uint32_t pos = b->host_pos[sequence];
+        if (size_t(pos) + count > static_cast<size_t>(d->ctx)) return fail(QUINTRIT_ERR_CONTEXT_OVERFLOW, "%zu tokens from position %u do not fit the context window of %d tokens", count, pos, d->ctx);
+        for (size_t i = 0; i < count; ++i)
+            if (tokens[i] >= static_cast<uint32_t>(d->vocab_full)) return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "token id %u is not below the vocabulary size %d", tokens[i], d->vocab_full);
+        if (logits != nullptr && logits_capacity < static_cast<size_t>(d->vocab)) return fail(QUINTRIT_ERR_BUFFER_TOO_SMALL, "logits hold %zu values, the vocabulary has %d", logits_capacity, d->vocab);
+        DeviceGuard g(d->device);
+        b->staged.assign(tokens, tokens + count);
+        BatchTarget tg;
+        tg.kc = b->kc + sequence * batch_cache_stride(d), tg.vc = b->vc + sequence * batch_cache_stride(d), tg.pos = d->pf.pos, tg.own = false;
+        if ((rc = decoder_prefill(d, b->staged.data(), count, pos, &tg)) != QUINTRIT_OK) return rc;
+        const uint32_t next = pos + static_cast<uint32_t>(count);
+        QTB_CUDA(cudaMemcpyAsync(b->d_pos + sequence, &next, sizeof next, cudaMemcpyHostToDevice, d->stream));
+        QTB_CUDA(cudaMemcpyAsync(b->d_last + sequence, d->d_token, sizeof(uint32_t), cudaMemcpyDeviceToDevice, d->stream));
+        if (logits) QTB_CUDA(cudaMemcpyAsync(logits, d->logits, size_t(d->vocab) * sizeof(float), cudaMemcpyDeviceToHost, d->stream));
+        if (out_token) QTB_CUDA(cudaMemcpyAsync(out_token, d->d_token, sizeof(uint32_t), cudaMemcpyDeviceToHost, d->stream));
+        if ((rc = decoder_check_status(d)) != QUINTRIT_OK) return rc;
+        if ((rc = batch_gemm_status(d)) != QUINTRIT_OK) return rc;
+        b->host_pos[sequence] = next;
+        return ok();
+    });
+}
+
+extern "C" int quintrit_b200_batch_step(quintrit_b200_batch_t* batch, const uint32_t* sequences, size_t count, const uint32_t* tokens, uint32_t* out_tokens, float* logits,
+                                        size_t logits_capacity) {
+    return guard([&]() -> int {
+        int rc = check_batch(batch);
+        if (rc != QUINTRIT_OK) return rc;
+        quintrit_b200_batch* b = batch;
+        quintrit_b200_decoder* d = b->d;
+        if (sequences == nullptr) count = static_cast<size_t>(b->n_seq);
+        if (count == 0 || count > static_cast<size_t>(b->n_seq)) return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "a step takes 1 to %d sequences, got %zu", b->n_seq, count);
+        const int n = static_cast<int>(count);
+        std::vector<char> seen(static_cast<size_t>(b->n_seq), 0);
+        for (int z = 0; z < n; ++z) {
+            const uint32_t sq = sequences != nullptr ? sequences[z] : static_cast<uint32_t>(z);
+            if (sq >= static_cast<uint32_t>(b->n_seq)) return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "sequence %u of %d", sq, b->n_seq);
+            if (seen[sq]) return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "sequence %u is listed twice", sq);
+            seen[sq] = 1;
+            if (b->host_pos[sq] >= static_cast<uint32_t>(d->ctx)) return fail(QUINTRIT_ERR_CONTEXT_OVERFLOW, "sequence %u has filled the context window of %d tokens", sq, d->ctx);
+            if (tokens == nullptr && b->host_pos[sq] == 0) return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "sequence %u has no previous token to continue from", sq);
+            if (tokens != nullptr && tokens[z] >= static_cast<uint32_t>(d->vocab_full)) return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "token id %u is not below the vocabulary size %d", tokens[z], d->vocab_full);
+        }
+        if (logits != nullptr && logits_capacity < count * static_cast<size_t>(d->vocab)) return fail(QUINTRIT_ERR_BUFFER_TOO_SMALL, "logits hold %zu values, %zu are needed", logits_capacity, count * static_cast<size_t>(d->vocab));
+        DeviceGuard g(d->device);
+        cudaStream_t s = d->stream;
+        b->staged.clear();  // the ids of both copies below, complete before the first copy is enqueued
+        if (sequences != nullptr) b->staged.insert(b->staged.end(), sequences, sequences + count);
+        if (tokens != nullptr) b->staged.insert(b->staged.end(), tokens, tokens + count);
+        const uint32_t* slot = nullptr;
+        if (sequences != nullptr) {
+            QTB_CUDA(cudaMemcpyAsync(b->d_slot, b->staged.data(), count * sizeof(uint32_t), cudaMemcpyHostToDevice, s));
+            slot = b->d_slot;
+        }
+        if (tokens != nullptr) {
+            QTB_CUDA(cudaMemcpyAsync(d->pf.tokens, b->staged.data() + (sequences != nullptr ? count : 0), count * sizeof(uint32_t), cudaMemcpyHostToDevice, s));
+        } else {
+            gather_tokens_kernel<<<(n + 255) / 256, 256, 0, s>>>(d->pf.tokens, b->d_last, slot, n);
+            QTB_LAUNCH_CHECK();
+        }
+        BatchTarget tg;
+        tg.kc = b->kc, tg.vc = b->vc, tg.pos = b->d_pos, tg.own = false;
+        tg.seq.slot = slot, tg.seq.pos_stride = 1, tg.seq.cache_stride = batch_cache_stride(d);
+        if ((rc = prefill_layers(d, n, tg)) != QUINTRIT_OK) return rc;
+        if ((rc = batch_head(b, n)) != QUINTRIT_OK) return rc;
+        advance_batch_kernel<<<(n + 255) / 256, 256, 0, s>>>(b->d_pos, b->d_last, b->d_chosen, slot, n);
+        QTB_LAUNCH_CHECK();
+        if (out_tokens) QTB_CUDA(cudaMemcpyAsync(out_tokens, b->d_chosen, count * sizeof(uint32_t), cudaMemcpyDeviceToHost, s));
+        if (logits) QTB_CUDA(cudaMemcpyAsync(logits, b->logits, count * d->vocab * sizeof(float), cudaMemcpyDeviceToHost, s));
+        if ((rc = decoder_check_status(d)) != QUINTRIT_OK) return rc;
+        if ((rc = batch_gemm_status(d)) != QUINTRIT_OK) return rc;
+        for (int z = 0; z < n; ++z) b->host_pos[sequences != nullptr ? sequences[z] : static_cast<uint32_t>(z)] += 1;
         return ok();
     });
 }

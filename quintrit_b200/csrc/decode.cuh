@@ -147,6 +147,23 @@ __device__ __forceinline__ void quantize_vector(const float* y_s, int n, float a
     if (tid == 0) scale_out[0] = s;
 }
 
+// ---- several sequences in one launch -------------------------------------------------------------------------------------
+// The kernels below take a token index in blockIdx.z. For a prompt chunk, token z sits at position pos[0] + z of the one
+// KV cache. For a step of several independent sequences (seq.pos_stride = 1), token z belongs to the sequence
+// s = slot[z] (or z without a slot list), sits at position pos[s] and uses the KV cache at cache + s * cache_stride.
+struct SeqIndex {
+    const uint32_t* slot;     // sequence of token z, or nullptr: z itself
+    int pos_stride;           // 0: one sequence, consecutive positions; 1: one position word per sequence
+    size_t cache_stride;      // elements between the caches of two sequences (this layer's cache of sequence s = base + s * stride)
+};
+__device__ __forceinline__ uint32_t seq_of(const SeqIndex& q, unsigned int z) { return q.slot != nullptr ? q.slot[z] : z; }
+__device__ __forceinline__ uint32_t seq_position(const SeqIndex& q, const uint32_t* pos, unsigned int z) {
+    return q.pos_stride != 0 ? pos[seq_of(q, z)] : pos[0] + z;
+}
+__device__ __forceinline__ size_t seq_cache_offset(const SeqIndex& q, unsigned int z) {
+    return q.pos_stride != 0 ? static_cast<size_t>(seq_of(q, z)) * q.cache_stride : 0;
+}
+
 // ---- embedding row: model.rs:308-317 ---------------------------------------------------------------------------------
 // A batch of tokens (prompt ingestion) runs as gridDim.y rows: token[y] -> x[y][hidden].
 __global__ void embed_kernel(const __half* __restrict__ table, const uint32_t* __restrict__ token, int hidden, float* __restrict__ x, bool bf16) {
@@ -179,6 +196,7 @@ struct NormQuantArgs {
     // A batch of tokens (prompt ingestion): token blockIdx.z uses x + z * b_x, acc_prev + z * b_acc, q_out + z * b_q, scale_prev + z and
     // scale_out + z when b_scale is set. All zero for the single-token launches.
     int b_x, b_acc, b_q, b_scale;
+    int b_y16;                // stride of y16_out between tokens
 };
 
 // x += acc * (ws / s)  (model.rs:85, 202 after layer.rs:143-147), y = rms_norm(x) (ops.rs:62-96), codes = quantise(y)
@@ -193,9 +211,10 @@ __global__ void __launch_bounds__(kRowThreads) norm_quant_kernel(NormQuantArgs a
         a.x += z * a.b_x;
         if (a.acc_prev != nullptr) a.acc_prev += z * a.b_acc;
         if (a.q_out != nullptr) a.q_out += z * a.b_q;
+        if (a.y16_out != nullptr) a.y16_out += z * a.b_y16;
         if (a.b_scale) {
             if (a.scale_prev != nullptr) a.scale_prev += z;
-            a.scale_out += z;
+            if (a.scale_out != nullptr) a.scale_out += z;
         }
     }
     for (int i = tid; i < a.zero_a_n; i += kRowThreads) a.zero_a[i] = 0;
@@ -248,7 +267,8 @@ struct RopeKvArgs {
     __half* k_cache;          // [ctx][kv_dim] of this layer
     __half* v_cache;
     int block_scaled;         // acc holds the F32 results of block-scaled projections: used as they are
-    int b_acc, b_q, b_scale;  // batch of tokens: token blockIdx.z at position pos[0] + z reads acc + z * b_acc and act_scale + z, writes q_out + z * b_q
+    int b_acc, b_q, b_scale;  // batch of tokens: token blockIdx.z reads acc + z * b_acc and act_scale + z, writes q_out + z * b_q
+    SeqIndex seq;             // its position and KV cache
 };
 
 __global__ void rope_kv_kernel(RopeKvArgs a) {
@@ -261,7 +281,9 @@ __global__ void rope_kv_kernel(RopeKvArgs a) {
     const float s = a.block_scaled ? 1.0f : a.act_scale[0];
     const bool live = s > 0.0f;
     const float pq = live ? __fdiv_rn(a.ws_q, s) : 0.0f, pk = live ? __fdiv_rn(a.ws_k, s) : 0.0f, pv = live ? __fdiv_rn(a.ws_v, s) : 0.0f;
-    const uint32_t pos = a.pos[0] + blockIdx.z;
+    const uint32_t pos = seq_position(a.seq, a.pos, blockIdx.z);
+    a.k_cache += seq_cache_offset(a.seq, blockIdx.z);
+    a.v_cache += seq_cache_offset(a.seq, blockIdx.z);
     const float* cs = a.cos_sin + static_cast<size_t>(pos) * a.rope_dims;
     const int half_pairs = a.rope_dims / 2;
     const int total_pairs = (a.q_dim + a.kv_dim) / 2;
@@ -330,7 +352,8 @@ struct AttnArgs {
     float scale;
     float* part_acc;          // [q_heads][4][head_dim] chunk accumulators (as F32; the F16 ones are widened exactly)
     float* part_ms;           // [q_heads][4][2]: M and S per chunk (S = 0 marks an empty chunk)
-    int b_q, b_acc, b_ms;     // batch of tokens: token blockIdx.z at position pos[0] + z uses q + z * b_q, part_acc + z * b_acc, part_ms + z * b_ms
+    int b_q, b_acc, b_ms;     // batch of tokens: token blockIdx.z uses q + z * b_q, part_acc + z * b_acc, part_ms + z * b_ms
+    SeqIndex seq;             // its position and KV cache
 };
 
 constexpr int kAttnThreads = 256;
@@ -365,7 +388,9 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(AttnArgs a) {
         a.part_acc += z * a.b_acc;
         a.part_ms += z * a.b_ms;
     }
-    const int seq_len = static_cast<int>(a.pos[0] + blockIdx.z) + 1;
+    const int seq_len = static_cast<int>(seq_position(a.seq, a.pos, blockIdx.z)) + 1;
+    a.k_cache += seq_cache_offset(a.seq, blockIdx.z);
+    a.v_cache += seq_cache_offset(a.seq, blockIdx.z);
     int n_kv = (seq_len + 255) / 256 * 256;
     if (n_kv < 256) n_kv = 256;
     if (n_kv > a.ctx) n_kv = a.ctx;
@@ -481,6 +506,7 @@ struct AttnFinishArgs {
     int zero_a_n;
     float* q8_d;              // block-scaled models: Q8_0 block scales of q_out (else nullptr: per-tensor int8)
     int b_acc, b_ms, b_q, b_scale;  // batch of tokens: per-token strides of part_acc, part_ms, q_out; scale_out + z when b_scale is set
+    SeqIndex seq;             // the token's position
 };
 
 __global__ void __launch_bounds__(kRowThreads) attn_finish_kernel(AttnFinishArgs a) {
@@ -496,7 +522,7 @@ __global__ void __launch_bounds__(kRowThreads) attn_finish_kernel(AttnFinishArgs
         if (a.b_scale) a.scale_out += z;
     }
     for (int i = tid; i < a.zero_a_n; i += kRowThreads) a.zero_a[i] = 0;
-    const int seq_len = static_cast<int>(a.pos[0] + blockIdx.z) + 1;
+    const int seq_len = static_cast<int>(seq_position(a.seq, a.pos, blockIdx.z)) + 1;
     int n_kv = (seq_len + 255) / 256 * 256;
     if (n_kv < 256) n_kv = 256;
     if (n_kv > a.ctx) n_kv = a.ctx;
@@ -628,6 +654,86 @@ __global__ void __launch_bounds__(256) lm_head_kernel(const __half* __restrict__
     }
 }
 
+// ---- output head for several tokens at once ------------------------------------------------------------------------------
+// The same dot products as lm_head_kernel (lane l of a warp owns the elements 32 i + l of a row and adds them in the order of
+// i, then the lanes are reduced), for up to kHeadTokens tokens against kHeadRows vocabulary rows per warp at a time: a row
+// element is read from HBM once per token group instead of once per token, and an activation read from shared memory serves
+// kHeadRows rows. The activations sit in shared memory as F32, laid out so that a lane reads its elements of four consecutive
+// steps with one 16-byte load: float4 index (t * hidden / 128 + k) * 32 + lane holds steps 4k .. 4k + 3.
+constexpr int kHeadTokens = 16, kHeadRows = 4, kHeadThreads = 256;
+__host__ __device__ constexpr size_t lm_head_batch_smem(int hidden) { return static_cast<size_t>(kHeadTokens) * hidden * sizeof(float); }
+
+__global__ void __launch_bounds__(kHeadThreads, 1) lm_head_batch_kernel(const __half* __restrict__ w, const __half* __restrict__ x16, int hidden, int vocab, int n,
+                                                                         float* __restrict__ logits, bool bf16) {
+    extern __shared__ float4 x4[];
+    float* xs = reinterpret_cast<float*>(x4);
+    const int t0 = blockIdx.y * kHeadTokens, nt = min(kHeadTokens, n - t0), k4 = hidden / 128;
+    for (int idx = threadIdx.x; idx < kHeadTokens * hidden; idx += kHeadThreads) {
+        const int t = idx / hidden, e = idx - t * hidden, step = e >> 5, l = e & 31;
+        const float v = t < nt ? table_to_float(x16[static_cast<size_t>(t0 + t) * hidden + e], bf16) : 0.0f;
+        xs[((static_cast<size_t>(t) * k4 + (step >> 2)) * 32 + l) * 4 + (step & 3)] = v;
+    }
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warps = kHeadThreads / 32;
+    for (int row0 = (blockIdx.x * warps + (threadIdx.x >> 5)) * kHeadRows; row0 < vocab; row0 += gridDim.x * warps * kHeadRows) {
+        const __half* wr[kHeadRows];
+#pragma unroll
+        for (int r = 0; r < kHeadRows; ++r) wr[r] = w + static_cast<size_t>(min(row0 + r, vocab - 1)) * hidden + lane;
+        float acc[kHeadTokens][kHeadRows];
+#pragma unroll
+        for (int t = 0; t < kHeadTokens; ++t)
+#pragma unroll
+            for (int r = 0; r < kHeadRows; ++r) acc[t][r] = 0.0f;
+        unsigned short raw[kHeadRows][4];
+#pragma unroll
+        for (int r = 0; r < kHeadRows; ++r)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) raw[r][j] = __half_as_ushort(wr[r][j * 32]);
+        for (int k = 0; k < k4; ++k) {
+            float wv[kHeadRows][4];
+#pragma unroll
+            for (int r = 0; r < kHeadRows; ++r)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) wv[r][j] = table_to_float(__ushort_as_half(raw[r][j]), bf16);
+            if (k + 1 < k4) {  // the next steps' row elements are requested before this step's arithmetic
+#pragma unroll
+                for (int r = 0; r < kHeadRows; ++r)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) raw[r][j] = __half_as_ushort(wr[r][(4 * (k + 1) + j) * 32]);
+            }
+            const float4* xk = x4 + static_cast<size_t>(k) * 32 + lane;
+            if (bf16) {  // ggml_vec_dot_bf16: product and sum rounded separately (ops.rs:694-700)
+#pragma unroll
+                for (int t = 0; t < kHeadTokens; ++t) {
+                    const float4 x = xk[static_cast<size_t>(t) * k4 * 32];
+                    const float xv[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+#pragma unroll
+                        for (int r = 0; r < kHeadRows; ++r) acc[t][r] = __fadd_rn(acc[t][r], __fmul_rn(xv[j], wv[r][j]));
+                }
+            } else {
+#pragma unroll
+                for (int t = 0; t < kHeadTokens; ++t) {
+                    const float4 x = xk[static_cast<size_t>(t) * k4 * 32];
+                    const float xv[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+#pragma unroll
+                        for (int r = 0; r < kHeadRows; ++r) acc[t][r] = __fmaf_rn(xv[j], wv[r][j], acc[t][r]);
+                }
+            }
+        }
+#pragma unroll
+        for (int t = 0; t < kHeadTokens; ++t)
+#pragma unroll
+            for (int r = 0; r < kHeadRows; ++r) {
+                const float sum = bf16 ? dot_lane_reduce_bf16(acc[t][r]) : dot_lane_reduce_f16(acc[t][r]);
+                if (lane == 0 && t < nt && row0 + r < vocab) logits[static_cast<size_t>(t0 + t) * vocab + row0 + r] = sum;
+            }
+    }
+}
+
 // ---- greedy sampler: first index of the strict maximum, NaN never wins (sampler.rs:73-83) ------------------------------
 __device__ __forceinline__ void argmax_merge(float& bv, unsigned int& bi, float v, unsigned int i) {
     if (v > bv || (v == bv && i < bi)) {
@@ -635,9 +741,12 @@ __device__ __forceinline__ void argmax_merge(float& bv, unsigned int& bi, float 
         bi = i;
     }
 }
+// Block b takes the row logits + b * n and writes out_token[b] (one block for a single token).
 __global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ logits, int n, uint32_t* __restrict__ out_token) {
     __shared__ float sv[32];
     __shared__ unsigned int si[32];
+    logits += static_cast<size_t>(blockIdx.x) * n;
+    out_token += blockIdx.x;
     float bv = -INFINITY;
     unsigned int bi = 0xFFFFFFFFu;
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
@@ -663,6 +772,19 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ 
 __global__ void advance_kernel(uint32_t* pos, uint32_t* history, const uint32_t* token) {
     history[pos[0]] = token[0];
     pos[0] += 1;
+}
+// the same for a step of several sequences: token z of the step belongs to sequence slot[z] (or z)
+__global__ void advance_batch_kernel(uint32_t* pos, uint32_t* last, const uint32_t* chosen, const uint32_t* slot, int n) {
+    const int z = blockIdx.x * blockDim.x + threadIdx.x;
+    if (z >= n) return;
+    const uint32_t s = slot != nullptr ? slot[z] : static_cast<uint32_t>(z);
+    last[s] = chosen[z];
+    pos[s] += 1;
+}
+// tokens of a step: the given ones, or the last chosen token of every listed sequence
+__global__ void gather_tokens_kernel(uint32_t* tokens, const uint32_t* last, const uint32_t* slot, int n) {
+    const int z = blockIdx.x * blockDim.x + threadIdx.x;
+    if (z < n) tokens[z] = last[slot != nullptr ? slot[z] : static_cast<uint32_t>(z)];
 }
 
 }  // namespace qtb

@@ -213,6 +213,12 @@ def prompt_tokens(config: int, n: int, vocab: int) -> np.ndarray:
     return (splitmix_u32(seed_for(config, 0, 0, 3), 0, n).astype(np.uint64) * np.uint64(vocab) >> np.uint64(32)).astype(np.uint32)
 
 
+def batch_lengths(config: int, n: int, lo: int = 256, hi: int = 2048) -> np.ndarray:
+    """Prompt lengths of a batch of sequences, uniform in [lo, hi], from stream 4."""
+    u = splitmix_u32(seed_for(config, 0, 0, 4), 0, n).astype(np.uint64)
+    return (np.uint64(lo) + (u * np.uint64(hi - lo + 1) >> np.uint64(32))).astype(np.int64)
+
+
 def shard_spec(spec: dict, rank: int, world: int) -> dict:
     """The share of `spec` (planar numpy projections) that rank `rank` of a tensor-parallel group of `world` GPUs holds:
     its rows of every projection - q / k / v rows of its heads, rows [rank * n / world, (rank + 1) * n / world) of o,
