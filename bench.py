@@ -213,6 +213,10 @@ def run_decode(args, local_rank: int):
     weights = sum(int(np.prod(sh)) for sh in [(spec["q_heads"] * spec["head_dim"], spec["hidden"]), (spec["kv_heads"] * spec["head_dim"], spec["hidden"]),
                                                (spec["kv_heads"] * spec["head_dim"], spec["hidden"]), (spec["hidden"], spec["q_heads"] * spec["head_dim"]),
                                                (spec["inter"], spec["hidden"]), (spec["inter"], spec["hidden"]), (spec["hidden"], spec["inter"])]) * spec["layers"]
+    if args.batch_only:  # profiling aid: the batched-decode leg alone
+        out = {"shape": spec["shape"], "layers": spec["layers"], "batched_decode": run_batched_decode(args, dec, spec, None)}
+        dec.free()
+        return out
     prompt = synth.prompt_tokens(2, args.prompt, spec["vocab"])
     # parity leg: a short prompt and a few greedy tokens against the CPU oracle (same arrays)
     parity = None
@@ -288,6 +292,8 @@ def run_batched_decode(args, dec, spec, single_ms: float):
     """Several sequences with prompts of different lengths decoded together (one batched pass over the weights per step): aggregate tokens/s of
     the greedy steps, wall clock around the C call with the chosen tokens read back every step, and a check of two sequences against the
     same sequences decoded alone."""
+    import torch
+
     import quintrit_b200 as q
 
     n_seq, steps = args.batch_seqs, args.batch_steps
@@ -301,12 +307,14 @@ def run_batched_decode(args, dec, spec, single_ms: float):
     for _ in range(3):
         batch.step()
     got = {i: [] for i in check}
+    torch.cuda.profiler.start()  # a profiler started with "--profile-from-start off" sees the timed steps only; a no-op otherwise
     t0 = time.perf_counter()
     for k in range(steps):
         toks, _ = batch.step()
         for i in check:
             got[i].append(int(toks[i]))
     step_s = (time.perf_counter() - t0) / steps
+    torch.cuda.profiler.stop()
     batch.free()
     same = True
     for i in check:
@@ -318,7 +326,7 @@ def run_batched_decode(args, dec, spec, single_ms: float):
             alone.append(int(tok))
         same = same and alone[3:] == got[i]
     return {"sequences": n_seq, "prompt_lengths": "uniform in [256, 2048] (stream 4)", "prompt_tokens_total": int(lengths.sum()), "mean_context": round(float(lengths.mean()), 1),
-            "steps": steps, "ms_per_step": round(step_s * 1e3, 3), "tokens_per_s": round(n_seq / step_s, 1), "speedup_vs_one_sequence": round(n_seq / step_s / (1e3 / single_ms), 2),
+            "steps": steps, "ms_per_step": round(step_s * 1e3, 3), "tokens_per_s": round(n_seq / step_s, 1), "speedup_vs_one_sequence": None if single_ms is None else round(n_seq / step_s / (1e3 / single_ms), 2),
             "prompt_ingestion_tokens_per_s": round(float(lengths.sum()) / ingest_s, 1), "sequences_checked_against_decoding_alone": len(check), "identical_tokens": bool(same),
             "timing": "wall clock around quintrit_b200_batch_step, the chosen tokens copied to the host every step"}
 
@@ -795,6 +803,7 @@ def main():
     ap.add_argument("--decode-shape", default="falcon3_10b", choices=["falcon3_10b", "bitnet_2b"])
     ap.add_argument("--decode-layers", type=int, default=None, help="fewer layers than the shape has (experiments)")
     ap.add_argument("--batch-seqs", type=int, default=32, help="sequences of the batched-decode leg (0 skips it)")
+    ap.add_argument("--batch-only", action="store_true", help="with --decode-only: run only the batched-decode leg (profiling aid)")
     ap.add_argument("--batch-steps", type=int, default=16, help="greedy steps timed in the batched-decode leg")
     ap.add_argument("--prompt", type=int, default=1024, help="context length at which a decode step is timed")
     ap.add_argument("--parity-full", action="store_true", help="decode the committed full-size fixtures (40 / 30 layers, 1024 + 512 / 512 + 256 tokens) from synthetic GGUF files in every encoding and compare with the CPU oracle's tokens and logits")

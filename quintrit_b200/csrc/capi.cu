@@ -799,6 +799,15 @@ size_t decoder_item_tiles(size_t tile_pairs, size_t slots) {
 
 int mega_setup(quintrit_b200_decoder* d, const quintrit_b200_decoder_desc_t* desc);
 
+// Lets a kernel use all the shared memory the device offers a block beyond the kernel's own static arrays.
+template <typename K>
+int allow_max_dynamic_smem(K kernel, int smem_optin) {
+    cudaFuncAttributes fa{};
+    QTB_CUDA(cudaFuncGetAttributes(&fa, kernel));
+    QTB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_optin - static_cast<int>(fa.sharedSizeBytes)));
+    return QUINTRIT_OK;
+}
+
 int decoder_create_impl(const quintrit_b200_decoder_desc_t* desc, quintrit_b200_decoder** out) {
     if (desc->struct_size < sizeof(quintrit_b200_decoder_desc_t))
         return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "struct_size %u is smaller than quintrit_b200_decoder_desc_t (%zu)", desc->struct_size,
@@ -973,18 +982,33 @@ int decoder_create_impl(const quintrit_b200_decoder_desc_t* desc, quintrit_b200_
     // one-time kernel set-up, before any stream capture
     GemvKernel k = nullptr;
     if ((rc = gemv_kernel_for_device(d->device, &k)) != QUINTRIT_OK) return rc;
-    const int big = static_cast<int>(std::max<size_t>({H, I, qd}) * sizeof(float));
-    QTB_CUDA(cudaFuncSetAttribute(norm_quant_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
-    QTB_CUDA(cudaFuncSetAttribute(attn_finish_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
-    QTB_CUDA(cudaFuncSetAttribute(act_quant_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
-    QTB_CUDA(cudaFuncSetAttribute(lm_head_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+    // The limit is a property of the kernel, shared by every decoder of the process: it is set to the most the device allows, so that a
+    // later, smaller model does not lower it under an earlier, larger one.
+    int smem_optin = 0;
+    QTB_CUDA(cudaDeviceGetAttribute(&smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, d->device));
+    const size_t big = std::max<size_t>({H, I, qd}) * sizeof(float);
+    if (big + 1024 > static_cast<size_t>(smem_optin)) return fail(QUINTRIT_ERR_UNSUPPORTED, "a vector of %zu bytes does not fit the shared memory of a multiprocessor (%d bytes)", big, smem_optin);
+    if ((rc = allow_max_dynamic_smem(norm_quant_kernel, smem_optin)) != QUINTRIT_OK) return rc;
+    if ((rc = allow_max_dynamic_smem(attn_finish_kernel, smem_optin)) != QUINTRIT_OK) return rc;
+    if ((rc = allow_max_dynamic_smem(act_quant_kernel, smem_optin)) != QUINTRIT_OK) return rc;
+    if ((rc = allow_max_dynamic_smem(lm_head_kernel, smem_optin)) != QUINTRIT_OK) return rc;
+    if ((rc = allow_max_dynamic_smem(lm_head_batch_kernel, smem_optin)) != QUINTRIT_OK) return rc;
+    // attention for all query heads of a KV head at once, where the group size and the head size allow it
+    d->attn_gqa = nullptr, d->attn_gqa_smem = 0;
+    if (hd % 32 == 0 && hd <= 256 && std::getenv("QUINTRIT_B200_ATTN_GQA_OFF") == nullptr) {
+        const int group = d->q_heads / d->kv_heads;
+        AttnGqaKernel kq = attention_gqa_for(group, d->f32_values != 0);
+        const size_t bytes = kq != nullptr ? attention_gqa_smem(group, static_cast<int>(hd), d->ctx) : 0;
+        if (kq != nullptr && bytes + 1024 <= static_cast<size_t>(smem_optin)) {
+            if ((rc = allow_max_dynamic_smem(kq, smem_optin)) != QUINTRIT_OK) return rc;
+            d->attn_gqa = kq, d->attn_gqa_smem = bytes;
+        }
+    }
     d->use_mega = false;
     const char* mode = std::getenv("QUINTRIT_B200_DECODE");  // "kernels" keeps the one-launch-per-step path (experiments)
     // the single-kernel path stages KV rows with a piece permutation that needs a power-of-two head_dim of at least 64
     // and one values unit of the longest chunk must fit the shared memory of an SM next to the activation vectors
     const int gqa_n = d->q_heads / d->kv_heads;
-    int smem_optin = 0;
-    QTB_CUDA(cudaDeviceGetAttribute(&smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, d->device));
     // the second form of the attention's second half (units that take all chunks of 8 coordinates) where its arrays fit
     d->attn_v2 = tp_world == 1 && d->ctx <= static_cast<uint32_t>(kV2MaxCtx) && gqa_n <= kV2MaxGqa && qd_full <= size_t(kNormPer) * kMegaThreads && hd % kV2Dims == 0 &&
                  d->kv_heads * (hd / kV2Dims) < static_cast<uint32_t>(d->sm_count);  // some CTAs must stay free to compute the softmax factors
@@ -2133,7 +2157,7 @@ int prefill_layers(quintrit_b200_decoder* d, int n, const BatchTarget& tg) {
         at.head_dim = hd, at.kv_dim = kvd, at.gqa = d->q_heads / d->kv_heads, at.ctx = d->ctx, at.f32_values = d->f32_values;
         at.scale = 1.0f / std::sqrt(static_cast<float>(hd));
         at.part_acc = d->pf.part_acc, at.b_acc = d->q_heads * 4 * hd, at.part_ms = d->pf.part_ms, at.b_ms = d->q_heads * 8;
-        attention_kernel<<<dim3(d->q_heads, 4, n), kAttnThreads, 0, s>>>(at);
+        launch_attention(d, at, n, s);
         QTB_LAUNCH_CHECK();
         AttnFinishArgs af{};
         af.part_acc = d->pf.part_acc, af.b_acc = d->q_heads * 4 * hd, af.part_ms = d->pf.part_ms, af.b_ms = d->q_heads * 8, af.pos = tg.pos, af.seq = tg.seq;
@@ -2321,15 +2345,6 @@ int batch_head(quintrit_b200_batch* b, int n) {
     norm_quant_kernel<<<dim3(1, 1, n), kRowThreads, H * sizeof(float), s>>>(nf);
     QTB_LAUNCH_CHECK();
     if (H % 128 == 0 && lm_head_batch_smem(H) <= 200 * 1024) {
-        static std::mutex attr_lock;
-        static bool attr_set[64] = {};
-        {
-            std::lock_guard<std::mutex> hold(attr_lock);
-            if (!attr_set[d->device & 63]) {
-                QTB_CUDA(cudaFuncSetAttribute(lm_head_batch_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-                attr_set[d->device & 63] = true;
-            }
-        }
         lm_head_batch_kernel<<<dim3(d->sm_count, (n + kHeadTokens - 1) / kHeadTokens), kHeadThreads, lm_head_batch_smem(H), s>>>(d->lm_head, b->x16, H, d->vocab, n, b->logits,
                                                                                                                                   d->bf16_tables);
         QTB_LAUNCH_CHECK();

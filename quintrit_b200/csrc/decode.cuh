@@ -492,6 +492,219 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(AttnArgs a) {
     }
 }
 
+// ---- the same attention for all query heads of a KV head at once --------------------------------------------------------
+// Grid (kv_heads, chunks, tokens), 288 threads: the G query heads that share a KV head (grouped-query attention) share one
+// pass over its keys and values. The arithmetic per head is attention_kernel's, operation for operation (the reference's
+// order: attention.rs:402-469); what changes is who does it:
+//  A. a warp takes a position, reads the key row once and forms the G dot products;
+//  B. warp g turns head g's scores into the running maximum and the factors ms / vs with a warp scan over blocks of 32
+//     positions (the running maximum is a prefix maximum, so the scan gives exactly the sequential values);
+//  C. thread d < head_dim runs the G value chains of coordinate d side by side, reading each value element once, while the
+//     ninth warp runs the G chains of the sums S.
+// Per position the factors vs of the G heads and a bit mask "ms != 1 for head g" sit in one record that phase C reads
+// with a single shared-memory load. Dynamic shared memory: attention_gqa_smem(G, head_dim, context).
+constexpr int kAttnGqaThreads = 288;
+__host__ __device__ constexpr int attn_gqa_record_words(int g) { return g <= 3 ? 4 : 8; }
+__host__ __device__ constexpr int attn_gqa_chunk_max(int ctx) { return ((ctx + 3) / 4 + 31) / 32 * 32 > 256 ? ((ctx + 3) / 4 + 31) / 32 * 32 : 256; }
+__host__ __device__ constexpr size_t attention_gqa_smem(int g, int head_dim, int ctx) {
+    return static_cast<size_t>(attn_gqa_chunk_max(ctx)) * (attn_gqa_record_words(g) + g) * 4 + static_cast<size_t>(g) * head_dim * 4 + 64;
+}
+
+template <bool F32>
+__device__ __forceinline__ float value_round(float x) {  // the accumulator is an F16 after every operation (bitnet.cpp numerics) or stays F32
+    return F32 ? x : __half2float(__float2half_rn(x));
+}
+
+template <int G, bool F32>
+__global__ void __launch_bounds__(kAttnGqaThreads) attention_gqa_kernel(AttnArgs a) {
+    constexpr int W = attn_gqa_record_words(G);
+    extern __shared__ __align__(16) unsigned char gqa_smem[];
+    const int kvh = blockIdx.x, c = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int hd = a.head_dim, cmax = attn_gqa_chunk_max(a.ctx);
+    float* s_rec = reinterpret_cast<float*>(gqa_smem);        // [cmax][W]: vs of head g at word g, the mask at word W - 1
+    float* s_ms = s_rec + static_cast<size_t>(cmax) * W;       // [G][cmax]: scores, then ms
+    float* s_q = s_ms + static_cast<size_t>(G) * cmax;         // [G][hd]
+    float* s_M = s_q + static_cast<size_t>(G) * hd;            // [G]: the chunk's maximum per head
+    if (blockIdx.z != 0) {
+        const size_t z = blockIdx.z;
+        a.q += z * a.b_q;
+        a.part_acc += z * a.b_acc;
+        a.part_ms += z * a.b_ms;
+    }
+    const int seq_len = static_cast<int>(seq_position(a.seq, a.pos, blockIdx.z)) + 1;
+    a.k_cache += seq_cache_offset(a.seq, blockIdx.z);
+    a.v_cache += seq_cache_offset(a.seq, blockIdx.z);
+    int n_kv = (seq_len + 255) / 256 * 256;
+    if (n_kv < 256) n_kv = 256;
+    if (n_kv > a.ctx) n_kv = a.ctx;
+    int start = 0, end = seq_len;
+    if (n_kv >= 512) {
+        const int chunk = (n_kv + 3) / 4;
+        start = c * chunk;
+        end = min(min(start + chunk, n_kv), seq_len);
+    } else if (c > 0) {
+        start = end;  // single-chunk case: chunks 1..3 are empty
+    }
+    const int h0 = kvh * G;
+    const int len = min(end - start, cmax);  // (a chunk never exceeds cmax: n_kv <= ctx)
+    if (len <= 0) {
+        if (tid < G) {
+            float* my_ms = a.part_ms + (static_cast<size_t>(h0 + tid) * 4 + c) * 2;
+            my_ms[0] = -INFINITY;
+            my_ms[1] = 0.0f;
+        }
+        return;
+    }
+    for (int i = tid; i < G * hd; i += kAttnGqaThreads) {
+        const float qv = a.q[h0 * hd + i];
+        s_q[i] = F32 ? qv : __half2float(__float2half_rn(qv));
+    }
+    __syncthreads();
+    const __half* kbase = a.k_cache + static_cast<size_t>(kvh) * hd + static_cast<size_t>(start) * a.kv_dim;
+    const __half* vbase = a.v_cache + static_cast<size_t>(kvh) * hd + static_cast<size_t>(start) * a.kv_dim;
+    // Phase A: lane l owns the elements 32 i + l of a row, added in the order of i (ggml_vec_dot_f16 / _f16_f32), then the lanes are reduced
+    {
+        const int nq = hd >> 5;  // <= 8
+        float qr[G][8];
+#pragma unroll
+        for (int g = 0; g < G; ++g)
+#pragma unroll
+            for (int i = 0; i < 8; ++i) qr[g][i] = i < nq ? s_q[g * hd + i * 32 + lane] : 0.0f;
+        constexpr int kWarps = kAttnGqaThreads / 32;
+        for (int p = warp; p < len; p += 2 * kWarps) {
+            const int p2 = p + kWarps;
+            const bool two = p2 < len;
+            const __half* k1 = kbase + static_cast<size_t>(p) * a.kv_dim + lane;
+            const __half* k2 = kbase + static_cast<size_t>(two ? p2 : p) * a.kv_dim + lane;
+            float x1[8], x2[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                x1[i] = i < nq ? __half2float(k1[i * 32]) : 0.0f;
+                x2[i] = i < nq ? __half2float(k2[i * 32]) : 0.0f;
+            }
+            float acc1[G], acc2[G];
+#pragma unroll
+            for (int g = 0; g < G; ++g) acc1[g] = 0.0f, acc2[g] = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                if (i < nq) {
+#pragma unroll
+                    for (int g = 0; g < G; ++g) {
+                        acc1[g] = __fmaf_rn(x1[i], qr[g][i], acc1[g]);
+                        acc2[g] = __fmaf_rn(x2[i], qr[g][i], acc2[g]);
+                    }
+                }
+            }
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                const float sc1 = F32 ? dot_lane_reduce_f16_f32(acc1[g]) : dot_lane_reduce_f16(acc1[g]);
+                const float sc2 = F32 ? dot_lane_reduce_f16_f32(acc2[g]) : dot_lane_reduce_f16(acc2[g]);
+                if (lane == 0) {
+                    s_ms[g * cmax + p] = __fmul_rn(sc1, a.scale);
+                    if (two) s_ms[g * cmax + p2] = __fmul_rn(sc2, a.scale);
+                }
+            }
+        }
+    }
+    __syncthreads();
+    // Phase B: warp g, head g
+    for (int i = tid; i < len; i += kAttnGqaThreads) reinterpret_cast<uint32_t*>(s_rec)[static_cast<size_t>(i) * W + W - 1] = 0u;
+    __syncthreads();
+    if (warp < G) {
+        const int g = warp;
+        float* sc_g = s_ms + g * cmax;
+        float carry = -INFINITY;  // the maximum of all earlier positions
+        for (int base = 0; base < len; base += 32) {
+            const int p = base + lane;
+            const float sc = p < len ? sc_g[p] : -INFINITY;
+            float incl = sc;  // inclusive prefix maximum over the block
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const float up = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl = fmaxf(incl, up);
+            }
+            float excl = __shfl_up_sync(0xffffffffu, incl, 1);
+            if (lane == 0) excl = -INFINITY;
+            const float m_old = fmaxf(carry, excl);
+            if (p < len) {
+                float ms = 1.0f, vs = 1.0f;
+                if (sc > m_old) {
+                    ms = device_expf(__fsub_rn(m_old, sc));
+                } else {
+                    vs = device_expf(__fsub_rn(sc, m_old));
+                }
+                sc_g[p] = ms;
+                s_rec[static_cast<size_t>(p) * W + g] = vs;
+                if (ms != 1.0f) atomicOr(reinterpret_cast<unsigned int*>(s_rec) + static_cast<size_t>(p) * W + W - 1, 1u << g);
+            }
+            carry = fmaxf(carry, __shfl_sync(0xffffffffu, incl, 31));
+        }
+        if (lane == 0) s_M[g] = carry;
+    }
+    __syncthreads();
+    // Phase C
+    if (warp == kAttnGqaThreads / 32 - 1) {  // the sums: S = fma(S, ms, vs) in position order (attention.rs:466)
+        if (lane < G) {
+            const float* ms_g = s_ms + lane * cmax;
+            float S = 0.0f;
+            for (int p = 0; p < len; ++p) S = __fmaf_rn(S, ms_g[p], s_rec[static_cast<size_t>(p) * W + lane]);
+            float* my_ms = a.part_ms + (static_cast<size_t>(h0 + lane) * 4 + c) * 2;
+            my_ms[0] = s_M[lane];
+            my_ms[1] = S;
+        }
+        return;
+    }
+    for (int d = tid; d < hd; d += kAttnGqaThreads - 32) {
+        const __half* vr = vbase + d;
+        float acc[G];
+#pragma unroll
+        for (int g = 0; g < G; ++g) acc[g] = 0.0f;
+        auto step = [&](int p, __half vh) {
+            float rec[W];
+            if constexpr (W == 4) {
+                const float4 r = *reinterpret_cast<const float4*>(s_rec + static_cast<size_t>(p) * 4);
+                rec[0] = r.x, rec[1] = r.y, rec[2] = r.z, rec[3] = r.w;
+            } else {
+                const float4 r0 = *reinterpret_cast<const float4*>(s_rec + static_cast<size_t>(p) * 8);
+                const float4 r1 = *reinterpret_cast<const float4*>(s_rec + static_cast<size_t>(p) * 8 + 4);
+                rec[0] = r0.x, rec[1] = r0.y, rec[2] = r0.z, rec[3] = r0.w, rec[4] = r1.x, rec[5] = r1.y, rec[6] = r1.z, rec[7] = r1.w;
+            }
+            const unsigned int mask = __float_as_uint(rec[W - 1]);
+            if (mask != 0u) {
+#pragma unroll
+                for (int g = 0; g < G; ++g)
+                    if ((mask >> g) & 1u) acc[g] = value_round<F32>(__fmul_rn(acc[g], s_ms[g * cmax + p]));
+            }
+            const float vf = __half2float(vh);
+#pragma unroll
+            for (int g = 0; g < G; ++g) acc[g] = value_round<F32>(__fmaf_rn(vf, rec[g], acc[g]));
+        };
+        int p = 0;
+        for (; p + 8 <= len; p += 8) {
+            __half v8[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v8[j] = vr[static_cast<size_t>(p + j) * a.kv_dim];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) step(p + j, v8[j]);
+        }
+        for (; p < len; ++p) step(p, vr[static_cast<size_t>(p) * a.kv_dim]);
+#pragma unroll
+        for (int g = 0; g < G; ++g) a.part_acc[(static_cast<size_t>(h0 + g) * 4 + c) * hd + d] = acc[g];
+    }
+}
+
+using AttnGqaKernel = void (*)(AttnArgs);
+// The instantiation for a group size and numerics, or nullptr: then attention_kernel runs one query head per block.
+inline AttnGqaKernel attention_gqa_for(int gqa, bool f32_values) {
+    switch (gqa) {
+        case 1: return f32_values ? attention_gqa_kernel<1, true> : attention_gqa_kernel<1, false>;
+        case 2: return f32_values ? attention_gqa_kernel<2, true> : attention_gqa_kernel<2, false>;
+        case 3: return f32_values ? attention_gqa_kernel<3, true> : attention_gqa_kernel<3, false>;
+        case 4: return f32_values ? attention_gqa_kernel<4, true> : attention_gqa_kernel<4, false>;
+        default: return nullptr;
+    }
+}
+
 // ---- combine the KV chunks (attention.rs:497-541), optional sub-norm, quantise for the o projection -------------------
 struct AttnFinishArgs {
     const float* part_acc;    // [q_heads][4][head_dim]

@@ -41,6 +41,8 @@ struct quintrit_b200_decoder {
     float *xa, *xb, *v_inter, *best_val;
     unsigned int *amax_bits, *best_idx, *bar;
     bool attn_v2 = false;
+    qtb::AttnGqaKernel attn_gqa = nullptr;     // one-launch-per-step and batched paths: the grouped attention kernel, if this model's shape has one
+    size_t attn_gqa_smem = 0;
     float* attn_out = nullptr;
     float *fac = nullptr, *fac_M = nullptr;
     unsigned int *fac_flags = nullptr, *fac_done = nullptr;
@@ -134,6 +136,14 @@ inline int decoder_gemv_bs(quintrit_b200_decoder* d, int layer, int which, const
     return QUINTRIT_OK;
 }
 
+// Attention of n tokens: all query heads of a KV head in one block where an instantiation exists, else one query head per block.
+inline void launch_attention(quintrit_b200_decoder* d, const AttnArgs& at, int n, cudaStream_t s) {
+    if (d->attn_gqa != nullptr)
+        d->attn_gqa<<<dim3(d->kv_heads, 4, n), kAttnGqaThreads, d->attn_gqa_smem, s>>>(at);
+    else
+        attention_kernel<<<dim3(d->q_heads, 4, n), kAttnThreads, 0, s>>>(at);
+}
+
 #define QTB_LAUNCH_CHECK()                                   \
     do {                                                     \
         ++g_launches;                                        \
@@ -198,7 +208,7 @@ inline int enqueue_token(quintrit_b200_decoder* d, bool with_head) {
         at.scale = 1.0f / std::sqrt(static_cast<float>(d->head_dim));  // attention.rs:46
         at.part_acc = d->part_acc;
         at.part_ms = d->part_ms;
-        attention_kernel<<<dim3(d->q_heads, 4), kAttnThreads, 0, s>>>(at);
+        launch_attention(d, at, 1, s);
         QTB_LAUNCH_CHECK();
         AttnFinishArgs af{};
         af.part_acc = d->part_acc;
