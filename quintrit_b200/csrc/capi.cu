@@ -1181,6 +1181,7 @@ int decoder_step(quintrit_b200_decoder* d) {
 
 // The status word of the decode kernel as an error of the C ABI.
 int kernel_status_error(unsigned int flag) {
+    if (flag == kGemmStatusTimeout) return fail(QUINTRIT_ERR_DEVICE, "the batched projection kernel on the CUDA device gave up waiting at a barrier");
     if (flag == 3) return fail(QUINTRIT_ERR_DEVICE, "the decode kernel on the CUDA device gave up waiting for another rank of the tensor-parallel group");
     if (flag == 2) return fail(QUINTRIT_ERR_DEVICE, "the decode kernel on the CUDA device gave up waiting at a grid barrier");
     if (flag != 0) return fail(QUINTRIT_ERR_DEVICE, "a kernel on the CUDA device found its shared-memory table at an unexpected address");
@@ -1954,8 +1955,12 @@ int gemm_prepare(quintrit_b200_matrix* m) {
 }
 
 // One launch for up to kGemmMaxN activation vectors that are on the device ([batch][cols]); d_out is [batch][rows].
-int gemm_launch(quintrit_b200_matrix* m, const int8_t* d_act, int batch, int32_t* d_out, cudaStream_t stream, int ldo = 0) {
+// With `defer`, a product whose K dimension is split leaves its parts where they are and describes them in *defer for the kernel that consumes the
+// sums (which adds them); otherwise a second kernel adds the parts into d_out.
+// `status` is the word a time-out is reported in: the matrix's own by default, a decoder's for the launches a decoder makes (one read-back per call).
+int gemm_launch(quintrit_b200_matrix* m, const int8_t* d_act, int batch, int32_t* d_out, cudaStream_t stream, int ldo = 0, AccView* defer = nullptr, unsigned int* status = nullptr) {
     if (ldo == 0) ldo = static_cast<int>(m->rows);
+    if (defer != nullptr) *defer = AccView{d_out, 1, 0, ldo};
     TensorMapEncodeFn encode = nullptr;
     int rc = tensor_map_encoder(&encode);
     if (rc != QUINTRIT_OK) return rc;
@@ -1980,7 +1985,7 @@ int gemm_launch(quintrit_b200_matrix* m, const int8_t* d_act, int batch, int32_t
                                CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (cr != CUDA_SUCCESS) return fail(QUINTRIT_ERR_DEVICE, "cuTensorMapEncodeTiled failed with CUDA driver error %d", static_cast<int>(cr));
     GemmArgs a;
-    a.w = m->d_gemm_w, a.out = d_out, a.status = m->d_gemm_status;
+    a.w = m->d_gemm_w, a.out = d_out, a.status = status != nullptr ? status : m->d_gemm_status;
     a.rows = static_cast<int>(m->rows), a.rows_padded = static_cast<int>(m->gemm_rows_padded), a.blocks = gblocks;
     a.n = n, a.batch = batch, a.ldo = ldo;
     a.stages = gemm_stages_for(n, kGemmSmemLimit);
@@ -2011,7 +2016,9 @@ int gemm_launch(quintrit_b200_matrix* m, const int8_t* d_act, int batch, int32_t
     }
     gemm_i8_tcgen05_kernel<<<std::min(m_tiles * ksplit, m->sm_count), kGemmThreads, gemm_smem_bytes(n, a.stages), stream>>>(map, a);
     ++g_launches;
-    if (ksplit > 1) {
+    if (ksplit > 1 && defer != nullptr) {
+        *defer = AccView{m->d_gemm_parts, ksplit, size_t(batch) * m->rows, static_cast<int>(m->rows)};
+    } else if (ksplit > 1) {
         const size_t count = size_t(batch) * m->rows;
         gemm_reduce_parts_kernel<<<static_cast<int>(std::min<size_t>((count + 255) / 256, size_t(m->sm_count) * 8)), 256, 0, stream>>>(m->d_gemm_parts, d_out, count, ksplit, static_cast<int>(m->rows), ldo);
         ++g_launches;
@@ -2129,6 +2136,12 @@ int prefill_layers(quintrit_b200_decoder* d, int n, const BatchTarget& tg) {
     QTB_LAUNCH_CHECK();
     auto mat = [&](int l, int k) { return const_cast<quintrit_b200_matrix*>(d->mats[size_t(l) * 7 + k]); };
     int rc;
+    // Projections whose K dimension is split leave their parts to the kernel that consumes the sums (AccView); only the last layer's down
+    // projection is completed by a pass of its own, because the final norm of a later launch reads it.
+    const bool defer = std::getenv("QUINTRIT_B200_GEMM_DEFER_OFF") == nullptr;
+    AccView v_q{}, v_k{}, v_v{}, v_o{}, v_gate{}, v_up{}, v_down{};
+    auto view = [&](AccView* v) { return defer ? v : nullptr; };
+    unsigned int* st = d->d_counters + 2;  // the decoder's status word: a time-out in a batched product is read back with the decoder's other failures
     for (int l = 0; l < d->layers; ++l) {
         const float* sc = d->scales.data() + l * 7;
         NormQuantArgs n1{};
@@ -2136,10 +2149,12 @@ int prefill_layers(quintrit_b200_decoder* d, int n, const BatchTarget& tg) {
         if (l > 0) n1.acc_prev = d->pf.acc_down, n1.b_acc = H, n1.scale_prev = d->pf.s_i, n1.ws_prev = d->scales[(l - 1) * 7 + 6];
         n1.norm_w = d->norms[l * 4 + 0], n1.eps = d->eps, n1.n = H;
         n1.q_out = d->pf.a8_h, n1.b_q = H, n1.scale_out = d->pf.s_h, n1.b_scale = 1;
+        if (l > 0) n1.v_prev = v_down;
         norm_quant_kernel<<<dim3(1, 1, n), kRowThreads, H * sizeof(float), s>>>(n1);
         QTB_LAUNCH_CHECK();
-        if ((rc = gemm_launch(mat(l, 0), d->pf.a8_h, n, d->pf.acc_qkv, s, qkv)) != QUINTRIT_OK || (rc = gemm_launch(mat(l, 1), d->pf.a8_h, n, d->pf.acc_qkv + qd, s, qkv)) != QUINTRIT_OK ||
-            (rc = gemm_launch(mat(l, 2), d->pf.a8_h, n, d->pf.acc_qkv + qd + kvd, s, qkv)) != QUINTRIT_OK)
+        if ((rc = gemm_launch(mat(l, 0), d->pf.a8_h, n, d->pf.acc_qkv, s, qkv, view(&v_q), st)) != QUINTRIT_OK ||
+            (rc = gemm_launch(mat(l, 1), d->pf.a8_h, n, d->pf.acc_qkv + qd, s, qkv, view(&v_k), st)) != QUINTRIT_OK ||
+            (rc = gemm_launch(mat(l, 2), d->pf.a8_h, n, d->pf.acc_qkv + qd + kvd, s, qkv, view(&v_v), st)) != QUINTRIT_OK)
             return rc;
         RopeKvArgs rk{};
         rk.acc = d->pf.acc_qkv, rk.b_acc = qkv, rk.act_scale = d->pf.s_h, rk.b_scale = 1;
@@ -2147,6 +2162,7 @@ int prefill_layers(quintrit_b200_decoder* d, int n, const BatchTarget& tg) {
         rk.cos_sin = d->cos_sin, rk.pos = tg.pos, rk.seq = tg.seq;
         rk.q_dim = qd, rk.kv_dim = kvd, rk.head_dim = hd, rk.rope_dims = d->rope_dims, rk.neox = d->arch == QUINTRIT_B200_ARCH_BITNET;
         rk.q_out = d->pf.q, rk.b_q = qd;
+        if (defer) rk.v_q = v_q, rk.v_k = v_k, rk.v_v = v_v;
         rk.k_cache = tg.kc + static_cast<size_t>(l) * d->ctx * kvd;
         rk.v_cache = tg.vc + static_cast<size_t>(l) * d->ctx * kvd;
         rope_kv_kernel<<<dim3(((qd + kvd) / 2 + kvd + 255) / 256, 1, n), 256, 0, s>>>(rk);
@@ -2166,14 +2182,16 @@ int prefill_layers(quintrit_b200_decoder* d, int n, const BatchTarget& tg) {
         af.q_out = d->pf.a8_q, af.b_q = qd, af.scale_out = d->pf.s_q, af.b_scale = 1;
         attn_finish_kernel<<<dim3(1, 1, n), kRowThreads, qd * sizeof(float), s>>>(af);
         QTB_LAUNCH_CHECK();
-        if ((rc = gemm_launch(mat(l, 3), d->pf.a8_q, n, d->pf.acc_o, s)) != QUINTRIT_OK) return rc;
+        if ((rc = gemm_launch(mat(l, 3), d->pf.a8_q, n, d->pf.acc_o, s, 0, view(&v_o), st)) != QUINTRIT_OK) return rc;
         NormQuantArgs n2{};
         n2.x = d->pf.x, n2.b_x = H, n2.acc_prev = d->pf.acc_o, n2.b_acc = H, n2.scale_prev = d->pf.s_q, n2.ws_prev = sc[3];
         n2.norm_w = d->norms[l * 4 + 1], n2.eps = d->eps, n2.n = H;
         n2.q_out = d->pf.a8_h, n2.b_q = H, n2.scale_out = d->pf.s_h, n2.b_scale = 1;
+        if (defer) n2.v_prev = v_o;
         norm_quant_kernel<<<dim3(1, 1, n), kRowThreads, H * sizeof(float), s>>>(n2);
         QTB_LAUNCH_CHECK();
-        if ((rc = gemm_launch(mat(l, 4), d->pf.a8_h, n, d->pf.acc_gu, s, 2 * I)) != QUINTRIT_OK || (rc = gemm_launch(mat(l, 5), d->pf.a8_h, n, d->pf.acc_gu + I, s, 2 * I)) != QUINTRIT_OK)
+        if ((rc = gemm_launch(mat(l, 4), d->pf.a8_h, n, d->pf.acc_gu, s, 2 * I, view(&v_gate), st)) != QUINTRIT_OK ||
+            (rc = gemm_launch(mat(l, 5), d->pf.a8_h, n, d->pf.acc_gu + I, s, 2 * I, view(&v_up), st)) != QUINTRIT_OK)
             return rc;
         ActQuantArgs aq{};
         aq.acc_gate = d->pf.acc_gu, aq.acc_up = d->pf.acc_gu + I, aq.b_acc = 2 * I, aq.act_scale = d->pf.s_h, aq.b_scale = 1;
@@ -2181,9 +2199,10 @@ int prefill_layers(quintrit_b200_decoder* d, int n, const BatchTarget& tg) {
         aq.n = I, aq.relu2 = d->arch == QUINTRIT_B200_ARCH_BITNET;
         aq.sub_norm_w = d->norms[l * 4 + 3], aq.eps = d->eps;
         aq.q_out = d->pf.a8_i, aq.b_q = I, aq.scale_out = d->pf.s_i;
+        if (defer) aq.v_gate = v_gate, aq.v_up = v_up;
         act_quant_kernel<<<dim3(1, 1, n), kRowThreads, I * sizeof(float), s>>>(aq);
         QTB_LAUNCH_CHECK();
-        if ((rc = gemm_launch(mat(l, 6), d->pf.a8_i, n, d->pf.acc_down, s)) != QUINTRIT_OK) return rc;
+        if ((rc = gemm_launch(mat(l, 6), d->pf.a8_i, n, d->pf.acc_down, s, 0, l + 1 < d->layers ? view(&v_down) : nullptr, st)) != QUINTRIT_OK) return rc;
     }
     return QUINTRIT_OK;
 }
@@ -2277,9 +2296,7 @@ extern "C" int quintrit_b200_decoder_prefill(quintrit_b200_decoder_t* decoder, c
         if ((rc = decoder_prefill(d, pinned.data(), count, pos)) != QUINTRIT_OK) return rc;
         if (logits) QTB_CUDA(cudaMemcpyAsync(logits, d->logits, size_t(d->vocab) * sizeof(float), cudaMemcpyDeviceToHost, d->stream));
         if (out_token) QTB_CUDA(cudaMemcpyAsync(out_token, d->d_token, sizeof(uint32_t), cudaMemcpyDeviceToHost, d->stream));
-        if ((rc = decoder_check_status(d)) != QUINTRIT_OK) return rc;
-        for (int k = 0; k < d->layers * 7; k += 7)  // the batched projections report through their matrices' status words; one per layer is enough to see a time-out
-            if ((rc = gemm_check_status(const_cast<quintrit_b200_matrix*>(d->mats[k]), d->stream)) != QUINTRIT_OK) return rc;
+        if ((rc = decoder_check_status(d)) != QUINTRIT_OK) return rc;  // (the batched projections report a time-out through the same word)
         d->host_pos = pos + static_cast<uint32_t>(count);
         return ok();
     });
@@ -2297,6 +2314,10 @@ struct quintrit_b200_batch {
     std::vector<uint32_t> host_pos;        // tokens cached per sequence
     std::vector<uint32_t> staged;          // host copy of the ids given to an asynchronous copy
     std::vector<void*> allocs;
+    // The launches of a step of n tokens (about 500 for 40 layers) are replayed as one CUDA graph from the third step of that size on: tokens,
+    // sequence list and positions are read from device memory, so the graph of a size serves every step of that size.
+    std::vector<cudaGraphExec_t> graph;    // [n_seq + 1], nullptr until captured
+    std::vector<char> warm;                // a step of that size has run as plain launches (lazy allocations done)
 };
 
 namespace {
@@ -2313,6 +2334,8 @@ void destroy_batch(quintrit_b200_batch* b) {
     int prev = -1;
     cudaGetDevice(&prev);
     cudaSetDevice(b->d->device);
+    for (cudaGraphExec_t g : b->graph)
+        if (g != nullptr) cudaGraphExecDestroy(g);
     for (void* p : b->allocs) cudaFree(p);
     if (prev >= 0) cudaSetDevice(prev);
     b->magic = 0;
@@ -2359,13 +2382,6 @@ int batch_head(quintrit_b200_batch* b, int n) {
     return QUINTRIT_OK;
 }
 
-int batch_gemm_status(quintrit_b200_decoder* d) {
-    int rc;
-    for (int k = 0; k < d->layers * 7; k += 7)
-        if ((rc = gemm_check_status(const_cast<quintrit_b200_matrix*>(d->mats[k]), d->stream)) != QUINTRIT_OK) return rc;
-    return QUINTRIT_OK;
-}
-
 }  // namespace
 
 extern "C" int quintrit_b200_batch_create(quintrit_b200_decoder_t* decoder, uint32_t sequences, quintrit_b200_batch_t** out_batch) {
@@ -2384,6 +2400,8 @@ extern "C" int quintrit_b200_batch_create(quintrit_b200_decoder_t* decoder, uint
         quintrit_b200_batch* b = new quintrit_b200_batch();
         b->magic = kMagicBatch, b->d = d, b->n_seq = static_cast<int>(sequences);
         b->host_pos.assign(sequences, 0);
+        b->graph.assign(sequences + 1, nullptr);
+        b->warm.assign(sequences + 1, 0);
         const size_t n = sequences;
         if ((rc = batch_alloc(b, &b->kc, n * batch_cache_stride(d))) != QUINTRIT_OK || (rc = batch_alloc(b, &b->vc, n * batch_cache_stride(d))) != QUINTRIT_OK ||
             (rc = batch_alloc(b, &b->d_pos, n)) != QUINTRIT_OK || (rc = batch_alloc(b, &b->d_last, n)) != QUINTRIT_OK || (rc = batch_alloc(b, &b->d_slot, n)) != QUINTRIT_OK ||
@@ -2456,7 +2474,6 @@ extern "C" int quintrit_b200_batch_prefill(quintrit_b200_batch_t* batch, uint32_
         if (logits) QTB_CUDA(cudaMemcpyAsync(logits, d->logits, size_t(d->vocab) * sizeof(float), cudaMemcpyDeviceToHost, d->stream));
         if (out_token) QTB_CUDA(cudaMemcpyAsync(out_token, d->d_token, sizeof(uint32_t), cudaMemcpyDeviceToHost, d->stream));
         if ((rc = decoder_check_status(d)) != QUINTRIT_OK) return rc;
-        if ((rc = batch_gemm_status(d)) != QUINTRIT_OK) return rc;
         b->host_pos[sequence] = next;
         return ok();
     });
@@ -2485,16 +2502,15 @@ extern "C" int quintrit_b200_batch_step(quintrit_b200_batch_t* batch, const uint
         if (logits != nullptr && logits_capacity < count * static_cast<size_t>(d->vocab)) return fail(QUINTRIT_ERR_BUFFER_TOO_SMALL, "logits hold %zu values, %zu are needed", logits_capacity, count * static_cast<size_t>(d->vocab));
         DeviceGuard g(d->device);
         cudaStream_t s = d->stream;
-        b->staged.clear();  // the ids of both copies below, complete before the first copy is enqueued
-        if (sequences != nullptr) b->staged.insert(b->staged.end(), sequences, sequences + count);
-        if (tokens != nullptr) b->staged.insert(b->staged.end(), tokens, tokens + count);
-        const uint32_t* slot = nullptr;
-        if (sequences != nullptr) {
-            QTB_CUDA(cudaMemcpyAsync(b->d_slot, b->staged.data(), count * sizeof(uint32_t), cudaMemcpyHostToDevice, s));
-            slot = b->d_slot;
-        }
+        // the ids of both copies below, complete before the first copy is enqueued; the sequence list is always read from device memory (one
+        // graph per step size), so "all sequences in order" is written out
+        b->staged.resize(count * (tokens != nullptr ? 2 : 1));
+        for (size_t z = 0; z < count; ++z) b->staged[z] = sequences != nullptr ? sequences[z] : static_cast<uint32_t>(z);
+        if (tokens != nullptr) std::copy(tokens, tokens + count, b->staged.begin() + count);
+        const uint32_t* slot = b->d_slot;
+        QTB_CUDA(cudaMemcpyAsync(b->d_slot, b->staged.data(), count * sizeof(uint32_t), cudaMemcpyHostToDevice, s));
         if (tokens != nullptr) {
-            QTB_CUDA(cudaMemcpyAsync(d->pf.tokens, b->staged.data() + (sequences != nullptr ? count : 0), count * sizeof(uint32_t), cudaMemcpyHostToDevice, s));
+            QTB_CUDA(cudaMemcpyAsync(d->pf.tokens, b->staged.data() + count, count * sizeof(uint32_t), cudaMemcpyHostToDevice, s));
         } else {
             gather_tokens_kernel<<<(n + 255) / 256, 256, 0, s>>>(d->pf.tokens, b->d_last, slot, n);
             QTB_LAUNCH_CHECK();
@@ -2502,14 +2518,40 @@ extern "C" int quintrit_b200_batch_step(quintrit_b200_batch_t* batch, const uint
         BatchTarget tg;
         tg.kc = b->kc, tg.vc = b->vc, tg.pos = b->d_pos, tg.own = false;
         tg.seq.slot = slot, tg.seq.pos_stride = 1, tg.seq.cache_stride = batch_cache_stride(d);
-        if ((rc = prefill_layers(d, n, tg)) != QUINTRIT_OK) return rc;
-        if ((rc = batch_head(b, n)) != QUINTRIT_OK) return rc;
-        advance_batch_kernel<<<(n + 255) / 256, 256, 0, s>>>(b->d_pos, b->d_last, b->d_chosen, slot, n);
-        QTB_LAUNCH_CHECK();
+        auto enqueue = [&]() -> int {
+            int r = prefill_layers(d, n, tg);
+            if (r == QUINTRIT_OK) r = batch_head(b, n);
+            if (r != QUINTRIT_OK) return r;
+            advance_batch_kernel<<<(n + 255) / 256, 256, 0, s>>>(b->d_pos, b->d_last, b->d_chosen, slot, n);
+            QTB_LAUNCH_CHECK();
+            return QUINTRIT_OK;
+        };
+        if (b->graph[n] != nullptr) {
+            QTB_CUDA(cudaGraphLaunch(b->graph[n], s));
+        } else if (b->warm[n] && std::getenv("QUINTRIT_B200_BATCH_GRAPH_OFF") == nullptr) {
+            cudaGraph_t g = nullptr;
+            QTB_CUDA(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
+            rc = enqueue();
+            const cudaError_t e = cudaStreamEndCapture(s, &g);
+            if (rc != QUINTRIT_OK) {
+                if (g) cudaGraphDestroy(g);
+                return rc;
+            }
+            if (e != cudaSuccess) return cuda_fail(e, "cudaStreamEndCapture(batch step)");
+            const cudaError_t ei = cudaGraphInstantiate(&b->graph[n], g, 0);
+            cudaGraphDestroy(g);
+            if (ei != cudaSuccess) {
+                b->graph[n] = nullptr;
+                return cuda_fail(ei, "cudaGraphInstantiate(batch step)");
+            }
+            QTB_CUDA(cudaGraphLaunch(b->graph[n], s));
+        } else {
+            if ((rc = enqueue()) != QUINTRIT_OK) return rc;
+            b->warm[n] = 1;
+        }
         if (out_tokens) QTB_CUDA(cudaMemcpyAsync(out_tokens, b->d_chosen, count * sizeof(uint32_t), cudaMemcpyDeviceToHost, s));
         if (logits) QTB_CUDA(cudaMemcpyAsync(logits, b->logits, count * d->vocab * sizeof(float), cudaMemcpyDeviceToHost, s));
         if ((rc = decoder_check_status(d)) != QUINTRIT_OK) return rc;
-        if ((rc = batch_gemm_status(d)) != QUINTRIT_OK) return rc;
         for (int z = 0; z < n; ++z) b->host_pos[sequences != nullptr ? sequences[z] : static_cast<uint32_t>(z)] += 1;
         return ok();
     });

@@ -164,6 +164,22 @@ __device__ __forceinline__ size_t seq_cache_offset(const SeqIndex& q, unsigned i
     return q.pos_stride != 0 ? static_cast<size_t>(seq_of(q, z)) * q.cache_stride : 0;
 }
 
+// The int32 sums of a batched projection whose K dimension was split over several blocks: `parts` partial results, part k
+// of token z at base + k * part_stride + z * ld. The kernel that consumes the sums adds the parts (integer addition: any
+// order gives the same sum) instead of a pass of its own that would. parts = 1 describes sums that are already complete.
+struct AccView {
+    const int32_t* base;      // nullptr: the consumer reads its plain pointer instead
+    int parts;
+    size_t part_stride;
+    int ld;
+};
+__device__ __forceinline__ int32_t acc_view_read(const AccView& v, size_t z, int i) {
+    const int32_t* p = v.base + z * v.ld + i;
+    int32_t sum = p[0];
+    for (int k = 1; k < v.parts; ++k) sum += p[static_cast<size_t>(k) * v.part_stride];
+    return sum;
+}
+
 // ---- embedding row: model.rs:308-317 ---------------------------------------------------------------------------------
 // A batch of tokens (prompt ingestion) runs as gridDim.y rows: token[y] -> x[y][hidden].
 __global__ void embed_kernel(const __half* __restrict__ table, const uint32_t* __restrict__ token, int hidden, float* __restrict__ x, bool bf16) {
@@ -197,6 +213,7 @@ struct NormQuantArgs {
     // scale_out + z when b_scale is set. All zero for the single-token launches.
     int b_x, b_acc, b_q, b_scale;
     int b_y16;                // stride of y16_out between tokens
+    AccView v_prev;           // the previous projection's sums as parts (then acc_prev only marks that there is a previous projection)
 };
 
 // x += acc * (ws / s)  (model.rs:85, 202 after layer.rs:143-147), y = rms_norm(x) (ops.rs:62-96), codes = quantise(y)
@@ -231,7 +248,7 @@ __global__ void __launch_bounds__(kRowThreads) norm_quant_kernel(NormQuantArgs a
         float v = a.x[i];
         if (a.acc_prev != nullptr) {
             const float d = a.block_scaled ? reinterpret_cast<const float*>(a.acc_prev)[i]
-                                           : (has_prev ? __fmul_rn(static_cast<float>(a.acc_prev[i]), post) : 0.0f);
+                                           : (has_prev ? __fmul_rn(static_cast<float>(a.v_prev.base != nullptr ? acc_view_read(a.v_prev, blockIdx.z, i) : a.acc_prev[i]), post) : 0.0f);
             v = __fadd_rn(v, d);
             a.x[i] = v;
         }
@@ -269,7 +286,16 @@ struct RopeKvArgs {
     int block_scaled;         // acc holds the F32 results of block-scaled projections: used as they are
     int b_acc, b_q, b_scale;  // batch of tokens: token blockIdx.z reads acc + z * b_acc and act_scale + z, writes q_out + z * b_q
     SeqIndex seq;             // its position and KV cache
+    AccView v_q, v_k, v_v;    // the three projections' sums as parts (v_q.base != nullptr), instead of the stacked acc
 };
+
+// Element idx of the stacked q | k | v sums of token z.
+__device__ __forceinline__ int32_t rope_acc(const RopeKvArgs& a, int idx) {
+    if (a.v_q.base == nullptr) return a.acc[idx];
+    if (idx < a.q_dim) return acc_view_read(a.v_q, blockIdx.z, idx);
+    if (idx < a.q_dim + a.kv_dim) return acc_view_read(a.v_k, blockIdx.z, idx - a.q_dim);
+    return acc_view_read(a.v_v, blockIdx.z, idx - a.q_dim - a.kv_dim);
+}
 
 __global__ void rope_kv_kernel(RopeKvArgs a) {
     if (blockIdx.z != 0) {
@@ -291,7 +317,7 @@ __global__ void rope_kv_kernel(RopeKvArgs a) {
         if (t >= total_pairs) {  // a value element: scale and append
             const int i = t - total_pairs;
             const float v = a.block_scaled ? reinterpret_cast<const float*>(a.acc)[a.q_dim + a.kv_dim + i]
-                                           : (live ? __fmul_rn(static_cast<float>(a.acc[a.q_dim + a.kv_dim + i]), pv) : 0.0f);
+                                           : (live ? __fmul_rn(static_cast<float>(rope_acc(a, a.q_dim + a.kv_dim + i)), pv) : 0.0f);
             a.v_cache[static_cast<size_t>(pos) * a.kv_dim + i] = __float2half_rn(v);
             continue;
         }
@@ -318,8 +344,8 @@ __global__ void rope_kv_kernel(RopeKvArgs a) {
             rot = p < half_pairs;
         }
         const float post = is_q ? pq : pk;
-        float x0 = a.block_scaled ? reinterpret_cast<const float*>(a.acc)[base + i0] : (live ? __fmul_rn(static_cast<float>(a.acc[base + i0]), post) : 0.0f);
-        float x1 = a.block_scaled ? reinterpret_cast<const float*>(a.acc)[base + i1] : (live ? __fmul_rn(static_cast<float>(a.acc[base + i1]), post) : 0.0f);
+        float x0 = a.block_scaled ? reinterpret_cast<const float*>(a.acc)[base + i0] : (live ? __fmul_rn(static_cast<float>(rope_acc(a, base + i0)), post) : 0.0f);
+        float x1 = a.block_scaled ? reinterpret_cast<const float*>(a.acc)[base + i1] : (live ? __fmul_rn(static_cast<float>(rope_acc(a, base + i1)), post) : 0.0f);
         if (rot) {
             const int ci = a.neox ? p : p;
             const float c = cs[2 * ci], sn = cs[2 * ci + 1];
@@ -495,24 +521,44 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(AttnArgs a) {
 // ---- the same attention for all query heads of a KV head at once --------------------------------------------------------
 // Grid (kv_heads, chunks, tokens), 288 threads: the G query heads that share a KV head (grouped-query attention) share one
 // pass over its keys and values. The arithmetic per head is attention_kernel's, operation for operation (the reference's
-// order: attention.rs:402-469); what changes is who does it:
-//  A. a warp takes a position, reads the key row once and forms the G dot products;
+// order: attention.rs:402-469); what changes is who does it and how the rows arrive:
+//  A. a warp takes a position and forms the G dot products from one copy of the key row;
 //  B. warp g turns head g's scores into the running maximum and the factors ms / vs with a warp scan over blocks of 32
 //     positions (the running maximum is a prefix maximum, so the scan gives exactly the sequential values);
-//  C. thread d < head_dim runs the G value chains of coordinate d side by side, reading each value element once, while the
-//     ninth warp runs the G chains of the sums S.
-// Per position the factors vs of the G heads and a bit mask "ms != 1 for head g" sit in one record that phase C reads
-// with a single shared-memory load. Dynamic shared memory: attention_gqa_smem(G, head_dim, context).
+//  C. thread d < head_dim runs the G value chains of coordinate d side by side, while the ninth warp runs the G chains of
+//     the sums S.
+// Key rows (phase A) and value rows (phase C) stream through a ring of three 16-row stages in shared memory filled by
+// asynchronous copies two stages ahead, so a block waits for HBM once, not once per row. Per position the factors vs of
+// the G heads and a bit mask "ms != 1 for head g" sit in one record that phase C reads with a single shared-memory load.
+// Dynamic shared memory: attention_gqa_smem(G, head_dim, context).
 constexpr int kAttnGqaThreads = 288;
+constexpr int kAttnRingRows = 16, kAttnRingStages = 3;
 __host__ __device__ constexpr int attn_gqa_record_words(int g) { return g <= 3 ? 4 : 8; }
 __host__ __device__ constexpr int attn_gqa_chunk_max(int ctx) { return ((ctx + 3) / 4 + 31) / 32 * 32 > 256 ? ((ctx + 3) / 4 + 31) / 32 * 32 : 256; }
 __host__ __device__ constexpr size_t attention_gqa_smem(int g, int head_dim, int ctx) {
-    return static_cast<size_t>(attn_gqa_chunk_max(ctx)) * (attn_gqa_record_words(g) + g) * 4 + static_cast<size_t>(g) * head_dim * 4 + 64;
+    return static_cast<size_t>(kAttnRingStages) * kAttnRingRows * head_dim * 2 + static_cast<size_t>(attn_gqa_chunk_max(ctx)) * (attn_gqa_record_words(g) + g) * 4 +
+           static_cast<size_t>(g) * head_dim * 4 + 64;
 }
 
 template <bool F32>
 __device__ __forceinline__ float value_round(float x) {  // the accumulator is an F16 after every operation (bitnet.cpp numerics) or stays F32
     return F32 ? x : __half2float(__float2half_rn(x));
+}
+
+__device__ __forceinline__ void attn_cp16(void* smem_dst, const void* gsrc) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst))), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void attn_cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void attn_cp_wait_all_but_one() { asm volatile("cp.async.wait_group 1;" ::: "memory"); }
+
+// Requests rows row0 .. row0 + 15 (those below len) of a chunk into a stage; always closes a copy group, so every thread counts the same groups.
+__device__ __forceinline__ void attn_ring_issue(__half* stage, const __half* rows, int row0, int len, int hd, int kv_dim, int tid) {
+    const int pieces = hd >> 3, n = min(kAttnRingRows, len - row0) * pieces;  // 16-byte pieces
+    for (int i = tid; i < n; i += kAttnGqaThreads) {
+        const int r = i / pieces, c = i - r * pieces;
+        attn_cp16(stage + r * hd + c * 8, rows + static_cast<size_t>(row0 + r) * kv_dim + c * 8);
+    }
+    attn_cp_commit();
 }
 
 template <int G, bool F32>
@@ -521,10 +567,12 @@ __global__ void __launch_bounds__(kAttnGqaThreads) attention_gqa_kernel(AttnArgs
     extern __shared__ __align__(16) unsigned char gqa_smem[];
     const int kvh = blockIdx.x, c = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int hd = a.head_dim, cmax = attn_gqa_chunk_max(a.ctx);
-    float* s_rec = reinterpret_cast<float*>(gqa_smem);        // [cmax][W]: vs of head g at word g, the mask at word W - 1
+    __half* s_ring = reinterpret_cast<__half*>(gqa_smem);                                        // [3][16][hd]
+    float* s_rec = reinterpret_cast<float*>(gqa_smem + static_cast<size_t>(kAttnRingStages) * kAttnRingRows * hd * 2);  // [cmax][W]: vs of head g at word g, the mask at word W - 1
     float* s_ms = s_rec + static_cast<size_t>(cmax) * W;       // [G][cmax]: scores, then ms
     float* s_q = s_ms + static_cast<size_t>(G) * cmax;         // [G][hd]
     float* s_M = s_q + static_cast<size_t>(G) * hd;            // [G]: the chunk's maximum per head
+    const int stage_halves = kAttnRingRows * hd;
     if (blockIdx.z != 0) {
         const size_t z = blockIdx.z;
         a.q += z * a.b_q;
@@ -555,14 +603,19 @@ __global__ void __launch_bounds__(kAttnGqaThreads) attention_gqa_kernel(AttnArgs
         }
         return;
     }
+    const __half* kbase = a.k_cache + static_cast<size_t>(kvh) * hd + static_cast<size_t>(start) * a.kv_dim;
+    const __half* vbase = a.v_cache + static_cast<size_t>(kvh) * hd + static_cast<size_t>(start) * a.kv_dim;
+    const int nblk = (len + kAttnRingRows - 1) / kAttnRingRows;
+    attn_ring_issue(s_ring, kbase, 0, len, hd, a.kv_dim, tid);
+    attn_ring_issue(s_ring + stage_halves, kbase, kAttnRingRows, len, hd, a.kv_dim, tid);
     for (int i = tid; i < G * hd; i += kAttnGqaThreads) {
         const float qv = a.q[h0 * hd + i];
         s_q[i] = F32 ? qv : __half2float(__float2half_rn(qv));
     }
+    for (int i = tid; i < len; i += kAttnGqaThreads) reinterpret_cast<uint32_t*>(s_rec)[static_cast<size_t>(i) * W + W - 1] = 0u;
     __syncthreads();
-    const __half* kbase = a.k_cache + static_cast<size_t>(kvh) * hd + static_cast<size_t>(start) * a.kv_dim;
-    const __half* vbase = a.v_cache + static_cast<size_t>(kvh) * hd + static_cast<size_t>(start) * a.kv_dim;
-    // Phase A: lane l owns the elements 32 i + l of a row, added in the order of i (ggml_vec_dot_f16 / _f16_f32), then the lanes are reduced
+    // Phase A: lane l owns the elements 32 i + l of a row, added in the order of i (ggml_vec_dot_f16 / _f16_f32), then the lanes are reduced.
+    // Warps 0-7 take two rows of a stage each.
     {
         const int nq = hd >> 5;  // <= 8
         float qr[G][8];
@@ -570,46 +623,46 @@ __global__ void __launch_bounds__(kAttnGqaThreads) attention_gqa_kernel(AttnArgs
         for (int g = 0; g < G; ++g)
 #pragma unroll
             for (int i = 0; i < 8; ++i) qr[g][i] = i < nq ? s_q[g * hd + i * 32 + lane] : 0.0f;
-        constexpr int kWarps = kAttnGqaThreads / 32;
-        for (int p = warp; p < len; p += 2 * kWarps) {
-            const int p2 = p + kWarps;
-            const bool two = p2 < len;
-            const __half* k1 = kbase + static_cast<size_t>(p) * a.kv_dim + lane;
-            const __half* k2 = kbase + static_cast<size_t>(two ? p2 : p) * a.kv_dim + lane;
-            float x1[8], x2[8];
+        for (int blk = 0; blk < nblk; ++blk) {
+            attn_cp_wait_all_but_one();
+            __syncthreads();
+            attn_ring_issue(s_ring + ((blk + 2) % kAttnRingStages) * stage_halves, kbase, (blk + 2) * kAttnRingRows, len, hd, a.kv_dim, tid);
+            const __half* st = s_ring + (blk % kAttnRingStages) * stage_halves;
+            const int r1 = 2 * warp, r2 = r1 + 1, p1 = blk * kAttnRingRows + r1, p2 = p1 + 1;
+            if (warp < 8 && p1 < len) {
+                const bool two = p2 < len;
+                const __half* k1 = st + r1 * hd + lane;
+                const __half* k2 = st + (two ? r2 : r1) * hd + lane;
+                float acc1[G], acc2[G];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                x1[i] = i < nq ? __half2float(k1[i * 32]) : 0.0f;
-                x2[i] = i < nq ? __half2float(k2[i * 32]) : 0.0f;
-            }
-            float acc1[G], acc2[G];
+                for (int g = 0; g < G; ++g) acc1[g] = 0.0f, acc2[g] = 0.0f;
 #pragma unroll
-            for (int g = 0; g < G; ++g) acc1[g] = 0.0f, acc2[g] = 0.0f;
+                for (int i = 0; i < 8; ++i) {
+                    if (i < nq) {
+                        const float x1 = __half2float(k1[i * 32]), x2 = __half2float(k2[i * 32]);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                if (i < nq) {
-#pragma unroll
-                    for (int g = 0; g < G; ++g) {
-                        acc1[g] = __fmaf_rn(x1[i], qr[g][i], acc1[g]);
-                        acc2[g] = __fmaf_rn(x2[i], qr[g][i], acc2[g]);
+                        for (int g = 0; g < G; ++g) {
+                            acc1[g] = __fmaf_rn(x1, qr[g][i], acc1[g]);
+                            acc2[g] = __fmaf_rn(x2, qr[g][i], acc2[g]);
+                        }
                     }
                 }
-            }
 #pragma unroll
-            for (int g = 0; g < G; ++g) {
-                const float sc1 = F32 ? dot_lane_reduce_f16_f32(acc1[g]) : dot_lane_reduce_f16(acc1[g]);
-                const float sc2 = F32 ? dot_lane_reduce_f16_f32(acc2[g]) : dot_lane_reduce_f16(acc2[g]);
-                if (lane == 0) {
-                    s_ms[g * cmax + p] = __fmul_rn(sc1, a.scale);
-                    if (two) s_ms[g * cmax + p2] = __fmul_rn(sc2, a.scale);
+                for (int g = 0; g < G; ++g) {
+                    const float sc1 = F32 ? dot_lane_reduce_f16_f32(acc1[g]) : dot_lane_reduce_f16(acc1[g]);
+                    const float sc2 = F32 ? dot_lane_reduce_f16_f32(acc2[g]) : dot_lane_reduce_f16(acc2[g]);
+                    if (lane == 0) {
+                        s_ms[g * cmax + p1] = __fmul_rn(sc1, a.scale);
+                        if (two) s_ms[g * cmax + p2] = __fmul_rn(sc2, a.scale);
+                    }
                 }
             }
         }
     }
-    __syncthreads();
+    __syncthreads();  // every score is written, every key stage is read
+    attn_ring_issue(s_ring, vbase, 0, len, hd, a.kv_dim, tid);  // the first value rows arrive while phase B runs
+    attn_ring_issue(s_ring + stage_halves, vbase, kAttnRingRows, len, hd, a.kv_dim, tid);
     // Phase B: warp g, head g
-    for (int i = tid; i < len; i += kAttnGqaThreads) reinterpret_cast<uint32_t*>(s_rec)[static_cast<size_t>(i) * W + W - 1] = 0u;
-    __syncthreads();
     if (warp < G) {
         const int g = warp;
         float* sc_g = s_ms + g * cmax;
@@ -641,55 +694,55 @@ __global__ void __launch_bounds__(kAttnGqaThreads) attention_gqa_kernel(AttnArgs
         }
         if (lane == 0) s_M[g] = carry;
     }
-    __syncthreads();
-    // Phase C
-    if (warp == kAttnGqaThreads / 32 - 1) {  // the sums: S = fma(S, ms, vs) in position order (attention.rs:466)
-        if (lane < G) {
+    // Phase C: threads below head_dim run the value chains of their coordinate, lanes below G of the last warp the sums
+    // S = fma(S, ms, vs) (attention.rs:466), stage by stage in position order.
+    const bool sum_lane = warp == kAttnGqaThreads / 32 - 1 && lane < G;
+    const bool chain_thread = warp < kAttnGqaThreads / 32 - 1 && tid < hd;
+    float acc[G];
+#pragma unroll
+    for (int g = 0; g < G; ++g) acc[g] = 0.0f;
+    float S = 0.0f;
+    for (int blk = 0; blk < nblk; ++blk) {
+        attn_cp_wait_all_but_one();
+        __syncthreads();  // (the first one also publishes phase B's records)
+        attn_ring_issue(s_ring + ((blk + 2) % kAttnRingStages) * stage_halves, vbase, (blk + 2) * kAttnRingRows, len, hd, a.kv_dim, tid);
+        const int p0 = blk * kAttnRingRows, rows = min(kAttnRingRows, len - p0);
+        if (chain_thread) {
+            const __half* st = s_ring + (blk % kAttnRingStages) * stage_halves + tid;
+#pragma unroll 4
+            for (int r = 0; r < rows; ++r) {
+                const int p = p0 + r;
+                float rec[W];
+                if constexpr (W == 4) {
+                    const float4 q4 = *reinterpret_cast<const float4*>(s_rec + static_cast<size_t>(p) * 4);
+                    rec[0] = q4.x, rec[1] = q4.y, rec[2] = q4.z, rec[3] = q4.w;
+                } else {
+                    const float4 q0 = *reinterpret_cast<const float4*>(s_rec + static_cast<size_t>(p) * 8);
+                    const float4 q1 = *reinterpret_cast<const float4*>(s_rec + static_cast<size_t>(p) * 8 + 4);
+                    rec[0] = q0.x, rec[1] = q0.y, rec[2] = q0.z, rec[3] = q0.w, rec[4] = q1.x, rec[5] = q1.y, rec[6] = q1.z, rec[7] = q1.w;
+                }
+                const unsigned int mask = __float_as_uint(rec[W - 1]);
+                if (mask != 0u) {
+#pragma unroll
+                    for (int g = 0; g < G; ++g)
+                        if ((mask >> g) & 1u) acc[g] = value_round<F32>(__fmul_rn(acc[g], s_ms[g * cmax + p]));
+                }
+                const float vf = __half2float(st[r * hd]);
+#pragma unroll
+                for (int g = 0; g < G; ++g) acc[g] = value_round<F32>(__fmaf_rn(vf, rec[g], acc[g]));
+            }
+        } else if (sum_lane) {
             const float* ms_g = s_ms + lane * cmax;
-            float S = 0.0f;
-            for (int p = 0; p < len; ++p) S = __fmaf_rn(S, ms_g[p], s_rec[static_cast<size_t>(p) * W + lane]);
-            float* my_ms = a.part_ms + (static_cast<size_t>(h0 + lane) * 4 + c) * 2;
-            my_ms[0] = s_M[lane];
-            my_ms[1] = S;
+            for (int r = 0; r < rows; ++r) S = __fmaf_rn(S, ms_g[p0 + r], s_rec[static_cast<size_t>(p0 + r) * W + lane]);
         }
-        return;
     }
-    for (int d = tid; d < hd; d += kAttnGqaThreads - 32) {
-        const __half* vr = vbase + d;
-        float acc[G];
+    if (chain_thread) {
 #pragma unroll
-        for (int g = 0; g < G; ++g) acc[g] = 0.0f;
-        auto step = [&](int p, __half vh) {
-            float rec[W];
-            if constexpr (W == 4) {
-                const float4 r = *reinterpret_cast<const float4*>(s_rec + static_cast<size_t>(p) * 4);
-                rec[0] = r.x, rec[1] = r.y, rec[2] = r.z, rec[3] = r.w;
-            } else {
-                const float4 r0 = *reinterpret_cast<const float4*>(s_rec + static_cast<size_t>(p) * 8);
-                const float4 r1 = *reinterpret_cast<const float4*>(s_rec + static_cast<size_t>(p) * 8 + 4);
-                rec[0] = r0.x, rec[1] = r0.y, rec[2] = r0.z, rec[3] = r0.w, rec[4] = r1.x, rec[5] = r1.y, rec[6] = r1.z, rec[7] = r1.w;
-            }
-            const unsigned int mask = __float_as_uint(rec[W - 1]);
-            if (mask != 0u) {
-#pragma unroll
-                for (int g = 0; g < G; ++g)
-                    if ((mask >> g) & 1u) acc[g] = value_round<F32>(__fmul_rn(acc[g], s_ms[g * cmax + p]));
-            }
-            const float vf = __half2float(vh);
-#pragma unroll
-            for (int g = 0; g < G; ++g) acc[g] = value_round<F32>(__fmaf_rn(vf, rec[g], acc[g]));
-        };
-        int p = 0;
-        for (; p + 8 <= len; p += 8) {
-            __half v8[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) v8[j] = vr[static_cast<size_t>(p + j) * a.kv_dim];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) step(p + j, v8[j]);
-        }
-        for (; p < len; ++p) step(p, vr[static_cast<size_t>(p) * a.kv_dim]);
-#pragma unroll
-        for (int g = 0; g < G; ++g) a.part_acc[(static_cast<size_t>(h0 + g) * 4 + c) * hd + d] = acc[g];
+        for (int g = 0; g < G; ++g) a.part_acc[(static_cast<size_t>(h0 + g) * 4 + c) * hd + tid] = acc[g];
+    } else if (sum_lane) {
+        float* my_ms = a.part_ms + (static_cast<size_t>(h0 + lane) * 4 + c) * 2;
+        my_ms[0] = s_M[lane];
+        my_ms[1] = S;
     }
 }
 
@@ -796,6 +849,7 @@ struct ActQuantArgs {
     int block_scaled;         // acc_gate / acc_up hold F32 results of block-scaled projections; codes are Q8_0 blocks
     float* q8_d;
     int b_acc, b_q, b_scale;  // batch of tokens: per-token strides of acc_gate / acc_up and of q_out; act_scale + z and scale_out + z when b_scale is set
+    AccView v_gate, v_up;     // the two projections' sums as parts (v_gate.base != nullptr), instead of acc_gate / acc_up
 };
 
 __global__ void __launch_bounds__(kRowThreads) act_quant_kernel(ActQuantArgs a) {
@@ -818,8 +872,8 @@ __global__ void __launch_bounds__(kRowThreads) act_quant_kernel(ActQuantArgs a) 
     const bool live = s_in > 0.0f;
     const float pg = live ? __fdiv_rn(a.ws_gate, s_in) : 0.0f, pu = live ? __fdiv_rn(a.ws_up, s_in) : 0.0f;
     for (int i = tid; i < a.n; i += kRowThreads) {
-        const float g = a.block_scaled ? reinterpret_cast<const float*>(a.acc_gate)[i] : (live ? __fmul_rn(static_cast<float>(a.acc_gate[i]), pg) : 0.0f);
-        const float u = a.block_scaled ? reinterpret_cast<const float*>(a.acc_up)[i] : (live ? __fmul_rn(static_cast<float>(a.acc_up[i]), pu) : 0.0f);
+        const float g = a.block_scaled ? reinterpret_cast<const float*>(a.acc_gate)[i] : (live ? __fmul_rn(static_cast<float>(a.v_gate.base != nullptr ? acc_view_read(a.v_gate, blockIdx.z, i) : a.acc_gate[i]), pg) : 0.0f);
+        const float u = a.block_scaled ? reinterpret_cast<const float*>(a.acc_up)[i] : (live ? __fmul_rn(static_cast<float>(a.v_up.base != nullptr ? acc_view_read(a.v_up, blockIdx.z, i) : a.acc_up[i]), pu) : 0.0f);
         float v;
         if (a.relu2) {
             const float p = g > 0.0f ? g : 0.0f;
