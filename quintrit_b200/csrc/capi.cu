@@ -46,6 +46,13 @@ struct quintrit_b200_matrix {
     int32_t* d_gemm_parts = nullptr;  // partial sums of a projection whose K is split: kGemmMaxParts x kGemmMaxN x rows
 };
 
+void qtb_release_stacked(quintrit_b200_matrix* m) {
+    if (m != nullptr) {
+        m->magic = 0;
+        delete m;
+    }
+}
+
 struct quintrit_b200_plan {
     uint32_t magic;
     int device;
@@ -1002,6 +1009,7 @@ int decoder_create_impl(const quintrit_b200_decoder_desc_t* desc, quintrit_b200_
         if (kq != nullptr && bytes + 1024 <= static_cast<size_t>(smem_optin)) {
             if ((rc = allow_max_dynamic_smem(kq, smem_optin)) != QUINTRIT_OK) return rc;
             d->attn_gqa = kq, d->attn_gqa_smem = bytes;
+            if (const char* pad = std::getenv("QUINTRIT_B200_ATTN_SMEM_PAD")) d->attn_gqa_pad = std::min<size_t>(static_cast<size_t>(std::atoi(pad)), smem_optin - 1024 - bytes);
         }
     }
     d->use_mega = false;
@@ -1937,7 +1945,7 @@ int gemm_prepare(quintrit_b200_matrix* m) {
     uint8_t* w = nullptr;
     QTB_CUDA(cudaMalloc(&w, gblocks * rows_padded * 32));
     const size_t bytes = gblocks * rows_padded * 32;
-    stream_to_two_bit_kernel<<<static_cast<int>(std::min<size_t>((bytes + 255) / 256, 148 * 32)), 256>>>(m->d_w, w, m->rows, m->cols, rows_padded, gblocks, m->blocks, m->tiles);
+    stream_to_two_bit_kernel<<<static_cast<int>(std::min<size_t>((bytes + 255) / 256, 148 * 32)), 256>>>(m->d_w, w, m->rows, m->cols, rows_padded, gblocks, m->blocks, m->tiles, 0, rows_padded);
     ++g_launches;
     cudaError_t e = cudaGetLastError();
     if (e == cudaSuccess) e = cudaMalloc(&m->d_gemm_act, size_t(kGemmMaxN) * k_pad);
@@ -1958,7 +1966,9 @@ int gemm_prepare(quintrit_b200_matrix* m) {
 // With `defer`, a product whose K dimension is split leaves its parts where they are and describes them in *defer for the kernel that consumes the
 // sums (which adds them); otherwise a second kernel adds the parts into d_out.
 // `status` is the word a time-out is reported in: the matrix's own by default, a decoder's for the launches a decoder makes (one read-back per call).
-int gemm_launch(quintrit_b200_matrix* m, const int8_t* d_act, int batch, int32_t* d_out, cudaStream_t stream, int ldo = 0, AccView* defer = nullptr, unsigned int* status = nullptr) {
+// `parts` is the buffer for the partial sums of a split K dimension (kGemmMaxParts x kGemmMaxN x rows values): the matrix's own, made on first need, by default.
+int gemm_launch(quintrit_b200_matrix* m, const int8_t* d_act, int batch, int32_t* d_out, cudaStream_t stream, int ldo = 0, AccView* defer = nullptr, unsigned int* status = nullptr,
+                int32_t* parts = nullptr) {
     if (ldo == 0) ldo = static_cast<int>(m->rows);
     if (defer != nullptr) *defer = AccView{d_out, 1, 0, ldo};
     TensorMapEncodeFn encode = nullptr;
@@ -2008,19 +2018,22 @@ int gemm_launch(quintrit_b200_matrix* m, const int8_t* d_act, int batch, int32_t
     a.blocks_per_cta = (a.blocks + ksplit - 1) / ksplit;
     ksplit = (a.blocks + a.blocks_per_cta - 1) / a.blocks_per_cta;
     if (ksplit > 1) {
-        if (m->d_gemm_parts == nullptr) {
-            std::lock_guard<std::mutex> hold(g_gemm_lock);
-            if (m->d_gemm_parts == nullptr) QTB_CUDA(cudaMalloc(&m->d_gemm_parts, size_t(kGemmMaxParts) * kGemmMaxN * m->rows * sizeof(int32_t)));
+        if (parts == nullptr) {
+            if (m->d_gemm_parts == nullptr) {
+                std::lock_guard<std::mutex> hold(g_gemm_lock);
+                if (m->d_gemm_parts == nullptr) QTB_CUDA(cudaMalloc(&m->d_gemm_parts, size_t(kGemmMaxParts) * kGemmMaxN * m->rows * sizeof(int32_t)));
+            }
+            parts = m->d_gemm_parts;
         }
-        a.out = m->d_gemm_parts, a.ldo = static_cast<int>(m->rows);
+        a.out = parts, a.ldo = static_cast<int>(m->rows);
     }
     gemm_i8_tcgen05_kernel<<<std::min(m_tiles * ksplit, m->sm_count), kGemmThreads, gemm_smem_bytes(n, a.stages), stream>>>(map, a);
     ++g_launches;
     if (ksplit > 1 && defer != nullptr) {
-        *defer = AccView{m->d_gemm_parts, ksplit, size_t(batch) * m->rows, static_cast<int>(m->rows)};
+        *defer = AccView{parts, ksplit, size_t(batch) * m->rows, static_cast<int>(m->rows)};
     } else if (ksplit > 1) {
         const size_t count = size_t(batch) * m->rows;
-        gemm_reduce_parts_kernel<<<static_cast<int>(std::min<size_t>((count + 255) / 256, size_t(m->sm_count) * 8)), 256, 0, stream>>>(m->d_gemm_parts, d_out, count, ksplit, static_cast<int>(m->rows), ldo);
+        gemm_reduce_parts_kernel<<<static_cast<int>(std::min<size_t>((count + 255) / 256, size_t(m->sm_count) * 8)), 256, 0, stream>>>(parts, d_out, count, ksplit, static_cast<int>(m->rows), ldo);
         ++g_launches;
     }
     const cudaError_t e = cudaGetLastError();
@@ -2097,6 +2110,74 @@ namespace {
 
 constexpr int kPrefillMax = kGemmMaxN;
 
+// The batched products of a decoder: q | k | v and gate | up of a layer are stacked row-wise into one matrix each where their row counts are whole
+// tiles (one launch instead of three or two, and no launch too small to fill the device); o and down keep their own two-bit copies. The partial
+// sums of split products go to four buffers of the decoder, one per kind of product, shared by all layers.
+int decoder_gemm_prepare(quintrit_b200_decoder* d) {
+    if (d->pf.gemm_ready) return QUINTRIT_OK;
+    auto mat = [&](int l, int k) { return const_cast<quintrit_b200_matrix*>(d->mats[size_t(l) * 7 + k]); };
+    const bool stack_off = std::getenv("QUINTRIT_B200_GEMM_STACK_OFF") != nullptr;
+    int rc;
+    d->pf.stack.assign(size_t(d->layers) * 2, nullptr);
+    auto stack = [&](int l, int first, int count, quintrit_b200_matrix** out) -> int {
+        size_t rows = 0;
+        for (int k = first; k < first + count; ++k) {
+            const quintrit_b200_matrix* m = mat(l, k);
+            if (m->rows % kGemmM != 0 || m->cols != mat(l, first)->cols || m->block_scaled) return QUINTRIT_OK;  // not stackable: separate launches
+            rows += m->rows;
+        }
+        const quintrit_b200_matrix* m0 = mat(l, first);
+        const size_t gblocks = (m0->cols + kGemmBlockCols - 1) / kGemmBlockCols;
+        uint8_t* w = nullptr;
+        int r = dev_alloc(d, &w, gblocks * rows * 32, false);
+        if (r != QUINTRIT_OK) return r;
+        size_t off = 0;
+        for (int k = first; k < first + count; ++k) {
+            const quintrit_b200_matrix* m = mat(l, k);
+            const size_t bytes = gblocks * m->rows * 32;
+            stream_to_two_bit_kernel<<<static_cast<int>(std::min<size_t>((bytes + 255) / 256, 148 * 32)), 256>>>(m->d_w, w, m->rows, m->cols, m->rows, gblocks, m->blocks, m->tiles, off, rows);
+            ++g_launches;
+            off += m->rows;
+        }
+        QTB_CUDA(cudaGetLastError());
+        quintrit_b200_matrix* sm = new quintrit_b200_matrix();
+        sm->magic = kMagicMatrix, sm->device = d->device, sm->sm_count = d->sm_count;
+        sm->rows = rows, sm->cols = m0->cols, sm->blocks = m0->blocks, sm->tiles = 0;
+        sm->d_w = nullptr, sm->w_bytes = 0, sm->d_items = nullptr, sm->n_items = 0, sm->d_counters = nullptr, sm->d_act = nullptr, sm->d_out = nullptr, sm->d_outf = nullptr;
+        sm->d_gemm_w = w, sm->gemm_rows_padded = rows;
+        d->pf.stacked_objects.push_back(sm);
+        *out = sm;
+        return QUINTRIT_OK;
+    };
+    size_t rows_kind[4] = {0, 0, 0, 0};  // qkv, o, gate|up, down
+    for (int l = 0; l < d->layers; ++l) {
+        quintrit_b200_matrix *sq = nullptr, *sg = nullptr;
+        if (!stack_off && ((rc = stack(l, 0, 3, &sq)) != QUINTRIT_OK || (rc = stack(l, 4, 2, &sg)) != QUINTRIT_OK)) return rc;
+        d->pf.stack[size_t(l) * 2] = sq, d->pf.stack[size_t(l) * 2 + 1] = sg;
+        for (int k = 0; k < 7; ++k) {
+            const bool stacked = (k < 3 && sq != nullptr) || ((k == 4 || k == 5) && sg != nullptr);
+            if (!stacked && (rc = gemm_prepare(mat(l, k))) != QUINTRIT_OK) return rc;
+        }
+        rows_kind[0] = std::max(rows_kind[0], sq != nullptr ? sq->rows : std::max({mat(l, 0)->rows, mat(l, 1)->rows, mat(l, 2)->rows}));
+        rows_kind[1] = std::max(rows_kind[1], mat(l, 3)->rows);
+        rows_kind[2] = std::max(rows_kind[2], sg != nullptr ? sg->rows : std::max(mat(l, 4)->rows, mat(l, 5)->rows));
+        rows_kind[3] = std::max(rows_kind[3], mat(l, 6)->rows);
+    }
+    // one buffer per product that can be in flight with deferred parts at the same time: q, k, v (or the stack), o, gate, up (or the stack), down
+    for (int k = 0; k < 7; ++k) {
+        const int kind = k < 3 ? 0 : k == 3 ? 1 : k < 6 ? 2 : 3;
+        const bool second_of_stack = (k == 1 || k == 2 || k == 5);
+        bool all_stacked = true;
+        for (int l = 0; l < d->layers; ++l) all_stacked = all_stacked && d->pf.stack[size_t(l) * 2 + (kind == 0 ? 0 : 1)] != nullptr;
+        if (second_of_stack && all_stacked && (kind == 0 || kind == 2)) continue;  // the stack's one buffer is parts[first of the kind]
+        if ((rc = dev_alloc(d, &d->pf.parts[k], size_t(kGemmMaxParts) * kGemmMaxN * rows_kind[kind], false)) != QUINTRIT_OK) return rc;
+    }
+    QTB_CUDA(cudaFuncSetAttribute(gemm_i8_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kGemmSmemLimit)));
+    QTB_CUDA(cudaDeviceSynchronize());
+    d->pf.gemm_ready = true;
+    return QUINTRIT_OK;
+}
+
 int prefill_buffers(quintrit_b200_decoder* d) {
     if (d->pf.x != nullptr) return QUINTRIT_OK;
     const size_t B = kPrefillMax, H = d->hidden, I = d->inter, qd = d->q_dim, kvd = d->kv_dim, hd = d->head_dim;
@@ -2152,17 +2233,23 @@ int prefill_layers(quintrit_b200_decoder* d, int n, const BatchTarget& tg) {
         if (l > 0) n1.v_prev = v_down;
         norm_quant_kernel<<<dim3(1, 1, n), kRowThreads, H * sizeof(float), s>>>(n1);
         QTB_LAUNCH_CHECK();
-        if ((rc = gemm_launch(mat(l, 0), d->pf.a8_h, n, d->pf.acc_qkv, s, qkv, view(&v_q), st)) != QUINTRIT_OK ||
-            (rc = gemm_launch(mat(l, 1), d->pf.a8_h, n, d->pf.acc_qkv + qd, s, qkv, view(&v_k), st)) != QUINTRIT_OK ||
-            (rc = gemm_launch(mat(l, 2), d->pf.a8_h, n, d->pf.acc_qkv + qd + kvd, s, qkv, view(&v_v), st)) != QUINTRIT_OK)
+        if (quintrit_b200_matrix* sq = d->pf.stack[size_t(l) * 2]) {  // q | k | v as one product
+            if ((rc = gemm_launch(sq, d->pf.a8_h, n, d->pf.acc_qkv, s, qkv, &v_q, st, d->pf.parts[0])) != QUINTRIT_OK) return rc;
+            v_k = v_q, v_k.base += qd;
+            v_v = v_q, v_v.base += qd + kvd;
+        } else if ((rc = gemm_launch(mat(l, 0), d->pf.a8_h, n, d->pf.acc_qkv, s, qkv, view(&v_q), st, d->pf.parts[0])) != QUINTRIT_OK ||
+                   (rc = gemm_launch(mat(l, 1), d->pf.a8_h, n, d->pf.acc_qkv + qd, s, qkv, view(&v_k), st, d->pf.parts[1])) != QUINTRIT_OK ||
+                   (rc = gemm_launch(mat(l, 2), d->pf.a8_h, n, d->pf.acc_qkv + qd + kvd, s, qkv, view(&v_v), st, d->pf.parts[2])) != QUINTRIT_OK) {
             return rc;
+        }
+        const bool qkv_views = defer || d->pf.stack[size_t(l) * 2] != nullptr;
         RopeKvArgs rk{};
         rk.acc = d->pf.acc_qkv, rk.b_acc = qkv, rk.act_scale = d->pf.s_h, rk.b_scale = 1;
         rk.ws_q = sc[0], rk.ws_k = sc[1], rk.ws_v = sc[2];
         rk.cos_sin = d->cos_sin, rk.pos = tg.pos, rk.seq = tg.seq;
         rk.q_dim = qd, rk.kv_dim = kvd, rk.head_dim = hd, rk.rope_dims = d->rope_dims, rk.neox = d->arch == QUINTRIT_B200_ARCH_BITNET;
         rk.q_out = d->pf.q, rk.b_q = qd;
-        if (defer) rk.v_q = v_q, rk.v_k = v_k, rk.v_v = v_v;
+        if (qkv_views) rk.v_q = v_q, rk.v_k = v_k, rk.v_v = v_v;
         rk.k_cache = tg.kc + static_cast<size_t>(l) * d->ctx * kvd;
         rk.v_cache = tg.vc + static_cast<size_t>(l) * d->ctx * kvd;
         rope_kv_kernel<<<dim3(((qd + kvd) / 2 + kvd + 255) / 256, 1, n), 256, 0, s>>>(rk);
@@ -2182,7 +2269,7 @@ int prefill_layers(quintrit_b200_decoder* d, int n, const BatchTarget& tg) {
         af.q_out = d->pf.a8_q, af.b_q = qd, af.scale_out = d->pf.s_q, af.b_scale = 1;
         attn_finish_kernel<<<dim3(1, 1, n), kRowThreads, qd * sizeof(float), s>>>(af);
         QTB_LAUNCH_CHECK();
-        if ((rc = gemm_launch(mat(l, 3), d->pf.a8_q, n, d->pf.acc_o, s, 0, view(&v_o), st)) != QUINTRIT_OK) return rc;
+        if ((rc = gemm_launch(mat(l, 3), d->pf.a8_q, n, d->pf.acc_o, s, 0, view(&v_o), st, d->pf.parts[3])) != QUINTRIT_OK) return rc;
         NormQuantArgs n2{};
         n2.x = d->pf.x, n2.b_x = H, n2.acc_prev = d->pf.acc_o, n2.b_acc = H, n2.scale_prev = d->pf.s_q, n2.ws_prev = sc[3];
         n2.norm_w = d->norms[l * 4 + 1], n2.eps = d->eps, n2.n = H;
@@ -2190,19 +2277,27 @@ int prefill_layers(quintrit_b200_decoder* d, int n, const BatchTarget& tg) {
         if (defer) n2.v_prev = v_o;
         norm_quant_kernel<<<dim3(1, 1, n), kRowThreads, H * sizeof(float), s>>>(n2);
         QTB_LAUNCH_CHECK();
-        if ((rc = gemm_launch(mat(l, 4), d->pf.a8_h, n, d->pf.acc_gu, s, 2 * I, view(&v_gate), st)) != QUINTRIT_OK ||
-            (rc = gemm_launch(mat(l, 5), d->pf.a8_h, n, d->pf.acc_gu + I, s, 2 * I, view(&v_up), st)) != QUINTRIT_OK)
+        if (quintrit_b200_matrix* sg = d->pf.stack[size_t(l) * 2 + 1]) {  // gate | up as one product
+            if ((rc = gemm_launch(sg, d->pf.a8_h, n, d->pf.acc_gu, s, 2 * I, &v_gate, st, d->pf.parts[4])) != QUINTRIT_OK) return rc;
+            v_up = v_gate, v_up.base += I;
+        } else if ((rc = gemm_launch(mat(l, 4), d->pf.a8_h, n, d->pf.acc_gu, s, 2 * I, view(&v_gate), st, d->pf.parts[4])) != QUINTRIT_OK ||
+                   (rc = gemm_launch(mat(l, 5), d->pf.a8_h, n, d->pf.acc_gu + I, s, 2 * I, view(&v_up), st, d->pf.parts[5])) != QUINTRIT_OK) {
             return rc;
+        }
+        const bool gu_views = defer || d->pf.stack[size_t(l) * 2 + 1] != nullptr;
         ActQuantArgs aq{};
         aq.acc_gate = d->pf.acc_gu, aq.acc_up = d->pf.acc_gu + I, aq.b_acc = 2 * I, aq.act_scale = d->pf.s_h, aq.b_scale = 1;
         aq.ws_gate = sc[4], aq.ws_up = sc[5];
         aq.n = I, aq.relu2 = d->arch == QUINTRIT_B200_ARCH_BITNET;
         aq.sub_norm_w = d->norms[l * 4 + 3], aq.eps = d->eps;
         aq.q_out = d->pf.a8_i, aq.b_q = I, aq.scale_out = d->pf.s_i;
-        if (defer) aq.v_gate = v_gate, aq.v_up = v_up;
-        act_quant_kernel<<<dim3(1, 1, n), kRowThreads, I * sizeof(float), s>>>(aq);
+        if (gu_views) aq.v_gate = v_gate, aq.v_up = v_up;
+        if (std::getenv("QUINTRIT_B200_ACT_CLUSTER_OFF") == nullptr)
+            act_quant_cluster_kernel<<<dim3(kActClusterSize, 1, n), kActClusterThreads, act_cluster_slice(I) * sizeof(float), s>>>(aq);
+        else
+            act_quant_kernel<<<dim3(1, 1, n), kRowThreads, I * sizeof(float), s>>>(aq);
         QTB_LAUNCH_CHECK();
-        if ((rc = gemm_launch(mat(l, 6), d->pf.a8_i, n, d->pf.acc_down, s, 0, l + 1 < d->layers ? view(&v_down) : nullptr, st)) != QUINTRIT_OK) return rc;
+        if ((rc = gemm_launch(mat(l, 6), d->pf.a8_i, n, d->pf.acc_down, s, 0, l + 1 < d->layers ? view(&v_down) : nullptr, st, d->pf.parts[6])) != QUINTRIT_OK) return rc;
     }
     return QUINTRIT_OK;
 }
@@ -2259,8 +2354,7 @@ bool prefill_available(const quintrit_b200_decoder* d) { return !d->block_scaled
 int decoder_prefill(quintrit_b200_decoder* d, const uint32_t* tokens, size_t count, uint32_t pos0, const BatchTarget* target = nullptr) {
     int rc = prefill_buffers(d);
     if (rc != QUINTRIT_OK) return rc;
-    for (int k = 0; k < d->layers * 7; ++k)
-        if ((rc = gemm_prepare(const_cast<quintrit_b200_matrix*>(d->mats[k]))) != QUINTRIT_OK) return rc;
+    if ((rc = decoder_gemm_prepare(d)) != QUINTRIT_OK) return rc;
     const BatchTarget tg = target != nullptr ? *target : own_target(d);
     for (size_t c0 = 0; c0 < count; c0 += kPrefillMax) {
         const int n = static_cast<int>(std::min<size_t>(kPrefillMax, count - c0));
@@ -2395,8 +2489,7 @@ extern "C" int quintrit_b200_batch_create(quintrit_b200_decoder_t* decoder, uint
         if (!prefill_available(d)) return fail(QUINTRIT_ERR_UNSUPPORTED, "this decoder has no batched pass (block-scaled or tensor-parallel model)");
         DeviceGuard g(d->device);
         if ((rc = prefill_buffers(d)) != QUINTRIT_OK) return rc;
-        for (int k = 0; k < d->layers * 7; ++k)
-            if ((rc = gemm_prepare(const_cast<quintrit_b200_matrix*>(d->mats[k]))) != QUINTRIT_OK) return rc;
+        if ((rc = decoder_gemm_prepare(d)) != QUINTRIT_OK) return rc;
         quintrit_b200_batch* b = new quintrit_b200_batch();
         b->magic = kMagicBatch, b->d = d, b->n_seq = static_cast<int>(sequences);
         b->host_pos.assign(sequences, 0);
@@ -2504,9 +2597,17 @@ extern "C" int quintrit_b200_batch_step(quintrit_b200_batch_t* batch, const uint
         cudaStream_t s = d->stream;
         // the ids of both copies below, complete before the first copy is enqueued; the sequence list is always read from device memory (one
         // graph per step size), so "all sequences in order" is written out
+        // Inside the step the tokens are ordered by the length of their sequences, longest first: the attention blocks of a launch are handed to the
+        // multiprocessors in order, and with that order every multiprocessor gets long and short ones alike. order[k] = the caller's index z.
+        std::vector<uint32_t> order(count);
+        for (size_t z = 0; z < count; ++z) order[z] = static_cast<uint32_t>(z);
+        auto seq_at = [&](uint32_t z) { return sequences != nullptr ? sequences[z] : z; };
+        std::stable_sort(order.begin(), order.end(), [&](uint32_t x, uint32_t y) { return b->host_pos[seq_at(x)] > b->host_pos[seq_at(y)]; });
         b->staged.resize(count * (tokens != nullptr ? 2 : 1));
-        for (size_t z = 0; z < count; ++z) b->staged[z] = sequences != nullptr ? sequences[z] : static_cast<uint32_t>(z);
-        if (tokens != nullptr) std::copy(tokens, tokens + count, b->staged.begin() + count);
+        for (size_t k = 0; k < count; ++k) {
+            b->staged[k] = seq_at(order[k]);
+            if (tokens != nullptr) b->staged[count + k] = tokens[order[k]];
+        }
         const uint32_t* slot = b->d_slot;
         QTB_CUDA(cudaMemcpyAsync(b->d_slot, b->staged.data(), count * sizeof(uint32_t), cudaMemcpyHostToDevice, s));
         if (tokens != nullptr) {
@@ -2549,9 +2650,14 @@ extern "C" int quintrit_b200_batch_step(quintrit_b200_batch_t* batch, const uint
             if ((rc = enqueue()) != QUINTRIT_OK) return rc;
             b->warm[n] = 1;
         }
-        if (out_tokens) QTB_CUDA(cudaMemcpyAsync(out_tokens, b->d_chosen, count * sizeof(uint32_t), cudaMemcpyDeviceToHost, s));
-        if (logits) QTB_CUDA(cudaMemcpyAsync(logits, b->logits, count * d->vocab * sizeof(float), cudaMemcpyDeviceToHost, s));
-        if ((rc = decoder_check_status(d)) != QUINTRIT_OK) return rc;
+        std::vector<uint32_t> chosen(out_tokens != nullptr ? count : 0);
+        if (out_tokens) QTB_CUDA(cudaMemcpyAsync(chosen.data(), b->d_chosen, count * sizeof(uint32_t), cudaMemcpyDeviceToHost, s));
+        if (logits)
+            for (size_t k = 0; k < count; ++k)
+                QTB_CUDA(cudaMemcpyAsync(logits + size_t(order[k]) * d->vocab, b->logits + k * d->vocab, size_t(d->vocab) * sizeof(float), cudaMemcpyDeviceToHost, s));
+        if ((rc = decoder_check_status(d)) != QUINTRIT_OK) return rc;  // (waits for the stream)
+        if (out_tokens)
+            for (size_t k = 0; k < count; ++k) out_tokens[order[k]] = chosen[k];
         for (int z = 0; z < n; ++z) b->host_pos[sequences != nullptr ? sequences[z] : static_cast<uint32_t>(z)] += 1;
         return ok();
     });

@@ -7,6 +7,7 @@
 // libm's cos/sin/pow through a table built on the host, glibc's expf restated in double (device_expf), F16 rounding
 // after every step of the attention accumulator.
 #pragma once
+#include <cooperative_groups.h>
 #include <cstdint>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -896,6 +897,83 @@ __global__ void __launch_bounds__(kRowThreads) act_quant_kernel(ActQuantArgs a) 
     for (int i = tid; i < a.n; i += kRowThreads) amax = fmaxf(amax, fabsf(y_s[i]));
     __syncthreads();
     quantize_vector(y_s, a.n, amax, a.q_out, a.scale_out, a.block_scaled ? a.q8_d : nullptr, sh_f);
+}
+
+// The same step for the batched paths, one token spread over a cluster of eight blocks: a block computes, normalises and
+// quantises an eighth of the vector; the two block-wide reductions (sum of squares for the sub-norm, maximum for the
+// scale) become cluster-wide by reading the other blocks' partial results through distributed shared memory, in rank
+// order. Grid (8, 1, tokens). Per-tensor int8 codes only (block-scaled models do not take the batched paths).
+constexpr int kActClusterSize = 8, kActClusterThreads = 512;
+__host__ __device__ constexpr int act_cluster_slice(int n) { return (n + kActClusterSize - 1) / kActClusterSize; }
+
+__global__ void __cluster_dims__(kActClusterSize, 1, 1) __launch_bounds__(kActClusterThreads) act_quant_cluster_kernel(ActQuantArgs a) {
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    __shared__ double sh_d[32];
+    __shared__ float sh_f[32];
+    __shared__ double x_sum;
+    __shared__ float x_max;
+    extern __shared__ float y_s[];  // this block's slice
+    const int tid = threadIdx.x, rank = static_cast<int>(cluster.block_rank());
+    if (blockIdx.z != 0) {
+        const size_t z = blockIdx.z;
+        a.acc_gate += z * a.b_acc;
+        a.acc_up += z * a.b_acc;
+        a.q_out += z * a.b_q;
+        if (a.b_scale) {
+            a.act_scale += z;
+            a.scale_out += z;
+        }
+    }
+    const int per = act_cluster_slice(a.n), i0 = min(a.n, rank * per), m = min(a.n, i0 + per) - i0;
+    const float s_in = a.act_scale[0];
+    const bool live = s_in > 0.0f;
+    const float pg = live ? __fdiv_rn(a.ws_gate, s_in) : 0.0f, pu = live ? __fdiv_rn(a.ws_up, s_in) : 0.0f;
+    for (int i = tid; i < m; i += kActClusterThreads) {
+        const int gi = i0 + i;
+        const float g = live ? __fmul_rn(static_cast<float>(a.v_gate.base != nullptr ? acc_view_read(a.v_gate, blockIdx.z, gi) : a.acc_gate[gi]), pg) : 0.0f;
+        const float u = live ? __fmul_rn(static_cast<float>(a.v_up.base != nullptr ? acc_view_read(a.v_up, blockIdx.z, gi) : a.acc_up[gi]), pu) : 0.0f;
+        float v;
+        if (a.relu2) {
+            const float p = g > 0.0f ? g : 0.0f;
+            v = __fmul_rn(__fmul_rn(p, p), u);
+        } else {
+            v = __fmul_rn(ggml_silu(g), u);
+        }
+        y_s[i] = v;
+    }
+    __syncthreads();
+    if (a.sub_norm_w != nullptr) {
+        double sum = 0.0;
+        for (int i = tid; i < m; i += kActClusterThreads) sum += static_cast<double>(__fmul_rn(y_s[i], y_s[i]));
+        sum = block_sum_f64(sum, sh_d);
+        if (tid == 0) x_sum = sum;
+        cluster.sync();
+        double total = 0.0;
+        for (int r = 0; r < kActClusterSize; ++r) total += *cluster.map_shared_rank(&x_sum, r);
+        const float mean = __double2float_rn(total / static_cast<double>(a.n));
+        const float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, a.eps)));
+        for (int i = tid; i < m; i += kActClusterThreads) y_s[i] = __fmul_rn(__fmul_rn(y_s[i], inv), a.sub_norm_w[i0 + i]);
+        __syncthreads();
+    }
+    float amax = 0.0f;
+    for (int i = tid; i < m; i += kActClusterThreads) amax = fmaxf(amax, fabsf(y_s[i]));
+    amax = block_max_f32(amax, sh_f);
+    if (tid == 0) x_max = amax;
+    cluster.sync();
+    amax = 0.0f;
+    for (int r = 0; r < kActClusterSize; ++r) amax = fmaxf(amax, *cluster.map_shared_rank(&x_max, r));
+    const float s = amax > 0.0f ? __fdiv_rn(127.0f, amax) : 0.0f;
+    for (int i = tid; i < m; i += kActClusterThreads) {
+        float q = 0.0f;
+        if (amax > 0.0f) {
+            q = roundf(__fmul_rn(y_s[i], s));
+            q = q != q ? 0.0f : fminf(fmaxf(q, -128.0f), 127.0f);
+        }
+        a.q_out[i0 + i] = static_cast<int8_t>(q);
+    }
+    if (rank == 0 && tid == 0) a.scale_out[0] = s;
+    cluster.sync();  // no block leaves while its partial results may still be read
 }
 
 // ---- output head: one warp per vocabulary row, ggml_vec_dot_f16 order (model.rs:346-375, ops.rs:970-1014) --------------

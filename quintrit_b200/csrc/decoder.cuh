@@ -11,6 +11,9 @@
 #include "gemv_lut.cuh"
 #include "megakernel.cuh"
 
+struct quintrit_b200_matrix;
+void qtb_release_stacked(quintrit_b200_matrix* m);  // capi.cu: deletes the host object of a stacked matrix
+
 struct quintrit_b200_decoder {
     uint32_t magic;
     int device, sm_count;
@@ -43,6 +46,7 @@ struct quintrit_b200_decoder {
     bool attn_v2 = false;
     qtb::AttnGqaKernel attn_gqa = nullptr;     // one-launch-per-step and batched paths: the grouped attention kernel, if this model's shape has one
     size_t attn_gqa_smem = 0;
+    size_t attn_gqa_pad = 0;                   // experiments: extra shared memory per block, which lowers the number of resident blocks
     float* attn_out = nullptr;
     float *fac = nullptr, *fac_M = nullptr;
     unsigned int *fac_flags = nullptr, *fac_done = nullptr;
@@ -72,6 +76,12 @@ struct quintrit_b200_decoder {
         int32_t *acc_qkv = nullptr, *acc_o = nullptr, *acc_gu = nullptr, *acc_down = nullptr;
         bool warm = false, graph_ready = false;  // a full chunk ran once (lazy allocations done); the graph of a full chunk exists
         cudaGraphExec_t graph = nullptr;
+        // batched products: per layer the row-wise stacks q | k | v and gate | up (nullptr: separate launches), and the buffers for the partial
+        // sums of split products, one per projection kind (q, k, v, o, gate, up, down; a stack uses the first of its kind)
+        bool gemm_ready = false;
+        std::vector<quintrit_b200_matrix*> stack;            // layers * 2
+        std::vector<quintrit_b200_matrix*> stacked_objects;  // owned: released with the decoder (their device memory is in `allocs`)
+        int32_t* parts[7] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
     } pf;
 };
 
@@ -112,6 +122,7 @@ inline void destroy_decoder(quintrit_b200_decoder* d) {
         if (q != nullptr) cudaIpcCloseMemHandle(q);
     if (d->graph_ready) cudaGraphExecDestroy(d->graph_step);
     if (d->pf.graph_ready) cudaGraphExecDestroy(d->pf.graph);
+    for (quintrit_b200_matrix* m : d->pf.stacked_objects) qtb_release_stacked(m);
     if (d->stream) cudaStreamDestroy(d->stream);
     for (void* p : d->allocs) cudaFree(p);
     if (prev >= 0) cudaSetDevice(prev);
@@ -139,7 +150,7 @@ inline int decoder_gemv_bs(quintrit_b200_decoder* d, int layer, int which, const
 // Attention of n tokens: all query heads of a KV head in one block where an instantiation exists, else one query head per block.
 inline void launch_attention(quintrit_b200_decoder* d, const AttnArgs& at, int n, cudaStream_t s) {
     if (d->attn_gqa != nullptr)
-        d->attn_gqa<<<dim3(d->kv_heads, 4, n), kAttnGqaThreads, d->attn_gqa_smem, s>>>(at);
+        d->attn_gqa<<<dim3(d->kv_heads, 4, n), kAttnGqaThreads, d->attn_gqa_smem + d->attn_gqa_pad, s>>>(at);
     else
         attention_kernel<<<dim3(d->q_heads, 4, n), kAttnThreads, 0, s>>>(at);
 }

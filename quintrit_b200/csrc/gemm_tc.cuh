@@ -76,8 +76,9 @@ inline size_t gemm_smem_bytes(int n, int stages) {
 }
 
 // stream layout (gemv_lut.cuh) -> two-bit block-major; `blocks` counts 128-column blocks here, `vblocks` the 160-trit velurex blocks of a row
+// The copy may be one of several matrices stacked row-wise into one (q | k | v, gate | up): its rows start at row_off of rows_total.
 __global__ void stream_to_two_bit_kernel(const uint4* __restrict__ stream, uint8_t* __restrict__ out, size_t rows, size_t cols, size_t rows_padded, size_t blocks, size_t vblocks,
-                                         size_t tiles) {
+                                         size_t tiles, size_t row_off, size_t rows_total) {
     const size_t total = blocks * rows_padded * 32;
     const uint8_t* s = reinterpret_cast<const uint8_t*>(stream);
     for (size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x; i < total; i += size_t(gridDim.x) * blockDim.x) {
@@ -95,7 +96,7 @@ __global__ void stream_to_two_bit_kernel(const uint4* __restrict__ stream, uint8
             }
             byte |= code << (2 * q);
         }
-        out[(g * rows_padded + r) * 32 + j] = static_cast<uint8_t>(byte);
+        out[(g * rows_total + row_off + r) * 32 + j] = static_cast<uint8_t>(byte);
     }
 }
 
