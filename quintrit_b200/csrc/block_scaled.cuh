@@ -7,6 +7,7 @@
 // (quantize_q8_0_scalar); rust/crates/quintrit-core/src/block_scaled.rs:175-202 (dot_row_scalar) and :140-145 (hsum8).
 // The reference runs this path on the CPU only.
 #pragma once
+#include <algorithm>
 #include <cstdint>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -70,13 +71,12 @@ __global__ void quantize_q8_0_kernel(const float* __restrict__ x, size_t n, int8
     }
 }
 
-// Trit tables in shared memory: for every byte value the trits of planes 0-3 as four int8 in one word, and plane 4 (in
-// the low byte of a word). Each table holds kBsCopies interleaved copies (entry b of copy c at index b * kBsCopies + c):
-// the 32 lanes of a warp look up unrelated bytes at the same time, and a lane that reads copy lane % kBsCopies meets at
-// most a quarter of the other lanes in its banks.
-constexpr int kBsCopies = 8;
-__device__ __forceinline__ void build_trit_tables(uint32_t* t0123, uint32_t* t4) {
-    for (int b = threadIdx.x; b < 256; b += blockDim.x) {
+// Trit table in shared memory: for every byte value the trits of planes 0-3 as four int8 in one word (.x) and the trit of
+// plane 4 in the low byte of a second word (.y). The table holds 32 copies, entry b of copy c at index b * 32 + c: lane l
+// of a warp reads copy l, so the 32 lanes hit different banks whatever bytes they look up.
+constexpr int kBsCopies = 32;
+__device__ __forceinline__ void build_trit_table(uint2* tab) {
+    for (int b = threadIdx.x; b < 256; b += blockDim.x) {  // the entry of a byte value is computed once and written 32 times
         int t[5] = {0, 0, 0, 0, 0};
         const bool valid = b <= 250 && b % 28 != 27;
         if (valid) {
@@ -92,119 +92,126 @@ __device__ __forceinline__ void build_trit_tables(uint32_t* t0123, uint32_t* t4)
         }
         const uint32_t w = (static_cast<uint32_t>(t[0]) & 0xFFu) | ((static_cast<uint32_t>(t[1]) & 0xFFu) << 8) | ((static_cast<uint32_t>(t[2]) & 0xFFu) << 16) |
                            ((static_cast<uint32_t>(t[3]) & 0xFFu) << 24);
-        for (int c = 0; c < kBsCopies; ++c) {
-            t0123[b * kBsCopies + c] = w;
-            t4[b * kBsCopies + c] = static_cast<uint32_t>(t[4]) & 0xFFu;
+        const uint2 e = make_uint2(w, static_cast<uint32_t>(t[4]) & 0xFFu);
+#pragma unroll 8
+        for (int c = 0; c < kBsCopies; ++c) tab[b * kBsCopies + ((c + b) & (kBsCopies - 1))] = e;  // (rotated: the threads of a warp write different banks)
+    }
+}
+
+constexpr int kBsTableBytes = 256 * kBsCopies * 8;  // 64 KiB
+constexpr int kBsThreads = 256;                      // eight warps of four rows each
+constexpr int kBsRowsPerCta = kBsThreads / 8;        // a row belongs to eight threads, one per lane of the reference's dot product
+
+// Look-up of byte K of `w`: the entry address is table base + byte * 256 + lane * 8, formed with one byte permute and one add.
+template <int K>
+__device__ __forceinline__ uint2 bs_lookup(uint32_t w, uint32_t tab_lane_addr) {
+    uint32_t off;
+    asm("prmt.b32 %0, %1, 0, %2;" : "=r"(off) : "r"(w), "n"(0x4404 | (K << 4)));  // byte K of w into bits 8-15
+    uint2 e;
+    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(e.x), "=r"(e.y) : "r"(tab_lane_addr + off));
+    return e;
+}
+
+// Four 160-trit blocks = twenty activation blocks s0 .. s0 + 19 of one thread's bytes. FULL: all twenty exist.
+template <bool FULL>
+__device__ __forceinline__ void bs_group(const uint32_t (&w)[4], uint32_t tab_lane_addr, const int* __restrict__ q4, const float* __restrict__ as, const float* __restrict__ ws, int s0,
+                                         int nact, float& acc0, float& acc1) {
+    float wsc[10], asc[20];
+#pragma unroll
+    for (int k = 0; k < 10; ++k) wsc[k] = (FULL || s0 + 2 * k < nact) ? __ldg(ws + k) : 0.0f;
+#pragma unroll
+    for (int k = 0; k < 20; ++k) asc[k] = (FULL || s0 + k < nact) ? as[k] : 0.0f;
+#pragma unroll
+    for (int bi = 0; bi < 4; ++bi) {
+        const uint2 e0 = bs_lookup<0>(w[bi], tab_lane_addr), e1 = bs_lookup<1>(w[bi], tab_lane_addr), e2 = bs_lookup<2>(w[bi], tab_lane_addr), e3 = bs_lookup<3>(w[bi], tab_lane_addr);
+        // transpose the 4 x 4 bytes: word p = the trits of plane p of the four weights
+        const uint32_t lo01 = __byte_perm(e0.x, e1.x, 0x5140), hi01 = __byte_perm(e0.x, e1.x, 0x7362);
+        const uint32_t lo23 = __byte_perm(e2.x, e3.x, 0x5140), hi23 = __byte_perm(e2.x, e3.x, 0x7362);
+        uint32_t plane[5];
+        plane[0] = __byte_perm(lo01, lo23, 0x5410);
+        plane[1] = __byte_perm(lo01, lo23, 0x7632);
+        plane[2] = __byte_perm(hi01, hi23, 0x5410);
+        plane[3] = __byte_perm(hi01, hi23, 0x7632);
+        plane[4] = __byte_perm(__byte_perm(e0.y, e1.y, 0x3340), __byte_perm(e2.y, e3.y, 0x3340), 0x5410);
+#pragma unroll
+        for (int p = 0; p < 5; ++p) {
+            const int i = bi * 5 + p;
+            if (FULL || s0 + i < nact) {
+                const float sum = static_cast<float>(__dp4a(static_cast<int>(plane[p]), q4[i * 8], 0));
+                const float dd = __fmul_rn(wsc[i >> 1], asc[i]);
+                if ((i >> 1) & 1)
+                    acc1 = __fmaf_rn(dd, sum, acc1);
+                else
+                    acc0 = __fmaf_rn(dd, sum, acc0);
+            }
         }
     }
 }
 
-constexpr int kBsTableBytes = 2 * 256 * kBsCopies * 4;  // the two trit tables
-constexpr int kBsThreads = 256;                       // eight warps, one row per warp at a time
-constexpr int kBsWarps = kBsThreads / 32;
-constexpr int kBsChunkBlocks = 32;                    // 160-trit blocks a warp decodes at once (one per lane)
-constexpr int kBsChunkActs = kBsChunkBlocks * 5;      // activation blocks of such a chunk
-constexpr int kBsLaneStride = 9;                      // floats per activation block in the scratch (8 lane sums + 1: no bank conflicts)
-constexpr int kBsWarpScratch = kBsChunkActs * kBsLaneStride + kBsChunkActs;  // floats: lane sums, then the scale products
-
-// Block-scaled GEMV, one row per warp, in two steps per chunk of 32 weight blocks (160 activation blocks):
-//  1. lane l decodes block l of the chunk (its 32 bytes: two 16-byte loads), forms for each of its five planes the eight
-//     exact integer lane sums (dp4a of four trits with four activation codes) and the product w_scale[s/2] * a_scale[s],
-//     and leaves them in the warp's scratch - this part is order-free, so it runs 32 blocks wide;
-//  2. sixteen lanes (two accumulators x eight lanes of the reference's dot product) run the multiply-add chains over the
-//     chunk strictly in the order of s: lane = fma(product, sum, lane), blocks of 64 weights alternating between the two
-//     accumulators (block_scaled.rs:175-202).
+// Block-scaled GEMV (block_scaled.rs:175-202). Eight threads own a row: thread j holds the two accumulators of lane j of the
+// reference's eight-lane dot product and walks the row's 160-trit blocks in order. Per block it reads its four bytes (the
+// planar bytes 4j .. 4j + 3, one 32-bit word), looks each byte up, transposes the 4 x 4 trits into one int8x4 word per plane
+// and forms, for each of the block's five activation blocks s = 5 b + p, the exact integer lane sum (dp4a with four activation
+// codes) and the step acc[(s / 2) & 1] = fma(w_scale[s / 2] * a_scale[s], sum, acc). Four blocks are unrolled together: twenty
+// activation blocks is the period after which the pattern of accumulators repeats, so the choice is made at compile time.
 // At the end the two accumulators are added and the eight lanes reduced as ((l0+l4) + (l2+l6)) + ((l1+l5) + (l3+l7)).
-// Activations (int8 codes and block scales) are staged in shared memory once per CTA.
+// Activations (int8 codes and block scales) are staged in shared memory once per CTA; CTAs walk the rows with a grid stride.
 __global__ void __launch_bounds__(kBsThreads) gemv_block_scaled_kernel(const uint8_t* __restrict__ planar, const float* __restrict__ w_scales,
                                                                         const int8_t* __restrict__ qs, const float* __restrict__ a_scales, size_t rows,
                                                                         size_t cols, float* __restrict__ out) {
     extern __shared__ __align__(16) unsigned char bs_smem[];
-    uint32_t* t0123 = reinterpret_cast<uint32_t*>(bs_smem);                    // 256 x kBsCopies words
-    uint32_t* t4 = t0123 + 256 * kBsCopies;                                    // likewise
-    float* s_as = reinterpret_cast<float*>(bs_smem + kBsTableBytes);           // cols / 32 floats
-    int8_t* s_q = reinterpret_cast<int8_t*>(s_as + cols / 32);          // cols codes (offset is a multiple of 4)
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    float* pf = reinterpret_cast<float*>(bs_smem + ((kBsTableBytes + (cols / 32) * 4 + cols + 15) / 16) * 16) + warp * kBsWarpScratch;
-    float* dd = pf + kBsChunkActs * kBsLaneStride;
-    build_trit_tables(t0123, t4);
+    uint2* tab = reinterpret_cast<uint2*>(bs_smem);
+    float* s_as = reinterpret_cast<float*>(bs_smem + kBsTableBytes);            // cols / 32 floats
+    int* s_q4 = reinterpret_cast<int*>(s_as + cols / 32);                       // cols codes, read as words of four
+    build_trit_table(tab);
     for (size_t i = threadIdx.x; i < cols / 32; i += kBsThreads) s_as[i] = a_scales[i];
-    for (size_t i = threadIdx.x; i < cols / 4; i += kBsThreads) reinterpret_cast<uint32_t*>(s_q)[i] = reinterpret_cast<const uint32_t*>(qs)[i];
+    for (size_t i = threadIdx.x; i < cols / 4; i += kBsThreads) s_q4[i] = reinterpret_cast<const int*>(qs)[i];
     __syncthreads();
-    const size_t row_bytes = (cols + kBlockTrits - 1) / kBlockTrits * kBlockBytes, sb = cols / 64, nact = cols / 32;
-    const size_t nblocks = (nact + 4) / 5;
-    const int chain_c = (lane >> 3) & 1, chain_j = lane & 7;  // lanes 0-15: accumulator and lane of the dot product
-    for (size_t r = static_cast<size_t>(blockIdx.x) * kBsWarps + warp; r < rows; r += static_cast<size_t>(gridDim.x) * kBsWarps) {
-        const uint8_t* row = planar + r * row_bytes;
-        const float* ws = w_scales + r * sb;
-        float acc = 0.0f;
-        for (size_t c0 = 0; c0 < nblocks; c0 += kBsChunkBlocks) {
-            const size_t b = c0 + lane;
-            if (b < nblocks) {
-                const uint4 lo = __ldg(reinterpret_cast<const uint4*>(row + b * kBlockBytes));
-                const uint4 hi = __ldg(reinterpret_cast<const uint4*>(row + b * kBlockBytes) + 1);
-                const uint32_t words[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+    const int lane = threadIdx.x & 31, j = lane & 7;
+    const int nact = static_cast<int>(cols / 32), nblocks = (nact + 4) / 5, ngroups = (nblocks + 3) / 4;
+    const size_t row_words = static_cast<size_t>(nblocks) * 8, sb = cols / 64;
+    const uint32_t tab_lane_addr = static_cast<uint32_t>(__cvta_generic_to_shared(tab)) + lane * 8;
+    for (size_t r0 = static_cast<size_t>(blockIdx.x) * kBsRowsPerCta; r0 < rows; r0 += static_cast<size_t>(gridDim.x) * kBsRowsPerCta) {
+        const size_t r = r0 + (threadIdx.x >> 3);
+        const bool valid = r < rows;
+        const size_t rr = valid ? r : rows - 1;  // threads beyond the last row walk it once more and store nothing
+        const uint32_t* roww = reinterpret_cast<const uint32_t*>(planar) + rr * row_words + j;
+        const float* ws = w_scales + rr * sb;
+        float acc0 = 0.0f, acc1 = 0.0f;
+        uint32_t next[4];
 #pragma unroll
-                for (int p = 0; p < 5; ++p) {
-                    const size_t s = b * 5 + p;
-                    if (s < nact) dd[lane * 5 + p] = __fmul_rn(__ldg(ws + s / 2), s_as[s]);
-                }
+        for (int bi = 0; bi < 4; ++bi) next[bi] = bi < nblocks ? __ldg(roww + bi * 8) : 0x7D7D7D7Du;
+        for (int g = 0; g < ngroups; ++g) {
+            uint32_t w[4];
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    const uint32_t w = words[j];
-                    const uint32_t b0 = w & 0xFFu, b1 = (w >> 8) & 0xFFu, b2 = (w >> 16) & 0xFFu, b3 = w >> 24;
-                    const int cp = lane & (kBsCopies - 1);
-                    const uint32_t x0 = t0123[b0 * kBsCopies + cp], x1 = t0123[b1 * kBsCopies + cp], x2 = t0123[b2 * kBsCopies + cp], x3 = t0123[b3 * kBsCopies + cp];
-                    // transpose the 4 x 4 bytes: word p = the trits of plane p of the four weights
-                    const uint32_t lo01 = __byte_perm(x0, x1, 0x5140), hi01 = __byte_perm(x0, x1, 0x7362);
-                    const uint32_t lo23 = __byte_perm(x2, x3, 0x5140), hi23 = __byte_perm(x2, x3, 0x7362);
-                    uint32_t plane[5];
-                    plane[0] = __byte_perm(lo01, lo23, 0x5410);
-                    plane[1] = __byte_perm(lo01, lo23, 0x7632);
-                    plane[2] = __byte_perm(hi01, hi23, 0x5410);
-                    plane[3] = __byte_perm(hi01, hi23, 0x7632);
-                    plane[4] = t4[b0 * kBsCopies + cp] | (t4[b1 * kBsCopies + cp] << 8) | (t4[b2 * kBsCopies + cp] << 16) | (t4[b3 * kBsCopies + cp] << 24);
-#pragma unroll
-                    for (int p = 0; p < 5; ++p) {
-                        const size_t s = b * 5 + p;
-                        if (s < nact) {
-                            const int a4 = *reinterpret_cast<const int*>(s_q + s * 32 + 4 * j);
-                            pf[(lane * 5 + p) * kBsLaneStride + j] = static_cast<float>(__dp4a(static_cast<int>(plane[p]), a4, 0));
-                        }
-                    }
-                }
+            for (int bi = 0; bi < 4; ++bi) {
+                w[bi] = next[bi];
+                const int b = (g + 1) * 4 + bi;
+                next[bi] = b < nblocks ? __ldg(roww + b * 8) : 0x7D7D7D7Du;  // byte 125: five zero trits
             }
-            __syncwarp();
-            // the chains: activation blocks 4m + 2c and 4m + 2c + 1 of the chunk belong to accumulator c (the chunk starts
-            // on a multiple of 160 activation blocks, so the pattern of the whole row is the pattern inside the chunk)
-            const int n_s = static_cast<int>(min(static_cast<size_t>(kBsChunkActs), nact - c0 * 5));
-            if (lane < 16) {
-#pragma unroll 4
-                for (int s0 = 2 * chain_c; s0 < n_s; s0 += 4) {
-                    acc = __fmaf_rn(dd[s0], pf[s0 * kBsLaneStride + chain_j], acc);
-                    if (s0 + 1 < n_s) acc = __fmaf_rn(dd[s0 + 1], pf[(s0 + 1) * kBsLaneStride + chain_j], acc);
-                }
-            }
-            __syncwarp();  // the scratch is rewritten by the next chunk
+            const int s0 = g * 20;
+            if (s0 + 20 <= nact)
+                bs_group<true>(w, tab_lane_addr, s_q4 + s0 * 8 + j, s_as + s0, ws + s0 / 2, s0, nact, acc0, acc1);
+            else
+                bs_group<false>(w, tab_lane_addr, s_q4 + s0 * 8 + j, s_as + s0, ws + s0 / 2, s0, nact, acc0, acc1);
         }
-        // lanes 0-7 hold accumulator 0, lanes 8-15 accumulator 1
-        float l = __fadd_rn(acc, __shfl_down_sync(0xffffffffu, acc, 8));
-        const float up4 = __shfl_down_sync(0xffffffffu, l, 4);
+        float l = __fadd_rn(acc0, acc1);
+        const float up4 = __shfl_down_sync(0xffffffffu, l, 4, 8);
         l = __fadd_rn(up4, l);  // r_j = l[j + 4] + l[j]
-        const float up2 = __shfl_down_sync(0xffffffffu, l, 2);
+        const float up2 = __shfl_down_sync(0xffffffffu, l, 2, 8);
         l = __fadd_rn(l, up2);  // (r0 + r2), (r1 + r3)
-        const float up1 = __shfl_down_sync(0xffffffffu, l, 1);
+        const float up1 = __shfl_down_sync(0xffffffffu, l, 1, 8);
         l = __fadd_rn(l, up1);
-        if (lane == 0) out[r] = l;
+        if (j == 0 && valid) out[r] = l;
     }
 }
 
-__host__ __device__ constexpr size_t block_scaled_smem_bytes(size_t cols) {
-    return ((kBsTableBytes + (cols / 32) * 4 + cols + 15) / 16) * 16 + static_cast<size_t>(kBsWarps) * kBsWarpScratch * 4;
-}
-// CTAs of a launch: eight rows per CTA at a time, a few CTAs per SM.
-inline int block_scaled_grid(size_t rows, int sm_count) {
-    const size_t want = (rows + kBsWarps - 1) / kBsWarps, cap = static_cast<size_t>(sm_count) * 3;
+__host__ __device__ constexpr size_t block_scaled_smem_bytes(size_t cols) { return ((kBsTableBytes + (cols / 32) * 4 + cols + 15) / 16) * 16; }
+// CTAs of a launch: 32 rows per CTA at a time, as many CTAs as fit the shared memory of the multiprocessors (all resident: what a
+// multiprocessor has to issue is the sum over its CTAs, and the CTAs that walk one row group more are spread over all of them).
+inline int block_scaled_grid(size_t rows, int sm_count, size_t cols = 0) {
+    const size_t per_sm = std::max<size_t>(1, std::min<size_t>(3, (227 * 1024) / (block_scaled_smem_bytes(cols) + 1024)));
+    const size_t want = (rows + kBsRowsPerCta - 1) / kBsRowsPerCta, cap = static_cast<size_t>(sm_count) * per_sm;
     return static_cast<int>(want < cap ? want : cap);
 }
 

@@ -562,7 +562,7 @@ int check_block_scaled(const quintrit_b200_matrix* m) {
     return QUINTRIT_OK;
 }
 int launch_block_scaled(const quintrit_b200_matrix* m) {
-    const int grid = block_scaled_grid(m->rows, m->sm_count);
+    const int grid = block_scaled_grid(m->rows, m->sm_count, m->cols);
     gemv_block_scaled_kernel<<<grid, kBsThreads, block_scaled_smem_bytes(m->cols)>>>(m->d_planar, m->d_wscales, m->d_act, m->d_as, m->rows, m->cols, m->d_outf);
     ++g_launches;
     QTB_CUDA(cudaGetLastError());

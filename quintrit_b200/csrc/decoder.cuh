@@ -139,7 +139,7 @@ inline int decoder_gemv(quintrit_b200_decoder* d, int layer, int which, const in
 // Block-scaled projection `which` (0..6) of a layer: out (F32) = W x for Q8_0 blocks (codes, d->q8_d).
 inline int decoder_gemv_bs(quintrit_b200_decoder* d, int layer, int which, const int8_t* codes, float* out) {
     const quintrit_b200_matrix* m = d->mats[static_cast<size_t>(layer) * 7 + which];
-    const int grid = block_scaled_grid(m->rows, d->sm_count);
+    const int grid = block_scaled_grid(m->rows, d->sm_count, m->cols);
     gemv_block_scaled_kernel<<<grid, kBsThreads, block_scaled_smem_bytes(m->cols), d->stream>>>(m->d_planar, m->d_wscales, codes, d->q8_d, m->rows, m->cols, out);
     ++g_launches;
     const cudaError_t e = cudaGetLastError();
