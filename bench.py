@@ -350,8 +350,8 @@ def run_decode_tp(args, rank: int, world: int, local_rank: int, dist):
     dev = torch.device("cuda", local_rank)
     ctx = (args.prompt + args.steps + 64 + 255) // 256 * 256
     shape = {"falcon3_10b": (12, 4, 3072, 23040, 131072), "bitnet_2b": (20, 5, 2560, 6912, 128256)}[args.decode_shape]
-    if args.decode_shape != "falcon3_10b" or shape[1] % world or shape[2] % world or shape[3] % world or shape[4] % world:
-        return {"tp_world": world, "skipped": f"{world} ranks do not divide the KV heads ({shape[1]}) of {args.decode_shape}"} if rank == 0 else None
+    if args.decode_shape != "falcon3_10b" or shape[2] % world or shape[3] % world or shape[4] % world:
+        return {"tp_world": world, "skipped": f"tensor-parallel decode is built for the LLaMA / Falcon3 architecture with {world} dividing hidden, FFN and vocabulary sizes"} if rank == 0 else None
     npar, ngen = 6, 6
     short = synth.prompt_tokens(2, npar, shape[4])
     want = None
@@ -392,7 +392,7 @@ def run_decode_tp(args, rank: int, world: int, local_rank: int, dist):
     bytes_tok = weights * BYTES_PER_WEIGHT
     return {"shape": spec["shape"], "layers": spec["layers"], "context": args.prompt, "tp_world": world, "tokens_per_s": round(1e3 / step_ms, 1),
             "ms_per_token": round(step_ms, 4), "best_ms_per_token": round(best_ms, 4), "velurex_bytes_per_token": int(bytes_tok),
-            "roofline_nominal_8tbs_frac": round(bytes_tok / (step_ms * 1e-3) / (world * 8e12), 4), "exchanges_per_token": 4 * spec["layers"] + 1,
+            "roofline_nominal_8tbs_frac": round(bytes_tok / (step_ms * 1e-3) / (world * 8e12), 4), "exchanges_per_token": (3 if shape[1] % world else 4) * spec["layers"] + 1, "attention": "replicated on every rank (the ranks do not divide the KV heads)" if shape[1] % world else "split by KV head",
             "transport": "8-byte (value, sequence) peer stores into every rank's box inside the token kernel, polled by the readers",
             "parity": {"greedy_tokens_checked": ngen, "all_ranks_agree": all(g == got for g in gathered), "identical_to_one_gpu": got == want},
             "setup_s": round(setup_s, 1)}

@@ -367,7 +367,8 @@ class Decoder:
         qd, kvd = spec["q_heads"] * hd, spec["kv_heads"] * hd
         self.tp_rank, self.tp_world = spec.get("tp_rank", 0), spec.get("tp_world", 1)
         w = self.tp_world  # a rank of a tensor-parallel group holds its rows of every projection (synth.shard_spec)
-        shapes = [(qd // w, H), (kvd // w, H), (kvd // w, H), (H // w, qd), (I // w, H), (I // w, H), (H // w, I)]
+        hw = w if spec["kv_heads"] % w == 0 else 1  # ranks that do not divide the KV heads hold q, k and v whole (attention is replicated)
+        shapes = [(qd // hw, H), (kvd // hw, H), (kvd // hw, H), (H // w, qd), (I // w, H), (I // w, H), (H // w, I)]
         self.matrices = []
         for i, w in enumerate(spec["weights"]):
             rows, cols = shapes[i % 7]

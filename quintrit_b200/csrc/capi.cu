@@ -838,10 +838,14 @@ int decoder_create_impl(const quintrit_b200_decoder_desc_t* desc, quintrit_b200_
         return fail(QUINTRIT_ERR_MODEL, "a model dimension is zero");
     if (tp_world > 1) {
         if (desc->arch != QUINTRIT_B200_ARCH_LLAMA) return fail(QUINTRIT_ERR_UNSUPPORTED, "tensor parallelism is available for the LLaMA / Falcon3 architecture only");
-        if (desc->num_kv_heads % tp_world || H % tp_world || I_full % tp_world || desc->vocab_size % tp_world)
-            return fail(QUINTRIT_ERR_UNSUPPORTED, "tp_world %u must divide the KV heads (%u), the hidden size, the FFN size and the vocabulary", tp_world,
-                        desc->num_kv_heads);
+        if (H % tp_world || I_full % tp_world || desc->vocab_size % tp_world)
+            return fail(QUINTRIT_ERR_UNSUPPORTED, "tp_world %u must divide the hidden size, the FFN size and the vocabulary", tp_world);
     }
+    // Where the ranks do not divide the KV heads (Falcon3's 4 KV heads on 8 GPUs) attention is replicated: every rank holds the whole q, k and v
+    // projections and the whole KV cache and computes every head, so the attention output needs no exchange; o, gate, up, down and the output
+    // head stay split as before.
+    const bool attn_replicated = tp_world > 1 && desc->num_kv_heads % tp_world != 0;
+    const uint32_t head_split = attn_replicated ? 1u : tp_world;
     const uint32_t I = I_full / tp_world;  // this rank's rows of gate and up
     if (hd % 32 != 0 || hd > 256) return fail(QUINTRIT_ERR_UNSUPPORTED, "head_dim %u is not supported (a multiple of 32, at most 256)", hd);
     if (H % 32 != 0) return fail(QUINTRIT_ERR_UNSUPPORTED, "the hidden size %u must be a multiple of 32", H);  // as gpu.rs:171-173
@@ -853,7 +857,7 @@ int decoder_create_impl(const quintrit_b200_decoder_desc_t* desc, quintrit_b200_
     if (ctx == 0 || ctx > 8192 || ctx % 8 != 0)
         return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "context_length %u must be a multiple of 8 below 256, or give 256..8192 after rounding down to a multiple of 256", desc->context_length);
     const size_t qd_full = size_t(desc->num_heads) * hd;
-    const size_t qd = qd_full / tp_world, kvd = size_t(desc->num_kv_heads) * hd / tp_world;  // this rank's query and KV widths
+    const size_t qd = qd_full / head_split, kvd = size_t(desc->num_kv_heads) * hd / head_split;  // this rank's query and KV widths
     const uint32_t vocab_local = desc->vocab_size / tp_world;
     if (std::max<size_t>({H, I_full, qd_full}) * sizeof(float) > 200 * 1024) return fail(QUINTRIT_ERR_UNSUPPORTED, "a vector of the model does not fit the shared memory of one block");
     cudaDeviceProp prop;
@@ -880,7 +884,8 @@ int decoder_create_impl(const quintrit_b200_decoder_desc_t* desc, quintrit_b200_
     d->device = static_cast<int>(desc->device_index);
     d->sm_count = prop.multiProcessorCount;
     d->arch = desc->arch, d->f32_values = desc->f32_values != 0;
-    d->hidden = H, d->inter = I, d->layers = L, d->q_heads = desc->num_heads / tp_world, d->kv_heads = desc->num_kv_heads / tp_world, d->head_dim = hd;
+    d->hidden = H, d->inter = I, d->layers = L, d->q_heads = desc->num_heads / head_split, d->kv_heads = desc->num_kv_heads / head_split, d->head_dim = hd;
+    d->attn_replicated = attn_replicated;
     d->tp_rank = static_cast<int>(tp_rank), d->tp_world = static_cast<int>(tp_world);
     d->bf16_tables = table_dtype == 1;
     d->block_scaled = block_scaled;
@@ -1141,7 +1146,7 @@ int mega_setup(quintrit_b200_decoder* d, const quintrit_b200_decoder_desc_t* des
         if ((rc = dev_alloc(d, &part, static_cast<size_t>(d->sm_count))) != QUINTRIT_OK) return rc;
         a.sumsq_part = part;
     }
-    a.tp_rank = d->tp_rank, a.tp_world = d->tp_world, a.tp_seq = d->tp_seq;
+    a.tp_rank = d->tp_rank, a.tp_world = d->tp_world, a.tp_seq = d->tp_seq, a.attn_replicated = d->attn_replicated ? 1 : 0;
     a.tp_wait_ns = kTpWaitLimitNs;
     if (const char* ms = std::getenv("QUINTRIT_B200_TP_WAIT_MS")) {  // shorter or longer patience with a silent peer, in milliseconds
         const long v = std::strtol(ms, nullptr, 10);

@@ -61,6 +61,7 @@ struct quintrit_b200_decoder {
     float* q8_d = nullptr;                     // Q8_0 block scales of the current projection input
     bool bf16_tables = false;                  // embedding and output head hold BF16 instead of F16 bit patterns
     int tp_rank = 0, tp_world = 1;
+    bool attn_replicated = false;              // tensor parallelism with every head on every rank (the ranks do not divide the KV heads)
     int q_dim_full = 0, inter_full = 0, vocab_full = 0;
     unsigned char* tp_box = nullptr;           // the exchange box of this rank (one allocation, shared with the peers)
     size_t tp_box_bytes = 0;

@@ -86,6 +86,7 @@ struct MegaArgs {
     int relu2;                 // BitNet: relu(gate)^2 * up instead of SwiGLU (ops.rs:301-308)
     double* sumsq_part;        // BitNet FFN sub-norm: one partial sum of squares per CTA
     int tp_rank, tp_world;
+    int attn_replicated;       // tensor parallelism with every head on every rank: the attention output needs no exchange
     unsigned char* tp_box[8];  // the boxes as mapped into this process, own box at [tp_rank]
     unsigned int* tp_seq;      // exchanges completed by earlier launches (the same on every rank)
     unsigned long long tp_wait_ns;  // how long a reader waits for a peer's pair before it gives up (kTpWaitLimitNs by default)
@@ -1634,7 +1635,7 @@ __device__ __noinline__ bool phase_combine(const MegaArgs& a, int l, unsigned in
     }
     QTB_FINE(a, 23);
     int n_all = qd;
-    if (a.tp_world > 1) {
+    if (a.tp_world > 1 && !a.attn_replicated) {
         // this rank's heads are a slice of the attention output: CTA p sends it to rank p, then every CTA takes the whole
         // vector from the own box as the pairs arrive
         __syncthreads();

@@ -188,7 +188,9 @@ def torch_model(shape: str, device, ctx: int, f32_values: bool = False, config: 
         for p, (rows, cols) in enumerate(shapes):
             if tp is None:
                 w = torch_planar(seed_for(config, l, p, 0), rows, cols, device)
-            else:  # only this rank's rows (see shard_spec)
+            elif p < 3 and kvh % tp[1] != 0:  # the ranks do not divide the KV heads: q, k and v whole on every rank (see shard_spec)
+                w = torch_planar(seed_for(config, l, p, 0), rows, cols, device)
+            else:  # only this rank's rows
                 n = rows // tp[1]
                 w = torch_planar(seed_for(config, l, p, 0), n, cols, device, row0=tp[0] * n)
             weights.append(w.cpu().numpy().reshape(-1))
@@ -222,17 +224,22 @@ def batch_lengths(config: int, n: int, lo: int = 256, hi: int = 2048) -> np.ndar
 def shard_spec(spec: dict, rank: int, world: int) -> dict:
     """The share of `spec` (planar numpy projections) that rank `rank` of a tensor-parallel group of `world` GPUs holds:
     its rows of every projection - q / k / v rows of its heads, rows [rank * n / world, (rank + 1) * n / world) of o,
-    gate, up and down - and its rows of the output head. Dimensions stay those of the whole model."""
+    gate, up and down - and its rows of the output head. Dimensions stay those of the whole model. Where `world` does not
+    divide the KV heads, q, k and v stay whole on every rank (attention is replicated, the rest is split)."""
     from . import api
 
     H, I, hd = spec["hidden"], spec["inter"], spec["head_dim"]
     qd, kvd = spec["q_heads"] * hd, spec["kv_heads"] * hd
-    assert spec["kv_heads"] % world == 0 and H % world == 0 and I % world == 0 and spec["vocab"] % world == 0
+    assert H % world == 0 and I % world == 0 and spec["vocab"] % world == 0
+    replicated = spec["kv_heads"] % world != 0
     shapes = [(qd, H), (kvd, H), (kvd, H), (H, qd), (I, H), (I, H), (H, I)]
     weights = []
     for i, w in enumerate(spec["weights"]):
         rows, cols = shapes[i % 7]
         rb = api.row_bytes(cols)
+        if replicated and i % 7 < 3:
+            weights.append(np.ascontiguousarray(np.asarray(w, np.uint8)).reshape(-1))
+            continue
         n = rows // world
         weights.append(np.ascontiguousarray(np.asarray(w, np.uint8).reshape(rows, rb)[rank * n:(rank + 1) * n]).reshape(-1))
     out = dict(spec, weights=weights, tp_rank=rank, tp_world=world)

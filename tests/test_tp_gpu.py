@@ -71,7 +71,8 @@ def _rank_main(rank: int, world: int, port: int, out_dir: str, geometry) -> None
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("geometry", [(False, 4, 2, 64, 256, 512), (True, 4, 2, 128, 512, 1024)])
+# the third geometry has three KV heads: two ranks do not divide them, so attention is replicated on both and only o, the FFN and the head are split
+@pytest.mark.parametrize("geometry", [(False, 4, 2, 64, 256, 512), (True, 4, 2, 128, 512, 1024), (False, 6, 3, 64, 384, 512)])
 def test_two_ranks_decode_like_one_cpu_model(tmp_path, geometry):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
