@@ -228,8 +228,10 @@ typedef struct quintrit_b200_decoder_desc {
      * tp_world in {1, 2, 4, 8} ranks, one process and one GPU each, share the model: the dimensions above stay those of
      * the whole model, and this rank supplies its rows of every projection - q / k / v for its num_heads / tp_world query
      * heads and num_kv_heads / tp_world KV heads, rows [tp_rank * n / tp_world, (tp_rank + 1) * n / tp_world) of o, gate,
-     * up and down - and, if lm_head is not NULL, its vocab_size / tp_world rows of the head (embed stays whole). After
-     * creation the ranks exchange quintrit_b200_decoder_tp_handle and call quintrit_b200_decoder_tp_attach. */
+     * up and down - and, if lm_head is not NULL, its vocab_size / tp_world rows of the head (embed stays whole). Where
+     * tp_world does not divide num_kv_heads, every rank supplies the whole q, k and v instead: attention is replicated on
+     * every rank and only o, gate, up, down and the head are split. After creation the ranks exchange
+     * quintrit_b200_decoder_tp_handle and call quintrit_b200_decoder_tp_attach. */
     uint32_t tp_rank, tp_world;
     /* 0: embed / lm_head hold F16 bit patterns (the reference's dense path, quintrit-runtime/src/model.rs:308-375);
      * 1: BF16 bit patterns, with the reference's BF16 projection arithmetic (quintrit-runtime/src/hybrid.rs:327-333, 364-367:
