@@ -85,5 +85,12 @@ def test_shards_are_the_row_ranges_of_the_whole_model(world):
     head = np.concatenate([np.asarray(s["lm_head"], np.uint16) for s in shards])
     assert np.array_equal(head, np.asarray(spec["lm_head"], np.uint16))
     assert all(np.array_equal(s["embed"], spec["embed"]) for s in shards)  # the embedding stays whole on every rank
-    with pytest.raises(AssertionError):
-        synth.shard_spec(spec, 0, 4)  # 2 KV heads do not split over 4 ranks
+    # 2 KV heads do not split over 4 ranks: q, k and v stay whole on every rank (attention is replicated), the rest is split by rows
+    four = [synth.shard_spec(spec, r, 4) for r in range(4)]
+    for i, (rows, cols) in enumerate(_shapes(spec) * spec["layers"]):
+        rb = q.row_bytes(cols)
+        whole = np.asarray(spec["weights"][i], np.uint8).reshape(rows, rb)
+        if i % 7 < 3:
+            assert all(np.array_equal(np.asarray(s["weights"][i], np.uint8).reshape(rows, rb), whole) for s in four)
+        else:
+            assert np.array_equal(np.concatenate([np.asarray(s["weights"][i], np.uint8).reshape(rows // 4, rb) for s in four]), whole)
