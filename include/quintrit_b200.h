@@ -412,6 +412,11 @@ int quintrit_session_logits(struct quintrit_session* session, float* out, size_t
 int quintrit_session_generate_tokens(struct quintrit_session* session, const uint32_t* prompt, size_t prompt_len, size_t max_new, uint32_t* out,
                                      size_t out_capacity, size_t* out_count);
 
+/* Prompt tokens that the last quintrit_session_generate call of this session found in the KV cache and did not compute again: a prompt
+ * that begins like the conversation the session holds is ingested from the first differing token on (the reference's
+ * InferenceEngine::reusable_prefix, quintrit-runtime/src/engine.rs:700-727; at least the last prompt token is always computed). */
+int quintrit_b200_session_reused_tokens(const struct quintrit_session* session, uint32_t* out_reused);
+
 /* ---- the tokenizer of a GGUF file on its own (byte-level BPE as quintrit-runtime/src/tokenizer.rs builds it; no GPU needed):
  * for a front end that tokenizes on another host and for tests. The runtime level uses the same object. ---- */
 typedef struct quintrit_b200_tokenizer quintrit_b200_tokenizer_t;

@@ -50,6 +50,11 @@ struct quintrit_session {
     uint32_t ctx = 0;
     std::vector<float> logits;  // of the last position fed, when they were fetched
     bool logits_valid = false;
+    // The tokens whose keys and values sit at positions 0 .. cached.size() - 1, as far as the host knows them: a new prompt that begins
+    // with the same tokens is ingested from the first difference on (quintrit-runtime/src/engine.rs:700-727). The record is trusted
+    // only while its length equals the decoder's position; calls that run the loop on the device clear it.
+    std::vector<uint32_t> cached;
+    uint32_t last_reused = 0;   // prompt tokens the last text generation found cached
 };
 struct quintrit_gguf {
     uint32_t magic;
@@ -197,6 +202,12 @@ int rt_forward(quintrit_session* s, uint32_t token, uint32_t pos, bool want_logi
     if (want_logits) QTB_CUDA(cudaMemcpyAsync(s->logits.data(), d->logits, size_t(d->vocab) * sizeof(float), cudaMemcpyDeviceToHost, d->stream));
     if (greedy) QTB_CUDA(cudaMemcpyAsync(greedy, d->d_token, sizeof(uint32_t), cudaMemcpyDeviceToHost, d->stream));
     if ((rc = decoder_check_status(d)) != QUINTRIT_OK) return rc;
+    if (s->cached.size() >= pos) {
+        s->cached.resize(pos);
+        s->cached.push_back(token);
+    } else {
+        s->cached.clear();
+    }
     d->host_pos = pos + 1;
     s->logits_valid = want_logits;
     return QUINTRIT_OK;
@@ -213,6 +224,12 @@ int rt_feed(quintrit_session* s, const uint32_t* ids, size_t n, uint32_t pos0, b
         if (want_logits) QTB_CUDA(cudaMemcpyAsync(s->logits.data(), d->logits, size_t(d->vocab) * sizeof(float), cudaMemcpyDeviceToHost, d->stream));
         if (greedy) QTB_CUDA(cudaMemcpyAsync(greedy, d->d_token, sizeof(uint32_t), cudaMemcpyDeviceToHost, d->stream));
         if ((rc = decoder_check_status(d)) != QUINTRIT_OK) return rc;
+        if (s->cached.size() >= pos0) {
+            s->cached.resize(pos0);
+            s->cached.insert(s->cached.end(), ids, ids + n);
+        } else {
+            s->cached.clear();
+        }
         d->host_pos = pos0 + static_cast<uint32_t>(n);
         s->logits_valid = want_logits;
         return QUINTRIT_OK;
@@ -220,6 +237,12 @@ int rt_feed(quintrit_session* s, const uint32_t* ids, size_t n, uint32_t pos0, b
     for (size_t i = 0; i + 1 < n; ++i) {
         int rc;
         if ((rc = decoder_set(d, ids[i], pos0 + static_cast<uint32_t>(i))) != QUINTRIT_OK || (rc = decoder_step(d)) != QUINTRIT_OK) return rc;
+    }
+    if (s->cached.size() >= pos0) {
+        s->cached.resize(pos0);
+        s->cached.insert(s->cached.end(), ids, ids + n - 1);
+    } else {
+        s->cached.clear();
     }
     return rt_forward(s, ids[n - 1], pos0 + static_cast<uint32_t>(n - 1), want_logits, greedy);
 }
@@ -895,6 +918,7 @@ extern "C" int quintrit_session_reset(quintrit_session_t* session) {
         RtSessionLock lk(session);
         if ((rc = lk.check()) != QUINTRIT_OK) return rc;
         session->dec->host_pos = 0;  // positions are rewritten from 0 on; nothing of the old conversation is read again
+        session->cached.clear();
         session->logits_valid = false;
         return ok();
     });
@@ -932,17 +956,27 @@ int rt_generate(quintrit_session* s, const std::string& prompt, const quintrit_g
     if (tokens.empty()) return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "the prompt produced no tokens");
     for (uint32_t t : tokens)
         if (t >= m.data.shape.vocab) return fail(QUINTRIT_ERR_MODEL, "tokenizer produced token %u outside the vocabulary of %llu", t, static_cast<unsigned long long>(m.data.shape.vocab));
-    const uint32_t pos0 = keep ? s->dec->host_pos : 0;
-    if (size_t(pos0) + tokens.size() > s->ctx)
-        return fail(QUINTRIT_ERR_CONTEXT_OVERFLOW, "%zu prompt tokens do not fit: the context window holds %u tokens and %u are already used", tokens.size(), s->ctx, pos0);
-    if (!keep) s->dec->host_pos = 0;
+    const uint32_t base = keep ? s->dec->host_pos : 0;
+    if (size_t(base) + tokens.size() > s->ctx)
+        return fail(QUINTRIT_ERR_CONTEXT_OVERFLOW, "%zu prompt tokens do not fit: the context window holds %u tokens and %u are already used", tokens.size(), s->ctx, base);
+    // A prompt that begins like the cached conversation is ingested from the first difference on; at least its last token is computed
+    // again, because its logits start the generation (engine.rs:700-727).
+    size_t common = 0;
+    if (!keep && s->cached.size() == s->dec->host_pos && std::getenv("QUINTRIT_B200_NO_PREFIX_REUSE") == nullptr)
+        while (common < s->cached.size() && common + 1 < tokens.size() && s->cached[common] == tokens[common]) ++common;
+    s->last_reused = static_cast<uint32_t>(common);
+    const uint32_t pos0 = keep ? base : static_cast<uint32_t>(common);
+    if (!keep) {
+        s->dec->host_pos = pos0;
+        s->cached.resize(common);
+    }
     RtSampler sampler(prm.temperature, prm.top_k, prm.top_p, prm.seed);
     const bool greedy = sampler.greedy();
     const bool llama_like = m.arch == "bitnet" || m.arch == "llama";
     uint32_t device_choice = 0;
-    int rc = rt_feed(s, tokens.data(), tokens.size(), pos0, !greedy, &device_choice);
+    int rc = rt_feed(s, tokens.data() + common, tokens.size() - common, pos0, !greedy, &device_choice);
     if (rc != QUINTRIT_OK) return rc;
-    uint32_t pos = pos0 + static_cast<uint32_t>(tokens.size());
+    uint32_t pos = base + static_cast<uint32_t>(tokens.size());
     std::string full, pending;
     uint32_t generated = 0;
     int reason = QUINTRIT_FINISH_LENGTH;
@@ -1101,8 +1135,19 @@ extern "C" int quintrit_session_generate_tokens(quintrit_session_t* session, con
         if ((rc = lk.check()) != QUINTRIT_OK) return rc;
         // greedy, without leaving the device between tokens; the session restarts from position 0
         if ((rc = quintrit_b200_decoder_generate(session->dec, prompt, prompt_len, max_new, out, out_capacity)) != QUINTRIT_OK) return rc;
+        session->cached.clear();  // the loop ran on the device: the host has no record of what the cache holds now
         session->logits_valid = false;
         *out_count = max_new;
+        return ok();
+    });
+}
+
+extern "C" int quintrit_b200_session_reused_tokens(const struct quintrit_session* session, uint32_t* out_reused) {
+    return guard([&]() -> int {
+        int rc = rt_check(session, kMagicSession, "session");
+        if (rc != QUINTRIT_OK) return rc;
+        if (out_reused == nullptr) return fail(QUINTRIT_ERR_NULL_POINTER, "out_reused is NULL");
+        *out_reused = session->last_reused;
         return ok();
     });
 }

@@ -341,6 +341,12 @@ class Model:
         _check(self._l.quintrit_session_logits(self._s, out.ctypes.data_as(C.POINTER(C.c_float)), out.size))
         return out
 
+    def reused_tokens(self) -> int:
+        """Prompt tokens the last ``generate`` / ``stream`` call found in the KV cache and did not compute again."""
+        n = C.c_uint32(0)
+        _check(self._l.quintrit_b200_session_reused_tokens(self._s, C.byref(n)))
+        return n.value
+
     def generate_tokens(self, prompt_ids, max_new: int) -> np.ndarray:
         a = _ids(prompt_ids)
         out, n = np.zeros(max_new, np.uint32), _sz(0)

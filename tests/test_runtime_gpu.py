@@ -125,6 +125,30 @@ def test_lengths_stops_context_and_errors(gpu, cpu, tok):
     assert gpu.generate(PROMPT, 20) == free  # the session is usable after every error
 
 
+def test_a_prompt_that_begins_like_the_cached_conversation_is_ingested_from_the_first_difference(cpu, tok):
+    """Prefix reuse (quintrit-runtime/src/engine.rs:700-727): the text is what a fresh session gives, and the count of prompt tokens that
+    were found cached is reported."""
+    m = Model.load(TINY, device="cuda")
+    first = m.generate(PROMPT, 6)
+    assert m.reused_tokens() == 0
+    n_prompt = len(tok.encode(PROMPT, add_bos=True))
+    again = m.generate(PROMPT, 6)  # the whole prompt is cached; its last token is computed again (its logits start the generation)
+    assert again == first == _oracle_text(cpu, tok, PROMPT, 6)[0] and m.reused_tokens() == n_prompt - 1
+    longer = PROMPT + " and the dog"
+    assert m.generate(longer, 5) == _oracle_text(cpu, tok, longer, 5)[0]
+    assert m.reused_tokens() >= n_prompt  # the prompt (and a generated token only if the new text happens to continue like it)
+    other = "the cat ran"
+    common = 0
+    a, b = tok.encode(longer, add_bos=True), tok.encode(other, add_bos=True)
+    while common < min(len(a), len(b)) and a[common] == b[common]:
+        common += 1
+    assert m.generate(other, 5, temperature=0.8, seed=3) == _oracle_text(cpu, tok, other, 5, temperature=0.8, top_k=40, top_p=0.9, seed=3)[0]
+    assert m.reused_tokens() >= min(common, len(b) - 1) > 0
+    m.generate_tokens(tok.encode(PROMPT, add_bos=True), 3)  # the loop runs on the device: the host's record of the cache is dropped
+    assert m.generate(PROMPT, 6) == first and m.reused_tokens() == 0
+    m.close()
+
+
 def test_a_session_in_use_is_busy_for_other_threads(gpu):
     started, release, seen = threading.Event(), threading.Event(), []
 
