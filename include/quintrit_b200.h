@@ -357,6 +357,16 @@ int quintrit_b200_selftest_barrier(uint32_t device_index, uint32_t ctas, uint32_
 int quintrit_b200_decoder_prefill(quintrit_b200_decoder_t* decoder, const uint32_t* tokens, size_t count, uint32_t pos, float* logits, size_t logits_capacity,
                                   uint32_t* out_token);
 
+/* ---- the token sampler on the device (temperature, top-k, nucleus; quintrit-runtime/src/sampler.rs:59-143) ----------------
+ * The runtime level (quintrit_session_generate) samples on the device when 1 <= top_k <= 1024: the logits never leave the GPU and
+ * the sampled token is the next step's input there. This entry runs the same kernel on `count` logits of the caller's (host
+ * memory): the candidates are the top_k largest logits / temperature in the total order of floats (ties by lower id, as the
+ * reference's stable sort leaves them), softmax with the float exponential summed in double, nucleus cut at top_p, and a draw
+ * with the xorshift64 generator whose state is *state (updated; never zero). The token is the one the reference's sampler
+ * returns for the same logits, parameters and state. */
+int quintrit_b200_sample_logits(uint32_t device_index, const float* logits, size_t count, float temperature, uint32_t top_k, float top_p, uint64_t* state,
+                                uint32_t* out_token);
+
 /* ---- several sequences decoded together (batched decode) ---------------------------------------------------------------
  * The reference decodes one sequence per session, one token per step (quintrit-runtime/src/engine.rs:282, 626-631); nothing in
  * it batches sequences. Here up to 256 independent sequences share one pass over the weights per step: the projections of a

@@ -29,6 +29,7 @@ from .api import (  # noqa: F401
     pack_planar,
     quantize_q8_0,
     row_bytes,
+    sample_logits,
     selftest_barrier,
     version,
 )

@@ -542,6 +542,16 @@ class Batch:
             pass
 
 
+def sample_logits(logits, temperature: float, top_k: int, top_p: float, state: int, device: int = 0):
+    """One draw of the device sampler from host logits: returns (token id, new generator state)."""
+    lg = np.ascontiguousarray(logits, dtype=np.float32).reshape(-1)
+    st, tok = C.c_uint64(state), C.c_uint32(0)
+    lib = load_library()
+    lib.quintrit_b200_sample_logits.argtypes = [C.c_uint32, _f32p, _sz, C.c_float, C.c_uint32, C.c_float, C.POINTER(C.c_uint64), C.POINTER(C.c_uint32)]
+    _check(lib.quintrit_b200_sample_logits(device, _p(lg, _f32p), lg.size, temperature, top_k, top_p, C.byref(st), C.byref(tok)))
+    return tok.value, st.value
+
+
 def quantize_q8_0(x, device: int = 0):
     """Q8_0 activation blocks computed on the device: (codes int8[n], scales f32[n / 32])."""
     xx = np.ascontiguousarray(x, dtype=np.float32).reshape(-1)

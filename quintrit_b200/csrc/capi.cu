@@ -3,6 +3,7 @@
 // Host code is C++ over the CUDA runtime API; the reference's host side for the same seam is
 // rust/crates/quintrit-cuda/src/{device.rs,gemv.rs,pack.rs} and rust/crates/quintrit-c/src/cuda.rs.
 #include <algorithm>
+#include <cmath>
 #include <cstdlib>
 #include <mutex>
 #include <new>
@@ -806,6 +807,19 @@ size_t decoder_item_tiles(size_t tile_pairs, size_t slots) {
 
 int mega_setup(quintrit_b200_decoder* d, const quintrit_b200_decoder_desc_t* desc);
 
+// The table of device_expf on the current device: glibc's 2^(i/32), correctly rounded (the host libm's exp2), minus i << 47.
+int upload_exp2_table() {
+    unsigned long long tab[32];
+    for (int i = 0; i < 32; ++i) {
+        const double v = std::exp2(static_cast<double>(i) / 32.0);
+        unsigned long long b;
+        std::memcpy(&b, &v, 8);
+        tab[i] = b - (static_cast<unsigned long long>(i) << 47);
+    }
+    QTB_CUDA(cudaMemcpyToSymbol(c_exp2_tab, tab, sizeof tab));
+    return QUINTRIT_OK;
+}
+
 // Lets a kernel use all the shared memory the device offers a block beyond the kernel's own static arrays.
 template <typename K>
 int allow_max_dynamic_smem(K kernel, int smem_optin) {
@@ -899,15 +913,7 @@ int decoder_create_impl(const quintrit_b200_decoder_desc_t* desc, quintrit_b200_
     d->host_pos = 0;
     QTB_CUDA(cudaStreamCreateWithFlags(&d->stream, cudaStreamNonBlocking));
 
-    // glibc expf table: 2^(i/32) correctly rounded (the host libm's exp2), minus i << 47
-    unsigned long long tab[32];
-    for (int i = 0; i < 32; ++i) {
-        const double v = std::exp2(static_cast<double>(i) / 32.0);
-        unsigned long long b;
-        std::memcpy(&b, &v, 8);
-        tab[i] = b - (static_cast<unsigned long long>(i) << 47);
-    }
-    QTB_CUDA(cudaMemcpyToSymbol(c_exp2_tab, tab, sizeof tab));
+    if ((rc = upload_exp2_table()) != QUINTRIT_OK) return rc;
     // cos / sin of every position with the host libm, chained as ops.rs:121-141 (freq_scale 1, no YaRN)
     {
         std::vector<float> cs(size_t(ctx) * desc->rope_dims);
@@ -2397,6 +2403,42 @@ extern "C" int quintrit_b200_decoder_prefill(quintrit_b200_decoder_t* decoder, c
         if (out_token) QTB_CUDA(cudaMemcpyAsync(out_token, d->d_token, sizeof(uint32_t), cudaMemcpyDeviceToHost, d->stream));
         if ((rc = decoder_check_status(d)) != QUINTRIT_OK) return rc;  // (the batched projections report a time-out through the same word)
         d->host_pos = pos + static_cast<uint32_t>(count);
+        return ok();
+    });
+}
+
+// ---- the device sampler on logits the caller holds -----------------------------------------------------------------------------------
+extern "C" int quintrit_b200_sample_logits(uint32_t device_index, const float* logits, size_t count, float temperature, uint32_t top_k, float top_p, uint64_t* state,
+                                           uint32_t* out_token) {
+    return guard([&]() -> int {
+        if (logits == nullptr || state == nullptr || out_token == nullptr) return fail(QUINTRIT_ERR_NULL_POINTER, "logits, state or out_token is NULL");
+        if (!(temperature > 0.0f) || !std::isfinite(temperature)) return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "temperature must be finite and positive");
+        if (!(top_p > 0.0f && top_p <= 1.0f)) return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "top_p must be in (0, 1]");
+        if (top_k < 1 || top_k > static_cast<uint32_t>(kSampleMaxK) || top_k >= count)
+            return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "top_k %u must be in [1, %d] and below the number of logits (%zu)", top_k, kSampleMaxK, count);
+        if (count > (size_t(1) << 24)) return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "at most 2^24 logits");
+        if (*state == 0) return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "the generator state must not be zero (a zero state never leaves zero)");
+        cudaDeviceProp prop;
+        int rc = require_b200(static_cast<int>(device_index), &prop);
+        if (rc != QUINTRIT_OK) return rc;
+        DeviceGuard g(static_cast<int>(device_index));
+        if ((rc = upload_exp2_table()) != QUINTRIT_OK) return rc;
+        unsigned char* buf = nullptr;
+        QTB_CUDA(cudaMalloc(&buf, count * sizeof(float) + 16));
+        float* d_logits = reinterpret_cast<float*>(buf + 16);
+        unsigned long long* d_rng = reinterpret_cast<unsigned long long*>(buf);
+        uint32_t* d_tok = reinterpret_cast<uint32_t*>(buf + 8);
+        cudaError_t e = cudaMemcpy(d_logits, logits, count * sizeof(float), cudaMemcpyHostToDevice);
+        if (e == cudaSuccess) e = cudaMemcpy(d_rng, state, sizeof(uint64_t), cudaMemcpyHostToDevice);
+        if (e == cudaSuccess) {
+            sample_topk_kernel<<<1, kSampleThreads>>>(d_logits, static_cast<int>(count), temperature, static_cast<int>(top_k), top_p, d_rng, d_tok);
+            ++g_launches;
+            e = cudaGetLastError();
+        }
+        if (e == cudaSuccess) e = cudaMemcpy(state, d_rng, sizeof(uint64_t), cudaMemcpyDeviceToHost);
+        if (e == cudaSuccess) e = cudaMemcpy(out_token, d_tok, sizeof(uint32_t), cudaMemcpyDeviceToHost);
+        cudaFree(buf);
+        if (e != cudaSuccess) return cuda_fail(e, "device sampler");
         return ok();
     });
 }

@@ -1113,6 +1113,145 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ 
     }
 }
 
+// ---- temperature / top-k / top-p sampling on the device (sampler.rs:59-143) ----------------------------------------------
+// One block of 1024 threads, for 1 <= top_k <= 1024 and top_k < n. The reference scales the logits by 1 / temperature, sorts the
+// candidates (stable, descending in the total order of floats), keeps top_k, takes exp(x - max) with the float libm
+// exponential, sums in double in candidate order, cuts the nucleus with a float running sum, normalises again and walks
+// the cumulative sum up to a number from its xorshift64 stream. Here: the k-th largest key is found by a four-pass radix
+// select over the keys of all n candidates (thread t owns a contiguous range, so ties at the k-th key are taken in index
+// order after one block-wide scan); the k survivors are ordered by counting, and thread 0 then performs the sequential
+// arithmetic exactly as written there. The chosen id replaces *token; *rng is the generator's state.
+constexpr int kSampleThreads = 1024, kSampleMaxK = 1024;
+
+__device__ __forceinline__ uint32_t sample_key(float v) {  // ascending unsigned order = f32::total_cmp order
+    const int32_t b = static_cast<int32_t>(__float_as_uint(v));
+    return static_cast<uint32_t>(b ^ static_cast<int32_t>(static_cast<uint32_t>(b >> 31) >> 1)) ^ 0x80000000u;
+}
+
+__global__ void __launch_bounds__(kSampleThreads) sample_topk_kernel(const float* __restrict__ logits, int n, float temperature, int top_k, float top_p,
+                                                                     unsigned long long* __restrict__ rng, uint32_t* __restrict__ token) {
+    __shared__ unsigned int hist[256];
+    __shared__ unsigned int s_prefix, s_need, s_count;
+    __shared__ unsigned int scan[kSampleThreads];
+    __shared__ uint32_t c_key[kSampleMaxK], c_idx[kSampleMaxK], o_idx[kSampleMaxK];
+    __shared__ float o_val[kSampleMaxK];
+    const int tid = threadIdx.x;
+    const float inv_temp = __fdiv_rn(1.0f, temperature);
+    const int per = (n + kSampleThreads - 1) / kSampleThreads, i0 = min(n, tid * per), i1 = min(n, i0 + per);
+    // radix select: after the pass of digit d the keys with the chosen prefix in their top 8 (4 - d) bits contain the k-th largest
+    unsigned int prefix = 0, need = static_cast<unsigned int>(top_k);
+    for (int d = 3; d >= 0; --d) {
+        if (tid < 256) hist[tid] = 0;
+        __syncthreads();
+        const unsigned int mask = d == 3 ? 0u : 0xFFFFFFFFu << (8 * (d + 1));
+        for (int j = 0; j < per; ++j) {  // (a uniform trip count: the lanes of a warp vote below)
+            const int i = i0 + j;
+            unsigned int bucket = 256u;  // no key, or a key outside the prefix
+            if (i < i1) {
+                const uint32_t k = sample_key(__fmul_rn(logits[i], inv_temp));
+                if ((k & mask) == prefix) bucket = (k >> (8 * d)) & 0xFFu;
+            }
+            // logits of one token share most of their leading bits: the lanes that hit the same bucket send one addition
+            const unsigned int peers = __match_any_sync(0xffffffffu, bucket);
+            if (bucket < 256u && (tid & 31) == __ffs(peers) - 1) atomicAdd(&hist[bucket], static_cast<unsigned int>(__popc(peers)));
+        }
+        __syncthreads();
+        if (tid == 0) {
+            unsigned int left = need;
+            int b = 255;
+            for (; b > 0; --b) {
+                if (hist[b] >= left) break;
+                left -= hist[b];
+            }
+            s_prefix = prefix | (static_cast<unsigned int>(b) << (8 * d));
+            s_need = left;  // how many keys of the chosen bucket are still wanted
+        }
+        __syncthreads();
+        prefix = s_prefix, need = s_need;
+        __syncthreads();
+    }
+    // every key above the k-th is a candidate; of the keys equal to it, the `need` lowest indices
+    unsigned int mine_eq = 0;
+    for (int i = i0; i < i1; ++i) mine_eq += sample_key(__fmul_rn(logits[i], inv_temp)) == prefix ? 1u : 0u;
+    scan[tid] = mine_eq;
+    if (tid == 0) s_count = 0;
+    __syncthreads();
+    for (int o = 1; o < kSampleThreads; o <<= 1) {  // inclusive scan
+        const unsigned int add = tid >= o ? scan[tid - o] : 0u;
+        __syncthreads();
+        scan[tid] += add;
+        __syncthreads();
+    }
+    unsigned int eq_rank = scan[tid] - mine_eq;  // equal keys in the ranges before this thread's
+    for (int i = i0; i < i1; ++i) {
+        const uint32_t k = sample_key(__fmul_rn(logits[i], inv_temp));
+        bool take = k > prefix;
+        if (k == prefix) take = eq_rank++ < need;
+        if (take) {
+            const unsigned int at = atomicAdd(&s_count, 1u);
+            if (at < static_cast<unsigned int>(kSampleMaxK)) c_key[at] = k, c_idx[at] = static_cast<uint32_t>(i);
+        }
+    }
+    __syncthreads();
+    const int m = min(static_cast<int>(s_count), top_k);  // = top_k
+    // order by counting: descending key, ascending index among equal keys (the stable sort's order)
+    if (tid < m) {
+        const uint32_t k = c_key[tid], ix = c_idx[tid];
+        int rank = 0;
+        for (int j = 0; j < m; ++j) rank += (c_key[j] > k || (c_key[j] == k && c_idx[j] < ix)) ? 1 : 0;
+        o_idx[rank] = ix;
+        o_val[rank] = __fmul_rn(logits[ix], inv_temp);
+    }
+    __syncthreads();
+    if (tid != 0) return;
+    float mx = o_val[0];
+    for (int i = 0; i < m; ++i)
+        if (o_val[i] > mx) mx = o_val[i];
+    double sum = 0.0;
+    for (int i = 0; i < m; ++i) {
+        const float p = device_expf(__fsub_rn(o_val[i], mx));
+        o_val[i] = p;
+        sum += static_cast<double>(p);
+    }
+    if (sum > 0.0) {
+        const float inv = __double2float_rn(1.0 / sum);
+        for (int i = 0; i < m; ++i) o_val[i] = __fmul_rn(o_val[i], inv);
+    }
+    int cutoff = m;
+    if (top_p < 1.0f) {
+        float cum = 0.0f;
+        for (int i = 0; i < m; ++i) {
+            cum = __fadd_rn(cum, o_val[i]);
+            if (cum >= top_p) {
+                cutoff = i + 1;
+                break;
+            }
+        }
+    }
+    float psum = 0.0f;
+    for (int i = 0; i < cutoff; ++i) psum = __fadd_rn(psum, o_val[i]);
+    if (psum > 0.0f) {
+        const float inv = __fdiv_rn(1.0f, psum);
+        for (int i = 0; i < cutoff; ++i) o_val[i] = __fmul_rn(o_val[i], inv);
+    }
+    unsigned long long x = *rng;
+    x ^= x << 13;
+    x ^= x >> 7;
+    x ^= x << 17;
+    *rng = x;
+    const float r = __fdiv_rn(__ull2float_rn(x), 18446744073709551616.0f);
+    float acc = 0.0f;
+    uint32_t chosen = o_idx[0];
+    for (int i = 0; i < cutoff; ++i) {
+        acc = __fadd_rn(acc, o_val[i]);
+        if (r <= acc || i + 1 == cutoff) {
+            chosen = o_idx[i];
+            break;
+        }
+    }
+    *token = chosen;
+}
+
 // next position (the generation loop runs on the device: the token comes from argmax_kernel, the position from here)
 __global__ void advance_kernel(uint32_t* pos, uint32_t* history, const uint32_t* token) {
     history[pos[0]] = token[0];

@@ -33,6 +33,7 @@ struct quintrit_b200_decoder {
     float *s_h, *s_q, *s_i;
     int32_t *acc_qkv, *acc_o, *acc_gu, *acc_down;
     uint32_t *d_token, *d_pos, *d_history;
+    unsigned long long* d_rng = nullptr;       // state of the sampler's xorshift64 generator (runtime level, sampling on the device)
     unsigned int* d_counters;
     qtb::GemvItem* d_items;
     std::vector<int> item_first, item_count;  // layers * 4 launches: qkv, o, gate+up, down

@@ -194,11 +194,24 @@ struct RtSampler {
 
 // One position through the decoder of a session; the logits are fetched only when asked for.
 // `on_device`: the device already holds this token and position (the token it chose itself at the position it advanced to).
-int rt_forward(quintrit_session* s, uint32_t token, uint32_t pos, bool want_logits, uint32_t* greedy, bool on_device = false) {
+// Sampling on the device (sample_topk_kernel): the parameters of one generation call, or nullptr for the greedy choice / host sampling.
+struct RtDeviceSampling {
+    float temperature, top_p;
+    int top_k;
+};
+int rt_enqueue_sample(quintrit_b200_decoder* d, const RtDeviceSampling* sp) {
+    if (sp == nullptr) return QUINTRIT_OK;
+    sample_topk_kernel<<<1, kSampleThreads, 0, d->stream>>>(d->logits, d->vocab, sp->temperature, sp->top_k, sp->top_p, d->d_rng, d->d_token);
+    QTB_LAUNCH_CHECK();
+    return QUINTRIT_OK;
+}
+
+int rt_forward(quintrit_session* s, uint32_t token, uint32_t pos, bool want_logits, uint32_t* greedy, bool on_device = false, const RtDeviceSampling* sample = nullptr) {
     quintrit_b200_decoder* d = s->dec;
     int rc;
     if (!on_device && (rc = decoder_set(d, token, pos)) != QUINTRIT_OK) return rc;
     if ((rc = decoder_step(d)) != QUINTRIT_OK) return rc;
+    if ((rc = rt_enqueue_sample(d, sample)) != QUINTRIT_OK) return rc;  // replaces the greedy choice in d_token by the sampled one
     if (want_logits) QTB_CUDA(cudaMemcpyAsync(s->logits.data(), d->logits, size_t(d->vocab) * sizeof(float), cudaMemcpyDeviceToHost, d->stream));
     if (greedy) QTB_CUDA(cudaMemcpyAsync(greedy, d->d_token, sizeof(uint32_t), cudaMemcpyDeviceToHost, d->stream));
     if ((rc = decoder_check_status(d)) != QUINTRIT_OK) return rc;
@@ -214,13 +227,14 @@ int rt_forward(quintrit_session* s, uint32_t token, uint32_t pos, bool want_logi
 }
 
 // Feeds tokens from position pos0 without waiting between them; only the last position's logits / greedy token are read back.
-int rt_feed(quintrit_session* s, const uint32_t* ids, size_t n, uint32_t pos0, bool want_logits, uint32_t* greedy) {
+int rt_feed(quintrit_session* s, const uint32_t* ids, size_t n, uint32_t pos0, bool want_logits, uint32_t* greedy, const RtDeviceSampling* sample = nullptr) {
     quintrit_b200_decoder* d = s->dec;
     DeviceGuard g(d->device);
     if (n >= 8 && prefill_available(d) && std::getenv("QUINTRIT_B200_NO_PREFILL") == nullptr) {
         // a prompt goes in chunks of up to 256 tokens with the projections on the tensor cores; the result is that of n single steps
         int rc = decoder_prefill(d, ids, n, pos0);
         if (rc != QUINTRIT_OK) return rc;
+        if ((rc = rt_enqueue_sample(d, sample)) != QUINTRIT_OK) return rc;
         if (want_logits) QTB_CUDA(cudaMemcpyAsync(s->logits.data(), d->logits, size_t(d->vocab) * sizeof(float), cudaMemcpyDeviceToHost, d->stream));
         if (greedy) QTB_CUDA(cudaMemcpyAsync(greedy, d->d_token, sizeof(uint32_t), cudaMemcpyDeviceToHost, d->stream));
         if ((rc = decoder_check_status(d)) != QUINTRIT_OK) return rc;
@@ -244,7 +258,7 @@ int rt_feed(quintrit_session* s, const uint32_t* ids, size_t n, uint32_t pos0, b
     } else {
         s->cached.clear();
     }
-    return rt_forward(s, ids[n - 1], pos0 + static_cast<uint32_t>(n - 1), want_logits, greedy);
+    return rt_forward(s, ids[n - 1], pos0 + static_cast<uint32_t>(n - 1), want_logits, greedy, false, sample);
 }
 
 // engine.rs:869-879: the first index of `pending` from which the rest could still be the beginning of a stop sequence.
@@ -971,10 +985,25 @@ int rt_generate(quintrit_session* s, const std::string& prompt, const quintrit_g
         s->cached.resize(common);
     }
     RtSampler sampler(prm.temperature, prm.top_k, prm.top_p, prm.seed);
-    const bool greedy = sampler.greedy();
+    // Sampling runs on the device where the candidates are cut to at most 1024 (top_k): the logits then never leave the GPU and the
+    // sampled token is the next step's input there, as the greedy choice is. Other settings sample on the host from the logits.
+    RtDeviceSampling dev_sampling{prm.temperature, prm.top_p, static_cast<int>(prm.top_k)};
+    const bool on_device_sampling = !sampler.greedy() && prm.top_k >= 1 && prm.top_k <= static_cast<uint32_t>(kSampleMaxK) && prm.top_k < m.data.shape.vocab &&
+                                    s->dec->tp_world == 1 && std::getenv("QUINTRIT_B200_HOST_SAMPLER") == nullptr;
+    const RtDeviceSampling* dsp = on_device_sampling ? &dev_sampling : nullptr;
+    if (on_device_sampling) {
+        DeviceGuard dg(s->dec->device);
+        if (s->dec->d_rng == nullptr) {
+            int rc0 = dev_alloc(s->dec, &s->dec->d_rng, 1);
+            if (rc0 != QUINTRIT_OK) return rc0;
+        }
+        QTB_CUDA(cudaMemcpyAsync(s->dec->d_rng, &sampler.state, sizeof sampler.state, cudaMemcpyHostToDevice, s->dec->stream));
+        QTB_CUDA(cudaStreamSynchronize(s->dec->stream));  // (the state is a local of this call)
+    }
+    const bool greedy = sampler.greedy() || on_device_sampling;  // the device chooses: only the token comes back
     const bool llama_like = m.arch == "bitnet" || m.arch == "llama";
     uint32_t device_choice = 0;
-    int rc = rt_feed(s, tokens.data() + common, tokens.size() - common, pos0, !greedy, &device_choice);
+    int rc = rt_feed(s, tokens.data() + common, tokens.size() - common, pos0, !greedy, &device_choice, dsp);
     if (rc != QUINTRIT_OK) return rc;
     uint32_t pos = base + static_cast<uint32_t>(tokens.size());
     std::string full, pending;
@@ -1026,7 +1055,7 @@ int rt_generate(quintrit_session* s, const std::string& prompt, const quintrit_g
             break;
         }
         // feed the token (also after a callback stop, so that the cache matches the text the caller has seen)
-        if ((rc = rt_forward(s, next, pos, !greedy, &device_choice, greedy)) != QUINTRIT_OK) return rc;
+        if ((rc = rt_forward(s, next, pos, !greedy, &device_choice, greedy, dsp)) != QUINTRIT_OK) return rc;
         ++pos;
         if (halt) break;
     }
