@@ -1117,9 +1117,9 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ 
 // One block of 1024 threads, for 1 <= top_k <= 1024 and top_k < n. The reference scales the logits by 1 / temperature, sorts the
 // candidates (stable, descending in the total order of floats), keeps top_k, takes exp(x - max) with the float libm
 // exponential, sums in double in candidate order, cuts the nucleus with a float running sum, normalises again and walks
-// the cumulative sum up to a number from its xorshift64 stream. Here: the k-th largest key is found by a four-pass radix
-// select over the keys of all n candidates (thread t owns a contiguous range, so ties at the k-th key are taken in index
-// order after one block-wide scan); the k survivors are ordered by counting, and thread 0 then performs the sequential
+// the cumulative sum up to a number from its xorshift64 stream. Here: the k-th largest key is found by a three-pass radix
+// select over the keys of all n candidates (where more keys equal the k-th than are wanted, thread t counts and takes
+// those of a contiguous range, so they are taken in index order after one block-wide scan); the k survivors are ordered by counting, and thread 0 then performs the sequential
 // arithmetic exactly as written there. The chosen id replaces *token; *rng is the generator's state.
 constexpr int kSampleThreads = 1024, kSampleMaxK = 1024;
 
@@ -1130,66 +1130,115 @@ __device__ __forceinline__ uint32_t sample_key(float v) {  // ascending unsigned
 
 __global__ void __launch_bounds__(kSampleThreads) sample_topk_kernel(const float* __restrict__ logits, int n, float temperature, int top_k, float top_p,
                                                                      unsigned long long* __restrict__ rng, uint32_t* __restrict__ token) {
-    __shared__ unsigned int hist[256];
-    __shared__ unsigned int s_prefix, s_need, s_count;
+    __shared__ unsigned int hist[2048];
+    __shared__ unsigned int s_prefix, s_need, s_count, s_equal;
     __shared__ unsigned int scan[kSampleThreads];
     __shared__ uint32_t c_key[kSampleMaxK], c_idx[kSampleMaxK], o_idx[kSampleMaxK];
     __shared__ float o_val[kSampleMaxK];
     const int tid = threadIdx.x;
     const float inv_temp = __fdiv_rn(1.0f, temperature);
-    const int per = (n + kSampleThreads - 1) / kSampleThreads, i0 = min(n, tid * per), i1 = min(n, i0 + per);
-    // radix select: after the pass of digit d the keys with the chosen prefix in their top 8 (4 - d) bits contain the k-th largest
+    // Radix select in three passes over digits of 11, 11 and 10 bits: after a pass the keys that carry the chosen digits contain the
+    // k-th largest. The passes read the logits with a stride of the block (neighbouring threads, neighbouring addresses), four at a time.
     unsigned int prefix = 0, need = static_cast<unsigned int>(top_k);
-    for (int d = 3; d >= 0; --d) {
-        if (tid < 256) hist[tid] = 0;
+    for (int pass = 0; pass < 3; ++pass) {
+        const int shift = pass == 0 ? 21 : pass == 1 ? 10 : 0, width = pass == 2 ? 10 : 11;
+        const unsigned int above = pass == 0 ? 0u : 0xFFFFFFFFu << (shift + width);  // the digits chosen so far
+        for (int i = tid; i < 2048; i += kSampleThreads) hist[i] = 0;
         __syncthreads();
-        const unsigned int mask = d == 3 ? 0u : 0xFFFFFFFFu << (8 * (d + 1));
-        for (int j = 0; j < per; ++j) {  // (a uniform trip count: the lanes of a warp vote below)
-            const int i = i0 + j;
-            unsigned int bucket = 256u;  // no key, or a key outside the prefix
-            if (i < i1) {
-                const uint32_t k = sample_key(__fmul_rn(logits[i], inv_temp));
-                if ((k & mask) == prefix) bucket = (k >> (8 * d)) & 0xFFu;
+        for (int base = 0; base < n; base += 4 * kSampleThreads) {  // (a uniform trip count: the lanes of a warp vote below)
+            float v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int i = base + u * kSampleThreads + tid;
+                v[u] = i < n ? logits[i] : 0.0f;
             }
-            // logits of one token share most of their leading bits: the lanes that hit the same bucket send one addition
-            const unsigned int peers = __match_any_sync(0xffffffffu, bucket);
-            if (bucket < 256u && (tid & 31) == __ffs(peers) - 1) atomicAdd(&hist[bucket], static_cast<unsigned int>(__popc(peers)));
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int i = base + u * kSampleThreads + tid;
+                unsigned int bucket = 2048u;  // no key, or a key outside the chosen digits
+                if (i < n) {
+                    const uint32_t k = sample_key(__fmul_rn(v[u], inv_temp));
+                    if ((k & above) == prefix) bucket = (k >> shift) & ((1u << width) - 1u);
+                }
+                if (pass == 0) {
+                    // the logits of one token share most of their leading bits: the lanes that hit the same bucket send one addition
+                    const unsigned int peers = __match_any_sync(0xffffffffu, bucket);
+                    if (bucket < 2048u && (tid & 31) == __ffs(peers) - 1) atomicAdd(&hist[bucket], static_cast<unsigned int>(__popc(peers)));
+                } else if (bucket < 2048u) {
+                    atomicAdd(&hist[bucket], 1u);
+                }
+            }
         }
         __syncthreads();
-        if (tid == 0) {
-            unsigned int left = need;
-            int b = 255;
-            for (; b > 0; --b) {
-                if (hist[b] >= left) break;
-                left -= hist[b];
+        if (tid < 32) {
+            // the bucket in which the count from the top reaches `need`: lane L sums buckets 64 L .. 64 L + 63, the lanes' sums are
+            // accumulated from the top, and the lane where the target falls walks its 64 buckets
+            unsigned int sum = 0;
+            for (int i = 0; i < 64; ++i) sum += hist[tid * 64 + i];
+            unsigned int from_here = sum;  // buckets of this lane and of all higher lanes
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const unsigned int up = __shfl_down_sync(0xffffffffu, from_here, o);
+                if (tid + o < 32) from_here += up;
             }
-            s_prefix = prefix | (static_cast<unsigned int>(b) << (8 * d));
-            s_need = left;  // how many keys of the chosen bucket are still wanted
+            const unsigned int reach = __ballot_sync(0xffffffffu, from_here >= need);  // lanes 0 .. L*: bit 0 is always set (need <= n)
+            const int lane_star = 31 - __clz(static_cast<int>(reach));
+            if (tid == lane_star) {
+                unsigned int left = need - (from_here - sum);
+                int bkt = tid * 64 + 63;
+                for (; bkt > tid * 64; --bkt) {
+                    if (hist[bkt] >= left) break;
+                    left -= hist[bkt];
+                }
+                s_prefix = prefix | (static_cast<unsigned int>(bkt) << shift);
+                s_need = left;          // how many keys of the chosen bucket are still wanted
+                s_equal = hist[bkt];    // (after the last pass: how many keys equal the k-th)
+                s_count = 0;
+            }
         }
         __syncthreads();
         prefix = s_prefix, need = s_need;
         __syncthreads();
     }
-    // every key above the k-th is a candidate; of the keys equal to it, the `need` lowest indices
-    unsigned int mine_eq = 0;
-    for (int i = i0; i < i1; ++i) mine_eq += sample_key(__fmul_rn(logits[i], inv_temp)) == prefix ? 1u : 0u;
-    scan[tid] = mine_eq;
-    if (tid == 0) s_count = 0;
-    __syncthreads();
-    for (int o = 1; o < kSampleThreads; o <<= 1) {  // inclusive scan
-        const unsigned int add = tid >= o ? scan[tid - o] : 0u;
-        __syncthreads();
-        scan[tid] += add;
-        __syncthreads();
+    // Every key above the k-th is a candidate. Of the keys equal to it the `need` lowest indices are: all of them in the usual case, which
+    // one more strided pass collects; otherwise thread t counts and takes the equal keys of a contiguous range, in index order, after a scan.
+    const bool all_equal_taken = s_equal == need;
+    for (int base = 0; base < n; base += 4 * kSampleThreads) {
+        float v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int i = base + u * kSampleThreads + tid;
+            v[u] = i < n ? logits[i] : 0.0f;
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int i = base + u * kSampleThreads + tid;
+            if (i >= n) continue;
+            const uint32_t k = sample_key(__fmul_rn(v[u], inv_temp));
+            if (k > prefix || (all_equal_taken && k == prefix)) {
+                const unsigned int at = atomicAdd(&s_count, 1u);
+                if (at < static_cast<unsigned int>(kSampleMaxK)) c_key[at] = k, c_idx[at] = static_cast<uint32_t>(i);
+            }
+        }
     }
-    unsigned int eq_rank = scan[tid] - mine_eq;  // equal keys in the ranges before this thread's
-    for (int i = i0; i < i1; ++i) {
-        const uint32_t k = sample_key(__fmul_rn(logits[i], inv_temp));
-        bool take = k > prefix;
-        if (k == prefix) take = eq_rank++ < need;
-        if (take) {
+    if (!all_equal_taken) {  // (uniform over the block)
+        const int per = (n + kSampleThreads - 1) / kSampleThreads, i0 = min(n, tid * per), i1 = min(n, i0 + per);
+        unsigned int mine_eq = 0;
+        for (int i = i0; i < i1; ++i) mine_eq += sample_key(__fmul_rn(logits[i], inv_temp)) == prefix ? 1u : 0u;
+        scan[tid] = mine_eq;
+        __syncthreads();
+        for (int o = 1; o < kSampleThreads; o <<= 1) {  // inclusive scan
+            const unsigned int add = tid >= o ? scan[tid - o] : 0u;
+            __syncthreads();
+            scan[tid] += add;
+            __syncthreads();
+        }
+        unsigned int eq_rank = scan[tid] - mine_eq;  // equal keys in the ranges before this thread's
+        for (int i = i0; i < i1 && eq_rank < need; ++i) {
+            if (sample_key(__fmul_rn(logits[i], inv_temp)) != prefix) continue;
+            ++eq_rank;
             const unsigned int at = atomicAdd(&s_count, 1u);
-            if (at < static_cast<unsigned int>(kSampleMaxK)) c_key[at] = k, c_idx[at] = static_cast<uint32_t>(i);
+            if (at < static_cast<unsigned int>(kSampleMaxK)) c_key[at] = prefix, c_idx[at] = static_cast<uint32_t>(i);
         }
     }
     __syncthreads();
