@@ -66,6 +66,15 @@ struct quintrit_b200_plan {
     unsigned int* d_counters;
     int8_t* d_act;
     int32_t* d_out;
+    // plan_run with host buffers works in up to four segments of consecutive matrices: the activations of the next segments go up and the
+    // results of the finished ones come down (on streams of their own) while a segment's kernel runs
+    struct Segment {
+        int item0, items;
+        size_t act0, act_bytes, out0, out_count;
+        cudaEvent_t up = nullptr, done = nullptr;
+    };
+    std::vector<Segment> segments;
+    cudaStream_t s_run = nullptr, s_copy = nullptr;
 };
 
 namespace {
@@ -657,6 +666,12 @@ namespace {
 void destroy_plan(quintrit_b200_plan* p) {
     if (p == nullptr) return;
     DeviceGuard g(p->device);
+    for (auto& sg : p->segments) {
+        if (sg.up) cudaEventDestroy(sg.up);
+        if (sg.done) cudaEventDestroy(sg.done);
+    }
+    if (p->s_run) cudaStreamDestroy(p->s_run);
+    if (p->s_copy) cudaStreamDestroy(p->s_copy);
     cudaFree(p->d_items);
     cudaFree(p->d_counters);
     cudaFree(p->d_act);
@@ -687,8 +702,11 @@ extern "C" int quintrit_b200_plan_create(const quintrit_b200_matrix_t* const* ma
         size_t act = 0, out = 0;
         size_t tiles_per_item = item_tiles_override();
         if (tiles_per_item == 0) tiles_per_item = 64;
+        std::vector<size_t> item_at(count + 1), weights_before(count + 1);
+        size_t weights = 0;
         for (size_t i = 0; i < count; ++i) {
             const quintrit_b200_matrix* m = matrices[i];
+            item_at[i] = items.size(), weights_before[i] = weights;
             p->act_off.push_back(act);
             p->out_off.push_back(out);
             p->rows.push_back(m->rows);
@@ -696,10 +714,33 @@ extern "C" int quintrit_b200_plan_create(const quintrit_b200_matrix_t* const* ma
             build_items(items, m->d_w, act, out, m->rows, m->cols, m->blocks, m->tiles, tiles_per_item);
             act += (m->cols + 15) / 16 * 16;
             out += (m->rows + 3) / 4 * 4;
+            weights += m->rows * m->cols;
         }
+        item_at[count] = items.size(), weights_before[count] = weights;
         p->act_total = act;
         p->out_total = out;
         p->n_items = static_cast<int>(items.size());
+        {
+            // segments of about equal weight counts, cut between matrices; small plans run as one
+            int want = 1;
+            if (const char* v = std::getenv("QUINTRIT_B200_PLAN_SEGMENTS")) want = std::max(1, std::min(16, std::atoi(v)));
+            else if (count >= 16 && weights >= (size_t(1) << 30)) want = 4;
+            size_t first = 0;
+            for (int sgi = 0; sgi < want && first < count; ++sgi) {
+                size_t last = count;  // exclusive
+                if (sgi + 1 < want) {
+                    const size_t target = weights * (sgi + 1) / want;
+                    last = first + 1;
+                    while (last < count && weights_before[last] < target) ++last;
+                }
+                quintrit_b200_plan::Segment sg;
+                sg.item0 = static_cast<int>(item_at[first]), sg.items = static_cast<int>(item_at[last] - item_at[first]);
+                sg.act0 = p->act_off[first], sg.act_bytes = (last < count ? p->act_off[last] : act) - sg.act0;
+                sg.out0 = p->out_off[first], sg.out_count = (last < count ? p->out_off[last] : out) - sg.out0;
+                p->segments.push_back(sg);
+                first = last;
+            }
+        }
         auto bail = [&](cudaError_t e, const char* what) {
             destroy_plan(p);
             return cuda_fail(e, what);
@@ -712,6 +753,11 @@ extern "C" int quintrit_b200_plan_create(const quintrit_b200_matrix_t* const* ma
         if ((e = cudaMemcpy(p->d_items, items.data(), items.size() * sizeof(GemvItem), cudaMemcpyHostToDevice)) != cudaSuccess) return bail(e, "cudaMemcpy(items)");
         if ((e = cudaMemset(p->d_counters, 0, 4 * sizeof(unsigned int))) != cudaSuccess) return bail(e, "cudaMemset(counters)");
         if ((e = cudaMemset(p->d_act, 0, act)) != cudaSuccess) return bail(e, "cudaMemset(activations)");
+        if ((e = cudaStreamCreateWithFlags(&p->s_run, cudaStreamNonBlocking)) != cudaSuccess) return bail(e, "cudaStreamCreate");
+        if ((e = cudaStreamCreateWithFlags(&p->s_copy, cudaStreamNonBlocking)) != cudaSuccess) return bail(e, "cudaStreamCreate");
+        for (auto& sg : p->segments)
+            if ((e = cudaEventCreateWithFlags(&sg.up, cudaEventDisableTiming)) != cudaSuccess || (e = cudaEventCreateWithFlags(&sg.done, cudaEventDisableTiming)) != cudaSuccess)
+                return bail(e, "cudaEventCreate");
         *out_plan = p;
         return ok();
     });
@@ -772,14 +818,27 @@ extern "C" int quintrit_b200_plan_run(quintrit_b200_plan_t* plan, const int8_t* 
         if (activations_len < plan->act_total) return fail(QUINTRIT_ERR_BUFFER_TOO_SMALL, "activations hold %zu bytes, %zu are needed", activations_len, plan->act_total);
         if (out_capacity < plan->out_total) return fail(QUINTRIT_ERR_BUFFER_TOO_SMALL, "out holds %zu values, %zu are needed", out_capacity, plan->out_total);
         DeviceGuard g(plan->device);
-        QTB_CUDA(cudaMemcpyAsync(plan->d_act, activations, plan->act_total, cudaMemcpyHostToDevice, 0));
-        QTB_CUDA(cudaMemsetAsync(plan->d_out, 0, plan->out_total * sizeof(int32_t), 0));
-        rc = launch_gemv(plan->d_items, plan->n_items, plan->d_act, plan->d_out, plan->d_counters, plan->sm_count, 0);
-        if (rc != QUINTRIT_OK) return rc;
-        QTB_CUDA(cudaMemcpyAsync(out, plan->d_out, plan->out_total * sizeof(int32_t), cudaMemcpyDeviceToHost, 0));
+        // Segment by segment: the copy stream brings the activations up (all of them, in segment order) and takes each segment's results down as
+        // soon as its kernel is done; the run stream clears the results and runs the kernels. With pinned host buffers the copies of one segment
+        // overlap the kernel of another; with pageable ones the runtime serialises them and the result is the same.
+        QTB_CUDA(cudaDeviceSynchronize());  // launches the caller made on streams of its own (plan_launch) use the same buffers: they come first
+        QTB_CUDA(cudaMemsetAsync(plan->d_out, 0, plan->out_total * sizeof(int32_t), plan->s_run));
+        for (auto& sg : plan->segments) {
+            QTB_CUDA(cudaMemcpyAsync(plan->d_act + sg.act0, activations + sg.act0, sg.act_bytes, cudaMemcpyHostToDevice, plan->s_copy));
+            QTB_CUDA(cudaEventRecord(sg.up, plan->s_copy));
+        }
+        for (auto& sg : plan->segments) {
+            QTB_CUDA(cudaStreamWaitEvent(plan->s_run, sg.up, 0));
+            rc = launch_gemv(plan->d_items + sg.item0, sg.items, plan->d_act, plan->d_out, plan->d_counters, plan->sm_count, plan->s_run);
+            if (rc != QUINTRIT_OK) return rc;
+            QTB_CUDA(cudaEventRecord(sg.done, plan->s_run));
+            QTB_CUDA(cudaStreamWaitEvent(plan->s_copy, sg.done, 0));
+            QTB_CUDA(cudaMemcpyAsync(out + sg.out0, plan->d_out + sg.out0, sg.out_count * sizeof(int32_t), cudaMemcpyDeviceToHost, plan->s_copy));
+        }
         unsigned int flag = 0;
-        QTB_CUDA(cudaMemcpyAsync(&flag, plan->d_counters + 2, sizeof flag, cudaMemcpyDeviceToHost, 0));
-        QTB_CUDA(cudaStreamSynchronize(0));
+        QTB_CUDA(cudaMemcpyAsync(&flag, plan->d_counters + 2, sizeof flag, cudaMemcpyDeviceToHost, plan->s_copy));
+        QTB_CUDA(cudaStreamSynchronize(plan->s_copy));
+        QTB_CUDA(cudaStreamSynchronize(plan->s_run));
         if (flag != 0) return fail(QUINTRIT_ERR_DEVICE, "GEMV kernel on the CUDA device found its shared-memory table at an unexpected address");
         return ok();
     });

@@ -120,7 +120,12 @@ def test_gguf_sources_transcode_on_device(oracle):
         assert np.array_equal(m.gemv_i32(act).astype(np.int64), want), src
 
 
-def test_plan_runs_many_projections_in_one_launch(oracle):
+@pytest.mark.parametrize("segments", [None, 3, 16])
+def test_plan_runs_many_projections_in_one_launch(oracle, monkeypatch, segments):
+    """A plan's host-buffer run is one launch for a small plan; large plans (and this test, through the experiment knob) run in segments of
+    consecutive matrices whose copies overlap the other segments' kernels: the results are the same."""
+    if segments is not None:
+        monkeypatch.setenv("QUINTRIT_B200_PLAN_SEGMENTS", str(segments))
     rng = np.random.default_rng(13)
     shapes = [(3072, 3072), (1024, 3072), (1024, 3072), (3072, 3072), (2304, 3072), (2304, 3072), (3072, 2304), (40, 161), (7, 1)]
     mats, planars, acts = [], [], []
@@ -133,7 +138,7 @@ def test_plan_runs_many_projections_in_one_launch(oracle):
     for _ in range(2):
         q.launch_count(reset=True)
         res = plan.split_results(plan.run(plan.pack_activations(acts)))
-        assert q.launch_count() == 1
+        assert q.launch_count() == (1 if segments is None else min(segments, len(shapes)))
         for (rows, cols), planar, a, r in zip(shapes, planars, acts, res):
             assert np.array_equal(r, oracle.gemv_planar(planar, rows, cols, a)), (rows, cols)
         acts = [rng.integers(-128, 128, c).astype(np.int8) for _, c in shapes]
