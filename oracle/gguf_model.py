@@ -16,6 +16,7 @@ import oracle
 
 _SCALAR = {0: "<B", 1: "<b", 2: "<H", 3: "<h", 4: "<I", 5: "<i", 6: "<f", 7: "<B", 10: "<Q", 11: "<q", 12: "<d"}
 F32, F16, BF16, TQ1_0, TQ2_0, I2_S, Q2_0 = 0, 1, 30, 34, 35, 36, 42
+VELUREX = 0x5156  # not a GGML type: planar velurex rows in a pre-transcoded container (quintrit_b200/container.py)
 
 
 class _Cursor:
@@ -78,8 +79,12 @@ def tensor_bytes(tensors, data, name: str, extra: int = 0) -> np.ndarray:
 
 def ternary_tensor(tensors, data, name: str):
     """(trits (rows, cols) int8, per-tensor scale float32) of an I2_S, TQ1_0 or TQ2_0 tensor."""
-    shape, t, _ = tensors[name]
+    shape, t, off = tensors[name]
     cols, rows = shape
+    if t == VELUREX:  # a pre-transcoded container's tensor: planar velurex rows, the f32 scale behind them
+        nbytes = rows * ((cols + 159) // 160) * 32
+        raw = np.frombuffer(bytes(data[off:off + nbytes + 4]), np.uint8)
+        return oracle.unpack_planar(raw[:-4], rows, cols), np.frombuffer(raw[-4:].tobytes(), np.float32)[0]
     if t == I2_S:
         raw = tensor_bytes(tensors, data, name, extra=4)
         scale = np.frombuffer(raw[-4:].tobytes(), np.float32)[0]
@@ -118,7 +123,7 @@ def model_spec(path, ctx: int | None = None) -> dict:
         for k, nm in enumerate(("attn_norm", "ffn_norm", "attn_sub_norm", "ffn_sub_norm")):
             norms.append(f32(f"blk.{l}.{nm}.weight") if (k < 2 or arch == 1) else None)
     return {
-        "arch": arch, "f32_values": not any(t == I2_S for _, t, _ in tensors.values()), "hidden": hidden, "inter": inter, "layers": layers,
+        "arch": arch, "f32_values": bool(meta["quintrit_b200.f32_values"]) if "quintrit_b200.f32_values" in meta else not any(t == I2_S for _, t, _ in tensors.values()), "hidden": hidden, "inter": inter, "layers": layers,
         "q_heads": heads, "kv_heads": kv_heads, "head_dim": head_dim, "vocab": vocab, "ctx": want, "rope_dims": g("rope.dimension_count", head_dim),
         "eps": float(g("attention.layer_norm_rms_epsilon", 1e-5)), "rope_theta": float(g("rope.freq_base", 500000.0)),
         "embed": tab("token_embd.weight"), "lm_head": tab("output.weight") if "output.weight" in tensors else None,

@@ -1359,6 +1359,9 @@ int read_shape(const GgufFile& g, GgufModelShape* out) {
         m.has_i2s |= kv.second.type == kGgmlI2S;
         m.has_q2 |= kv.second.type == kGgmlQ2;
     }
+    // a pre-transcoded container records which attention numerics its source file selected (config.rs:425-429 decides by tensor type)
+    if (const GgufValue* v = g.find("quintrit_b200.f32_values"))
+        if (v->is_int()) m.has_i2s = v->u == 0;
     m.tied = g.tensor("output.weight") == nullptr;
     return QUINTRIT_OK;
 }
@@ -1369,13 +1372,18 @@ int projection(const GgufFile& g, const std::string& name, uint64_t rows, uint64
                float* scale) {
     const GgufTensor* t = g.tensor(name);
     if (t == nullptr) return fail(QUINTRIT_ERR_MODEL, "Missing %s", name.c_str());
-    if (t->type != kGgmlI2S && t->type != kGgmlTq1 && t->type != kGgmlTq2 && t->type != kGgmlQ2)
+    if (t->type != kGgmlI2S && t->type != kGgmlTq1 && t->type != kGgmlTq2 && t->type != kGgmlQ2 && t->type != kGgmlVelurex)
         return fail(QUINTRIT_ERR_UNSUPPORTED, "%s has GGML type %u; the GPU decoder needs I2_S, TQ1_0, TQ2_0 or Q2_0 projections", name.c_str(), t->type);
     if (t->shape.size() != 2 || t->shape[0] != cols || t->shape[1] != rows)
         return fail(QUINTRIT_ERR_MODEL, "%s does not have the shape %llu x %llu", name.c_str(), static_cast<unsigned long long>(rows), static_cast<unsigned long long>(cols));
     *data = g.data(*t, len);
     if (*data == nullptr) return fail(QUINTRIT_ERR_FORMAT, "the payload of %s does not lie inside the file", name.c_str());
     *source = static_cast<int32_t>(t->type);
+    if (t->type == kGgmlVelurex) {  // the container's planar velurex rows: nothing to decode, the scale sits behind the payload as I2_S has it
+        *source = kSrcPlanar;
+        if (!g.trailing_scale(*t, scale)) return fail(QUINTRIT_ERR_FORMAT, "the scale of %s does not lie inside the file", name.c_str());
+        return QUINTRIT_OK;
+    }
     if (t->type == kGgmlQ2) {  // one scale per 64 weights inside the payload: no tensor scale
         *scale = 1.0f;
         return QUINTRIT_OK;

@@ -21,7 +21,10 @@
 
 namespace qtb {
 
-enum GgmlType : uint32_t { kGgmlF32 = 0, kGgmlF16 = 1, kGgmlQ8_0 = 8, kGgmlBF16 = 30, kGgmlTq1 = 34, kGgmlTq2 = 35, kGgmlI2S = 36, kGgmlQ2 = 42 };
+enum GgmlType : uint32_t { kGgmlF32 = 0, kGgmlF16 = 1, kGgmlQ8_0 = 8, kGgmlBF16 = 30, kGgmlTq1 = 34, kGgmlTq2 = 35, kGgmlI2S = 36, kGgmlQ2 = 42,
+                           // not a GGML type: a projection already transcoded to planar velurex rows (ceil(cols / 160) blocks of 32 bytes per row) with its
+                           // f32 scale behind the payload, as the pre-transcoded container of this library stores it (quintrit_b200/container.py)
+                           kGgmlVelurex = 0x5156 };
 
 struct GgufValue {
     uint32_t type = 0;      // the GGUF value type; arrays keep only their element type and count
@@ -59,6 +62,7 @@ struct GgufTensor {
             case kGgmlBF16: return n * 2;
             case kGgmlQ8_0: return n % 32 == 0 ? n / 32 * 34 : 0;
             case kGgmlI2S: return (n + 3) / 4;
+            case kGgmlVelurex: return shape.size() == 2 ? shape[1] * ((shape[0] + 159) / 160) * 32 : 0;  // rows x planar row bytes
             case kGgmlTq1: return n % 256 == 0 ? n / 256 * 54 : 0;
             case kGgmlTq2: return n % 256 == 0 ? n / 256 * 66 : 0;
             case kGgmlQ2: return n % 64 == 0 ? n / 64 * 18 : 0;

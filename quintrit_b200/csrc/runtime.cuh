@@ -390,6 +390,7 @@ const char* rt_type_name(uint32_t t) {
         case kGgmlTq1: return "TQ1_0";
         case kGgmlTq2: return "TQ2_0";
         case kGgmlI2S: return "I2_S";
+        case kGgmlVelurex: return "VELUREX";
         case kGgmlQ2: return "Q2_0";
         default: return "UNKNOWN";
     }
