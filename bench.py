@@ -423,6 +423,56 @@ def run_block_scaled(args, local_rank: int):
     return out
 
 
+def run_moe(args, local_rank: int):
+    """One mixture-of-experts feed-forward block of the Qwen3-30B-A3B shape (hidden 2048, 128 experts of width 768, top-8 softmax routing,
+    BF16 router, ternary experts) for a batch of 16 tokens on one GPU: device time of the block's launches, the time of the C call with host
+    buffers, and two tokens checked against the composition of the reference's pieces (oracle/moe.py). The block only: attention, norms and
+    the exchange between GPUs of an expert-parallel model are not part of it."""
+    import torch
+
+    import quintrit_b200 as q
+
+    dev = torch.device("cuda", local_rank)
+    H, I, E, K, B = 2048, 768, 128, 8, 16
+    cfg = 4
+    t0 = time.time()
+    gu, dn, scales = [], [], []
+    for e in range(E):
+        g = synth.torch_planar(synth.seed_for(cfg, e, 4, 0), I, H, dev).cpu().numpy().reshape(-1)
+        u = synth.torch_planar(synth.seed_for(cfg, e, 5, 0), I, H, dev).cpu().numpy().reshape(-1)
+        gu.append(np.concatenate([g, u]))
+        dn.append(synth.torch_planar(synth.seed_for(cfg, e, 6, 0), H, I, dev).cpu().numpy().reshape(-1))
+        scales.append([synth.weight_scale(synth.seed_for(cfg, e, p, 1)) for p in (4, 5, 6)])
+    router = synth.table_bits_np(synth.seed_for(cfg, 254, 0, 0), E * H, bf16=True)
+    block = q.Moe(H, I, K, router, gu, dn, np.array(scales, np.float32), max_batch=B, device=local_rank)
+    setup_s = time.time() - t0
+    x = np.stack([synth.normal_f32(synth.seed_for(cfg, 253, b, 2), H) for b in range(B)])
+    out, ids, w = block.forward(x)
+    parity = None
+    if not args.no_cpu:
+        from oracle import moe as omoe
+
+        same = True
+        for b in (0, B - 1):
+            want, want_ids, want_w = omoe.forward(x[b], router, gu, dn, np.array(scales, np.float32), H, I, K)
+            same = same and list(ids[b]) == list(want_ids) and np.array_equal(w[b].view(np.uint32), want_w.view(np.uint32)) and np.array_equal(out[b].view(np.uint32), want.view(np.uint32))
+        parity = {"tokens_checked": 2, "bit_exact": bool(same), "oracle": "composition of the reference's pieces (no reference run exists for this block: parity unpinned)"}
+    for _ in range(3):
+        block.forward(x)
+    t1 = time.perf_counter()
+    for _ in range(args.steps):
+        block.forward(x)
+    e2e_ms = (time.perf_counter() - t1) * 1e3 / args.steps
+    ms = block.time_ms(B, max(args.steps, 20))
+    weights = B * K * 3 * I * H
+    experts_used = len(set(int(i) for i in ids.reshape(-1)))
+    block.free()
+    return {"shape": "qwen3_30b_a3b FFN block", "hidden": H, "expert_width": I, "experts": E, "top_k": K, "batch": B, "ms_per_block": round(ms, 4), "ms_per_block_host_buffers": round(e2e_ms, 4),
+            "weights_streamed": weights, "gweights_per_s": round(weights / (ms * 1e-3) / 1e9, 1), "hbm_frac_of_measured": round(weights * BYTES_PER_WEIGHT / (ms * 1e-3) / 1e9 / measured_peaks()[0], 4),
+            "distinct_experts_in_batch": experts_used, "tokens_per_s_ffn_blocks_of_48_layers": round(B / (48 * ms * 1e-3), 1), "setup_s": round(setup_s, 1), "parity_vs_cpu": parity,
+            "note": "every (token, expert) pair streams its expert's weights (no sharing between tokens that chose the same expert); one GPU, no expert parallelism"}
+
+
 def cpu_decode(shape: str, layers, prompt_len: int, tail: int = 32):
     """The CPU oracle's whole-token decode on the host cores: the seeded prompt is ingested token by token (the reference
     ingests prompts this way, engine.rs:626-631) and the time per token is the mean over the last `tail` positions, i.e. at
@@ -772,6 +822,11 @@ def run_ours(args, rank: int, world: int, local_rank: int):
             line["decode"] = run_decode(args, local_rank)
         except Exception as e:  # the sweep line must still be printed
             line["decode"] = {"error": f"{type(e).__name__}: {e}"}
+    if world == 1 and not args.no_moe:
+        try:
+            line["moe"] = run_moe(args, local_rank)
+        except Exception as e:
+            line["moe"] = {"error": f"{type(e).__name__}: {e}"}
     if world == 1 and not args.no_cpu:
         threads = pin_to_all_cores()
         sweep = CpuSweep(args.layers)
@@ -802,6 +857,8 @@ def main():
     ap.add_argument("--block-scaled-only", action="store_true", help="run only the block-scaled (Q2_0) projection on the model's shapes (profiling aid)")
     ap.add_argument("--decode-shape", default="falcon3_10b", choices=["falcon3_10b", "bitnet_2b"])
     ap.add_argument("--decode-layers", type=int, default=None, help="fewer layers than the shape has (experiments)")
+    ap.add_argument("--moe-only", action="store_true", help="run only the mixture-of-experts block leg and print its object")
+    ap.add_argument("--no-moe", action="store_true", help="skip the mixture-of-experts block leg")
     ap.add_argument("--batch-seqs", type=int, default=32, help="sequences of the batched-decode leg (0 skips it)")
     ap.add_argument("--batch-only", action="store_true", help="with --decode-only: run only the batched-decode leg (profiling aid)")
     ap.add_argument("--batch-steps", type=int, default=16, help="greedy steps timed in the batched-decode leg")
@@ -830,6 +887,9 @@ def main():
         return
     if args.block_scaled_only:
         print(json.dumps({"block_scaled": run_block_scaled(args, local_rank)}), flush=True)
+        return
+    if args.moe_only:
+        print(json.dumps({"moe": run_moe(args, local_rank)}), flush=True)
         return
     if args.decode_only:
         print(json.dumps({"decode": run_decode(args, local_rank)}), flush=True)

@@ -357,6 +357,28 @@ int quintrit_b200_selftest_barrier(uint32_t device_index, uint32_t ctas, uint32_
 int quintrit_b200_decoder_prefill(quintrit_b200_decoder_t* decoder, const uint32_t* tokens, size_t count, uint32_t pos, float* logits, size_t logits_capacity,
                                   uint32_t* out_token);
 
+/* ---- mixture-of-experts feed-forward block (BASELINE's Qwen3-30B-A3B shape: softmax router, top-k of n experts, ternary SwiGLU experts) ----
+ * The reference has no block of this kind (its Moe is Nemotron-H's, quintrit-runtime/src/hybrid.rs:798-869); this one is composed of
+ * the reference's pieces, each computed as the reference computes it: the router as a BF16 projection (hybrid.rs:327-333), softmax
+ * (ops.rs:274-298), experts by descending probability as std::sort leaves them (hybrid.rs:828-831), their probabilities divided by
+ * their sum (hybrid.rs:833-839), an expert as the dense model's FFN (int8 absmax activations, exact integer sums, one multiply by
+ * weight_scale / act_scale, SwiGLU: layer.rs:123-177, ops.rs:241-267, 427-464), the weighted outputs added in selection order
+ * (hybrid.rs:847-858). One GPU; the experts of a batch run as two persistent GEMV launches whose work lists are built on the device
+ * from the chosen ids.
+ *
+ * router_bf16: n_experts x hidden BF16 bit patterns. gate_up[e]: a matrix of 2 * inter rows (the expert's gate rows, then its up
+ * rows) x hidden columns; down[e]: hidden x inter; scales[3 e + 0 / 1 / 2]: the weight scales of expert e's gate, up and down. The
+ * matrices stay the caller's and must outlive the block. hidden is a multiple of 128 (at most 3200), inter a multiple of 16. */
+typedef struct quintrit_b200_moe quintrit_b200_moe_t;
+int quintrit_b200_moe_create(uint32_t device_index, uint32_t hidden, uint32_t inter, uint32_t n_experts, uint32_t top_k, uint32_t max_batch, const uint16_t* router_bf16,
+                             const quintrit_b200_matrix_t* const* gate_up, const quintrit_b200_matrix_t* const* down, const float* scales, quintrit_b200_moe_t** out_moe);
+void quintrit_b200_moe_free(quintrit_b200_moe_t* moe);
+/* batch tokens (x: [batch][hidden] floats in host memory) through the block; out: [batch][hidden]; out_experts / out_weights
+ * ([batch][top_k], may be NULL): the chosen experts in selection order and their weights. */
+int quintrit_b200_moe_forward(quintrit_b200_moe_t* moe, const float* x, size_t batch, float* out, uint32_t* out_experts, float* out_weights);
+/* Device time of the block's launches for the inputs of the last forward call, averaged over `repeats` back-to-back runs. */
+int quintrit_b200_moe_time(quintrit_b200_moe_t* moe, size_t batch, uint32_t repeats, float* out_ms);
+
 /* ---- the token sampler on the device (temperature, top-k, nucleus; quintrit-runtime/src/sampler.rs:59-143) ----------------
  * The runtime level (quintrit_session_generate) samples on the device when 1 <= top_k <= 1024: the logits never leave the GPU and
  * the sampled token is the next step's input there. This entry runs the same kernel on `count` logits of the caller's (host

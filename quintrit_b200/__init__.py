@@ -12,6 +12,7 @@ from .api import (  # noqa: F401
     Decoder,
     DeviceInfo,
     Matrix,
+    Moe,
     Plan,
     QuintritError,
     SRC_I2_S,

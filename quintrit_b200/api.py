@@ -542,6 +542,57 @@ class Batch:
             pass
 
 
+class Moe:
+    """A mixture-of-experts feed-forward block on the GPU (``quintrit_b200_moe_*``): softmax router over BF16 rows, top-k experts, every
+    expert a ternary SwiGLU FFN. ``gate_up[e]`` / ``down[e]``: planar velurex rows (gate rows then up rows; down rows), ``scales[e]`` =
+    (gate, up, down)."""
+
+    def __init__(self, hidden: int, inter: int, top_k: int, router_bits, gate_up, down, scales, max_batch: int = 16, device: int = 0):
+        n = len(gate_up)
+        self.hidden, self.inter, self.top_k, self.n_experts, self.max_batch = hidden, inter, top_k, n, max_batch
+        self.matrices = [Matrix(w, 2 * inter, hidden, device=device) for w in gate_up] + [Matrix(w, hidden, inter, device=device) for w in down]
+        gu = (C.c_void_p * n)(*[m.handle for m in self.matrices[:n]])
+        dn = (C.c_void_p * n)(*[m.handle for m in self.matrices[n:]])
+        rb = np.ascontiguousarray(router_bits, dtype=np.uint16).reshape(-1)
+        sc = np.ascontiguousarray(scales, dtype=np.float32).reshape(-1)
+        assert rb.size == n * hidden and sc.size == 3 * n
+        self._h = C.c_void_p()
+        lib = load_library()
+        lib.quintrit_b200_moe_create.argtypes = [C.c_uint32] * 6 + [C.POINTER(C.c_uint16), C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), _f32p, C.POINTER(C.c_void_p)]
+        lib.quintrit_b200_moe_forward.argtypes = [C.c_void_p, _f32p, _sz, _f32p, C.POINTER(C.c_uint32), _f32p]
+        lib.quintrit_b200_moe_time.argtypes = [C.c_void_p, _sz, C.c_uint32, _f32p]
+        lib.quintrit_b200_moe_free.argtypes = [C.c_void_p]
+        lib.quintrit_b200_moe_free.restype = None
+        _check(lib.quintrit_b200_moe_create(device, hidden, inter, n, top_k, max_batch, rb.ctypes.data_as(C.POINTER(C.c_uint16)), gu, dn, _p(sc, _f32p), C.byref(self._h)))
+
+    def forward(self, x):
+        """x: [batch][hidden] floats -> (output [batch][hidden], chosen experts [batch][top_k], weights [batch][top_k])."""
+        xx = np.ascontiguousarray(x, dtype=np.float32).reshape(-1, self.hidden)
+        b = xx.shape[0]
+        out, ids, w = np.zeros((b, self.hidden), np.float32), np.zeros((b, self.top_k), np.uint32), np.zeros((b, self.top_k), np.float32)
+        _check(load_library().quintrit_b200_moe_forward(self._h, _p(xx, _f32p), b, _p(out, _f32p), ids.ctypes.data_as(C.POINTER(C.c_uint32)), _p(w, _f32p)))
+        return out, ids, w
+
+    def time_ms(self, batch: int, repeats: int = 20) -> float:
+        ms = C.c_float(0)
+        _check(load_library().quintrit_b200_moe_time(self._h, batch, repeats, C.byref(ms)))
+        return ms.value
+
+    def free(self) -> None:
+        if self._h:
+            load_library().quintrit_b200_moe_free(self._h)
+            self._h = C.c_void_p()
+        for m in self.matrices:
+            m.free()
+        self.matrices = []
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
 def sample_logits(logits, temperature: float, top_k: int, top_p: float, state: int, device: int = 0):
     """One draw of the device sampler from host logits: returns (token id, new generator state)."""
     lg = np.ascontiguousarray(logits, dtype=np.float32).reshape(-1)

@@ -214,6 +214,7 @@ struct DeviceGuard {
 }  // namespace
 
 #include "decoder.cuh"
+#include "moe.cuh"
 #include "gguf.hpp"
 
 // ---------------------------------------------------------------------------------------------------------------------
@@ -2470,6 +2471,231 @@ extern "C" int quintrit_b200_decoder_prefill(quintrit_b200_decoder_t* decoder, c
         if (out_token) QTB_CUDA(cudaMemcpyAsync(out_token, d->d_token, sizeof(uint32_t), cudaMemcpyDeviceToHost, d->stream));
         if ((rc = decoder_check_status(d)) != QUINTRIT_OK) return rc;  // (the batched projections report a time-out through the same word)
         d->host_pos = pos + static_cast<uint32_t>(count);
+        return ok();
+    });
+}
+
+// ---- mixture-of-experts feed-forward block ------------------------------------------------------------------------------------------
+struct quintrit_b200_moe {
+    uint32_t magic;
+    int device, sm_count;
+    int hidden, inter, inter_pad, n_experts, top_k, max_batch, chunks_down;
+    std::vector<void*> allocs;
+    __half *router = nullptr, *x16 = nullptr;
+    MoeExpertRef* experts = nullptr;
+    float *x = nullptr, *s_x = nullptr, *logits = nullptr, *probs = nullptr, *weights = nullptr, *s_i = nullptr, *out = nullptr;
+    int8_t *a8_x = nullptr, *a8_i = nullptr;
+    uint32_t* chosen = nullptr;
+    unsigned int *tie = nullptr, *counters = nullptr;
+    int32_t *acc_gu = nullptr, *acc_down = nullptr;
+    GemvItem *gu_items = nullptr, *down_items = nullptr;
+    cudaStream_t stream = nullptr;
+};
+
+namespace {
+
+constexpr uint32_t kMagicMoe = 0x51544258u;  // "QTBX"
+
+int check_moe(const quintrit_b200_moe* m) {
+    if (m == nullptr || m->magic != kMagicMoe) return fail(QUINTRIT_ERR_INVALID_HANDLE, "mixture-of-experts handle is NULL, freed or of the wrong type");
+    return QUINTRIT_OK;
+}
+
+void destroy_moe(quintrit_b200_moe* m) {
+    if (m == nullptr) return;
+    DeviceGuard g(m->device);
+    if (m->stream) cudaStreamDestroy(m->stream);
+    for (void* p : m->allocs) cudaFree(p);
+    m->magic = 0;
+    delete m;
+}
+
+template <typename T>
+int moe_alloc(quintrit_b200_moe* m, T** p, size_t count) {
+    void* q = nullptr;
+    const size_t bytes = std::max<size_t>(count * sizeof(T), 16);
+    cudaError_t e = cudaMalloc(&q, bytes);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc(mixture-of-experts buffer)");
+    m->allocs.push_back(q);
+    if ((e = cudaMemset(q, 0, bytes)) != cudaSuccess) return cuda_fail(e, "cudaMemset(mixture-of-experts buffer)");
+    *p = static_cast<T*>(q);
+    return QUINTRIT_OK;
+}
+
+// The launches of one batch on the block's stream; x is on the device in m->x, the result lands in m->out.
+int moe_enqueue(quintrit_b200_moe* m, int batch) {
+    cudaStream_t s = m->stream;
+    const int H = m->hidden, I = m->inter, E = m->n_experts, K = m->top_k, nz = batch * K;
+    moe_prepare_kernel<<<batch, kRowThreads, H * sizeof(float), s>>>(m->x, H, m->x16, m->a8_x, m->s_x);
+    QTB_LAUNCH_CHECK();
+    lm_head_batch_kernel<<<dim3(std::min(m->sm_count, (E + 31) / 32), (batch + kHeadTokens - 1) / kHeadTokens), kHeadThreads, lm_head_batch_smem(H), s>>>(m->router, m->x16, H, E, batch,
+                                                                                                                                                         m->logits, true);
+    QTB_LAUNCH_CHECK();
+    moe_select_kernel<<<batch, 256, (E + K) * sizeof(float), s>>>(m->logits, E, K, m->probs, m->chosen, m->weights, m->tie);
+    QTB_LAUNCH_CHECK();
+    return QUINTRIT_OK;
+}
+int moe_enqueue_experts(quintrit_b200_moe* m, int batch) {
+    cudaStream_t s = m->stream;
+    const int H = m->hidden, I = m->inter, K = m->top_k, nz = batch * K;
+    const int pairs_gu = ((H + kBlockTrits - 1) / kBlockTrits + 1) / 2, pairs_d = ((I + kBlockTrits - 1) / kBlockTrits + 1) / 2;
+    const int n_gu = nz * pairs_gu, n_d = nz * pairs_d * m->chunks_down;
+    moe_items_kernel<<<(n_gu + n_d + 255) / 256, 256, 0, s>>>(m->experts, m->chosen, nz, K, H, I, m->inter_pad, m->chunks_down, m->gu_items, m->down_items);
+    QTB_LAUNCH_CHECK();
+    QTB_CUDA(cudaMemsetAsync(m->acc_gu, 0, size_t(nz) * 2 * I * sizeof(int32_t), s));
+    QTB_CUDA(cudaMemsetAsync(m->acc_down, 0, size_t(nz) * H * sizeof(int32_t), s));
+    int rc = launch_gemv(m->gu_items, n_gu, m->a8_x, m->acc_gu, m->counters, m->sm_count, s);
+    if (rc != QUINTRIT_OK) return rc;
+    moe_act_quant_kernel<<<nz, kRowThreads, I * sizeof(float), s>>>(m->acc_gu, m->experts, m->chosen, m->s_x, K, I, m->inter_pad, m->a8_i, m->s_i);
+    QTB_LAUNCH_CHECK();
+    if ((rc = launch_gemv(m->down_items, n_d, m->a8_i, m->acc_down, m->counters, m->sm_count, s)) != QUINTRIT_OK) return rc;
+    moe_combine_kernel<<<dim3((H + 255) / 256, batch), 256, 0, s>>>(m->acc_down, m->experts, m->chosen, m->weights, m->s_i, K, H, m->out);
+    QTB_LAUNCH_CHECK();
+    return QUINTRIT_OK;
+}
+
+}  // namespace
+
+extern "C" int quintrit_b200_moe_create(uint32_t device_index, uint32_t hidden, uint32_t inter, uint32_t n_experts, uint32_t top_k, uint32_t max_batch, const uint16_t* router_bf16,
+                                        const quintrit_b200_matrix_t* const* gate_up, const quintrit_b200_matrix_t* const* down, const float* scales,
+                                        quintrit_b200_moe_t** out_moe) {
+    return guard([&]() -> int {
+        if (out_moe == nullptr) return fail(QUINTRIT_ERR_NULL_POINTER, "out_moe is NULL");
+        *out_moe = nullptr;
+        if (router_bf16 == nullptr || gate_up == nullptr || down == nullptr || scales == nullptr) return fail(QUINTRIT_ERR_NULL_POINTER, "router_bf16, gate_up, down or scales is NULL");
+        if (hidden == 0 || hidden % 128 != 0 || lm_head_batch_smem(static_cast<int>(hidden)) > 200 * 1024)
+            return fail(QUINTRIT_ERR_UNSUPPORTED, "the hidden size %u must be a multiple of 128, at most 3200", hidden);
+        if (inter == 0 || inter % 16 != 0 || inter > 49152) return fail(QUINTRIT_ERR_UNSUPPORTED, "the expert width %u must be a multiple of 16, at most 49152", inter);
+        if (n_experts == 0 || n_experts > 1024 || top_k == 0 || top_k > n_experts || top_k > 64) return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "%u experts with top-%u routing are not supported (at most 1024 experts, top-64)", n_experts, top_k);
+        if (max_batch == 0 || max_batch > 256) return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "max_batch must be in [1, 256]");
+        cudaDeviceProp prop;
+        int rc = require_b200(static_cast<int>(device_index), &prop);
+        if (rc != QUINTRIT_OK) return rc;
+        std::vector<MoeExpertRef> refs(n_experts);
+        for (uint32_t e = 0; e < n_experts; ++e) {
+            if ((rc = check_matrix(gate_up[e])) != QUINTRIT_OK || (rc = check_matrix(down[e])) != QUINTRIT_OK) return rc;
+            if (gate_up[e]->device != static_cast<int>(device_index) || down[e]->device != static_cast<int>(device_index)) return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "expert %u lives on another device", e);
+            if (gate_up[e]->rows != size_t(2) * inter || gate_up[e]->cols != hidden)
+                return fail(QUINTRIT_ERR_INVALID_SHAPE, "gate_up of expert %u is %zu x %zu, the block needs %u x %u (gate rows, then up rows)", e, gate_up[e]->rows, gate_up[e]->cols, 2 * inter, hidden);
+            if (down[e]->rows != hidden || down[e]->cols != inter) return fail(QUINTRIT_ERR_INVALID_SHAPE, "down of expert %u is %zu x %zu, the block needs %u x %u", e, down[e]->rows, down[e]->cols, hidden, inter);
+            refs[e] = MoeExpertRef{gate_up[e]->d_w, down[e]->d_w, scales[3 * e], scales[3 * e + 1], scales[3 * e + 2], 0};
+        }
+        DeviceGuard g(static_cast<int>(device_index));
+        if ((rc = upload_exp2_table()) != QUINTRIT_OK) return rc;
+        GemvKernel k = nullptr;
+        if ((rc = gemv_kernel_for_device(static_cast<int>(device_index), &k)) != QUINTRIT_OK) return rc;
+        int smem_optin = 0;
+        QTB_CUDA(cudaDeviceGetAttribute(&smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, static_cast<int>(device_index)));
+        if ((rc = allow_max_dynamic_smem(lm_head_batch_kernel, smem_optin)) != QUINTRIT_OK || (rc = allow_max_dynamic_smem(moe_prepare_kernel, smem_optin)) != QUINTRIT_OK ||
+            (rc = allow_max_dynamic_smem(moe_act_quant_kernel, smem_optin)) != QUINTRIT_OK)
+            return rc;
+        quintrit_b200_moe* m = new quintrit_b200_moe();
+        m->magic = kMagicMoe, m->device = static_cast<int>(device_index), m->sm_count = prop.multiProcessorCount;
+        m->hidden = static_cast<int>(hidden), m->inter = static_cast<int>(inter), m->inter_pad = static_cast<int>((inter + 15) / 16 * 16);
+        m->n_experts = static_cast<int>(n_experts), m->top_k = static_cast<int>(top_k), m->max_batch = static_cast<int>(max_batch);
+        const int tiles_d = (m->hidden + kTileRows - 1) / kTileRows;
+        m->chunks_down = std::max(1, tiles_d / 32);  // down items of about 32 row tiles
+        const size_t B = max_batch, Z = B * top_k, H = hidden, I = inter, E = n_experts;
+        const size_t pairs_gu = ((H + kBlockTrits - 1) / kBlockTrits + 1) / 2, pairs_d = ((I + kBlockTrits - 1) / kBlockTrits + 1) / 2;
+        auto bail = [&](int code) {
+            destroy_moe(m);
+            return code;
+        };
+        if ((rc = moe_alloc(m, &m->router, E * H)) != QUINTRIT_OK || (rc = moe_alloc(m, &m->experts, E)) != QUINTRIT_OK || (rc = moe_alloc(m, &m->x, B * H)) != QUINTRIT_OK ||
+            (rc = moe_alloc(m, &m->x16, B * H)) != QUINTRIT_OK || (rc = moe_alloc(m, &m->a8_x, B * H + 256)) != QUINTRIT_OK || (rc = moe_alloc(m, &m->s_x, B)) != QUINTRIT_OK ||
+            (rc = moe_alloc(m, &m->logits, B * E)) != QUINTRIT_OK || (rc = moe_alloc(m, &m->probs, B * E)) != QUINTRIT_OK || (rc = moe_alloc(m, &m->chosen, Z)) != QUINTRIT_OK ||
+            (rc = moe_alloc(m, &m->weights, Z)) != QUINTRIT_OK || (rc = moe_alloc(m, &m->tie, B)) != QUINTRIT_OK || (rc = moe_alloc(m, &m->counters, 4)) != QUINTRIT_OK ||
+            (rc = moe_alloc(m, &m->acc_gu, Z * 2 * I)) != QUINTRIT_OK || (rc = moe_alloc(m, &m->a8_i, Z * m->inter_pad + 256)) != QUINTRIT_OK || (rc = moe_alloc(m, &m->s_i, Z)) != QUINTRIT_OK ||
+            (rc = moe_alloc(m, &m->acc_down, Z * H)) != QUINTRIT_OK || (rc = moe_alloc(m, &m->out, B * H)) != QUINTRIT_OK || (rc = moe_alloc(m, &m->gu_items, Z * pairs_gu)) != QUINTRIT_OK ||
+            (rc = moe_alloc(m, &m->down_items, Z * pairs_d * m->chunks_down)) != QUINTRIT_OK)
+            return bail(rc);
+        cudaError_t e = cudaMemcpy(m->router, router_bf16, E * H * sizeof(uint16_t), cudaMemcpyHostToDevice);
+        if (e == cudaSuccess) e = cudaMemcpy(m->experts, refs.data(), E * sizeof(MoeExpertRef), cudaMemcpyHostToDevice);
+        if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking);
+        if (e != cudaSuccess) {
+            destroy_moe(m);
+            return cuda_fail(e, "set-up of the mixture-of-experts block");
+        }
+        *out_moe = m;
+        return ok();
+    });
+}
+
+extern "C" void quintrit_b200_moe_free(quintrit_b200_moe_t* moe) {
+    if (moe == nullptr || moe->magic != kMagicMoe) return;
+    destroy_moe(moe);
+}
+
+extern "C" int quintrit_b200_moe_forward(quintrit_b200_moe_t* moe, const float* x, size_t batch, float* out, uint32_t* out_experts, float* out_weights) {
+    return guard([&]() -> int {
+        int rc = check_moe(moe);
+        if (rc != QUINTRIT_OK) return rc;
+        quintrit_b200_moe* m = moe;
+        if (x == nullptr || out == nullptr) return fail(QUINTRIT_ERR_NULL_POINTER, "x or out is NULL");
+        if (batch == 0 || batch > static_cast<size_t>(m->max_batch)) return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "a batch of %zu tokens (the block was made for 1 to %d)", batch, m->max_batch);
+        DeviceGuard g(m->device);
+        cudaStream_t s = m->stream;
+        const int B = static_cast<int>(batch), K = m->top_k, E = m->n_experts;
+        QTB_CUDA(cudaMemcpyAsync(m->x, x, batch * m->hidden * sizeof(float), cudaMemcpyHostToDevice, s));
+        if ((rc = moe_enqueue(m, B)) != QUINTRIT_OK) return rc;
+        // Experts with exactly equal probabilities: std::sort (the reference's choice, hybrid.rs:828-831) orders them by its algorithm. The
+        // device ranks such ties by id and flags the token; the host then sorts that token's experts with the standard library's std::sort
+        // and replaces the device's choice and weights.
+        std::vector<unsigned int> tie(batch);
+        QTB_CUDA(cudaMemcpyAsync(tie.data(), m->tie, batch * sizeof(unsigned int), cudaMemcpyDeviceToHost, s));
+        QTB_CUDA(cudaStreamSynchronize(s));
+        for (int b = 0; b < B; ++b) {
+            if (tie[b] == 0) continue;
+            std::vector<float> p(E);
+            QTB_CUDA(cudaMemcpy(p.data(), m->probs + size_t(b) * E, E * sizeof(float), cudaMemcpyDeviceToHost));
+            std::vector<uint32_t> order(E);
+            for (int i = 0; i < E; ++i) order[i] = static_cast<uint32_t>(i);
+            std::sort(order.begin(), order.end(), [&](uint32_t a, uint32_t c) { return p[a] > p[c]; });
+            std::vector<float> w(K);
+            double sum = 0.0;
+            for (int i = 0; i < K; ++i) w[i] = p[order[i]], sum += static_cast<double>(w[i]);
+            const float sc = std::max(static_cast<float>(sum), 6.103515625e-5f);
+            for (int i = 0; i < K; ++i) w[i] /= sc;
+            QTB_CUDA(cudaMemcpy(m->chosen + size_t(b) * K, order.data(), K * sizeof(uint32_t), cudaMemcpyHostToDevice));
+            QTB_CUDA(cudaMemcpy(m->weights + size_t(b) * K, w.data(), K * sizeof(float), cudaMemcpyHostToDevice));
+        }
+        if ((rc = moe_enqueue_experts(m, B)) != QUINTRIT_OK) return rc;
+        QTB_CUDA(cudaMemcpyAsync(out, m->out, batch * m->hidden * sizeof(float), cudaMemcpyDeviceToHost, s));
+        if (out_experts) QTB_CUDA(cudaMemcpyAsync(out_experts, m->chosen, batch * K * sizeof(uint32_t), cudaMemcpyDeviceToHost, s));
+        if (out_weights) QTB_CUDA(cudaMemcpyAsync(out_weights, m->weights, batch * K * sizeof(float), cudaMemcpyDeviceToHost, s));
+        unsigned int flag = 0;
+        QTB_CUDA(cudaMemcpyAsync(&flag, m->counters + 2, sizeof flag, cudaMemcpyDeviceToHost, s));
+        QTB_CUDA(cudaStreamSynchronize(s));
+        if (flag != 0) return fail(QUINTRIT_ERR_DEVICE, "GEMV kernel on the CUDA device found its shared-memory table at an unexpected address");
+        return ok();
+    });
+}
+
+extern "C" int quintrit_b200_moe_time(quintrit_b200_moe_t* moe, size_t batch, uint32_t repeats, float* out_ms) {
+    return guard([&]() -> int {
+        int rc = check_moe(moe);
+        if (rc != QUINTRIT_OK) return rc;
+        quintrit_b200_moe* m = moe;
+        if (out_ms == nullptr) return fail(QUINTRIT_ERR_NULL_POINTER, "out_ms is NULL");
+        if (batch == 0 || batch > static_cast<size_t>(m->max_batch) || repeats == 0) return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "batch must be in [1, %d] and repeats at least 1", m->max_batch);
+        DeviceGuard g(m->device);
+        cudaEvent_t e0, e1;
+        QTB_CUDA(cudaEventCreate(&e0));
+        QTB_CUDA(cudaEventCreate(&e1));
+        QTB_CUDA(cudaEventRecord(e0, m->stream));
+        for (uint32_t r = 0; r < repeats && rc == QUINTRIT_OK; ++r) {
+            rc = moe_enqueue(m, static_cast<int>(batch));
+            if (rc == QUINTRIT_OK) rc = moe_enqueue_experts(m, static_cast<int>(batch));
+        }
+        cudaEventRecord(e1, m->stream);
+        cudaError_t e = cudaStreamSynchronize(m->stream);
+        float ms = 0.0f;
+        if (e == cudaSuccess) e = cudaEventElapsedTime(&ms, e0, e1);
+        cudaEventDestroy(e0);
+        cudaEventDestroy(e1);
+        if (rc != QUINTRIT_OK) return rc;
+        if (e != cudaSuccess) return cuda_fail(e, "timing of the mixture-of-experts block");
+        *out_ms = ms / static_cast<float>(repeats);
         return ok();
     });
 }
