@@ -1252,16 +1252,19 @@ __global__ void __launch_bounds__(kSampleThreads) sample_topk_kernel(const float
         o_val[rank] = __fmul_rn(logits[ix], inv_temp);
     }
     __syncthreads();
-    if (tid != 0) return;
-    float mx = o_val[0];
-    for (int i = 0; i < m; ++i)
-        if (o_val[i] > mx) mx = o_val[i];
-    double sum = 0.0;
-    for (int i = 0; i < m; ++i) {
-        const float p = device_expf(__fsub_rn(o_val[i], mx));
-        o_val[i] = p;
-        sum += static_cast<double>(p);
+    __shared__ float s_mx;
+    if (tid == 0) {
+        float mx = o_val[0];
+        for (int i = 0; i < m; ++i)
+            if (o_val[i] > mx) mx = o_val[i];
+        s_mx = mx;
     }
+    __syncthreads();
+    if (tid < m) o_val[tid] = device_expf(__fsub_rn(o_val[tid], s_mx));  // every exponential on its own; the sums below stay in candidate order
+    __syncthreads();
+    if (tid != 0) return;
+    double sum = 0.0;
+    for (int i = 0; i < m; ++i) sum += static_cast<double>(o_val[i]);
     if (sum > 0.0) {
         const float inv = __double2float_rn(1.0 / sum);
         for (int i = 0; i < m; ++i) o_val[i] = __fmul_rn(o_val[i], inv);

@@ -54,21 +54,23 @@ __global__ void __launch_bounds__(256) moe_select_kernel(const float* __restrict
     for (int i = tid; i < n_experts; i += 256) p_s[i] = logits[b * n_experts + i];
     if (tid == 0) tie[b] = 0u;
     __syncthreads();
+    __shared__ float s_mx, s_inv;
     if (tid == 0) {
         float mx = p_s[0];
         for (int i = 1; i < n_experts; ++i)
             if (p_s[i] > mx) mx = p_s[i];
-        double sum = 0.0;
-        for (int i = 0; i < n_experts; ++i) {
-            const float e = device_expf(__fsub_rn(p_s[i], mx));
-            p_s[i] = e;
-            sum += static_cast<double>(e);
-        }
-        if (sum > 0.0) {
-            const float inv = __double2float_rn(1.0 / sum);
-            for (int i = 0; i < n_experts; ++i) p_s[i] = __fmul_rn(p_s[i], inv);
-        }
+        s_mx = mx;
     }
+    __syncthreads();
+    for (int i = tid; i < n_experts; i += 256) p_s[i] = device_expf(__fsub_rn(p_s[i], s_mx));  // (every exponential on its own: any thread may take it)
+    __syncthreads();
+    if (tid == 0) {
+        double sum = 0.0;
+        for (int i = 0; i < n_experts; ++i) sum += static_cast<double>(p_s[i]);  // in the order of the experts, as the reference adds them
+        s_inv = sum > 0.0 ? __double2float_rn(1.0 / sum) : 1.0f;
+    }
+    __syncthreads();
+    for (int i = tid; i < n_experts; i += 256) p_s[i] = __fmul_rn(p_s[i], s_inv);  // (a sum of zero leaves the values as they are: times 1)
     __syncthreads();
     for (int i = tid; i < n_experts; i += 256) {
         const float p = p_s[i];
