@@ -2528,8 +2528,7 @@ int moe_enqueue(quintrit_b200_moe* m, int batch) {
     const int H = m->hidden, I = m->inter, E = m->n_experts, K = m->top_k, nz = batch * K;
     moe_prepare_kernel<<<batch, kRowThreads, H * sizeof(float), s>>>(m->x, H, m->x16, m->a8_x, m->s_x);
     QTB_LAUNCH_CHECK();
-    lm_head_batch_kernel<<<dim3(std::min(m->sm_count, (E + 31) / 32), (batch + kHeadTokens - 1) / kHeadTokens), kHeadThreads, lm_head_batch_smem(H), s>>>(m->router, m->x16, H, E, batch,
-                                                                                                                                                         m->logits, true);
+    moe_router_kernel<<<dim3((E + 3) / 4, (batch + 3) / 4), 128, 0, s>>>(m->router, m->x16, H, E, batch, m->logits);
     QTB_LAUNCH_CHECK();
     moe_select_kernel<<<batch, 256, (E + K) * sizeof(float), s>>>(m->logits, E, K, m->probs, m->chosen, m->weights, m->tie);
     QTB_LAUNCH_CHECK();

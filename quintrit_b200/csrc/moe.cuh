@@ -42,6 +42,45 @@ __global__ void __launch_bounds__(kRowThreads) moe_prepare_kernel(const float* _
     quantize_vector(y_s, hidden, amax, a8 + b * hidden, s_x + b, nullptr, sh_f);
 }
 
+// Router logits: one warp per expert row and group of four tokens. The dot product is ggml_vec_dot_bf16's (ops.rs:688-712): lane l owns the
+// elements 32 i + l, product and sum rounded separately in the order of i, then the lanes are reduced (dot_lane_reduce_bf16), which is what
+// lm_head_kernel does for BF16 tables; a few hundred rows against a handful of tokens are latency, not bandwidth, so the rows are spread
+// over many small blocks instead of the head kernel's few large ones.
+__global__ void __launch_bounds__(128) moe_router_kernel(const __half* __restrict__ router, const __half* __restrict__ x16, int hidden, int n_experts, int batch,
+                                                         float* __restrict__ logits) {
+    // grid (rows / 4, tokens / 4): a warp takes one expert row and four tokens; the elements of eight steps are requested together
+    const int lane = threadIdx.x & 31, row = blockIdx.x * 4 + (threadIdx.x >> 5), b0 = blockIdx.y * 4;
+    if (row >= n_experts) return;
+    const __half* w = router + static_cast<size_t>(row) * hidden + lane;
+    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    const __half* x[4];
+#pragma unroll
+    for (int t = 0; t < 4; ++t) x[t] = x16 + static_cast<size_t>(min(b0 + t, batch - 1)) * hidden + lane;
+    for (int i0 = 0; i0 < hidden; i0 += 256) {
+        unsigned short wr[8], xr[4][8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const int i = i0 + 32 * k;
+            wr[k] = i < hidden ? __half_as_ushort(w[i]) : 0;
+#pragma unroll
+            for (int t = 0; t < 4; ++t) xr[t][k] = i < hidden ? __half_as_ushort(x[t][i]) : 0;
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            if (i0 + 32 * k < hidden) {
+                const float wv = bf16_bits_to_float(wr[k]);
+#pragma unroll
+                for (int t = 0; t < 4; ++t) acc[t] = __fadd_rn(acc[t], __fmul_rn(bf16_bits_to_float(xr[t][k]), wv));
+            }
+        }
+    }
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+        const float sum = dot_lane_reduce_bf16(acc[t]);
+        if (lane == 0 && b0 + t < batch) logits[static_cast<size_t>(b0 + t) * n_experts + row] = sum;
+    }
+}
+
 // One block per token: softmax of the router logits as ops.rs:274-298 writes it (one thread, in order), every expert's rank by
 // counting (descending probability; equal probabilities by lower id, and the token is flagged: std::sort decides such ties by its
 // algorithm, which the host then runs), the first top_k chosen, their probabilities divided by their sum.
