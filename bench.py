@@ -473,6 +473,64 @@ def run_moe(args, local_rank: int):
             "note": "every (token, expert) pair streams its expert's weights (no sharing between tokens that chose the same expert); one GPU, no expert parallelism"}
 
 
+def run_moe_ep(args, rank: int, world: int, local_rank: int, dist):
+    """The mixture-of-experts block of run_moe with its 128 experts spread over the GPUs (expert parallelism): every rank routes all 16 tokens,
+    runs the (token, expert) pairs of the experts it holds and leaves one row of floats per pair; an NCCL all-reduce over the rows viewed as
+    int32 adds the ranks' shares (exactly one share of a value is not zero), then every rank weights and adds the pairs in order. Rank 0 also
+    runs the whole block alone and compares bits. Wall clock around partial forward + all-reduce + finish, maximum over ranks."""
+    import torch
+
+    import quintrit_b200 as q
+
+    dev = torch.device("cuda", local_rank)
+    H, I, E, K, B = 2048, 768, 128, 8, 16
+    cfg = 4
+    if E % world:
+        return {"ep_world": world, "skipped": f"{world} ranks do not divide {E} experts"} if rank == 0 else None
+
+    def expert(e):
+        g = synth.torch_planar(synth.seed_for(cfg, e, 4, 0), I, H, dev).cpu().numpy().reshape(-1)
+        u = synth.torch_planar(synth.seed_for(cfg, e, 5, 0), I, H, dev).cpu().numpy().reshape(-1)
+        d = synth.torch_planar(synth.seed_for(cfg, e, 6, 0), H, I, dev).cpu().numpy().reshape(-1)
+        return np.concatenate([g, u]), d, [synth.weight_scale(synth.seed_for(cfg, e, p, 1)) for p in (4, 5, 6)]
+
+    per = E // world
+    mine = [expert(e) for e in range(rank * per, (rank + 1) * per)]
+    router = synth.table_bits_np(synth.seed_for(cfg, 254, 0, 0), E * H, bf16=True)
+    x = np.stack([synth.normal_f32(synth.seed_for(cfg, 253, b, 2), H) for b in range(B)])
+    block = q.Moe(H, I, K, router, [m[0] for m in mine], [m[1] for m in mine], np.array([m[2] for m in mine], np.float32), max_batch=B, device=local_rank, n_experts=E,
+                  expert_first=rank * per)
+
+    def step():
+        block.forward_partial(x)
+        dist.all_reduce(block.pairs_tensor())
+        torch.cuda.synchronize()
+        return block.finish()
+
+    out, ids, w = step()
+    same = None
+    if rank == 0:
+        everything = [expert(e) for e in range(E)]
+        whole = q.Moe(H, I, K, router, [m[0] for m in everything], [m[1] for m in everything], np.array([m[2] for m in everything], np.float32), max_batch=B, device=local_rank)
+        want, want_ids, want_w = whole.forward(x)
+        same = bool(np.array_equal(out.view(np.uint32), want.view(np.uint32)) and np.array_equal(ids, want_ids) and np.array_equal(w.view(np.uint32), want_w.view(np.uint32)))
+        whole.free()
+    for _ in range(3):
+        step()
+    dist.barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    ms = (time.perf_counter() - t0) * 1e3 / args.steps
+    t = torch.tensor([ms], device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    block.free()
+    if rank != 0:
+        return None
+    return {"shape": "qwen3_30b_a3b FFN block", "ep_world": world, "experts_per_gpu": per, "batch": B, "ms_per_block_host_buffers": round(float(t.item()), 4),
+            "exchange": f"NCCL all-reduce of {B * K * H * 4} bytes (the pairs' rows as int32: one share of every value is not zero)", "identical_to_one_gpu": same}
+
+
 def cpu_decode(shape: str, layers, prompt_len: int, tail: int = 32):
     """The CPU oracle's whole-token decode on the host cores: the seeded prompt is ingested token by token (the reference
     ingests prompts this way, engine.rs:626-631) and the time per token is the mean over the last `tail` positions, i.e. at
@@ -781,6 +839,12 @@ def run_ours(args, rank: int, world: int, local_rank: int):
             decode_tp = run_decode_tp(args, rank, world, local_rank, dist)
         except Exception as e:  # the sweep line must still be printed
             decode_tp = {"tp_world": world, "error": f"{type(e).__name__}: {e}"}
+    moe_ep = None
+    if dist is not None and not args.no_moe:
+        try:
+            moe_ep = run_moe_ep(args, rank, world, local_rank, dist)
+        except Exception as e:  # the sweep line must still be printed
+            moe_ep = {"ep_world": world, "error": f"{type(e).__name__}: {e}"}
     if rank != 0:
         if dist is not None:
             dist.destroy_process_group()
@@ -815,6 +879,8 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         line["prefill"] = prefill
     if decode_tp is not None:
         line["decode"] = decode_tp
+    if moe_ep is not None:
+        line["moe"] = moe_ep
     if world == 1 and not args.no_decode:
         del plan, mats
         torch.cuda.empty_cache()

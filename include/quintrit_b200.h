@@ -376,8 +376,20 @@ void quintrit_b200_moe_free(quintrit_b200_moe_t* moe);
 /* batch tokens (x: [batch][hidden] floats in host memory) through the block; out: [batch][hidden]; out_experts / out_weights
  * ([batch][top_k], may be NULL): the chosen experts in selection order and their weights. */
 int quintrit_b200_moe_forward(quintrit_b200_moe_t* moe, const float* x, size_t batch, float* out, uint32_t* out_experts, float* out_weights);
-/* Device time of the block's launches for the inputs of the last forward call, averaged over `repeats` back-to-back runs. */
+/* Device time of the block's launches for the inputs of the last forward call (batch = its batch), averaged over `repeats` back-to-back runs. */
 int quintrit_b200_moe_time(quintrit_b200_moe_t* moe, size_t batch, uint32_t repeats, float* out_ms);
+/* Expert parallelism: a block that holds experts expert_first .. expert_first + expert_count - 1 only (gate_up, down and scales list those
+ * experts; the router stays whole on every GPU). Every GPU routes every token (the same choice everywhere), runs the pairs whose expert it
+ * holds, and leaves every pair's result - one row of `hidden` floats per (token, selection slot), zero bits where the expert lives
+ * elsewhere - in a device buffer (quintrit_b200_moe_pairs). The caller adds the buffers of all GPUs as 32-bit integers (exactly one share of
+ * every value is not zero, so the sum is that share bit for bit; with NCCL: an all-reduce of the buffer viewed as int32) and calls
+ * quintrit_b200_moe_finish, which weights and adds the pairs in selection order. The result is the one-GPU result. */
+int quintrit_b200_moe_create_shard(uint32_t device_index, uint32_t hidden, uint32_t inter, uint32_t n_experts, uint32_t top_k, uint32_t max_batch, const uint16_t* router_bf16,
+                                   uint32_t expert_first, uint32_t expert_count, const quintrit_b200_matrix_t* const* gate_up, const quintrit_b200_matrix_t* const* down,
+                                   const float* scales, quintrit_b200_moe_t** out_moe);
+int quintrit_b200_moe_forward_partial(quintrit_b200_moe_t* moe, const float* x, size_t batch);
+int quintrit_b200_moe_pairs(quintrit_b200_moe_t* moe, void** out_device_pointer, size_t* out_floats);
+int quintrit_b200_moe_finish(quintrit_b200_moe_t* moe, size_t batch, float* out, uint32_t* out_experts, float* out_weights);
 
 /* ---- the token sampler on the device (temperature, top-k, nucleus; quintrit-runtime/src/sampler.rs:59-143) ----------------
  * The runtime level (quintrit_session_generate) samples on the device when 1 <= top_k <= 1024: the logits never leave the GPU and

@@ -547,23 +547,33 @@ class Moe:
     expert a ternary SwiGLU FFN. ``gate_up[e]`` / ``down[e]``: planar velurex rows (gate rows then up rows; down rows), ``scales[e]`` =
     (gate, up, down)."""
 
-    def __init__(self, hidden: int, inter: int, top_k: int, router_bits, gate_up, down, scales, max_batch: int = 16, device: int = 0):
+    def __init__(self, hidden: int, inter: int, top_k: int, router_bits, gate_up, down, scales, max_batch: int = 16, device: int = 0, n_experts: int | None = None,
+                 expert_first: int = 0):
+        """With ``n_experts`` larger than ``len(gate_up)`` the block is one GPU's share of an expert-parallel block: it holds the experts
+        ``expert_first .. expert_first + len(gate_up) - 1`` (``forward_partial`` / ``pairs_tensor`` / ``finish``)."""
         n = len(gate_up)
-        self.hidden, self.inter, self.top_k, self.n_experts, self.max_batch = hidden, inter, top_k, n, max_batch
+        total = n if n_experts is None else n_experts
+        self.hidden, self.inter, self.top_k, self.n_experts, self.max_batch = hidden, inter, top_k, total, max_batch
+        self._batch = 0
         self.matrices = [Matrix(w, 2 * inter, hidden, device=device) for w in gate_up] + [Matrix(w, hidden, inter, device=device) for w in down]
         gu = (C.c_void_p * n)(*[m.handle for m in self.matrices[:n]])
         dn = (C.c_void_p * n)(*[m.handle for m in self.matrices[n:]])
         rb = np.ascontiguousarray(router_bits, dtype=np.uint16).reshape(-1)
         sc = np.ascontiguousarray(scales, dtype=np.float32).reshape(-1)
-        assert rb.size == n * hidden and sc.size == 3 * n
+        assert rb.size == total * hidden and sc.size == 3 * n
         self._h = C.c_void_p()
         lib = load_library()
-        lib.quintrit_b200_moe_create.argtypes = [C.c_uint32] * 6 + [C.POINTER(C.c_uint16), C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), _f32p, C.POINTER(C.c_void_p)]
+        lib.quintrit_b200_moe_create_shard.argtypes = [C.c_uint32] * 6 + [C.POINTER(C.c_uint16), C.c_uint32, C.c_uint32, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), _f32p,
+                                                       C.POINTER(C.c_void_p)]
+        lib.quintrit_b200_moe_forward_partial.argtypes = [C.c_void_p, _f32p, _sz]
+        lib.quintrit_b200_moe_pairs.argtypes = [C.c_void_p, C.POINTER(C.c_void_p), C.POINTER(_sz)]
+        lib.quintrit_b200_moe_finish.argtypes = [C.c_void_p, _sz, _f32p, C.POINTER(C.c_uint32), _f32p]
         lib.quintrit_b200_moe_forward.argtypes = [C.c_void_p, _f32p, _sz, _f32p, C.POINTER(C.c_uint32), _f32p]
         lib.quintrit_b200_moe_time.argtypes = [C.c_void_p, _sz, C.c_uint32, _f32p]
         lib.quintrit_b200_moe_free.argtypes = [C.c_void_p]
         lib.quintrit_b200_moe_free.restype = None
-        _check(lib.quintrit_b200_moe_create(device, hidden, inter, n, top_k, max_batch, rb.ctypes.data_as(C.POINTER(C.c_uint16)), gu, dn, _p(sc, _f32p), C.byref(self._h)))
+        _check(lib.quintrit_b200_moe_create_shard(device, hidden, inter, total, top_k, max_batch, rb.ctypes.data_as(C.POINTER(C.c_uint16)), expert_first, n, gu, dn, _p(sc, _f32p),
+                                                  C.byref(self._h)))
 
     def forward(self, x):
         """x: [batch][hidden] floats -> (output [batch][hidden], chosen experts [batch][top_k], weights [batch][top_k])."""
@@ -571,6 +581,31 @@ class Moe:
         b = xx.shape[0]
         out, ids, w = np.zeros((b, self.hidden), np.float32), np.zeros((b, self.top_k), np.uint32), np.zeros((b, self.top_k), np.float32)
         _check(load_library().quintrit_b200_moe_forward(self._h, _p(xx, _f32p), b, _p(out, _f32p), ids.ctypes.data_as(C.POINTER(C.c_uint32)), _p(w, _f32p)))
+        return out, ids, w
+
+    def forward_partial(self, x) -> None:
+        """Routes the tokens and runs the pairs whose expert this block holds; the pairs' results stay on the device (``pairs_tensor``)."""
+        xx = np.ascontiguousarray(x, dtype=np.float32).reshape(-1, self.hidden)
+        self._batch = xx.shape[0]
+        _check(load_library().quintrit_b200_moe_forward_partial(self._h, _p(xx, _f32p), self._batch))
+
+    def pairs_tensor(self):
+        """The pairs' results of the last partial forward as a torch int32 tensor over the block's device buffer ([batch * top_k * hidden]; the
+        bits are floats): the shares of all GPUs are added in place (``torch.distributed.all_reduce``) before ``finish``."""
+        import torch
+
+        ptr, n = C.c_void_p(), _sz(0)
+        _check(load_library().quintrit_b200_moe_pairs(self._h, C.byref(ptr), C.byref(n)))
+
+        class _View:
+            __cuda_array_interface__ = {"shape": (n.value,), "typestr": "<i4", "data": (ptr.value, False), "version": 2}
+
+        return torch.as_tensor(_View(), device="cuda")
+
+    def finish(self):
+        b = self._batch
+        out, ids, w = np.zeros((b, self.hidden), np.float32), np.zeros((b, self.top_k), np.uint32), np.zeros((b, self.top_k), np.float32)
+        _check(load_library().quintrit_b200_moe_finish(self._h, b, _p(out, _f32p), ids.ctypes.data_as(C.POINTER(C.c_uint32)), _p(w, _f32p)))
         return out, ids, w
 
     def time_ms(self, batch: int, repeats: int = 20) -> float:

@@ -2485,9 +2485,11 @@ struct quintrit_b200_moe {
     MoeExpertRef* experts = nullptr;
     float *x = nullptr, *s_x = nullptr, *logits = nullptr, *probs = nullptr, *weights = nullptr, *s_i = nullptr, *out = nullptr;
     int8_t *a8_x = nullptr, *a8_i = nullptr;
-    uint32_t* chosen = nullptr;
+    uint32_t *chosen = nullptr, *local_z = nullptr;
     unsigned int *tie = nullptr, *counters = nullptr;
     int32_t *acc_gu = nullptr, *acc_down = nullptr;
+    float* pairs = nullptr;      // [max_batch * top_k][hidden]: every pair's down result as floats (zeros for pairs of experts held elsewhere)
+    int expert_first = 0, expert_count = 0, n_local = 0, last_batch = 0;  // this GPU's experts; the local pairs of the last forward
     GemvItem *gu_items = nullptr, *down_items = nullptr;
     cudaStream_t stream = nullptr;
 };
@@ -2534,30 +2536,93 @@ int moe_enqueue(quintrit_b200_moe* m, int batch) {
     QTB_LAUNCH_CHECK();
     return QUINTRIT_OK;
 }
+// The experts of the local pairs (m->local_z, m->n_local: set by the caller from the chosen ids) up to every pair's down result as floats.
 int moe_enqueue_experts(quintrit_b200_moe* m, int batch) {
     cudaStream_t s = m->stream;
-    const int H = m->hidden, I = m->inter, K = m->top_k, nz = batch * K;
+    const int H = m->hidden, I = m->inter, K = m->top_k, nz = batch * K, nl = m->n_local;
     const int pairs_gu = ((H + kBlockTrits - 1) / kBlockTrits + 1) / 2, pairs_d = ((I + kBlockTrits - 1) / kBlockTrits + 1) / 2;
-    const int n_gu = nz * pairs_gu, n_d = nz * pairs_d * m->chunks_down;
-    moe_items_kernel<<<(n_gu + n_d + 255) / 256, 256, 0, s>>>(m->experts, m->chosen, nz, K, H, I, m->inter_pad, m->chunks_down, m->gu_items, m->down_items);
-    QTB_LAUNCH_CHECK();
-    QTB_CUDA(cudaMemsetAsync(m->acc_gu, 0, size_t(nz) * 2 * I * sizeof(int32_t), s));
+    const int n_gu = nl * pairs_gu, n_d = nl * pairs_d * m->chunks_down;
     QTB_CUDA(cudaMemsetAsync(m->acc_down, 0, size_t(nz) * H * sizeof(int32_t), s));
-    int rc = launch_gemv(m->gu_items, n_gu, m->a8_x, m->acc_gu, m->counters, m->sm_count, s);
+    if (nl > 0) {
+        moe_items_kernel<<<(n_gu + n_d + 255) / 256, 256, 0, s>>>(m->experts, m->chosen, m->local_z, nl, K, H, I, m->inter_pad, m->chunks_down, m->gu_items, m->down_items);
+        QTB_LAUNCH_CHECK();
+        QTB_CUDA(cudaMemsetAsync(m->acc_gu, 0, size_t(nz) * 2 * I * sizeof(int32_t), s));
+        int rc = launch_gemv(m->gu_items, n_gu, m->a8_x, m->acc_gu, m->counters, m->sm_count, s);
+        if (rc != QUINTRIT_OK) return rc;
+        moe_act_quant_kernel<<<nl, kRowThreads, I * sizeof(float), s>>>(m->acc_gu, m->experts, m->chosen, m->local_z, m->s_x, K, I, m->inter_pad, m->a8_i, m->s_i);
+        QTB_LAUNCH_CHECK();
+        if ((rc = launch_gemv(m->down_items, n_d, m->a8_i, m->acc_down, m->counters, m->sm_count, s)) != QUINTRIT_OK) return rc;
+    }
+    moe_scale_pairs_kernel<<<dim3((H + 255) / 256, nz), 256, 0, s>>>(m->acc_down, m->experts, m->chosen, m->s_i, H, m->pairs);
+    QTB_LAUNCH_CHECK();
+    return QUINTRIT_OK;
+}
+int moe_enqueue_combine(quintrit_b200_moe* m, int batch) {
+    moe_combine_kernel<<<dim3((m->hidden + 255) / 256, batch), 256, 0, m->stream>>>(m->pairs, m->weights, m->top_k, m->hidden, m->out);
+    QTB_LAUNCH_CHECK();
+    return QUINTRIT_OK;
+}
+
+// Router, selection (with the host's std::sort for tokens with equal probabilities), the list of local pairs, the local experts: everything up
+// to the pairs' results, then a synchronisation.
+int moe_partial(quintrit_b200_moe* m, const float* x, size_t batch) {
+    cudaStream_t s = m->stream;
+    const int B = static_cast<int>(batch), K = m->top_k, E = m->n_experts;
+    QTB_CUDA(cudaMemcpyAsync(m->x, x, batch * m->hidden * sizeof(float), cudaMemcpyHostToDevice, s));
+    int rc = moe_enqueue(m, B);
     if (rc != QUINTRIT_OK) return rc;
-    moe_act_quant_kernel<<<nz, kRowThreads, I * sizeof(float), s>>>(m->acc_gu, m->experts, m->chosen, m->s_x, K, I, m->inter_pad, m->a8_i, m->s_i);
-    QTB_LAUNCH_CHECK();
-    if ((rc = launch_gemv(m->down_items, n_d, m->a8_i, m->acc_down, m->counters, m->sm_count, s)) != QUINTRIT_OK) return rc;
-    moe_combine_kernel<<<dim3((H + 255) / 256, batch), 256, 0, s>>>(m->acc_down, m->experts, m->chosen, m->weights, m->s_i, K, H, m->out);
-    QTB_LAUNCH_CHECK();
+    // Experts with exactly equal probabilities: std::sort (the reference's choice, hybrid.rs:828-831) orders them by its algorithm. The
+    // device ranks such ties by id and flags the token; the host then sorts that token's experts with the standard library's std::sort
+    // and replaces the device's choice and weights.
+    std::vector<unsigned int> tie(batch);
+    std::vector<uint32_t> chosen(batch * K);
+    QTB_CUDA(cudaMemcpyAsync(tie.data(), m->tie, batch * sizeof(unsigned int), cudaMemcpyDeviceToHost, s));
+    QTB_CUDA(cudaMemcpyAsync(chosen.data(), m->chosen, batch * K * sizeof(uint32_t), cudaMemcpyDeviceToHost, s));
+    QTB_CUDA(cudaStreamSynchronize(s));
+    for (int b = 0; b < B; ++b) {
+        if (tie[b] == 0) continue;
+        std::vector<float> p(E);
+        QTB_CUDA(cudaMemcpy(p.data(), m->probs + size_t(b) * E, E * sizeof(float), cudaMemcpyDeviceToHost));
+        std::vector<uint32_t> order(E);
+        for (int i = 0; i < E; ++i) order[i] = static_cast<uint32_t>(i);
+        std::sort(order.begin(), order.end(), [&](uint32_t a, uint32_t c) { return p[a] > p[c]; });
+        std::vector<float> w(K);
+        double sum = 0.0;
+        for (int i = 0; i < K; ++i) w[i] = p[order[i]], sum += static_cast<double>(w[i]);
+        const float sc = std::max(static_cast<float>(sum), 6.103515625e-5f);
+        for (int i = 0; i < K; ++i) w[i] /= sc, chosen[size_t(b) * K + i] = order[i];
+        QTB_CUDA(cudaMemcpy(m->chosen + size_t(b) * K, order.data(), K * sizeof(uint32_t), cudaMemcpyHostToDevice));
+        QTB_CUDA(cudaMemcpy(m->weights + size_t(b) * K, w.data(), K * sizeof(float), cudaMemcpyHostToDevice));
+    }
+    std::vector<uint32_t> local;
+    for (size_t z = 0; z < chosen.size(); ++z)
+        if (chosen[z] >= static_cast<uint32_t>(m->expert_first) && chosen[z] < static_cast<uint32_t>(m->expert_first + m->expert_count)) local.push_back(static_cast<uint32_t>(z));
+    m->n_local = static_cast<int>(local.size()), m->last_batch = B;
+    if (!local.empty()) QTB_CUDA(cudaMemcpyAsync(m->local_z, local.data(), local.size() * sizeof(uint32_t), cudaMemcpyHostToDevice, s));
+    if ((rc = moe_enqueue_experts(m, B)) != QUINTRIT_OK) return rc;
+    unsigned int flag = 0;
+    QTB_CUDA(cudaMemcpyAsync(&flag, m->counters + 2, sizeof flag, cudaMemcpyDeviceToHost, s));
+    QTB_CUDA(cudaStreamSynchronize(s));  // (also keeps `local` alive until its copy is done)
+    if (flag != 0) return fail(QUINTRIT_ERR_DEVICE, "GEMV kernel on the CUDA device found its shared-memory table at an unexpected address");
+    return QUINTRIT_OK;
+}
+
+int moe_finish(quintrit_b200_moe* m, size_t batch, float* out, uint32_t* out_experts, float* out_weights) {
+    cudaStream_t s = m->stream;
+    int rc = moe_enqueue_combine(m, static_cast<int>(batch));
+    if (rc != QUINTRIT_OK) return rc;
+    QTB_CUDA(cudaMemcpyAsync(out, m->out, batch * m->hidden * sizeof(float), cudaMemcpyDeviceToHost, s));
+    if (out_experts) QTB_CUDA(cudaMemcpyAsync(out_experts, m->chosen, batch * m->top_k * sizeof(uint32_t), cudaMemcpyDeviceToHost, s));
+    if (out_weights) QTB_CUDA(cudaMemcpyAsync(out_weights, m->weights, batch * m->top_k * sizeof(float), cudaMemcpyDeviceToHost, s));
+    QTB_CUDA(cudaStreamSynchronize(s));
     return QUINTRIT_OK;
 }
 
 }  // namespace
 
-extern "C" int quintrit_b200_moe_create(uint32_t device_index, uint32_t hidden, uint32_t inter, uint32_t n_experts, uint32_t top_k, uint32_t max_batch, const uint16_t* router_bf16,
-                                        const quintrit_b200_matrix_t* const* gate_up, const quintrit_b200_matrix_t* const* down, const float* scales,
-                                        quintrit_b200_moe_t** out_moe) {
+extern "C" int quintrit_b200_moe_create_shard(uint32_t device_index, uint32_t hidden, uint32_t inter, uint32_t n_experts, uint32_t top_k, uint32_t max_batch,
+                                              const uint16_t* router_bf16, uint32_t expert_first, uint32_t expert_count, const quintrit_b200_matrix_t* const* gate_up,
+                                              const quintrit_b200_matrix_t* const* down, const float* scales, quintrit_b200_moe_t** out_moe) {
     return guard([&]() -> int {
         if (out_moe == nullptr) return fail(QUINTRIT_ERR_NULL_POINTER, "out_moe is NULL");
         *out_moe = nullptr;
@@ -2570,14 +2635,16 @@ extern "C" int quintrit_b200_moe_create(uint32_t device_index, uint32_t hidden, 
         cudaDeviceProp prop;
         int rc = require_b200(static_cast<int>(device_index), &prop);
         if (rc != QUINTRIT_OK) return rc;
-        std::vector<MoeExpertRef> refs(n_experts);
-        for (uint32_t e = 0; e < n_experts; ++e) {
+        if (expert_count == 0 || expert_first > n_experts || expert_count > n_experts - expert_first)
+            return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "experts %u .. %u + %u do not lie inside the %u experts of the block", expert_first, expert_first, expert_count, n_experts);
+        std::vector<MoeExpertRef> refs(n_experts, MoeExpertRef{nullptr, nullptr, 0.0f, 0.0f, 0.0f, 0});  // experts held elsewhere keep null weights
+        for (uint32_t e = 0; e < expert_count; ++e) {
             if ((rc = check_matrix(gate_up[e])) != QUINTRIT_OK || (rc = check_matrix(down[e])) != QUINTRIT_OK) return rc;
             if (gate_up[e]->device != static_cast<int>(device_index) || down[e]->device != static_cast<int>(device_index)) return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "expert %u lives on another device", e);
             if (gate_up[e]->rows != size_t(2) * inter || gate_up[e]->cols != hidden)
                 return fail(QUINTRIT_ERR_INVALID_SHAPE, "gate_up of expert %u is %zu x %zu, the block needs %u x %u (gate rows, then up rows)", e, gate_up[e]->rows, gate_up[e]->cols, 2 * inter, hidden);
             if (down[e]->rows != hidden || down[e]->cols != inter) return fail(QUINTRIT_ERR_INVALID_SHAPE, "down of expert %u is %zu x %zu, the block needs %u x %u", e, down[e]->rows, down[e]->cols, hidden, inter);
-            refs[e] = MoeExpertRef{gate_up[e]->d_w, down[e]->d_w, scales[3 * e], scales[3 * e + 1], scales[3 * e + 2], 0};
+            refs[expert_first + e] = MoeExpertRef{gate_up[e]->d_w, down[e]->d_w, scales[3 * e], scales[3 * e + 1], scales[3 * e + 2], 0};
         }
         DeviceGuard g(static_cast<int>(device_index));
         if ((rc = upload_exp2_table()) != QUINTRIT_OK) return rc;
@@ -2592,6 +2659,7 @@ extern "C" int quintrit_b200_moe_create(uint32_t device_index, uint32_t hidden, 
         m->magic = kMagicMoe, m->device = static_cast<int>(device_index), m->sm_count = prop.multiProcessorCount;
         m->hidden = static_cast<int>(hidden), m->inter = static_cast<int>(inter), m->inter_pad = static_cast<int>((inter + 15) / 16 * 16);
         m->n_experts = static_cast<int>(n_experts), m->top_k = static_cast<int>(top_k), m->max_batch = static_cast<int>(max_batch);
+        m->expert_first = static_cast<int>(expert_first), m->expert_count = static_cast<int>(expert_count);
         const int tiles_d = (m->hidden + kTileRows - 1) / kTileRows;
         m->chunks_down = std::max(1, tiles_d / 32);  // down items of about 32 row tiles
         const size_t B = max_batch, Z = B * top_k, H = hidden, I = inter, E = n_experts;
@@ -2606,7 +2674,8 @@ extern "C" int quintrit_b200_moe_create(uint32_t device_index, uint32_t hidden, 
             (rc = moe_alloc(m, &m->weights, Z)) != QUINTRIT_OK || (rc = moe_alloc(m, &m->tie, B)) != QUINTRIT_OK || (rc = moe_alloc(m, &m->counters, 4)) != QUINTRIT_OK ||
             (rc = moe_alloc(m, &m->acc_gu, Z * 2 * I)) != QUINTRIT_OK || (rc = moe_alloc(m, &m->a8_i, Z * m->inter_pad + 256)) != QUINTRIT_OK || (rc = moe_alloc(m, &m->s_i, Z)) != QUINTRIT_OK ||
             (rc = moe_alloc(m, &m->acc_down, Z * H)) != QUINTRIT_OK || (rc = moe_alloc(m, &m->out, B * H)) != QUINTRIT_OK || (rc = moe_alloc(m, &m->gu_items, Z * pairs_gu)) != QUINTRIT_OK ||
-            (rc = moe_alloc(m, &m->down_items, Z * pairs_d * m->chunks_down)) != QUINTRIT_OK)
+            (rc = moe_alloc(m, &m->down_items, Z * pairs_d * m->chunks_down)) != QUINTRIT_OK || (rc = moe_alloc(m, &m->local_z, Z)) != QUINTRIT_OK ||
+            (rc = moe_alloc(m, &m->pairs, Z * H)) != QUINTRIT_OK)
             return bail(rc);
         cudaError_t e = cudaMemcpy(m->router, router_bf16, E * H * sizeof(uint16_t), cudaMemcpyHostToDevice);
         if (e == cudaSuccess) e = cudaMemcpy(m->experts, refs.data(), E * sizeof(MoeExpertRef), cudaMemcpyHostToDevice);
@@ -2625,47 +2694,64 @@ extern "C" void quintrit_b200_moe_free(quintrit_b200_moe_t* moe) {
     destroy_moe(moe);
 }
 
+extern "C" int quintrit_b200_moe_create(uint32_t device_index, uint32_t hidden, uint32_t inter, uint32_t n_experts, uint32_t top_k, uint32_t max_batch, const uint16_t* router_bf16,
+                                        const quintrit_b200_matrix_t* const* gate_up, const quintrit_b200_matrix_t* const* down, const float* scales,
+                                        quintrit_b200_moe_t** out_moe) {
+    return quintrit_b200_moe_create_shard(device_index, hidden, inter, n_experts, top_k, max_batch, router_bf16, 0, n_experts, gate_up, down, scales, out_moe);
+}
+
+namespace {
+int moe_check_batch(quintrit_b200_moe* m, size_t batch) {
+    if (batch == 0 || batch > static_cast<size_t>(m->max_batch)) return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "a batch of %zu tokens (the block was made for 1 to %d)", batch, m->max_batch);
+    return QUINTRIT_OK;
+}
+}  // namespace
+
 extern "C" int quintrit_b200_moe_forward(quintrit_b200_moe_t* moe, const float* x, size_t batch, float* out, uint32_t* out_experts, float* out_weights) {
     return guard([&]() -> int {
         int rc = check_moe(moe);
         if (rc != QUINTRIT_OK) return rc;
-        quintrit_b200_moe* m = moe;
         if (x == nullptr || out == nullptr) return fail(QUINTRIT_ERR_NULL_POINTER, "x or out is NULL");
-        if (batch == 0 || batch > static_cast<size_t>(m->max_batch)) return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "a batch of %zu tokens (the block was made for 1 to %d)", batch, m->max_batch);
-        DeviceGuard g(m->device);
-        cudaStream_t s = m->stream;
-        const int B = static_cast<int>(batch), K = m->top_k, E = m->n_experts;
-        QTB_CUDA(cudaMemcpyAsync(m->x, x, batch * m->hidden * sizeof(float), cudaMemcpyHostToDevice, s));
-        if ((rc = moe_enqueue(m, B)) != QUINTRIT_OK) return rc;
-        // Experts with exactly equal probabilities: std::sort (the reference's choice, hybrid.rs:828-831) orders them by its algorithm. The
-        // device ranks such ties by id and flags the token; the host then sorts that token's experts with the standard library's std::sort
-        // and replaces the device's choice and weights.
-        std::vector<unsigned int> tie(batch);
-        QTB_CUDA(cudaMemcpyAsync(tie.data(), m->tie, batch * sizeof(unsigned int), cudaMemcpyDeviceToHost, s));
-        QTB_CUDA(cudaStreamSynchronize(s));
-        for (int b = 0; b < B; ++b) {
-            if (tie[b] == 0) continue;
-            std::vector<float> p(E);
-            QTB_CUDA(cudaMemcpy(p.data(), m->probs + size_t(b) * E, E * sizeof(float), cudaMemcpyDeviceToHost));
-            std::vector<uint32_t> order(E);
-            for (int i = 0; i < E; ++i) order[i] = static_cast<uint32_t>(i);
-            std::sort(order.begin(), order.end(), [&](uint32_t a, uint32_t c) { return p[a] > p[c]; });
-            std::vector<float> w(K);
-            double sum = 0.0;
-            for (int i = 0; i < K; ++i) w[i] = p[order[i]], sum += static_cast<double>(w[i]);
-            const float sc = std::max(static_cast<float>(sum), 6.103515625e-5f);
-            for (int i = 0; i < K; ++i) w[i] /= sc;
-            QTB_CUDA(cudaMemcpy(m->chosen + size_t(b) * K, order.data(), K * sizeof(uint32_t), cudaMemcpyHostToDevice));
-            QTB_CUDA(cudaMemcpy(m->weights + size_t(b) * K, w.data(), K * sizeof(float), cudaMemcpyHostToDevice));
-        }
-        if ((rc = moe_enqueue_experts(m, B)) != QUINTRIT_OK) return rc;
-        QTB_CUDA(cudaMemcpyAsync(out, m->out, batch * m->hidden * sizeof(float), cudaMemcpyDeviceToHost, s));
-        if (out_experts) QTB_CUDA(cudaMemcpyAsync(out_experts, m->chosen, batch * K * sizeof(uint32_t), cudaMemcpyDeviceToHost, s));
-        if (out_weights) QTB_CUDA(cudaMemcpyAsync(out_weights, m->weights, batch * K * sizeof(float), cudaMemcpyDeviceToHost, s));
-        unsigned int flag = 0;
-        QTB_CUDA(cudaMemcpyAsync(&flag, m->counters + 2, sizeof flag, cudaMemcpyDeviceToHost, s));
-        QTB_CUDA(cudaStreamSynchronize(s));
-        if (flag != 0) return fail(QUINTRIT_ERR_DEVICE, "GEMV kernel on the CUDA device found its shared-memory table at an unexpected address");
+        if ((rc = moe_check_batch(moe, batch)) != QUINTRIT_OK) return rc;
+        if (moe->expert_count != moe->n_experts) return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "this block holds experts %d .. %d of %d: run quintrit_b200_moe_forward_partial, add the pairs of all GPUs, then quintrit_b200_moe_finish", moe->expert_first, moe->expert_first + moe->expert_count, moe->n_experts);
+        DeviceGuard g(moe->device);
+        if ((rc = moe_partial(moe, x, batch)) != QUINTRIT_OK) return rc;
+        if ((rc = moe_finish(moe, batch, out, out_experts, out_weights)) != QUINTRIT_OK) return rc;
+        return ok();
+    });
+}
+
+extern "C" int quintrit_b200_moe_forward_partial(quintrit_b200_moe_t* moe, const float* x, size_t batch) {
+    return guard([&]() -> int {
+        int rc = check_moe(moe);
+        if (rc != QUINTRIT_OK) return rc;
+        if (x == nullptr) return fail(QUINTRIT_ERR_NULL_POINTER, "x is NULL");
+        if ((rc = moe_check_batch(moe, batch)) != QUINTRIT_OK) return rc;
+        DeviceGuard g(moe->device);
+        if ((rc = moe_partial(moe, x, batch)) != QUINTRIT_OK) return rc;
+        return ok();
+    });
+}
+
+extern "C" int quintrit_b200_moe_pairs(quintrit_b200_moe_t* moe, void** out_device_pointer, size_t* out_floats) {
+    return guard([&]() -> int {
+        int rc = check_moe(moe);
+        if (rc != QUINTRIT_OK) return rc;
+        if (out_device_pointer == nullptr || out_floats == nullptr) return fail(QUINTRIT_ERR_NULL_POINTER, "out_device_pointer or out_floats is NULL");
+        *out_device_pointer = moe->pairs;
+        *out_floats = size_t(moe->last_batch) * moe->top_k * moe->hidden;
+        return ok();
+    });
+}
+
+extern "C" int quintrit_b200_moe_finish(quintrit_b200_moe_t* moe, size_t batch, float* out, uint32_t* out_experts, float* out_weights) {
+    return guard([&]() -> int {
+        int rc = check_moe(moe);
+        if (rc != QUINTRIT_OK) return rc;
+        if (out == nullptr) return fail(QUINTRIT_ERR_NULL_POINTER, "out is NULL");
+        if (batch == 0 || batch != static_cast<size_t>(moe->last_batch)) return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "the last partial forward held %d tokens, not %zu", moe->last_batch, batch);
+        DeviceGuard g(moe->device);
+        if ((rc = moe_finish(moe, batch, out, out_experts, out_weights)) != QUINTRIT_OK) return rc;
         return ok();
     });
 }
@@ -2676,7 +2762,7 @@ extern "C" int quintrit_b200_moe_time(quintrit_b200_moe_t* moe, size_t batch, ui
         if (rc != QUINTRIT_OK) return rc;
         quintrit_b200_moe* m = moe;
         if (out_ms == nullptr) return fail(QUINTRIT_ERR_NULL_POINTER, "out_ms is NULL");
-        if (batch == 0 || batch > static_cast<size_t>(m->max_batch) || repeats == 0) return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "batch must be in [1, %d] and repeats at least 1", m->max_batch);
+        if (repeats == 0 || batch == 0 || batch != static_cast<size_t>(m->last_batch)) return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "the block is timed on the batch of its last forward (%d tokens), at least once", m->last_batch);
         DeviceGuard g(m->device);
         cudaEvent_t e0, e1;
         QTB_CUDA(cudaEventCreate(&e0));
@@ -2685,6 +2771,7 @@ extern "C" int quintrit_b200_moe_time(quintrit_b200_moe_t* moe, size_t batch, ui
         for (uint32_t r = 0; r < repeats && rc == QUINTRIT_OK; ++r) {
             rc = moe_enqueue(m, static_cast<int>(batch));
             if (rc == QUINTRIT_OK) rc = moe_enqueue_experts(m, static_cast<int>(batch));
+            if (rc == QUINTRIT_OK) rc = moe_enqueue_combine(m, static_cast<int>(batch));
         }
         cudaEventRecord(e1, m->stream);
         cudaError_t e = cudaStreamSynchronize(m->stream);

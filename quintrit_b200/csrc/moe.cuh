@@ -139,15 +139,16 @@ __global__ void __launch_bounds__(256) moe_select_kernel(const float* __restrict
 // The work lists of the two GEMV launches, one thread per item: for pair z = (token, selection slot) the chosen expert's gate | up
 // projection (block pairs over the hidden columns, all row tiles in one item) and its down projection (block pairs over the
 // intermediate columns, the row tiles in `chunks_down` ranges). Same decomposition as build_items on the host.
-__global__ void moe_items_kernel(const MoeExpertRef* __restrict__ experts, const uint32_t* __restrict__ chosen, int n_z, int top_k, int hidden, int inter, int inter_pad,
-                                 int chunks_down, GemvItem* __restrict__ gu_items, GemvItem* __restrict__ down_items) {
+// `local_z` lists the n_z pairs whose expert this GPU holds (all pairs on one GPU; a share of them under expert parallelism).
+__global__ void moe_items_kernel(const MoeExpertRef* __restrict__ experts, const uint32_t* __restrict__ chosen, const uint32_t* __restrict__ local_z, int n_z, int top_k, int hidden,
+                                 int inter, int inter_pad, int chunks_down, GemvItem* __restrict__ gu_items, GemvItem* __restrict__ down_items) {
     const int blocks_gu = (hidden + kBlockTrits - 1) / kBlockTrits, pairs_gu = (blocks_gu + 1) / 2, tiles_gu = (2 * inter + kTileRows - 1) / kTileRows;
     const int blocks_d = (inter + kBlockTrits - 1) / kBlockTrits, pairs_d = (blocks_d + 1) / 2, tiles_d = (hidden + kTileRows - 1) / kTileRows;
     const int n_gu = n_z * pairs_gu, n_d = n_z * pairs_d * chunks_down;
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n_gu + n_d; i += gridDim.x * blockDim.x) {
         GemvItem it{};
         if (i < n_gu) {
-            const int z = i / pairs_gu, g = 2 * (i % pairs_gu);
+            const int z = static_cast<int>(local_z[i / pairs_gu]), g = 2 * (i % pairs_gu);
             const MoeExpertRef& e = experts[chosen[z]];
             it.wa = e.w_gu + static_cast<size_t>(g) * tiles_gu * 64;
             it.nblk = g + 1 < blocks_gu ? 2 : 1;
@@ -157,7 +158,7 @@ __global__ void moe_items_kernel(const MoeExpertRef* __restrict__ experts, const
             it.rows = 2 * inter, it.cols = hidden, it.col0 = g * kBlockTrits, it.tile0 = 0, it.ntiles = tiles_gu;
             gu_items[i] = it;
         } else {
-            const int k = i - n_gu, c = k % chunks_down, p = (k / chunks_down) % pairs_d, z = k / (chunks_down * pairs_d), g = 2 * p;
+            const int k = i - n_gu, c = k % chunks_down, p = (k / chunks_down) % pairs_d, z = static_cast<int>(local_z[k / (chunks_down * pairs_d)]), g = 2 * p;
             const MoeExpertRef& e = experts[chosen[z]];
             const int t0 = tiles_d * c / chunks_down, t1 = tiles_d * (c + 1) / chunks_down;
             it.wa = e.w_down + (static_cast<size_t>(g) * tiles_d + t0) * 64;
@@ -174,11 +175,11 @@ __global__ void moe_items_kernel(const MoeExpertRef* __restrict__ experts, const
 // One block per pair z: gate and up sums to floats (one multiply by weight_scale / act_scale each, layer.rs:143-147), SwiGLU
 // (ops.rs:427-464), int8 absmax codes of the result for the down projection.
 __global__ void __launch_bounds__(kRowThreads) moe_act_quant_kernel(const int32_t* __restrict__ acc_gu, const MoeExpertRef* __restrict__ experts, const uint32_t* __restrict__ chosen,
-                                                                    const float* __restrict__ s_x, int top_k, int inter, int inter_pad, int8_t* __restrict__ a8_i,
-                                                                    float* __restrict__ s_i) {
+                                                                    const uint32_t* __restrict__ local_z, const float* __restrict__ s_x, int top_k, int inter, int inter_pad,
+                                                                    int8_t* __restrict__ a8_i, float* __restrict__ s_i) {
     __shared__ float sh_f[32];
     extern __shared__ float y_s[];
-    const size_t z = blockIdx.x;
+    const size_t z = local_z[blockIdx.x];
     const MoeExpertRef& e = experts[chosen[z]];
     const float s_in = s_x[z / top_k];
     const bool live = s_in > 0.0f;
@@ -196,19 +197,28 @@ __global__ void __launch_bounds__(kRowThreads) moe_act_quant_kernel(const int32_
     quantize_vector(y_s, inter, amax, a8_i + z * inter_pad, s_i + z, nullptr, sh_f);
 }
 
-// out[token][h] = the experts' down results, each scaled (one multiply by weight_scale / act_scale, zero for a zero activation scale:
-// layer.rs:143-150) and weighted, added in selection order with the first one assigned (hybrid.rs:853-857).
-__global__ void moe_combine_kernel(const int32_t* __restrict__ acc_down, const MoeExpertRef* __restrict__ experts, const uint32_t* __restrict__ chosen,
-                                   const float* __restrict__ weights, const float* __restrict__ s_i, int top_k, int hidden, float* __restrict__ out) {
+// pairs[z][h] = the down result of pair z as floats: one multiply by weight_scale / act_scale, zero for a zero activation scale
+// (layer.rs:143-150) and for a pair whose expert another GPU holds (that GPU writes the value; the exchange adds the shares, of which
+// exactly one is not zero).
+__global__ void moe_scale_pairs_kernel(const int32_t* __restrict__ acc_down, const MoeExpertRef* __restrict__ experts, const uint32_t* __restrict__ chosen,
+                                       const float* __restrict__ s_i, int hidden, float* __restrict__ pairs) {
+    const size_t z = blockIdx.y;
+    const MoeExpertRef& e = experts[chosen[z]];
+    const float s = s_i[z];
+    const bool live = e.w_down != nullptr && s > 0.0f;
+    const float post = live ? __fdiv_rn(e.ws_down, s) : 0.0f;
+    for (int h = blockIdx.x * blockDim.x + threadIdx.x; h < hidden; h += gridDim.x * blockDim.x)
+        pairs[z * hidden + h] = live ? __fmul_rn(static_cast<float>(acc_down[z * hidden + h]), post) : 0.0f;
+}
+
+// out[token][h] = the pairs' results weighted and added in selection order, the first one assigned (hybrid.rs:853-857).
+__global__ void moe_combine_kernel(const float* __restrict__ pairs, const float* __restrict__ weights, int top_k, int hidden, float* __restrict__ out) {
     const size_t b = blockIdx.y;
     for (int h = blockIdx.x * blockDim.x + threadIdx.x; h < hidden; h += gridDim.x * blockDim.x) {
         float o = 0.0f;
         for (int i = 0; i < top_k; ++i) {
             const size_t z = b * top_k + i;
-            const float s = s_i[z];
-            float v = 0.0f;
-            if (s > 0.0f) v = __fmul_rn(static_cast<float>(acc_down[z * hidden + h]), __fdiv_rn(experts[chosen[z]].ws_down, s));
-            v = __fmul_rn(v, weights[z]);
+            const float v = __fmul_rn(pairs[z * hidden + h], weights[z]);
             o = i == 0 ? v : __fadd_rn(o, v);
         }
         out[b * hidden + h] = o;
