@@ -51,6 +51,15 @@ def expert(x, gate_up_planar, down_planar, hidden: int, inter: int, ws_gate, ws_
     return oracle.rescale(oracle.gemv_planar(down_planar, hidden, inter, a2), ws_down, s2)
 
 
+def combine(pairs, w) -> np.ndarray:
+    """The pairs' results ([top_k][hidden]) weighted and added in selection order, the first one assigned (hybrid.rs:853-857)."""
+    out = None
+    for i in range(len(w)):
+        y = (np.asarray(pairs[i], np.float32) * w[i]).astype(np.float32)
+        out = y if i == 0 else (out + y).astype(np.float32)
+    return out
+
+
 def forward(x, router_bits, gate_up, down, scales, hidden: int, inter: int, top_k: int):
     """One token through the block. gate_up[e]: planar rows of the expert's gate rows followed by its up rows; down[e]: planar rows of its
     down projection; scales[e] = (gate, up, down). Returns (output, chosen experts, their weights)."""
