@@ -357,7 +357,7 @@ int quintrit_b200_selftest_barrier(uint32_t device_index, uint32_t ctas, uint32_
 int quintrit_b200_decoder_prefill(quintrit_b200_decoder_t* decoder, const uint32_t* tokens, size_t count, uint32_t pos, float* logits, size_t logits_capacity,
                                   uint32_t* out_token);
 
-/* ---- mixture-of-experts feed-forward block (BASELINE's Qwen3-30B-A3B shape: softmax router, top-k of n experts, ternary SwiGLU experts) ----
+/* ---- mixture-of-experts feed-forward block (the shape of Qwen3-30B-A3B: softmax router, top-k of n experts, ternary SwiGLU experts) ----
  * The reference has no block of this kind (its Moe is Nemotron-H's, quintrit-runtime/src/hybrid.rs:798-869); this one is composed of
  * the reference's pieces, each computed as the reference computes it: the router as a BF16 projection (hybrid.rs:327-333), softmax
  * (ops.rs:274-298), experts by descending probability as std::sort leaves them (hybrid.rs:828-831), their probabilities divided by
