@@ -702,7 +702,13 @@ extern "C" int quintrit_b200_plan_create(const quintrit_b200_matrix_t* const* ma
         std::vector<GemvItem> items;
         size_t act = 0, out = 0;
         size_t tiles_per_item = item_tiles_override();
-        if (tiles_per_item == 0) tiles_per_item = 96;  // measured on the 280 projections of the Falcon3-10B shape: 48 and 64 tiles 21 300, 96 tiles 22 360, 128 tiles 22 130, 192 tiles 22 070 Gweights/s
+        if (tiles_per_item == 0) {
+            // Measured on the 280 projections of the Falcon3-10B shape: items of 48 and 64 row tiles 21 300, 96 tiles 22 360, 128 tiles 22 130, 192 tiles
+            // 22 070 Gweights/s (fewer table builds against a longer tail). A small plan keeps 64, so that every CTA slot still gets several items.
+            size_t pair_tiles = 0;
+            for (size_t i = 0; i < count; ++i) pair_tiles += (matrices[i]->blocks + 1) / 2 * matrices[i]->tiles;
+            tiles_per_item = pair_tiles / 96 >= size_t(8) * p->sm_count * kCtasPerSm ? 96 : 64;
+        }
         std::vector<size_t> item_at(count + 1), weights_before(count + 1);
         size_t weights = 0;
         for (size_t i = 0; i < count; ++i) {
