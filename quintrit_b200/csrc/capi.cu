@@ -2832,6 +2832,7 @@ extern "C" int quintrit_b200_sample_logits(uint32_t device_index, const float* l
 struct quintrit_b200_batch {
     uint32_t magic;
     quintrit_b200_decoder* d;              // weights, stream and the per-token buffers of the batched pass are the decoder's
+    int device;                            // (kept here too: releasing the batch must not read a decoder that was freed first)
     int n_seq;
     __half *kc = nullptr, *vc = nullptr;   // [n_seq][layers][ctx][kv_dim]
     uint32_t *d_pos = nullptr, *d_last = nullptr, *d_slot = nullptr, *d_chosen = nullptr;
@@ -2859,7 +2860,7 @@ void destroy_batch(quintrit_b200_batch* b) {
     if (b == nullptr) return;
     int prev = -1;
     cudaGetDevice(&prev);
-    cudaSetDevice(b->d->device);
+    cudaSetDevice(b->device);
     for (cudaGraphExec_t g : b->graph)
         if (g != nullptr) cudaGraphExecDestroy(g);
     for (void* p : b->allocs) cudaFree(p);
@@ -2923,7 +2924,7 @@ extern "C" int quintrit_b200_batch_create(quintrit_b200_decoder_t* decoder, uint
         if ((rc = prefill_buffers(d)) != QUINTRIT_OK) return rc;
         if ((rc = decoder_gemm_prepare(d)) != QUINTRIT_OK) return rc;
         quintrit_b200_batch* b = new quintrit_b200_batch();
-        b->magic = kMagicBatch, b->d = d, b->n_seq = static_cast<int>(sequences);
+        b->magic = kMagicBatch, b->d = d, b->device = d->device, b->n_seq = static_cast<int>(sequences);
         b->host_pos.assign(sequences, 0);
         b->graph.assign(sequences + 1, nullptr);
         b->warm.assign(sequences + 1, 0);
