@@ -200,6 +200,7 @@ typedef struct quintrit_b200_decoder quintrit_b200_decoder_t;
 
 #define QUINTRIT_B200_ARCH_LLAMA 0  /* LLaMA / Falcon3: interleaved RoPE pairs, SwiGLU (quintrit-runtime/src/config.rs:284-288, 464-467) */
 #define QUINTRIT_B200_ARCH_BITNET 1 /* BitNet b1.58: NEOX RoPE pairs, squared ReLU, attention and FFN sub-norms (config.rs:419-422) */
+#define QUINTRIT_B200_ARCH_QWEN 2   /* Qwen2 / Qwen3: NEOX RoPE pairs (config.rs:464-467), SwiGLU; Qwen3 adds query/key-norm (desc.qk_norms) */
 
 /*
  * Description of a model whose ternary projections are already on the device. It plays the part of GpuModel::load
@@ -238,6 +239,10 @@ typedef struct quintrit_b200_decoder_desc {
      * the row widened with bf16_to_f32, the normalised vector rounded with f32_to_bf16, rows through ggml_vec_dot_bf16,
      * ops.rs:650-712). The hidden size must be a multiple of 32 either way. */
     uint32_t table_dtype;
+    /* Query/key-norm (quintrit-runtime/src/attention.rs:282-294): num_layers * 2 arrays of head_dim weights - the RMSNorm of every query
+     * head and of every key head before RoPE - or NULL. The reference has this step on its block-scaled path only, and so has this
+     * library: with per-tensor projections it gives QUINTRIT_ERR_UNSUPPORTED. */
+    const float* const* qk_norms;
 } quintrit_b200_decoder_desc_t;
 
 int quintrit_b200_decoder_create(const quintrit_b200_decoder_desc_t* desc, quintrit_b200_decoder_t** out_decoder);

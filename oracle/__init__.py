@@ -371,6 +371,7 @@ def _declare_model(l: C.CDLL) -> None:
     l.qto_model_forward.argtypes = [C.c_void_p, C.c_uint32, _sz, _f32p]
     l.qto_model_set_bf16_tables.argtypes = [C.c_void_p, C.c_int]
     l.qto_model_set_block_scales.argtypes = [C.c_void_p, C.POINTER(_f32p)]
+    l.qto_model_set_qk_norms.argtypes = [C.c_void_p, C.POINTER(_f32p)]
     l.qto_vec_dot_bf16.restype = C.c_float
     l.qto_vec_dot_bf16.argtypes = [_u16p, _u16p, _sz]
     l.qto_f32_to_bf16.restype = C.c_uint16
@@ -508,6 +509,15 @@ class Model:
                 bsc[i] = _p(a, _f32p)
             self._keep.append(bsc)
             l.qto_model_set_block_scales(self._h, bsc)
+
+        if spec.get("qk_norms") is not None:  # layers * 2 arrays of head_dim weights (query norm, key norm)
+            qkn = (_f32p * (L * 2))()
+            for i, a in enumerate(spec["qk_norms"]):
+                a = _c(a, np.float32)
+                self._keep.append(a)
+                qkn[i] = _p(a, _f32p)
+            self._keep.append(qkn)
+            l.qto_model_set_qk_norms(self._h, qkn)
 
     def forward(self, token: int, pos: int) -> np.ndarray:
         logits = np.zeros(self.spec["vocab"], np.float32)

@@ -99,7 +99,7 @@ def model_spec(path, ctx: int | None = None) -> dict:
     """The model of a GGUF file as oracle.Model takes it (per-tensor ternary projections, F16 or BF16 tables)."""
     _, meta, tensors, data = read_gguf(path)
     a = meta.get("general.architecture", "bitnet-b1.58")
-    arch = 1 if a in ("bitnet-b1.58", "bitnet") else 0
+    arch = 1 if a in ("bitnet-b1.58", "bitnet") else 2 if a in ("qwen2", "qwen3") else 0  # config.rs:419-424, 464-467
     g = lambda k, d: meta.get(f"{a}.{k}", d)  # noqa: E731
     hidden, inter, layers = g("embedding_length", 2560), g("feed_forward_length", 6912), g("block_count", 30)
     heads, kv_heads = g("attention.head_count", 20), g("attention.head_count_kv", 5)
@@ -111,7 +111,7 @@ def model_spec(path, ctx: int | None = None) -> dict:
     table_t = tensors["token_embd.weight"][1]
     tab = lambda name: np.frombuffer(tensor_bytes(tensors, data, name).tobytes(), np.uint16).copy()  # noqa: E731
     f32 = lambda name: np.frombuffer(tensor_bytes(tensors, data, name).tobytes(), np.float32).copy()  # noqa: E731
-    weights, scales, norms = [], [], []
+    weights, scales, norms, qk_norms = [], [], [], []
     qd, kvd = heads * head_dim, kv_heads * head_dim
     shapes = [(qd, hidden), (kvd, hidden), (kvd, hidden), (hidden, qd), (inter, hidden), (inter, hidden), (hidden, inter)]
     for l in range(layers):
@@ -122,7 +122,10 @@ def model_spec(path, ctx: int | None = None) -> dict:
             scales.append(s)
         for k, nm in enumerate(("attn_norm", "ffn_norm", "attn_sub_norm", "ffn_sub_norm")):
             norms.append(f32(f"blk.{l}.{nm}.weight") if (k < 2 or arch == 1) else None)
+        if a == "qwen3":  # engine.rs:480: query and key head norms
+            qk_norms += [f32(f"blk.{l}.attn_q_norm.weight"), f32(f"blk.{l}.attn_k_norm.weight")]
     return {
+        **({"qk_norms": qk_norms} if qk_norms else {}),
         "arch": arch, "f32_values": bool(meta["quintrit_b200.f32_values"]) if "quintrit_b200.f32_values" in meta else not any(t == I2_S for _, t, _ in tensors.values()), "hidden": hidden, "inter": inter, "layers": layers,
         "q_heads": heads, "kv_heads": kv_heads, "head_dim": head_dim, "vocab": vocab, "ctx": want, "rope_dims": g("rope.dimension_count", head_dim),
         "eps": float(g("attention.layer_norm_rms_epsilon", 1e-5)), "rope_theta": float(g("rope.freq_base", 500000.0)),

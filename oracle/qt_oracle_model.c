@@ -468,7 +468,7 @@ void qto_gemv_block_scaled(const uint8_t* planar, const float* w_scales, const i
                            float* out);
 
 typedef struct qto_model {
-    int arch;     /* 0 = llama / falcon3 (interleaved RoPE, SwiGLU), 1 = bitnet (NEOX RoPE, relu^2, sub-norms) */
+    int arch;     /* 0 = llama / falcon3 (interleaved RoPE, SwiGLU), 1 = bitnet (NEOX RoPE, relu^2, sub-norms), 2 = qwen2 / qwen3 (NEOX RoPE, SwiGLU; config.rs:464-467) */
     int f32_values; /* attention accumulators: 0 = F16 (I2_S files), 1 = F32 (TQ1_0 / TQ2_0 files) */
     int hidden, inter, layers, q_heads, kv_heads, head_dim, vocab, ctx, rope_dims;
     float eps, rope_theta;
@@ -482,6 +482,7 @@ typedef struct qto_model {
     uint8_t** w64;           /* 64-row tiled copies for the AVX-512 GEMV (same integers, only faster), or NULL */
     int bf16_tables;         /* embedding and output head are BF16 instead of F16 (qto_model_set_bf16_tables) */
     const float** block_scales; /* layers * 7 arrays of rows * cols / 64 weight scales: Q2_0 projections (qto_model_set_block_scales) */
+    const float** qk_norms;  /* layers * 2 arrays of head_dim weights: RMSNorm of every query and key head before RoPE (qto_model_set_qk_norms), or NULL */
 } qto_model_t;
 
 qto_model_t* qto_model_create(int arch, int f32_values, int hidden, int inter, int layers, int q_heads, int kv_heads, int head_dim,
@@ -508,6 +509,8 @@ qto_model_t* qto_model_create(int arch, int f32_values, int hidden, int inter, i
 void qto_model_set_bf16_tables(qto_model_t* m, int on) { m->bf16_tables = on != 0; }
 /* Q2_0 models: every projection is block-scaled (attention.rs:262-344, model.rs:209-229); the tensor scales are unused */
 void qto_model_set_block_scales(qto_model_t* m, const float** scales) { m->block_scales = scales; }
+/* query/key-norm models (attention.rs:282-294: the block-scaled path normalises every query and key head before RoPE) */
+void qto_model_set_qk_norms(qto_model_t* m, const float** norms) { m->qk_norms = norms; }
 
 void qto_model_free(qto_model_t* m) {
     if (!m) return;
@@ -577,9 +580,20 @@ void qto_model_forward(qto_model_t* m, uint32_t token, size_t pos, float* logits
             project(m, l, 1, kvd, H, a8, s, k);
             project(m, l, 2, kvd, H, a8, s, v);
         }
+        if (m->qk_norms != NULL && m->qk_norms[l * 2] != NULL && m->qk_norms[l * 2 + 1] != NULL) { /* attention.rs:282-294 */
+            float head[4096];
+            for (size_t h = 0; h < (size_t)m->q_heads; ++h) {
+                memcpy(head, q + h * hd, hd * 4);
+                qto_rms_norm(head, m->qk_norms[l * 2], hd, m->eps, q + h * hd);
+            }
+            for (size_t h = 0; h < (size_t)m->kv_heads; ++h) {
+                memcpy(head, k + h * hd, hd * 4);
+                qto_rms_norm(head, m->qk_norms[l * 2 + 1], hd, m->eps, k + h * hd);
+            }
+        }
         qto_rope_cache(pos, (size_t)m->rope_dims, m->rope_theta, cache);
-        qto_rope_apply(q, (size_t)m->q_heads, hd, m->arch == 1, cache, (size_t)m->rope_dims);
-        qto_rope_apply(k, (size_t)m->kv_heads, hd, m->arch == 1, cache, (size_t)m->rope_dims);
+        qto_rope_apply(q, (size_t)m->q_heads, hd, m->arch != 0, cache, (size_t)m->rope_dims);
+        qto_rope_apply(k, (size_t)m->kv_heads, hd, m->arch != 0, cache, (size_t)m->rope_dims);
         uint16_t* kc = m->kc + ((size_t)l * m->ctx) * kvd;
         uint16_t* vc = m->vc + ((size_t)l * m->ctx) * kvd;
         for (size_t i = 0; i < kvd; ++i) {

@@ -8,6 +8,7 @@ compute call goes to the CUDA library and raises ``QuintritError`` if it is miss
 from .api import (  # noqa: F401
     ARCH_BITNET,
     ARCH_LLAMA,
+    ARCH_QWEN,
     Batch,
     Decoder,
     DeviceInfo,

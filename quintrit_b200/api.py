@@ -53,7 +53,8 @@ class _DecoderDescC(C.Structure):
                 ("num_kv_heads", C.c_uint32), ("head_dim", C.c_uint32), ("vocab_size", C.c_uint32), ("context_length", C.c_uint32),
                 ("rope_dims", C.c_uint32), ("rms_norm_eps", C.c_float), ("rope_theta", C.c_float), ("embed", C.POINTER(C.c_uint16)),
                 ("lm_head", C.POINTER(C.c_uint16)), ("output_norm", _f32p), ("matrices", C.POINTER(C.c_void_p)), ("scales", _f32p),
-                ("norms", C.POINTER(_f32p)), ("tp_rank", C.c_uint32), ("tp_world", C.c_uint32), ("table_dtype", C.c_uint32)]
+                ("norms", C.POINTER(_f32p)), ("tp_rank", C.c_uint32), ("tp_world", C.c_uint32), ("table_dtype", C.c_uint32),
+                ("qk_norms", C.POINTER(_f32p))]
 
 
 @dataclass
@@ -350,7 +351,7 @@ class Plan:
             pass
 
 
-ARCH_LLAMA, ARCH_BITNET = 0, 1
+ARCH_LLAMA, ARCH_BITNET, ARCH_QWEN = 0, 1, 2
 
 
 class Decoder:
@@ -401,6 +402,14 @@ class Decoder:
         d.matrices, d.scales, d.norms = mats, _p(scales, _f32p), norms
         d.tp_rank, d.tp_world = self.tp_rank, self.tp_world
         d.table_dtype = 1 if spec.get("bf16_tables") else 0
+        if spec.get("qk_norms") is not None:  # layers * 2 arrays of head_dim weights (query norm, key norm)
+            qkn = (_f32p * (L * 2))()
+            for i, a in enumerate(spec["qk_norms"]):
+                a = np.ascontiguousarray(a, dtype=np.float32)
+                keep.append(a)
+                qkn[i] = _p(a, _f32p)
+            keep.append(qkn)
+            d.qk_norms = qkn
         h = C.c_void_p()
         _check(load_library().quintrit_b200_decoder_create(C.byref(d), C.byref(h)))
         self._h = h

@@ -901,7 +901,7 @@ int decoder_create_impl(const quintrit_b200_decoder_desc_t* desc, quintrit_b200_
                     sizeof(quintrit_b200_decoder_desc_t));
     if (!desc->embed || !desc->output_norm || !desc->matrices || !desc->scales || !desc->norms)
         return fail(QUINTRIT_ERR_NULL_POINTER, "a required pointer of the decoder description is NULL");
-    if (desc->arch != QUINTRIT_B200_ARCH_LLAMA && desc->arch != QUINTRIT_B200_ARCH_BITNET)
+    if (desc->arch != QUINTRIT_B200_ARCH_LLAMA && desc->arch != QUINTRIT_B200_ARCH_BITNET && desc->arch != QUINTRIT_B200_ARCH_QWEN)
         return fail(QUINTRIT_ERR_INVALID_ARGUMENT, "unknown architecture %d", desc->arch);
     // tensor parallelism: the fields exist only in descriptions of the newer size
     uint32_t tp_rank = 0, tp_world = 1;
@@ -968,6 +968,16 @@ int decoder_create_impl(const quintrit_b200_decoder_desc_t* desc, quintrit_b200_
     d->attn_replicated = attn_replicated;
     d->tp_rank = static_cast<int>(tp_rank), d->tp_world = static_cast<int>(tp_world);
     d->bf16_tables = table_dtype == 1;
+    const float* const* qk_norms = nullptr;
+    if (desc->struct_size >= offsetof(quintrit_b200_decoder_desc_t, qk_norms) + sizeof(void*)) qk_norms = desc->qk_norms;
+    if (qk_norms != nullptr) {
+        if (!block_scaled) return fail(QUINTRIT_ERR_UNSUPPORTED, "query/key-norm is available for block-scaled (Q2_0) models only, as in the reference");
+        d->qk_norms.assign(size_t(L) * 2, nullptr);
+        for (size_t i = 0; i < size_t(L) * 2; ++i) {
+            if (qk_norms[i] == nullptr) return fail(QUINTRIT_ERR_NULL_POINTER, "qk_norms[%zu] is NULL", i);
+            if ((rc = dev_upload(d, &d->qk_norms[i], qk_norms[i], hd)) != QUINTRIT_OK) return rc;
+        }
+    }
     d->block_scaled = block_scaled;
     d->mats.assign(desc->matrices, desc->matrices + size_t(L) * 7);
     d->q_dim_full = static_cast<int>(qd_full), d->inter_full = static_cast<int>(I_full), d->vocab_full = static_cast<int>(desc->vocab_size);
@@ -1211,7 +1221,7 @@ int mega_setup(quintrit_b200_decoder* d, const quintrit_b200_decoder_desc_t* des
     a.bf16_tables = d->bf16_tables ? 1 : 0;
     a.l2_prefetch = 1;
     if (const char* pf = std::getenv("QUINTRIT_B200_L2_PREFETCH")) a.l2_prefetch = pf[0] != '0';  // experiments: "0" keeps the cold streams
-    a.neox = d->arch == QUINTRIT_B200_ARCH_BITNET, a.relu2 = d->arch == QUINTRIT_B200_ARCH_BITNET;
+    a.neox = d->arch != QUINTRIT_B200_ARCH_LLAMA, a.relu2 = d->arch == QUINTRIT_B200_ARCH_BITNET;
     a.sumsq_part = nullptr;
     if (d->arch == QUINTRIT_B200_ARCH_BITNET) {
         double* part = nullptr;
@@ -1311,6 +1321,7 @@ struct GgufModelShape {
     uint64_t vocab = 0, hidden = 0, inter = 0, layers = 0, heads = 0, kv_heads = 0, head_dim = 0, ctx_train = 0, rope_dims = 0;
     float eps = 1e-5f, theta = 500000.0f;
     bool has_i2s = false, has_q2 = false, tied = false;
+    bool qk_norm = false;  // Qwen3: every query and key head is RMS-normalised before RoPE (blk.N.attn_q_norm / attn_k_norm)
 };
 
 uint64_t meta_usize(const GgufFile& g, const std::string& key, uint64_t fallback, bool allow_array_max = false) {
@@ -1335,9 +1346,11 @@ int read_shape(const GgufFile& g, GgufModelShape* out) {
     GgufModelShape& m = *out;
     m.arch = meta_str(g, "general.architecture", "bitnet-b1.58");
     const std::string a = m.arch;
-    if (a == "qwen3" || a == "qwen35" || a == "nemotron_h_moe")
-        return fail(QUINTRIT_ERR_UNSUPPORTED, "architecture '%s' is not supported by the GPU decoder (hybrid, mixture-of-experts and query/key-norm models run on the CPU only)", a.c_str());
-    m.arch_id = (a == "bitnet-b1.58" || a == "bitnet") ? QUINTRIT_B200_ARCH_BITNET : QUINTRIT_B200_ARCH_LLAMA;
+    if (a == "qwen35" || a == "nemotron_h_moe")
+        return fail(QUINTRIT_ERR_UNSUPPORTED, "architecture '%s' is not supported by the GPU decoder (hybrid and mixture-of-experts models run on the CPU only)", a.c_str());
+    // config.rs:276-290, 419-424, 464-467: BitNet (NEOX RoPE, squared ReLU, sub-norms); Qwen2 / Qwen3 (NEOX RoPE; Qwen3 with query/key-norm); else LLaMA
+    m.arch_id = (a == "bitnet-b1.58" || a == "bitnet") ? QUINTRIT_B200_ARCH_BITNET : (a == "qwen2" || a == "qwen3") ? QUINTRIT_B200_ARCH_QWEN : QUINTRIT_B200_ARCH_LLAMA;
+    m.qk_norm = a == "qwen3";
     const GgufTensor* embd = g.tensor("token_embd.weight");
     uint64_t vocab_fallback = 128256;
     if (embd != nullptr && embd->shape.size() >= 2) vocab_fallback = embd->shape[1];
@@ -1421,6 +1434,7 @@ struct GgufModel {
     std::vector<float> scales;
     std::vector<std::vector<float>> f32_store;
     std::vector<const float*> norms;
+    std::vector<const float*> qk_norms;  // layers * 2 (query, key) when the architecture has them, else empty
     const uint16_t* embed = nullptr;
     const uint16_t* head = nullptr;
     const float* out_norm = nullptr;
@@ -1482,7 +1496,7 @@ int load_gguf_model(const char* path, uint32_t device, GgufModel* out) {
 
     const char* proj_names[7] = {"attn_q", "attn_k", "attn_v", "attn_output", "ffn_gate", "ffn_up", "ffn_down"};
     const uint64_t shapes[7][2] = {{qd, m.hidden}, {kvd, m.hidden}, {kvd, m.hidden}, {m.hidden, qd}, {m.inter, m.hidden}, {m.inter, m.hidden}, {m.hidden, m.inter}};
-    md.f32_store.reserve(m.layers * 4 + 1);
+    md.f32_store.reserve(m.layers * 6 + 1);
     for (uint64_t l = 0; l < m.layers && rc == QUINTRIT_OK; ++l) {
         const std::string prefix = "blk." + std::to_string(l) + ".";
         for (int k = 0; k < 7 && rc == QUINTRIT_OK; ++k) {
@@ -1504,6 +1518,12 @@ int load_gguf_model(const char* path, uint32_t device, GgufModel* out) {
             const float* p = nullptr;
             if (k < 2 || m.arch_id == QUINTRIT_B200_ARCH_BITNET) rc = dense_f32(prefix + norm_names[k] + ".weight", norm_len[k], &p);
             md.norms.push_back(p);
+        }
+        const char* head_norms[2] = {"attn_q_norm", "attn_k_norm"};  // engine.rs:480, validate.rs:250-251: head_dim F32 values each
+        for (int k = 0; k < 2 && rc == QUINTRIT_OK && m.qk_norm; ++k) {
+            const float* p = nullptr;
+            rc = dense_f32(prefix + head_norms[k] + ".weight", m.head_dim, &p);
+            md.qk_norms.push_back(p);
         }
     }
     if (rc == QUINTRIT_OK) rc = dense_f16("token_embd.weight", m.vocab * m.hidden, &md.embed);
@@ -1530,6 +1550,7 @@ int decoder_from_model(const GgufModel& md, uint32_t ctx, quintrit_b200_decoder*
     desc.matrices = reinterpret_cast<const quintrit_b200_matrix_t* const*>(md.mats.data());
     desc.scales = md.scales.data();
     desc.norms = md.norms.data();
+    desc.qk_norms = md.qk_norms.empty() ? nullptr : md.qk_norms.data();
     quintrit_b200_decoder* d = nullptr;
     const int rc = decoder_create_impl(&desc, &d);
     if (rc != QUINTRIT_OK) {
@@ -2332,7 +2353,7 @@ int prefill_layers(quintrit_b200_decoder* d, int n, const BatchTarget& tg) {
         rk.acc = d->pf.acc_qkv, rk.b_acc = qkv, rk.act_scale = d->pf.s_h, rk.b_scale = 1;
         rk.ws_q = sc[0], rk.ws_k = sc[1], rk.ws_v = sc[2];
         rk.cos_sin = d->cos_sin, rk.pos = tg.pos, rk.seq = tg.seq;
-        rk.q_dim = qd, rk.kv_dim = kvd, rk.head_dim = hd, rk.rope_dims = d->rope_dims, rk.neox = d->arch == QUINTRIT_B200_ARCH_BITNET;
+        rk.q_dim = qd, rk.kv_dim = kvd, rk.head_dim = hd, rk.rope_dims = d->rope_dims, rk.neox = d->arch != QUINTRIT_B200_ARCH_LLAMA;
         rk.q_out = d->pf.q, rk.b_q = qd;
         if (qkv_views) rk.v_q = v_q, rk.v_k = v_k, rk.v_v = v_v;
         rk.k_cache = tg.kc + static_cast<size_t>(l) * d->ctx * kvd;

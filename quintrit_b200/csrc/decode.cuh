@@ -273,6 +273,22 @@ __global__ void __launch_bounds__(kRowThreads) norm_quant_kernel(NormQuantArgs a
     quantize_vector(y_s, a.n, amax, a.q_out, a.scale_out, a.block_scaled ? a.q8_d : nullptr, sh_f);
 }
 
+// ---- query/key-norm (attention.rs:282-294): RMSNorm (ops.rs:62-96) of every query head and every key head before RoPE -------
+// One warp per head, in place on the projection results (floats: the block-scaled path, the only one that has this step in the
+// reference). Heads 0 .. q_heads - 1 are query heads (weights q_w), the rest key heads (k_w); the value rows behind them are left.
+__global__ void qk_norm_kernel(float* __restrict__ qkv, int q_heads, int kv_heads, int head_dim, const float* __restrict__ q_w, const float* __restrict__ k_w, float eps) {
+    const int head = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (head >= q_heads + kv_heads) return;
+    float* x = qkv + static_cast<size_t>(head) * head_dim;  // the key heads follow the query heads in the stacked row
+    const float* w = head < q_heads ? q_w : k_w;
+    double sum = 0.0;
+    for (int i = lane; i < head_dim; i += 32) sum += static_cast<double>(__fmul_rn(x[i], x[i]));
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    const float mean = __double2float_rn(sum / static_cast<double>(head_dim));
+    const float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, eps)));
+    for (int i = lane; i < head_dim; i += 32) x[i] = __fmul_rn(__fmul_rn(x[i], inv), w[i]);
+}
+
 // ---- q/k/v finish: post-scale, RoPE, KV append (attention.rs:171-203, ops.rs:160-221) --------------------------------
 struct RopeKvArgs {
     const int32_t* acc;       // stacked q | k | v sums (q_dim + 2 kv_dim)

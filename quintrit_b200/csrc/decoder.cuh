@@ -29,6 +29,7 @@ struct quintrit_b200_decoder {
     float *out_norm, *cos_sin, *x, *q, *part_acc, *part_ms, *logits;
     float* scores = nullptr;  // single-kernel path: attention scores of the current token, [q_heads][ctx]
     std::vector<float*> norms;  // layers * 4 (device)
+    std::vector<float*> qk_norms;  // layers * 2 (device): query and key head norms, empty for models without them
     int8_t *a8_h, *a8_q, *a8_i;
     float *s_h, *s_q, *s_i;
     int32_t *acc_qkv, *acc_o, *acc_gu, *acc_down;
@@ -199,13 +200,18 @@ inline int enqueue_token(quintrit_b200_decoder* d, bool with_head) {
         } else if ((rc = decoder_gemv(d, l, 0, d->a8_h, d->acc_qkv)) != QUINTRIT_OK) {
             return rc;
         }
+        if (!d->qk_norms.empty() && d->qk_norms[l * 2] != nullptr) {  // query/key-norm (block-scaled models: acc_qkv holds floats)
+            const int heads = d->q_heads + d->kv_heads;
+            qk_norm_kernel<<<(heads + 3) / 4, 128, 0, s>>>(reinterpret_cast<float*>(d->acc_qkv), d->q_heads, d->kv_heads, d->head_dim, d->qk_norms[l * 2], d->qk_norms[l * 2 + 1], d->eps);
+            QTB_LAUNCH_CHECK();
+        }
         RopeKvArgs rk{};
         rk.acc = d->acc_qkv;
         rk.act_scale = d->s_h;
         rk.ws_q = sc[0], rk.ws_k = sc[1], rk.ws_v = sc[2];
         rk.cos_sin = d->cos_sin;
         rk.pos = d->d_pos;
-        rk.q_dim = qd, rk.kv_dim = kvd, rk.head_dim = d->head_dim, rk.rope_dims = d->rope_dims, rk.neox = d->arch == QUINTRIT_B200_ARCH_BITNET;
+        rk.q_dim = qd, rk.kv_dim = kvd, rk.head_dim = d->head_dim, rk.rope_dims = d->rope_dims, rk.neox = d->arch != QUINTRIT_B200_ARCH_LLAMA;
         rk.q_out = d->q;
         rk.k_cache = d->kc + static_cast<size_t>(l) * d->ctx * kvd;
         rk.v_cache = d->vc + static_cast<size_t>(l) * d->ctx * kvd;

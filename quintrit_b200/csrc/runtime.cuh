@@ -28,7 +28,7 @@ struct RtModelInner {
     GgufModel data;
     qtb::BpeTokenizer tok;
     std::string tok_error;  // why the file's tokenizer cannot be used (empty: it can)
-    std::string arch;       // "bitnet", "falcon3" or "llama" (quintrit-c/src/runtime.rs:222-231)
+    std::string arch;       // "bitnet", "falcon3", "qwen3" or "llama" (quintrit-c/src/runtime.rs:222-231)
     uint32_t max_ctx = 0;
     uint32_t threads = 0;   // what quintrit_model_open / _set_threads were given: reported back, used for nothing
     int32_t kernel = QUINTRIT_KERNEL_AUTO;
@@ -298,6 +298,13 @@ std::string rt_format_chat(const std::vector<std::pair<std::string, std::string>
         }
         return p + "<|assistant|>\n";
     }
+    if (arch == "qwen3") {  // ChatML with an empty thinking block (engine.rs:70-87)
+        for (const auto& m : msgs) {
+            const std::string role = role_of(m.first);
+            p += "<|im_start|>" + std::string(role == "system" || role == "assistant" ? role : "user") + "\n" + m.second + "<|im_end|>\n";
+        }
+        return p + "<|im_start|>assistant\n<think>\n\n</think>\n\n";
+    }
     for (const auto& m : msgs) {
         const std::string role = role_of(m.first);
         p += role == "system" ? "### System:\n" : (role == "assistant" ? "### Assistant:\n" : "### User:\n");
@@ -357,6 +364,7 @@ int rt_open_gpu(const char* path, const quintrit_gpu_options_t* options, quintri
         for (char& c : name) c = static_cast<char>(std::tolower(static_cast<unsigned char>(c)));
         for (char& c : base) c = static_cast<char>(std::tolower(static_cast<unsigned char>(c)));
         inner->arch = m.arch_id == QUINTRIT_B200_ARCH_BITNET ? "bitnet"
+                      : m.arch == "qwen3" ? "qwen3"
                       : (m.arch == "falcon3" || name.find("falcon") != std::string::npos || base.find("falcon") != std::string::npos) ? "falcon3" : "llama";
     }
     inner->tok_error = rt_build_tokenizer(g, &inner->tok);

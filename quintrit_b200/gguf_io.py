@@ -159,6 +159,9 @@ def write_model_gguf(path, spec: dict, trits: list, encoding: int = GGML_I2_S, a
             w = spec["norms"][l * 4 + k]
             if w is not None:
                 tensors.append((f"blk.{l}.{norm_names[k]}.weight", (len(w),), GGML_F32, np.ascontiguousarray(w, np.float32).tobytes()))
+        for k, nm in enumerate(("attn_q_norm", "attn_k_norm")):  # query/key head norms (Qwen3), head_dim values each
+            if spec.get("qk_norms"):
+                tensors.append((f"blk.{l}.{nm}.weight", (hd,), GGML_F32, np.ascontiguousarray(spec["qk_norms"][l * 2 + k], np.float32).tobytes()))
     tensors.append(("output_norm.weight", (H,), GGML_F32, np.ascontiguousarray(spec["out_norm"], np.float32).tobytes()))
     if spec.get("lm_head") is not None:
         tensors.append(("output.weight", (H, spec["vocab"]), table_type, np.ascontiguousarray(spec["lm_head"], np.uint16).tobytes()))

@@ -136,6 +136,50 @@ def test_q2_0_model_decodes_like_the_oracle(oracle, arch):
     assert e.value.code == 6
 
 
+def _head_norms(spec, seed):
+    rng = np.random.default_rng(seed)
+    return [rng.uniform(0.5, 1.5, spec["head_dim"]).astype(np.float32) for _ in range(spec["layers"] * 2)]
+
+
+def test_qwen3_shape_with_query_and_key_head_norms(oracle):
+    """Qwen3: every query and key head is RMS-normalised with its own weights before NEOX RoPE (attention.rs:282-294,
+    config.rs:424, 464-467); only block-scaled models have it, as in the reference."""
+    spec, payloads = _q2_0_model(q.ARCH_LLAMA, 29)
+    spec = dict(spec, arch=q.ARCH_QWEN, qk_norms=_head_norms(spec, 5))
+    dec = q.Decoder(dict(spec, weights=payloads))
+    ref, plain = oracle.Model(spec), oracle.Model({k: v for k, v in spec.items() if k != "qk_norms"})
+    for pos, tok in enumerate(synth.prompt_tokens(6, 12, spec["vocab"])):
+        want = ref.forward(int(tok), pos)
+        got, greedy = dec.forward(int(tok), pos)
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), f"logits differ at position {pos}"
+        assert greedy == oracle.argmax(want)
+        other = plain.forward(int(tok), pos)
+        assert pos == 0 or not np.array_equal(want, other)  # the head norms change the result once there is more than one key
+    dec.free()
+    per_tensor = synth.make_model(q.ARCH_QWEN, True, 320, 704, 2, 4, 2, 64, 300, 256, 500000.0, 1e-5, config=29)
+    with pytest.raises(q.QuintritError) as e:
+        q.Decoder(dict(per_tensor, qk_norms=_head_norms(per_tensor, 5)))
+    assert e.value.code == 6
+
+
+@pytest.mark.parametrize("f32_values", [False, True])
+def test_qwen2_shape_rotates_neox_pairs_and_keeps_swiglu(oracle, f32_values):
+    """Qwen2: LLaMA blocks with NEOX RoPE pairs (config.rs:464-467), on the single-kernel path and in prompt chunks."""
+    spec = synth.make_model(q.ARCH_QWEN, f32_values, 320, 704, 2, 4, 2, 64, 300, 256, 500000.0, 1e-5, config=31, random_norms=True)
+    toks = synth.prompt_tokens(8, 20, spec["vocab"])
+    dec, _ = _run(spec, toks[:10], oracle)
+    ref = oracle.Model(spec)
+    for pos, tok in enumerate(toks):
+        want = ref.forward(int(tok), pos)
+    got, _ = dec.prefill(toks, 0)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    llama = oracle.Model(dict(spec, arch=q.ARCH_LLAMA))
+    for pos, tok in enumerate(toks):
+        other = llama.forward(int(tok), pos)
+    assert not np.array_equal(other, want)
+    dec.free()
+
+
 @pytest.mark.parametrize("arch,f32_values", [(q.ARCH_LLAMA, False), (q.ARCH_BITNET, True)])
 def test_one_kernel_per_step_path_stays_exact(oracle, monkeypatch, arch, f32_values):
     """Both decode paths serve both architectures; QUINTRIT_B200_DECODE=kernels selects the one-kernel-per-step path, which

@@ -83,7 +83,7 @@ def test_error_classes(tmp_path):
     d = q.gguf_describe(cut)
     assert not all(t["inside_file"] for t in d["tensors"])
     moe = tmp_path / "moe.gguf"
-    gguf_io.write_gguf(moe, {"general.architecture": "qwen3"}, [])
+    gguf_io.write_gguf(moe, {"general.architecture": "qwen35"}, [])
     assert code(moe) == 6                                # QUINTRIT_ERR_UNSUPPORTED
     odd = tmp_path / "odd.gguf"
     gguf_io.write_gguf(odd, {"general.architecture": "llama", "llama.attention.key_length": 63}, [])

@@ -207,6 +207,38 @@ def _synth_like_the_reference_c_tests(path):
     gguf_io.write_model_gguf(path, spec, trits, gguf_io.GGML_I2_S, extra_metadata=tokenizer)
 
 
+def test_a_qwen3_file_loads_with_its_head_norms_and_the_chatml_prompt(tmp_path):
+    """general.architecture "qwen3": NEOX RoPE, blk.N.attn_q_norm / attn_k_norm applied to every head before it
+    (config.rs:278-279, 424, 465; engine.rs:480), ChatML with an empty thinking block as the chat prompt (engine.rs:70-87)."""
+    spec = synth.make_model(2, True, 128, 256, 2, 4, 2, 32, 264, 48, 10000.0, 1e-6, config=13, random_norms=True)
+    shapes = [(128, 128), (64, 128), (64, 128), (128, 128), (256, 128), (256, 128), (128, 256)]
+    trits = [synth.trits(synth.seed_for(13, l, p, 0), r * c).reshape(r, c) for l in range(2) for p, (r, c) in enumerate(shapes)]
+    rng = np.random.default_rng(13)
+    spec["block_scales"] = [rng.uniform(0.5, 2.0, r * c // 64).astype(np.float16).astype(np.float32) for _ in range(2) for r, c in shapes]
+    spec["qk_norms"] = [rng.uniform(0.5, 1.5, 32).astype(np.float32) for _ in range(4)]
+    tokens = [chr(0x100 + b) for b in range(256)] + ["<s>", "</s>"] + [f"<f{i}>" for i in range(6)]
+    tokenizer = {"tokenizer.ggml.model": "gpt2", "tokenizer.ggml.tokens": tokens, "tokenizer.ggml.merges": [], "tokenizer.ggml.bos_token_id": 256,
+                 "tokenizer.ggml.eos_token_id": 257, "tokenizer.ggml.add_bos_token": True}
+    path = tmp_path / "qwen3.gguf"
+    gguf_io.write_model_gguf(path, spec, trits, gguf_io.GGML_Q2_0, architecture="qwen3", extra_metadata=tokenizer)
+    m = Model.load(str(path), device="cuda")
+    assert m.architecture == "qwen3"
+    msgs = [{"role": "system", "content": "Be brief."}, {"role": " User ", "content": "hi"}, {"role": "assistant", "content": "hello"},
+            {"role": "tool", "content": "x"}]
+    assert m.format_chat(msgs) == ("<|im_start|>system\nBe brief.<|im_end|>\n<|im_start|>user\nhi<|im_end|>\n<|im_start|>assistant\nhello<|im_end|>\n"
+                                   "<|im_start|>user\nx<|im_end|>\n<|im_start|>assistant\n<think>\n\n</think>\n\n")
+    m.close()
+    from quintrit_b200 import api
+
+    dec, ref = api.Decoder.open(str(path)), oracle.Model(spec)
+    for pos, t in enumerate(synth.prompt_tokens(3, 12, 264)):
+        want = ref.forward(int(t), pos)
+        got, greedy = dec.forward(int(t), pos)
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), pos
+        assert greedy == oracle.argmax(want)
+    dec.free()
+
+
 def _run_acceptance(tmp_path, model, prompt):
     exe = tmp_path / "runtime_acceptance"
     lib_dir = os.path.join(ROOT, "quintrit_b200")
