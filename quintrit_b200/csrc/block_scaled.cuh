@@ -156,9 +156,25 @@ __device__ __forceinline__ void bs_group(const uint32_t (&w)[4], uint32_t tab_la
 // activation blocks is the period after which the pattern of accumulators repeats, so the choice is made at compile time.
 // At the end the two accumulators are added and the eight lanes reduced as ((l0+l4) + (l2+l6)) + ((l1+l5) + (l3+l7)).
 // Activations (int8 codes and block scales) are staged in shared memory once per CTA; CTAs walk the rows with a grid stride.
-__global__ void __launch_bounds__(kBsThreads) gemv_block_scaled_kernel(const uint8_t* __restrict__ planar, const float* __restrict__ w_scales,
-                                                                        const int8_t* __restrict__ qs, const float* __restrict__ a_scales, size_t rows,
-                                                                        size_t cols, float* __restrict__ out) {
+// A launch serves up to three matrices that take the same activation vector (q | k | v, gate | up): their groups of 32 rows are
+// numbered one after the other and the CTAs walk that numbering.
+struct BsMatrices {
+    const uint8_t* planar[3];
+    const float* w_scales[3];
+    float* out[3];
+    unsigned rows[3];
+    unsigned group_end[3];  // groups of 32 rows up to and including matrix i
+    int count;
+};
+inline BsMatrices bs_one_matrix(const uint8_t* planar, const float* w_scales, size_t rows, float* out) {
+    BsMatrices m{};
+    m.planar[0] = planar, m.w_scales[0] = w_scales, m.out[0] = out, m.rows[0] = static_cast<unsigned>(rows);
+    m.group_end[0] = m.group_end[1] = m.group_end[2] = static_cast<unsigned>((rows + 31) / 32);
+    m.count = 1;
+    return m;
+}
+
+__global__ void __launch_bounds__(kBsThreads) gemv_block_scaled_kernel(BsMatrices m, const int8_t* __restrict__ qs, const float* __restrict__ a_scales, size_t cols) {
     extern __shared__ __align__(16) unsigned char bs_smem[];
     uint2* tab = reinterpret_cast<uint2*>(bs_smem);
     float* s_as = reinterpret_cast<float*>(bs_smem + kBsTableBytes);            // cols / 32 floats
@@ -171,8 +187,14 @@ __global__ void __launch_bounds__(kBsThreads) gemv_block_scaled_kernel(const uin
     const int nact = static_cast<int>(cols / 32), nblocks = (nact + 4) / 5, ngroups = (nblocks + 3) / 4;
     const size_t row_words = static_cast<size_t>(nblocks) * 8, sb = cols / 64;
     const uint32_t tab_lane_addr = static_cast<uint32_t>(__cvta_generic_to_shared(tab)) + lane * 8;
-    for (size_t r0 = static_cast<size_t>(blockIdx.x) * kBsRowsPerCta; r0 < rows; r0 += static_cast<size_t>(gridDim.x) * kBsRowsPerCta) {
-        const size_t r = r0 + (threadIdx.x >> 3);
+    for (unsigned grp = blockIdx.x; grp < m.group_end[2]; grp += gridDim.x) {
+        const int which = grp < m.group_end[0] ? 0 : (grp < m.group_end[1] ? 1 : 2);
+        const unsigned grp0 = which == 0 ? 0u : (which == 1 ? m.group_end[0] : m.group_end[1]);
+        const uint8_t* __restrict__ planar = which == 0 ? m.planar[0] : (which == 1 ? m.planar[1] : m.planar[2]);
+        const float* __restrict__ w_scales = which == 0 ? m.w_scales[0] : (which == 1 ? m.w_scales[1] : m.w_scales[2]);
+        float* __restrict__ out = which == 0 ? m.out[0] : (which == 1 ? m.out[1] : m.out[2]);
+        const size_t rows = which == 0 ? m.rows[0] : (which == 1 ? m.rows[1] : m.rows[2]);
+        const size_t r = static_cast<size_t>(grp - grp0) * kBsRowsPerCta + (threadIdx.x >> 3);
         const bool valid = r < rows;
         const size_t rr = valid ? r : rows - 1;  // threads beyond the last row walk it once more and store nothing
         const uint32_t* roww = reinterpret_cast<const uint32_t*>(planar) + rr * row_words + j;

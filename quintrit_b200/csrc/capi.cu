@@ -574,7 +574,7 @@ int check_block_scaled(const quintrit_b200_matrix* m) {
 }
 int launch_block_scaled(const quintrit_b200_matrix* m) {
     const int grid = block_scaled_grid(m->rows, m->sm_count, m->cols);
-    gemv_block_scaled_kernel<<<grid, kBsThreads, block_scaled_smem_bytes(m->cols)>>>(m->d_planar, m->d_wscales, m->d_act, m->d_as, m->rows, m->cols, m->d_outf);
+    gemv_block_scaled_kernel<<<grid, kBsThreads, block_scaled_smem_bytes(m->cols)>>>(bs_one_matrix(m->d_planar, m->d_wscales, m->rows, m->d_outf), m->d_act, m->d_as, m->cols);
     ++g_launches;
     QTB_CUDA(cudaGetLastError());
     return QUINTRIT_OK;
@@ -1041,6 +1041,7 @@ int decoder_create_impl(const quintrit_b200_decoder_desc_t* desc, quintrit_b200_
         QTB_CUDA(cudaFuncSetAttribute(attn_finish_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, big_bs));
         QTB_CUDA(cudaFuncSetAttribute(act_quant_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, big_bs));
         QTB_CUDA(cudaFuncSetAttribute(lm_head_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, big_bs));
+        QTB_CUDA(cudaFuncSetAttribute(attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(attention_smem(256))));
         d->use_mega = false;
         QTB_CUDA(cudaDeviceSynchronize());
         return QUINTRIT_OK;
@@ -1087,6 +1088,7 @@ int decoder_create_impl(const quintrit_b200_decoder_desc_t* desc, quintrit_b200_
     if ((rc = allow_max_dynamic_smem(act_quant_kernel, smem_optin)) != QUINTRIT_OK) return rc;
     if ((rc = allow_max_dynamic_smem(lm_head_kernel, smem_optin)) != QUINTRIT_OK) return rc;
     if ((rc = allow_max_dynamic_smem(lm_head_batch_kernel, smem_optin)) != QUINTRIT_OK) return rc;
+    if ((rc = allow_max_dynamic_smem(attention_kernel, smem_optin)) != QUINTRIT_OK) return rc;
     // attention for all query heads of a KV head at once, where the group size and the head size allow it
     d->attn_gqa = nullptr, d->attn_gqa_smem = 0;
     if (hd % 32 == 0 && hd <= 256 && std::getenv("QUINTRIT_B200_ATTN_GQA_OFF") == nullptr) {

@@ -117,22 +117,24 @@ __device__ __forceinline__ float dot_lane_reduce_bf16(float v) {
 // (Q2_0) projection (ops.rs:898-910): one warp per block of 32 values, d = f16(amax / 127) to q8_d[block], codes rounded to
 // nearest even. `amax` is the thread's partial maximum of |y| (used by the per-tensor form only). n is a multiple of 32 in
 // the block form. All threads of the block must call it.
+// One Q8_0 block (ops.rs:898-910) by one warp: lane i holds value i of block b.
+__device__ __forceinline__ void quantize_q8_0_block(float v, int b, int lane, int8_t* q_out, float* q8_d) {
+    float m = fabsf(v);
+    if (m != m) m = 0.0f;  // f32::max ignores a NaN
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if (lane == 0) q8_d[b] = __half2float(__float2half_rn(__fdiv_rn(m, 127.0f)));
+    const float id = m != 0.0f ? __fdiv_rn(127.0f, m) : 0.0f;
+    const float r = rintf(__fmul_rn(v, id));
+    int q = 0;
+    if (r == r) q = static_cast<int>(fminf(fmaxf(r, -128.0f), 127.0f));
+    q_out[b * 32 + lane] = static_cast<int8_t>(q);
+}
+
 __device__ __forceinline__ void quantize_vector(const float* y_s, int n, float amax, int8_t* q_out, float* scale_out, float* q8_d, float* sh_f) {
     const int tid = threadIdx.x, nthreads = blockDim.x;
     if (q8_d != nullptr) {
         const int lane = tid & 31, warp = tid >> 5, nwarps = nthreads >> 5;
-        for (int b = warp; b < n / 32; b += nwarps) {
-            const float v = y_s[b * 32 + lane];
-            float m = fabsf(v);
-            if (m != m) m = 0.0f;  // f32::max ignores a NaN
-            for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-            if (lane == 0) q8_d[b] = __half2float(__float2half_rn(__fdiv_rn(m, 127.0f)));
-            const float id = m != 0.0f ? __fdiv_rn(127.0f, m) : 0.0f;
-            const float r = rintf(__fmul_rn(v, id));
-            int q = 0;
-            if (r == r) q = static_cast<int>(fminf(fmaxf(r, -128.0f), 127.0f));
-            q_out[b * 32 + lane] = static_cast<int8_t>(q);
-        }
+        for (int b = warp; b < n / 32; b += nwarps) quantize_q8_0_block(y_s[b * 32 + lane], b, lane, q_out, q8_d);
         return;
     }
     amax = block_max_f32(amax, sh_f);
@@ -399,8 +401,10 @@ struct AttnArgs {
     SeqIndex seq;             // its position and KV cache
 };
 
-constexpr int kAttnThreads = 256;
+constexpr int kAttnThreads = 1024;
 constexpr int kAttnMaxChunk = 2048;  // positions per chunk held in shared memory (context <= 8192)
+constexpr int kAttnTileRows = 32, kAttnTileStages = 6;  // the ring of key / value rows of attention_kernel
+__host__ __device__ constexpr size_t attention_smem(int head_dim) { return static_cast<size_t>(kAttnTileStages) * kAttnTileRows * head_dim * 2; }
 
 __device__ __forceinline__ float dot_lane_reduce_f16(float v) {  // (a0+a2)+(a1+a3), fold 4, two horizontal adds
     v = __fadd_rn(v, __shfl_down_sync(0xffffffffu, v, 16));
@@ -419,10 +423,45 @@ __device__ __forceinline__ float dot_lane_reduce_f16_f32(float v) {  // (a0+a1)+
     return v;  // lane 0
 }
 
+__device__ __forceinline__ void attn_cp16(void* smem_dst, const void* gsrc) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst))), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void attn_cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void attn_cp_wait_all_but_one() { asm volatile("cp.async.wait_group 1;" ::: "memory"); }
+
+// Requests tile t (32 rows, those below len) of a chunk's key or value rows into its stage of the ring; always closes a copy
+// group, so every thread counts the same groups.
+__device__ __forceinline__ void attn_tile_issue(__half* ring, const __half* rows, int t, int len, int hd, int kv_dim, int tid) {
+    const int row0 = t * kAttnTileRows;
+    if (row0 < len) {
+        __half* stage = ring + static_cast<size_t>(t % kAttnTileStages) * kAttnTileRows * hd;
+        const int pieces = hd >> 3, n = min(kAttnTileRows, len - row0) * pieces;  // 16-byte pieces
+        for (int i = tid; i < n; i += kAttnThreads) {
+            const int r = i / pieces, c = i - r * pieces;
+            attn_cp16(stage + r * hd + c * 8, rows + static_cast<size_t>(row0 + r) * kv_dim + c * 8);
+        }
+    }
+    attn_cp_commit();
+}
+__device__ __forceinline__ void attn_tile_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(kAttnTileStages - 2) : "memory"); }
+
+// One query head and one of the four KV chunks per block (attention.rs:402-469), grid (q_heads, 4, tokens), 1024 threads.
+// A block waits for memory, not for arithmetic: a chunk of a long context is a few hundred KB of rows read once. So the key
+// rows (phase A) and then the value rows (phase C) stream through a ring of six 32-row tiles in shared memory, requested
+// five tiles ahead by all threads with 16-byte asynchronous copies: about 80 KB in flight per block.
+//  A. warp w forms the score of row w of the tile (the lane order of ggml_vec_dot_f16 / _f16_f32);
+//  B. a scan over the scores gives every position its running maximum and from it the factors ms (rescale of what came
+//     before) and vs (weight of this row) - the running maximum is a prefix maximum, so the scan gives the sequential values;
+//  C. thread d < head_dim runs the chain of coordinate d over the tile's rows, in position order; meanwhile the first lane
+//     of the last warp runs the chain of the sum S over the same positions.
+// Dynamic shared memory: attention_smem(head_dim).
 __global__ void __launch_bounds__(kAttnThreads) attention_kernel(AttnArgs a) {
     __shared__ float s_score[kAttnMaxChunk];  // scores, then vs
-    __shared__ float s_ms[kAttnMaxChunk];     // prefix maximum, then ms
+    __shared__ float s_ms[kAttnMaxChunk];     // ms
     __shared__ float s_q[256];
+    __shared__ float s_tm[kAttnThreads / 32];
+    extern __shared__ __align__(16) unsigned char attn_ring_raw[];
+    __half* ring = reinterpret_cast<__half*>(attn_ring_raw);
     const int h = blockIdx.x, c = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int hd = a.head_dim, kvh = h / a.gqa;
     if (blockIdx.z != 0) {
@@ -455,40 +494,47 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(AttnArgs a) {
         }
         return;
     }
+    const __half* krows = a.k_cache + static_cast<size_t>(kvh) * hd + static_cast<size_t>(start) * a.kv_dim;
+    const __half* vrows = a.v_cache + static_cast<size_t>(kvh) * hd + static_cast<size_t>(start) * a.kv_dim;
+    const int tiles = (len + kAttnTileRows - 1) / kAttnTileRows;
+    for (int t = 0; t < kAttnTileStages - 1; ++t) attn_tile_issue(ring, krows, t, len, hd, a.kv_dim, tid);
     // the query: F16-rounded for bitnet.cpp numerics (attention.rs:212-214), F32 for llama.cpp numerics
-    for (int d = tid; d < hd; d += kAttnThreads) {
-        const float qv = a.q[h * hd + d];
-        s_q[d] = a.f32_values ? qv : __half2float(__float2half_rn(qv));
+    if (tid < hd) {
+        const float qv = a.q[h * hd + tid];
+        s_q[tid] = a.f32_values ? qv : __half2float(__float2half_rn(qv));
     }
-    __syncthreads();
-    const __half* kbase = a.k_cache + static_cast<size_t>(kvh) * hd;
-    const __half* vbase = a.v_cache + static_cast<size_t>(kvh) * hd;
     // Phase A
-    for (int p = warp; p < len; p += kAttnThreads / 32) {
-        const __half* kr = kbase + static_cast<size_t>(start + p) * a.kv_dim;
-        float acc = 0.0f;
-        int i = 0;
-        for (; i + 32 <= hd; i += 32) acc = __fmaf_rn(__half2float(kr[i + lane]), s_q[i + lane], acc);
-        float sc;
-        if (a.f32_values) {
-            sc = dot_lane_reduce_f16_f32(acc);
-        } else {
-            sc = dot_lane_reduce_f16(acc);
+    for (int t = 0; t < tiles; ++t) {
+        attn_tile_wait();
+        __syncthreads();  // tile t has arrived for every thread, and every warp is done with tile t - 1, whose stage the next request reuses
+        attn_tile_issue(ring, krows, t + kAttnTileStages - 1, len, hd, a.kv_dim, tid);
+        const int p = t * kAttnTileRows + warp;
+        if (p < len) {
+            const __half* kr = ring + (static_cast<size_t>(t % kAttnTileStages) * kAttnTileRows + warp) * hd;
+            float acc = 0.0f;
+            for (int i = 0; i + 32 <= hd; i += 32) acc = __fmaf_rn(__half2float(kr[i + lane]), s_q[i + lane], acc);
+            const float sc = a.f32_values ? dot_lane_reduce_f16_f32(acc) : dot_lane_reduce_f16(acc);
+            if (lane == 0) s_score[p] = __fmul_rn(sc, a.scale);
         }
-        if (lane == 0) s_score[p] = __fmul_rn(sc, a.scale);
     }
-    __syncthreads();
-    // Phase B: s_ms[p] = max(score[0..p]) by a block-wide inclusive scan in position order
+    __syncthreads();  // all scores are written and every stage is free
+    for (int t = 0; t < kAttnTileStages - 1; ++t) attn_tile_issue(ring, vrows, t, len, hd, a.kv_dim, tid);  // the value rows travel during phase B
+    // Phase B: thread tid owns positions p0 .. p1; the maximum of everything before p0 comes from a scan in position order
     {
         const int per = (len + kAttnThreads - 1) / kAttnThreads;
-        const int p0 = tid * per, p1 = min(p0 + per, len);
+        const int p0 = min(tid * per, len), p1 = min(p0 + per, len);
         float m = -INFINITY;
         for (int p = p0; p < p1; ++p) m = fmaxf(m, s_score[p]);
-        __shared__ float s_tm[kAttnThreads];
-        s_tm[tid] = m;
+        float incl = m;
+        for (int o = 1; o < 32; o <<= 1) {
+            const float up = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl = fmaxf(incl, up);
+        }
+        float before = __shfl_up_sync(0xffffffffu, incl, 1);
+        if (lane == 0) before = -INFINITY;
+        if (lane == 31) s_tm[warp] = incl;
         __syncthreads();
-        float before = -INFINITY;
-        for (int t = 0; t < tid; ++t) before = fmaxf(before, s_tm[t]);
+        for (int w = 0; w < warp; ++w) before = fmaxf(before, s_tm[w]);
         float run = before;
         for (int p = p0; p < p1; ++p) {
             const float sc = s_score[p];
@@ -503,35 +549,40 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(AttnArgs a) {
             s_ms[p] = ms;
             s_score[p] = vs;
         }
+    }
+    // Phase C (the barrier of its first tile also publishes the factors of phase B)
+    float acc = 0.0f, S = 0.0f;
+    const bool sum_lane = tid == kAttnThreads - 32;
+    for (int t = 0; t < tiles; ++t) {
+        attn_tile_wait();
         __syncthreads();
-        if (tid == 0) {
-            float S = 0.0f, M = -INFINITY;
-            for (int t = 0; t < kAttnThreads; ++t) M = fmaxf(M, s_tm[t]);
-            for (int p = 0; p < len; ++p) S = __fmaf_rn(S, s_ms[p], s_score[p]);  // attention.rs:466
-            my_ms[0] = M;
-            my_ms[1] = S;
+        attn_tile_issue(ring, vrows, t + kAttnTileStages - 1, len, hd, a.kv_dim, tid);
+        const int p_lo = t * kAttnTileRows, rows = min(kAttnTileRows, len - p_lo);
+        if (tid < hd) {
+            const __half* vr = ring + static_cast<size_t>(t % kAttnTileStages) * kAttnTileRows * hd + tid;
+            if (a.f32_values) {
+                for (int r = 0; r < rows; ++r) {
+                    const float ms = s_ms[p_lo + r];
+                    if (ms != 1.0f) acc = __fmul_rn(acc, ms);
+                    acc = __fmaf_rn(__half2float(vr[r * hd]), s_score[p_lo + r], acc);
+                }
+            } else {  // the accumulator is an F16 after every operation
+                for (int r = 0; r < rows; ++r) {
+                    const float ms = s_ms[p_lo + r];
+                    if (ms != 1.0f) acc = __half2float(__float2half_rn(__fmul_rn(acc, ms)));
+                    acc = __half2float(__float2half_rn(__fmaf_rn(__half2float(vr[r * hd]), s_score[p_lo + r], acc)));
+                }
+            }
+        } else if (sum_lane) {
+            for (int r = 0; r < rows; ++r) S = __fmaf_rn(S, s_ms[p_lo + r], s_score[p_lo + r]);  // attention.rs:466
         }
     }
-    // Phase C
-    for (int d = tid; d < hd; d += kAttnThreads) {
-        const __half* vr = vbase + static_cast<size_t>(start) * a.kv_dim + d;
-        if (a.f32_values) {
-            float acc = 0.0f;
-            for (int p = 0; p < len; ++p) {
-                const float ms = s_ms[p];
-                if (ms != 1.0f) acc = __fmul_rn(acc, ms);
-                acc = __fmaf_rn(__half2float(vr[static_cast<size_t>(p) * a.kv_dim]), s_score[p], acc);
-            }
-            my_acc[d] = acc;
-        } else {
-            __half acc = __float2half_rn(0.0f);
-            for (int p = 0; p < len; ++p) {
-                const float ms = s_ms[p];
-                if (ms != 1.0f) acc = __float2half_rn(__fmul_rn(__half2float(acc), ms));
-                acc = __float2half_rn(__fmaf_rn(__half2float(vr[static_cast<size_t>(p) * a.kv_dim]), s_score[p], __half2float(acc)));
-            }
-            my_acc[d] = __half2float(acc);
-        }
+    if (tid < hd) my_acc[tid] = acc;
+    if (sum_lane) {
+        float M = -INFINITY;
+        for (int w = 0; w < kAttnThreads / 32; ++w) M = fmaxf(M, s_tm[w]);
+        my_ms[0] = M;
+        my_ms[1] = S;
     }
 }
 
@@ -562,11 +613,6 @@ __device__ __forceinline__ float value_round(float x) {  // the accumulator is a
     return F32 ? x : __half2float(__float2half_rn(x));
 }
 
-__device__ __forceinline__ void attn_cp16(void* smem_dst, const void* gsrc) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst))), "l"(gsrc) : "memory");
-}
-__device__ __forceinline__ void attn_cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void attn_cp_wait_all_but_one() { asm volatile("cp.async.wait_group 1;" ::: "memory"); }
 
 // Requests rows row0 .. row0 + 15 (those below len) of a chunk into a stage; always closes a copy group, so every thread counts the same groups.
 __device__ __forceinline__ void attn_ring_issue(__half* stage, const __half* rows, int row0, int len, int hd, int kv_dim, int tid) {
@@ -792,6 +838,43 @@ struct AttnFinishArgs {
     SeqIndex seq;             // the token's position
 };
 
+// Coordinate d of head h from the four chunks' accumulators and their (M, S) pairs (attention.rs:497-541).
+__device__ __forceinline__ float attn_combine_chunks(const float* part_acc, const float* part_ms, int h, int d, int hd, int n_kv) {
+    const float* pa = part_acc + static_cast<size_t>(h) * 4 * hd + d;
+    const float* pm = part_ms + static_cast<size_t>(h) * 8;
+    if (n_kv < 512) {
+        const float S = pm[1];
+        const float s_inv = S == 0.0f ? 0.0f : __fdiv_rn(1.0f, S);
+        return __fmul_rn(pa[0], s_inv);
+    }
+    float m_final = -INFINITY, s_final = 0.0f, acc = 0.0f;
+    for (int c = 0; c < 4; ++c) {
+        const float m_chunk = pm[2 * c], s_chunk = pm[2 * c + 1];
+        if (s_chunk == 0.0f) continue;  // empty or fully masked chunk
+        const float m_new = fmaxf(m_final, m_chunk);
+        const float scale_old = device_expf(__fsub_rn(m_final, m_new));
+        const float scale_new = device_expf(__fsub_rn(m_chunk, m_new));
+        acc = __fmaf_rn(acc, scale_old, __fmul_rn(pa[c * hd], scale_new));
+        s_final = __fmaf_rn(s_final, scale_old, __fmul_rn(s_chunk, scale_new));
+        m_final = m_new;
+    }
+    return s_final != 0.0f ? __fmul_rn(acc, __fdiv_rn(1.0f, s_final)) : acc;
+}
+
+// Block-scaled models without a sub-norm: a Q8_0 block of 32 values needs nothing from the rest of the vector, so one warp
+// combines and quantises one block and the vector spreads over as many blocks of threads as it has blocks of eight. One token.
+constexpr int kQ8BlockThreads = 256;
+__global__ void __launch_bounds__(kQ8BlockThreads) attn_finish_q8_kernel(AttnFinishArgs a) {
+    const int lane = threadIdx.x & 31, b = blockIdx.x * (kQ8BlockThreads / 32) + (threadIdx.x >> 5), hd = a.head_dim;
+    if (b >= a.q_heads * hd / 32) return;
+    const int seq_len = static_cast<int>(seq_position(a.seq, a.pos, 0)) + 1;
+    int n_kv = (seq_len + 255) / 256 * 256;
+    if (n_kv < 256) n_kv = 256;
+    if (n_kv > a.ctx) n_kv = a.ctx;
+    const int i = b * 32 + lane;
+    quantize_q8_0_block(attn_combine_chunks(a.part_acc, a.part_ms, i / hd, i % hd, hd, n_kv), b, lane, a.q_out, a.q8_d);
+}
+
 __global__ void __launch_bounds__(kRowThreads) attn_finish_kernel(AttnFinishArgs a) {
     __shared__ double sh_d[32];
     __shared__ float sh_f[32];
@@ -809,31 +892,7 @@ __global__ void __launch_bounds__(kRowThreads) attn_finish_kernel(AttnFinishArgs
     int n_kv = (seq_len + 255) / 256 * 256;
     if (n_kv < 256) n_kv = 256;
     if (n_kv > a.ctx) n_kv = a.ctx;
-    for (int i = tid; i < n; i += kRowThreads) {
-        const int h = i / hd, d = i % hd;
-        const float* pa = a.part_acc + static_cast<size_t>(h) * 4 * hd + d;
-        const float* pm = a.part_ms + static_cast<size_t>(h) * 8;
-        float out;
-        if (n_kv < 512) {
-            const float S = pm[1];
-            const float s_inv = S == 0.0f ? 0.0f : __fdiv_rn(1.0f, S);
-            out = __fmul_rn(pa[0], s_inv);
-        } else {
-            float m_final = -INFINITY, s_final = 0.0f, acc = 0.0f;
-            for (int c = 0; c < 4; ++c) {
-                const float m_chunk = pm[2 * c], s_chunk = pm[2 * c + 1];
-                if (s_chunk == 0.0f) continue;  // empty or fully masked chunk
-                const float m_new = fmaxf(m_final, m_chunk);
-                const float scale_old = device_expf(__fsub_rn(m_final, m_new));
-                const float scale_new = device_expf(__fsub_rn(m_chunk, m_new));
-                acc = __fmaf_rn(acc, scale_old, __fmul_rn(pa[c * hd], scale_new));
-                s_final = __fmaf_rn(s_final, scale_old, __fmul_rn(s_chunk, scale_new));
-                m_final = m_new;
-            }
-            out = s_final != 0.0f ? __fmul_rn(acc, __fdiv_rn(1.0f, s_final)) : acc;
-        }
-        y_s[i] = out;
-    }
+    for (int i = tid; i < n; i += kRowThreads) y_s[i] = attn_combine_chunks(a.part_acc, a.part_ms, i / hd, i % hd, hd, n_kv);
     __syncthreads();
     if (a.sub_norm_w != nullptr) {
         double sum = 0.0;
@@ -868,6 +927,22 @@ struct ActQuantArgs {
     int b_acc, b_q, b_scale;  // batch of tokens: per-token strides of acc_gate / acc_up and of q_out; act_scale + z and scale_out + z when b_scale is set
     AccView v_gate, v_up;     // the two projections' sums as parts (v_gate.base != nullptr), instead of acc_gate / acc_up
 };
+
+// The same for block-scaled models without an FFN sub-norm: one warp per Q8_0 block of the gated vector. One token.
+__global__ void __launch_bounds__(kQ8BlockThreads) act_quant_q8_kernel(ActQuantArgs a) {
+    const int lane = threadIdx.x & 31, b = blockIdx.x * (kQ8BlockThreads / 32) + (threadIdx.x >> 5);
+    if (b >= a.n / 32) return;
+    const int i = b * 32 + lane;
+    const float g = reinterpret_cast<const float*>(a.acc_gate)[i], u = reinterpret_cast<const float*>(a.acc_up)[i];
+    float v;
+    if (a.relu2) {
+        const float p = g > 0.0f ? g : 0.0f;
+        v = __fmul_rn(__fmul_rn(p, p), u);
+    } else {
+        v = __fmul_rn(ggml_silu(g), u);
+    }
+    quantize_q8_0_block(v, b, lane, a.q_out, a.q8_d);
+}
 
 __global__ void __launch_bounds__(kRowThreads) act_quant_kernel(ActQuantArgs a) {
     __shared__ double sh_d[32];
@@ -1110,9 +1185,26 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ 
     out_token += blockIdx.x;
     float bv = -INFINITY;
     unsigned int bi = 0xFFFFFFFFu;
-    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    int done = 0;
+    if (n % 4 == 0) {  // rows start on 16-byte boundaries: four values per load, four loads in flight, indices ascending per thread
+        const float4* l4 = reinterpret_cast<const float4*>(logits);
+        const int n4 = n / 4;
+#pragma unroll 4
+        for (int i = threadIdx.x; i < n4; i += blockDim.x) {
+            const float4 v = l4[i];
+            const float e[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+                if (e[k] > bv) {  // strict: the earlier index stays on ties
+                    bv = e[k];
+                    bi = static_cast<unsigned int>(i * 4 + k);
+                }
+        }
+        done = n;
+    }
+    for (int i = done + threadIdx.x; i < n; i += blockDim.x) {
         const float v = logits[i];
-        if (v > bv) {  // strict: the earlier index stays on ties
+        if (v > bv) {
             bv = v;
             bi = static_cast<unsigned int>(i);
         }

@@ -140,10 +140,25 @@ inline int decoder_gemv(quintrit_b200_decoder* d, int layer, int which, const in
 }
 
 // Block-scaled projection `which` (0..6) of a layer: out (F32) = W x for Q8_0 blocks (codes, d->q8_d).
-inline int decoder_gemv_bs(quintrit_b200_decoder* d, int layer, int which, const int8_t* codes, float* out) {
-    const quintrit_b200_matrix* m = d->mats[static_cast<size_t>(layer) * 7 + which];
-    const int grid = block_scaled_grid(m->rows, d->sm_count, m->cols);
-    gemv_block_scaled_kernel<<<grid, kBsThreads, block_scaled_smem_bytes(m->cols), d->stream>>>(m->d_planar, m->d_wscales, codes, d->q8_d, m->rows, m->cols, out);
+// Block-scaled projections `first` .. `first + count - 1` of a layer (at most three, all over the activation codes `codes`) in one
+// launch; their results go to `out` one after the other.
+inline int decoder_gemv_bs(quintrit_b200_decoder* d, int layer, int first, const int8_t* codes, float* out, int count = 1) {
+    BsMatrices bm{};
+    size_t rows_all = 0;
+    unsigned groups = 0;
+    const quintrit_b200_matrix* m0 = d->mats[static_cast<size_t>(layer) * 7 + first];
+    for (int i = 0; i < 3; ++i) {
+        if (i < count) {
+            const quintrit_b200_matrix* m = d->mats[static_cast<size_t>(layer) * 7 + first + i];
+            bm.planar[i] = m->d_planar, bm.w_scales[i] = m->d_wscales, bm.out[i] = out + rows_all, bm.rows[i] = static_cast<unsigned>(m->rows);
+            rows_all += m->rows;
+            groups += static_cast<unsigned>((m->rows + kBsRowsPerCta - 1) / kBsRowsPerCta);
+        }
+        bm.group_end[i] = groups;
+    }
+    bm.count = count;
+    const int grid = block_scaled_grid(static_cast<size_t>(groups) * kBsRowsPerCta, d->sm_count, m0->cols);
+    gemv_block_scaled_kernel<<<grid, kBsThreads, block_scaled_smem_bytes(m0->cols), d->stream>>>(bm, codes, d->q8_d, m0->cols);
     ++g_launches;
     const cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "block-scaled GEMV launch");
@@ -152,10 +167,11 @@ inline int decoder_gemv_bs(quintrit_b200_decoder* d, int layer, int which, const
 
 // Attention of n tokens: all query heads of a KV head in one block where an instantiation exists, else one query head per block.
 inline void launch_attention(quintrit_b200_decoder* d, const AttnArgs& at, int n, cudaStream_t s) {
-    if (d->attn_gqa != nullptr)
+    // several tokens: the query heads of a KV head share one pass over its rows; one token: more, wider blocks pull the rows faster
+    if (d->attn_gqa != nullptr && n > 1)
         d->attn_gqa<<<dim3(d->kv_heads, 4, n), kAttnGqaThreads, d->attn_gqa_smem + d->attn_gqa_pad, s>>>(at);
     else
-        attention_kernel<<<dim3(d->q_heads, 4, n), kAttnThreads, 0, s>>>(at);
+        attention_kernel<<<dim3(d->q_heads, 4, n), kAttnThreads, attention_smem(d->head_dim), s>>>(at);
 }
 
 #define QTB_LAUNCH_CHECK()                                   \
@@ -194,9 +210,7 @@ inline int enqueue_token(quintrit_b200_decoder* d, bool with_head) {
         int rc;
         if (bs) {
             float* f = reinterpret_cast<float*>(d->acc_qkv);
-            if ((rc = decoder_gemv_bs(d, l, 0, d->a8_h, f)) != QUINTRIT_OK || (rc = decoder_gemv_bs(d, l, 1, d->a8_h, f + qd)) != QUINTRIT_OK ||
-                (rc = decoder_gemv_bs(d, l, 2, d->a8_h, f + qd + kvd)) != QUINTRIT_OK)
-                return rc;
+            if ((rc = decoder_gemv_bs(d, l, 0, d->a8_h, f, 3)) != QUINTRIT_OK) return rc;  // q | k | v
         } else if ((rc = decoder_gemv(d, l, 0, d->a8_h, d->acc_qkv)) != QUINTRIT_OK) {
             return rc;
         }
@@ -241,7 +255,10 @@ inline int enqueue_token(quintrit_b200_decoder* d, bool with_head) {
         af.zero_a = d->acc_o;
         af.zero_a_n = bs ? 0 : H;
         af.q8_d = bs ? d->q8_d : nullptr;
-        attn_finish_kernel<<<1, kRowThreads, qd * sizeof(float), s>>>(af);
+        if (bs && af.sub_norm_w == nullptr)
+            attn_finish_q8_kernel<<<(qd / 32 + kQ8BlockThreads / 32 - 1) / (kQ8BlockThreads / 32), kQ8BlockThreads, 0, s>>>(af);
+        else
+            attn_finish_kernel<<<1, kRowThreads, qd * sizeof(float), s>>>(af);
         QTB_LAUNCH_CHECK();
         rc = bs ? decoder_gemv_bs(d, l, 3, d->a8_q, reinterpret_cast<float*>(d->acc_o)) : decoder_gemv(d, l, 1, d->a8_q, d->acc_o);
         if (rc != QUINTRIT_OK) return rc;
@@ -262,7 +279,7 @@ inline int enqueue_token(quintrit_b200_decoder* d, bool with_head) {
         QTB_LAUNCH_CHECK();
         if (bs) {
             float* f = reinterpret_cast<float*>(d->acc_gu);
-            if ((rc = decoder_gemv_bs(d, l, 4, d->a8_h, f)) != QUINTRIT_OK || (rc = decoder_gemv_bs(d, l, 5, d->a8_h, f + I)) != QUINTRIT_OK) return rc;
+            if ((rc = decoder_gemv_bs(d, l, 4, d->a8_h, f, 2)) != QUINTRIT_OK) return rc;  // gate | up
         } else if ((rc = decoder_gemv(d, l, 2, d->a8_h, d->acc_gu)) != QUINTRIT_OK) {
             return rc;
         }
@@ -279,7 +296,10 @@ inline int enqueue_token(quintrit_b200_decoder* d, bool with_head) {
         aq.zero_a = d->acc_down;
         aq.zero_a_n = bs ? 0 : H;
         aq.block_scaled = bs, aq.q8_d = d->q8_d;
-        act_quant_kernel<<<1, kRowThreads, I * sizeof(float), s>>>(aq);
+        if (bs && aq.sub_norm_w == nullptr)
+            act_quant_q8_kernel<<<(I / 32 + kQ8BlockThreads / 32 - 1) / (kQ8BlockThreads / 32), kQ8BlockThreads, 0, s>>>(aq);
+        else
+            act_quant_kernel<<<1, kRowThreads, I * sizeof(float), s>>>(aq);
         QTB_LAUNCH_CHECK();
         rc = bs ? decoder_gemv_bs(d, l, 6, d->a8_i, reinterpret_cast<float*>(d->acc_down)) : decoder_gemv(d, l, 3, d->a8_i, d->acc_down);
         if (rc != QUINTRIT_OK) return rc;

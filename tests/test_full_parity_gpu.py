@@ -59,7 +59,8 @@ def check_against_fixture(model: str, variant: str, tables: str, encoding: int, 
         rel = float(np.max(np.abs(logits - want)) / max(np.max(np.abs(want)), 1e-30))
         assert bit_exact, f"{name}: last logits differ, max-abs relative {rel:.3g}"
         return {"fixture": name, "encoding": encoding, "layers": info["num_layers"], "prompt": P, "greedy_tokens_checked": G, "identical": True,
-                "logits_bit_exact": bit_exact, "logits_max_rel": rel, "smallest_margin": float(fx["margins"].min()), "single_kernel": info["single_kernel"]}
+                "logits_bit_exact": bit_exact, "logits_max_rel": rel, "smallest_margin": float(fx["margins"].min()), "single_kernel": info["single_kernel"],
+                "ms_per_token": round(dec.time_token(3, 20), 4), "context": P + G - 1}
     finally:
         dec.free()
 
