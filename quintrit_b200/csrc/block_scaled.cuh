@@ -114,13 +114,19 @@ __device__ __forceinline__ uint2 bs_lookup(uint32_t w, uint32_t tab_lane_addr) {
 
 // Four 160-trit blocks = twenty activation blocks s0 .. s0 + 19 of one thread's bytes. FULL: all twenty exist.
 template <bool FULL>
-__device__ __forceinline__ void bs_group(const uint32_t (&w)[4], uint32_t tab_lane_addr, const int* __restrict__ q4, const float* __restrict__ as, const float* __restrict__ ws, int s0,
+__device__ __forceinline__ void bs_group(const uint32_t (&w)[4], uint32_t tab_lane_addr, const int4* __restrict__ q4, const float4* __restrict__ as, float ws_a, float ws_b, int s0,
                                          int nact, float& acc0, float& acc1) {
     float wsc[10], asc[20];
+    int qv[20];
 #pragma unroll
-    for (int k = 0; k < 10; ++k) wsc[k] = (FULL || s0 + 2 * k < nact) ? __ldg(ws + k) : 0.0f;
+    for (int k = 0; k < 10; ++k) wsc[k] = __shfl_sync(0xffffffffu, k < 8 ? ws_a : ws_b, k & 7, 8);  // lane k (k - 8) of the row's eight holds scale k (zero past the end)
 #pragma unroll
-    for (int k = 0; k < 20; ++k) asc[k] = (FULL || s0 + k < nact) ? as[k] : 0.0f;
+    for (int t = 0; t < 5; ++t) {  // the group's twenty activation scales and this lane's twenty code words: five 16-byte loads each (zeros past the end)
+        const float4 a4 = as[t];
+        const int4 c4 = q4[t];
+        asc[4 * t] = a4.x, asc[4 * t + 1] = a4.y, asc[4 * t + 2] = a4.z, asc[4 * t + 3] = a4.w;
+        qv[4 * t] = c4.x, qv[4 * t + 1] = c4.y, qv[4 * t + 2] = c4.z, qv[4 * t + 3] = c4.w;
+    }
 #pragma unroll
     for (int bi = 0; bi < 4; ++bi) {
         const uint2 e0 = bs_lookup<0>(w[bi], tab_lane_addr), e1 = bs_lookup<1>(w[bi], tab_lane_addr), e2 = bs_lookup<2>(w[bi], tab_lane_addr), e3 = bs_lookup<3>(w[bi], tab_lane_addr);
@@ -137,7 +143,7 @@ __device__ __forceinline__ void bs_group(const uint32_t (&w)[4], uint32_t tab_la
         for (int p = 0; p < 5; ++p) {
             const int i = bi * 5 + p;
             if (FULL || s0 + i < nact) {
-                const float sum = static_cast<float>(__dp4a(static_cast<int>(plane[p]), q4[i * 8], 0));
+                const float sum = static_cast<float>(__dp4a(static_cast<int>(plane[p]), qv[i], 0));
                 const float dd = __fmul_rn(wsc[i >> 1], asc[i]);
                 if ((i >> 1) & 1)
                     acc1 = __fmaf_rn(dd, sum, acc1);
@@ -174,17 +180,23 @@ inline BsMatrices bs_one_matrix(const uint8_t* planar, const float* w_scales, si
     return m;
 }
 
-__global__ void __launch_bounds__(kBsThreads) gemv_block_scaled_kernel(BsMatrices m, const int8_t* __restrict__ qs, const float* __restrict__ a_scales, size_t cols) {
+__global__ void __launch_bounds__(kBsThreads, 3) gemv_block_scaled_kernel(BsMatrices m, const int8_t* __restrict__ qs, const float* __restrict__ a_scales, size_t cols) {
     extern __shared__ __align__(16) unsigned char bs_smem[];
     uint2* tab = reinterpret_cast<uint2*>(bs_smem);
-    float* s_as = reinterpret_cast<float*>(bs_smem + kBsTableBytes);            // cols / 32 floats
-    int* s_q4 = reinterpret_cast<int*>(s_as + cols / 32);                       // cols codes, read as words of four
+    const int nact = static_cast<int>(cols / 32), nblocks = (nact + 4) / 5, ngroups = (nblocks + 3) / 4;
+    // Activations, staged once per CTA in the order the walk reads them: twenty scales per group of four blocks, and per group
+    // and lane j the twenty code words (activation block s, bytes 4j .. 4j + 3) side by side - so a walk step fetches each with
+    // five 16-byte loads, the eight lanes of a row from eight different bank groups. Zeros past the end of the row.
+    float* s_as = reinterpret_cast<float*>(bs_smem + kBsTableBytes);  // ngroups * 20 floats
+    int* s_q4 = reinterpret_cast<int*>(s_as + ngroups * 20);         // ngroups * 8 * 20 words
     build_trit_table(tab);
-    for (size_t i = threadIdx.x; i < cols / 32; i += kBsThreads) s_as[i] = a_scales[i];
-    for (size_t i = threadIdx.x; i < cols / 4; i += kBsThreads) s_q4[i] = reinterpret_cast<const int*>(qs)[i];
+    for (int i = threadIdx.x; i < ngroups * 20; i += kBsThreads) s_as[i] = i < nact ? a_scales[i] : 0.0f;
+    for (int i = threadIdx.x; i < ngroups * 160; i += kBsThreads) {
+        const int s = i >> 3, jj = i & 7;  // word jj of activation block s: read in the order of the codes, stored transposed
+        s_q4[((s / 20) * 8 + jj) * 20 + s % 20] = s < nact ? reinterpret_cast<const int*>(qs)[i] : 0;
+    }
     __syncthreads();
     const int lane = threadIdx.x & 31, j = lane & 7;
-    const int nact = static_cast<int>(cols / 32), nblocks = (nact + 4) / 5, ngroups = (nblocks + 3) / 4;
     const size_t row_words = static_cast<size_t>(nblocks) * 8, sb = cols / 64;
     const uint32_t tab_lane_addr = static_cast<uint32_t>(__cvta_generic_to_shared(tab)) + lane * 8;
     for (unsigned grp = blockIdx.x; grp < m.group_end[2]; grp += gridDim.x) {
@@ -200,22 +212,30 @@ __global__ void __launch_bounds__(kBsThreads) gemv_block_scaled_kernel(BsMatrice
         const uint32_t* roww = reinterpret_cast<const uint32_t*>(planar) + rr * row_words + j;
         const float* ws = w_scales + rr * sb;
         float acc0 = 0.0f, acc1 = 0.0f;
-        uint32_t next[4];
+        // What a group needs from memory - the lane's four words and the row's ten weight scales, of which lane j fetches
+        // scale j and lanes 0 and 1 also scales 8 and 9 - is requested two groups ahead and held in registers meanwhile.
+        uint32_t n1[4], n2[4];
+        float a1, b1, a2, b2;
+        auto fetch = [&](int g, uint32_t (&nw)[4], float& sa, float& sb2) {
 #pragma unroll
-        for (int bi = 0; bi < 4; ++bi) next[bi] = bi < nblocks ? __ldg(roww + bi * 8) : 0x7D7D7D7Du;
+            for (int bi = 0; bi < 4; ++bi) nw[bi] = g * 4 + bi < nblocks ? __ldg(roww + (g * 4 + bi) * 8) : 0x7D7D7D7Du;  // byte 125: five zero trits
+            sa = g * 10 + j < static_cast<int>(sb) ? __ldg(ws + g * 10 + j) : 0.0f;
+            sb2 = (j < 2 && g * 10 + 8 + j < static_cast<int>(sb)) ? __ldg(ws + g * 10 + 8 + j) : 0.0f;
+        };
+        fetch(0, n1, a1, b1);
+        fetch(1, n2, a2, b2);
         for (int g = 0; g < ngroups; ++g) {
             uint32_t w[4];
 #pragma unroll
-            for (int bi = 0; bi < 4; ++bi) {
-                w[bi] = next[bi];
-                const int b = (g + 1) * 4 + bi;
-                next[bi] = b < nblocks ? __ldg(roww + b * 8) : 0x7D7D7D7Du;  // byte 125: five zero trits
-            }
+            for (int bi = 0; bi < 4; ++bi) w[bi] = n1[bi], n1[bi] = n2[bi];
+            const float wa = a1, wb = b1;
+            a1 = a2, b1 = b2;
+            fetch(g + 2, n2, a2, b2);
             const int s0 = g * 20;
             if (s0 + 20 <= nact)
-                bs_group<true>(w, tab_lane_addr, s_q4 + s0 * 8 + j, s_as + s0, ws + s0 / 2, s0, nact, acc0, acc1);
+                bs_group<true>(w, tab_lane_addr, reinterpret_cast<const int4*>(s_q4) + (g * 8 + j) * 5, reinterpret_cast<const float4*>(s_as) + g * 5, wa, wb, s0, nact, acc0, acc1);
             else
-                bs_group<false>(w, tab_lane_addr, s_q4 + s0 * 8 + j, s_as + s0, ws + s0 / 2, s0, nact, acc0, acc1);
+                bs_group<false>(w, tab_lane_addr, reinterpret_cast<const int4*>(s_q4) + (g * 8 + j) * 5, reinterpret_cast<const float4*>(s_as) + g * 5, wa, wb, s0, nact, acc0, acc1);
         }
         float l = __fadd_rn(acc0, acc1);
         const float up4 = __shfl_down_sync(0xffffffffu, l, 4, 8);
@@ -228,7 +248,8 @@ __global__ void __launch_bounds__(kBsThreads) gemv_block_scaled_kernel(BsMatrice
     }
 }
 
-__host__ __device__ constexpr size_t block_scaled_smem_bytes(size_t cols) { return ((kBsTableBytes + (cols / 32) * 4 + cols + 15) / 16) * 16; }
+__host__ __device__ constexpr size_t block_scaled_groups(size_t cols) { return ((cols / 32 + 4) / 5 + 3) / 4; }  // groups of four 160-trit blocks in a row
+__host__ __device__ constexpr size_t block_scaled_smem_bytes(size_t cols) { return kBsTableBytes + block_scaled_groups(cols) * (20 * 4 + 160 * 4); }
 // CTAs of a launch: 32 rows per CTA at a time, as many CTAs as fit the shared memory of the multiprocessors (all resident: what a
 // multiprocessor has to issue is the sum over its CTAs, and the CTAs that walk one row group more are spread over all of them).
 inline int block_scaled_grid(size_t rows, int sm_count, size_t cols = 0) {

@@ -10,7 +10,8 @@ import quintrit_b200 as q
 
 pytestmark = pytest.mark.gpu
 
-GRID = [(1, 64), (3, 128), (70, 192), (65, 320), (33, 2048), (130, 2560), (17, 640), (9, 704), (66, 1280), (5, 9728), (256, 3072), (96, 23040)]
+GRID = [(1, 64), (3, 128), (70, 192), (65, 320), (33, 2048), (130, 2560), (17, 640), (9, 704), (66, 1280), (5, 9728), (256, 3072), (96, 23040),
+        (9607, 192), (19001, 64), (3, 131072), (40, 49152)]  # more row groups than resident blocks; the widest rows (two ring slots); twelve slots
 
 
 def q2_0_payload(trits: np.ndarray, scales_f16: np.ndarray) -> np.ndarray:
