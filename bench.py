@@ -423,6 +423,38 @@ def run_block_scaled(args, local_rank: int):
     return out
 
 
+def run_block_scaled_decode(args, local_rank: int):
+    """Whole-token decode of a block-scaled (Q2_0) model of the decode shape, loaded from a synthetic GGUF file, at context
+    --prompt; --decode-layers layers (default 4: a launch list needs no more). The two steps between the profiler marks are the
+    ones an ncu launch list with --profile-from-start off sees; the time is read with the decoder's own device timer."""
+    import tempfile
+
+    import torch
+
+    import quintrit_b200 as q
+    from quintrit_b200 import gguf_io, synth
+
+    layers = args.decode_layers or 4
+    ctx = (args.prompt + 256) // 256 * 256
+    with tempfile.TemporaryDirectory() as tmp:
+        path = os.path.join(tmp, "m.gguf")
+        d = gguf_io.write_full_model_gguf(path, args.decode_shape, gguf_io.GGML_Q2_0, torch.device("cuda", local_rank), ctx, layers=layers)
+        torch.cuda.empty_cache()
+        dec = q.Decoder.open(path, context=ctx, device=local_rank)
+    got = dec.generate(synth.prompt_tokens(d["config"], args.prompt - 1, d["vocab"]), 1)
+    torch.cuda.synchronize()
+    torch.cuda.profiler.start()
+    for i in range(2):
+        dec.forward(int(got[-1]), args.prompt - 1 + i, want_logits=False)
+    torch.cuda.synchronize()
+    torch.cuda.profiler.stop()
+    ms = dec.time_token(3, 20)
+    out = {"model": args.decode_shape, "encoding": "q2_0", "layers": layers, "context": args.prompt + 1, "ms_per_token": round(ms, 4),
+           "single_kernel": dec.info()["single_kernel"]}
+    dec.free()
+    return out
+
+
 def run_moe(args, local_rank: int):
     """One mixture-of-experts feed-forward block of the Qwen3-30B-A3B shape (hidden 2048, 128 experts of width 768, top-8 softmax routing,
     BF16 router, ternary experts) for a batch of 16 tokens on one GPU: device time of the block's launches, the time of the C call with host
@@ -921,6 +953,7 @@ def main():
     ap.add_argument("--no-prefill", action="store_true", help="skip the batched-projection (tensor core) leg")
     ap.add_argument("--decode-only", action="store_true", help="run only the whole-token decode leg and print its object (profiling aid)")
     ap.add_argument("--block-scaled-only", action="store_true", help="run only the block-scaled (Q2_0) projection on the model's shapes (profiling aid)")
+    ap.add_argument("--block-scaled-decode", action="store_true", help="run only a whole-token decode of a block-scaled (Q2_0) model of the decode shape (profiling aid)")
     ap.add_argument("--decode-shape", default="falcon3_10b", choices=["falcon3_10b", "bitnet_2b"])
     ap.add_argument("--decode-layers", type=int, default=None, help="fewer layers than the shape has (experiments)")
     ap.add_argument("--moe-only", action="store_true", help="run only the mixture-of-experts block leg and print its object")
@@ -953,6 +986,9 @@ def main():
         return
     if args.block_scaled_only:
         print(json.dumps({"block_scaled": run_block_scaled(args, local_rank)}), flush=True)
+        return
+    if args.block_scaled_decode:
+        print(json.dumps({"block_scaled_decode": run_block_scaled_decode(args, local_rank)}), flush=True)
         return
     if args.moe_only:
         print(json.dumps({"moe": run_moe(args, local_rank)}), flush=True)
