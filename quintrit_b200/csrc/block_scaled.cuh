@@ -180,7 +180,10 @@ inline BsMatrices bs_one_matrix(const uint8_t* planar, const float* w_scales, si
     return m;
 }
 
-__global__ void __launch_bounds__(kBsThreads, 3) gemv_block_scaled_kernel(BsMatrices m, const int8_t* __restrict__ qs, const float* __restrict__ a_scales, size_t cols) {
+// ROOMY: a launch whose CTAs do not fill the multiprocessors three deep anyway (few rows, or long rows whose activations take
+// the shared memory) is compiled without the register ceiling that three resident CTAs need.
+template <bool ROOMY>
+__global__ void __launch_bounds__(kBsThreads, ROOMY ? 1 : 3) gemv_block_scaled_kernel(BsMatrices m, const int8_t* __restrict__ qs, const float* __restrict__ a_scales, size_t cols) {
     extern __shared__ __align__(16) unsigned char bs_smem[];
     uint2* tab = reinterpret_cast<uint2*>(bs_smem);
     const int nact = static_cast<int>(cols / 32), nblocks = (nact + 4) / 5, ngroups = (nblocks + 3) / 4;
@@ -256,6 +259,22 @@ inline int block_scaled_grid(size_t rows, int sm_count, size_t cols = 0) {
     const size_t per_sm = std::max<size_t>(1, std::min<size_t>(3, (227 * 1024) / (block_scaled_smem_bytes(cols) + 1024)));
     const size_t want = (rows + kBsRowsPerCta - 1) / kBsRowsPerCta, cap = static_cast<size_t>(sm_count) * per_sm;
     return static_cast<int>(want < cap ? want : cap);
+}
+
+// Lets both forms of the kernel use the shared memory of a multiprocessor.
+inline cudaError_t block_scaled_allow_smem() {
+    const int most = static_cast<int>(block_scaled_smem_bytes(131072));
+    cudaError_t e = cudaFuncSetAttribute(gemv_block_scaled_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, most);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemv_block_scaled_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, most);
+    return e;
+}
+// The launch for the matrices of `m` (all of `cols` columns, over the activation blocks qs / a_scales).
+inline void block_scaled_launch(const BsMatrices& m, const int8_t* qs, const float* a_scales, size_t cols, int sm_count, cudaStream_t stream) {
+    const int grid = block_scaled_grid(static_cast<size_t>(m.group_end[2]) * kBsRowsPerCta, sm_count, cols);
+    if (grid <= 2 * sm_count)
+        gemv_block_scaled_kernel<true><<<grid, kBsThreads, block_scaled_smem_bytes(cols), stream>>>(m, qs, a_scales, cols);
+    else
+        gemv_block_scaled_kernel<false><<<grid, kBsThreads, block_scaled_smem_bytes(cols), stream>>>(m, qs, a_scales, cols);
 }
 
 }  // namespace qtb

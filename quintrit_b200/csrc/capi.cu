@@ -415,8 +415,7 @@ extern "C" int quintrit_b200_matrix_upload(uint32_t device_index, int32_t source
                 destroy_matrix(m);
                 return fail(QUINTRIT_ERR_FORMAT, "Q2_0 weight %llu uses code 3 (+2), which is not ternary", bad);
             }
-            QTB_CUDA(cudaFuncSetAttribute(gemv_block_scaled_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          static_cast<int>(block_scaled_smem_bytes(131072))));
+            QTB_CUDA(block_scaled_allow_smem());
             *out_matrix = m;
             return ok();
         }
@@ -573,8 +572,7 @@ int check_block_scaled(const quintrit_b200_matrix* m) {
     return QUINTRIT_OK;
 }
 int launch_block_scaled(const quintrit_b200_matrix* m) {
-    const int grid = block_scaled_grid(m->rows, m->sm_count, m->cols);
-    gemv_block_scaled_kernel<<<grid, kBsThreads, block_scaled_smem_bytes(m->cols)>>>(bs_one_matrix(m->d_planar, m->d_wscales, m->rows, m->d_outf), m->d_act, m->d_as, m->cols);
+    block_scaled_launch(bs_one_matrix(m->d_planar, m->d_wscales, m->rows, m->d_outf), m->d_act, m->d_as, m->cols, m->sm_count, nullptr);
     ++g_launches;
     QTB_CUDA(cudaGetLastError());
     return QUINTRIT_OK;
@@ -1035,7 +1033,7 @@ int decoder_create_impl(const quintrit_b200_decoder_desc_t* desc, quintrit_b200_
 
     if ((rc = dev_alloc(d, &d->q8_d, std::max<size_t>({H, I, qd}) / 32 + 1)) != QUINTRIT_OK) return rc;
     if (block_scaled) {  // no work items: the block-scaled projections are plain launches; one kernel per step
-        QTB_CUDA(cudaFuncSetAttribute(gemv_block_scaled_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(block_scaled_smem_bytes(131072))));
+        QTB_CUDA(block_scaled_allow_smem());
         const int big_bs = static_cast<int>(std::max<size_t>({H, I, qd}) * sizeof(float));
         QTB_CUDA(cudaFuncSetAttribute(norm_quant_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, big_bs));
         QTB_CUDA(cudaFuncSetAttribute(attn_finish_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, big_bs));

@@ -157,8 +157,7 @@ inline int decoder_gemv_bs(quintrit_b200_decoder* d, int layer, int first, const
         bm.group_end[i] = groups;
     }
     bm.count = count;
-    const int grid = block_scaled_grid(static_cast<size_t>(groups) * kBsRowsPerCta, d->sm_count, m0->cols);
-    gemv_block_scaled_kernel<<<grid, kBsThreads, block_scaled_smem_bytes(m0->cols), d->stream>>>(bm, codes, d->q8_d, m0->cols);
+    block_scaled_launch(bm, codes, d->q8_d, m0->cols, d->sm_count, d->stream);
     ++g_launches;
     const cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "block-scaled GEMV launch");
