@@ -57,6 +57,28 @@ def test_defaults_tied_head_and_numerics(tmp_path):
     assert d["num_kv_heads"] == "8" and d["head_dim"] == "64"
 
 
+def test_qwen_files_name_their_architecture_and_carry_head_norms(tmp_path):
+    """general.architecture "qwen2" / "qwen3" (config.rs:278-279, 464-467): read like any other file; a qwen3 file holds
+    blk.N.attn_q_norm / attn_k_norm of head_dim values (validate.rs:250-251), which the CPU oracle's reader hands on."""
+    from oracle import gguf_model
+
+    spec, trits = _tiny(arch=2)
+    rng = np.random.default_rng(8)
+    spec["qk_norms"] = [rng.uniform(0.5, 1.5, 64).astype(np.float32) for _ in range(4)]
+    path = tmp_path / "qwen3.gguf"
+    gguf_io.write_model_gguf(path, spec, trits, gguf_io.GGML_I2_S, architecture="qwen3")
+    d = q.gguf_describe(path)
+    assert d["architecture"] == "qwen3" and int(d["head_dim"]) == 64
+    by_name = {t["name"]: t for t in d["tensors"]}
+    assert by_name["blk.1.attn_k_norm.weight"]["shape"] == (64,) and by_name["blk.0.attn_q_norm.weight"]["type"] == 0
+    got = gguf_model.model_spec(path)
+    assert got["arch"] == 2 and all(np.array_equal(a, b) for a, b in zip(got["qk_norms"], spec["qk_norms"]))
+    plain = tmp_path / "qwen2.gguf"
+    gguf_io.write_model_gguf(plain, {k: v for k, v in spec.items() if k != "qk_norms"}, trits, gguf_io.GGML_I2_S, architecture="qwen2")
+    got = gguf_model.model_spec(plain)
+    assert got["arch"] == 2 and "qk_norms" not in got and q.gguf_describe(plain)["architecture"] == "qwen2"
+
+
 def test_error_classes(tmp_path):
     def code(path):
         with pytest.raises(q.QuintritError) as e:

@@ -38,6 +38,21 @@ def test_chunked_ingestion_equals_single_steps(arch, f32_values, n):
     assert np.array_equal(got.view(np.uint32), r.view(np.uint32))
 
 
+@pytest.mark.parametrize("heads,kv_heads,off", [(8, 1, False), (4, 2, True)])
+def test_chunks_with_one_query_head_per_attention_block(monkeypatch, heads, kv_heads, off):
+    """Where no attention kernel for the whole group of query heads exists (eight heads per KV head) or it is switched off, the
+    kernel with one query head per block serves the tokens of a chunk, each at its own position."""
+    if off:
+        monkeypatch.setenv("QUINTRIT_B200_ATTN_GQA_OFF", "1")
+    spec = synth.make_model(q.ARCH_LLAMA, False, 256, 512, 2, heads, kv_heads, 64, 300, 1024, 500000.0, 1e-5, config=41 + heads, random_norms=True)
+    tokens = synth.prompt_tokens(7, 600, spec["vocab"])  # past 512 positions: all four KV chunks in use
+    a, b = q.Decoder(spec), q.Decoder(spec)
+    for pos, t in enumerate(tokens):
+        want, want_next = a.forward(int(t), pos, want_logits=pos == len(tokens) - 1)
+    got, got_next = b.prefill(tokens)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32)) and got_next == want_next
+
+
 def test_ingestion_in_two_calls_and_after_decoding():
     spec = _spec(q.ARCH_LLAMA, False, 77)
     tokens = synth.prompt_tokens(5, 90, spec["vocab"])
