@@ -192,6 +192,22 @@ __global__ void __launch_bounds__(kBsThreads, ROOMY ? 1 : 3) gemv_block_scaled_k
     // five 16-byte loads, the eight lanes of a row from eight different bank groups. Zeros past the end of the row.
     float* s_as = reinterpret_cast<float*>(bs_smem + kBsTableBytes);  // ngroups * 20 floats
     int* s_q4 = reinterpret_cast<int*>(s_as + ngroups * 20);         // ngroups * 8 * 20 words
+    {   // The first row group's planar rows and scales (two contiguous ranges) are requested into L2 as a whole while the table is built.
+        const unsigned grp = blockIdx.x;
+        if (grp < m.group_end[2]) {
+            const int which = grp < m.group_end[0] ? 0 : (grp < m.group_end[1] ? 1 : 2);
+            const unsigned grp0 = which == 0 ? 0u : (which == 1 ? m.group_end[0] : m.group_end[1]);
+            const size_t rows = which == 0 ? m.rows[0] : (which == 1 ? m.rows[1] : m.rows[2]);
+            const size_t r0 = static_cast<size_t>(grp - grp0) * kBsRowsPerCta, nr = min(static_cast<size_t>(kBsRowsPerCta), rows - r0);
+            const size_t row_bytes = static_cast<size_t>(nblocks) * 32, scale_bytes = (cols / 64) * 4;
+            const char* pw = reinterpret_cast<const char*>(which == 0 ? m.planar[0] : (which == 1 ? m.planar[1] : m.planar[2])) + r0 * row_bytes;
+            const char* ps = reinterpret_cast<const char*>(which == 0 ? m.w_scales[0] : (which == 1 ? m.w_scales[1] : m.w_scales[2])) + r0 * scale_bytes;
+            for (size_t off = static_cast<size_t>(threadIdx.x) * 128; off < nr * row_bytes; off += static_cast<size_t>(kBsThreads) * 128)
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(pw + off));
+            for (size_t off = static_cast<size_t>(threadIdx.x) * 128; off < nr * scale_bytes; off += static_cast<size_t>(kBsThreads) * 128)
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(ps + off));
+        }
+    }
     build_trit_table(tab);
     for (int i = threadIdx.x; i < ngroups * 20; i += kBsThreads) s_as[i] = i < nact ? a_scales[i] : 0.0f;
     for (int i = threadIdx.x; i < ngroups * 160; i += kBsThreads) {

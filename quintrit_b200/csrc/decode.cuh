@@ -246,6 +246,9 @@ __global__ void __launch_bounds__(kRowThreads) norm_quant_kernel(NormQuantArgs a
         post = s > 0.0f ? __fdiv_rn(a.ws_prev, s) : 0.0f;
         if (!(s > 0.0f)) has_prev = false;  // layer.rs:148-150: a zero activation scale gives a zero projection
     }
+    float w_early[4];  // the norm weights of this thread's first four elements, requested before the sum instead of after it
+#pragma unroll
+    for (int k = 0; k < 4; ++k) w_early[k] = tid + k * kRowThreads < a.n ? a.norm_w[tid + k * kRowThreads] : 0.0f;
     double sum = 0.0;
     for (int i = tid; i < a.n; i += kRowThreads) {
         float v = a.x[i];
@@ -262,7 +265,16 @@ __global__ void __launch_bounds__(kRowThreads) norm_quant_kernel(NormQuantArgs a
     const float mean = __double2float_rn(sum / static_cast<double>(a.n));
     const float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, a.eps)));
     float amax = 0.0f;
-    for (int i = tid; i < a.n; i += kRowThreads) {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int i = tid + k * kRowThreads;
+        if (i < a.n) {
+            const float y = __fmul_rn(__fmul_rn(y_s[i], inv), w_early[k]);
+            y_s[i] = y;
+            amax = fmaxf(amax, fabsf(y));
+        }
+    }
+    for (int i = tid + 4 * kRowThreads; i < a.n; i += kRowThreads) {
         const float y = __fmul_rn(__fmul_rn(y_s[i], inv), a.norm_w[i]);
         y_s[i] = y;
         amax = fmaxf(amax, fabsf(y));
