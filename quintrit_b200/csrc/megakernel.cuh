@@ -2038,7 +2038,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const __g
 // whose two barriers both reported the failure. Nothing faults and nothing spins beyond the limit.
 __global__ void barrier_selftest_kernel(unsigned int* bar, unsigned int* status, unsigned int spin_limit, unsigned int* out) {
     __shared__ int s_flag;
-    const bool first = grid_barrier(bar, 2u, status, &s_flag, spin_limit);   // round 2 at the first barrier: twice the arrivals there are
+    const bool first = grid_barrier(bar, 2u, status, &s_flag, spin_limit);   // the first barrier asks for twice the arrivals there are
     const bool second = grid_barrier(bar, 4u, status, &s_flag, spin_limit);
     if (threadIdx.x == 0) out[blockIdx.x] = (!first && !second) ? 1u : 0u;
 }
