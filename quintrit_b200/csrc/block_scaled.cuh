@@ -243,18 +243,23 @@ __global__ void __launch_bounds__(kBsThreads, ROOMY ? 1 : 3) gemv_block_scaled_k
         };
         fetch(0, n1, a1, b1);
         fetch(1, n2, a2, b2);
-        for (int g = 0; g < ngroups; ++g) {
+        // Two groups per turn, the two register sets taking turns: a set is copied out only once its own loads (two groups old)
+        // are back, and never waits for the other set's younger ones. (Four sets, four groups ahead, measured slower.)
+        auto step = [&](int g, uint32_t (&nw)[4], float& sa, float& sb2) {
             uint32_t w[4];
 #pragma unroll
-            for (int bi = 0; bi < 4; ++bi) w[bi] = n1[bi], n1[bi] = n2[bi];
-            const float wa = a1, wb = b1;
-            a1 = a2, b1 = b2;
-            fetch(g + 2, n2, a2, b2);
+            for (int bi = 0; bi < 4; ++bi) w[bi] = nw[bi];
+            const float wa = sa, wb = sb2;
+            fetch(g + 2, nw, sa, sb2);
             const int s0 = g * 20;
             if (s0 + 20 <= nact)
                 bs_group<true>(w, tab_lane_addr, reinterpret_cast<const int4*>(s_q4) + (g * 8 + j) * 5, reinterpret_cast<const float4*>(s_as) + g * 5, wa, wb, s0, nact, acc0, acc1);
             else
                 bs_group<false>(w, tab_lane_addr, reinterpret_cast<const int4*>(s_q4) + (g * 8 + j) * 5, reinterpret_cast<const float4*>(s_as) + g * 5, wa, wb, s0, nact, acc0, acc1);
+        };
+        for (int g = 0; g < ngroups; g += 2) {
+            step(g, n1, a1, b1);
+            if (g + 1 < ngroups) step(g + 1, n2, a2, b2);
         }
         float l = __fadd_rn(acc0, acc1);
         const float up4 = __shfl_down_sync(0xffffffffu, l, 4, 8);
