@@ -182,3 +182,30 @@ def test_vec_dot_bf16_follows_the_documented_order(oracle):
         assert oracle.vec_dot_bf16(x, y).view(np.uint32) == want.view(np.uint32), n
     ones = np.full(64, 0x3F80, np.uint16)
     assert oracle.vec_dot_bf16(ones, ones) == np.float32(64.0)
+
+
+def test_head_norms_reach_the_queries_and_keys_of_their_layer(oracle):
+    """Query/key-norm (attention.rs:282-294): the query heads take the layer's first weight vector, the key heads the second.
+    Halving the query weights and doubling the key weights (powers of two: exact through the norm, RoPE, the F16 key cache
+    and every product of a score) leaves each score and so the logits bit for bit; giving the keys the queries' weights, or
+    a layer the other layer's, does not."""
+    from quintrit_b200 import synth
+
+    spec = synth.make_model(2, True, 128, 256, 2, 4, 2, 32, 200, 64, 10000.0, 1e-6, config=17, random_norms=True)
+    shapes = [(128, 128), (64, 128), (64, 128), (128, 128), (256, 128), (256, 128), (128, 256)]
+    rng = np.random.default_rng(17)
+    spec["block_scales"] = [rng.uniform(0.5, 2.0, r * c // 64).astype(np.float16).astype(np.float32) for _ in range(2) for r, c in shapes]
+    w = [rng.uniform(0.5, 1.5, 32).astype(np.float32) for _ in range(4)]
+    tokens = synth.prompt_tokens(2, 9, 200)
+
+    def logits(head_norms):
+        m = oracle.Model(dict(spec, qk_norms=head_norms))
+        return [m.forward(int(t), p).copy() for p, t in enumerate(tokens)]
+
+    base = logits(w)
+    traded = logits([w[0] * np.float32(0.5), w[1] * np.float32(2.0), w[2] * np.float32(4.0), w[3] * np.float32(0.25)])
+    assert all(np.array_equal(a.view(np.uint32), b.view(np.uint32)) for a, b in zip(base, traded))
+    swapped_roles = logits([w[1], w[0], w[2], w[3]])
+    swapped_layers = logits([w[2], w[3], w[0], w[1]])
+    assert not np.array_equal(base[-1], swapped_roles[-1]) and not np.array_equal(base[-1], swapped_layers[-1])
+    assert np.array_equal(base[0], swapped_roles[0])  # one position: the only key has weight 1 whatever its score
