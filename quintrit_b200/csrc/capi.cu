@@ -1354,6 +1354,7 @@ int read_shape(const GgufFile& g, GgufModelShape* out) {
     const GgufTensor* embd = g.tensor("token_embd.weight");
     uint64_t vocab_fallback = 128256;
     if (embd != nullptr && embd->shape.size() >= 2) vocab_fallback = embd->shape[1];
+    else if (const GgufValue* toks = g.find("tokenizer.ggml.tokens"); toks != nullptr && toks->type == 9) vocab_fallback = toks->count;  // config.rs:293-304
     m.vocab = meta_usize(g, a + ".vocab_size", vocab_fallback);
     m.hidden = meta_usize(g, a + ".embedding_length", 2560);
     m.inter = meta_usize(g, a + ".feed_forward_length", 6912, true);

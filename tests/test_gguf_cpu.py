@@ -49,6 +49,10 @@ def test_defaults_tied_head_and_numerics(tmp_path):
     d = q.gguf_describe(bare)
     assert [int(d[k]) for k in ("vocab_size", "hidden_size", "intermediate_size", "num_layers", "num_heads", "num_kv_heads", "head_dim",
                                 "context_length")] == [128256, 2560, 6912, 30, 20, 5, 128, 4096]
+    # without <arch>.vocab_size and without an embedding the tokenizer's token list gives the vocabulary (config.rs:293-304)
+    toks = tmp_path / "toks.gguf"
+    gguf_io.write_gguf(toks, {"general.architecture": "qwen2", "tokenizer.ggml.tokens": [f"t{i}" for i in range(77)]}, [])
+    assert q.gguf_describe(toks)["vocab_size"] == "77"
     # per-layer arrays give their maximum (config.rs:502-512)
     arr = tmp_path / "arr.gguf"
     gguf_io.write_gguf(arr, {"general.architecture": "llama", "llama.attention.head_count_kv": [2, 8, 4], "llama.embedding_length": 512,
